@@ -1,0 +1,350 @@
+#!/usr/bin/env python
+"""Benchmark of the EXL3 decode hot path on B200.
+
+Workload (BASELINE configuration 1): the dense 27B-shaped decode stack at 4 bpw -- MLP
+gate/up 5120->17408 (fp16 out), silu*up, down 17408->5120 (fp32 out), and the attention
+projections q 5120->6144, k/v 5120->1024, o 6144->5120 -- for a batch of M fp16 token rows.
+One "step" is one pass over one layer's seven trellis matrices; LAYERS distinct seeded layers
+(> L2 in total) are cycled so that no step finds its weights in L2.
+
+Metric: effective HBM GB/s on the algorithmic bytes of the pass (trellis + sign-scale vectors
++ activations in/out), value = bytes moved by all ranks / device time (CUDA events, max over
+ranks).  `e2e` is the same metric through the host-buffer API: pinned host activations are
+copied in and the results read back every step.  `roofline` is measured live for the dominant
+kernel (the gate/up GEMV).  `cpu_baseline` times the CPU oracle on a bounded sample.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--m M] [--impl reference]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HIDDEN, INTER, QDIM, KVDIM = 5120, 17408, 6144, 1024
+BITS, CB = 4, 2
+# (name, K, N, fp32 out, input)
+SHAPES = [("gate", HIDDEN, INTER, 0, "x"), ("up", HIDDEN, INTER, 0, "x"), ("down", INTER, HIDDEN, 1, "act"),
+          ("q", HIDDEN, QDIM, 0, "xa"), ("k", HIDDEN, KVDIM, 0, "xa"), ("v", HIDDEN, KVDIM, 0, "xa"),
+          ("o", QDIM, HIDDEN, 1, "attn")]
+LAYERS = 4
+METRIC = "exl3_gemv_eff_hbm_gbs"
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_exl3_gemv launch on the gate shape
+# (5120x17408, 4 bpw, m=1), from the ncu capture summarised under profiles/.  None until captured.
+NCU_TRAFFIC_GATE_BYTES = None
+
+
+def linear_bytes(k: int, n: int, m: int, fp32: int, bits: int = BITS) -> int:
+    """Algorithmic bytes of one linear: trellis + suh + svh + x in + y out."""
+    return k * n * bits // 8 + 2 * k + 2 * n + 2 * m * k + (4 if fp32 else 2) * m * n
+
+
+def step_bytes(m: int) -> int:
+    return sum(linear_bytes(k, n, m, f) for _, k, n, f, _ in SHAPES)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------ clocks
+
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------ the workload on the GPU
+
+class DecodeStack:
+    """LAYERS layers of the seven 27B-shaped EXL3 linears, resident in HBM, with the host-side
+    callers of berth_b200.engine (Exl3Linear / MlpLayer)."""
+
+    def __init__(self, m: int, rank: int):
+        import torch
+        from berth_b200 import synth
+        from berth_b200.engine import Exl3Linear, Gpu, MlpLayer
+        from berth_b200.kernels import Codebook
+        self.torch = torch
+        self.m = m
+        self.gpu = Gpu(torch.cuda.current_device())
+        self.layers = []
+        for l in range(LAYERS):
+            lin = {}
+            for name, k, n, _, _ in SHAPES:
+                w = synth.linear_weights(synth.MASTER_SEED, f"r{rank}.layers.{l}.{name}", k, n, BITS)
+                lin[name] = Exl3Linear(self.gpu, f"layers.{l}.{name}", w["trellis"], w["suh"], w["svh"], BITS,
+                                       Codebook(CB), max_rows=m)
+            mlp = MlpLayer(self.gpu, lin["gate"], lin["up"], lin["down"], max_rows=m)
+            self.layers.append((mlp, lin))
+        dev = self.gpu.device
+        f16, f32 = torch.float16, torch.float32
+        # host inputs (pinned) and device activations
+        self.h_x = torch.from_numpy(synth.activations(1234, f"r{rank}.x", m, HIDDEN)).pin_memory()
+        self.h_xa = torch.from_numpy(synth.activations(1234, f"r{rank}.xa", m, HIDDEN)).pin_memory()
+        self.h_attn = torch.from_numpy(synth.activations(1234, f"r{rank}.attn", m, QDIM)).pin_memory()
+        self.x = self.h_x.to(dev); self.xa = self.h_xa.to(dev); self.attn = self.h_attn.to(dev)
+        self.mlp_out = torch.empty((m, HIDDEN), dtype=f32, device=dev)
+        self.q = torch.empty((m, QDIM), dtype=f16, device=dev)
+        self.k = torch.empty((m, KVDIM), dtype=f16, device=dev)
+        self.v = torch.empty((m, KVDIM), dtype=f16, device=dev)
+        self.o = torch.empty((m, HIDDEN), dtype=f32, device=dev)
+        self.h_mlp_out = torch.empty((m, HIDDEN), dtype=f32).pin_memory()
+        self.h_q = torch.empty((m, QDIM), dtype=f16).pin_memory()
+        self.h_k = torch.empty((m, KVDIM), dtype=f16).pin_memory()
+        self.h_v = torch.empty((m, KVDIM), dtype=f16).pin_memory()
+        self.h_o = torch.empty((m, HIDDEN), dtype=f32).pin_memory()
+        self.h2d_bytes = 2 * m * (HIDDEN + HIDDEN + QDIM)
+        self.d2h_bytes = m * (4 * HIDDEN + 2 * QDIM + 4 * KVDIM + 4 * HIDDEN)
+        self.launches_per_step = 8   # 7 x k_exl3_gemv + 1 x k_silu_mul
+
+    def step(self, i: int) -> None:
+        from berth_b200.kernels import OutDtype
+        mlp, lin = self.layers[i % LAYERS]
+        g, m = self.gpu, self.m
+        mlp.forward_n(g, m, self.x, self.mlp_out)
+        lin["q"].forward_n(g, m, self.xa, self.q, OutDtype.F16)
+        lin["k"].forward_n(g, m, self.xa, self.k, OutDtype.F16)
+        lin["v"].forward_n(g, m, self.xa, self.v, OutDtype.F16)
+        lin["o"].forward_n(g, m, self.attn, self.o, OutDtype.F32)
+
+    def step_e2e(self, i: int) -> None:
+        """Host buffers in, host buffers out: what a caller without device residency pays."""
+        self.x.copy_(self.h_x, non_blocking=True)
+        self.xa.copy_(self.h_xa, non_blocking=True)
+        self.attn.copy_(self.h_attn, non_blocking=True)
+        self.step(i)
+        self.h_mlp_out.copy_(self.mlp_out, non_blocking=True)
+        self.h_q.copy_(self.q, non_blocking=True)
+        self.h_k.copy_(self.k, non_blocking=True)
+        self.h_v.copy_(self.v, non_blocking=True)
+        self.h_o.copy_(self.o, non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+
+    def time_gate_kernel(self, reps: int) -> float:
+        """Average duration (ms) of one k_exl3_gemv launch on the gate/up shape: 2*LAYERS distinct
+        44.6 MB matrices (357 MB > L2) launched back to back between two CUDA events."""
+        torch = self.torch
+        from berth_b200.kernels import OutDtype
+        mats = [l[1][n] for l in self.layers for n in ("gate", "up")]
+        out = self.layers[0][0].gate_out
+        for lin in mats:
+            lin.forward_n(self.gpu, self.m, self.x, out, OutDtype.F16)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            for lin in mats:
+                lin.forward_n(self.gpu, self.m, self.x, out, OutDtype.F16)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (reps * len(mats))
+
+
+# ------------------------------------------------------------------ CPU arm
+
+def cpu_pass(m: int, passes: int):
+    """The CPU oracle (a restatement of the path; berth ships no CPU implementation) on `passes`
+    full seven-matrix passes.  Returns (GB/s, seconds, threads)."""
+    from berth_b200 import synth
+    from oracle import exl3_oracle as orc
+    orc.build()
+    ws = {name: synth.linear_weights(synth.MASTER_SEED, f"cpu.{name}", k, n, BITS) for name, k, n, _, _ in SHAPES}
+    x = {"x": synth.activations(1234, "cpu.x", m, HIDDEN), "xa": synth.activations(1234, "cpu.xa", m, HIDDEN),
+         "attn": synth.activations(1234, "cpu.attn", m, QDIM)}
+    t0 = time.perf_counter()
+    for _ in range(passes):
+        g, _ = orc.linear(x["x"], ws["gate"]["trellis"], ws["gate"]["suh"], ws["gate"]["svh"], HIDDEN, INTER, BITS, CB, False)
+        u, _ = orc.linear(x["x"], ws["up"]["trellis"], ws["up"]["suh"], ws["up"]["svh"], HIDDEN, INTER, BITS, CB, False)
+        act = orc.silu_mul(g, u)
+        orc.linear(act, ws["down"]["trellis"], ws["down"]["suh"], ws["down"]["svh"], INTER, HIDDEN, BITS, CB, True)
+        for name, k, n, f, src in SHAPES[3:]:
+            orc.linear(x[src], ws[name]["trellis"], ws[name]["suh"], ws[name]["svh"], k, n, BITS, CB, bool(f))
+    dt = time.perf_counter() - t0
+    return step_bytes(m) * passes / dt / 1e9, dt, orc.num_threads()
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    m = args.m
+    for _ in range(min(args.warmup, 1)):
+        cpu_pass(m, 1)
+    gbs, dt, threads = cpu_pass(m, args.steps)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16 x trellis-u16, fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": "c1_dense_27b_decode_stack_4bpw", "m": m, "bits": BITS, "codebook": "mul1",
+                   "bytes_per_step": step_bytes(m)},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"{args.steps} full seven-matrix passes at m={m} (berth has no CPU path; "
+                                   "this is the repo's CPU oracle, OpenMP)"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ main
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--m", type=int, default=1, help="token rows per step (1, 8 or 32 in configuration 1)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if args.steps > 10:
+            args.steps = 3
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU: berth_b200 has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    warmup = max(args.warmup, 3)
+
+    stack = DecodeStack(args.m, rank)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing
+    for i in range(warmup):
+        stack.step(i)
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        stack.step(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    # ---- end to end with host buffers
+    for i in range(3):
+        stack.step_e2e(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        stack.step_e2e(i)
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    # ---- dominant kernel alone
+    gate_ms = stack.time_gate_kernel(max(4, args.steps // 8))
+    clocks = sampler.stop() if rank == 0 else None
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+
+    if rank == 0:
+        sb = step_bytes(args.m)
+        value = sb * args.steps * world / (ms * 1e-3) / 1e9
+        e2e = sb * args.steps * world / (e2e_ms * 1e-3) / 1e9
+        peak, peak_kind = peaks()
+        gate_bytes = linear_bytes(HIDDEN, INTER, args.m, 0)
+        achieved = gate_bytes / (gate_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp16 x trellis-u16, fp32 accumulate", "data": "synthetic",
+            "config": {"workload": "c1_dense_27b_decode_stack_4bpw", "m": args.m, "bits": BITS, "codebook": "mul1",
+                       "bytes_per_step": sb, "layers_cycled": LAYERS,
+                       "l2": f"{LAYERS} distinct layers ({LAYERS * sb / 1e6:.0f} MB) cycled; inputs larger than L2",
+                       "parallelism": "replicas" if world > 1 else "single"},
+            "frac_of_hbm_peak": value / world / peak, "peak_kind": peak_kind,
+            "tokens_per_s": args.m * args.steps * world / (ms * 1e-3),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": NCU_TRAFFIC_GATE_BYTES, "kernel": "k_exl3_gemv<4,2,mg>",
+                         "launch": f"gate/up 5120x17408 m={args.m}: {gate_bytes} algorithmic bytes in {gate_ms * 1e3:.2f} us",
+                         "peak_kind": f"of {peak_kind}"},
+            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": stack.h2d_bytes,
+                    "d2h_bytes_per_step": stack.d2h_bytes, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": stack.launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            gbs, dt, threads = cpu_pass(args.m, 2)
+            line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                                    "sample": f"2 full seven-matrix passes at m={args.m}, {dt:.1f} s "
+                                              "(the repo's CPU oracle; berth ships no CPU path)"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

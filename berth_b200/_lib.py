@@ -1,0 +1,72 @@
+"""Loads ``libberth_b200.so`` and declares the C ABI of ``include/berth_b200.h``."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+SO_PATH = os.path.join(_HERE, "libberth_b200.so")
+CSRC = os.path.join(_HERE, "csrc")
+
+_vp, _i, _i64, _f, _u64 = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_uint64
+_ip = C.POINTER(C.c_int)
+
+
+class MoeWeights(C.Structure):
+    """``berth_moe_weights`` of include/berth_b200.h."""
+    _fields_ = [(n, _i) for n in ("hidden", "inter", "shared_inter", "n_experts", "top_k", "k_bits", "codebook")] + [
+        (n, _vp) for n in (
+            "w_router", "router_bias", "gate_trellis", "up_trellis", "down_trellis",
+            "gate_suh", "gate_svh", "up_suh", "up_svh", "down_suh", "down_svh",
+            "sh_gate_trellis", "sh_up_trellis", "sh_down_trellis",
+            "sh_gate_suh", "sh_gate_svh", "sh_up_suh", "sh_up_svh", "sh_down_suh", "sh_down_svh")]
+
+
+# name -> (restype, argtypes); every symbol the header declares.
+SIGNATURES = {
+    "berth_exl3_linear": (_i, [_vp] * 6 + [_i] * 6 + [_vp]),
+    "berth_exl3_last_error": (C.c_char_p, []),
+    "berth_exl3_last_launch": (C.c_char_p, []),
+    "berth_device_cc": (_i, [_i]),
+    "berth_device_sms": (_i, [_i]),
+    "berth_exl3_gemm_tune_key": (_u64, [_i] * 9),
+    "berth_exl3_smoke_int8": (_i, [_i]),
+    "berth_exl3_smoke_gemm": (_i, []),
+    "berth_prefill_exl3_linear": (_i, [_vp] * 7 + [_i] * 6 + [_vp]),
+    "berth_prefill_last_error": (C.c_char_p, []),
+    "berth_prefill_last_launch": (C.c_char_p, []),
+    "berth_exl3_gemv_cfg": (_i, [_i] * 8),
+    "berth_prefill_reconstruct": (_i, [_vp, _vp] + [_i] * 6 + [_vp]),
+    "berth_prefill_had_r_128": (_i, [_vp] * 3 + [_i] * 4 + [_vp]),
+    "berth_ops_silu_mul": (_i, [_vp] * 3 + [_i64, _f, _vp]),
+    "berth_ops_add_f32": (_i, [_vp] * 3 + [_i, _vp]),
+    "berth_ops_last_error": (C.c_char_p, []),
+    "berth_ops_last_launch": (C.c_char_p, []),
+}
+
+_lib = None
+
+
+def build(verbose: bool = False) -> str:
+    """Compile the CUDA library in-tree with the Makefile under csrc/ (nvcc, sm_100a)."""
+    out = None if verbose else subprocess.DEVNULL
+    subprocess.run(["make", "-C", CSRC, "-j8"], check=True, stdout=out)
+    return SO_PATH
+
+
+def lib() -> C.CDLL:
+    """The loaded library.  Raises if it has not been built: there is no fallback."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(SO_PATH):
+            raise RuntimeError(
+                f"{SO_PATH} is missing: build it with `make -C {CSRC}` (or __graft_entry__.build()); "
+                "berth_b200 has no CPU or PyTorch fallback")
+        l = C.CDLL(SO_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(l, name)   # AttributeError here = header and library disagree
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib

@@ -1,0 +1,77 @@
+// Shared host/device helpers of libberth_b200: error convention of the C boundary, per-device
+// state, small fp16 utilities.  sm_100a only.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ < 1000)
+#error "libberth_b200 is written for sm_100a (B200) only"
+#endif
+
+namespace berth {
+
+// Host-side CUDA check: the message goes back through the C ABI, nothing aborts
+// (same convention as crates/berth-kernels/csrc/check.cuh:8-14 of berth).
+inline void cuda_ok(cudaError_t err, const char* what)
+{
+    if (err == cudaSuccess) return;
+    throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(err));
+}
+
+// One family of entry points = one pair of thread-local strings (last error / last launch).
+struct CallState {
+    std::string err;
+    std::string launch;
+    void clear() { err.clear(); launch.clear(); }
+};
+CallState& exl3_state();     // berth_exl3_*
+CallState& prefill_state();  // berth_prefill_*
+CallState& ops_state();      // berth_ops_*
+CallState& moe_state();      // berth_moe_*
+
+// Runs `fn`, turning any exception into rc -1 + message, clearing the sticky CUDA error the
+// way crates/berth-kernels/csrc/linear.cu:377-394 does.
+template <typename F>
+inline int guarded(CallState& st, F&& fn)
+{
+    try {
+        st.clear();
+        fn();
+        return 0;
+    } catch (const std::exception& e) {
+        st.err = e.what();
+        st.launch.clear();
+        cudaGetLastError();
+        return -1;
+    }
+}
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceInfo {
+    int sms = 0;
+    int cc = 0;       // 1 old, 2 Ampere, 3 Ada, 4 Hopper, 5 Blackwell
+    int major = 0;
+};
+const DeviceInfo& device_info(int device);
+int current_device();
+
+// Split-K workspace of the decode GEMV: fp32 partial sums + one arrival counter per 128-column
+// band.  Allocated once per device at first use, never grown, never freed
+// (cf. crates/berth-kernels/csrc/int8_sq.cu:20-47).
+constexpr size_t kGemvWorkspaceBytes = size_t(32) << 20;
+constexpr int kGemvMaxBands = 1 << 16;
+struct GemvWorkspace {
+    float* partial = nullptr;
+    unsigned* counters = nullptr;
+};
+GemvWorkspace gemv_workspace(int device);
+
+constexpr float kRScale = 0.088388347648f;  // 1/sqrt(128), csrc/prefill_lin/reconstruct.cu:43-44
+
+}  // namespace berth

@@ -1,0 +1,180 @@
+// Device-side EXL3 decode primitives: trellis window extraction, the three procedural
+// codebooks, the 128-wide Hadamard butterfly on a warp, and the m16n8k16 MMA wrapper.
+//
+// Format (the checker in oracle/exl3_oracle.c states the same rules on the CPU):
+//   * a 16x16 tile is 16*BITS uint16 words read most-significant-bit first as one cyclic
+//     stream of 256*BITS bits; weight t (0..255) is decoded from the 16-bit window that starts
+//     at stream bit t*BITS (tail-biting: positions wrap);
+//   * weight t = 8*lane + j sits at col = (lane>>2) + 8*((j>>1)&1),
+//     row = 2*(lane&3) + (j&1) + 8*(j>>2): the eight weights of a lane are the four fp16 pairs
+//     of an m16n8k16 A fragment of the transposed tile (row index = weight column);
+//   * codebook 0 (3INST): x = s*89226354 + 64248484; x = (x & 0x8fff8fff) ^ 0x3b603b60;
+//     w = half(x.lo) + half(x.hi);  codebook 1 (MCG): x = s*0xCBAC1FED, same tail;
+//     codebook 2 (MUL1): x = s*0x83DCD12D, u = byte sum of x, w = fma(half(u), S, B) in fp16.
+#pragma once
+
+#include "common.cuh"
+
+namespace berth {
+namespace dq {
+
+constexpr unsigned kFull = 0xffffffffu;
+constexpr unsigned short kMul1S = 0x1EEE;  // 1/147.8
+constexpr unsigned short kMul1B = 0xC2E7;  // -510/147.8
+
+__device__ __forceinline__ uint32_t lop3_mask_xor(uint32_t x)
+{
+    asm("lop3.b32 %0, %0, 0x8fff8fff, 0x3b603b60, 0x6a;" : "+r"(x));
+    return x;
+}
+
+// The 32-bit word of codebooks 0 and 1 after multiply(+add) and mask/xor: two fp16 halves whose
+// sum is the weight.
+template <int CB>
+__device__ __forceinline__ uint32_t mix32(uint32_t s)
+{
+    static_assert(CB == 0 || CB == 1, "mix32 is defined for the 3INST and MCG codebooks");
+    uint32_t x = (CB == 0) ? s * 89226354u + 64248484u : s * 0xCBAC1FEDu;
+    return lop3_mask_xor(x);
+}
+
+// Byte sum of the MUL1 product (0..1020).
+__device__ __forceinline__ uint32_t mul1_sum(uint32_t s)
+{
+    return __dp4a(s * 0x83DCD12Du, 0x01010101u, 0u);
+}
+
+// One state -> one fp16 weight, bit-exact with the specification.
+template <int CB>
+__device__ __forceinline__ __half decode(uint32_t s)
+{
+    if constexpr (CB == 2) {
+        return __hfma(__uint2half_rn(mul1_sum(s)), __ushort_as_half(kMul1S), __ushort_as_half(kMul1B));
+    } else {
+        uint32_t x = mix32<CB>(s);
+        __half2 h = *reinterpret_cast<__half2*>(&x);
+        return __hadd(__low2half(h), __high2half(h));
+    }
+}
+
+__device__ __forceinline__ uint32_t pack_half2(__half lo, __half hi)
+{
+    __half2 h = __halves2half2(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Number of 32-bit words a lane needs to cover its eight windows (7*BITS+16 bits after a start
+// offset of up to 24 bits).
+template <int BITS>
+struct LaneWords {
+    static constexpr int rmax = (BITS % 4 == 0) ? 0 : ((BITS % 2 == 0) ? 16 : 24);
+    static constexpr int value = (rmax + 7 * BITS + 16 + 31) / 32;
+};
+
+// Raw (little-endian uint16 pair) word -> stream order (first uint16 in the high half).
+__device__ __forceinline__ uint32_t stream_order(uint32_t raw) { return __byte_perm(raw, 0, 0x1032); }
+
+// Index of the first raw 32-bit word of the lane's span inside the tile, and the residual
+// left shift (a multiple of 8 below 32).
+template <int BITS>
+__device__ __forceinline__ void lane_span(int lane, int& word, int& shift)
+{
+    int bitpos = 8 * lane * BITS;
+    word = bitpos >> 5;
+    shift = bitpos & 31;
+}
+
+// Eight 16-bit states from the lane's stream-ordered words a0,a1,a2 (a2 ignored when the span
+// fits two words) already shifted so that the lane's first window starts at bit 31 of a0.
+template <int BITS>
+__device__ __forceinline__ void states_aligned(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t (&s)[8])
+{
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int p = j * BITS;
+        const int wi = p >> 5, sh = p & 31;
+        uint32_t hi = wi == 0 ? a0 : (wi == 1 ? a1 : a2);
+        uint32_t lo = wi == 0 ? a1 : (wi == 1 ? a2 : 0u);
+        s[j] = __funnelshift_l(lo, hi, sh) >> 16;
+    }
+}
+
+// Loads the lane's words from a tile (global or shared pointer to its 8*BITS raw words), with
+// the tail-biting wrap, and returns the eight states.
+template <int BITS>
+__device__ __forceinline__ void lane_states(const uint32_t* tile, int lane, uint32_t (&s)[8])
+{
+    constexpr int NW = 8 * BITS;
+    constexpr int NL = LaneWords<BITS>::value;
+    int w, r;
+    lane_span<BITS>(lane, w, r);
+    int w1 = w + 1; if (w1 >= NW) w1 -= NW;
+    uint32_t a0 = stream_order(tile[w]);
+    uint32_t a1 = stream_order(tile[w1]);
+    uint32_t a2 = 0;
+    if constexpr (NL > 2) {
+        int w2 = w1 + 1; if (w2 >= NW) w2 -= NW;
+        a2 = stream_order(tile[w2]);
+    }
+    if constexpr (BITS % 4 != 0) {
+        a0 = __funnelshift_l(a1, a0, r);
+        a1 = __funnelshift_l(a2, a1, r);
+        a2 = a2 << r;
+    }
+    states_aligned<BITS>(a0, a1, a2, s);
+}
+
+// Same from raw words already in registers (the order lane_states would load them in).
+template <int BITS>
+__device__ __forceinline__ void lane_states_regs(uint32_t r0, uint32_t r1, uint32_t r2, int lane, uint32_t (&s)[8])
+{
+    int w, r;
+    lane_span<BITS>(lane, w, r);
+    uint32_t a0 = stream_order(r0), a1 = stream_order(r1), a2 = stream_order(r2);
+    if constexpr (BITS % 4 != 0) {
+        a0 = __funnelshift_l(a1, a0, r);
+        a1 = __funnelshift_l(a2, a1, r);
+        a2 = a2 << r;
+    }
+    states_aligned<BITS>(a0, a1, a2, s);
+}
+
+// Eight states -> the four packed fp16 pairs (j=0,1), (2,3), (4,5), (6,7): the A fragment
+// a0..a3 of mma.m16n8k16 for the transposed tile.
+template <int CB>
+__device__ __forceinline__ void decode_frag(const uint32_t (&s)[8], uint32_t (&a)[4])
+{
+#pragma unroll
+    for (int r = 0; r < 4; ++r) a[r] = pack_half2(decode<CB>(s[2 * r]), decode<CB>(s[2 * r + 1]));
+}
+
+// D(16x8, fp32) += A(16x16, fp16, row) * B(16x8, fp16, col)
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Unnormalised 128-point Sylvester-Hadamard transform across a warp; lane L holds elements
+// 4L..4L+3.  Strides 1,2 in registers, 4..64 by shuffles; lower index gets a+b, upper a-b, so
+// every output equals the sequential butterfly of the checker bit for bit.
+__device__ __forceinline__ void had128_warp(float (&v)[4], int lane)
+{
+    float a = __fadd_rn(v[0], v[1]), b = __fsub_rn(v[0], v[1]);
+    float c = __fadd_rn(v[2], v[3]), d = __fsub_rn(v[2], v[3]);
+    v[0] = __fadd_rn(a, c); v[2] = __fsub_rn(a, c);
+    v[1] = __fadd_rn(b, d); v[3] = __fsub_rn(b, d);
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float o = __shfl_xor_sync(kFull, v[i], off);
+            v[i] = (lane & off) ? __fsub_rn(o, v[i]) : __fadd_rn(v[i], o);
+        }
+    }
+}
+
+}  // namespace dq
+}  // namespace berth

@@ -1,0 +1,121 @@
+// C entry points of the EXL3 linear: host validation in berth's order and wording, then the
+// fused decode GEMV (size_m <= 32 per launch).
+#include "common.cuh"
+#include "../../include/berth_b200.h"
+
+#include <algorithm>
+
+namespace berth {
+
+std::string launch_gemv(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
+                        int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, float* ws,
+                        size_t ws_bytes, unsigned* counters, int sms, cudaStream_t stream);
+
+// Any row count through the GEMV kernel, 32 rows per launch.
+std::string linear_rows(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
+                        int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, cudaStream_t stream)
+{
+    const int device = current_device();
+    const DeviceInfo& info = device_info(device);
+    if (info.major != 10)
+        throw std::runtime_error("exl3 linear: no linked kernel for this GPU (library is built for sm_100a only)");
+    GemvWorkspace w = gemv_workspace(device);
+    std::string desc;
+    const size_t csz = out_fp32 ? 4 : 2;
+    for (int m0 = 0; m0 < size_m; m0 += 32) {
+        const int rows = std::min(32, size_m - m0);
+        desc = launch_gemv(static_cast<const char*>(a) + size_t(m0) * size_k * 2, trellis,
+                           static_cast<char*>(c) + size_t(m0) * size_n * csz, suh,
+                           static_cast<char*>(a_had) + size_t(m0) * size_k * 2, svh, rows, size_k, size_n, k_bits,
+                           codebook, out_fp32, w.partial, kGemvWorkspaceBytes, w.counters, info.sms, stream);
+    }
+    if (size_m > 32) desc += " x" + std::to_string((size_m + 31) / 32) + " row chunks";
+    return desc;
+}
+
+namespace {
+
+// Checks of crates/berth-kernels/csrc/linear.cu:224-237 (berth), same order, same wording.
+void check_linear_args(const char* who, const void* a, const void* trellis, const void* c, const void* suh,
+                       const void* a_had, const void* svh, int size_k, int size_n, int k_bits, int codebook)
+{
+    const std::string w(who);
+    if (!a || !trellis || !c || !suh || !a_had || !svh) throw std::runtime_error(w + ": null device pointer");
+    if (size_k < 1 || size_n < 1) throw std::runtime_error(w + ": sizes must be positive");
+    if (k_bits < 1 || k_bits > 8) throw std::runtime_error(w + ": K must be in 1..=8");
+    if (codebook < 0 || codebook > 2) throw std::runtime_error(w + ": codebook must be 0 (default), 1 (mcg), or 2 (mul1)");
+    if (size_k % 16 != 0) throw std::runtime_error(w + ": size_k must be a multiple of 16");
+    if (size_n % 128 != 0) throw std::runtime_error(w + ": size_n must be a multiple of 128");
+}
+
+struct DevBuf {
+    void* p = nullptr;
+    ~DevBuf() { if (p) cudaFree(p); }
+    void* alloc(size_t bytes)
+    {
+        cuda_ok(cudaMalloc(&p, bytes), "smoke cudaMalloc");
+        cuda_ok(cudaMemset(p, 0, bytes), "smoke cudaMemset");
+        return p;
+    }
+};
+
+int smoke(int m, int k, int n, int bits, int cb, int out_fp32)
+{
+    CallState& st = exl3_state();
+    try {
+        DevBuf a, t, c, suh, ah, svh;
+        size_t tb = size_t(k / 16) * (n / 16) * 16 * bits * 2;
+        int rc = berth_exl3_linear(a.alloc(size_t(m) * k * 2), t.alloc(tb), c.alloc(size_t(m) * n * (out_fp32 ? 4 : 2)),
+                                   suh.alloc(size_t(k) * 2), ah.alloc(size_t(m) * k * 2), svh.alloc(size_t(n) * 2), m, k,
+                                   n, bits, cb, out_fp32, nullptr);
+        if (rc != 0) return rc;
+        cuda_ok(cudaDeviceSynchronize(), "smoke sync");
+        return 0;
+    } catch (const std::exception& e) {
+        st.err = e.what();
+        cudaGetLastError();
+        return -1;
+    }
+}
+
+}  // namespace
+}  // namespace berth
+
+using namespace berth;
+
+extern "C" int berth_exl3_linear(const void* a, const void* trellis, void* c, const void* suh, void* a_had,
+                                 const void* svh, int size_m, int size_k, int size_n, int k_bits, int codebook,
+                                 int out_fp32, void* stream)
+{
+    CallState& st = exl3_state();
+    return guarded(st, [&] {
+        if (!a || !trellis || !c || !suh || !a_had || !svh) throw std::runtime_error("exl3 linear: null device pointer");
+        if (size_m < 1 || size_k < 1 || size_n < 1) throw std::runtime_error("exl3 linear: sizes must be positive");
+        check_linear_args("exl3 linear", a, trellis, c, suh, a_had, svh, size_k, size_n, k_bits, codebook);
+        st.launch = linear_rows(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, out_fp32,
+                                (cudaStream_t) stream);
+    });
+}
+
+extern "C" int berth_prefill_exl3_linear(const void* a, const void* trellis, void* c, const void* suh, void* a_had,
+                                         const void* svh, void* w_scratch, int size_m, int size_k, int size_n,
+                                         int k_bits, int codebook, int c_fp32, void* stream)
+{
+    CallState& st = prefill_state();
+    return guarded(st, [&] {
+        // crates/berth-kernels/csrc/prefill_lin/linear.cu:248-266 (berth)
+        if (!a || !trellis || !c || !suh || !a_had || !svh)
+            throw std::runtime_error("prefill exl3 linear: null device pointer");
+        if (size_m < 2) throw std::runtime_error("prefill exl3 linear: size_m must be > 1 (m = 1 is exl3_linear)");
+        check_linear_args("prefill exl3 linear", a, trellis, c, suh, a_had, svh, size_k, size_n, k_bits, codebook);
+        if (size_m > 144 && !w_scratch)
+            throw std::runtime_error(
+                "prefill exl3 linear: w_scratch (fp16, size_k * min(size_n, 32768)) is required when rows > 144");
+        st.launch = linear_rows(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, c_fp32,
+                                (cudaStream_t) stream);
+    });
+}
+
+// Smallest shapes of the two regimes berth's self tests exercise (csrc/linear.cu:406-465 of berth-kernels).
+extern "C" int berth_exl3_smoke_int8(int out_fp32) { return smoke(1, 128, 256, 4, 2, out_fp32); }
+extern "C" int berth_exl3_smoke_gemm(void) { return smoke(1, 128, 512, 6, 2, 0); }

@@ -1,0 +1,263 @@
+// Bandwidth-bound helpers of the EXL3 path: trellis -> fp16 weight reconstruction, the
+// standalone 128-wide Hadamard, silu(gate)*up and the fp32 residual add.
+#include "exl3_decode.cuh"
+#include "../../include/berth_b200.h"
+
+#include <algorithm>
+
+namespace berth {
+namespace {
+
+// ---------------------------------------------------------------- reconstruct
+// One CTA = one k-tile row of one 128-column band: 8 warps decode one 16x16 tile each into a
+// [16][128] shared tile, then the CTA writes sixteen 256-byte rows.
+// Algorithmic bytes per weight: BITS/8 read + 2 written.
+template <int BITS, int CB>
+__global__ void __launch_bounds__(256) k_trellis_decode(__half* __restrict__ out, const uint32_t* __restrict__ trellis,
+                                                        int tiles_n_full, int tile_n0, int slice_n)
+{
+    __shared__ __align__(16) __half tile[16][128 + 8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kt = blockIdx.y, band = blockIdx.x;
+    const uint32_t* src = trellis + (size_t(kt) * tiles_n_full + tile_n0 + band * 8 + warp) * (8 * BITS);
+    uint32_t s[8];
+    dq::lane_states<BITS>(src, lane, s);
+    const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int col = g + 8 * ((j >> 1) & 1);
+        const int row = 2 * q + (j & 1) + 8 * (j >> 2);
+        tile[row][warp * 16 + col] = dq::decode<CB>(s[j]);
+    }
+    __syncthreads();
+    // 16 rows x 128 halves = 16 x 16 uint4
+    const int row = threadIdx.x >> 4, seg = threadIdx.x & 15;
+    uint4 v = *reinterpret_cast<const uint4*>(&tile[row][seg * 8]);
+    *reinterpret_cast<uint4*>(out + (size_t(kt) * 16 + row) * slice_n + band * 128 + seg * 8) = v;
+}
+
+template <int BITS>
+void launch_decode_cb(int cb, dim3 grid, cudaStream_t st, __half* out, const uint32_t* t, int tnf, int tn0, int sn)
+{
+    switch (cb) {
+        case 0: k_trellis_decode<BITS, 0><<<grid, 256, 0, st>>>(out, t, tnf, tn0, sn); break;
+        case 1: k_trellis_decode<BITS, 1><<<grid, 256, 0, st>>>(out, t, tnf, tn0, sn); break;
+        default: k_trellis_decode<BITS, 2><<<grid, 256, 0, st>>>(out, t, tnf, tn0, sn); break;
+    }
+}
+
+void check_div(int value, int by, const char* what)
+{
+    if (value % by != 0)
+        throw std::runtime_error(std::string("prefill reconstruct: ") + what + " must be a multiple of " + std::to_string(by));
+}
+
+// ---------------------------------------------------------------- had_r_128
+// One warp per (row, 128-block); lane holds 4 consecutive elements.  4 or 8 bytes per element.
+template <bool FP32, bool PRE>
+__global__ void __launch_bounds__(128) k_had128(const void* __restrict__ in, void* __restrict__ out,
+                                                const __half* __restrict__ scale, int rows, int blocks_per_row)
+{
+    const int lane = threadIdx.x & 31;
+    const long long total = (long long) rows * blocks_per_row;
+    for (long long idx = (long long) blockIdx.x * 4 + (threadIdx.x >> 5); idx < total; idx += (long long) gridDim.x * 4) {
+        const int b = int(idx % blocks_per_row);
+        const size_t base = size_t(idx) * 128 + lane * 4;
+        float v[4], sc[4] = {1.f, 1.f, 1.f, 1.f};
+        if (scale) {
+            uint2 raw = *reinterpret_cast<const uint2*>(scale + b * 128 + lane * 4);
+            __half2 s0 = *reinterpret_cast<__half2*>(&raw.x), s1 = *reinterpret_cast<__half2*>(&raw.y);
+            sc[0] = __low2float(s0); sc[1] = __high2float(s0); sc[2] = __low2float(s1); sc[3] = __high2float(s1);
+        }
+        if constexpr (FP32) {
+            float4 x = *reinterpret_cast<const float4*>(static_cast<const float*>(in) + base);
+            v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+        } else {
+            uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __half*>(in) + base);
+            __half2 x0 = *reinterpret_cast<__half2*>(&raw.x), x1 = *reinterpret_cast<__half2*>(&raw.y);
+            v[0] = __low2float(x0); v[1] = __high2float(x0); v[2] = __low2float(x1); v[3] = __high2float(x1);
+        }
+        if constexpr (PRE) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] = __fmul_rn(v[i], sc[i]);
+        }
+        dq::had128_warp(v, lane);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[i] = __fmul_rn(v[i], kRScale);
+            if constexpr (!PRE) v[i] = __fmul_rn(v[i], sc[i]);
+        }
+        if constexpr (FP32) {
+            *reinterpret_cast<float4*>(static_cast<float*>(out) + base) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+            uint2 o;
+            o.x = dq::pack_half2(__float2half_rn(v[0]), __float2half_rn(v[1]));
+            o.y = dq::pack_half2(__float2half_rn(v[2]), __float2half_rn(v[3]));
+            *reinterpret_cast<uint2*>(static_cast<__half*>(out) + base) = o;
+        }
+    }
+}
+
+// ---------------------------------------------------------------- silu_mul
+// exp(x) from fmaf/mul only: the same operation sequence as the CPU checker, hence the same
+// bits.  x is clamped to the range where fp16 neither overflows nor underflows.
+__device__ __forceinline__ float exp_f32_det(float x)
+{
+    x = fminf(x, 12.0f);
+    x = fmaxf(x, -20.0f);
+    float n = rintf(__fmul_rn(x, 1.44269504088896341f));
+    float r = __fmaf_rn(n, -0.693145751953125f, x);
+    r = __fmaf_rn(n, -1.42860682030941723e-6f, r);
+    float p = 1.0f / 5040.0f;
+    p = __fmaf_rn(p, r, 1.0f / 720.0f);
+    p = __fmaf_rn(p, r, 1.0f / 120.0f);
+    p = __fmaf_rn(p, r, 1.0f / 24.0f);
+    p = __fmaf_rn(p, r, 1.0f / 6.0f);
+    p = __fmaf_rn(p, r, 0.5f);
+    p = __fmaf_rn(p, r, 1.0f);
+    p = __fmaf_rn(p, r, 1.0f);
+    return __fmul_rn(p, __int_as_float((int(n) + 127) << 23));
+}
+
+// e = h(exp(-g)); d = h(1+e); r = h(1/d); s = h(g*r); out = h(s*u): every step rounded to fp16,
+// which reproduces berth's silu.out.bin fixture bit for bit.
+__device__ __forceinline__ __half silu_mul_one(__half g, __half u, float limit)
+{
+    const float gf = __half2float(g);
+    __half e = (gf != gf) ? __ushort_as_half(0x7e00) : __float2half_rn(exp_f32_det(-gf));
+    __half d = __float2half_rn(__fadd_rn(1.0f, __half2float(e)));
+    __half r = __float2half_rn(__fdiv_rn(1.0f, __half2float(d)));
+    __half s = __float2half_rn(__fmul_rn(gf, __half2float(r)));
+    __half o = __float2half_rn(__fmul_rn(__half2float(s), __half2float(u)));
+    if (limit != 0.0f) {
+        float lim = __half2float(__float2half_rn(fabsf(limit)));
+        float p = __half2float(o);
+        p = p > lim ? lim : p;
+        p = p < -lim ? -lim : p;
+        o = __float2half_rn(p);
+    }
+    return o;
+}
+
+__global__ void __launch_bounds__(256) k_silu_mul(const __half2* gate, const __half2* up,
+                                                  __half2* out, long long pairs, float limit)
+{
+    for (long long i = (long long) blockIdx.x * 256 + threadIdx.x; i < pairs; i += (long long) gridDim.x * 256) {
+        __half2 g = gate[i], u = up[i];
+        out[i] = __halves2half2(silu_mul_one(__low2half(g), __low2half(u), limit),
+                                silu_mul_one(__high2half(g), __high2half(u), limit));
+    }
+}
+
+__global__ void __launch_bounds__(256) k_add_f32(const float* a, const float* b, float* c, int n)
+{
+    int i = blockIdx.x * 256 + threadIdx.x;
+    if (i < n) c[i] = __fadd_rn(a[i], b[i]);
+}
+
+}  // namespace
+
+// Internal C++ entry points (shared with the prefill path).
+void reconstruct(void* unpacked, const void* packed, int size_k, int slice_n, int full_n, int n_offset,
+                 int k_bits, int codebook, cudaStream_t stream)
+{
+    check_div(size_k, 16, "K");
+    check_div(slice_n, 128, "slice N");
+    check_div(full_n, 16, "full N");
+    check_div(n_offset, 128, "n_offset");
+    if (n_offset < 0 || n_offset + slice_n > full_n)
+        throw std::runtime_error("prefill reconstruct: slice exceeds the trellis");
+    dim3 grid(slice_n / 128, size_k / 16);
+    __half* out = static_cast<__half*>(unpacked);
+    const uint32_t* t = static_cast<const uint32_t*>(packed);
+    const int tnf = full_n / 16, tn0 = n_offset / 16;
+    switch (k_bits) {
+        case 1: launch_decode_cb<1>(codebook, grid, stream, out, t, tnf, tn0, slice_n); break;
+        case 2: launch_decode_cb<2>(codebook, grid, stream, out, t, tnf, tn0, slice_n); break;
+        case 3: launch_decode_cb<3>(codebook, grid, stream, out, t, tnf, tn0, slice_n); break;
+        case 4: launch_decode_cb<4>(codebook, grid, stream, out, t, tnf, tn0, slice_n); break;
+        case 5: launch_decode_cb<5>(codebook, grid, stream, out, t, tnf, tn0, slice_n); break;
+        case 6: launch_decode_cb<6>(codebook, grid, stream, out, t, tnf, tn0, slice_n); break;
+        case 7: launch_decode_cb<7>(codebook, grid, stream, out, t, tnf, tn0, slice_n); break;
+        case 8: launch_decode_cb<8>(codebook, grid, stream, out, t, tnf, tn0, slice_n); break;
+        default: throw std::runtime_error("prefill reconstruct: K must be in 1..=8");
+    }
+    cuda_ok(cudaPeekAtLastError(), "k_trellis_decode");
+}
+
+void had_r_128(const void* input, void* output, const void* scale, int pre_scale, int rows, int cols, int fp32,
+               cudaStream_t stream)
+{
+    if (cols % 128 != 0) throw std::runtime_error("prefill had_r_128: had columns must be a multiple of 128");
+    if (rows < 1) throw std::runtime_error("prefill had_r_128: rows must be positive");
+    const int bpr = cols / 128;
+    long long total = (long long) rows * bpr;
+    int grid = int(std::min<long long>((total + 3) / 4, 148LL * 16));
+    const __half* sc = static_cast<const __half*>(scale);
+    if (fp32) {
+        if (pre_scale) k_had128<true, true><<<grid, 128, 0, stream>>>(input, output, sc, rows, bpr);
+        else k_had128<true, false><<<grid, 128, 0, stream>>>(input, output, sc, rows, bpr);
+    } else {
+        if (pre_scale) k_had128<false, true><<<grid, 128, 0, stream>>>(input, output, sc, rows, bpr);
+        else k_had128<false, false><<<grid, 128, 0, stream>>>(input, output, sc, rows, bpr);
+    }
+    cuda_ok(cudaPeekAtLastError(), "k_had128");
+}
+
+}  // namespace berth
+
+using namespace berth;
+
+extern "C" int berth_prefill_reconstruct(void* unpacked, const void* packed, int size_k, int slice_n, int full_n,
+                                         int n_offset, int k_bits, int codebook, void* stream)
+{
+    CallState& st = prefill_state();
+    return guarded(st, [&] {
+        if (!unpacked || !packed) throw std::runtime_error("prefill reconstruct: null device pointer");
+        if (size_k < 1 || slice_n < 1 || full_n < 1) throw std::runtime_error("prefill reconstruct: sizes must be positive");
+        if (codebook < 0 || codebook > 2) throw std::runtime_error("prefill reconstruct: codebook must be 0, 1, or 2");
+        reconstruct(unpacked, packed, size_k, slice_n, full_n, n_offset, k_bits, codebook, (cudaStream_t) stream);
+        st.launch = "k_trellis_decode<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "> block=256 grid=" +
+                    std::to_string(slice_n / 128) + "x" + std::to_string(size_k / 16);
+    });
+}
+
+extern "C" int berth_prefill_had_r_128(const void* input, void* output, const void* scale, int pre_scale, int rows,
+                                       int cols, int fp32, void* stream)
+{
+    CallState& st = prefill_state();
+    return guarded(st, [&] {
+        if (!input || !output) throw std::runtime_error("prefill had_r_128: null device pointer");
+        had_r_128(input, output, scale, pre_scale, rows, cols, fp32, (cudaStream_t) stream);
+        st.launch = std::string("k_had128<") + (fp32 ? "f32" : "f16") + (pre_scale ? ",pre" : ",post") + "> block=128";
+    });
+}
+
+extern "C" int berth_ops_silu_mul(const void* gate, const void* up, void* out, int64_t numel, float act_limit,
+                                  void* stream)
+{
+    CallState& st = ops_state();
+    return guarded(st, [&] {
+        if (!gate || !up || !out) throw std::runtime_error("silu_mul: null device pointer");
+        if (numel < 2 || (numel & 1)) throw std::runtime_error("silu_mul: numel must be positive and even");
+        long long pairs = numel / 2;
+        int grid = int(std::min<long long>((pairs + 255) / 256, 148LL * 8));
+        k_silu_mul<<<grid, 256, 0, (cudaStream_t) stream>>>((const __half2*) gate, (const __half2*) up, (__half2*) out,
+                                                            pairs, act_limit);
+        cuda_ok(cudaGetLastError(), "silu_mul launch");
+        st.launch = "k_silu_mul block=256 grid=" + std::to_string(grid);
+    });
+}
+
+extern "C" int berth_ops_add_f32(const void* a, const void* b, void* c, int n, void* stream)
+{
+    CallState& st = ops_state();
+    return guarded(st, [&] {
+        if (!a || !b || !c) throw std::runtime_error("add_f32: null device pointer");
+        if (n < 1) throw std::runtime_error("add_f32: n must be positive");
+        int grid = (n + 255) / 256;
+        k_add_f32<<<grid, 256, 0, (cudaStream_t) stream>>>((const float*) a, (const float*) b, (float*) c, n);
+        cuda_ok(cudaGetLastError(), "add_f32 launch");
+        st.launch = "k_add_f32 block=256 grid=" + std::to_string(grid);
+    });
+}

@@ -1,0 +1,171 @@
+"""Host-side callers of the EXL3 linear, mirroring ``berth-engine``:
+``Gpu`` (crates/berth-engine/src/device.rs:15-43), ``Exl3Linear`` (device.rs:77-164,206-268),
+``RowScratch`` (device.rs:178-204) and ``MlpLayer`` (crates/berth-engine/src/mlp.rs:25-150,219-305).
+
+PyTorch is used only to own device memory and streams; every computation is a call into
+``libberth_b200.so`` through :mod:`berth_b200.kernels`.  Buffers are torch CUDA tensors.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import kernels
+from .kernels import Codebook, OutDtype
+
+ACT_LIMIT = 0.0          # crates/berth-engine/src/mlp.rs:22
+MAX_RECONSTRUCT_N = 32768  # crates/berth-engine/src/device.rs:176
+
+
+class Error(RuntimeError):
+    """``berth_engine::Error`` (Weights / Input)."""
+
+
+class Gpu:
+    """One device and the stream every launch of a model goes to."""
+
+    def __init__(self, device: int = 0, stream: torch.cuda.Stream | None = None):
+        if not torch.cuda.is_available():
+            raise Error("berth_b200 needs a CUDA device: there is no CPU path")
+        self.device = torch.device("cuda", device)
+        torch.cuda.set_device(self.device)
+        self.stream = stream if stream is not None else torch.cuda.current_stream(self.device)
+        self.sms = kernels.device_sms(device)
+
+    def raw_stream(self) -> int:
+        return self.stream.cuda_stream
+
+    def zeroed(self, nbytes: int) -> torch.Tensor:
+        return torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+
+    def upload(self, a: np.ndarray) -> torch.Tensor:
+        a = np.ascontiguousarray(a)
+        if a.dtype == np.uint16:
+            a = a.view(np.int16)
+        return torch.from_numpy(a).to(self.device, non_blocking=False)
+
+
+class Exl3Linear:
+    """One EXL3 linear resident on the device: trellis, fp16 sign-scales and the fp16 scratch the
+    kernel writes the rotated input to."""
+
+    def __init__(self, gpu: Gpu, prefix: str, trellis, suh, svh, k_bits: int, codebook: Codebook, max_rows: int = 1):
+        self.prefix = prefix
+        self.trellis = trellis if isinstance(trellis, torch.Tensor) else gpu.upload(trellis)
+        self.suh = suh if isinstance(suh, torch.Tensor) else gpu.upload(suh)
+        self.svh = svh if isinstance(svh, torch.Tensor) else gpu.upload(svh)
+        self.size_k = int(self.suh.numel())
+        self.size_n = int(self.svh.numel())
+        self.k_bits = int(k_bits)
+        self.codebook = Codebook(codebook)
+        if tuple(self.trellis.shape) != (self.size_k // 16, self.size_n // 16, 16 * self.k_bits):
+            raise Error(f"{prefix}: trellis shape {tuple(self.trellis.shape)} does not match "
+                        f"({self.size_k // 16}, {self.size_n // 16}, {16 * self.k_bits})")
+        self.a_had = torch.zeros(max_rows * self.size_k, dtype=torch.float16, device=gpu.device)
+
+    @classmethod
+    def load(cls, gpu: Gpu, tensors: dict, prefix: str, k_bits: int, codebook: Codebook) -> "Exl3Linear":
+        """From a mapping ``<prefix>.trellis/.suh/.svh`` -> array, the grouping rule of
+        crates/berth-exl3/src/linear.rs:122-138."""
+        for part in ("trellis", "suh", "svh"):
+            if f"{prefix}.{part}" not in tensors:
+                raise Error(f"{prefix} is not an EXL3 linear (no {part})")
+        if f"{prefix}.bias" in tensors:
+            raise Error(f"{prefix}: bias is present and is not applied")
+        return cls(gpu, prefix, tensors[f"{prefix}.trellis"], tensors[f"{prefix}.suh"], tensors[f"{prefix}.svh"],
+                   k_bits, codebook)
+
+    def compressed_bytes(self) -> int:
+        return self.trellis.numel() * 2
+
+    def forward(self, gpu: Gpu, a: torch.Tensor, c: torch.Tensor, out: OutDtype) -> None:
+        """``c = a @ W`` for one row: a fp16 [size_k], c [size_n] of ``out``."""
+        self.forward_n(gpu, 1, a, c, out)
+
+    def forward_n(self, gpu: Gpu, rows: int, a: torch.Tensor, c: torch.Tensor, out: OutDtype) -> None:
+        """Decode-path launch for ``rows`` rows (crates/berth-engine/src/device.rs:285-366)."""
+        out_bytes = 2 if out == OutDtype.F16 else 4
+        if a.numel() * a.element_size() < rows * self.size_k * 2 or \
+                c.numel() * c.element_size() < rows * self.size_n * out_bytes:
+            raise Error(f"{self.prefix}: buffer too small")
+        if self.a_had.numel() < rows * self.size_k:
+            self.a_had = torch.zeros(rows * self.size_k, dtype=torch.float16, device=gpu.device)
+        kernels.exl3_linear(a, self.trellis, c, self.suh, self.a_had, self.svh, rows, self.size_k, self.size_n,
+                            self.k_bits, self.codebook, out, gpu.raw_stream())
+
+    def forward_rows(self, gpu: Gpu, rows: int, a: torch.Tensor, c: torch.Tensor, out: OutDtype,
+                     scratch: "RowScratch") -> None:
+        """Prefill-path launch, rows > 1 (crates/berth-engine/src/device.rs:210-268)."""
+        if rows > scratch.max_rows or self.size_k > scratch.max_k or self.size_n > scratch.max_n:
+            raise Error(f"{self.prefix}: scratch too small")
+        kernels.prefill_lin.exl3_linear(a, self.trellis, c, self.suh, scratch.a_had, self.svh,
+                                        scratch.weight if rows > 144 else None, rows, self.size_k, self.size_n,
+                                        self.k_bits, self.codebook, out, gpu.raw_stream())
+
+
+class RowScratch:
+    """Scratch shared by every linear of a prefill chunk.  ``weight`` is kept because the
+    boundary requires a non-null pointer above 144 rows; the B200 kernels never write it, so it
+    is a token allocation rather than size_k * min(size_n, 32768) halves."""
+
+    def __init__(self, gpu: Gpu, max_rows: int, max_k: int, max_n: int):
+        self.a_had = torch.zeros(max_rows * max_k, dtype=torch.float16, device=gpu.device)
+        self.weight = torch.zeros(16, dtype=torch.float16, device=gpu.device)
+        self.max_rows, self.max_k, self.max_n = max_rows, max_k, max_n
+
+
+class MlpLayer:
+    """``output = down(silu(gate(input)) * up(input))``; gate/up fp16 out, down fp32 out."""
+
+    def __init__(self, gpu: Gpu, gate: Exl3Linear, up: Exl3Linear, down: Exl3Linear, max_rows: int = 1):
+        if gate.size_k != up.size_k or gate.size_n != up.size_n:
+            raise Error(f"gate is {gate.size_k}x{gate.size_n}, up is {up.size_k}x{up.size_n}")
+        if down.size_k != gate.size_n or down.size_n != gate.size_k:
+            raise Error(f"down is {down.size_k}x{down.size_n}, gate is {gate.size_k}x{gate.size_n}")
+        self.gate, self.up, self.down = gate, up, down
+        self.hidden, self.intermediate = gate.size_k, gate.size_n
+        if self.intermediate < 2 or self.intermediate % 2:
+            raise Error(f"intermediate {self.intermediate} must be positive and even")
+        self._alloc(gpu, max_rows)
+
+    def _alloc(self, gpu: Gpu, rows: int) -> None:
+        n = rows * self.intermediate
+        self.max_rows = rows
+        self.gate_out = torch.zeros(n, dtype=torch.float16, device=gpu.device)
+        self.up_out = torch.zeros(n, dtype=torch.float16, device=gpu.device)
+        self.activated = torch.zeros(n, dtype=torch.float16, device=gpu.device)
+
+    @classmethod
+    def load_prefixed(cls, gpu: Gpu, tensors: dict, prefix: str, k_bits: int, codebook: Codebook) -> "MlpLayer":
+        parts = [Exl3Linear.load(gpu, tensors, f"{prefix}.{p}", k_bits, codebook)
+                 for p in ("gate_proj", "up_proj", "down_proj")]
+        return cls(gpu, *parts)
+
+    def compressed_bytes(self) -> int:
+        return self.gate.compressed_bytes() + self.up.compressed_bytes() + self.down.compressed_bytes()
+
+    def forward(self, gpu: Gpu, inp: torch.Tensor, output: torch.Tensor) -> None:
+        self.forward_n(gpu, 1, inp, output)
+
+    def forward_n(self, gpu: Gpu, rows: int, inp: torch.Tensor, output: torch.Tensor) -> None:
+        """inp fp16 [rows][hidden]; output fp32 [rows][hidden]."""
+        if inp.numel() * inp.element_size() < rows * self.hidden * 2 or \
+                output.numel() * output.element_size() < rows * self.hidden * 4:
+            raise Error(f"{self.gate.prefix}: buffer too small")
+        if rows > self.max_rows:
+            self._alloc(gpu, rows)
+        self.gate.forward_n(gpu, rows, inp, self.gate_out, OutDtype.F16)
+        self.up.forward_n(gpu, rows, inp, self.up_out, OutDtype.F16)
+        kernels.ops.silu_mul(self.gate_out, self.up_out, self.activated, rows * self.intermediate, ACT_LIMIT,
+                             gpu.raw_stream())
+        self.down.forward_n(gpu, rows, self.activated, output, OutDtype.F32)
+
+    def prefill(self, gpu: Gpu, rows: int, inp: torch.Tensor, output: torch.Tensor, scratch: RowScratch) -> None:
+        """crates/berth-engine/src/mlp.rs:219-305."""
+        if rows > self.max_rows:
+            self._alloc(gpu, rows)
+        self.gate.forward_rows(gpu, rows, inp, self.gate_out, OutDtype.F16, scratch)
+        self.up.forward_rows(gpu, rows, inp, self.up_out, OutDtype.F16, scratch)
+        kernels.ops.silu_mul(self.gate_out, self.up_out, self.activated, rows * self.intermediate, ACT_LIMIT,
+                             gpu.raw_stream())
+        self.down.forward_rows(gpu, rows, self.activated, output, OutDtype.F32, scratch)

@@ -1,0 +1,152 @@
+"""Host-side mirror of berth's ``berth-kernels`` crate over the C ABI.
+
+Function names, argument order and error behaviour follow the Rust wrappers:
+``exl3_linear`` / ``last_launch`` / ``last_error`` (crates/berth-kernels/src/lib.rs:135-205),
+``prefill_lin::exl3_linear`` / ``exl3_gemv_cfg`` (src/prefill_lin.rs:117-161,224),
+``ops::silu_mul`` / ``ops::add_f32`` (src/ops.rs:507-520).  Pointers are device addresses: pass
+an ``int`` or anything with ``data_ptr()`` (a torch CUDA tensor).  A non-zero return code of
+the library raises :class:`Error` with the library's message, as ``Error::Launch`` does.
+"""
+from __future__ import annotations
+
+import enum
+
+from . import _lib
+
+
+class Error(RuntimeError):
+    """``berth_kernels::Error::Launch``."""
+
+
+class Codebook(enum.IntEnum):
+    """crates/berth-kernels/src/lib.rs:54-63."""
+    Default = 0
+    Mcg = 1
+    Mul1 = 2
+
+
+class OutDtype(enum.IntEnum):
+    """crates/berth-kernels/src/lib.rs:70-84."""
+    F16 = 0
+    F32 = 1
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    return x.data_ptr()
+
+
+def _stream(stream):
+    if stream is None:
+        return None
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+def _s(b) -> str:
+    return (b or b"").decode("utf-8", "replace")
+
+
+def last_launch() -> str:
+    return _s(_lib.lib().berth_exl3_last_launch())
+
+
+def last_error() -> str:
+    return _s(_lib.lib().berth_exl3_last_error())
+
+
+def exl3_linear(a, trellis, c, suh, a_had, svh, size_m: int, size_k: int, size_n: int, k_bits: int,
+                codebook: Codebook, out: OutDtype, stream=None) -> None:
+    """One EXL3 linear ``C = A @ trellis`` with the Hadamard sign-scales; decode passes size_m = 1."""
+    l = _lib.lib()
+    rc = l.berth_exl3_linear(_ptr(a), _ptr(trellis), _ptr(c), _ptr(suh), _ptr(a_had), _ptr(svh), size_m, size_k,
+                             size_n, k_bits, int(codebook), int(out), _stream(stream))
+    if rc != 0:
+        raise Error(last_error() or f"exl3 linear launch failed ({rc})")
+
+
+def device_cc(device: int) -> int:
+    return _lib.lib().berth_device_cc(device)
+
+
+def device_sms(device: int) -> int:
+    return _lib.lib().berth_device_sms(device)
+
+
+def gemm_tune_key(size_m, size_k, size_n, k_bits, out_fp32, device, cc, sms, cb) -> int:
+    return _lib.lib().berth_exl3_gemm_tune_key(size_m, size_k, size_n, k_bits, out_fp32, device, cc, sms, cb)
+
+
+class prefill_lin:
+    """crates/berth-kernels/src/prefill_lin.rs."""
+
+    @staticmethod
+    def last_launch() -> str:
+        return _s(_lib.lib().berth_prefill_last_launch())
+
+    @staticmethod
+    def last_error() -> str:
+        return _s(_lib.lib().berth_prefill_last_error())
+
+    @staticmethod
+    def exl3_linear(a, trellis, c, suh, a_had, svh, w_scratch, size_m, size_k, size_n, k_bits,
+                    codebook: Codebook, out: OutDtype, stream=None) -> None:
+        l = _lib.lib()
+        rc = l.berth_prefill_exl3_linear(_ptr(a), _ptr(trellis), _ptr(c), _ptr(suh), _ptr(a_had), _ptr(svh),
+                                         _ptr(w_scratch), size_m, size_k, size_n, k_bits, int(codebook), int(out),
+                                         _stream(stream))
+        if rc != 0:
+            raise Error(prefill_lin.last_error() or f"prefill exl3 linear launch failed ({rc})")
+
+    @staticmethod
+    def hgemm(a, b, c, size_m, size_k, size_n, ldc, out: OutDtype, stream=None) -> None:
+        rc = _lib.lib().berth_prefill_hgemm(_ptr(a), _ptr(b), _ptr(c), size_m, size_k, size_n, ldc, int(out),
+                                            _stream(stream))
+        if rc != 0:
+            raise Error(prefill_lin.last_error() or f"prefill hgemm launch failed ({rc})")
+
+    @staticmethod
+    def exl3_gemv_cfg(cc, size_m, size_k, size_n, k_bits, cb, mode, narrow_coresident) -> int:
+        return _lib.lib().berth_exl3_gemv_cfg(cc, size_m, size_k, size_n, k_bits, int(cb), mode, narrow_coresident)
+
+    @staticmethod
+    def reconstruct(unpacked, packed, size_k, slice_n, full_n, n_offset, k_bits, codebook, stream=None) -> None:
+        rc = _lib.lib().berth_prefill_reconstruct(_ptr(unpacked), _ptr(packed), size_k, slice_n, full_n, n_offset,
+                                                  k_bits, int(codebook), _stream(stream))
+        if rc != 0:
+            raise Error(prefill_lin.last_error())
+
+    @staticmethod
+    def had_r_128(inp, out, scale, pre_scale: bool, rows, cols, fp32: bool, stream=None) -> None:
+        rc = _lib.lib().berth_prefill_had_r_128(_ptr(inp), _ptr(out), _ptr(scale), int(pre_scale), rows, cols,
+                                                int(fp32), _stream(stream))
+        if rc != 0:
+            raise Error(prefill_lin.last_error())
+
+
+class ops:
+    """crates/berth-kernels/src/ops.rs."""
+
+    @staticmethod
+    def last_launch() -> str:
+        return _s(_lib.lib().berth_ops_last_launch())
+
+    @staticmethod
+    def last_error() -> str:
+        return _s(_lib.lib().berth_ops_last_error())
+
+    @staticmethod
+    def silu_mul(gate, up, out, numel: int, act_limit: float = 0.0, stream=None) -> None:
+        rc = _lib.lib().berth_ops_silu_mul(_ptr(gate), _ptr(up), _ptr(out), numel, act_limit, _stream(stream))
+        if rc != 0:
+            raise Error(ops.last_error() or f"silu_mul launch failed ({rc})")
+
+    @staticmethod
+    def add_f32(a, b, c, n: int, stream=None) -> None:
+        rc = _lib.lib().berth_ops_add_f32(_ptr(a), _ptr(b), _ptr(c), n, _stream(stream))
+        if rc != 0:
+            raise Error(ops.last_error() or f"add_f32 launch failed ({rc})")

@@ -1,0 +1,111 @@
+/*
+ * berth_b200.h -- C ABI of libberth_b200.so: the EXL3 trellis-linear / A3B-MoE hot path of
+ * berth, written for NVIDIA B200 (sm_100a).
+ *
+ * Conventions, identical to the library berth's Rust crate `berth-kernels` binds
+ * (crates/berth-kernels/src/ffi.rs:1-24, src/prefill_lin.rs:33-80, src/ops.rs:13-148):
+ *   - every tensor pointer is a DEVICE address; the caller owns the buffers and keeps them
+ *     alive until `stream` has finished; `stream` is a cudaStream_t, NULL = default stream;
+ *   - launches are asynchronous on `stream`; nothing here synchronises the device;
+ *   - return 0 = ok, -1 = error (berth_ops_mgemm: > 0 = ok, <= 0 = error); no C++ exception
+ *     crosses the boundary; the message of the last failed call and the description of the
+ *     last successful launch are kept per host thread and stay valid until the next call of
+ *     the same family on that thread;
+ *   - host checks (null pointer, size, bitrate, codebook) fail before any CUDA call, with the
+ *     substrings berth's tests look for: "null", "positive", "multiple of 16",
+ *     "multiple of 128", "size_m", "no linked kernel";
+ *   - an unsupported shape fails closed; there is no fallback kernel, no CPU path, no
+ *     runtime autotuning, no environment-variable policy and no file written anywhere.
+ *
+ * Tensor layout (crates/berth-kernels/src/lib.rs:86-103):
+ *   a        fp16 [size_m][size_k]                     activations, row major
+ *   trellis  int16 [size_k/16][size_n/16][16*k_bits]   one 16x16 weight tile per last-dim row
+ *   suh      fp16 [size_k]   input-side sign-scale;  svh fp16 [size_n] output-side sign-scale
+ *   a_had    fp16 [size_m][size_k]   scratch the kernel fills with H128(a*suh)/sqrt(128)
+ *   c        fp16 or fp32 [size_m][size_n]
+ *   codebook 0 = 3INST, 1 = MCG, 2 = MUL1 (crates/berth-kernels/src/lib.rs:49-63)
+ *
+ * Per-device state owned by the library, allocated at the first launch on a device and kept
+ * until exit (the counterpart of the lock buffer and 16 MiB split-K workspace of
+ * crates/berth-kernels/csrc/linear.cu:334-345 and csrc/int8_sq.cu:20-47): one split-K
+ * workspace with self-resetting arrival counters.  Launches that overlap on one device
+ * (different streams) must not share it: berth drives one stream per device, and so must
+ * every other caller.
+ */
+#ifndef BERTH_B200_H
+#define BERTH_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ decode linear (m >= 1)
+ * Replaces berth_exl3_linear (crates/berth-kernels/src/ffi.rs:7-21,
+ * crates/berth-kernels/csrc/linear.cu:209-286,362-394): c = H(H(a*suh) . W(trellis)) * svh.
+ * Serves every size_m with the fused decode GEMV (size_m <= 32) or the tensor-core GEMM. */
+int berth_exl3_linear(const void* a, const void* trellis, void* c, const void* suh, void* a_had,
+                      const void* svh, int size_m, int size_k, int size_n, int k_bits,
+                      int codebook, int out_fp32, void* stream);
+const char* berth_exl3_last_error(void);    /* crates/berth-kernels/csrc/linear.cu:396-399 */
+const char* berth_exl3_last_launch(void);   /* crates/berth-kernels/csrc/linear.cu:401-404 */
+
+/* Device queries of crates/berth-kernels/csrc/internal.h:11-13 (class 1..5 as the fork's CC_*
+ * enumeration orders them: old, Ampere, Ada, Hopper, Blackwell; SM count). -1 on error. */
+int berth_device_cc(int device);
+int berth_device_sms(int device);
+
+/* FNV-1a shape key of crates/berth-kernels/csrc/linear.cu:65-104,345-358.  Kept because berth's
+ * tests pin its value; this library never tunes at run time.  No CUDA call. */
+uint64_t berth_exl3_gemm_tune_key(int size_m, int size_k, int size_n, int k_bits, int out_fp32,
+                                  int device, int cc, int sms, int cb);
+
+/* Smallest-shape self tests of crates/berth-kernels/csrc/linear.cu:406-465 (allocate, launch,
+ * synchronise, free).  0 = ok. */
+int berth_exl3_smoke_int8(int out_fp32);
+int berth_exl3_smoke_gemm(void);
+
+/* ------------------------------------------------------------------ prefill linear (m > 1)
+ * Replaces berth_prefill_exl3_linear (crates/berth-kernels/src/prefill_lin.rs:37-52,
+ * crates/berth-kernels/csrc/prefill_lin/linear.cu:232-381).  w_scratch (fp16,
+ * size_k*min(size_n,32768)) is required when size_m > 144, as in berth, but is not written:
+ * the weight tiles are decoded straight into shared memory. */
+int berth_prefill_exl3_linear(const void* a, const void* trellis, void* c, const void* suh,
+                              void* a_had, const void* svh, void* w_scratch, int size_m,
+                              int size_k, int size_n, int k_bits, int codebook, int c_fp32,
+                              void* stream);
+const char* berth_prefill_last_error(void);
+const char* berth_prefill_last_launch(void);
+/* Shape heuristic of crates/berth-kernels/csrc/prefill_lin/gemv.cu:72-101 (pure integer logic,
+ * no CUDA call).  Kept for ABI parity; this library does not consult it. */
+int berth_exl3_gemv_cfg(int cc, int size_m, int size_k, int size_n, int k_bits, int cb, int mode,
+                        int narrow_coresident);
+
+/* The two stages berth's prefill path is built from, exported so the decoded weight tiles
+ * can be checked bit for bit (crates/berth-kernels/csrc/prefill_lin/api.h:70-84,
+ * csrc/prefill_lin/reconstruct.cu:31-95).  Errors are reported through berth_prefill_last_error.
+ *   reconstruct: unpacked fp16 [size_k][slice_n] <- columns [n_offset, n_offset+slice_n) of the
+ *                trellis of a [size_k][full_n] matrix;
+ *   had_r_128:   128-wide Hadamard / sqrt(128) on every 128-column block of every row, the fp16
+ *                sign-scale vector applied before (pre_scale != 0) or after the transform;
+ *                fp32 != 0 selects fp32 tensors, else fp16; output may alias input. */
+int berth_prefill_reconstruct(void* unpacked, const void* packed, int size_k, int slice_n,
+                              int full_n, int n_offset, int k_bits, int codebook, void* stream);
+int berth_prefill_had_r_128(const void* input, void* output, const void* scale, int pre_scale,
+                            int rows, int cols, int fp32, void* stream);
+
+/* ------------------------------------------------------------------ ops
+ * silu(gate)*up in fp16, every step rounded to fp16; out may alias gate or up
+ * (crates/berth-kernels/src/ops.rs:82-89,507-520, csrc/ops/act.cu:35-69). */
+int berth_ops_silu_mul(const void* gate, const void* up, void* out, int64_t numel,
+                       float act_limit, void* stream);
+/* c = a + b, fp32; c may alias a (crates/berth-kernels/src/ops.rs:91-97, csrc/ops/add.cu:29-54). */
+int berth_ops_add_f32(const void* a, const void* b, void* c, int n, void* stream);
+const char* berth_ops_last_error(void);
+const char* berth_ops_last_launch(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BERTH_B200_H */

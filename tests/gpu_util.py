@@ -1,0 +1,44 @@
+"""Helpers shared by the GPU parity tests: device buffers from numpy, the tolerance rule."""
+import numpy as np
+import torch
+
+from berth_b200 import Codebook, OutDtype, kernels
+
+
+def dev(a: np.ndarray) -> torch.Tensor:
+    a = np.ascontiguousarray(a)
+    if a.dtype == np.uint16:
+        a = a.view(np.int16)
+    return torch.from_numpy(a).cuda()
+
+
+def host_u16(t: torch.Tensor) -> np.ndarray:
+    return t.cpu().numpy().view(np.uint16)
+
+
+def run_linear(x, w, bits, cb, out_fp32, prefill=False):
+    """x float16 [m][k] numpy; w dict(trellis,suh,svh,size_k,size_n).  Returns (c numpy, a_had uint16 numpy)."""
+    m, k = x.shape
+    n = w["size_n"]
+    xd, td, sd, vd = dev(x), dev(w["trellis"]), dev(w["suh"]), dev(w["svh"])
+    c = torch.full((m, n), float("nan"), dtype=torch.float32 if out_fp32 else torch.float16, device="cuda")
+    ah = torch.zeros((m, k), dtype=torch.float16, device="cuda")
+    out = OutDtype.F32 if out_fp32 else OutDtype.F16
+    if prefill:
+        scratch = torch.empty(1, dtype=torch.float16, device="cuda")
+        kernels.prefill_lin.exl3_linear(xd, td, c, sd, ah, vd, scratch, m, k, n, bits, Codebook(cb), out)
+    else:
+        kernels.exl3_linear(xd, td, c, sd, ah, vd, m, k, n, bits, Codebook(cb), out)
+    torch.cuda.synchronize()
+    return c.cpu().numpy(), host_u16(ah)
+
+
+def rel_errors(got, y64):
+    """(max, mean) of |got - y64| / rms(y64): the scale of the 1e-2 / 1e-3 gates."""
+    y64 = np.asarray(y64, np.float64)
+    rms = np.sqrt((y64 ** 2).mean())
+    err = np.abs(np.asarray(got, np.float64) - y64) / rms
+    return float(err.max()), float(err.mean())
+
+
+MAX_REL, MEAN_REL = 1e-2, 1e-3   # tolerance of fp32-accumulated outputs against the fp64 evaluation

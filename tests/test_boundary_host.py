@@ -1,0 +1,135 @@
+"""The C boundary without a GPU: the library loads, exports every symbol the header declares,
+and rejects bad arguments before any CUDA call with the wording berth's own boundary tests
+look for (crates/berth-kernels/src/lib.rs:236-319, src/prefill_lin.rs:338-383, src/ops.rs:775-857)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from berth_b200 import Codebook, Error, OutDtype, _lib, kernels
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+P = 64  # non-null, never dereferenced: the checks return first
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not os.path.exists(_lib.SO_PATH):
+        _lib.build()
+    return _lib.lib()
+
+
+def _declared_symbols():
+    names = set()
+    inc = os.path.join(ROOT, "include")
+    for f in os.listdir(inc):
+        text = open(os.path.join(inc, f)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(berth_\w+)\s*\(", text))
+    return names
+
+
+def test_every_declared_symbol_is_exported_and_bound(lib):
+    declared = _declared_symbols()
+    assert declared, "no declarations found"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/ but not exported"
+    assert declared == set(_lib.SIGNATURES), "Python binding table and header disagree"
+
+
+def test_exl3_linear_null_and_bad_sizes_do_not_call_cuda(lib):
+    with pytest.raises(Error, match="null"):
+        kernels.exl3_linear(None, None, None, None, None, None, 1, 128, 256, 4, Codebook.Mul1, OutDtype.F16)
+    assert kernels.last_launch() == ""
+    with pytest.raises(Error, match="multiple of 16"):
+        kernels.exl3_linear(P, P, P, P, P, P, 1, 15, 256, 4, Codebook.Mul1, OutDtype.F32)
+    with pytest.raises(Error, match="multiple of 128"):
+        kernels.exl3_linear(P, P, P, P, P, P, 1, 16, 100, 4, Codebook.Mul1, OutDtype.F16)
+    with pytest.raises(Error, match="positive"):
+        kernels.exl3_linear(P, P, P, P, P, P, 0, 16, 128, 4, Codebook.Mul1, OutDtype.F16)
+    with pytest.raises(Error, match="K must be in 1..=8"):
+        kernels.exl3_linear(P, P, P, P, P, P, 1, 128, 128, 9, Codebook.Mul1, OutDtype.F16)
+    assert lib.berth_exl3_linear(P, P, P, P, P, P, 1, 128, 128, 4, 3, 0, None) == -1
+    assert "codebook" in kernels.last_error()
+    assert kernels.last_error() != ""
+
+
+def test_prefill_null_and_m1_do_not_launch(lib):
+    pl = kernels.prefill_lin
+    with pytest.raises(Error, match="null"):
+        pl.exl3_linear(None, None, None, None, None, None, None, 2, 128, 256, 4, Codebook.Mul1, OutDtype.F16)
+    assert pl.last_launch() == ""
+    with pytest.raises(Error, match="size_m"):
+        pl.exl3_linear(P, P, P, P, P, P, None, 1, 128, 256, 4, Codebook.Mul1, OutDtype.F16)
+    with pytest.raises(Error, match="w_scratch"):
+        pl.exl3_linear(P, P, P, P, P, P, None, 145, 128, 256, 4, Codebook.Mul1, OutDtype.F16)
+    with pytest.raises(Error, match="multiple of 16"):
+        pl.exl3_linear(P, P, P, P, P, P, None, 2, 24, 256, 4, Codebook.Mul1, OutDtype.F16)
+    with pytest.raises(Error, match="multiple of 128"):
+        pl.exl3_linear(P, P, P, P, P, P, None, 2, 128, 200, 4, Codebook.Mul1, OutDtype.F16)
+
+
+def test_ops_argument_checks(lib):
+    with pytest.raises(Error, match="null"):
+        kernels.ops.silu_mul(None, P, P, 16)
+    with pytest.raises(Error, match="positive and even"):
+        kernels.ops.silu_mul(P, P, P, 17)
+    with pytest.raises(Error, match="positive and even"):
+        kernels.ops.silu_mul(P, P, P, 0)
+    with pytest.raises(Error, match="null"):
+        kernels.ops.add_f32(P, None, P, 4)
+    with pytest.raises(Error, match="positive"):
+        kernels.ops.add_f32(P, P, P, 0)
+    with pytest.raises(Error, match="multiple of 128"):
+        kernels.prefill_lin.reconstruct(P, P, 16, 100, 128, 0, 4, 2)
+    with pytest.raises(Error, match="exceeds"):
+        kernels.prefill_lin.reconstruct(P, P, 16, 256, 256, 128, 4, 2)
+    with pytest.raises(Error, match="multiple of 128"):
+        kernels.prefill_lin.had_r_128(P, P, None, True, 1, 100, False)
+
+
+def test_lm_head_tune_key_matches_berth(lib):
+    # crates/berth-kernels/src/lib.rs:224-233
+    assert kernels.gemm_tune_key(1, 5120, 248320, 6, 0, 0, 2, 82, int(Codebook.Mul1)) == 0x51F40C1BD7CAE3A7
+
+
+def test_exl3_gemv_cfg_matches_27b_shapes(lib):
+    # crates/berth-kernels/src/prefill_lin.rs:386-442
+    f = kernels.prefill_lin.exl3_gemv_cfg
+    AMP, ADA, MODE, K, CB, NARROW = 2, 3, 1, 4, 2, 164
+    for m in (3, 5, 8):
+        assert f(AMP, m, 5120, 17408, K, CB, MODE, NARROW) == -1
+        assert f(AMP, m, 17408, 5120, K, CB, MODE, NARROW) == 0
+        assert f(AMP, m, 6144, 5120, K, CB, MODE, NARROW) == 0
+        assert f(AMP, m, 10240, 5120, K, CB, MODE, NARROW) == 0
+    assert f(AMP, 9, 17408, 5120, K, CB, MODE, NARROW) == -1
+    assert f(AMP, 2, 17408, 5120, K, CB, MODE, NARROW) == 0
+    assert f(AMP, 3, 17408, 5120, K, CB, 0, NARROW) == -1
+    assert f(AMP, 3, 5120, 8192, K, CB, MODE, NARROW) == 1
+    assert f(ADA, 3, 5120, 8192, K, CB, MODE, NARROW) == -1
+
+
+def test_library_matches_oracle_on_host_logic(lib, oracle):
+    import itertools
+    for cc, m, k, n, bits, cb, mode in itertools.product((2, 3, 5), (1, 4, 9), (2048, 5120), (5120, 8192, 17408),
+                                                         (2, 3, 4, 5), (0, 2), (0, 1, 2, 3, 4)):
+        assert kernels.prefill_lin.exl3_gemv_cfg(cc, m, k, n, bits, cb, mode, 164) == oracle.gemv_cfg(
+            cc, m, k, n, bits, cb, mode, 164)
+    for m in (1, 2, 3, 16, 17, 31, 32, 63, 64, 127, 128, 4096):
+        assert kernels.gemm_tune_key(m, 5120, 6144, 4, 1, 0, 5, 148, 2) == oracle.gemm_tune_key(
+            m, 5120, 6144, 4, 1, 0, 5, 148, 2)
+
+
+def test_product_does_not_touch_the_oracle():
+    """Nothing under berth_b200/ may import, link or execute the CPU checker."""
+    pkg = os.path.join(ROOT, "berth_b200")
+    for dirpath, _, files in os.walk(pkg):
+        if os.path.basename(dirpath) == "build":
+            continue
+        for f in files:
+            if not f.endswith((".py", ".cu", ".cuh", ".cpp", ".h", "Makefile")):
+                continue
+            text = open(os.path.join(dirpath, f), errors="replace").read()
+            for needle in ("exl3o_", "import oracle", "from oracle", "libexl3_oracle"):
+                assert needle not in text, f"{f} references the oracle ({needle})"

@@ -1,0 +1,238 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle on the same seeded inputs.
+
+Integer/byte work (decoded weight tiles, rotated activations, silu_mul, add) must be
+bit-exact; fp32-accumulated linear outputs must be within max relative error 1e-2 and mean
+relative error 1e-3 of the fp64 evaluation, errors taken relative to the RMS of the fp64 output.
+"""
+import os
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from berth_b200 import Codebook, OutDtype, kernels, synth   # noqa: E402
+from tests.gpu_util import MAX_REL, MEAN_REL, dev, host_u16, rel_errors, run_linear   # noqa: E402
+
+
+# ---------------------------------------------------------------- decoded weight tiles: bit-exact
+
+@pytest.mark.parametrize("bits", [1, 2, 3, 4, 5, 6, 7, 8])
+@pytest.mark.parametrize("cb", [0, 1, 2])
+def test_reconstruct_bit_exact_small(oracle, bits, cb):
+    K, N = 128, 256
+    t = synth.trellis(1234, f"rec{bits}", K, N, bits)
+    out = torch.zeros((K, N), dtype=torch.float16, device="cuda")
+    kernels.prefill_lin.reconstruct(out, dev(t), K, N, N, 0, bits, cb)
+    exp = oracle.reconstruct(t, K, N, bits, cb).view(np.uint16)
+    assert int((host_u16(out) != exp).sum()) == 0
+
+
+def test_reconstruct_column_band(oracle):
+    K, N, bits, cb = 64, 640, 4, 2
+    t = synth.trellis(1234, "band", K, N, bits)
+    out = torch.zeros((K, 256), dtype=torch.float16, device="cuda")
+    kernels.prefill_lin.reconstruct(out, dev(t), K, 256, N, 384, bits, cb)
+    exp = oracle.reconstruct(t, K, N, bits, cb, n_offset=384, slice_n=256).view(np.uint16)
+    assert int((host_u16(out) != exp).sum()) == 0
+
+
+@pytest.mark.parametrize("cb", [0, 1, 2])
+def test_reconstruct_bit_exact_config0(oracle, cb):
+    """All 122,880 tiles of the 5120 x 6144, 4 bpw matrix."""
+    K, N, bits = 5120, 6144, 4
+    t = synth.trellis(1234, "c0.trellis", K, N, bits)
+    out = torch.zeros((K, N), dtype=torch.float16, device="cuda")
+    kernels.prefill_lin.reconstruct(out, dev(t), K, N, N, 0, bits, cb)
+    exp = oracle.reconstruct(t, K, N, bits, cb).view(np.uint16)
+    assert int((host_u16(out) != exp).sum()) == 0
+
+
+# ---------------------------------------------------------------- Hadamard: bit-exact
+
+@pytest.mark.parametrize("fp32", [False, True])
+@pytest.mark.parametrize("pre", [False, True])
+def test_had_r_128_bit_exact(oracle, fp32, pre):
+    rows, cols = 5, 640
+    x = synth.activations(7, "hadx", rows, cols)
+    sc = synth.sign_scale(7, "hads", cols)
+    xin = x.astype(np.float32) if fp32 else x
+    d_in = dev(xin)
+    d_out = torch.empty_like(d_in)
+    kernels.prefill_lin.had_r_128(d_in, d_out, dev(sc), pre, rows, cols, fp32)
+    exp = oracle.had_r_128(xin, sc, pre)
+    got = d_out.cpu().numpy()
+    if fp32:
+        assert (got.view(np.uint32) == exp.view(np.uint32)).all()
+    else:
+        assert (got.view(np.uint16) == exp.view(np.uint16)).all()
+    # in place
+    kernels.prefill_lin.had_r_128(d_in, d_in, dev(sc), pre, rows, cols, fp32)
+    assert torch.equal(d_in, d_out)
+
+
+# ---------------------------------------------------------------- silu_mul / add: bit-exact, golden
+
+def test_silu_mul_golden_and_oracle(oracle, golden_dir):
+    d = os.path.join(golden_dir, "berth_ops")
+    g = np.fromfile(os.path.join(d, "silu.gate.bin"), np.uint16)
+    u = np.fromfile(os.path.join(d, "silu.up.bin"), np.uint16)
+    o = np.fromfile(os.path.join(d, "silu.out.bin"), np.uint16)
+    dg, du = dev(g), dev(u)
+    out = torch.empty_like(dg)
+    kernels.ops.silu_mul(dg, du, out, g.size, 0.0)
+    assert int((host_u16(out) != o).sum()) == 0
+    # aliasing: out may be gate
+    kernels.ops.silu_mul(dg, du, dg, g.size, 0.0)
+    assert int((host_u16(dg) != o).sum()) == 0
+    # every finite fp16 gate value against the oracle, two different up values
+    allg = np.arange(65536, dtype=np.uint16)
+    fin = np.isfinite(allg.view(np.float16))
+    allg = allg[fin]
+    if allg.size & 1:
+        allg = allg[:-1]
+    for upv in (1.0, -0.3333):
+        up = np.full(allg.size, upv, np.float16)
+        out = torch.empty(allg.size, dtype=torch.float16, device="cuda")
+        kernels.ops.silu_mul(dev(allg), dev(up), out, allg.size, 0.0)
+        exp = oracle.silu_mul(allg, up).view(np.uint16)
+        got = host_u16(out)
+        both_nan = np.isnan(got.view(np.float16)) & np.isnan(exp.view(np.float16))
+        assert ((got == exp) | both_nan).all()
+    # clamp
+    x = synth.activations(3, "sg", 1, 4096).ravel() * np.float16(4)
+    y = synth.activations(3, "su", 1, 4096).ravel() * np.float16(4)
+    out = torch.empty(4096, dtype=torch.float16, device="cuda")
+    kernels.ops.silu_mul(dev(x), dev(y), out, 4096, 2.5)
+    assert (host_u16(out) == oracle.silu_mul(x, y, 2.5).view(np.uint16)).all()
+
+
+def test_add_f32_golden(golden_dir):
+    d = os.path.join(golden_dir, "berth_ops")
+    a = np.fromfile(os.path.join(d, "add.a.bin"), np.float32)
+    b = np.fromfile(os.path.join(d, "add.b.bin"), np.float32)
+    c = np.fromfile(os.path.join(d, "add.c.bin"), np.float32)
+    da, db = dev(a), dev(b)
+    kernels.ops.add_f32(da, db, da, a.size)   # c aliases a
+    assert (da.cpu().numpy().view(np.uint32) == c.view(np.uint32)).all()
+
+
+# ---------------------------------------------------------------- the linear
+
+@pytest.mark.parametrize("m", [1, 2, 5, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("bits,cb,out_fp32", [(4, 0, False), (4, 2, True), (3, 1, False), (5, 2, False), (6, 2, True)])
+def test_linear_small_vs_oracle(oracle, m, bits, cb, out_fp32):
+    K, N = 512, 384
+    w = synth.linear_weights(1234, f"lin{bits}{cb}", K, N, bits)
+    x = synth.activations(1234, f"x{m}", m, K)
+    c, ah = run_linear(x, w, bits, cb, out_fp32)
+    y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, N, bits, cb)
+    mx, mean = rel_errors(c, y64)
+    assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
+    exp_c, exp_ah = oracle.linear(x, w["trellis"], w["suh"], w["svh"], K, N, bits, cb, out_fp32)
+    assert (ah == exp_ah.view(np.uint16)).all()          # rotated activations: bit-exact
+    # against the fp32 oracle the only difference is summation order
+    rms = np.sqrt((y64 ** 2).mean())
+    assert np.abs(c.astype(np.float64) - exp_c.astype(np.float64)).max() <= 2e-3 * rms
+    assert "k_exl3_gemv" in kernels.last_launch()
+
+
+@pytest.mark.parametrize("bits", [1, 2, 7, 8])
+def test_linear_every_bitrate(oracle, bits):
+    K, N, m, cb = 256, 256, 3, 2
+    w = synth.linear_weights(1234, f"rate{bits}", K, N, bits)
+    x = synth.activations(1234, "xr", m, K)
+    c, _ = run_linear(x, w, bits, cb, True)
+    y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, N, bits, cb)
+    mx, mean = rel_errors(c, y64)
+    assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
+
+
+def test_linear_split_k_shapes(oracle):
+    """Tall (deep split-K, chunked activations) and wide (no split) shapes."""
+    for (K, N, m) in ((4096, 128, 4), (4352, 256, 32), (128, 2048, 1), (2176, 640, 17)):
+        w = synth.linear_weights(1234, f"sk{K}x{N}", K, N, 4)
+        x = synth.activations(1234, f"skx{K}", m, K)
+        c, ah = run_linear(x, w, 4, 0, False)
+        y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, N, 4, 0)
+        mx, mean = rel_errors(c, y64)
+        assert mx <= MAX_REL and mean <= MEAN_REL, (K, N, m, mx, mean)
+
+
+def test_linear_is_deterministic_and_counters_reset():
+    K, N, m = 2048, 512, 3
+    w = synth.linear_weights(1234, "det", K, N, 4)
+    x = synth.activations(1234, "detx", m, K)
+    first, _ = run_linear(x, w, 4, 1, True)
+    for _ in range(3):
+        again, _ = run_linear(x, w, 4, 1, True)
+        assert (again.view(np.uint32) == first.view(np.uint32)).all()
+
+
+@pytest.mark.parametrize("cb", [0, 2])
+def test_linear_config0_vs_oracle(oracle, cb):
+    """BASELINE configuration 0: in=5120, out=6144, 4 bpw, one fp16 row, fp16 out."""
+    K, N, bits = 5120, 6144, 4
+    w = synth.linear_weights(1234, "c0", K, N, bits)
+    x = synth.activations(1234, "c0.x", 1, K)
+    c, ah = run_linear(x, w, bits, cb, False)
+    y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, N, bits, cb)
+    mx, mean = rel_errors(c, y64)
+    assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
+    exp_ah = oracle.had_r_128(x, w["suh"], True)
+    assert (ah == exp_ah.view(np.uint16)).all()
+
+
+def test_prefill_entry_point_rows(oracle):
+    """berth_prefill_exl3_linear over row counts berth's prefill tests use (2, 47, 144, 145)."""
+    K, N, bits, cb = 256, 256, 4, 2
+    w = synth.linear_weights(1234, "pf", K, N, bits)
+    for m in (2, 47, 144, 145):
+        x = synth.activations(1234, f"pfx{m}", m, K)
+        c, ah = run_linear(x, w, bits, cb, m % 2 == 0, prefill=True)
+        y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, N, bits, cb)
+        mx, mean = rel_errors(c, y64)
+        assert mx <= MAX_REL and mean <= MEAN_REL, (m, mx, mean)
+        assert (ah == oracle.had_r_128(x, w["suh"], True).view(np.uint16)).all()
+
+
+# ---------------------------------------------------------------- full 27B shapes: properties
+
+def _torch_reference(x, w, bits, cb):
+    """y = H(H(x*suh) W) svh evaluated on the GPU in fp32/fp64 from the library's own bit-exact-checked
+    reconstruct output: a size-independent cross-check of the fused kernel at full size."""
+    K, N = w["size_k"], w["size_n"]
+    W = torch.empty((K, N), dtype=torch.float16, device="cuda")
+    kernels.prefill_lin.reconstruct(W, dev(w["trellis"]), K, N, N, 0, bits, cb)
+    H = torch.tensor([[1.0]], dtype=torch.float64, device="cuda")
+    while H.shape[0] < 128:
+        H = torch.cat([torch.cat([H, H], 1), torch.cat([H, -H], 1)], 0)
+    H = H / (128.0 ** 0.5)
+    xs = dev(x).double() * dev(w["suh"]).double()
+    ah = (xs.view(-1, K // 128, 128) @ H).view(-1, K)
+    c = ah @ W.double()
+    y = (c.view(-1, N // 128, 128) @ H).view(-1, N) * dev(w["svh"]).double()
+    return y.cpu().numpy()
+
+
+@pytest.mark.parametrize("name,K,N,out_fp32", [("gate", 5120, 17408, False), ("down", 17408, 5120, True),
+                                               ("k", 5120, 1024, False), ("o", 6144, 5120, True)])
+@pytest.mark.parametrize("m", [1, 8, 32])
+def test_linear_27b_shapes_full_size(name, K, N, out_fp32, m):
+    bits, cb = 4, 2
+    w = synth.linear_weights(1234, f"l0.{name}", K, N, bits)
+    x = synth.activations(1234, f"l0.{name}.x", m, K)
+    c, _ = run_linear(x, w, bits, cb, out_fp32)
+    y64 = _torch_reference(x, w, bits, cb)
+    mx, mean = rel_errors(c, y64)
+    assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
+    # linearity in the activations: f(x1 + x2) = f(x1) + f(x2) up to rounding
+    if m == 1:
+        x2 = synth.activations(1234, f"l0.{name}.x2", 1, K)
+        c2, _ = run_linear(x2, w, bits, cb, True)
+        c1, _ = run_linear(x, w, bits, cb, True)
+        xs = (x.astype(np.float32) + x2.astype(np.float32)).astype(np.float16)
+        cs, _ = run_linear(xs, w, bits, cb, True)
+        rms = np.sqrt((cs.astype(np.float64) ** 2).mean())
+        assert np.abs(cs - (c1 + c2)).max() <= 5e-3 * rms
