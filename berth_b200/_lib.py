@@ -26,6 +26,7 @@ class MoeWeights(C.Structure):
 # name -> (restype, argtypes); every symbol the header declares.
 SIGNATURES = {
     "berth_exl3_linear": (_i, [_vp] * 6 + [_i] * 6 + [_vp]),
+    "berth_exl3_linear_static_scratch": (_i, [_vp] * 6 + [_i] * 6 + [_vp]),
     "berth_exl3_last_error": (C.c_char_p, []),
     "berth_exl3_last_launch": (C.c_char_p, []),
     "berth_device_cc": (_i, [_i]),

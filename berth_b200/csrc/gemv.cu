@@ -16,6 +16,7 @@
 #include "../../include/berth_b200.h"
 
 #include <algorithm>
+#include <mutex>
 
 namespace berth {
 namespace {
@@ -308,3 +309,88 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
 }
 
 }  // namespace berth
+
+// ------------------------------------------------------------------------------------------
+// Decode linear for callers that must not allocate device memory.
+//
+// Who needs it: a host that has already handed every byte of HBM to its own planner (berth's
+// placement plan budgets the whole device), or a decode loop that cannot afford the implicit
+// device-wide synchronisation of cudaMalloc on its first launch.  The ordinary entry point
+// creates its split-K workspace with cudaMalloc at the first launch on a device; this one
+// keeps a fixed scratch area inside the library image instead, so it never calls cudaMalloc,
+// cudaFree or any allocating routine.
+//
+// The scratch is one file-scope __device__ array: kStaticPartialBytes of fp32 partial sums plus
+// one arrival counter per 128-column band.  Every GPU that loads the library carries it until
+// the process exits.  All calls on a device share it and it keeps whatever the previous call
+// left behind: the counters are cleared on the stream before each launch, the partial sums are
+// fully overwritten before they are read.  Two calls that overlap on the GPU (different
+// streams) race on it; issue them on one stream.
+namespace berth {
+namespace {
+
+constexpr size_t kStaticPartialBytes = size_t(4) << 20;   // 4 MiB of split-K partial sums
+constexpr int kStaticMaxBands = 1024;                     // size_n <= 131072
+constexpr int kStaticMaxRows = 32;
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticPartialBytes + kStaticMaxBands * sizeof(unsigned)];
+
+struct StaticScratch {
+    float* partial = nullptr;
+    unsigned* counters = nullptr;
+};
+StaticScratch g_static_ptr[kMaxDevices];
+std::mutex g_static_mu;
+
+// The array's name is only a host-side handle; the device address has to be asked for, once
+// per device, while that device is current.
+StaticScratch static_scratch(int device)
+{
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    StaticScratch& s = g_static_ptr[device];
+    if (!s.partial) {
+        void* base = nullptr;
+        cuda_ok(cudaGetSymbolAddress(&base, g_static_scratch), "cudaGetSymbolAddress(static scratch)");
+        if (!base) throw std::runtime_error("exl3 linear (static scratch): symbol address is null");
+        s.partial = static_cast<float*>(base);
+        s.counters = reinterpret_cast<unsigned*>(static_cast<unsigned char*>(base) + kStaticPartialBytes);
+    }
+    return s;
+}
+
+}  // namespace
+}  // namespace berth
+
+extern "C" int berth_exl3_linear_static_scratch(const void* a, const void* trellis, void* c, const void* suh,
+                                                void* a_had, const void* svh, int size_m, int size_k, int size_n,
+                                                int k_bits, int codebook, int out_fp32, void* stream)
+{
+    using namespace berth;
+    CallState& st = exl3_state();
+    return guarded(st, [&] {
+        if (!a || !trellis || !c || !suh || !a_had || !svh) throw std::runtime_error("exl3 linear: null device pointer");
+        if (size_m < 1 || size_k < 1 || size_n < 1) throw std::runtime_error("exl3 linear: sizes must be positive");
+        if (k_bits < 1 || k_bits > 8) throw std::runtime_error("exl3 linear: K must be in 1..=8");
+        if (codebook < 0 || codebook > 2)
+            throw std::runtime_error("exl3 linear: codebook must be 0 (default), 1 (mcg), or 2 (mul1)");
+        if (size_k % 16 != 0) throw std::runtime_error("exl3 linear: size_k must be a multiple of 16");
+        if (size_n % 128 != 0) throw std::runtime_error("exl3 linear: size_n must be a multiple of 128");
+        if (size_m > kStaticMaxRows)
+            throw std::runtime_error("exl3 linear (static scratch): size_m " + std::to_string(size_m) +
+                                     " exceeds the maximum of " + std::to_string(kStaticMaxRows) + " rows");
+        if (size_n / 128 > kStaticMaxBands)
+            throw std::runtime_error("exl3 linear (static scratch): size_n " + std::to_string(size_n) +
+                                     " exceeds the maximum of " + std::to_string(kStaticMaxBands * 128) + " columns");
+        const int device = current_device();
+        const DeviceInfo& info = device_info(device);
+        if (info.major != 10)
+            throw std::runtime_error("exl3 linear: no linked kernel for this GPU (library is built for sm_100a only)");
+        StaticScratch s = static_scratch(device);
+        cudaStream_t cs = (cudaStream_t) stream;
+        // Arrival counters must start at zero; the partial sums need no clearing.
+        cuda_ok(cudaMemsetAsync(s.counters, 0, size_t(size_n / 128) * sizeof(unsigned), cs), "static scratch counter reset");
+        st.launch = launch_gemv(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, out_fp32,
+                                s.partial, kStaticPartialBytes, s.counters, info.sms, cs) + " static-scratch";
+    });
+}
+

@@ -69,6 +69,20 @@ def exl3_linear(a, trellis, c, suh, a_had, svh, size_m: int, size_k: int, size_n
         raise Error(last_error() or f"exl3 linear launch failed ({rc})")
 
 
+def exl3_linear_static_scratch(a, trellis, c, suh, a_had, svh, size_m: int, size_k: int, size_n: int, k_bits: int,
+                               codebook: Codebook, out: OutDtype, stream=None) -> None:
+    """:func:`exl3_linear` for hosts that must not allocate device memory (their own planner owns
+    all of HBM, or the decode loop cannot take a ``cudaMalloc`` stall): the split-K scratch is a
+    fixed 4 MiB array inside the library, shared by every call on the device.  ``size_m <= 32``,
+    ``size_n <= 131072``; calls must not overlap on the GPU; make the first call on a device before
+    any stream capture."""
+    rc = _lib.lib().berth_exl3_linear_static_scratch(_ptr(a), _ptr(trellis), _ptr(c), _ptr(suh), _ptr(a_had),
+                                                     _ptr(svh), size_m, size_k, size_n, k_bits, int(codebook),
+                                                     int(out), _stream(stream))
+    if rc != 0:
+        raise Error(last_error() or f"exl3 linear (static scratch) launch failed ({rc})")
+
+
 def device_cc(device: int) -> int:
     return _lib.lib().berth_device_cc(device)
 

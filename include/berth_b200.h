@@ -51,6 +51,21 @@ int berth_exl3_linear(const void* a, const void* trellis, void* c, const void* s
 const char* berth_exl3_last_error(void);    /* crates/berth-kernels/csrc/linear.cu:396-399 */
 const char* berth_exl3_last_launch(void);   /* crates/berth-kernels/csrc/linear.cu:401-404 */
 
+/* Same linear for callers that must not allocate device memory (a host whose own planner owns
+ * every byte of HBM, or a decode loop that cannot take cudaMalloc's device-wide synchronisation).
+ * No counterpart in berth: its library allocates its workspaces with cudaMalloc at first use.
+ * The split-K scratch is a fixed 4 MiB + 4 KiB __device__ array inside the library image, held by
+ * every GPU that loads the library until the process exits; nothing is allocated or freed.
+ * Limits: size_m <= 32 and size_n <= 131072, larger sizes are rejected with an error.  The first
+ * call on a device looks the array's device address up (cudaGetSymbolAddress); make that first
+ * call before any stream capture begins.  All calls on a device share the scratch, which keeps
+ * the previous call's contents (the counters are cleared on `stream` before each launch): calls
+ * that overlap on the GPU race, so issue them on one stream. */
+int berth_exl3_linear_static_scratch(const void* a, const void* trellis, void* c, const void* suh,
+                                     void* a_had, const void* svh, int size_m, int size_k,
+                                     int size_n, int k_bits, int codebook, int out_fp32,
+                                     void* stream);
+
 /* Device queries of crates/berth-kernels/csrc/internal.h:11-13 (class 1..5 as the fork's CC_*
  * enumeration orders them: old, Ampere, Ada, Hopper, Blackwell; SM count). -1 on error. */
 int berth_device_cc(int device);
