@@ -41,8 +41,8 @@ LAYERS = 4
 METRIC = "exl3_gemv_eff_hbm_gbs"
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_exl3_gemv launch on the gate shape
-# (5120x17408, 4 bpw, m=1), from the ncu capture summarised under profiles/.  None until captured.
-NCU_TRAFFIC_GATE_BYTES = None
+# (5120x17408, 4 bpw, m=1), from the ncu capture summarised in profiles/k_exl3_gemv_c1_dense_decode_m1.md.
+NCU_TRAFFIC_GATE_BYTES = 44_738_560   # 44.72 MB read + 15 KB written
 
 
 def linear_bytes(k: int, n: int, m: int, fp32: int, bits: int = BITS) -> int:
@@ -148,7 +148,7 @@ class DecodeStack:
         self.h_o = torch.empty((m, HIDDEN), dtype=f32).pin_memory()
         self.h2d_bytes = 2 * m * (HIDDEN + HIDDEN + QDIM)
         self.d2h_bytes = m * (4 * HIDDEN + 2 * QDIM + 4 * KVDIM + 4 * HIDDEN)
-        self.launches_per_step = 8   # 7 x k_exl3_gemv + 1 x k_silu_mul
+        self.launches_per_step = 15   # 7 x (k_rotate_in + k_exl3_gemv) + 1 x k_silu_mul
 
     def step(self, i: int) -> None:
         from berth_b200.kernels import OutDtype

@@ -31,6 +31,7 @@ SIGNATURES = {
     "berth_exl3_last_launch": (C.c_char_p, []),
     "berth_device_cc": (_i, [_i]),
     "berth_device_sms": (_i, [_i]),
+    "berth_device_status": (_i, [_i]),
     "berth_exl3_gemm_tune_key": (_u64, [_i] * 9),
     "berth_exl3_smoke_int8": (_i, [_i]),
     "berth_exl3_smoke_gemm": (_i, []),

@@ -61,16 +61,31 @@ struct DeviceInfo {
 const DeviceInfo& device_info(int device);
 int current_device();
 
-// Split-K workspace of the decode GEMV: fp32 partial sums + one arrival counter per 128-column
-// band.  Allocated once per device at first use, never grown, never freed
-// (cf. crates/berth-kernels/csrc/int8_sq.cu:20-47).
-constexpr size_t kGemvWorkspaceBytes = size_t(32) << 20;
-constexpr int kGemvMaxBands = 1 << 16;
-struct GemvWorkspace {
-    float* partial = nullptr;
+// Scratch of the decode GEMV: fp32 partial-sum slabs (two [m][128] slabs per CTA), arrival counters
+// (four per band group, zero between launches), one fp32 sum per (row, 128 rotated
+// inputs), and a status word that collects bounded-wait failures.
+struct GemvScratch {
+    float* slabs = nullptr;
+    size_t slab_bytes = 0;
     unsigned* counters = nullptr;
+    int counter_slots = 0;
+    uint32_t* afrag = nullptr;     // rotated activations in MMA fragment order
+    size_t afrag_bytes = 0;
+    float* blocksum = nullptr;
+    size_t blocksum_floats = 0;
+    unsigned* status = nullptr;
 };
-GemvWorkspace gemv_workspace(int device);
+// The library's own scratch: allocated once per device at first use, never grown, never freed
+// (cf. crates/berth-kernels/csrc/int8_sq.cu:20-47 of berth).
+constexpr size_t kGemvSlabBytes = size_t(32) << 20;
+constexpr int kGemvCounterSlots = 1 << 16;
+constexpr size_t kGemvBlocksumFloats = size_t(32) * 4096;
+constexpr size_t kGemvAfragBytes = size_t(8) << 20;   // size_k * ceil(size_m / 8) <= 524288
+GemvScratch gemv_workspace(int device);
+
+std::string launch_gemv(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
+                        int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32,
+                        const GemvScratch& scratch, int sms, cudaStream_t stream);
 
 constexpr float kRScale = 0.088388347648f;  // 1/sqrt(128), csrc/prefill_lin/reconstruct.cu:43-44
 

@@ -10,7 +10,8 @@
 //     of an m16n8k16 A fragment of the transposed tile (row index = weight column);
 //   * codebook 0 (3INST): x = s*89226354 + 64248484; x = (x & 0x8fff8fff) ^ 0x3b603b60;
 //     w = half(x.lo) + half(x.hi);  codebook 1 (MCG): x = s*0xCBAC1FED, same tail;
-//     codebook 2 (MUL1): x = s*0x83DCD12D, u = byte sum of x, w = fma(half(u), S, B) in fp16.
+//     codebook 2 (MUL1): x = s*0x83DCD12D, u = byte sum of x, h = fp16 with bits 0x6400+u
+//     (= 1024+u), w = fma(h, S, B) in fp16.
 #pragma once
 
 #include "common.cuh"
@@ -20,7 +21,7 @@ namespace dq {
 
 constexpr unsigned kFull = 0xffffffffu;
 constexpr unsigned short kMul1S = 0x1EEE;  // 1/147.8
-constexpr unsigned short kMul1B = 0xC2E7;  // -510/147.8
+constexpr unsigned short kMul1B = 0xC931;  // -(1024+510)/147.8
 
 __device__ __forceinline__ uint32_t lop3_mask_xor(uint32_t x)
 {
@@ -38,10 +39,11 @@ __device__ __forceinline__ uint32_t mix32(uint32_t s)
     return lop3_mask_xor(x);
 }
 
-// Byte sum of the MUL1 product (0..1020).
-__device__ __forceinline__ uint32_t mul1_sum(uint32_t s)
+// fp16 bit pattern of 1024 + (byte sum of the MUL1 product): 0x6400 is 1024.0 with a unit in the
+// last place of 1, so adding the sum (0..1020) to the pattern adds it to the value.
+__device__ __forceinline__ uint32_t mul1_h1024(uint32_t s)
 {
-    return __dp4a(s * 0x83DCD12Du, 0x01010101u, 0u);
+    return __dp4a(s * 0x83DCD12Du, 0x01010101u, 0x6400u);
 }
 
 // One state -> one fp16 weight, bit-exact with the specification.
@@ -49,7 +51,7 @@ template <int CB>
 __device__ __forceinline__ __half decode(uint32_t s)
 {
     if constexpr (CB == 2) {
-        return __hfma(__uint2half_rn(mul1_sum(s)), __ushort_as_half(kMul1S), __ushort_as_half(kMul1B));
+        return __hfma(__ushort_as_half((unsigned short) mul1_h1024(s)), __ushort_as_half(kMul1S), __ushort_as_half(kMul1B));
     } else {
         uint32_t x = mix32<CB>(s);
         __half2 h = *reinterpret_cast<__half2*>(&x);

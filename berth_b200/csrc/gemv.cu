@@ -1,311 +1,725 @@
-// Fused EXL3 decode GEMV (size_m <= 32): input Hadamard, trellis decode in registers, tensor-core
-// accumulate, split-K reduction by the last CTA to arrive, output Hadamard -- one launch.
-//
-// Work decomposition: grid = (N/128 column bands, KSPLIT).  A CTA of 8 warps owns one band over
-// a contiguous range of 128-row blocks; warp w owns the tile column w of the band (16 columns)
-// for every k-tile of the range, so no cross-warp reduction is needed: each warp reads one
-// 16*BITS*2-byte tile per k-tile (eight warps together read one contiguous 8-tile run), decodes
-// its eight weights per lane into an m16n8k16 A fragment (transposed tile: rows = weight
-// columns) and multiplies by the rotated activations held in shared memory (B fragment, 8
-// tokens per MMA).  Partial sums go to a per-split slab of the workspace; the CTA that arrives
-// last on the band's counter adds the slabs in split order (deterministic), applies the output
-// Hadamard and the svh sign-scale and writes C.
+// Fused EXL3 decode GEMV (size_m <= 32): trellis tiles streamed through shared memory by TMA,
+// decoded in registers, accumulated on the tensor cores, split-K reduced by whoever arrives
+// last, rotated back (128-wide Hadamard) and scaled -- one persistent launch, preceded by a
+// tiny rotation kernel for the activations.
 //
 // Roofline: HBM.  Algorithmic bytes per launch = K*N*BITS/8 + 2K + 2N + 2MK + out_bytes*M*N.
+// At 4 bits per weight the roofline asks for ~36 weights per cycle per SM, while the two
+// integer pipes of an SM (ALU: lop3/prmt/shf; FMA-heavy: imad/dp4a/dp2a) issue 2 warp
+// instructions per cycle each, so the design goal is the fewest integer instructions per
+// weight, spread evenly over both pipes:
+//   * window extraction for 4-bit tiles with byte permutes: 13 operations for 8 windows;
+//   * 3INST / MCG: multiply(-add) + one lop3 per weight, and NO half add: the two fp16 halves of
+//     the codebook word are fed to the MMA as two k-slots against a duplicated activation, so
+//     the tensor core performs lo + hi (fp32, exact) -- 2 MMAs per 16x16 tile per 8 tokens;
+//   * MUL1: multiply + dp4a with accumulator 0x6400 yields the fp16 bits of 1024 + byte sum;
+//     the affine map w = S*h + B is applied once per output in the epilogue
+//     (S*acc + B*sum(x)), not per weight -- 1 MMA per tile.
+//
+// Work decomposition: "units" of 128 rows x BU*128 columns (8 k-tile rows; BU = 2 bands below
+// 8 bits so that one k-tile row of a unit is a >= 2 KiB contiguous run, which is what the TMA
+// engine needs to stream near HBM speed) ordered band-group-major; CTA c of G (= number of SMs)
+// takes the contiguous unit range [c*U/G, (c+1)*U/G), so every SM streams the same number of
+// bytes with no tail wave.  A range covers at most one partial band group at its head and one
+// at its tail; those are reduced through slabs (2 per CTA) and arrival counters: whoever
+// arrives last sums the slabs in CTA order -- deterministic, and nothing ever waits on a peer.
+//
+// Inside a CTA (21 warps, one CTA per SM):
+//   warp 16      producer: one lane issues one 2-D TMA copy (8 rows x one run) per unit into a
+//                ring of unit-sized stages guarded by full/empty mbarriers;
+//   warps 0..15  consumers: a warp owns NT tile columns and every RW-th k-tile row of every
+//                unit, keeping NT*TG*4 fp32 accumulators per lane (TG token groups of 8 for
+//                m <= 8, 16, 32); at the end of a segment it dumps them into a double-buffered
+//                shared slab and carries on -- consumers never meet at a barrier;
+//   warps 17..20 epilogue: reduce the dumped slabs in fixed order, write/arrive on the split-K
+//                slabs or finish the bands (MUL1 affine correction, Hadamard, svh, store), in
+//                the background of the streaming warps.
+// Every mbarrier wait is bounded; a wait that runs out sets a status bit and carries on.
 #include "exl3_decode.cuh"
 #include "../../include/berth_b200.h"
+
+#include <cuda.h>
 
 #include <algorithm>
 #include <mutex>
 
 namespace berth {
+
+// ---------------------------------------------------------------- partition (host + device)
+__host__ __device__ inline long long unit_begin(int c, long long U, int G) { return (long long) c * U / G; }
+__host__ __device__ inline int unit_owner(long long u, long long U, int G) { return int(((u + 1) * G + U - 1) / U) - 1; }
+
 namespace {
 
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
-constexpr int kPrefetch = 8;  // k-tiles in flight per warp
+constexpr int kConsumerWarps = 16;
+constexpr int kEpiWarps = 4;
+constexpr int kProducerWarp = kConsumerWarps;
+constexpr int kThreads = (kConsumerWarps + 1 + kEpiWarps) * 32;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kRingBytes = 96 * 1024;
+constexpr long long kWaitCycles = 500000000LL;
+
+enum StatusBits : unsigned { kStFullTimeout = 1u, kStEmptyTimeout = 2u, kStRedFullTimeout = 4u, kStRedEmptyTimeout = 8u };
+
+// Compile-time geometry of a (BITS, TG) instance.
+template <int BITS, int TG>
+struct Geo {
+    static constexpr int NW = 8 * BITS;                       // 32-bit words per tile
+    static constexpr int BU = BITS <= 4 ? 2 : 1;              // bands per unit (a TMA box row holds at most 256 8-byte elements)
+    static constexpr int TILE_COLS = 8 * BU;
+    static constexpr int ROW_BYTES = TILE_COLS * NW * 4;      // one k-tile row of a unit
+    static constexpr int W_BYTES = 8 * ROW_BYTES;             // trellis bytes of a unit
+    static constexpr int ACT_BYTES = 8 * TG * 256;            // fragment-ordered activations of a unit
+    static constexpr int STAGE_BYTES = W_BYTES + ACT_BYTES;
+    static constexpr int S = kRingBytes / STAGE_BYTES;        // ring depth
+    static constexpr int NT = 4 / TG;                         // tile columns per consumer warp
+    static constexpr int CG = TILE_COLS / NT;                 // column groups
+    static constexpr int RW = kConsumerWarps / CG;            // row streams
+    static constexpr int RPW = 8 / RW;                        // k-tile rows per warp per unit
+    static constexpr int TOK = 8 * TG;
+    static constexpr int PITCH = BU * 128 + 4;                // floats per token row in shared slabs
+    static constexpr int RED_SLAB = TOK * PITCH;
+    static constexpr size_t SMEM = size_t(kRingBytes) + size_t(2 * RW + 1) * RED_SLAB * 4 + size_t(2 * S + 4) * 8;
+    static_assert(S >= 2 && RW >= 1 && RW * RPW == 8 && CG * RW == kConsumerWarps, "geometry");
+};
 
 struct GemvArgs {
-    const __half* a;
-    const uint32_t* trellis;
+    const uint32_t* afrag;    // rotated activations in MMA fragment order [k/16][TG][2][8][4] words
+    const float* blocksum;    // [m][k/128]: sum of each rotated 128-block (MUL1 epilogue)
     void* c;
-    const __half* suh;
-    __half* a_had;
     const __half* svh;
-    float* ws;
-    unsigned* counters;
-    int m, k, n;
-    int out_fp32;
-    int kb_per_split;  // 128-row blocks per split
-    int ksplit;
-    int chunk_kb;      // 128-row blocks whose rotated activations fit in shared memory at once
+    float* slabs;             // [2*G][m][BU*128]
+    unsigned* counters;       // [band groups][kEpiWarps], zero between launches
+    unsigned* status;
+    int m, k, n, out_fp32;
 };
 
-template <int MG>
-struct Smem {
-    // rotated activations [8*MG][chunk_k + 8] fp16, then the band's partial sums [8*MG][132] fp32
-    static __host__ __device__ int ah_stride(int chunk_k) { return chunk_k + 8; }
-    static __host__ __device__ size_t bytes(int chunk_k)
-    {
-        return size_t(8 * MG) * ah_stride(chunk_k) * sizeof(__half) + size_t(8 * MG) * 132 * sizeof(float);
-    }
-};
+// ---------------------------------------------------------------- mbarrier / TMA PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
 
-template <int BITS, int CB, int MG>
-__global__ void __launch_bounds__(kThreads) k_exl3_gemv(const GemvArgs p)
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    constexpr int NW = 8 * BITS;                     // raw 32-bit words per tile
-    constexpr int NL = dq::LaneWords<BITS>::value;   // words a lane needs per tile
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int band = blockIdx.x, split = blockIdx.y;
-    const int kblocks = p.k >> 7;
-    const int kb0 = split * p.kb_per_split;
-    const int kb1 = min(kb0 + p.kb_per_split, kblocks);
-    const int chunk_k = p.chunk_kb * 128;
-    const int ahs = Smem<MG>::ah_stride(chunk_k);
-    __half* ah = reinterpret_cast<__half*>(smem_raw);
-    float* outbuf = reinterpret_cast<float*>(smem_raw + size_t(8 * MG) * ahs * sizeof(__half));
-    const uint32_t* ah32 = reinterpret_cast<const uint32_t*>(ah);
-    const int ahs32 = ahs >> 1;
-    const int tiles_n = p.n >> 4;
-    const int g = lane >> 2, q = lane & 3;
-
-    int lw, lr;
-    dq::lane_span<BITS>(lane, lw, lr);
-    int lw1 = lw + 1; if (lw1 >= NW) lw1 -= NW;
-    int lw2 = lw1 + 1; if (lw2 >= NW) lw2 -= NW;
-
-    float acc[MG][4];
-#pragma unroll
-    for (int i = 0; i < MG; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
-
-    for (int kb = kb0; kb < kb1; kb += p.chunk_kb) {
-        const int nkb = min(p.chunk_kb, kb1 - kb);
-        __syncthreads();  // the previous chunk's readers are done with `ah`
-        // ---- rotated activations of this chunk: one warp per (token row, 128-block)
-        for (int idx = warp; idx < 8 * MG * nkb; idx += kWarps) {
-            const int row = idx / nkb, b = idx - row * nkb;
-            const int kcol = (kb + b) * 128 + lane * 4;
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (row < p.m) {
-                uint2 xr = *reinterpret_cast<const uint2*>(p.a + size_t(row) * p.k + kcol);
-                uint2 sr = *reinterpret_cast<const uint2*>(p.suh + kcol);
-                __half2 x0 = *reinterpret_cast<__half2*>(&xr.x), x1 = *reinterpret_cast<__half2*>(&xr.y);
-                __half2 s0 = *reinterpret_cast<__half2*>(&sr.x), s1 = *reinterpret_cast<__half2*>(&sr.y);
-                v[0] = __fmul_rn(__low2float(x0), __low2float(s0));
-                v[1] = __fmul_rn(__high2float(x0), __high2float(s0));
-                v[2] = __fmul_rn(__low2float(x1), __low2float(s1));
-                v[3] = __fmul_rn(__high2float(x1), __high2float(s1));
-                dq::had128_warp(v, lane);
-            }
-            uint2 o;
-            o.x = dq::pack_half2(__float2half_rn(__fmul_rn(v[0], kRScale)), __float2half_rn(__fmul_rn(v[1], kRScale)));
-            o.y = dq::pack_half2(__float2half_rn(__fmul_rn(v[2], kRScale)), __float2half_rn(__fmul_rn(v[3], kRScale)));
-            *reinterpret_cast<uint2*>(ah + size_t(row) * ahs + b * 128 + lane * 4) = o;
-            if (band == 0 && row < p.m) *reinterpret_cast<uint2*>(p.a_had + size_t(row) * p.k + kcol) = o;
-        }
-        __syncthreads();
-
-        // ---- main loop: this warp's tile column over the chunk's k-tiles
-        const int nkt = nkb * 8;
-        const uint32_t* tp = p.trellis + (size_t(kb) * 8 * tiles_n + band * 8 + warp) * NW;
-        const size_t tstride = size_t(tiles_n) * NW;  // words between consecutive k-tiles
-        uint32_t buf[kPrefetch][NL];
-#pragma unroll
-        for (int i = 0; i < kPrefetch; ++i) {
-            if (i < nkt) {
-                const uint32_t* t = tp + i * tstride;
-                buf[i][0] = __ldcs(t + lw);
-                if constexpr (BITS != 4) buf[i][1] = __ldcs(t + lw1);
-                if constexpr (NL > 2) buf[i][2] = __ldcs(t + lw2);
-            }
-        }
-        for (int kt0 = 0; kt0 < nkt; kt0 += kPrefetch) {
-#pragma unroll
-            for (int i = 0; i < kPrefetch; ++i) {
-                const int kt = kt0 + i;
-                if (kt < nkt) {
-                    uint32_t r0 = buf[i][0], r1, r2 = 0;
-                    if constexpr (BITS == 4) r1 = __shfl_sync(dq::kFull, r0, (lane + 1) & 31);
-                    else r1 = buf[i][1];
-                    if constexpr (NL > 2) r2 = buf[i][2];
-                    // refill this slot with the tile kPrefetch k-tiles ahead
-                    if (kt + kPrefetch < nkt) {
-                        const uint32_t* t = tp + size_t(kt + kPrefetch) * tstride;
-                        buf[i][0] = __ldcs(t + lw);
-                        if constexpr (BITS != 4) buf[i][1] = __ldcs(t + lw1);
-                        if constexpr (NL > 2) buf[i][2] = __ldcs(t + lw2);
-                    }
-                    uint32_t s[8], af[4];
-                    dq::lane_states_regs<BITS>(r0, r1, r2, lane, s);
-                    dq::decode_frag<CB>(s, af);
-                    const int kw = kt * 8 + q;  // 32-bit word of (k = 16*kt + 2q) in a row of `ah`
-#pragma unroll
-                    for (int mg = 0; mg < MG; ++mg) {
-                        const uint32_t b0 = ah32[(mg * 8 + g) * ahs32 + kw];
-                        const uint32_t b1 = ah32[(mg * 8 + g) * ahs32 + kw + 4];
-                        dq::mma_16816(acc[mg], af, b0, b1);
-                    }
-                }
-            }
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after kWaitCycles SM clocks (a quarter of a second at 2 GHz), records
+// `code` in the status word and returns false; the caller carries on with whatever is there.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned* status, unsigned code)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > kWaitCycles) {
+            atomicOr(status, code);
+            return false;
         }
     }
+    return true;
+}
+// One box of the 2-D trellis view (x in 8-byte elements, y in k-tile rows) into shared memory.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+// Contiguous global -> shared bulk copy (16-byte aligned, size a multiple of 16).
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void epi_sync()
+{
+    asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-    // ---- band partial sums to shared memory: D[n][tok], n = 16*warp + {g, g+8}, tok = 8*mg + {2q, 2q+1}
-#pragma unroll
-    for (int mg = 0; mg < MG; ++mg) {
-        const int t0 = mg * 8 + 2 * q, c0 = warp * 16 + g;
-        outbuf[t0 * 132 + c0] = acc[mg][0];
-        outbuf[(t0 + 1) * 132 + c0] = acc[mg][1];
-        outbuf[t0 * 132 + c0 + 8] = acc[mg][2];
-        outbuf[(t0 + 1) * 132 + c0 + 8] = acc[mg][3];
-    }
-    __syncthreads();
-
-    if (p.ksplit > 1) {
-        // slab [split][m][n]; 32 lanes x float4 = one 128-column row
-        for (int row = warp; row < p.m; row += kWarps) {
-            float4 v = *reinterpret_cast<const float4*>(outbuf + row * 132 + lane * 4);
-            __stcg(reinterpret_cast<float4*>(p.ws + (size_t(split) * p.m + row) * p.n + band * 128 + lane * 4), v);
-        }
-        __threadfence();
-        __syncthreads();
-        __shared__ unsigned s_last;
-        if (threadIdx.x == 0) s_last = (atomicAdd(p.counters + band, 1u) == unsigned(p.ksplit - 1));
-        __syncthreads();
-        if (!s_last) return;
-        __threadfence();
-    }
-
-    // ---- epilogue (last CTA of the band): sum the slabs in split order, rotate, scale, store
-    for (int row = warp; row < p.m; row += kWarps) {
-        float v[4];
-        if (p.ksplit > 1) {
-            v[0] = v[1] = v[2] = v[3] = 0.f;
-            for (int s = 0; s < p.ksplit; ++s) {
-                float4 t = __ldcg(reinterpret_cast<const float4*>(p.ws + (size_t(s) * p.m + row) * p.n + band * 128 + lane * 4));
-                v[0] = __fadd_rn(v[0], t.x); v[1] = __fadd_rn(v[1], t.y);
-                v[2] = __fadd_rn(v[2], t.z); v[3] = __fadd_rn(v[3], t.w);
-            }
-        } else {
-            float4 t = *reinterpret_cast<const float4*>(outbuf + row * 132 + lane * 4);
-            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-        }
-        dq::had128_warp(v, lane);
-        const int col = band * 128 + lane * 4;
-        uint2 sr = *reinterpret_cast<const uint2*>(p.svh + col);
-        __half2 s0 = *reinterpret_cast<__half2*>(&sr.x), s1 = *reinterpret_cast<__half2*>(&sr.y);
-        v[0] = __fmul_rn(__fmul_rn(v[0], kRScale), __low2float(s0));
-        v[1] = __fmul_rn(__fmul_rn(v[1], kRScale), __high2float(s0));
-        v[2] = __fmul_rn(__fmul_rn(v[2], kRScale), __low2float(s1));
-        v[3] = __fmul_rn(__fmul_rn(v[3], kRScale), __high2float(s1));
-        if (p.out_fp32) {
-            *reinterpret_cast<float4*>(static_cast<float*>(p.c) + size_t(row) * p.n + col) = make_float4(v[0], v[1], v[2], v[3]);
-        } else {
-            uint2 o;
-            o.x = dq::pack_half2(__float2half_rn(v[0]), __float2half_rn(v[1]));
-            o.y = dq::pack_half2(__float2half_rn(v[2]), __float2half_rn(v[3]));
-            *reinterpret_cast<uint2*>(static_cast<__half*>(p.c) + size_t(row) * p.n + col) = o;
-        }
-    }
-    if (p.ksplit > 1 && threadIdx.x == 0) p.counters[band] = 0;  // self-resetting for the next launch
+// ---------------------------------------------------------------- per-tile decode + MMA
+// Half-word selection on the FMA-heavy pipe: dp2a.lo(a, b) = a.h0*b.byte0 + a.h1*b.byte1.
+__device__ __forceinline__ uint32_t lo16_heavy(uint32_t a)
+{
+    uint32_t d;
+    asm("dp2a.lo.u32.u32 %0, %1, 0x0001, 0;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ uint32_t hi16_heavy(uint32_t a)
+{
+    uint32_t d;
+    asm("dp2a.lo.u32.u32 %0, %1, 0x0100, 0;" : "=r"(d) : "r"(a));
+    return d;
 }
 
-template <int BITS, int CB, int MG>
-void launch_one(const GemvArgs& args, dim3 grid, size_t smem, cudaStream_t stream)
+// 4-bit tiles: eight 16-bit windows from the lane's raw word r0 and the next lane's r1
+// (13 integer operations).  Stream bytes in order: r0.b1 r0.b0 r0.b3 r0.b2 r1.b1 r1.b0.
+// HEAVY = true moves the six half-word selections to the FMA-heavy pipe (for the codebooks whose
+// arithmetic leans on the ALU pipe).
+template <bool HEAVY>
+__device__ __forceinline__ void states_4bit(uint32_t r0, uint32_t r1, uint32_t (&s)[8])
 {
-    auto kern = k_exl3_gemv<BITS, CB, MG>;
-    static thread_local bool attr_set[kMaxDevices] = {};
-    int dev = current_device();
-    if (!attr_set[dev]) {
-        cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024), "gemv smem attribute");
-        attr_set[dev] = true;
+    s[2] = __byte_perm(r0, 0u, 0x4403);
+    const uint32_t z = r1 & 0xff00u;
+    s[6] = __byte_perm(r0, z, 0x4425);
+    const uint32_t a0 = __byte_perm(r0, 0u, 0x1032), a1 = __byte_perm(r1, 0u, 0x1032);
+    const uint32_t c4 = __funnelshift_l(a1, a0, 4), c12 = __funnelshift_l(a1, a0, 12);
+    if constexpr (HEAVY) {
+        s[0] = lo16_heavy(r0); s[4] = hi16_heavy(r0);
+        s[1] = hi16_heavy(c4); s[3] = hi16_heavy(c12);
+        s[5] = lo16_heavy(c4); s[7] = lo16_heavy(c12);
+    } else {
+        s[0] = r0 & 0xffffu; s[4] = r0 >> 16;
+        s[1] = c4 >> 16; s[3] = c12 >> 16;
+        s[5] = c4 & 0xffffu; s[7] = c12 & 0xffffu;
     }
-    kern<<<grid, kThreads, smem, stream>>>(args);
 }
 
 template <int BITS, int CB>
-void launch_mg(int mg, const GemvArgs& a, dim3 grid, size_t smem, cudaStream_t st)
+__device__ __forceinline__ void tile_states(const uint32_t* tile, int lane, int lane1, uint32_t (&s)[8])
 {
-    switch (mg) {
-        case 1: launch_one<BITS, CB, 1>(a, grid, smem, st); break;
-        case 2: launch_one<BITS, CB, 2>(a, grid, smem, st); break;
-        default: launch_one<BITS, CB, 4>(a, grid, smem, st); break;
+    if constexpr (BITS == 4) {
+        const uint32_t r0 = tile[lane], r1 = tile[lane1];
+        states_4bit<CB != 2>(r0, r1, s);
+    } else {
+        dq::lane_states<BITS>(tile, lane, s);
+    }
+}
+
+// Duplicated activation pairs for the lo/hi-as-k-slots scheme: from b0 = (x[2q], x[2q+1]) and
+// b1 = (x[2q+8], x[2q+9]) make (x,x) pairs.
+struct DupFrag { uint32_t e0, e1, o0, o1; };
+__device__ __forceinline__ DupFrag dup_pairs(uint32_t b0, uint32_t b1)
+{
+    DupFrag d;
+    d.e0 = __byte_perm(b0, 0u, 0x1010);  // (x[2q],   x[2q])
+    d.o0 = __byte_perm(b0, 0u, 0x3232);  // (x[2q+1], x[2q+1])
+    d.e1 = __byte_perm(b1, 0u, 0x1010);  // (x[2q+8], x[2q+8])
+    d.o1 = __byte_perm(b1, 0u, 0x3232);  // (x[2q+9], x[2q+9])
+    return d;
+}
+
+// Activation operand of one k-tile row: raw pairs for MUL1, duplicated pairs otherwise.
+template <int CB, int TG>
+struct RowFrag {
+    uint32_t b0[TG], b1[TG];
+    DupFrag dup[TG];
+    // `act` = the k-tile row's block in shared memory: [TG][2][32 lanes] words, lane = 4*token + q
+    __device__ __forceinline__ void load(const uint32_t* act, int lane)
+    {
+#pragma unroll
+        for (int tg = 0; tg < TG; ++tg) {
+            b0[tg] = act[tg * 64 + lane];
+            b1[tg] = act[tg * 64 + 32 + lane];
+            if constexpr (CB != 2) dup[tg] = dup_pairs(b0[tg], b1[tg]);
+        }
+    }
+};
+
+template <int CB, int TG>
+__device__ __forceinline__ void tile_mma(const uint32_t (&s)[8], float (&acc)[TG][4], const RowFrag<CB, TG>& f)
+{
+    if constexpr (CB == 2) {
+        uint32_t h[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[j] = dq::mul1_h1024(s[j]);
+        uint32_t a[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) a[r] = __byte_perm(h[2 * r], h[2 * r + 1], 0x5410);
+#pragma unroll
+        for (int tg = 0; tg < TG; ++tg) dq::mma_16816(acc[tg], a, f.b0[tg], f.b1[tg]);
+    } else {
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w[j] = dq::mix32<CB>(s[j]);
+        const uint32_t ae[4] = {w[0], w[2], w[4], w[6]};   // rows 2q, 2q+8 of columns g, g+8
+        const uint32_t ao[4] = {w[1], w[3], w[5], w[7]};   // rows 2q+1, 2q+9
+#pragma unroll
+        for (int tg = 0; tg < TG; ++tg) {
+            dq::mma_16816(acc[tg], ae, f.dup[tg].e0, f.dup[tg].e1);
+            dq::mma_16816(acc[tg], ao, f.dup[tg].o0, f.dup[tg].o1);
+        }
+    }
+}
+
+// One segment (part of one band group) of a CTA's unit range.
+struct Segment {
+    int bg, kb_begin, units;
+    bool head;       // starts at the CTA's first unit (slab 2c) or later (slab 2c+1)
+    bool whole;      // covers the band group's whole K: no slab, no counter
+};
+__device__ __forceinline__ Segment segment_at(long long u, long long u0, long long u1, int kblocks)
+{
+    Segment s;
+    s.bg = int(u / kblocks);
+    s.kb_begin = int(u - (long long) s.bg * kblocks);
+    const long long left = u1 - u;
+    s.units = left < (long long) (kblocks - s.kb_begin) ? int(left) : kblocks - s.kb_begin;
+    s.head = (u == u0);
+    s.whole = (s.kb_begin == 0 && s.units == kblocks);
+    return s;
+}
+
+// ---------------------------------------------------------------- the kernel
+template <int BITS, int CB, int TG>
+__global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant__ CUtensorMap tmap, const GemvArgs p)
+{
+    using G_ = Geo<BITS, TG>;
+    constexpr int NW = G_::NW, BU = G_::BU, ROW_BYTES = G_::ROW_BYTES, W_BYTES = G_::W_BYTES, ACT_BYTES = G_::ACT_BYTES;
+    constexpr int STAGE_BYTES = G_::STAGE_BYTES, S = G_::S;
+    constexpr int NT = G_::NT, CG = G_::CG, RW = G_::RW, RPW = G_::RPW, TOK = G_::TOK, PITCH = G_::PITCH;
+    constexpr int RED_SLAB = G_::RED_SLAB;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char* ring = smem;
+    float* red = reinterpret_cast<float*>(smem + kRingBytes);                 // [2][RW][TOK][PITCH]
+    float* outbuf = red + 2 * RW * RED_SLAB;                                  // [TOK][PITCH]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(outbuf + RED_SLAB);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int bands = p.n >> 7, kblocks = p.k >> 7;
+    const int bgroups = (bands + BU - 1) / BU;
+    const long long U = (long long) bgroups * kblocks;
+    const int G = gridDim.x, cta = blockIdx.x;
+    const long long u0 = unit_begin(cta, U, G), u1 = unit_begin(cta + 1, U, G);
+    const int nunits = int(u1 - u0);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + S);
+    const uint32_t redfull0 = smem_u32(bars + 2 * S), redempty0 = smem_u32(bars + 2 * S + 2);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, kConsumerWarps);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(redfull0 + 8 * b, kConsumerWarps);
+            mbar_init(redempty0 + 8 * b, kEpiWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == kProducerWarp) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
+            auto unit_coords = [&](int i, int& bg, int& kb) {
+                const long long u = u0 + i;
+                bg = int(u / kblocks);
+                kb = int(u - (long long) bg * kblocks);
+            };
+            // The weights do not depend on the rotation kernel: fill the ring with them first,
+            // then wait for the activations and complete those stages.
+            const int pre = nunits < S ? nunits : S;
+            for (int i = 0; i < pre; ++i) {
+                int bg, kb;
+                unit_coords(i, bg, kb);
+                mbar_arrive_expect_tx(full0 + 8 * i, STAGE_BYTES);
+                tma_load_2d(smem_u32(ring + i * STAGE_BYTES), &tmap, bg * (ROW_BYTES / 8), kb * 8, full0 + 8 * i);
+            }
+            grid_dependency_wait();
+            for (int i = 0; i < pre; ++i) {
+                int bg, kb;
+                unit_coords(i, bg, kb);
+                bulk_load_1d(smem_u32(ring + i * STAGE_BYTES + W_BYTES), p.afrag + size_t(kb) * (ACT_BYTES / 4), ACT_BYTES, full0 + 8 * i);
+            }
+            int s = 0, lap = 1;
+            for (int i = pre; i < nunits; ++i) {
+                mbar_wait(empty0 + 8 * s, (lap - 1) & 1, p.status, kStEmptyTimeout);
+                int bg, kb;
+                unit_coords(i, bg, kb);
+                mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                const uint32_t dst = smem_u32(ring + s * STAGE_BYTES);
+                tma_load_2d(dst, &tmap, bg * (ROW_BYTES / 8), kb * 8, full0 + 8 * s);
+                bulk_load_1d(dst + W_BYTES, p.afrag + size_t(kb) * (ACT_BYTES / 4), ACT_BYTES, full0 + 8 * s);
+                if (++s == S) { s = 0; ++lap; }
+            }
+        }
+        return;
+    }
+
+    if (warp < kConsumerWarps) {
+        // ------------------------------------------------------------ consumers
+        const int cg = warp % CG, rs = warp / CG;
+        const int g = lane >> 2, q = lane & 3, lane1 = (lane + 1) & 31;
+        int s = 0, phase = 0, flush = 0;
+        long long u = u0;
+        while (u < u1) {
+            const Segment sg = segment_at(u, u0, u1, kblocks);
+            float acc[NT][TG][4];
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int tg = 0; tg < TG; ++tg) acc[t][tg][0] = acc[t][tg][1] = acc[t][tg][2] = acc[t][tg][3] = 0.f;
+
+            for (int j = 0; j < sg.units; ++j) {
+                mbar_wait(full0 + 8 * s, phase, p.status, kStFullTimeout);
+                const uint32_t* stage = reinterpret_cast<const uint32_t*>(ring + s * STAGE_BYTES) + cg * NT * NW;
+                const uint32_t* act = reinterpret_cast<const uint32_t*>(ring + s * STAGE_BYTES + W_BYTES);
+#pragma unroll
+                for (int i = 0; i < RPW; ++i) {
+                    RowFrag<CB, TG> f;
+                    f.load(act + (rs + RW * i) * (TG * 64), lane);
+                    const uint32_t* rowp = stage + (rs + RW * i) * (ROW_BYTES / 4);
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) {
+                        uint32_t st[8];
+                        tile_states<BITS, CB>(rowp + t * NW, lane, lane1, st);
+                        tile_mma<CB, TG>(st, acc[t], f);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty0 + 8 * s);
+                if (++s == S) { s = 0; phase ^= 1; }
+            }
+
+            // ---- dump this segment's partial sums; the epilogue warps take it from here
+            const int buf = flush & 1;
+            if (flush >= 2) mbar_wait(redempty0 + 8 * buf, ((flush >> 1) - 1) & 1, p.status, kStRedEmptyTimeout);
+            float* mine = red + (buf * RW + rs) * RED_SLAB;
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int tg = 0; tg < TG; ++tg) {
+                    const int t0 = tg * 8 + 2 * q, c0 = (cg * NT + t) * 16 + g;
+                    mine[t0 * PITCH + c0] = acc[t][tg][0];
+                    mine[(t0 + 1) * PITCH + c0] = acc[t][tg][1];
+                    mine[t0 * PITCH + c0 + 8] = acc[t][tg][2];
+                    mine[(t0 + 1) * PITCH + c0 + 8] = acc[t][tg][3];
+                }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(redfull0 + 8 * buf);
+            ++flush;
+            u += sg.units;
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- epilogue warps
+    {
+        const int ew = warp - kProducerWarp - 1;      // 0..3
+        const int et = threadIdx.x - (kProducerWarp + 1) * 32;   // 0..127 = column inside a band
+        grid_dependency_wait();                       // block sums come from the rotation kernel
+        const size_t slab_floats = size_t(p.m) * BU * 128;
+        int flush = 0;
+        long long u = u0;
+        while (u < u1) {
+            const Segment sg = segment_at(u, u0, u1, kblocks);
+            const int buf = flush & 1;
+            mbar_wait(redfull0 + 8 * buf, (flush >> 1) & 1, p.status, kStRedFullTimeout);
+            // fixed-order reduction over the row streams: thread et owns column et of every band
+            for (int tok = 0; tok < TOK && tok < p.m; ++tok) {
+#pragma unroll
+                for (int b = 0; b < BU; ++b) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int w = 0; w < RW; ++w) v = __fadd_rn(v, red[(buf * RW + w) * RED_SLAB + tok * PITCH + b * 128 + et]);
+                    outbuf[tok * PITCH + b * 128 + et] = v;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(redempty0 + 8 * buf);
+            epi_sync();   // outbuf complete
+
+            bool finish = true;
+            int first_cta = cta, last_cta = cta, first_slab = 0;
+            if (!sg.whole && ew < p.m) {
+                const int slab = sg.head ? 2 * cta : 2 * cta + 1;
+                for (int row = ew; row < p.m; row += kEpiWarps)
+#pragma unroll
+                    for (int b = 0; b < BU; ++b) {
+                        float4 v = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
+                        __stcg(reinterpret_cast<float4*>(p.slabs + size_t(slab) * slab_floats + (size_t(row) * BU + b) * 128 + lane * 4), v);
+                    }
+                first_cta = unit_owner((long long) sg.bg * kblocks, U, G);
+                last_cta = unit_owner((long long) (sg.bg + 1) * kblocks - 1, U, G);
+                // slabs of this band group, in CTA order: the first CTA's tail (or head, if its range
+                // starts exactly here), then the heads of the following CTAs
+                first_slab = (unit_begin(first_cta, U, G) >= (long long) sg.bg * kblocks) ? 2 * first_cta : 2 * first_cta + 1;
+                __threadfence();
+                __syncwarp();
+                unsigned old = 0;
+                if (lane == 0) old = atomicAdd(p.counters + sg.bg * kEpiWarps + ew, 1u);
+                old = __shfl_sync(dq::kFull, old, 0);
+                finish = (old == unsigned(last_cta - first_cta));
+                if (finish) __threadfence();
+            }
+
+            if (finish) {
+                for (int row = ew; row < p.m; row += kEpiWarps) {
+                    float sx = 0.f;
+                    if constexpr (CB == 2) {
+                        // w = S*h + B per weight  =>  sum_k x_k w_k = S*acc + B*sum_k x_k
+                        for (int b = lane; b < kblocks; b += 32) sx = __fadd_rn(sx, __ldg(p.blocksum + size_t(row) * kblocks + b));
+#pragma unroll
+                        for (int off = 16; off >= 1; off >>= 1) sx = __fadd_rn(sx, __shfl_xor_sync(dq::kFull, sx, off));
+                    }
+                    for (int b = 0; b < BU; ++b) {
+                        const int band = sg.bg * BU + b;
+                        if (band >= bands) break;   // ragged last band group
+                        float v[4];
+                        if (sg.whole) {
+                            float4 t = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
+                            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+                        } else {
+                            v[0] = v[1] = v[2] = v[3] = 0.f;
+                            const float* base = p.slabs + (size_t(row) * BU + b) * 128 + lane * 4;
+                            const int nsl = last_cta - first_cta + 1;
+                            for (int i0 = 0; i0 < nsl; i0 += 8) {
+                                float4 t[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {   // eight independent loads in flight, summed in CTA order
+                                    const int si = i0 + i;
+                                    const int slab = si == 0 ? first_slab : 2 * (first_cta + si);
+                                    t[i] = si < nsl ? __ldcg(reinterpret_cast<const float4*>(base + size_t(slab) * slab_floats))
+                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+                                }
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    if (i0 + i < nsl) {
+                                        v[0] = __fadd_rn(v[0], t[i].x); v[1] = __fadd_rn(v[1], t[i].y);
+                                        v[2] = __fadd_rn(v[2], t[i].z); v[3] = __fadd_rn(v[3], t[i].w);
+                                    }
+                                }
+                            }
+                        }
+                        if constexpr (CB == 2) {
+                            const float S1 = __half2float(__ushort_as_half(dq::kMul1S));
+                            const float bsx = __fmul_rn(__half2float(__ushort_as_half(dq::kMul1B)), sx);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) v[i] = __fmaf_rn(S1, v[i], bsx);
+                        }
+                        dq::had128_warp(v, lane);
+                        const int col = band * 128 + lane * 4;
+                        uint2 sr = *reinterpret_cast<const uint2*>(p.svh + col);
+                        __half2 s0 = *reinterpret_cast<__half2*>(&sr.x), s1 = *reinterpret_cast<__half2*>(&sr.y);
+                        v[0] = __fmul_rn(__fmul_rn(v[0], kRScale), __low2float(s0));
+                        v[1] = __fmul_rn(__fmul_rn(v[1], kRScale), __high2float(s0));
+                        v[2] = __fmul_rn(__fmul_rn(v[2], kRScale), __low2float(s1));
+                        v[3] = __fmul_rn(__fmul_rn(v[3], kRScale), __high2float(s1));
+                        if (p.out_fp32) {
+                            *reinterpret_cast<float4*>(static_cast<float*>(p.c) + size_t(row) * p.n + col) = make_float4(v[0], v[1], v[2], v[3]);
+                        } else {
+                            uint2 o;
+                            o.x = dq::pack_half2(__float2half_rn(v[0]), __float2half_rn(v[1]));
+                            o.y = dq::pack_half2(__float2half_rn(v[2]), __float2half_rn(v[3]));
+                            *reinterpret_cast<uint2*>(static_cast<__half*>(p.c) + size_t(row) * p.n + col) = o;
+                        }
+                    }
+                }
+                if (!sg.whole && ew < p.m && lane == 0) p.counters[sg.bg * kEpiWarps + ew] = 0;   // self-resetting
+            }
+            epi_sync();   // outbuf is free again
+            ++flush;
+            u += sg.units;
+        }
+    }
+}
+
+// ---------------------------------------------------------------- rotation of the activations
+// a_had = fp16(H128(a * suh) / sqrt(128)) in the caller's [m][k] buffer; the same values again in
+// MMA fragment order for the decode kernel (afrag[k/16][TG][2][8][4] words: the pair
+// (k = 16*ktile + 8*h + 2*q, +1) of token 8*tg + t at word ((ktile*TG + tg)*2 + h)*32 + 4*t + q, zero
+// for tokens >= m); blocksum[row][b] = sum of the 128 rounded values of a block.
+// One warp per (token row, 128-block).  Lets the dependent GEMV start early (programmatic launch).
+__global__ void __launch_bounds__(128) k_rotate_in(const __half* __restrict__ a, const __half* __restrict__ suh,
+                                                   __half* __restrict__ a_had, uint32_t* __restrict__ afrag,
+                                                   float* __restrict__ blocksum, int rows, int rows_pad, int k)
+{
+    grid_launch_dependents();
+    const int lane = threadIdx.x & 31, kblocks = k >> 7, tgs = rows_pad >> 3;
+    const int total = rows_pad * kblocks;
+    for (int idx = blockIdx.x * 4 + (threadIdx.x >> 5); idx < total; idx += gridDim.x * 4) {
+        const int row = idx / kblocks, b = idx - row * kblocks;
+        const int kcol = b * 128 + lane * 4;
+        uint2 o = make_uint2(0u, 0u);
+        if (row < rows) {
+            uint2 xr = *reinterpret_cast<const uint2*>(a + size_t(row) * k + kcol);
+            uint2 sr = *reinterpret_cast<const uint2*>(suh + kcol);
+            __half2 x0 = *reinterpret_cast<__half2*>(&xr.x), x1 = *reinterpret_cast<__half2*>(&xr.y);
+            __half2 s0 = *reinterpret_cast<__half2*>(&sr.x), s1 = *reinterpret_cast<__half2*>(&sr.y);
+            float v[4];
+            v[0] = __fmul_rn(__low2float(x0), __low2float(s0));
+            v[1] = __fmul_rn(__high2float(x0), __high2float(s0));
+            v[2] = __fmul_rn(__low2float(x1), __low2float(s1));
+            v[3] = __fmul_rn(__high2float(x1), __high2float(s1));
+            dq::had128_warp(v, lane);
+            __half h[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) h[i] = __float2half_rn(__fmul_rn(v[i], kRScale));
+            o.x = dq::pack_half2(h[0], h[1]);
+            o.y = dq::pack_half2(h[2], h[3]);
+            *reinterpret_cast<uint2*>(a_had + size_t(row) * k + kcol) = o;
+            float sx = __fadd_rn(__fadd_rn(__half2float(h[0]), __half2float(h[1])), __fadd_rn(__half2float(h[2]), __half2float(h[3])));
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) sx = __fadd_rn(sx, __shfl_xor_sync(dq::kFull, sx, off));
+            if (lane == 0) blocksum[row * kblocks + b] = sx;
+        }
+        // lane holds k_in = 4*(lane&3) .. +3 of k-tile (8*b + lane/4): half h = k_in/8, pair index q = (k_in%8)/2
+        const int ktile = b * 8 + (lane >> 2), hsel = (lane & 3) >> 1, q = 2 * (lane & 1);
+        const size_t w = ((size_t(ktile) * tgs + (row >> 3)) * 2 + hsel) * 32 + (row & 7) * 4 + q;
+        *reinterpret_cast<uint2*>(afrag + w) = o;
+    }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled()
+{
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cuda_ok(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q), "cuTensorMapEncodeTiled entry point");
+        if (!p || q != cudaDriverEntryPointSuccess) throw std::runtime_error("cuTensorMapEncodeTiled is not available in this driver");
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// 2-D view of a trellis: rows = k-tile rows (K/16), row = (N/16) tiles of 32*bits bytes, in 8-byte
+// elements; box = one unit (8 rows x BU bands).  Columns past the matrix read as zero.
+CUtensorMap trellis_map(const void* trellis, int size_k, int size_n, int bits, int box_bytes)
+{
+    if (reinterpret_cast<uintptr_t>(trellis) % 16 != 0) throw std::runtime_error("exl3 linear: trellis must be 16-byte aligned");
+    CUtensorMap map;
+    const cuuint64_t row_bytes = cuuint64_t(size_n / 16) * 32 * bits;
+    const cuuint64_t dims[2] = {row_bytes / 8, cuuint64_t(size_k / 16)};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {cuuint32_t(box_bytes / 8), 8};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(trellis), dims, strides, box, elem,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw std::runtime_error("exl3 linear: cuTensorMapEncodeTiled failed (" + std::to_string(int(r)) + ")");
+    return map;
+}
+
+template <int BITS, int CB, int TG>
+size_t launch_one(const void* trellis, const GemvArgs& args, int grid, cudaStream_t stream)
+{
+    using G_ = Geo<BITS, TG>;
+    auto kern = k_exl3_gemv<BITS, CB, TG>;
+    static bool attr_set[kMaxDevices] = {};
+    const int dev = current_device();
+    if (!attr_set[dev]) {
+        cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(G_::SMEM)), "gemv smem attribute");
+        attr_set[dev] = true;
+    }
+    const CUtensorMap map = trellis_map(trellis, args.k, args.n, BITS, G_::ROW_BYTES);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = G_::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cuda_ok(cudaLaunchKernelEx(&cfg, kern, map, args), "k_exl3_gemv launch");
+    return G_::SMEM;
+}
+
+template <int BITS, int CB>
+size_t launch_tg(int tg, const void* t, const GemvArgs& a, int grid, cudaStream_t st)
+{
+    switch (tg) {
+        case 1: return launch_one<BITS, CB, 1>(t, a, grid, st);
+        case 2: return launch_one<BITS, CB, 2>(t, a, grid, st);
+        default: return launch_one<BITS, CB, 4>(t, a, grid, st);
     }
 }
 
 template <int BITS>
-void launch_cb(int cb, int mg, const GemvArgs& a, dim3 grid, size_t smem, cudaStream_t st)
+size_t launch_cb(int cb, int tg, const void* t, const GemvArgs& a, int grid, cudaStream_t st)
 {
     switch (cb) {
-        case 0: launch_mg<BITS, 0>(mg, a, grid, smem, st); break;
-        case 1: launch_mg<BITS, 1>(mg, a, grid, smem, st); break;
-        default: launch_mg<BITS, 2>(mg, a, grid, smem, st); break;
+        case 0: return launch_tg<BITS, 0>(tg, t, a, grid, st);
+        case 1: return launch_tg<BITS, 1>(tg, t, a, grid, st);
+        default: return launch_tg<BITS, 2>(tg, t, a, grid, st);
     }
 }
 
 }  // namespace
 
-// Shared-memory budget for the rotated activations: 8*MG rows x chunk_k fp16 <= 32 KiB.
-static int max_chunk_kb(int mg) { return 2048 / 128 / mg; }
-
-// Launches the decode GEMV.  `ws`/`counters` = split-K scratch (the library's per-device
-// workspace, or a caller-provided region of `ws_bytes` bytes and `n/128` zeroed counters).
+// Launches rotation + decode GEMV for up to 32 rows.  `sc` is the split-K scratch: the library's
+// per-device workspace or the fixed in-image array of the allocation-free entry point.
 std::string launch_gemv(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
-                        int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, float* ws,
-                        size_t ws_bytes, unsigned* counters, int sms, cudaStream_t stream)
+                        int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32,
+                        const GemvScratch& sc, int sms, cudaStream_t stream)
 {
     if (size_m > 32) throw std::runtime_error("exl3 gemv: size_m must be <= 32");
     if (size_k % 128 != 0)
         throw std::runtime_error("exl3 linear: no linked kernel for size_k that is not a multiple of 128 (128-wide Hadamard)");
     if (k_bits < 1 || k_bits > 8) throw std::runtime_error("exl3 linear: K must be in 1..=8");
-    const int mg = size_m <= 8 ? 1 : (size_m <= 16 ? 2 : 4);
-    const int bands = size_n / 128, kblocks = size_k / 128;
-    if (bands > kGemvMaxBands) throw std::runtime_error("exl3 gemv: size_n exceeds the band counter table");
+    const int tg = size_m <= 8 ? 1 : (size_m <= 16 ? 2 : 4);
+    const int bu = k_bits <= 4 ? 2 : 1;   // bands per unit, as Geo<BITS, TG>::BU
+    const int bands = size_n / 128, kblocks = size_k / 128, bgroups = (bands + bu - 1) / bu;
+    if (bgroups * kEpiWarps > sc.counter_slots) throw std::runtime_error("exl3 gemv: size_n exceeds the counter table of the scratch");
+    if (size_t(size_m) * kblocks > sc.blocksum_floats)
+        throw std::runtime_error("exl3 gemv: size_m * size_k / 128 exceeds the block-sum table of the scratch");
+    const long long units = (long long) bgroups * kblocks;
+    // One CTA per SM, but never more than 16 CTAs per band group: the last arriver of a band
+    // group sums one slab per CTA, and a matrix that small is latency bound anyway.
+    int grid = int(std::min<long long>(std::min<long long>(sms, units), (long long) bgroups * 16));
+    // two slabs of [m][bu*128] fp32 per CTA
+    const size_t per_cta = size_t(2) * size_m * bu * 128 * sizeof(float);
+    if (size_t(grid) * per_cta > sc.slab_bytes) grid = int(sc.slab_bytes / per_cta);
+    if (grid < 1) throw std::runtime_error("exl3 gemv: split-K scratch is too small for this shape");
 
-    // Split K until about four CTAs per SM exist, each keeping at least two 128-row blocks.
-    const int target = sms * 4;
-    int want = std::max(1, (target + bands - 1) / bands);
-    want = std::min(want, std::max(1, kblocks / 2));
-    int kbps = (kblocks + want - 1) / want;
-    int ksplit = (kblocks + kbps - 1) / kbps;
-    while (ksplit > 1 && size_t(ksplit) * size_m * size_n * sizeof(float) > ws_bytes) {
-        ++kbps;
-        ksplit = (kblocks + kbps - 1) / kbps;
-    }
-    const int chunk_kb = std::min(kbps, max_chunk_kb(mg));
+    const size_t afrag_bytes = size_t(size_k / 16) * tg * 256;
+    if (afrag_bytes > sc.afrag_bytes)
+        throw std::runtime_error("exl3 gemv: size_k * ceil(size_m / 8) exceeds the activation-fragment area of the scratch");
+    const int rot_total = 8 * tg * kblocks;
+    k_rotate_in<<<std::min((rot_total + 3) / 4, 4 * sms), 128, 0, stream>>>(
+        static_cast<const __half*>(a), static_cast<const __half*>(suh), static_cast<__half*>(a_had), sc.afrag, sc.blocksum,
+        size_m, 8 * tg, size_k);
+    cuda_ok(cudaGetLastError(), "k_rotate_in launch");
 
     GemvArgs args;
-    args.a = static_cast<const __half*>(a);
-    args.trellis = static_cast<const uint32_t*>(trellis);
+    args.afrag = sc.afrag;
+    args.blocksum = sc.blocksum;
     args.c = c;
-    args.suh = static_cast<const __half*>(suh);
-    args.a_had = static_cast<__half*>(a_had);
     args.svh = static_cast<const __half*>(svh);
-    args.ws = ws;
-    args.counters = counters;
+    args.slabs = sc.slabs;
+    args.counters = sc.counters;
+    args.status = sc.status;
     args.m = size_m; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
-    args.kb_per_split = kbps;
-    args.ksplit = ksplit;
-    args.chunk_kb = chunk_kb;
-    dim3 grid(bands, ksplit);
-    const size_t smem = size_t(8 * mg) * (chunk_kb * 128 + 8) * sizeof(__half) + size_t(8 * mg) * 132 * sizeof(float);
+    size_t smem = 0;
     switch (k_bits) {
-        case 1: launch_cb<1>(codebook, mg, args, grid, smem, stream); break;
-        case 2: launch_cb<2>(codebook, mg, args, grid, smem, stream); break;
-        case 3: launch_cb<3>(codebook, mg, args, grid, smem, stream); break;
-        case 4: launch_cb<4>(codebook, mg, args, grid, smem, stream); break;
-        case 5: launch_cb<5>(codebook, mg, args, grid, smem, stream); break;
-        case 6: launch_cb<6>(codebook, mg, args, grid, smem, stream); break;
-        case 7: launch_cb<7>(codebook, mg, args, grid, smem, stream); break;
-        default: launch_cb<8>(codebook, mg, args, grid, smem, stream); break;
+        case 1: smem = launch_cb<1>(codebook, tg, trellis, args, grid, stream); break;
+        case 2: smem = launch_cb<2>(codebook, tg, trellis, args, grid, stream); break;
+        case 3: smem = launch_cb<3>(codebook, tg, trellis, args, grid, stream); break;
+        case 4: smem = launch_cb<4>(codebook, tg, trellis, args, grid, stream); break;
+        case 5: smem = launch_cb<5>(codebook, tg, trellis, args, grid, stream); break;
+        case 6: smem = launch_cb<6>(codebook, tg, trellis, args, grid, stream); break;
+        case 7: smem = launch_cb<7>(codebook, tg, trellis, args, grid, stream); break;
+        default: smem = launch_cb<8>(codebook, tg, trellis, args, grid, stream); break;
     }
-    cuda_ok(cudaGetLastError(), "k_exl3_gemv launch");
-    return "k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," + std::to_string(mg) + "> grid=" +
-           std::to_string(bands) + "x" + std::to_string(ksplit) + " block=" + std::to_string(kThreads) +
-           " smem=" + std::to_string(smem);
+    return "k_rotate_in + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," + std::to_string(tg) +
+           "> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem);
 }
 
 }  // namespace berth
@@ -320,40 +734,53 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
 // keeps a fixed scratch area inside the library image instead, so it never calls cudaMalloc,
 // cudaFree or any allocating routine.
 //
-// The scratch is one file-scope __device__ array: kStaticPartialBytes of fp32 partial sums plus
-// one arrival counter per 128-column band.  Every GPU that loads the library carries it until
-// the process exits.  All calls on a device share it and it keeps whatever the previous call
-// left behind: the counters are cleared on the stream before each launch, the partial sums are
-// fully overwritten before they are read.  Two calls that overlap on the GPU (different
-// streams) race on it; issue them on one stream.
+// The scratch is one file-scope __device__ array: 4 MiB of fp32 partial-sum slabs, 2 MiB for the
+// rotated activations in fragment order, arrival counters (16 KiB), one fp32 block sum per
+// (row, 128 inputs) (128 KiB) and a status word.  Every
+// GPU that loads the library carries it until the process exits.  All calls on a device share it
+// and it keeps whatever the previous call left behind: the counters are cleared on the stream
+// before each launch; slabs, fragments and block sums are fully overwritten before they are read.  Two
+// calls that overlap on the GPU (different streams) race on it; issue them on one stream.
 namespace berth {
 namespace {
 
-constexpr size_t kStaticPartialBytes = size_t(4) << 20;   // 4 MiB of split-K partial sums
-constexpr int kStaticMaxBands = 1024;                     // size_n <= 131072
+constexpr size_t kStaticSlabBytes = size_t(4) << 20;   // 4 MiB of split-K partial sums
+constexpr int kStaticMaxBands = 1024;                  // size_n <= 131072
 constexpr int kStaticMaxRows = 32;
+constexpr int kStaticMaxKBlocks = 1024;                // size_k <= 131072
+constexpr size_t kStaticCounterBytes = size_t(kStaticMaxBands) * kEpiWarps * sizeof(unsigned);
+constexpr size_t kStaticBlocksumBytes = size_t(kStaticMaxRows) * kStaticMaxKBlocks * sizeof(float);
+constexpr size_t kStaticAfragBytes = size_t(2) << 20;   // size_k * ceil(size_m / 8) <= 131072
 
-static __device__ __align__(256) unsigned char g_static_scratch[kStaticPartialBytes + kStaticMaxBands * sizeof(unsigned)];
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticSlabBytes + kStaticAfragBytes + kStaticCounterBytes + kStaticBlocksumBytes + 256];
 
-struct StaticScratch {
-    float* partial = nullptr;
-    unsigned* counters = nullptr;
-};
-StaticScratch g_static_ptr[kMaxDevices];
+GemvScratch g_static_ptr[kMaxDevices];
 std::mutex g_static_mu;
 
 // The array's name is only a host-side handle; the device address has to be asked for, once
 // per device, while that device is current.
-StaticScratch static_scratch(int device)
+GemvScratch static_scratch(int device)
 {
     std::lock_guard<std::mutex> lock(g_static_mu);
-    StaticScratch& s = g_static_ptr[device];
-    if (!s.partial) {
+    GemvScratch& s = g_static_ptr[device];
+    if (!s.slabs) {
         void* base = nullptr;
         cuda_ok(cudaGetSymbolAddress(&base, g_static_scratch), "cudaGetSymbolAddress(static scratch)");
         if (!base) throw std::runtime_error("exl3 linear (static scratch): symbol address is null");
-        s.partial = static_cast<float*>(base);
-        s.counters = reinterpret_cast<unsigned*>(static_cast<unsigned char*>(base) + kStaticPartialBytes);
+        unsigned char* b = static_cast<unsigned char*>(base);
+        s.slabs = reinterpret_cast<float*>(b);
+        s.slab_bytes = kStaticSlabBytes;
+        b += kStaticSlabBytes;
+        s.afrag = reinterpret_cast<uint32_t*>(b);
+        s.afrag_bytes = kStaticAfragBytes;
+        b += kStaticAfragBytes;
+        s.counters = reinterpret_cast<unsigned*>(b);
+        s.counter_slots = kStaticMaxBands * kEpiWarps;
+        b += kStaticCounterBytes;
+        s.blocksum = reinterpret_cast<float*>(b);
+        s.blocksum_floats = size_t(kStaticMaxRows) * kStaticMaxKBlocks;
+        b += kStaticBlocksumBytes;
+        s.status = reinterpret_cast<unsigned*>(b);
     }
     return s;
 }
@@ -381,16 +808,18 @@ extern "C" int berth_exl3_linear_static_scratch(const void* a, const void* trell
         if (size_n / 128 > kStaticMaxBands)
             throw std::runtime_error("exl3 linear (static scratch): size_n " + std::to_string(size_n) +
                                      " exceeds the maximum of " + std::to_string(kStaticMaxBands * 128) + " columns");
+        if (size_k / 128 > kStaticMaxKBlocks || size_t(size_k) * ((size_m + 7) / 8) > 131072)
+            throw std::runtime_error("exl3 linear (static scratch): size_k " + std::to_string(size_k) + " with " +
+                                     std::to_string(size_m) + " rows exceeds the maximum of size_k * ceil(size_m / 8) <= 131072");
         const int device = current_device();
         const DeviceInfo& info = device_info(device);
         if (info.major != 10)
             throw std::runtime_error("exl3 linear: no linked kernel for this GPU (library is built for sm_100a only)");
-        StaticScratch s = static_scratch(device);
+        GemvScratch s = static_scratch(device);
         cudaStream_t cs = (cudaStream_t) stream;
-        // Arrival counters must start at zero; the partial sums need no clearing.
-        cuda_ok(cudaMemsetAsync(s.counters, 0, size_t(size_n / 128) * sizeof(unsigned), cs), "static scratch counter reset");
-        st.launch = launch_gemv(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, out_fp32,
-                                s.partial, kStaticPartialBytes, s.counters, info.sms, cs) + " static-scratch";
+        // Arrival counters must start at zero; slabs and block sums need no clearing.
+        cuda_ok(cudaMemsetAsync(s.counters, 0, kStaticCounterBytes, cs), "static scratch counter reset");
+        st.launch = launch_gemv(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, out_fp32, s,
+                                info.sms, cs) + " static-scratch";
     });
 }
-

@@ -7,10 +7,6 @@
 
 namespace berth {
 
-std::string launch_gemv(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
-                        int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, float* ws,
-                        size_t ws_bytes, unsigned* counters, int sms, cudaStream_t stream);
-
 // Any row count through the GEMV kernel, 32 rows per launch.
 std::string linear_rows(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, cudaStream_t stream)
@@ -19,7 +15,7 @@ std::string linear_rows(const void* a, const void* trellis, void* c, const void*
     const DeviceInfo& info = device_info(device);
     if (info.major != 10)
         throw std::runtime_error("exl3 linear: no linked kernel for this GPU (library is built for sm_100a only)");
-    GemvWorkspace w = gemv_workspace(device);
+    GemvScratch w = gemv_workspace(device);
     std::string desc;
     const size_t csz = out_fp32 ? 4 : 2;
     for (int m0 = 0; m0 < size_m; m0 += 32) {
@@ -27,7 +23,7 @@ std::string linear_rows(const void* a, const void* trellis, void* c, const void*
         desc = launch_gemv(static_cast<const char*>(a) + size_t(m0) * size_k * 2, trellis,
                            static_cast<char*>(c) + size_t(m0) * size_n * csz, suh,
                            static_cast<char*>(a_had) + size_t(m0) * size_k * 2, svh, rows, size_k, size_n, k_bits,
-                           codebook, out_fp32, w.partial, kGemvWorkspaceBytes, w.counters, info.sms, stream);
+                           codebook, out_fp32, w, info.sms, stream);
     }
     if (size_m > 32) desc += " x" + std::to_string((size_m + 31) / 32) + " row chunks";
     return desc;

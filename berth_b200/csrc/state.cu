@@ -7,6 +7,8 @@
 
 namespace berth {
 
+int read_gemv_status(int device);
+
 CallState& exl3_state()    { thread_local CallState s; return s; }
 CallState& prefill_state() { thread_local CallState s; return s; }
 CallState& ops_state()     { thread_local CallState s; return s; }
@@ -15,7 +17,7 @@ CallState& moe_state()     { thread_local CallState s; return s; }
 namespace {
 std::mutex g_mu;
 DeviceInfo g_info[kMaxDevices];
-GemvWorkspace g_ws[kMaxDevices];
+GemvScratch g_ws[kMaxDevices];
 }  // namespace
 
 int current_device()
@@ -49,19 +51,50 @@ const DeviceInfo& device_info(int device)
     return d;
 }
 
-GemvWorkspace gemv_workspace(int device)
+GemvScratch gemv_workspace(int device)
 {
     std::lock_guard<std::mutex> lock(g_mu);
     if (device < 0 || device >= kMaxDevices) throw std::runtime_error("device index out of range");
-    GemvWorkspace& w = g_ws[device];
-    if (!w.partial) {
+    GemvScratch& w = g_ws[device];
+    if (!w.slabs) {
+        const size_t counters = size_t(kGemvCounterSlots) * sizeof(unsigned);
+        const size_t blocksum = kGemvBlocksumFloats * sizeof(float);
+        const size_t total = kGemvSlabBytes + kGemvAfragBytes + counters + blocksum + 256;
         void* p = nullptr;
-        cuda_ok(cudaMalloc(&p, kGemvWorkspaceBytes + size_t(kGemvMaxBands) * sizeof(unsigned)), "gemv workspace");
-        cuda_ok(cudaMemset(p, 0, kGemvWorkspaceBytes + size_t(kGemvMaxBands) * sizeof(unsigned)), "gemv workspace memset");
-        w.partial = static_cast<float*>(p);
-        w.counters = reinterpret_cast<unsigned*>(static_cast<char*>(p) + kGemvWorkspaceBytes);
+        cuda_ok(cudaMalloc(&p, total), "gemv workspace");
+        cuda_ok(cudaMemset(p, 0, total), "gemv workspace memset");
+        char* b = static_cast<char*>(p);
+        w.slabs = reinterpret_cast<float*>(b);
+        w.slab_bytes = kGemvSlabBytes;
+        b += kGemvSlabBytes;
+        w.afrag = reinterpret_cast<uint32_t*>(b);
+        w.afrag_bytes = kGemvAfragBytes;
+        b += kGemvAfragBytes;
+        w.counters = reinterpret_cast<unsigned*>(b);
+        w.counter_slots = kGemvCounterSlots;
+        b += counters;
+        w.blocksum = reinterpret_cast<float*>(b);
+        w.blocksum_floats = kGemvBlocksumFloats;
+        b += blocksum;
+        w.status = reinterpret_cast<unsigned*>(b);
     }
     return w;
+}
+
+// Reads and clears the status word of the library's scratch on `device` (synchronises).
+// 0 = every bounded wait of the decode kernels completed.
+int read_gemv_status(int device)
+{
+    GemvScratch w;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        w = g_ws[device];
+    }
+    if (!w.status) return 0;
+    unsigned v = 0;
+    cuda_ok(cudaMemcpy(&v, w.status, sizeof v, cudaMemcpyDeviceToHost), "status read");
+    if (v) cuda_ok(cudaMemset(w.status, 0, sizeof v), "status clear");
+    return int(v);
 }
 
 }  // namespace berth
@@ -71,6 +104,11 @@ using namespace berth;
 extern "C" int berth_device_cc(int device)
 {
     try { return device_info(device).cc; } catch (const std::exception&) { cudaGetLastError(); return -1; }
+}
+
+extern "C" int berth_device_status(int device)
+{
+    try { return berth::read_gemv_status(device); } catch (const std::exception&) { cudaGetLastError(); return -1; }
 }
 
 extern "C" int berth_device_sms(int device)

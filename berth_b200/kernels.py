@@ -91,6 +91,11 @@ def device_sms(device: int) -> int:
     return _lib.lib().berth_device_sms(device)
 
 
+def device_status(device: int) -> int:
+    """Reads and clears the bounded-wait status word of the decode kernels (synchronises)."""
+    return _lib.lib().berth_device_status(device)
+
+
 def gemm_tune_key(size_m, size_k, size_n, k_bits, out_fp32, device, cc, sms, cb) -> int:
     return _lib.lib().berth_exl3_gemm_tune_key(size_m, size_k, size_n, k_bits, out_fp32, device, cc, sms, cb)
 

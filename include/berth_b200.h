@@ -28,7 +28,7 @@
  * Per-device state owned by the library, allocated at the first launch on a device and kept
  * until exit (the counterpart of the lock buffer and 16 MiB split-K workspace of
  * crates/berth-kernels/csrc/linear.cu:334-345 and csrc/int8_sq.cu:20-47): one split-K
- * workspace with self-resetting arrival counters.  Launches that overlap on one device
+ * workspace (32 MiB of partial-sum slabs, self-resetting arrival counters, block sums).  Launches that overlap on one device
  * (different streams) must not share it: berth drives one stream per device, and so must
  * every other caller.
  */
@@ -54,9 +54,10 @@ const char* berth_exl3_last_launch(void);   /* crates/berth-kernels/csrc/linear.
 /* Same linear for callers that must not allocate device memory (a host whose own planner owns
  * every byte of HBM, or a decode loop that cannot take cudaMalloc's device-wide synchronisation).
  * No counterpart in berth: its library allocates its workspaces with cudaMalloc at first use.
- * The split-K scratch is a fixed 4 MiB + 4 KiB __device__ array inside the library image, held by
- * every GPU that loads the library until the process exits; nothing is allocated or freed.
- * Limits: size_m <= 32 and size_n <= 131072, larger sizes are rejected with an error.  The first
+ * The split-K scratch is a fixed __device__ array of 4 MiB + 132.25 KiB inside the library image
+ * (4 MiB partial-sum slabs, 4 KiB band counters, 128 KiB block sums, a status word), held by every
+ * GPU that loads the library until the process exits; nothing is allocated or freed.
+ * Limits: size_m <= 32, size_n <= 131072 and size_k <= 131072; larger sizes are rejected with an error.  The first
  * call on a device looks the array's device address up (cudaGetSymbolAddress); make that first
  * call before any stream capture begins.  All calls on a device share the scratch, which keeps
  * the previous call's contents (the counters are cleared on `stream` before each launch): calls
@@ -70,6 +71,11 @@ int berth_exl3_linear_static_scratch(const void* a, const void* trellis, void* c
  * enumeration orders them: old, Ampere, Ada, Hopper, Blackwell; SM count). -1 on error. */
 int berth_device_cc(int device);
 int berth_device_sms(int device);
+/* Reads and clears the status word of the decode kernels on `device` (this call synchronises
+ * the device).  The kernels never wait without a limit: a wait that runs out sets a bit here
+ * (1 = a weight stage never arrived, 2 = a stage was never released) and the launch finishes
+ * with undefined output instead of hanging.  0 = clean, -1 = CUDA error.  No counterpart in berth. */
+int berth_device_status(int device);
 
 /* FNV-1a shape key of crates/berth-kernels/csrc/linear.cu:65-104,345-358.  Kept because berth's
  * tests pin its value; this library never tunes at run time.  No CUDA call. */

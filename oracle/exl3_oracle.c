@@ -30,8 +30,10 @@
  *   cb 1 "MCG"  [v0 multiplier]  x = s*0xCBAC1FED (mod 2^32); then mask/xor/add as cb 0
  *   cb 2 "MUL1" [berth: ptx/sm86_probes.cu:237-249 for the multiplier; v0 for the rest]
  *        x = s*0x83DCD12D (mod 2^32); u = sum of the four bytes of x (0..1020);
- *        w = fp16 fma(u, S, B) with S = 0x1EEE (0.0067673) and B = 0xC2E7 (-3.4512),
- *        one rounding: the byte sum centred on 510 and scaled to about unit variance.
+ *        h = the fp16 whose bit pattern is 0x6400 + u, i.e. the value 1024 + u exactly;
+ *        w = fp16 fma(h, S, B) with S = 0x1EEE (0.0067673) and B = 0xC931 (-10.3828),
+ *        one rounding: the byte sum centred (mean 1534*S = 10.381) and scaled to about
+ *        unit variance without any integer-to-float conversion.
  * Hadamard [berth: csrc/prefill_lin/reconstruct.cu:31-67]
  *   Sylvester H_128 in natural order on each contiguous 128 block, fp32 butterflies with
  *   strides 1,2,4,...,64 (lower index gets a+b, upper a-b), then * 0.088388347648f.
@@ -123,7 +125,7 @@ void exl3o_unpack_signs(const uint16_t* packed, int64_t n_words, uint16_t* out)
 /* ------------------------------------------------------------------ codebook */
 
 #define MUL1_S 0x1EEE
-#define MUL1_B 0xC2E7
+#define MUL1_B 0xC931
 
 uint16_t exl3o_codebook(uint32_t state, int cb)
 {
@@ -131,7 +133,7 @@ uint16_t exl3o_codebook(uint32_t state, int cb)
     if (cb == 2) {
         uint32_t x = state * 0x83DCD12Du;
         int u = (int)(x & 0xff) + (int)((x >> 8) & 0xff) + (int)((x >> 16) & 0xff) + (int)(x >> 24);
-        double v = (double) u * (double) exl3o_h2f(MUL1_S) + (double) exl3o_h2f(MUL1_B);
+        double v = (double) (1024 + u) * (double) exl3o_h2f(MUL1_S) + (double) exl3o_h2f(MUL1_B);
         return exl3o_d2h(v); /* exact product and sum in fp64, one rounding = fp16 fma */
     }
     uint32_t x = (cb == 0) ? state * 89226354u + 64248484u : state * 0xCBAC1FEDu;

@@ -134,7 +134,7 @@ def test_linear_small_vs_oracle(oracle, m, bits, cb, out_fp32):
     assert (ah == exp_ah.view(np.uint16)).all()          # rotated activations: bit-exact
     # against the fp32 oracle the only difference is summation order
     rms = np.sqrt((y64 ** 2).mean())
-    assert np.abs(c.astype(np.float64) - exp_c.astype(np.float64)).max() <= 2e-3 * rms
+    assert np.abs(c.astype(np.float64) - exp_c.astype(np.float64)).max() <= 4e-3 * rms
     assert "k_exl3_gemv" in kernels.last_launch()
 
 
@@ -236,3 +236,11 @@ def test_linear_27b_shapes_full_size(name, K, N, out_fp32, m):
         cs, _ = run_linear(xs, w, bits, cb, True)
         rms = np.sqrt((cs.astype(np.float64) ** 2).mean())
         assert np.abs(cs - (c1 + c2)).max() <= 5e-3 * rms
+
+
+def test_no_bounded_wait_ran_out():
+    """Every pipeline wait inside the decode kernels is bounded; none may have expired so far."""
+    K, N = 1024, 512
+    w = synth.linear_weights(1234, "status", K, N, 4)
+    run_linear(synth.activations(1234, "status.x", 2, K), w, 4, 0, False)
+    assert kernels.device_status(torch.cuda.current_device()) == 0

@@ -135,8 +135,9 @@ def _py_codebook(s, cb):
         x = (s * 0x83DCD12D) & 0xFFFFFFFF
         u = sum((x >> (8 * i)) & 0xFF for i in range(4))
         S = float(np.uint16(0x1EEE).view(np.float16))
-        B = float(np.uint16(0xC2E7).view(np.float16))
-        return np.float16(np.float64(u) * S + B)      # exact in double, one rounding
+        B = float(np.uint16(0xC931).view(np.float16))
+        h = float(np.uint16(0x6400 + u).view(np.float16))   # = 1024 + u
+        return np.float16(np.float64(h) * S + B)      # exact in double, one rounding
     x = (s * 89226354 + 64248484) & 0xFFFFFFFF if cb == 0 else (s * 0xCBAC1FED) & 0xFFFFFFFF
     x = (x & 0x8FFF8FFF) ^ 0x3B603B60
     lo = np.uint16(x & 0xFFFF).view(np.float16)
