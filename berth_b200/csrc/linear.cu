@@ -7,7 +7,11 @@
 
 namespace berth {
 
-// Any row count through the GEMV kernel, 32 rows per launch.
+std::string launch_gemm_tc(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
+                           int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, unsigned* status,
+                           cudaStream_t stream);
+
+// Two kernels serve every row count: the fused decode GEMV up to 32 rows, the tensor-core GEMM above.
 std::string linear_rows(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, cudaStream_t stream)
 {
@@ -16,17 +20,10 @@ std::string linear_rows(const void* a, const void* trellis, void* c, const void*
     if (info.major != 10)
         throw std::runtime_error("exl3 linear: no linked kernel for this GPU (library is built for sm_100a only)");
     GemvScratch w = gemv_workspace(device);
-    std::string desc;
-    const size_t csz = out_fp32 ? 4 : 2;
-    for (int m0 = 0; m0 < size_m; m0 += 32) {
-        const int rows = std::min(32, size_m - m0);
-        desc = launch_gemv(static_cast<const char*>(a) + size_t(m0) * size_k * 2, trellis,
-                           static_cast<char*>(c) + size_t(m0) * size_n * csz, suh,
-                           static_cast<char*>(a_had) + size_t(m0) * size_k * 2, svh, rows, size_k, size_n, k_bits,
-                           codebook, out_fp32, w, info.sms, stream);
-    }
-    if (size_m > 32) desc += " x" + std::to_string((size_m + 31) / 32) + " row chunks";
-    return desc;
+    if (size_m <= 32)
+        return launch_gemv(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, out_fp32, w, info.sms,
+                           stream);
+    return launch_gemm_tc(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, out_fp32, w.status, stream);
 }
 
 namespace {

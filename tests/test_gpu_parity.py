@@ -244,3 +244,32 @@ def test_no_bounded_wait_ran_out():
     w = synth.linear_weights(1234, "status", K, N, 4)
     run_linear(synth.activations(1234, "status.x", 2, K), w, 4, 0, False)
     assert kernels.device_status(torch.cuda.current_device()) == 0
+
+
+# ---------------------------------------------------------------- tensor-core prefill GEMM (rows > 32)
+
+@pytest.mark.parametrize("m,K,N,bits,cb,out_fp32", [(33, 128, 128, 4, 2, True), (128, 256, 256, 4, 0, False),
+                                                   (200, 512, 384, 3, 1, True), (513, 1024, 256, 5, 2, False),
+                                                   (1499, 512, 128, 4, 2, True), (640, 256, 640, 6, 0, False)])
+def test_prefill_gemm_vs_oracle(oracle, m, K, N, bits, cb, out_fp32):
+    w = synth.linear_weights(1234, f"tc{K}x{N}b{bits}", K, N, bits)
+    x = synth.activations(1234, f"tc.x{m}", m, K, outlier_frac=0.001)
+    c, ah = run_linear(x, w, bits, cb, out_fp32, prefill=True)
+    assert "k_exl3_gemm_tc" in kernels.prefill_lin.last_launch()
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+    y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, N, bits, cb)
+    mx, mean = rel_errors(c, y64)
+    assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
+    assert (ah == oracle.had_r_128(x, w["suh"], True).view(np.uint16)).all()
+
+
+def test_prefill_gemm_matches_decode_kernel():
+    """The GEMM (rows > 32) and the GEMV (rows <= 32) agree row by row."""
+    K, N, bits, cb = 1024, 512, 4, 2
+    w = synth.linear_weights(1234, "tcvsgemv", K, N, bits)
+    x = synth.activations(1234, "tcvsgemv.x", 96, K)
+    big, _ = run_linear(x, w, bits, cb, True, prefill=True)
+    rms = np.sqrt((big.astype(np.float64) ** 2).mean())
+    for r0 in (0, 32, 64):
+        small, _ = run_linear(x[r0:r0 + 32], w, bits, cb, True)
+        assert np.abs(big[r0:r0 + 32] - small).max() <= 1e-3 * rms
