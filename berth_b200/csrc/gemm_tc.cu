@@ -56,6 +56,7 @@ struct GemmArgs {
     const __half* svh;
     unsigned* status;
     int m, k, n, out_fp32;
+    int nsub_max;   // 128-row sub-tiles per CTA (1..4): the row block of a CTA is nsub_max*128 tokens
 };
 
 // ---------------------------------------------------------------- PTX helpers
@@ -199,8 +200,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
     __shared__ uint32_t s_tmem_base;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int band = blockIdx.x, m0 = blockIdx.y * (MAX_SUB * SUB);
-    const int rows_here = min(p.m - m0, MAX_SUB * SUB);
+    const int band = blockIdx.x, m0 = blockIdx.y * (p.nsub_max * SUB);
+    const int rows_here = min(p.m - m0, p.nsub_max * SUB);
     const int nsub = (rows_here + SUB - 1) / SUB;
     const int kstages = p.k / BK;
 
@@ -422,7 +423,7 @@ void launch_tc(const void* a_had, const void* trellis, const GemmArgs& args, cud
     const cuuint64_t row_bytes = cuuint64_t(args.n / 16) * 32 * BITS;
     const CUtensorMap map_t = make_map(CU_TENSOR_MAP_DATA_TYPE_UINT64, trellis, row_bytes / 8, cuuint64_t(args.k / 16), row_bytes,
                                        TG_::TROW_BYTES / 8, 4, CU_TENSOR_MAP_SWIZZLE_NONE);
-    dim3 grid(args.n / BN, (args.m + MAX_SUB * SUB - 1) / (MAX_SUB * SUB));
+    dim3 grid(args.n / BN, (args.m + args.nsub_max * SUB - 1) / (args.nsub_max * SUB));
     kern<<<grid, kThreads, TG_::SMEM, stream>>>(map_a, map_t, args);
     cuda_ok(cudaGetLastError(), "k_exl3_gemm_tc launch");
 }
@@ -456,6 +457,20 @@ std::string launch_gemm_tc(const void* a, const void* trellis, void* c, const vo
     args.status = status;
     args.m = size_m; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
+    // Rows per CTA: 128..512.  More rows per decoded weight keep the kernel MMA bound (the decode
+    // warps need ~640 cycles per 64-deep stage, one 128-row sub-tile 256), fewer rows give more
+    // CTAs; pick the count with the fewest (waves x stage time) on this device.
+    {
+        const int sms = device_info(current_device()).sms;
+        const int bands = size_n / BN;
+        long long best = -1;
+        for (int ns = 1; ns <= MAX_SUB; ++ns) {
+            const long long ctas = (long long) bands * ((size_m + ns * SUB - 1) / (ns * SUB));
+            const long long waves = (ctas + sms - 1) / sms;
+            const long long cost = waves * std::max(ns * 256, 640);
+            if (best < 0 || cost <= best) { best = cost; args.nsub_max = ns; }   // ties: more rows per CTA
+        }
+    }
     switch (k_bits) {
         case 1: launch_tc_cb<1>(codebook, a_had, trellis, args, stream); break;
         case 2: launch_tc_cb<2>(codebook, a_had, trellis, args, stream); break;
@@ -468,8 +483,8 @@ std::string launch_gemm_tc(const void* a, const void* trellis, void* c, const vo
         default: throw std::runtime_error("exl3 linear: K must be in 1..=8");
     }
     return "k_had128<f16,pre> + k_exl3_gemm_tc<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "> grid=" +
-           std::to_string(size_n / BN) + "x" + std::to_string((size_m + MAX_SUB * SUB - 1) / (MAX_SUB * SUB)) +
-           " block=" + std::to_string(kThreads) + " tile=512x128x64 tmem=512";
+           std::to_string(size_n / BN) + "x" + std::to_string((size_m + args.nsub_max * SUB - 1) / (args.nsub_max * SUB)) +
+           " block=" + std::to_string(kThreads) + " tile=" + std::to_string(args.nsub_max * SUB) + "x128x64 tmem=512";
 }
 
 }  // namespace berth
