@@ -124,7 +124,7 @@ class DecodeStack:
         for l in range(LAYERS):
             lin = {}
             for name, k, n, _, _ in SHAPES:
-                w = synth.linear_weights(synth.MASTER_SEED, f"r{rank}.layers.{l}.{name}", k, n, BITS)
+                w = synth.linear_weights(synth.MASTER_SEED, f"r{rank}.layers.{l}.{name}", k, n, BITS, fan_in_gain=True)
                 lin[name] = Exl3Linear(self.gpu, f"layers.{l}.{name}", w["trellis"], w["suh"], w["svh"], BITS,
                                        Codebook(CB), max_rows=m)
             mlp = MlpLayer(self.gpu, lin["gate"], lin["up"], lin["down"], max_rows=m)
@@ -201,7 +201,7 @@ def cpu_pass(m: int, passes: int):
     from berth_b200 import synth
     from oracle import exl3_oracle as orc
     orc.build()
-    ws = {name: synth.linear_weights(synth.MASTER_SEED, f"cpu.{name}", k, n, BITS) for name, k, n, _, _ in SHAPES}
+    ws = {name: synth.linear_weights(synth.MASTER_SEED, f"cpu.{name}", k, n, BITS, fan_in_gain=True) for name, k, n, _, _ in SHAPES}
     x = {"x": synth.activations(1234, "cpu.x", m, HIDDEN), "xa": synth.activations(1234, "cpu.xa", m, HIDDEN),
          "attn": synth.activations(1234, "cpu.attn", m, QDIM)}
     t0 = time.perf_counter()

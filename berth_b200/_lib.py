@@ -43,6 +43,11 @@ SIGNATURES = {
     "berth_prefill_had_r_128": (_i, [_vp] * 3 + [_i] * 4 + [_vp]),
     "berth_ops_silu_mul": (_i, [_vp] * 3 + [_i64, _f, _vp]),
     "berth_ops_add_f32": (_i, [_vp] * 3 + [_i, _vp]),
+    "berth_moe_router_topk": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
+    "berth_moe_workspace_bytes": (C.c_size_t, [_i] * 6),
+    "berth_moe_layer": (_i, [C.POINTER(MoeWeights), _vp, _i, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
+    "berth_moe_last_error": (C.c_char_p, []),
+    "berth_moe_last_launch": (C.c_char_p, []),
     "berth_ops_last_error": (C.c_char_p, []),
     "berth_ops_last_launch": (C.c_char_p, []),
 }

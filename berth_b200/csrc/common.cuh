@@ -83,6 +83,22 @@ constexpr size_t kGemvBlocksumFloats = size_t(32) * 4096;
 constexpr size_t kGemvAfragBytes = size_t(8) << 20;   // size_k * ceil(size_m / 8) <= 524288
 GemvScratch gemv_workspace(int device);
 
+// One problem of a grouped decode launch: matrix `z` of a trellis stack applied to `rows` (at most
+// 8*TG) consecutive rows starting at `row0` of the activation / output row arrays.
+struct GemvProblem {
+    int z, row0, rows, pad;
+};
+
+// Grouped decode launch over a stack of equally shaped matrices (the experts of an MoE layer):
+// `problems` / `n_problems` live on the device (built by the dispatch kernels), xr fp16 [R][k] are
+// the routed rows, c the outputs [R][n]; suh_stack [experts][k], svh_stack [experts][n].
+// afrag / blocksum scratch must hold max_problems * (k/16) * tg * 256 bytes and
+// max_problems * 8 * tg * (k/128) floats.
+std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n_experts, void* c, const void* suh_stack,
+                                const void* svh_stack, const GemvProblem* problems, const int* n_problems, int max_problems,
+                                int tg, uint32_t* afrag, float* blocksum, int size_k, int size_n, int k_bits, int codebook,
+                                int out_fp32, const GemvScratch& scratch, int sms, cudaStream_t stream);
+
 std::string launch_gemv(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32,
                         const GemvScratch& scratch, int sms, cudaStream_t stream);

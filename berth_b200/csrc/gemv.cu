@@ -84,10 +84,12 @@ struct Geo {
 };
 
 struct GemvArgs {
-    const uint32_t* afrag;    // rotated activations in MMA fragment order [k/16][TG][2][8][4] words
-    const float* blocksum;    // [m][k/128]: sum of each rotated 128-block (MUL1 epilogue)
-    void* c;
-    const __half* svh;
+    const uint32_t* afrag;    // rotated activations in MMA fragment order [problem][k/16][TG][2][8][4] words
+    const float* blocksum;    // [problem][8*TG or m][k/128]: sum of each rotated 128-block (MUL1 epilogue)
+    void* c;                  // output rows [rows][n]
+    const __half* svh;        // [n], or the stack [experts][n] when grouped
+    const GemvProblem* problems;   // grouped launch: one entry per (expert, chunk of <= 8*TG rows); else null
+    const int* n_problems;         // grouped launch: device-side count
     float* slabs;             // [2*G][m][BU*128]
     unsigned* counters;       // [band groups][kEpiWarps], zero between launches
     unsigned* status;
@@ -135,11 +137,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
     }
     return true;
 }
-// One box of the 2-D trellis view (x in 8-byte elements, y in k-tile rows) into shared memory.
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
+// One box of the trellis view (x in 8-byte elements, y in k-tile rows, z = matrix of the stack)
+// into shared memory.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar)
 {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
                  : "memory");
 }
 // Contiguous global -> shared bulk copy (16-byte aligned, size a multiple of 16).
@@ -297,9 +300,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bands = p.n >> 7, kblocks = p.k >> 7;
-    const int bgroups = (bands + BU - 1) / BU;
-    const long long U = (long long) bgroups * kblocks;
-    const int G = gridDim.x, cta = blockIdx.x;
+    const int bgroups = (bands + BU - 1) / BU;          // band groups of one problem
+    const bool grouped = p.problems != nullptr;
+    const int nprob = grouped ? __ldg(p.n_problems) : 1;
+    const long long U = (long long) nprob * bgroups * kblocks;
+    const int cta = blockIdx.x;
+    const int G = U < (long long) gridDim.x ? int(U) : int(gridDim.x);   // CTAs that own units
+    if (cta >= G) return;
     const long long u0 = unit_begin(cta, U, G), u1 = unit_begin(cta + 1, U, G);
     const int nunits = int(u1 - u0);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + S);
@@ -322,35 +329,38 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
         // ------------------------------------------------------------ producer
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
-            auto unit_coords = [&](int i, int& bg, int& kb) {
+            // unit -> TMA coordinates of the weights and source of the activation block
+            auto issue_weights = [&](int i, uint32_t dst, uint32_t bar) {
                 const long long u = u0 + i;
-                bg = int(u / kblocks);
-                kb = int(u - (long long) bg * kblocks);
+                const int gbg = int(u / kblocks), kb = int(u - (long long) gbg * kblocks);
+                const int pi = gbg / bgroups, lbg = gbg - pi * bgroups;
+                const int z = grouped ? p.problems[pi].z : 0;
+                tma_load_3d(dst, &tmap, lbg * (ROW_BYTES / 8), kb * 8, z, bar);
+            };
+            auto issue_acts = [&](int i, uint32_t dst, uint32_t bar) {
+                const long long u = u0 + i;
+                const int gbg = int(u / kblocks), kb = int(u - (long long) gbg * kblocks);
+                const int pi = gbg / bgroups;
+                bulk_load_1d(dst, p.afrag + (size_t(pi) * kblocks + kb) * (ACT_BYTES / 4), ACT_BYTES, bar);
             };
             // The weights do not depend on the rotation kernel: fill the ring with them first,
             // then wait for the activations and complete those stages.
             const int pre = nunits < S ? nunits : S;
+            // (a grouped launch's problem table was written before the rotation kernel started, so it
+            // is already visible here)
             for (int i = 0; i < pre; ++i) {
-                int bg, kb;
-                unit_coords(i, bg, kb);
                 mbar_arrive_expect_tx(full0 + 8 * i, STAGE_BYTES);
-                tma_load_2d(smem_u32(ring + i * STAGE_BYTES), &tmap, bg * (ROW_BYTES / 8), kb * 8, full0 + 8 * i);
+                issue_weights(i, smem_u32(ring + i * STAGE_BYTES), full0 + 8 * i);
             }
             grid_dependency_wait();
-            for (int i = 0; i < pre; ++i) {
-                int bg, kb;
-                unit_coords(i, bg, kb);
-                bulk_load_1d(smem_u32(ring + i * STAGE_BYTES + W_BYTES), p.afrag + size_t(kb) * (ACT_BYTES / 4), ACT_BYTES, full0 + 8 * i);
-            }
+            for (int i = 0; i < pre; ++i) issue_acts(i, smem_u32(ring + i * STAGE_BYTES + W_BYTES), full0 + 8 * i);
             int s = 0, lap = 1;
             for (int i = pre; i < nunits; ++i) {
                 mbar_wait(empty0 + 8 * s, (lap - 1) & 1, p.status, kStEmptyTimeout);
-                int bg, kb;
-                unit_coords(i, bg, kb);
                 mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 const uint32_t dst = smem_u32(ring + s * STAGE_BYTES);
-                tma_load_2d(dst, &tmap, bg * (ROW_BYTES / 8), kb * 8, full0 + 8 * s);
-                bulk_load_1d(dst + W_BYTES, p.afrag + size_t(kb) * (ACT_BYTES / 4), ACT_BYTES, full0 + 8 * s);
+                issue_weights(i, dst, full0 + 8 * s);
+                issue_acts(i, dst + W_BYTES, full0 + 8 * s);
                 if (++s == S) { s = 0; ++lap; }
             }
         }
@@ -418,16 +428,26 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
     {
         const int ew = warp - kProducerWarp - 1;      // 0..3
         const int et = threadIdx.x - (kProducerWarp + 1) * 32;   // 0..127 = column inside a band
-        grid_dependency_wait();                       // block sums come from the rotation kernel
-        const size_t slab_floats = size_t(p.m) * BU * 128;
+        grid_dependency_wait();                       // block sums and problem table come from the preceding kernels
+        const int slab_rows = grouped ? TOK : p.m;
+        const size_t slab_floats = size_t(slab_rows) * BU * 128;
         int flush = 0;
         long long u = u0;
         while (u < u1) {
             const Segment sg = segment_at(u, u0, u1, kblocks);
+            // the problem this band group belongs to: its rows, output rows, sign-scale vector
+            const int pi = sg.bg / bgroups, lbg = sg.bg - pi * bgroups;
+            int rows = p.m, row0 = 0, z = 0;
+            if (grouped) {
+                const GemvProblem pr = p.problems[pi];
+                rows = pr.rows; row0 = pr.row0; z = pr.z;
+            }
+            const __half* svh = p.svh + size_t(z) * p.n;
+            const float* bsum = p.blocksum + size_t(pi) * slab_rows * kblocks;
             const int buf = flush & 1;
             mbar_wait(redfull0 + 8 * buf, (flush >> 1) & 1, p.status, kStRedFullTimeout);
             // fixed-order reduction over the row streams: thread et owns column et of every band
-            for (int tok = 0; tok < TOK && tok < p.m; ++tok) {
+            for (int tok = 0; tok < TOK && tok < rows; ++tok) {
 #pragma unroll
                 for (int b = 0; b < BU; ++b) {
                     float v = 0.f;
@@ -442,9 +462,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
 
             bool finish = true;
             int first_cta = cta, last_cta = cta, first_slab = 0;
-            if (!sg.whole && ew < p.m) {
+            if (!sg.whole && ew < rows) {
                 const int slab = sg.head ? 2 * cta : 2 * cta + 1;
-                for (int row = ew; row < p.m; row += kEpiWarps)
+                for (int row = ew; row < rows; row += kEpiWarps)
 #pragma unroll
                     for (int b = 0; b < BU; ++b) {
                         float4 v = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
@@ -465,16 +485,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
             }
 
             if (finish) {
-                for (int row = ew; row < p.m; row += kEpiWarps) {
+                for (int row = ew; row < rows; row += kEpiWarps) {
                     float sx = 0.f;
                     if constexpr (CB == 2) {
                         // w = S*h + B per weight  =>  sum_k x_k w_k = S*acc + B*sum_k x_k
-                        for (int b = lane; b < kblocks; b += 32) sx = __fadd_rn(sx, __ldg(p.blocksum + size_t(row) * kblocks + b));
+                        for (int b = lane; b < kblocks; b += 32) sx = __fadd_rn(sx, __ldg(bsum + size_t(row) * kblocks + b));
 #pragma unroll
                         for (int off = 16; off >= 1; off >>= 1) sx = __fadd_rn(sx, __shfl_xor_sync(dq::kFull, sx, off));
                     }
                     for (int b = 0; b < BU; ++b) {
-                        const int band = sg.bg * BU + b;
+                        const int band = lbg * BU + b;
                         if (band >= bands) break;   // ragged last band group
                         float v[4];
                         if (sg.whole) {
@@ -510,23 +530,23 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
                         }
                         dq::had128_warp(v, lane);
                         const int col = band * 128 + lane * 4;
-                        uint2 sr = *reinterpret_cast<const uint2*>(p.svh + col);
+                        uint2 sr = *reinterpret_cast<const uint2*>(svh + col);
                         __half2 s0 = *reinterpret_cast<__half2*>(&sr.x), s1 = *reinterpret_cast<__half2*>(&sr.y);
                         v[0] = __fmul_rn(__fmul_rn(v[0], kRScale), __low2float(s0));
                         v[1] = __fmul_rn(__fmul_rn(v[1], kRScale), __high2float(s0));
                         v[2] = __fmul_rn(__fmul_rn(v[2], kRScale), __low2float(s1));
                         v[3] = __fmul_rn(__fmul_rn(v[3], kRScale), __high2float(s1));
                         if (p.out_fp32) {
-                            *reinterpret_cast<float4*>(static_cast<float*>(p.c) + size_t(row) * p.n + col) = make_float4(v[0], v[1], v[2], v[3]);
+                            *reinterpret_cast<float4*>(static_cast<float*>(p.c) + size_t(row0 + row) * p.n + col) = make_float4(v[0], v[1], v[2], v[3]);
                         } else {
                             uint2 o;
                             o.x = dq::pack_half2(__float2half_rn(v[0]), __float2half_rn(v[1]));
                             o.y = dq::pack_half2(__float2half_rn(v[2]), __float2half_rn(v[3]));
-                            *reinterpret_cast<uint2*>(static_cast<__half*>(p.c) + size_t(row) * p.n + col) = o;
+                            *reinterpret_cast<uint2*>(static_cast<__half*>(p.c) + size_t(row0 + row) * p.n + col) = o;
                         }
                     }
                 }
-                if (!sg.whole && ew < p.m && lane == 0) p.counters[sg.bg * kEpiWarps + ew] = 0;   // self-resetting
+                if (!sg.whole && ew < rows && lane == 0) p.counters[sg.bg * kEpiWarps + ew] = 0;   // self-resetting
             }
             epi_sync();   // outbuf is free again
             ++flush;
@@ -597,18 +617,19 @@ EncodeTiledFn encode_tiled()
     return fn;
 }
 
-// 2-D view of a trellis: rows = k-tile rows (K/16), row = (N/16) tiles of 32*bits bytes, in 8-byte
-// elements; box = one unit (8 rows x BU bands).  Columns past the matrix read as zero.
-CUtensorMap trellis_map(const void* trellis, int size_k, int size_n, int bits, int box_bytes)
+// 3-D view of a trellis stack: z = matrix, y = k-tile row (K/16), x = the row's (N/16) tiles of
+// 32*bits bytes in 8-byte elements; box = one unit (8 rows x BU bands of one matrix).  Columns
+// past the matrix read as zero.
+CUtensorMap trellis_map(const void* trellis, int n_matrices, int size_k, int size_n, int bits, int box_bytes)
 {
     if (reinterpret_cast<uintptr_t>(trellis) % 16 != 0) throw std::runtime_error("exl3 linear: trellis must be 16-byte aligned");
     CUtensorMap map;
     const cuuint64_t row_bytes = cuuint64_t(size_n / 16) * 32 * bits;
-    const cuuint64_t dims[2] = {row_bytes / 8, cuuint64_t(size_k / 16)};
-    const cuuint64_t strides[1] = {row_bytes};
-    const cuuint32_t box[2] = {cuuint32_t(box_bytes / 8), 8};
-    const cuuint32_t elem[2] = {1, 1};
-    CUresult r = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(trellis), dims, strides, box, elem,
+    const cuuint64_t dims[3] = {row_bytes / 8, cuuint64_t(size_k / 16), cuuint64_t(n_matrices)};
+    const cuuint64_t strides[2] = {row_bytes, row_bytes * cuuint64_t(size_k / 16)};
+    const cuuint32_t box[3] = {cuuint32_t(box_bytes / 8), 8, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void*>(trellis), dims, strides, box, elem,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) throw std::runtime_error("exl3 linear: cuTensorMapEncodeTiled failed (" + std::to_string(int(r)) + ")");
@@ -616,7 +637,7 @@ CUtensorMap trellis_map(const void* trellis, int size_k, int size_n, int bits, i
 }
 
 template <int BITS, int CB, int TG>
-size_t launch_one(const void* trellis, const GemvArgs& args, int grid, cudaStream_t stream)
+size_t launch_one(const void* trellis, int n_matrices, const GemvArgs& args, int grid, cudaStream_t stream)
 {
     using G_ = Geo<BITS, TG>;
     auto kern = k_exl3_gemv<BITS, CB, TG>;
@@ -626,7 +647,7 @@ size_t launch_one(const void* trellis, const GemvArgs& args, int grid, cudaStrea
         cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(G_::SMEM)), "gemv smem attribute");
         attr_set[dev] = true;
     }
-    const CUtensorMap map = trellis_map(trellis, args.k, args.n, BITS, G_::ROW_BYTES);
+    const CUtensorMap map = trellis_map(trellis, n_matrices, args.k, args.n, BITS, G_::ROW_BYTES);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);
@@ -642,22 +663,81 @@ size_t launch_one(const void* trellis, const GemvArgs& args, int grid, cudaStrea
 }
 
 template <int BITS, int CB>
-size_t launch_tg(int tg, const void* t, const GemvArgs& a, int grid, cudaStream_t st)
+size_t launch_tg(int tg, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
 {
     switch (tg) {
-        case 1: return launch_one<BITS, CB, 1>(t, a, grid, st);
-        case 2: return launch_one<BITS, CB, 2>(t, a, grid, st);
-        default: return launch_one<BITS, CB, 4>(t, a, grid, st);
+        case 1: return launch_one<BITS, CB, 1>(t, nm, a, grid, st);
+        case 2: return launch_one<BITS, CB, 2>(t, nm, a, grid, st);
+        default: return launch_one<BITS, CB, 4>(t, nm, a, grid, st);
     }
 }
 
 template <int BITS>
-size_t launch_cb(int cb, int tg, const void* t, const GemvArgs& a, int grid, cudaStream_t st)
+size_t launch_cb(int cb, int tg, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
 {
     switch (cb) {
-        case 0: return launch_tg<BITS, 0>(tg, t, a, grid, st);
-        case 1: return launch_tg<BITS, 1>(tg, t, a, grid, st);
-        default: return launch_tg<BITS, 2>(tg, t, a, grid, st);
+        case 0: return launch_tg<BITS, 0>(tg, t, nm, a, grid, st);
+        case 1: return launch_tg<BITS, 1>(tg, t, nm, a, grid, st);
+        default: return launch_tg<BITS, 2>(tg, t, nm, a, grid, st);
+    }
+}
+
+size_t launch_bits(int k_bits, int cb, int tg, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
+{
+    switch (k_bits) {
+        case 1: return launch_cb<1>(cb, tg, t, nm, a, grid, st);
+        case 2: return launch_cb<2>(cb, tg, t, nm, a, grid, st);
+        case 3: return launch_cb<3>(cb, tg, t, nm, a, grid, st);
+        case 4: return launch_cb<4>(cb, tg, t, nm, a, grid, st);
+        case 5: return launch_cb<5>(cb, tg, t, nm, a, grid, st);
+        case 6: return launch_cb<6>(cb, tg, t, nm, a, grid, st);
+        case 7: return launch_cb<7>(cb, tg, t, nm, a, grid, st);
+        case 8: return launch_cb<8>(cb, tg, t, nm, a, grid, st);
+        default: throw std::runtime_error("exl3 linear: K must be in 1..=8");
+    }
+}
+
+// Rotation for a grouped launch: routed rows xr [R][k], one warp per (problem, padded row, 128-block);
+// the row's expert picks the sign-scale vector.  Rows past a problem's count are written as zeros.
+__global__ void __launch_bounds__(128) k_rotate_rows(const __half* __restrict__ xr, const __half* __restrict__ suh_stack,
+                                                     const GemvProblem* __restrict__ problems, const int* __restrict__ n_problems,
+                                                     uint32_t* __restrict__ afrag, float* __restrict__ blocksum, int tok, int k)
+{
+    grid_dependency_wait();      // the problem table comes from the preceding kernel
+    grid_launch_dependents();
+    const int lane = threadIdx.x & 31, kblocks = k >> 7, tgs = tok >> 3;
+    const long long total = (long long) __ldg(n_problems) * tok * kblocks;
+    for (long long idx = (long long) blockIdx.x * 4 + (threadIdx.x >> 5); idx < total; idx += (long long) gridDim.x * 4) {
+        const int b = int(idx % kblocks);
+        const int lr = int((idx / kblocks) % tok);
+        const int pi = int(idx / ((long long) kblocks * tok));
+        const GemvProblem pr = problems[pi];
+        const int kcol = b * 128 + lane * 4;
+        uint2 o = make_uint2(0u, 0u);
+        if (lr < pr.rows) {
+            uint2 xw = *reinterpret_cast<const uint2*>(xr + size_t(pr.row0 + lr) * k + kcol);
+            uint2 sr = *reinterpret_cast<const uint2*>(suh_stack + size_t(pr.z) * k + kcol);
+            __half2 x0 = *reinterpret_cast<__half2*>(&xw.x), x1 = *reinterpret_cast<__half2*>(&xw.y);
+            __half2 s0 = *reinterpret_cast<__half2*>(&sr.x), s1 = *reinterpret_cast<__half2*>(&sr.y);
+            float v[4];
+            v[0] = __fmul_rn(__low2float(x0), __low2float(s0));
+            v[1] = __fmul_rn(__high2float(x0), __high2float(s0));
+            v[2] = __fmul_rn(__low2float(x1), __low2float(s1));
+            v[3] = __fmul_rn(__high2float(x1), __high2float(s1));
+            dq::had128_warp(v, lane);
+            __half h[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) h[i] = __float2half_rn(__fmul_rn(v[i], kRScale));
+            o.x = dq::pack_half2(h[0], h[1]);
+            o.y = dq::pack_half2(h[2], h[3]);
+            float sx = __fadd_rn(__fadd_rn(__half2float(h[0]), __half2float(h[1])), __fadd_rn(__half2float(h[2]), __half2float(h[3])));
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) sx = __fadd_rn(sx, __shfl_xor_sync(dq::kFull, sx, off));
+            if (lane == 0) blocksum[(size_t(pi) * tok + lr) * kblocks + b] = sx;
+        }
+        const int ktile = b * 8 + (lane >> 2), hsel = (lane & 3) >> 1, q = 2 * (lane & 1);
+        const size_t w = (((size_t(pi) * (k >> 4) + ktile) * tgs + (lr >> 3)) * 2 + hsel) * 32 + (lr & 7) * 4 + q;
+        *reinterpret_cast<uint2*>(afrag + w) = o;
     }
 }
 
@@ -707,19 +787,48 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     args.status = sc.status;
     args.m = size_m; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
-    size_t smem = 0;
-    switch (k_bits) {
-        case 1: smem = launch_cb<1>(codebook, tg, trellis, args, grid, stream); break;
-        case 2: smem = launch_cb<2>(codebook, tg, trellis, args, grid, stream); break;
-        case 3: smem = launch_cb<3>(codebook, tg, trellis, args, grid, stream); break;
-        case 4: smem = launch_cb<4>(codebook, tg, trellis, args, grid, stream); break;
-        case 5: smem = launch_cb<5>(codebook, tg, trellis, args, grid, stream); break;
-        case 6: smem = launch_cb<6>(codebook, tg, trellis, args, grid, stream); break;
-        case 7: smem = launch_cb<7>(codebook, tg, trellis, args, grid, stream); break;
-        default: smem = launch_cb<8>(codebook, tg, trellis, args, grid, stream); break;
-    }
+    args.problems = nullptr;
+    args.n_problems = nullptr;
+    const size_t smem = launch_bits(k_bits, codebook, tg, trellis, 1, args, grid, stream);
     return "k_rotate_in + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," + std::to_string(tg) +
            "> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem);
+}
+
+std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n_experts, void* c, const void* suh_stack,
+                                const void* svh_stack, const GemvProblem* problems, const int* n_problems, int max_problems,
+                                int tg, uint32_t* afrag, float* blocksum, int size_k, int size_n, int k_bits, int codebook,
+                                int out_fp32, const GemvScratch& sc, int sms, cudaStream_t stream)
+{
+    if (size_k % 128 != 0 || size_n % 128 != 0)
+        throw std::runtime_error("exl3 grouped gemv: size_k and size_n must be multiples of 128");
+    if (tg != 1 && tg != 2 && tg != 4) throw std::runtime_error("exl3 grouped gemv: token groups must be 1, 2 or 4");
+    const int bu = k_bits <= 4 ? 2 : 1;
+    const int bands = size_n / 128, bgroups = (bands + bu - 1) / bu;
+    if ((long long) max_problems * bgroups * kEpiWarps > sc.counter_slots)
+        throw std::runtime_error("exl3 grouped gemv: problems x band groups exceed the counter table of the scratch");
+    int grid = sms;
+    const size_t per_cta = size_t(2) * 8 * tg * bu * 128 * sizeof(float);
+    if (size_t(grid) * per_cta > sc.slab_bytes) grid = int(sc.slab_bytes / per_cta);
+    if (grid < 1) throw std::runtime_error("exl3 grouped gemv: split-K scratch is too small");
+    const long long warps = (long long) max_problems * 8 * tg * (size_k / 128);
+    k_rotate_rows<<<int(std::min<long long>((warps + 3) / 4, 8LL * sms)), 128, 0, stream>>>(
+        static_cast<const __half*>(xr), static_cast<const __half*>(suh_stack), problems, n_problems, afrag, blocksum, 8 * tg, size_k);
+    cuda_ok(cudaGetLastError(), "k_rotate_rows launch");
+    GemvArgs args;
+    args.afrag = afrag;
+    args.blocksum = blocksum;
+    args.c = c;
+    args.svh = static_cast<const __half*>(svh_stack);
+    args.problems = problems;
+    args.n_problems = n_problems;
+    args.slabs = sc.slabs;
+    args.counters = sc.counters;
+    args.status = sc.status;
+    args.m = 8 * tg; args.k = size_k; args.n = size_n;
+    args.out_fp32 = out_fp32;
+    const size_t smem = launch_bits(k_bits, codebook, tg, trellis_stack, n_experts, args, grid, stream);
+    return "k_rotate_rows + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," + std::to_string(tg) +
+           ",grouped> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem);
 }
 
 }  // namespace berth

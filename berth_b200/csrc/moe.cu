@@ -1,0 +1,369 @@
+// A3B-style mixture-of-experts layer on top of the grouped decode kernel: router (fixed-order
+// fp32 logits, warp top-k with ties to the lower expert index, softmax over the selection),
+// dispatch (per-expert count, exclusive scan, stable permutation, row gather, problem table),
+// grouped gate/up/SiLU/down over the routed rows, weighted combine plus shared expert.
+// berth has the shape contract of this block but no operator; the arithmetic contract is the
+// one the CPU checker under oracle/ states (router summation order, tie rule, rounding points).
+#include "exl3_decode.cuh"
+#include "../../include/berth_b200.h"
+
+#include <algorithm>
+
+namespace berth {
+
+std::string linear_rows(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
+                        int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, cudaStream_t stream);
+
+namespace {
+
+// ---------------------------------------------------------------- router
+// logits[t][e] = sum over 32 chunks of H/32 sequential fmaf, chunks combined by an xor tree: the
+// summation order of the CPU checker, so the top-k indices can be compared bit for bit.
+// Block = 32 experts x 32 chunks; a warp holds the 32 chunks of one expert.
+__global__ void __launch_bounds__(1024) k_moe_router_logits(const __half* __restrict__ x, const __half* __restrict__ w,
+                                                            const float* __restrict__ bias, float* __restrict__ logits,
+                                                            int H, int E)
+{
+    const int t = blockIdx.y, e = blockIdx.x * 32 + (threadIdx.x >> 5), j = threadIdx.x & 31;
+    const int chunk = H / 32;
+    const __half* xr = x + size_t(t) * H + j * chunk;
+    const __half* wr = w + size_t(j) * chunk * E + e;
+    float acc = 0.f;
+    for (int i = 0; i < chunk; ++i) acc = __fmaf_rn(__half2float(xr[i]), __half2float(wr[size_t(i) * E]), acc);
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(dq::kFull, acc, off));
+    if (j == 0) logits[size_t(t) * E + e] = __fadd_rn(acc, bias ? bias[e] : 0.f);
+}
+
+// One warp per token: k rounds of arg-max, value descending then index ascending.
+__global__ void __launch_bounds__(128) k_moe_topk(const float* __restrict__ logits, int32_t* __restrict__ topk_idx,
+                                                  float* __restrict__ topk_w, int T, int E, int k)
+{
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    const float* l = logits + size_t(t) * E;
+    constexpr int kMaxPerLane = 32;   // E <= 1024
+    float v[kMaxPerLane];
+    const int per = (E + 31) / 32;
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) v[i] = (i < per && lane + 32 * i < E) ? l[lane + 32 * i] : -INFINITY;
+    unsigned taken = 0;   // bit i: this lane's i-th expert already selected
+    float first = 0.f, mine = 0.f, sum = 0.f;
+    for (int s = 0; s < k; ++s) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < kMaxPerLane; ++i)
+            if (i < per && !((taken >> i) & 1u) && lane + 32 * i < E) {
+                const int idx = lane + 32 * i;
+                if (v[i] > bv || (v[i] == bv && idx < bi)) { bv = v[i]; bi = idx; }
+            }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const float ov = __shfl_xor_sync(dq::kFull, bv, off);
+            const int oi = __shfl_xor_sync(dq::kFull, bi, off);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+        if (s == 0) first = bv;
+        const float ex = expf(bv - first);
+        sum += ex;
+        if (lane == s) mine = ex;      // k <= 32
+        if (lane == 0) topk_idx[size_t(t) * k + s] = bi;
+    }
+    if (lane < k) topk_w[size_t(t) * k + lane] = mine / sum;
+}
+
+// ---------------------------------------------------------------- dispatch
+// counts[j] = number of entries whose key is e0 + j.  One block per local expert.
+__global__ void __launch_bounds__(256) k_moe_count(const int32_t* __restrict__ keys, int n, int e0, int* __restrict__ counts)
+{
+    const int e = e0 + blockIdx.x;
+    int c = 0;
+    for (int i = threadIdx.x; i < n; i += 256) c += (keys[i] == e);
+    __shared__ int red[8];
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) c += __shfl_xor_sync(dq::kFull, c, off);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int s = 0;
+        for (int i = 0; i < 8; ++i) s += red[i];
+        counts[blockIdx.x] = s;
+    }
+}
+
+// offsets[0..n_local] = exclusive scan of counts; problem table: every expert's rows in chunks of
+// `chunk` rows.  One thread: n_local is a few hundred.
+__global__ void k_moe_scan(const int* __restrict__ counts, int* __restrict__ offsets, GemvProblem* __restrict__ problems,
+                           int* __restrict__ n_problems, int n_local, int chunk)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int off = 0, np = 0;
+    for (int j = 0; j < n_local; ++j) {
+        offsets[j] = off;
+        const int c = counts[j];
+        for (int r0 = 0; r0 < c; r0 += chunk) {
+            GemvProblem pr;
+            pr.z = j; pr.row0 = off + r0; pr.rows = min(chunk, c - r0); pr.pad = 0;
+            problems[np++] = pr;
+        }
+        off += c;
+    }
+    offsets[n_local] = off;
+    *n_problems = np;
+}
+
+// Stable permutation: block j walks the entries in order; the r-th entry with key e0 + j goes to
+// position offsets[j] + r.  perm[pos] = entry, inv[entry] = pos.
+__global__ void __launch_bounds__(256) k_moe_scatter(const int32_t* __restrict__ keys, int n, int e0,
+                                                     const int* __restrict__ offsets, int32_t* __restrict__ perm,
+                                                     int32_t* __restrict__ inv)
+{
+    const int e = e0 + blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ int wsum[8];
+    int running = offsets[blockIdx.x];
+    for (int base = 0; base < n; base += 256) {
+        const int i = base + threadIdx.x;
+        const bool hit = i < n && keys[i] == e;
+        const unsigned ballot = __ballot_sync(dq::kFull, hit);
+        if (lane == 0) wsum[warp] = __popc(ballot);
+        __syncthreads();
+        int before = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const int c = wsum[w];
+            before += (w < warp) ? c : 0;
+            total += c;
+        }
+        if (hit) {
+            const int pos = running + before + __popc(ballot & ((1u << lane) - 1u));
+            perm[pos] = i;
+            inv[i] = pos;
+        }
+        running += total;
+        __syncthreads();
+    }
+}
+
+// xr[pos][:] = x[perm[pos] / div][:]  (div = top_k when entries are (token, slot) pairs).
+__global__ void __launch_bounds__(256) k_moe_gather_rows(const __half* __restrict__ x, const int32_t* __restrict__ perm,
+                                                         const int* __restrict__ n_rows, int div, __half* __restrict__ xr, int H)
+{
+    const int R = __ldg(n_rows);
+    for (int pos = blockIdx.x; pos < R; pos += gridDim.x) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + size_t(perm[pos] / div) * H);
+        uint4* dst = reinterpret_cast<uint4*>(xr + size_t(pos) * H);
+        for (int i = threadIdx.x; i < H / 8; i += 256) dst[i] = src[i];
+    }
+}
+
+// out[t][h] = sum_s w[t][s] * y[inv[t*k+s]][h]  (fmaf chain in slot order)  + ysh[t][h]
+__global__ void __launch_bounds__(256) k_moe_combine(const __half* __restrict__ y, const int32_t* __restrict__ inv,
+                                                     const float* __restrict__ topk_w, const __half* __restrict__ ysh,
+                                                     float* __restrict__ out, int H, int k)
+{
+    const int t = blockIdx.x;
+    for (int h = threadIdx.x * 2; h < H; h += 512) {
+        float a0 = 0.f, a1 = 0.f;
+        for (int s = 0; s < k; ++s) {
+            const float w = topk_w[size_t(t) * k + s];
+            const __half2 v = *reinterpret_cast<const __half2*>(y + size_t(inv[size_t(t) * k + s]) * H + h);
+            a0 = __fmaf_rn(w, __low2float(v), a0);
+            a1 = __fmaf_rn(w, __high2float(v), a1);
+        }
+        if (ysh) {
+            const __half2 v = *reinterpret_cast<const __half2*>(ysh + size_t(t) * H + h);
+            a0 = __fadd_rn(a0, __low2float(v));
+            a1 = __fadd_rn(a1, __high2float(v));
+        }
+        *reinterpret_cast<float2*>(out + size_t(t) * H + h) = make_float2(a0, a1);
+    }
+}
+
+inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+int token_groups(int max_rows_per_expert) { return max_rows_per_expert <= 8 ? 1 : (max_rows_per_expert <= 16 ? 2 : 4); }
+
+// Workspace carve-up of the expert stage for up to R routed rows.
+struct ExpertScratch {
+    int* counts; int* offsets; int* n_problems; GemvProblem* problems;
+    uint32_t* afrag; float* blocksum; __half* g; __half* u; int max_problems;
+    size_t bytes;
+};
+ExpertScratch carve_experts(void* base, int R, int n_local, int hidden, int inter, int tg)
+{
+    ExpertScratch s{};
+    const int chunk = 8 * tg;
+    s.max_problems = R / chunk + n_local;
+    const int kmax = std::max(hidden, inter);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off += align256(bytes); return o; };
+    const size_t o_counts = take(size_t(n_local) * 4), o_offsets = take(size_t(n_local + 1) * 4), o_np = take(4);
+    const size_t o_prob = take(size_t(s.max_problems) * sizeof(GemvProblem));
+    const size_t o_afrag = take(size_t(s.max_problems) * (kmax / 16) * tg * 256);
+    const size_t o_bsum = take(size_t(s.max_problems) * chunk * (kmax / 128) * 4);
+    const size_t o_g = take(size_t(R) * inter * 2), o_u = take(size_t(R) * inter * 2);
+    s.bytes = off;
+    if (base) {
+        char* b = static_cast<char*>(base);
+        s.counts = (int*) (b + o_counts); s.offsets = (int*) (b + o_offsets); s.n_problems = (int*) (b + o_np);
+        s.problems = (GemvProblem*) (b + o_prob); s.afrag = (uint32_t*) (b + o_afrag); s.blocksum = (float*) (b + o_bsum);
+        s.g = (__half*) (b + o_g); s.u = (__half*) (b + o_u);
+    }
+    return s;
+}
+
+void check_moe_shapes(const berth_moe_weights* w, int T)
+{
+    if (!w) throw std::runtime_error("moe: null weights");
+    if (T < 1) throw std::runtime_error("moe: T must be positive");
+    if (w->hidden % 128 || w->inter % 128 || w->hidden < 128 || w->inter < 128)
+        throw std::runtime_error("moe: hidden and inter must be multiples of 128");
+    if (w->shared_inter % 128) throw std::runtime_error("moe: shared_inter must be a multiple of 128");
+    if (w->n_experts < 1 || w->n_experts > 1024 || w->n_experts % 32)
+        throw std::runtime_error("moe: n_experts must be a multiple of 32 up to 1024");
+    if (w->top_k < 1 || w->top_k > 32 || w->top_k > w->n_experts) throw std::runtime_error("moe: top_k must be in 1..=32");
+    if (w->hidden % 32) throw std::runtime_error("moe: hidden must be a multiple of 32");
+    if (w->k_bits < 1 || w->k_bits > 8) throw std::runtime_error("moe: K must be in 1..=8");
+    if (w->codebook < 0 || w->codebook > 2) throw std::runtime_error("moe: codebook must be 0, 1, or 2");
+}
+
+void router_topk(const void* x, const void* w_router, const float* bias, int32_t* topk_idx, float* topk_w, float* logits,
+                 int T, int H, int E, int k, cudaStream_t st)
+{
+    k_moe_router_logits<<<dim3(E / 32, T), 1024, 0, st>>>((const __half*) x, (const __half*) w_router, bias, logits, H, E);
+    cuda_ok(cudaGetLastError(), "k_moe_router_logits launch");
+    k_moe_topk<<<(T + 3) / 4, 128, 0, st>>>(logits, topk_idx, topk_w, T, E, k);
+    cuda_ok(cudaGetLastError(), "k_moe_topk launch");
+}
+
+// keys[n] -> counts/offsets/problems + perm/inv; experts [e0, e0 + n_local).
+void dispatch(const int32_t* keys, int n, int e0, int n_local, int chunk, const ExpertScratch& s, int32_t* perm, int32_t* inv,
+              cudaStream_t st)
+{
+    k_moe_count<<<n_local, 256, 0, st>>>(keys, n, e0, s.counts);
+    cuda_ok(cudaGetLastError(), "k_moe_count launch");
+    k_moe_scan<<<1, 32, 0, st>>>(s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk);
+    cuda_ok(cudaGetLastError(), "k_moe_scan launch");
+    k_moe_scatter<<<n_local, 256, 0, st>>>(keys, n, e0, s.offsets, perm, inv);
+    cuda_ok(cudaGetLastError(), "k_moe_scatter launch");
+}
+
+// Grouped gate/up -> silu*up -> down over routed rows xr [R][hidden]; yr fp16 [R][hidden].
+std::string experts(const berth_moe_weights* w, const void* gate_t, const void* up_t, const void* down_t, const void* gsuh,
+                    const void* gsvh, const void* usuh, const void* usvh, const void* dsuh, const void* dsvh, int n_local,
+                    const void* xr, void* yr, int R, int tg, const ExpertScratch& s, const GemvScratch& sc, int sms, cudaStream_t st)
+{
+    const int H = w->hidden, I = w->inter;
+    std::string d = launch_gemv_grouped(xr, gate_t, n_local, s.g, gsuh, gsvh, s.problems, s.n_problems, s.max_problems, tg, s.afrag,
+                                        s.blocksum, H, I, w->k_bits, w->codebook, 0, sc, sms, st);
+    launch_gemv_grouped(xr, up_t, n_local, s.u, usuh, usvh, s.problems, s.n_problems, s.max_problems, tg, s.afrag, s.blocksum, H, I,
+                        w->k_bits, w->codebook, 0, sc, sms, st);
+    if (berth_ops_silu_mul(s.g, s.u, s.g, int64_t(R) * I, 0.0f, st) != 0) throw std::runtime_error(berth_ops_last_error());
+    launch_gemv_grouped(s.g, down_t, n_local, yr, dsuh, dsvh, s.problems, s.n_problems, s.max_problems, tg, s.afrag, s.blocksum, I, H,
+                        w->k_bits, w->codebook, 0, sc, sms, st);
+    return d;
+}
+
+}  // namespace
+}  // namespace berth
+
+using namespace berth;
+
+extern "C" const char* berth_moe_last_error(void) { return moe_state().err.c_str(); }
+extern "C" const char* berth_moe_last_launch(void) { return moe_state().launch.c_str(); }
+
+extern "C" int berth_moe_router_topk(const void* x, const void* w_router, const float* router_bias, int32_t* topk_idx,
+                                     float* topk_w, float* logits, int T, int hidden, int n_experts, int top_k, void* stream)
+{
+    CallState& st = moe_state();
+    return guarded(st, [&] {
+        if (!x || !w_router || !topk_idx || !topk_w || !logits) throw std::runtime_error("moe router: null device pointer");
+        if (T < 1) throw std::runtime_error("moe router: T must be positive");
+        if (hidden < 32 || hidden % 32) throw std::runtime_error("moe router: hidden must be a multiple of 32");
+        if (n_experts < 32 || n_experts % 32 || n_experts > 1024)
+            throw std::runtime_error("moe router: n_experts must be a multiple of 32 up to 1024");
+        if (top_k < 1 || top_k > 32 || top_k > n_experts) throw std::runtime_error("moe router: top_k must be in 1..=32");
+        router_topk(x, w_router, router_bias, topk_idx, topk_w, logits, T, hidden, n_experts, top_k, (cudaStream_t) stream);
+        st.launch = "k_moe_router_logits grid=" + std::to_string(n_experts / 32) + "x" + std::to_string(T) + " + k_moe_topk";
+    });
+}
+
+extern "C" size_t berth_moe_workspace_bytes(int T, int hidden, int inter, int shared_inter, int n_experts, int top_k)
+{
+    if (T < 1 || hidden < 128 || inter < 128 || n_experts < 1 || top_k < 1) return 0;
+    const int R = T * top_k;
+    const int tg = token_groups(T);
+    const ExpertScratch es = carve_experts(nullptr, R, n_experts, hidden, inter, tg);
+    size_t total = 0;
+    total += align256(size_t(T) * n_experts * 4);            // logits
+    total += 2 * align256(size_t(R) * 4);                    // perm, inv
+    total += 2 * align256(size_t(R) * hidden * 2);           // xr, yr
+    total += es.bytes;
+    if (shared_inter > 0) {
+        total += 3 * align256(size_t(T) * shared_inter * 2);                 // shared gate, up outputs + rotated
+        total += align256(size_t(T) * hidden * 2) * 2;                        // shared out, rotated input
+    }
+    return total + 4096;
+}
+
+extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T, void* out, int32_t* topk_idx, float* topk_w,
+                               void* workspace, size_t workspace_bytes, void* stream)
+{
+    CallState& st = moe_state();
+    return guarded(st, [&] {
+        check_moe_shapes(w, T);
+        if (!x || !out || !topk_idx || !topk_w || !workspace) throw std::runtime_error("moe layer: null device pointer");
+        if (!w->w_router || !w->gate_trellis || !w->up_trellis || !w->down_trellis || !w->gate_suh || !w->gate_svh ||
+            !w->up_suh || !w->up_svh || !w->down_suh || !w->down_svh)
+            throw std::runtime_error("moe layer: null weight pointer");
+        const size_t need = berth_moe_workspace_bytes(T, w->hidden, w->inter, w->shared_inter, w->n_experts, w->top_k);
+        if (workspace_bytes < need)
+            throw std::runtime_error("moe layer: workspace of " + std::to_string(workspace_bytes) + " bytes is smaller than the " +
+                                     std::to_string(need) + " required");
+        const int device = current_device();
+        const DeviceInfo& info = device_info(device);
+        if (info.major != 10) throw std::runtime_error("moe layer: no linked kernel for this GPU (library is built for sm_100a only)");
+        GemvScratch sc = gemv_workspace(device);
+        cudaStream_t cs = (cudaStream_t) stream;
+        const int H = w->hidden, I = w->inter, E = w->n_experts, K = w->top_k, R = T * K, SI = w->shared_inter;
+        const int tg = token_groups(T);
+
+        char* b = static_cast<char*>(workspace);
+        b = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(b) + 255) & ~uintptr_t(255));
+        auto take = [&](size_t bytes) { char* p = b; b += align256(bytes); return p; };
+        float* logits = (float*) take(size_t(T) * E * 4);
+        int32_t* perm = (int32_t*) take(size_t(R) * 4);
+        int32_t* inv = (int32_t*) take(size_t(R) * 4);
+        __half* xr = (__half*) take(size_t(R) * H * 2);
+        __half* yr = (__half*) take(size_t(R) * H * 2);
+        ExpertScratch es = carve_experts(b, R, E, H, I, tg);
+        b += es.bytes;
+
+        router_topk(x, w->w_router, w->router_bias, topk_idx, topk_w, logits, T, H, E, K, cs);
+        dispatch(topk_idx, R, 0, E, 8 * tg, es, perm, inv, cs);
+        k_moe_gather_rows<<<std::min(R, 148 * 8), 256, 0, cs>>>((const __half*) x, perm, es.offsets + E, K, xr, H);
+        cuda_ok(cudaGetLastError(), "k_moe_gather_rows launch");
+        st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
+                            w->down_suh, w->down_svh, E, xr, yr, R, tg, es, sc, info.sms, cs);
+
+        __half* ysh = nullptr;
+        if (SI > 0) {
+            if (!w->sh_gate_trellis || !w->sh_up_trellis || !w->sh_down_trellis) throw std::runtime_error("moe layer: null shared-expert pointer");
+            __half* sg = (__half*) take(size_t(T) * SI * 2);
+            __half* su = (__half*) take(size_t(T) * SI * 2);
+            __half* sr = (__half*) take(size_t(T) * SI * 2);     // rotated-input scratch of the down projection
+            ysh = (__half*) take(size_t(T) * H * 2);
+            __half* xrot = (__half*) take(size_t(T) * H * 2);    // rotated-input scratch of gate / up
+            linear_rows(x, w->sh_gate_trellis, sg, w->sh_gate_suh, xrot, w->sh_gate_svh, T, H, SI, w->k_bits, w->codebook, 0, cs);
+            linear_rows(x, w->sh_up_trellis, su, w->sh_up_suh, xrot, w->sh_up_svh, T, H, SI, w->k_bits, w->codebook, 0, cs);
+            if (berth_ops_silu_mul(sg, su, sg, int64_t(T) * SI, 0.0f, cs) != 0) throw std::runtime_error(berth_ops_last_error());
+            linear_rows(sg, w->sh_down_trellis, ysh, w->sh_down_suh, sr, w->sh_down_svh, T, SI, H, w->k_bits, w->codebook, 0, cs);
+        }
+        k_moe_combine<<<T, 256, 0, cs>>>(yr, inv, topk_w, ysh, (float*) out, H, K);
+        cuda_ok(cudaGetLastError(), "k_moe_combine launch");
+        st.launch = "k_moe_router_logits + k_moe_topk + k_moe_count/scan/scatter + k_moe_gather_rows + 3 x (" + st.launch +
+                    ") + k_silu_mul + k_moe_combine";
+    });
+}

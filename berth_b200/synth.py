@@ -61,11 +61,11 @@ def trellis(seed: int, name: str, size_k: int, size_n: int, bits: int) -> np.nda
     return np.ascontiguousarray(words).reshape(size_k // 16, size_n // 16, 16 * bits)
 
 
-def sign_scale(seed: int, name: str, n: int) -> np.ndarray:
-    """float16 [n]: random sign times N(1, 0.05)."""
+def sign_scale(seed: int, name: str, n: int, gain: float = 1.0) -> np.ndarray:
+    """float16 [n]: random sign times N(1, 0.05), times `gain`."""
     mag = 1.0 + 0.05 * normal(seed, name, n)
     sign = np.where(raw_u64(seed, name, n, 3) & np.uint64(1), -1.0, 1.0)
-    return (sign * mag).astype(np.float16)
+    return (sign * mag * gain).astype(np.float16)
 
 
 def activations(seed: int, name: str, rows: int, cols: int, outlier_frac: float = 0.0,
@@ -92,11 +92,15 @@ def zipf_router_bias(seed: int, name: str, n_experts: int, s: float = 1.1, stren
     return (strength * (-s) * np.log(rank.astype(np.float64))).astype(np.float32)
 
 
-def linear_weights(seed: int, name: str, size_k: int, size_n: int, bits: int) -> dict:
+def linear_weights(seed: int, name: str, size_k: int, size_n: int, bits: int, fan_in_gain: bool = False) -> dict:
+    """One EXL3 linear.  With fan_in_gain the output sign-scale carries 1/sqrt(size_k), the factor a
+    trained checkpoint's scales carry; chains of linears (MLP, experts) need it or their fp16
+    intermediates overflow with unit-variance codebook weights."""
+    gain = 1.0 / np.sqrt(size_k) if fan_in_gain else 1.0
     return {
         "trellis": trellis(seed, name + ".trellis", size_k, size_n, bits),
         "suh": sign_scale(seed, name + ".suh", size_k),
-        "svh": sign_scale(seed, name + ".svh", size_n),
+        "svh": sign_scale(seed, name + ".svh", size_n, gain),
         "size_k": size_k, "size_n": size_n, "bits": bits,
     }
 
@@ -104,7 +108,7 @@ def linear_weights(seed: int, name: str, size_k: int, size_n: int, bits: int) ->
 def _stack(seed, name, n, size_k, size_n, bits):
     t = np.stack([trellis(seed, f"{name}.{e}.trellis", size_k, size_n, bits) for e in range(n)])
     suh = np.stack([sign_scale(seed, f"{name}.{e}.suh", size_k) for e in range(n)])
-    svh = np.stack([sign_scale(seed, f"{name}.{e}.svh", size_n) for e in range(n)])
+    svh = np.stack([sign_scale(seed, f"{name}.{e}.svh", size_n, 1.0 / np.sqrt(size_k)) for e in range(n)])
     return t, suh, svh
 
 
@@ -113,7 +117,8 @@ def moe_layer_weights(seed: int, name: str, hidden: int, inter: int, n_experts: 
                       router_bias: np.ndarray | None = None) -> dict:
     """Weights of one A3B-style MoE layer.  Expert stacks: gate/up trellis
     (E, hidden/16, inter/16, 16*bits), down (E, inter/16, hidden/16, 16*bits); suh/svh stacks
-    [E][.]; optional shared expert with its own intermediate size."""
+    [E][.]; optional shared expert with its own intermediate size.  Every svh carries the
+    1/sqrt(fan_in) gain (see linear_weights), so activations keep unit scale through the layer."""
     w = {"hidden": hidden, "inter": inter, "n_experts": n_experts, "top_k": top_k, "bits": bits,
          "cb": cb, "shared_inter": shared_inter or 0,
          "w_router": router_weight(seed, name + ".gate.weight", hidden, n_experts),
@@ -124,6 +129,6 @@ def moe_layer_weights(seed: int, name: str, hidden: int, inter: int, n_experts: 
     if shared_inter:
         for p, (k, n) in (("gate", (hidden, shared_inter)), ("up", (hidden, shared_inter)),
                           ("down", (shared_inter, hidden))):
-            lw = linear_weights(seed, f"{name}.shared_expert.{p}_proj", k, n, bits)
+            lw = linear_weights(seed, f"{name}.shared_expert.{p}_proj", k, n, bits, fan_in_gain=True)
             w[f"sh_{p}_trellis"], w[f"sh_{p}_suh"], w[f"sh_{p}_svh"] = lw["trellis"], lw["suh"], lw["svh"]
     return w

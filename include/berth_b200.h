@@ -35,6 +35,7 @@
 #ifndef BERTH_B200_H
 #define BERTH_B200_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -125,6 +126,43 @@ int berth_ops_silu_mul(const void* gate, const void* up, void* out, int64_t nume
 int berth_ops_add_f32(const void* a, const void* b, void* c, int n, void* stream);
 const char* berth_ops_last_error(void);
 const char* berth_ops_last_launch(void);
+
+/* ------------------------------------------------------------------ MoE layer
+ * berth has the shape contract of the A3B mixture-of-experts block (crates/berth-plan/src/plan.rs:43-57,
+ * 204-219; crates/berth-plan/src/shape.rs:59-69) but no operator for it
+ * (crates/berth-engine/src/model.rs:404-411), so these entry points have no counterpart in
+ * berth's FFI; they follow the same conventions. */
+typedef struct berth_moe_weights {
+    int hidden, inter, shared_inter, n_experts, top_k, k_bits, codebook;
+    const void* w_router;        /* fp16 [hidden][n_experts] */
+    const float* router_bias;    /* fp32 [n_experts] or NULL */
+    /* expert stacks: trellis (E, K/16, N/16, 16*k_bits), suh [E][K], svh [E][N] */
+    const void *gate_trellis, *up_trellis, *down_trellis;
+    const void *gate_suh, *gate_svh, *up_suh, *up_svh, *down_suh, *down_svh;
+    /* shared expert (shared_inter > 0) */
+    const void *sh_gate_trellis, *sh_up_trellis, *sh_down_trellis;
+    const void *sh_gate_suh, *sh_gate_svh, *sh_up_suh, *sh_up_svh, *sh_down_suh, *sh_down_svh;
+} berth_moe_weights;
+
+/* Router: logits = x . w_router (+ bias) in fp32 with a fixed summation order (32 chunk sums of
+ * hidden/32 sequential fmaf, then an xor tree), top-k with ties to the lower expert index,
+ * weights = softmax over the selected logits.
+ * x fp16 [T][hidden]; topk_idx int32 [T][k]; topk_w fp32 [T][k]; logits fp32 [T][E] scratch/output. */
+int berth_moe_router_topk(const void* x, const void* w_router, const float* router_bias,
+                          int32_t* topk_idx, float* topk_w, float* logits, int T, int hidden,
+                          int n_experts, int top_k, void* stream);
+/* Bytes of caller-provided scratch berth_moe_layer needs for T tokens (the library allocates
+ * nothing per layer). */
+size_t berth_moe_workspace_bytes(int T, int hidden, int inter, int shared_inter, int n_experts,
+                                 int top_k);
+/* The whole layer on one GPU: router, dispatch, grouped gate/up/SiLU/down over the routed rows,
+ * shared expert, weighted combine.  x fp16 [T][hidden]; out fp32 [T][hidden]; topk_idx / topk_w
+ * receive the routing ([T][k]).  Expert outputs are rounded to fp16 and combined in fp32 in slot
+ * order, shared expert last. */
+int berth_moe_layer(const berth_moe_weights* w, const void* x, int T, void* out, int32_t* topk_idx,
+                    float* topk_w, void* workspace, size_t workspace_bytes, void* stream);
+const char* berth_moe_last_error(void);
+const char* berth_moe_last_launch(void);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,113 @@
+"""MoE layer parity: router top-k indices bit-exact against the CPU oracle (ties to the lower
+expert index), layer output within the fp32-accumulation tolerance of the fp64 evaluation."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from berth_b200 import kernels, moe, synth   # noqa: E402
+from tests.gpu_util import MAX_REL, MEAN_REL, dev, rel_errors   # noqa: E402
+
+
+def _route(x, wr, bias, k):
+    T, H = x.shape
+    E = wr.shape[1]
+    idx = torch.empty((T, k), dtype=torch.int32, device="cuda")
+    w = torch.empty((T, k), dtype=torch.float32, device="cuda")
+    logits = torch.empty((T, E), dtype=torch.float32, device="cuda")
+    b = None if bias is None else torch.from_numpy(bias).cuda()
+    moe.router_topk(dev(x), dev(wr), b, idx, w, logits, T, H, E, k)
+    torch.cuda.synchronize()
+    return idx.cpu().numpy(), w.cpu().numpy(), logits.cpu().numpy()
+
+
+@pytest.mark.parametrize("T", [1, 64, 1024])
+def test_router_topk_config3_bit_exact(oracle, T):
+    H, E, k = 2048, 256, 8
+    x = synth.activations(1234, f"c3.x{T}", T, H)
+    wr = synth.router_weight(1234, "c3.gate.weight", H, E)
+    idx, w, logits = _route(x, wr, None, k)
+    exp_logits = oracle.router_logits(x, wr)
+    assert (logits.view(np.uint32) == exp_logits.view(np.uint32)).all()      # fixed summation order
+    exp_idx, exp_w = oracle.router_topk(exp_logits, k)
+    assert (idx == exp_idx).all()
+    assert np.abs(w - exp_w).max() <= 1e-6
+    assert np.allclose(w.sum(axis=1), 1.0, atol=1e-5)
+
+
+def test_router_ties_and_bias(oracle):
+    H, E, k = 128, 64, 4
+    x = np.zeros((3, H), np.float16)           # all logits equal -> ties everywhere
+    wr = synth.router_weight(5, "tie.w", H, E)
+    idx, w, _ = _route(x, wr, None, k)
+    assert (idx == np.arange(k)[None, :]).all()
+    assert np.allclose(w, 1.0 / k)
+    bias = synth.zipf_router_bias(5, "tie.b", E)
+    x = synth.activations(5, "tie.x", 7, H)
+    idx, w, logits = _route(x, wr, bias, k)
+    exp_logits = oracle.router_logits(x, wr, bias)
+    assert (logits.view(np.uint32) == exp_logits.view(np.uint32)).all()
+    exp_idx, _ = oracle.router_topk(exp_logits, k)
+    assert (idx == exp_idx).all()
+
+
+def _run_layer(wts, x):
+    T = x.shape[0]
+    layer = moe.MoeLayer(torch.device("cuda"), wts, T)
+    out = torch.full((T, wts["hidden"]), float("nan"), dtype=torch.float32, device="cuda")
+    idx = torch.empty((T, wts["top_k"]), dtype=torch.int32, device="cuda")
+    w = torch.empty((T, wts["top_k"]), dtype=torch.float32, device="cuda")
+    layer.forward(dev(x), out, idx, w)
+    torch.cuda.synchronize()
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+    return out.cpu().numpy(), idx.cpu().numpy(), w.cpu().numpy()
+
+
+@pytest.mark.parametrize("T", [1, 5, 40, 130])
+@pytest.mark.parametrize("bits,cb,shared", [(4, 2, 128), (4, 0, 0), (3, 1, 256)])
+def test_moe_layer_small_vs_oracle(oracle, T, bits, cb, shared):
+    H, I, E, k = 256, 128, 32, 4
+    wts = synth.moe_layer_weights(1234, f"moe{bits}{cb}", H, I, E, k, bits, cb, shared_inter=shared)
+    x = synth.activations(1234, f"moe.x{T}", T, H)
+    out, idx, w = _run_layer(wts, x)
+    exp_out, exp_idx, exp_w = oracle.moe_layer(wts, x)
+    assert (idx == exp_idx).all()                       # routing: bit-exact
+    assert np.abs(w - exp_w).max() <= 1e-6
+    y64 = oracle.moe_layer_f64(wts, x, exp_idx, exp_w)
+    mx, mean = rel_errors(out, y64)
+    assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
+    rms = np.sqrt((y64 ** 2).mean())
+    assert np.abs(out - exp_out).max() <= 4e-3 * rms
+
+
+@pytest.mark.parametrize("T", [1, 64])
+def test_moe_layer_config3_vs_oracle(oracle, T):
+    """BASELINE configuration 3: hidden 2048, 256 experts + shared, top-8, intermediate 512, 4 bpw."""
+    H, I, E, k, bits, cb = 2048, 512, 256, 8, 4, 2
+    wts = synth.moe_layer_weights(1234, "c3", H, I, E, k, bits, cb, shared_inter=512)
+    x = synth.activations(1234, f"c3.x{T}", T, H)
+    out, idx, w = _run_layer(wts, x)
+    exp_out, exp_idx, exp_w = oracle.moe_layer(wts, x)
+    assert (idx == exp_idx).all()
+    y64 = oracle.moe_layer_f64(wts, x, exp_idx, exp_w)
+    mx, mean = rel_errors(out, y64)
+    assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
+
+
+def test_moe_layer_skewed_routing_property():
+    """Zipf-biased router at 1024 tokens: every token's output equals the same token run alone
+    (the layer is row-wise), which checks dispatch / permutation / combine at full size without
+    the CPU checker."""
+    H, I, E, k, bits, cb = 2048, 512, 256, 8, 4, 2
+    bias = synth.zipf_router_bias(1234, "c4.bias", E, s=1.1, strength=0.25)
+    wts = synth.moe_layer_weights(1234, "c3", H, I, E, k, bits, cb, shared_inter=512, router_bias=bias)
+    x = synth.activations(1234, "c4.x", 1024, H)
+    out, idx, w = _run_layer(wts, x)
+    counts = np.bincount(idx.ravel(), minlength=E)
+    assert counts.sum() == 1024 * k and counts.max() > 2 * counts.mean()      # visibly skewed
+    rms = np.sqrt((out.astype(np.float64) ** 2).mean())
+    for t in (0, 17, 500, 1023):
+        o1, i1, w1 = _run_layer(wts, x[t:t + 1])
+        assert (i1[0] == idx[t]).all()
+        assert np.abs(o1[0] - out[t]).max() <= 4e-3 * rms
