@@ -46,6 +46,11 @@ SIGNATURES = {
     "berth_moe_router_topk": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
     "berth_moe_workspace_bytes": (C.c_size_t, [_i] * 6),
     "berth_moe_layer": (_i, [C.POINTER(MoeWeights), _vp, _i, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
+    "berth_moe_experts_workspace_bytes": (C.c_size_t, [_i] * 5),
+    "berth_moe_sort_rows": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, C.c_size_t, _i, _i, _i, _i, _vp]),
+    "berth_moe_gather": (_i, [_vp, _vp, _i, _i, _vp, _i, _vp]),
+    "berth_moe_experts": (_i, [C.POINTER(MoeWeights), _vp, _vp, _i, _vp, C.c_size_t, _i, _i, _vp]),
+    "berth_moe_combine": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "berth_moe_last_error": (C.c_char_p, []),
     "berth_moe_last_launch": (C.c_char_p, []),
     "berth_ops_last_error": (C.c_char_p, []),

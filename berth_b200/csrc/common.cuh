@@ -92,12 +92,13 @@ struct GemvProblem {
 // Grouped decode launch over a stack of equally shaped matrices (the experts of an MoE layer):
 // `problems` / `n_problems` live on the device (built by the dispatch kernels), xr fp16 [R][k] are
 // the routed rows, c the outputs [R][n]; suh_stack [experts][k], svh_stack [experts][n].
-// afrag / blocksum scratch must hold max_problems * (k/16) * tg * 256 bytes and
+// Table entries are clamped on the device to max_problems, n_experts and max_rows (the number of
+// rows of xr / c).  afrag / blocksum scratch must hold max_problems * (k/16) * tg * 256 bytes and
 // max_problems * 8 * tg * (k/128) floats.
 std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n_experts, void* c, const void* suh_stack,
                                 const void* svh_stack, const GemvProblem* problems, const int* n_problems, int max_problems,
-                                int tg, uint32_t* afrag, float* blocksum, int size_k, int size_n, int k_bits, int codebook,
-                                int out_fp32, const GemvScratch& scratch, int sms, cudaStream_t stream);
+                                int max_rows, int tg, uint32_t* afrag, float* blocksum, int size_k, int size_n, int k_bits,
+                                int codebook, int out_fp32, const GemvScratch& scratch, int sms, cudaStream_t stream);
 
 std::string launch_gemv(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32,

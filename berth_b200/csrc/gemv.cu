@@ -90,11 +90,23 @@ struct GemvArgs {
     const __half* svh;        // [n], or the stack [experts][n] when grouped
     const GemvProblem* problems;   // grouped launch: one entry per (expert, chunk of <= 8*TG rows); else null
     const int* n_problems;         // grouped launch: device-side count
+    int max_problems, n_matrices, max_rows;   // bounds the table entries are clamped to
     float* slabs;             // [2*G][m][BU*128]
     unsigned* counters;       // [band groups][kEpiWarps], zero between launches
     unsigned* status;
     int m, k, n, out_fp32;
 };
+
+// A problem-table entry with every field forced into range, so that a table the caller forgot to
+// build (or built for another shape) yields wrong numbers, never a wild address.
+__device__ __forceinline__ GemvProblem load_problem(const GemvProblem* table, int i, int n_matrices, int tok, int max_rows)
+{
+    GemvProblem pr = table[i];
+    pr.z = min(max(pr.z, 0), n_matrices - 1);
+    pr.rows = min(max(pr.rows, 0), tok);
+    pr.row0 = min(max(pr.row0, 0), max(max_rows - pr.rows, 0));
+    return pr;
+}
 
 // ---------------------------------------------------------------- mbarrier / TMA PTX
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
@@ -302,7 +314,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
     const int bands = p.n >> 7, kblocks = p.k >> 7;
     const int bgroups = (bands + BU - 1) / BU;          // band groups of one problem
     const bool grouped = p.problems != nullptr;
-    const int nprob = grouped ? __ldg(p.n_problems) : 1;
+    const int nprob = grouped ? min(max(__ldg(p.n_problems), 0), p.max_problems) : 1;
     const long long U = (long long) nprob * bgroups * kblocks;
     const int cta = blockIdx.x;
     const int G = U < (long long) gridDim.x ? int(U) : int(gridDim.x);   // CTAs that own units
@@ -334,7 +346,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
                 const long long u = u0 + i;
                 const int gbg = int(u / kblocks), kb = int(u - (long long) gbg * kblocks);
                 const int pi = gbg / bgroups, lbg = gbg - pi * bgroups;
-                const int z = grouped ? p.problems[pi].z : 0;
+                const int z = grouped ? load_problem(p.problems, pi, p.n_matrices, TOK, p.max_rows).z : 0;
                 tma_load_3d(dst, &tmap, lbg * (ROW_BYTES / 8), kb * 8, z, bar);
             };
             auto issue_acts = [&](int i, uint32_t dst, uint32_t bar) {
@@ -439,7 +451,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
             const int pi = sg.bg / bgroups, lbg = sg.bg - pi * bgroups;
             int rows = p.m, row0 = 0, z = 0;
             if (grouped) {
-                const GemvProblem pr = p.problems[pi];
+                const GemvProblem pr = load_problem(p.problems, pi, p.n_matrices, TOK, p.max_rows);
                 rows = pr.rows; row0 = pr.row0; z = pr.z;
             }
             const __half* svh = p.svh + size_t(z) * p.n;
@@ -701,17 +713,18 @@ size_t launch_bits(int k_bits, int cb, int tg, const void* t, int nm, const Gemv
 // the row's expert picks the sign-scale vector.  Rows past a problem's count are written as zeros.
 __global__ void __launch_bounds__(128) k_rotate_rows(const __half* __restrict__ xr, const __half* __restrict__ suh_stack,
                                                      const GemvProblem* __restrict__ problems, const int* __restrict__ n_problems,
-                                                     uint32_t* __restrict__ afrag, float* __restrict__ blocksum, int tok, int k)
+                                                     uint32_t* __restrict__ afrag, float* __restrict__ blocksum, int tok, int k,
+                                                     int max_problems, int n_matrices, int max_rows)
 {
     grid_dependency_wait();      // the problem table comes from the preceding kernel
     grid_launch_dependents();
     const int lane = threadIdx.x & 31, kblocks = k >> 7, tgs = tok >> 3;
-    const long long total = (long long) __ldg(n_problems) * tok * kblocks;
+    const long long total = (long long) min(max(__ldg(n_problems), 0), max_problems) * tok * kblocks;
     for (long long idx = (long long) blockIdx.x * 4 + (threadIdx.x >> 5); idx < total; idx += (long long) gridDim.x * 4) {
         const int b = int(idx % kblocks);
         const int lr = int((idx / kblocks) % tok);
         const int pi = int(idx / ((long long) kblocks * tok));
-        const GemvProblem pr = problems[pi];
+        const GemvProblem pr = load_problem(problems, pi, n_matrices, tok, max_rows);
         const int kcol = b * 128 + lane * 4;
         uint2 o = make_uint2(0u, 0u);
         if (lr < pr.rows) {
@@ -789,6 +802,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     args.out_fp32 = out_fp32;
     args.problems = nullptr;
     args.n_problems = nullptr;
+    args.max_problems = 1; args.n_matrices = 1; args.max_rows = size_m;
     const size_t smem = launch_bits(k_bits, codebook, tg, trellis, 1, args, grid, stream);
     return "k_rotate_in + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," + std::to_string(tg) +
            "> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem);
@@ -796,8 +810,8 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
 
 std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n_experts, void* c, const void* suh_stack,
                                 const void* svh_stack, const GemvProblem* problems, const int* n_problems, int max_problems,
-                                int tg, uint32_t* afrag, float* blocksum, int size_k, int size_n, int k_bits, int codebook,
-                                int out_fp32, const GemvScratch& sc, int sms, cudaStream_t stream)
+                                int max_rows, int tg, uint32_t* afrag, float* blocksum, int size_k, int size_n, int k_bits,
+                                int codebook, int out_fp32, const GemvScratch& sc, int sms, cudaStream_t stream)
 {
     if (size_k % 128 != 0 || size_n % 128 != 0)
         throw std::runtime_error("exl3 grouped gemv: size_k and size_n must be multiples of 128");
@@ -812,7 +826,7 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
     if (grid < 1) throw std::runtime_error("exl3 grouped gemv: split-K scratch is too small");
     const long long warps = (long long) max_problems * 8 * tg * (size_k / 128);
     k_rotate_rows<<<int(std::min<long long>((warps + 3) / 4, 8LL * sms)), 128, 0, stream>>>(
-        static_cast<const __half*>(xr), static_cast<const __half*>(suh_stack), problems, n_problems, afrag, blocksum, 8 * tg, size_k);
+        static_cast<const __half*>(xr), static_cast<const __half*>(suh_stack), problems, n_problems, afrag, blocksum, 8 * tg, size_k, max_problems, n_experts, max_rows);
     cuda_ok(cudaGetLastError(), "k_rotate_rows launch");
     GemvArgs args;
     args.afrag = afrag;
@@ -821,6 +835,9 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
     args.svh = static_cast<const __half*>(svh_stack);
     args.problems = problems;
     args.n_problems = n_problems;
+    args.max_problems = max_problems;
+    args.n_matrices = n_experts;
+    args.max_rows = max_rows;
     args.slabs = sc.slabs;
     args.counters = sc.counters;
     args.status = sc.status;

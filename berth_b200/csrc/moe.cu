@@ -17,22 +17,45 @@ std::string linear_rows(const void* a, const void* trellis, void* c, const void*
 namespace {
 
 // ---------------------------------------------------------------- router
-// logits[t][e] = sum over 32 chunks of H/32 sequential fmaf, chunks combined by an xor tree: the
-// summation order of the CPU checker, so the top-k indices can be compared bit for bit.
-// Block = 32 experts x 32 chunks; a warp holds the 32 chunks of one expert.
+// logits[t][e] = sum over 32 chunks of H/32 sequential fmaf, chunks combined by a halving tree
+// ((p0+p16)+(p8+p24))+...: the summation order of the CPU checker, so the top-k indices can be
+// compared bit for bit.  Block = 32 chunk-warps x 32 experts for kRouterTok tokens: warp j
+// accumulates chunk j with coalesced reads of the router rows (each row read once per token tile).
+constexpr int kRouterTok = 8;
 __global__ void __launch_bounds__(1024) k_moe_router_logits(const __half* __restrict__ x, const __half* __restrict__ w,
                                                             const float* __restrict__ bias, float* __restrict__ logits,
-                                                            int H, int E)
+                                                            int T, int H, int E)
 {
-    const int t = blockIdx.y, e = blockIdx.x * 32 + (threadIdx.x >> 5), j = threadIdx.x & 31;
+    __shared__ float part[32][kRouterTok][33];
+    const int j = threadIdx.x >> 5, el = threadIdx.x & 31;
+    const int e = blockIdx.x * 32 + el, t0 = blockIdx.y * kRouterTok;
     const int chunk = H / 32;
-    const __half* xr = x + size_t(t) * H + j * chunk;
     const __half* wr = w + size_t(j) * chunk * E + e;
-    float acc = 0.f;
-    for (int i = 0; i < chunk; ++i) acc = __fmaf_rn(__half2float(xr[i]), __half2float(wr[size_t(i) * E]), acc);
+    float acc[kRouterTok];
 #pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(dq::kFull, acc, off));
-    if (j == 0) logits[size_t(t) * E + e] = __fadd_rn(acc, bias ? bias[e] : 0.f);
+    for (int tt = 0; tt < kRouterTok; ++tt) acc[tt] = 0.f;
+    for (int i = 0; i < chunk; ++i) {
+        const float wv = __half2float(wr[size_t(i) * E]);
+#pragma unroll
+        for (int tt = 0; tt < kRouterTok; ++tt) {
+            const int t = min(t0 + tt, T - 1);
+            acc[tt] = __fmaf_rn(__half2float(x[size_t(t) * H + j * chunk + i]), wv, acc[tt]);
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < kRouterTok; ++tt) part[j][tt][el] = acc[tt];
+    __syncthreads();
+    // warp tt reduces token tt: lane = expert; the same halving tree as a 32-lane xor butterfly's lane 0
+    if (j < kRouterTok && t0 + j < T) {
+        float p[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) p[c] = part[c][j][el];
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1)
+#pragma unroll
+            for (int c = 0; c < off; ++c) p[c] = __fadd_rn(p[c], p[c + off]);
+        logits[size_t(t0 + j) * E + e] = __fadd_rn(p[0], bias ? bias[e] : 0.f);
+    }
 }
 
 // One warp per token: k rounds of arg-max, value descending then index ascending.
@@ -94,24 +117,44 @@ __global__ void __launch_bounds__(256) k_moe_count(const int32_t* __restrict__ k
 }
 
 // offsets[0..n_local] = exclusive scan of counts; problem table: every expert's rows in chunks of
-// `chunk` rows.  One thread: n_local is a few hundred.
-__global__ void k_moe_scan(const int* __restrict__ counts, int* __restrict__ offsets, GemvProblem* __restrict__ problems,
-                           int* __restrict__ n_problems, int n_local, int chunk)
+// `chunk` rows, experts in ascending order.  One block of 1024 threads, one expert per thread.
+__global__ void __launch_bounds__(1024) k_moe_scan(const int* __restrict__ counts, int* __restrict__ offsets,
+                                                   GemvProblem* __restrict__ problems, int* __restrict__ n_problems,
+                                                   int n_local, int chunk)
 {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
-    int off = 0, np = 0;
-    for (int j = 0; j < n_local; ++j) {
-        offsets[j] = off;
-        const int c = counts[j];
-        for (int r0 = 0; r0 < c; r0 += chunk) {
-            GemvProblem pr;
-            pr.z = j; pr.row0 = off + r0; pr.rows = min(chunk, c - r0); pr.pad = 0;
-            problems[np++] = pr;
-        }
-        off += c;
+    __shared__ int wrows[32], wprob[32];
+    const int j = threadIdx.x, lane = j & 31, warp = j >> 5;
+    const int c = j < n_local ? counts[j] : 0;
+    const int np = (c + chunk - 1) / chunk;
+    int prow = c, pprob = np;     // inclusive warp scans
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int a = __shfl_up_sync(dq::kFull, prow, off), b = __shfl_up_sync(dq::kFull, pprob, off);
+        if (lane >= off) { prow += a; pprob += b; }
     }
-    offsets[n_local] = off;
-    *n_problems = np;
+    if (lane == 31) { wrows[warp] = prow; wprob[warp] = pprob; }
+    __syncthreads();
+    if (warp == 0) {
+        int a = wrows[lane], b = wprob[lane];
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int ua = __shfl_up_sync(dq::kFull, a, off), ub = __shfl_up_sync(dq::kFull, b, off);
+            if (lane >= off) { a += ua; b += ub; }
+        }
+        wrows[lane] = a; wprob[lane] = b;
+    }
+    __syncthreads();
+    const int row0 = prow - c + (warp ? wrows[warp - 1] : 0);
+    const int p0 = pprob - np + (warp ? wprob[warp - 1] : 0);
+    if (j < n_local) {
+        offsets[j] = row0;
+        for (int i = 0; i < np; ++i) {
+            GemvProblem pr;
+            pr.z = j; pr.row0 = row0 + i * chunk; pr.rows = min(chunk, c - i * chunk); pr.pad = 0;
+            problems[p0 + i] = pr;
+        }
+    }
+    if (j == 0) { offsets[n_local] = wrows[31]; *n_problems = wprob[31]; }
 }
 
 // Stable permutation: block j walks the entries in order; the r-th entry with key e0 + j goes to
@@ -155,6 +198,17 @@ __global__ void __launch_bounds__(256) k_moe_gather_rows(const __half* __restric
         const uint4* src = reinterpret_cast<const uint4*>(x + size_t(perm[pos] / div) * H);
         uint4* dst = reinterpret_cast<uint4*>(xr + size_t(pos) * H);
         for (int i = threadIdx.x; i < H / 8; i += 256) dst[i] = src[i];
+    }
+}
+
+// Same with the row count known on the host.
+__global__ void __launch_bounds__(256) k_moe_gather_n(const __half* __restrict__ x, const int32_t* __restrict__ index, int n,
+                                                      int div, __half* __restrict__ dst, int H)
+{
+    for (int pos = blockIdx.x; pos < n; pos += gridDim.x) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + size_t(index[pos] / div) * H);
+        uint4* d = reinterpret_cast<uint4*>(dst + size_t(pos) * H);
+        for (int i = threadIdx.x; i < H / 8; i += 256) d[i] = src[i];
     }
 }
 
@@ -232,7 +286,8 @@ void check_moe_shapes(const berth_moe_weights* w, int T)
 void router_topk(const void* x, const void* w_router, const float* bias, int32_t* topk_idx, float* topk_w, float* logits,
                  int T, int H, int E, int k, cudaStream_t st)
 {
-    k_moe_router_logits<<<dim3(E / 32, T), 1024, 0, st>>>((const __half*) x, (const __half*) w_router, bias, logits, H, E);
+    k_moe_router_logits<<<dim3(E / 32, (T + kRouterTok - 1) / kRouterTok), 1024, 0, st>>>((const __half*) x, (const __half*) w_router,
+                                                                                        bias, logits, T, H, E);
     cuda_ok(cudaGetLastError(), "k_moe_router_logits launch");
     k_moe_topk<<<(T + 3) / 4, 128, 0, st>>>(logits, topk_idx, topk_w, T, E, k);
     cuda_ok(cudaGetLastError(), "k_moe_topk launch");
@@ -244,7 +299,7 @@ void dispatch(const int32_t* keys, int n, int e0, int n_local, int chunk, const 
 {
     k_moe_count<<<n_local, 256, 0, st>>>(keys, n, e0, s.counts);
     cuda_ok(cudaGetLastError(), "k_moe_count launch");
-    k_moe_scan<<<1, 32, 0, st>>>(s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk);
+    k_moe_scan<<<1, 1024, 0, st>>>(s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk);
     cuda_ok(cudaGetLastError(), "k_moe_scan launch");
     k_moe_scatter<<<n_local, 256, 0, st>>>(keys, n, e0, s.offsets, perm, inv);
     cuda_ok(cudaGetLastError(), "k_moe_scatter launch");
@@ -253,15 +308,15 @@ void dispatch(const int32_t* keys, int n, int e0, int n_local, int chunk, const 
 // Grouped gate/up -> silu*up -> down over routed rows xr [R][hidden]; yr fp16 [R][hidden].
 std::string experts(const berth_moe_weights* w, const void* gate_t, const void* up_t, const void* down_t, const void* gsuh,
                     const void* gsvh, const void* usuh, const void* usvh, const void* dsuh, const void* dsvh, int n_local,
-                    const void* xr, void* yr, int R, int tg, const ExpertScratch& s, const GemvScratch& sc, int sms, cudaStream_t st)
+                    const void* xr, void* yr, int R, int max_rows, int tg, const ExpertScratch& s, const GemvScratch& sc, int sms, cudaStream_t st)
 {
     const int H = w->hidden, I = w->inter;
-    std::string d = launch_gemv_grouped(xr, gate_t, n_local, s.g, gsuh, gsvh, s.problems, s.n_problems, s.max_problems, tg, s.afrag,
+    std::string d = launch_gemv_grouped(xr, gate_t, n_local, s.g, gsuh, gsvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag,
                                         s.blocksum, H, I, w->k_bits, w->codebook, 0, sc, sms, st);
-    launch_gemv_grouped(xr, up_t, n_local, s.u, usuh, usvh, s.problems, s.n_problems, s.max_problems, tg, s.afrag, s.blocksum, H, I,
+    launch_gemv_grouped(xr, up_t, n_local, s.u, usuh, usvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag, s.blocksum, H, I,
                         w->k_bits, w->codebook, 0, sc, sms, st);
     if (berth_ops_silu_mul(s.g, s.u, s.g, int64_t(R) * I, 0.0f, st) != 0) throw std::runtime_error(berth_ops_last_error());
-    launch_gemv_grouped(s.g, down_t, n_local, yr, dsuh, dsvh, s.problems, s.n_problems, s.max_problems, tg, s.afrag, s.blocksum, I, H,
+    launch_gemv_grouped(s.g, down_t, n_local, yr, dsuh, dsvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag, s.blocksum, I, H,
                         w->k_bits, w->codebook, 0, sc, sms, st);
     return d;
 }
@@ -286,7 +341,92 @@ extern "C" int berth_moe_router_topk(const void* x, const void* w_router, const 
             throw std::runtime_error("moe router: n_experts must be a multiple of 32 up to 1024");
         if (top_k < 1 || top_k > 32 || top_k > n_experts) throw std::runtime_error("moe router: top_k must be in 1..=32");
         router_topk(x, w_router, router_bias, topk_idx, topk_w, logits, T, hidden, n_experts, top_k, (cudaStream_t) stream);
-        st.launch = "k_moe_router_logits grid=" + std::to_string(n_experts / 32) + "x" + std::to_string(T) + " + k_moe_topk";
+        st.launch = "k_moe_router_logits grid=" + std::to_string(n_experts / 32) + "x" + std::to_string((T + kRouterTok - 1) / kRouterTok) + " + k_moe_topk";
+    });
+}
+
+// ---- the stages of the layer, exported one by one for hosts that put a collective between them
+// (expert parallelism: sort -> gather -> all-to-all -> sort -> gather -> experts -> gather ->
+// all-to-all -> combine).  `ews` is the expert-stage scratch of berth_moe_experts_workspace_bytes.
+
+extern "C" size_t berth_moe_experts_workspace_bytes(int max_rows, int n_local, int hidden, int inter, int max_rows_per_expert)
+{
+    if (max_rows < 1 || n_local < 1 || hidden < 128 || inter < 128) return 0;
+    return carve_experts(nullptr, max_rows, n_local, hidden, inter, token_groups(max_rows_per_expert)).bytes + 256;
+}
+
+static ExpertScratch expert_scratch(void* ews, size_t ews_bytes, int max_rows, int n_local, int hidden, int inter, int mrpe)
+{
+    if (!ews) throw std::runtime_error("moe: null expert workspace");
+    const size_t need = berth_moe_experts_workspace_bytes(max_rows, n_local, hidden, inter, mrpe);
+    if (ews_bytes < need)
+        throw std::runtime_error("moe: expert workspace of " + std::to_string(ews_bytes) + " bytes is smaller than the " +
+                                 std::to_string(need) + " required");
+    void* b = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(ews) + 255) & ~uintptr_t(255));
+    return carve_experts(b, max_rows, n_local, hidden, inter, token_groups(mrpe));
+}
+
+extern "C" int berth_moe_sort_rows(const int32_t* keys, int n, int e0, int n_local, int32_t* perm, int32_t* inv,
+                                   int32_t* offsets_out, void* ews, size_t ews_bytes, int max_rows, int hidden, int inter,
+                                   int max_rows_per_expert, void* stream)
+{
+    CallState& st = moe_state();
+    return guarded(st, [&] {
+        if (!keys || !perm || !inv) throw std::runtime_error("moe sort: null device pointer");
+        if (n < 0 || n > max_rows) throw std::runtime_error("moe sort: n must be within 0..max_rows");
+        if (n_local < 1 || n_local > 1024) throw std::runtime_error("moe sort: n_local must be in 1..=1024");
+        ExpertScratch es = expert_scratch(ews, ews_bytes, max_rows, n_local, hidden, inter, max_rows_per_expert);
+        dispatch(keys, n, e0, n_local, 8 * token_groups(max_rows_per_expert), es, perm, inv, (cudaStream_t) stream);
+        if (offsets_out)
+            cuda_ok(cudaMemcpyAsync(offsets_out, es.offsets, size_t(n_local + 1) * 4, cudaMemcpyDeviceToDevice, (cudaStream_t) stream),
+                    "moe sort offsets copy");
+        st.launch = "k_moe_count + k_moe_scan + k_moe_scatter grid=" + std::to_string(n_local);
+    });
+}
+
+// dst[i][:] = src[index[i] / div][:] for i < n (fp16 rows of `hidden` elements).
+extern "C" int berth_moe_gather(const void* src, const int32_t* index, int div, int n, void* dst, int hidden, void* stream)
+{
+    CallState& st = moe_state();
+    return guarded(st, [&] {
+        if (!src || !index || !dst) throw std::runtime_error("moe gather: null device pointer");
+        if (n < 0 || div < 1 || hidden < 8 || hidden % 8) throw std::runtime_error("moe gather: bad sizes");
+        if (n == 0) return;
+        k_moe_gather_n<<<std::min(n, 148 * 8), 256, 0, (cudaStream_t) stream>>>((const __half*) src, index, n, div, (__half*) dst, hidden);
+        cuda_ok(cudaGetLastError(), "k_moe_gather launch");
+        st.launch = "k_moe_gather_n";
+    });
+}
+
+extern "C" int berth_moe_experts(const berth_moe_weights* w, const void* xr, void* yr, int n_rows, void* ews, size_t ews_bytes,
+                                 int max_rows, int max_rows_per_expert, void* stream)
+{
+    CallState& st = moe_state();
+    return guarded(st, [&] {
+        check_moe_shapes(w, 1);
+        if (!xr || !yr) throw std::runtime_error("moe experts: null device pointer");
+        if (n_rows < 0 || n_rows > max_rows) throw std::runtime_error("moe experts: n_rows must be within 0..max_rows");
+        const int device = current_device();
+        const DeviceInfo& info = device_info(device);
+        if (info.major != 10) throw std::runtime_error("moe experts: no linked kernel for this GPU (library is built for sm_100a only)");
+        ExpertScratch es = expert_scratch(ews, ews_bytes, max_rows, w->n_experts, w->hidden, w->inter, max_rows_per_expert);
+        if (n_rows == 0) return;
+        st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
+                            w->down_suh, w->down_svh, w->n_experts, xr, yr, n_rows, n_rows, token_groups(max_rows_per_expert), es,
+                            gemv_workspace(device), info.sms, (cudaStream_t) stream);
+    });
+}
+
+extern "C" int berth_moe_combine(const void* y, const int32_t* inv, const float* topk_w, const void* ysh, void* out, int T,
+                                 int hidden, int top_k, void* stream)
+{
+    CallState& st = moe_state();
+    return guarded(st, [&] {
+        if (!y || !inv || !topk_w || !out) throw std::runtime_error("moe combine: null device pointer");
+        if (T < 1 || hidden < 2 || hidden % 2 || top_k < 1) throw std::runtime_error("moe combine: bad sizes");
+        k_moe_combine<<<T, 256, 0, (cudaStream_t) stream>>>((const __half*) y, inv, topk_w, (const __half*) ysh, (float*) out, hidden, top_k);
+        cuda_ok(cudaGetLastError(), "k_moe_combine launch");
+        st.launch = "k_moe_combine grid=" + std::to_string(T);
     });
 }
 
@@ -346,7 +486,7 @@ extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T,
         k_moe_gather_rows<<<std::min(R, 148 * 8), 256, 0, cs>>>((const __half*) x, perm, es.offsets + E, K, xr, H);
         cuda_ok(cudaGetLastError(), "k_moe_gather_rows launch");
         st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
-                            w->down_suh, w->down_svh, E, xr, yr, R, tg, es, sc, info.sms, cs);
+                            w->down_suh, w->down_svh, E, xr, yr, R, R, tg, es, sc, info.sms, cs);
 
         __half* ysh = nullptr;
         if (SI > 0) {

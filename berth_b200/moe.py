@@ -81,3 +81,160 @@ class MoeLayer:
                                         None if stream is None else stream.cuda_stream)
         if rc != 0:
             raise Error(last_error() or f"moe layer launch failed ({rc})")
+
+
+# ---------------------------------------------------------------------------------------------
+# Expert parallelism.  berth runs on one GPU (crates/berth-cuda/src/context.rs:46-49); sharding the
+# experts of the MoE layer over the GPUs of one NVSwitch box is new here.  Tokens stay
+# data-parallel (each rank routes its own tokens), experts are split in contiguous blocks,
+# and the only exchange steps are two all-to-alls: routed rows out, expert outputs back.
+
+class GpuStages:
+    """The compute stages of the layer on one GPU, through the C ABI.  ``weights`` holds this
+    rank's expert stacks (``n_experts`` = number of LOCAL experts), the full router and the shared
+    expert."""
+
+    def __init__(self, device: torch.device, weights: dict, n_experts_total: int, max_rows: int, max_rows_per_expert: int):
+        self.device = device
+        self.layer = MoeLayer.__new__(MoeLayer)
+        MoeLayer.__init__(self.layer, device, weights, 1)
+        self.d = self.layer.dims
+        self.E = n_experts_total
+        self.max_rows, self.mrpe = max_rows, max_rows_per_expert
+        l = _lib.lib()
+        # one scratch for the send-side sort over all experts, one for the local experts
+        self.ews_all = torch.empty(l.berth_moe_experts_workspace_bytes(max_rows, self.E, self.d["hidden"], self.d["inter"], max_rows_per_expert),
+                                   dtype=torch.uint8, device=device)
+        self.ews_loc = torch.empty(l.berth_moe_experts_workspace_bytes(max_rows, self.d["n_experts"], self.d["hidden"], self.d["inter"],
+                                                                       max_rows_per_expert), dtype=torch.uint8, device=device)
+        from .engine import Exl3Linear, Gpu
+        self.shared = None
+        if self.d["shared_inter"]:
+            from .kernels import Codebook
+            g = Gpu(device.index if device.index is not None else torch.cuda.current_device())
+            k = self.layer._keep
+            mk = lambda p: Exl3Linear(g, f"shared_expert.{p}_proj", k[f"sh_{p}_trellis"], k[f"sh_{p}_suh"], k[f"sh_{p}_svh"],
+                                      self.d["bits"], Codebook(self.d["cb"]))
+            self.shared = (g, mk("gate"), mk("up"), mk("down"))
+
+    def _check(self, rc):
+        if rc != 0:
+            raise Error(last_error() or f"moe stage failed ({rc})")
+
+    def route(self, x):
+        T, H = x.shape
+        k = self.d["top_k"]
+        idx = torch.empty((T, k), dtype=torch.int32, device=self.device)
+        w = torch.empty((T, k), dtype=torch.float32, device=self.device)
+        logits = torch.empty((T, self.E), dtype=torch.float32, device=self.device)
+        router_topk(x, self.layer._keep["w_router"], self.layer._keep.get("router_bias"), idx, w, logits, T, H, self.E, k)
+        return idx, w
+
+    def sort(self, keys, e0: int, n_local: int, for_experts: bool = False):
+        """Stable sort by expert.  for_experts=True also leaves the problem table of the following
+        experts() call in the local-expert scratch (n_local must then be this rank's expert count)."""
+        n = keys.numel()
+        perm = torch.empty(max(n, 1), dtype=torch.int32, device=self.device)
+        inv = torch.empty(max(n, 1), dtype=torch.int32, device=self.device)
+        offsets = torch.empty(n_local + 1, dtype=torch.int32, device=self.device)
+        ews = self.ews_loc if for_experts else self.ews_all
+        self._check(_lib.lib().berth_moe_sort_rows(keys.data_ptr(), n, e0, n_local, perm.data_ptr(), inv.data_ptr(), offsets.data_ptr(),
+                                                   ews.data_ptr(), ews.numel(), self.max_rows, self.d["hidden"], self.d["inter"],
+                                                   self.mrpe, None))
+        return perm[:n], inv[:n], offsets
+
+    def gather(self, src, index, div: int):
+        n, H = index.numel(), src.shape[1]
+        dst = torch.empty((n, H), dtype=torch.float16, device=self.device)
+        if n:
+            self._check(_lib.lib().berth_moe_gather(src.data_ptr(), index.data_ptr(), div, n, dst.data_ptr(), H, None))
+        return dst
+
+    def experts(self, xr):
+        R = xr.shape[0]
+        yr = torch.empty_like(xr)
+        self._check(_lib.lib().berth_moe_experts(C.byref(self.layer.c), xr.data_ptr(), yr.data_ptr(), R, self.ews_loc.data_ptr(),
+                                                 self.ews_loc.numel(), self.max_rows, self.mrpe, None))
+        return yr
+
+    def shared_expert(self, x):
+        if self.shared is None:
+            return None
+        from .kernels import OutDtype, ops
+        g, gate, up, down = self.shared
+        T = x.shape[0]
+        si, H = self.d["shared_inter"], self.d["hidden"]
+        a = torch.empty((T, si), dtype=torch.float16, device=self.device)
+        b = torch.empty((T, si), dtype=torch.float16, device=self.device)
+        y = torch.empty((T, H), dtype=torch.float16, device=self.device)
+        fwd = (lambda lin, i, o: lin.forward_n(g, T, i, o, OutDtype.F16)) if T <= 32 else None
+        if fwd is None:
+            from .engine import RowScratch
+            sc = RowScratch(g, T, max(H, si), max(H, si))
+            fwd = lambda lin, i, o: lin.forward_rows(g, T, i, o, OutDtype.F16, sc)
+        fwd(gate, x, a)
+        fwd(up, x, b)
+        ops.silu_mul(a, b, a, T * si, 0.0)
+        fwd(down, a, y)
+        return y
+
+    def combine(self, y, inv, w, ysh):
+        T, k = w.shape
+        H = y.shape[1]
+        out = torch.empty((T, H), dtype=torch.float32, device=self.device)
+        self._check(_lib.lib().berth_moe_combine(y.data_ptr(), inv.data_ptr(), w.data_ptr(), None if ysh is None else ysh.data_ptr(),
+                                                 out.data_ptr(), T, H, k, None))
+        return out
+
+
+class EpMoeLayer:
+    """Expert-parallel MoE layer over a ``torch.distributed`` group (NCCL on GPUs, gloo in the CPU
+    tests).  ``stages`` provides route / sort / gather / experts / shared_expert / combine on this
+    rank's device; this class owns only the exchange logic:
+
+        route local tokens -> sort (token, slot) pairs by expert (= by destination rank, experts
+        are split in contiguous blocks) -> all-to-all rows + expert ids -> regroup by local expert
+        -> experts -> undo the regrouping -> all-to-all back -> weighted combine + shared expert.
+    """
+
+    def __init__(self, stages, group, n_experts: int, top_k: int):
+        import torch.distributed as dist
+        self.dist, self.group, self.stages = dist, group, stages
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if n_experts % self.world:
+            raise Error(f"{n_experts} experts do not split evenly over {self.world} ranks")
+        self.E, self.k = n_experts, top_k
+        self.n_local = n_experts // self.world
+        self.e0 = self.rank * self.n_local
+        self.last_stats = {}
+
+    def forward(self, x: torch.Tensor):
+        """x fp16 [T_local][hidden] -> (out fp32 [T_local][hidden], topk_idx, topk_w)."""
+        dist, st = self.dist, self.stages
+        T, k, W = x.shape[0], self.k, self.world
+        idx, w = st.route(x)
+        keys = idx.reshape(-1)
+        perm, inv, offsets = st.sort(keys, 0, self.E)                     # rows sorted by expert = by rank
+        send_rows = st.gather(x, perm, k)
+        send_keys = keys[perm.long()].contiguous()
+        bounds = offsets[:: self.n_local].to("cpu", torch.int64)          # first row of every rank's block (host sync)
+        send_counts = (bounds[1:] - bounds[:-1]).tolist()
+        counts_dev = torch.tensor(send_counts, dtype=torch.int64, device=x.device)
+        recv_dev = torch.empty_like(counts_dev)
+        dist.all_to_all_single(recv_dev, counts_dev, group=self.group)
+        recv_counts = recv_dev.tolist()
+        R = sum(recv_counts)
+        recv_rows = torch.empty((R, x.shape[1]), dtype=x.dtype, device=x.device)
+        recv_keys = torch.empty(R, dtype=torch.int32, device=x.device)
+        dist.all_to_all_single(recv_rows, send_rows, recv_counts, send_counts, group=self.group)
+        dist.all_to_all_single(recv_keys, send_keys, recv_counts, send_counts, group=self.group)
+        perm2, inv2, _ = st.sort(recv_keys, self.e0, self.n_local, for_experts=True)   # regroup by local expert
+        xr = st.gather(recv_rows, perm2, 1)
+        yr = st.experts(xr)
+        back = st.gather(yr, inv2, 1)                                      # expert outputs in arrival order
+        y_sorted = torch.empty_like(send_rows)
+        dist.all_to_all_single(y_sorted, back, send_counts, recv_counts, group=self.group)
+        out = st.combine(y_sorted, inv, w, st.shared_expert(x))
+        self.last_stats = {"sent_rows": T * k, "recv_rows": R, "send_counts": send_counts, "recv_counts": recv_counts}
+        return out, idx, w

@@ -161,6 +161,28 @@ size_t berth_moe_workspace_bytes(int T, int hidden, int inter, int shared_inter,
  * order, shared expert last. */
 int berth_moe_layer(const berth_moe_weights* w, const void* x, int T, void* out, int32_t* topk_idx,
                     float* topk_w, void* workspace, size_t workspace_bytes, void* stream);
+/* The stages of the layer one by one, for hosts that put a collective between them (expert
+ * parallelism).  `ews` is caller-provided scratch of berth_moe_experts_workspace_bytes(max_rows,
+ * n_local, hidden, inter, max_rows_per_expert) bytes; the same five values must be passed to
+ * berth_moe_sort_rows and berth_moe_experts, which share the problem table inside it.
+ *   sort_rows: stable sort of n entries by key (expert id) restricted to [e0, e0 + n_local):
+ *              perm[pos] = entry, inv[entry] = pos, offsets_out[0..n_local] = first row of each
+ *              expert (optional), and the problem table of the following berth_moe_experts call;
+ *   gather:    dst[i][:] = src[index[i] / div][:], fp16 rows of `hidden` elements;
+ *   experts:   yr = down(silu(gate(xr)) * up(xr)) row by row, xr fp16 [n_rows][hidden] sorted by
+ *              expert as sort_rows left them; w holds the LOCAL expert stacks (n_experts = n_local);
+ *   combine:   out[t] = sum_s topk_w[t][s] * y[inv[t*k+s]] (+ ysh[t]), fp32. */
+size_t berth_moe_experts_workspace_bytes(int max_rows, int n_local, int hidden, int inter,
+                                         int max_rows_per_expert);
+int berth_moe_sort_rows(const int32_t* keys, int n, int e0, int n_local, int32_t* perm, int32_t* inv,
+                        int32_t* offsets_out, void* ews, size_t ews_bytes, int max_rows, int hidden,
+                        int inter, int max_rows_per_expert, void* stream);
+int berth_moe_gather(const void* src, const int32_t* index, int div, int n, void* dst, int hidden,
+                     void* stream);
+int berth_moe_experts(const berth_moe_weights* w, const void* xr, void* yr, int n_rows, void* ews,
+                      size_t ews_bytes, int max_rows, int max_rows_per_expert, void* stream);
+int berth_moe_combine(const void* y, const int32_t* inv, const float* topk_w, const void* ysh,
+                      void* out, int T, int hidden, int top_k, void* stream);
 const char* berth_moe_last_error(void);
 const char* berth_moe_last_launch(void);
 

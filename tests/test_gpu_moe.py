@@ -111,3 +111,38 @@ def test_moe_layer_skewed_routing_property():
         o1, i1, w1 = _run_layer(wts, x[t:t + 1])
         assert (i1[0] == idx[t]).all()
         assert np.abs(o1[0] - out[t]).max() <= 4e-3 * rms
+
+
+class _OneRankDist:
+    """A one-rank stand-in for torch.distributed: an all-to-all among one rank is a copy."""
+    @staticmethod
+    def get_world_size(group=None):
+        return 1
+
+    @staticmethod
+    def get_rank(group=None):
+        return 0
+
+    @staticmethod
+    def all_to_all_single(out, inp, out_splits=None, in_splits=None, group=None):
+        out.copy_(inp)
+
+
+@pytest.mark.parametrize("T", [1, 48])
+def test_expert_parallel_stages_match_fused_layer(T):
+    """The staged path the expert-parallel host uses (sort / gather / experts / gather / combine through
+    the C ABI) gives the same result as berth_moe_layer."""
+    H, I, E, k, bits, cb = 256, 128, 32, 4, 4, 2
+    wts = synth.moe_layer_weights(1234, "ep1", H, I, E, k, bits, cb, shared_inter=128)
+    x = synth.activations(1234, f"ep1.x{T}", T, H)
+    ref, ref_idx, _ = _run_layer(wts, x)
+    stages = moe.GpuStages(torch.device("cuda", torch.cuda.current_device()), wts, E, max_rows=T * k, max_rows_per_expert=T)
+    layer = moe.EpMoeLayer.__new__(moe.EpMoeLayer)
+    layer.dist, layer.group, layer.stages = _OneRankDist, None, stages
+    layer.world, layer.rank, layer.E, layer.k, layer.n_local, layer.e0, layer.last_stats = 1, 0, E, k, E, 0, {}
+    out, idx, w = layer.forward(dev(x))
+    torch.cuda.synchronize()
+    assert (idx.cpu().numpy() == ref_idx).all()
+    rms = np.sqrt((ref.astype(np.float64) ** 2).mean())
+    assert np.abs(out.cpu().numpy() - ref).max() <= 1e-3 * rms
+    assert layer.last_stats["recv_rows"] == T * k
