@@ -113,6 +113,7 @@ class DecodeStack:
     callers of berth_b200.engine (Exl3Linear / MlpLayer)."""
 
     def __init__(self, m: int, rank: int):
+        """m = token rows per step (buffers are sized for it)."""
         import torch
         from berth_b200 import synth
         from berth_b200.engine import Exl3Linear, Gpu, MlpLayer
@@ -193,6 +194,123 @@ class DecodeStack:
         return e0.elapsed_time(e1) / (reps * len(mats))
 
 
+# ------------------------------------------------------------------ configuration 2: prefill GEMM
+
+PREFILL_M = 4096
+# (name, K, N, bits, fp32 out): gate/up/q/o at 4 bpw, down at 5, k/v at 3 (a fixed mix of the three rates)
+PREFILL_SHAPES = [("gate", HIDDEN, INTER, 4, 0), ("up", HIDDEN, INTER, 4, 0), ("down", INTER, HIDDEN, 5, 1),
+                  ("q", HIDDEN, QDIM, 4, 0), ("k", HIDDEN, KVDIM, 3, 0), ("v", HIDDEN, KVDIM, 3, 0), ("o", QDIM, HIDDEN, 4, 1)]
+
+
+def bench_prefill(rank: int, reps: int = 5) -> dict:
+    """The seven 27B-shaped matrices at M = 4096 through berth_prefill_exl3_linear (rotation kernel +
+    tcgen05 GEMM with in-kernel trellis decode).  Activations N(0,1) fp16 with 0.1 % x20 outliers."""
+    import torch
+    from berth_b200 import synth
+    from berth_b200.kernels import Codebook, OutDtype, prefill_lin
+    dev = torch.device("cuda", torch.cuda.current_device())
+    up = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16) if a.dtype == np.uint16 else np.ascontiguousarray(a)).to(dev)
+    M = PREFILL_M
+    xs = {k: up(synth.activations(1234, f"pf.x{k}", M, k, outlier_frac=0.001)) for k in (HIDDEN, INTER, QDIM)}
+    scratch = torch.empty(16, dtype=torch.float16, device=dev)
+    ahad = torch.empty(M * INTER, dtype=torch.float16, device=dev)
+    runs, flops = [], 0
+    for name, k, n, bits, f32 in PREFILL_SHAPES:
+        w = synth.linear_weights(synth.MASTER_SEED, f"pf.{name}", k, n, bits, fan_in_gain=True)
+        t, su, sv = up(w["trellis"]), up(w["suh"]), up(w["svh"])
+        c = torch.empty((M, n), dtype=torch.float32 if f32 else torch.float16, device=dev)
+        runs.append((xs[k], t, c, su, sv, k, n, bits, f32))
+        flops += 2 * M * k * n
+
+    def one_pass():
+        for x, t, c, su, sv, k, n, bits, f32 in runs:
+            prefill_lin.exl3_linear(x, t, c, su, ahad, sv, scratch, M, k, n, bits, Codebook(CB), OutDtype(f32))
+    for _ in range(3):
+        one_pass()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        one_pass()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = float(json.load(open(p))["bf16_tflops"]) if os.path.exists(p) else 1590.0
+    tf = flops / ms / 1e9
+    return {"workload": "c2_prefill_27b_shapes_m4096_mixed_3_4_5_bpw", "ms_per_pass": ms, "tflops": tf, "flops_per_pass": flops,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                         "peak_kind": "of measured (burst)" if os.path.exists(p) else "of fallback", "traffic": None},
+            "kernel": prefill_lin.last_launch()}
+
+
+# ------------------------------------------------------------------ configuration 3: MoE layer
+
+MOE = dict(hidden=2048, inter=512, n_experts=256, top_k=8, shared_inter=512)
+
+
+def bench_moe(rank: int, world: int, steps: int = 20) -> dict:
+    """A3B MoE layer (256 experts + shared, top-8, 4 bpw) at 1, 64 and 1024 tokens in total.  One GPU: the
+    fused berth_moe_layer.  N GPUs: experts sharded in blocks of 256/N, tokens split evenly, two NCCL
+    all-to-alls per layer (expert parallelism); time = max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from berth_b200 import moe, synth
+    dev = torch.device("cuda", torch.cuda.current_device())
+    H, I, E, K, SI = MOE["hidden"], MOE["inter"], MOE["n_experts"], MOE["top_k"], MOE["shared_inter"]
+    n_local = E // world
+    # each rank builds only its own expert block (same seeds and names as the full layer)
+    w = {"hidden": H, "inter": I, "n_experts": n_local, "top_k": K, "bits": BITS, "cb": CB, "shared_inter": SI,
+         "w_router": synth.router_weight(1234, "c3.gate.weight", H, E), "router_bias": None}
+    def stack(proj, k, n):
+        ids = range(rank * n_local, (rank + 1) * n_local)
+        t = np.stack([synth.trellis(1234, f"c3.experts.{proj}.{e}.trellis", k, n, BITS) for e in ids])
+        su = np.stack([synth.sign_scale(1234, f"c3.experts.{proj}.{e}.suh", k) for e in ids])
+        sv = np.stack([synth.sign_scale(1234, f"c3.experts.{proj}.{e}.svh", n, 1.0 / np.sqrt(k)) for e in ids])
+        return t, su, sv
+    w["gate_trellis"], w["gate_suh"], w["gate_svh"] = stack("gate_proj", H, I)
+    w["up_trellis"], w["up_suh"], w["up_svh"] = stack("up_proj", H, I)
+    w["down_trellis"], w["down_suh"], w["down_svh"] = stack("down_proj", I, H)
+    for pname, (k, n) in (("gate", (H, SI)), ("up", (H, SI)), ("down", (SI, H))):
+        lw = synth.linear_weights(1234, f"c3.shared_expert.{pname}_proj", k, n, BITS, fan_in_gain=True)
+        w[f"sh_{pname}_trellis"], w[f"sh_{pname}_suh"], w[f"sh_{pname}_svh"] = lw["trellis"], lw["suh"], lw["svh"]
+    out = {"workload": "c3_a3b_moe_layer_4bpw", "parallelism": "single" if world == 1 else f"ep{world}", "by_tokens": {}}
+    if world == 1:
+        layer = moe.MoeLayer(dev, w, 1024)
+    else:
+        stages = moe.GpuStages(dev, w, E, max_rows=1024 * K, max_rows_per_expert=1024)
+        layer = moe.EpMoeLayer(stages, dist.group.WORLD, E, K)
+    for T in (1, 64, 1024):
+        t_loc = T // world if T >= world else (1 if rank < T else 0)    # tokens of this rank
+        x = torch.from_numpy(synth.activations(1234, f"c3.x{T}.r{rank}", max(t_loc, 1), H)).to(dev)[:t_loc]
+        if world == 1:
+            o = torch.empty((T, H), dtype=torch.float32, device=dev)
+            idx = torch.empty((T, K), dtype=torch.int32, device=dev)
+            tw = torch.empty((T, K), dtype=torch.float32, device=dev)
+            run = lambda: layer.forward(x, o, idx, tw)
+        else:
+            run = lambda: layer.forward(x)
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t[0])
+        total = (T // world) * world if T >= world else T
+        out["by_tokens"][str(T)] = {"us_per_layer": ms * 1e3, "tokens_per_s": total / ms * 1e3}
+    return out
+
+
 # ------------------------------------------------------------------ CPU arm
 
 def cpu_pass(m: int, passes: int):
@@ -250,6 +368,7 @@ def main() -> None:
     ap.add_argument("--m", type=int, default=1, help="token rows per step (1, 8 or 32 in configuration 1)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the prefill (configuration 2) and MoE (configuration 3) measurements")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 10:
@@ -303,7 +422,21 @@ def main() -> None:
     e2e_ms = (time.perf_counter() - t0) * 1e3
     # ---- dominant kernel alone
     gate_ms = stack.time_gate_kernel(max(4, args.steps // 8))
+    # nvidia-smi samples every 100 ms; a short timed region ends before the first sample, so the same
+    # step loop is repeated for about 1.5 s under the sampler (same kernels, same clocks regime).
+    t_end = time.perf_counter() + 1.5
+    i = 0
+    while time.perf_counter() < t_end:
+        stack.step(i)
+        i += 1
+        if i % 64 == 0:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        clocks["window"] = "timed region + end-to-end region + 1.5 s repeat of the same step loop"
+    prefill = bench_prefill(rank) if (rank == 0 and not args.no_extras) else None
+    moe_res = None if args.no_extras else bench_moe(rank, world)
 
     if world > 1:
         t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
@@ -335,6 +468,8 @@ def main() -> None:
                     "d2h_bytes_per_step": stack.d2h_bytes, "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": stack.launches_per_step * args.steps,
             "clocks": clocks,
+            "prefill": prefill,
+            "moe": moe_res,
         }
         if not args.no_cpu_baseline and world == 1:
             gbs, dt, threads = cpu_pass(args.m, 2)

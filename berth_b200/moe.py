@@ -213,7 +213,11 @@ class EpMoeLayer:
         """x fp16 [T_local][hidden] -> (out fp32 [T_local][hidden], topk_idx, topk_w)."""
         dist, st = self.dist, self.stages
         T, k, W = x.shape[0], self.k, self.world
-        idx, w = st.route(x)
+        if T:
+            idx, w = st.route(x)
+        else:   # a rank without tokens still takes part in the exchanges
+            idx = torch.empty((0, k), dtype=torch.int32, device=x.device)
+            w = torch.empty((0, k), dtype=torch.float32, device=x.device)
         keys = idx.reshape(-1)
         perm, inv, offsets = st.sort(keys, 0, self.E)                     # rows sorted by expert = by rank
         send_rows = st.gather(x, perm, k)
@@ -235,6 +239,6 @@ class EpMoeLayer:
         back = st.gather(yr, inv2, 1)                                      # expert outputs in arrival order
         y_sorted = torch.empty_like(send_rows)
         dist.all_to_all_single(y_sorted, back, send_counts, recv_counts, group=self.group)
-        out = st.combine(y_sorted, inv, w, st.shared_expert(x))
+        out = st.combine(y_sorted, inv, w, st.shared_expert(x)) if T else torch.empty((0, x.shape[1]), dtype=torch.float32, device=x.device)
         self.last_stats = {"sent_rows": T * k, "recv_rows": R, "send_counts": send_counts, "recv_counts": recv_counts}
         return out, idx, w
