@@ -372,7 +372,7 @@ extern "C" int berth_moe_sort_rows(const int32_t* keys, int n, int e0, int n_loc
 {
     CallState& st = moe_state();
     return guarded(st, [&] {
-        if (!keys || !perm || !inv) throw std::runtime_error("moe sort: null device pointer");
+        if ((n > 0 && !keys) || !perm || !inv) throw std::runtime_error("moe sort: null device pointer");
         if (n < 0 || n > max_rows) throw std::runtime_error("moe sort: n must be within 0..max_rows");
         if (n_local < 1 || n_local > 1024) throw std::runtime_error("moe sort: n_local must be in 1..=1024");
         ExpertScratch es = expert_scratch(ews, ews_bytes, max_rows, n_local, hidden, inter, max_rows_per_expert);

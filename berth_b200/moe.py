@@ -138,6 +138,8 @@ class GpuStages:
         inv = torch.empty(max(n, 1), dtype=torch.int32, device=self.device)
         offsets = torch.empty(n_local + 1, dtype=torch.int32, device=self.device)
         ews = self.ews_loc if for_experts else self.ews_all
+        if n == 0:   # an empty torch tensor has a null data pointer
+            keys = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._check(_lib.lib().berth_moe_sort_rows(keys.data_ptr(), n, e0, n_local, perm.data_ptr(), inv.data_ptr(), offsets.data_ptr(),
                                                    ews.data_ptr(), ews.numel(), self.max_rows, self.d["hidden"], self.d["inter"],
                                                    self.mrpe, None))
