@@ -72,10 +72,10 @@ def exl3_linear(a, trellis, c, suh, a_had, svh, size_m: int, size_k: int, size_n
 def exl3_linear_static_scratch(a, trellis, c, suh, a_had, svh, size_m: int, size_k: int, size_n: int, k_bits: int,
                                codebook: Codebook, out: OutDtype, stream=None) -> None:
     """:func:`exl3_linear` for hosts that must not allocate device memory (their own planner owns
-    all of HBM, or the decode loop cannot take a ``cudaMalloc`` stall): the split-K scratch is a
-    fixed 4 MiB array inside the library, shared by every call on the device.  ``size_m <= 32``,
-    ``size_n <= 131072``; calls must not overlap on the GPU; make the first call on a device before
-    any stream capture."""
+    all of HBM, or the decode loop cannot take a ``cudaMalloc`` stall): the scratch is a fixed array
+    of about 6.1 MiB inside the library, shared by every call on the device.  ``size_m <= 32``,
+    ``size_n <= 131072``, ``size_k * ceil(size_m / 8) <= 131072``; calls must not overlap on the GPU;
+    make the first call on a device before any stream capture."""
     rc = _lib.lib().berth_exl3_linear_static_scratch(_ptr(a), _ptr(trellis), _ptr(c), _ptr(suh), _ptr(a_had),
                                                      _ptr(svh), size_m, size_k, size_n, k_bits, int(codebook),
                                                      int(out), _stream(stream))

@@ -27,8 +27,8 @@
  *
  * Per-device state owned by the library, allocated at the first launch on a device and kept
  * until exit (the counterpart of the lock buffer and 16 MiB split-K workspace of
- * crates/berth-kernels/csrc/linear.cu:334-345 and csrc/int8_sq.cu:20-47): one split-K
- * workspace (32 MiB of partial-sum slabs, self-resetting arrival counters, block sums).  Launches that overlap on one device
+ * crates/berth-kernels/csrc/linear.cu:334-345 and csrc/int8_sq.cu:20-47): about 40 MiB (split-K
+ * partial-sum slabs, rotated activations, self-resetting arrival counters, block sums).  Launches that overlap on one device
  * (different streams) must not share it: berth drives one stream per device, and so must
  * every other caller.
  */
@@ -45,7 +45,7 @@ extern "C" {
 /* ------------------------------------------------------------------ decode linear (m >= 1)
  * Replaces berth_exl3_linear (crates/berth-kernels/src/ffi.rs:7-21,
  * crates/berth-kernels/csrc/linear.cu:209-286,362-394): c = H(H(a*suh) . W(trellis)) * svh.
- * Serves every size_m with the fused decode GEMV (size_m <= 32) or the tensor-core GEMM. */
+ * Serves every size_m: the fused decode GEMV up to 32 rows, the tcgen05 tensor-core GEMM above. */
 int berth_exl3_linear(const void* a, const void* trellis, void* c, const void* suh, void* a_had,
                       const void* svh, int size_m, int size_k, int size_n, int k_bits,
                       int codebook, int out_fp32, void* stream);
@@ -55,10 +55,11 @@ const char* berth_exl3_last_launch(void);   /* crates/berth-kernels/csrc/linear.
 /* Same linear for callers that must not allocate device memory (a host whose own planner owns
  * every byte of HBM, or a decode loop that cannot take cudaMalloc's device-wide synchronisation).
  * No counterpart in berth: its library allocates its workspaces with cudaMalloc at first use.
- * The split-K scratch is a fixed __device__ array of 4 MiB + 132.25 KiB inside the library image
- * (4 MiB partial-sum slabs, 4 KiB band counters, 128 KiB block sums, a status word), held by every
- * GPU that loads the library until the process exits; nothing is allocated or freed.
- * Limits: size_m <= 32, size_n <= 131072 and size_k <= 131072; larger sizes are rejected with an error.  The first
+ * The scratch is a fixed __device__ array of about 6.1 MiB inside the library image (4 MiB
+ * partial-sum slabs, 2 MiB rotated activations, 16 KiB counters, 128 KiB block sums, a status
+ * word), held by every GPU that loads the library until the process exits; nothing is allocated
+ * or freed.  Limits: size_m <= 32, size_n <= 131072 and size_k * ceil(size_m / 8) <= 131072;
+ * larger sizes are rejected with an error.  The first
  * call on a device looks the array's device address up (cudaGetSymbolAddress); make that first
  * call before any stream capture begins.  All calls on a device share the scratch, which keeps
  * the previous call's contents (the counters are cleared on `stream` before each launch): calls
