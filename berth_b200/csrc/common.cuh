@@ -23,6 +23,32 @@ inline void cuda_ok(cudaError_t err, const char* what)
     throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(err));
 }
 
+// Programmatic dependent launch: the kernel may become resident while its predecessor on the
+// stream is still running (hiding its launch latency), so it must execute pdl_wait() before its
+// first access to anything the predecessor may have written, and should call pdl_trigger() early
+// to extend the same courtesy to its own successor.  A predecessor that never triggers (any foreign
+// kernel) behaves as an ordinary stream dependency.
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const char* what,
+                       Args&&... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cuda_ok(cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...), what);
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 // One family of entry points = one pair of thread-local strings (last error / last launch).
 struct CallState {
     std::string err;

@@ -57,9 +57,8 @@ constexpr int kProducerWarp = kConsumerWarps;
 constexpr int kThreads = (kConsumerWarps + 1 + kEpiWarps) * 32;
 constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kRingBytes = 96 * 1024;
-constexpr long long kWaitCycles = 500000000LL;
 
-enum StatusBits : unsigned { kStFullTimeout = 1u, kStEmptyTimeout = 2u, kStRedFullTimeout = 4u, kStRedEmptyTimeout = 8u };
+enum StatusBits : unsigned { kStFullTimeout = 1u, kStEmptyTimeout = 2u };
 
 // Compile-time geometry of a (BITS, TG) instance.
 template <int BITS, int TG>
@@ -79,7 +78,7 @@ struct Geo {
     static constexpr int TOK = 8 * TG;
     static constexpr int PITCH = BU * 128 + 4;                // floats per token row in shared slabs
     static constexpr int RED_SLAB = TOK * PITCH;
-    static constexpr size_t SMEM = size_t(kRingBytes) + size_t(2 * RW + 1) * RED_SLAB * 4 + size_t(2 * S + 4) * 8;
+    static constexpr size_t SMEM = size_t(kRingBytes) + size_t(2 * RW + 1) * RED_SLAB * 4 + size_t(2 * S) * 8;
     static_assert(S >= 2 && RW >= 1 && RW * RPW == 8 && CG * RW == kConsumerWarps, "geometry");
 };
 
@@ -135,19 +134,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after kWaitCycles SM clocks (a quarter of a second at 2 GHz), records
-// `code` in the status word and returns false; the caller carries on with whatever is there.
+// Bounded waits.  Both give up after roughly half a second, record `code` in the status word and
+// return false; the caller carries on with whatever is there.
+//   mbar_wait:        for the streaming warps, which expect the data to be there: tight polling;
+//   mbar_wait_parked: for the producer, which waits about a microsecond per stage: sleeps between
+//                     polls so that it leaves the issue slots to the decoding warps.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned* status, unsigned code)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > kWaitCycles) {
-            atomicOr(status, code);
-            return false;
-        }
+    for (uint32_t i = 0; i < (1u << 24); ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicOr(status, code);
+    return false;
+}
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, unsigned* status, unsigned code)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t i = 0; i < (1u << 21); ++i) {
+        __nanosleep(200);
+        if (mbar_try_wait(bar, parity)) return true;
     }
-    return true;
+    atomicOr(status, code);
+    return false;
 }
 // One box of the trellis view (x in 8-byte elements, y in k-tile rows, z = matrix of the stack)
 // into shared memory.
@@ -168,8 +176,21 @@ __device__ __forceinline__ void epi_sync()
 {
     asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
 }
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Hand-over of the partial-sum buffers between the streaming warps and the epilogue warps through
+// hardware named barriers (ids 2,3 = buffer filled, 4,5 = buffer drained): the waiting side blocks in
+// the barrier unit and takes no issue slots, the signalling side does not wait.  Every barrier counts
+// all streaming and all epilogue threads.
+constexpr int kHandoverThreads = (kConsumerWarps + kEpiWarps) * 32;
+__device__ __forceinline__ void handover_signal(int id)
+{
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(kHandoverThreads) : "memory");
+}
+__device__ __forceinline__ void handover_wait(int id)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(kHandoverThreads) : "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() { pdl_wait(); }
+__device__ __forceinline__ void grid_launch_dependents() { pdl_trigger(); }
 
 // ---------------------------------------------------------------- per-tile decode + MMA
 // Half-word selection on the FMA-heavy pipe: dp2a.lo(a, b) = a.h0*b.byte0 + a.h1*b.byte1.
@@ -310,6 +331,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
     float* outbuf = red + 2 * RW * RED_SLAB;                                  // [TOK][PITCH]
     uint64_t* bars = reinterpret_cast<uint64_t*>(outbuf + RED_SLAB);
 
+    // Let the next kernel on the stream (normally the next linear's rotation) become resident now; it
+    // waits for this grid's completion before it touches memory.
+    grid_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bands = p.n >> 7, kblocks = p.k >> 7;
     const int bgroups = (bands + BU - 1) / BU;          // band groups of one problem
@@ -322,16 +346,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
     const long long u0 = unit_begin(cta, U, G), u1 = unit_begin(cta + 1, U, G);
     const int nunits = int(u1 - u0);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + S);
-    const uint32_t redfull0 = smem_u32(bars + 2 * S), redempty0 = smem_u32(bars + 2 * S + 2);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, kConsumerWarps);
-        }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(redfull0 + 8 * b, kConsumerWarps);
-            mbar_init(redempty0 + 8 * b, kEpiWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -368,7 +387,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
             for (int i = 0; i < pre; ++i) issue_acts(i, smem_u32(ring + i * STAGE_BYTES + W_BYTES), full0 + 8 * i);
             int s = 0, lap = 1;
             for (int i = pre; i < nunits; ++i) {
-                mbar_wait(empty0 + 8 * s, (lap - 1) & 1, p.status, kStEmptyTimeout);
+                mbar_wait_parked(empty0 + 8 * s, (lap - 1) & 1, p.status, kStEmptyTimeout);
                 mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 const uint32_t dst = smem_u32(ring + s * STAGE_BYTES);
                 issue_weights(i, dst, full0 + 8 * s);
@@ -416,7 +435,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
 
             // ---- dump this segment's partial sums; the epilogue warps take it from here
             const int buf = flush & 1;
-            if (flush >= 2) mbar_wait(redempty0 + 8 * buf, ((flush >> 1) - 1) & 1, p.status, kStRedEmptyTimeout);
+            if (flush >= 2) handover_wait(4 + buf);   // the epilogue warps have drained this buffer
             float* mine = red + (buf * RW + rs) * RED_SLAB;
 #pragma unroll
             for (int t = 0; t < NT; ++t)
@@ -428,8 +447,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
                     mine[t0 * PITCH + c0 + 8] = acc[t][tg][2];
                     mine[(t0 + 1) * PITCH + c0 + 8] = acc[t][tg][3];
                 }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(redfull0 + 8 * buf);
+            handover_signal(2 + buf);
             ++flush;
             u += sg.units;
         }
@@ -457,7 +475,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
             const __half* svh = p.svh + size_t(z) * p.n;
             const float* bsum = p.blocksum + size_t(pi) * slab_rows * kblocks;
             const int buf = flush & 1;
-            mbar_wait(redfull0 + 8 * buf, (flush >> 1) & 1, p.status, kStRedFullTimeout);
+            handover_wait(2 + buf);
             // fixed-order reduction over the row streams: thread et owns column et of every band
             for (int tok = 0; tok < TOK && tok < rows; ++tok) {
 #pragma unroll
@@ -468,8 +486,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
                     outbuf[tok * PITCH + b * 128 + et] = v;
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(redempty0 + 8 * buf);
+            handover_signal(4 + buf);   // the streaming warps may refill this buffer
             epi_sync();   // outbuf complete
 
             bool finish = true;
@@ -577,6 +594,7 @@ __global__ void __launch_bounds__(128) k_rotate_in(const __half* __restrict__ a,
                                                    __half* __restrict__ a_had, uint32_t* __restrict__ afrag,
                                                    float* __restrict__ blocksum, int rows, int rows_pad, int k)
 {
+    grid_dependency_wait();      // the activations (and the scratch this kernel overwrites) belong to the preceding kernels
     grid_launch_dependents();
     const int lane = threadIdx.x & 31, kblocks = k >> 7, tgs = rows_pad >> 3;
     const int total = rows_pad * kblocks;
@@ -785,10 +803,9 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     if (afrag_bytes > sc.afrag_bytes)
         throw std::runtime_error("exl3 gemv: size_k * ceil(size_m / 8) exceeds the activation-fragment area of the scratch");
     const int rot_total = 8 * tg * kblocks;
-    k_rotate_in<<<std::min((rot_total + 3) / 4, 4 * sms), 128, 0, stream>>>(
-        static_cast<const __half*>(a), static_cast<const __half*>(suh), static_cast<__half*>(a_had), sc.afrag, sc.blocksum,
-        size_m, 8 * tg, size_k);
-    cuda_ok(cudaGetLastError(), "k_rotate_in launch");
+    launch_pdl(k_rotate_in, dim3(std::min((rot_total + 3) / 4, 4 * sms)), dim3(128), 0, stream, "k_rotate_in launch",
+               static_cast<const __half*>(a), static_cast<const __half*>(suh), static_cast<__half*>(a_had), sc.afrag, sc.blocksum,
+               size_m, 8 * tg, size_k);
 
     GemvArgs args;
     args.afrag = sc.afrag;
@@ -825,9 +842,9 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
     if (size_t(grid) * per_cta > sc.slab_bytes) grid = int(sc.slab_bytes / per_cta);
     if (grid < 1) throw std::runtime_error("exl3 grouped gemv: split-K scratch is too small");
     const long long warps = (long long) max_problems * 8 * tg * (size_k / 128);
-    k_rotate_rows<<<int(std::min<long long>((warps + 3) / 4, 8LL * sms)), 128, 0, stream>>>(
-        static_cast<const __half*>(xr), static_cast<const __half*>(suh_stack), problems, n_problems, afrag, blocksum, 8 * tg, size_k, max_problems, n_experts, max_rows);
-    cuda_ok(cudaGetLastError(), "k_rotate_rows launch");
+    launch_pdl(k_rotate_rows, dim3(int(std::min<long long>((warps + 3) / 4, 8LL * sms))), dim3(128), 0, stream, "k_rotate_rows launch",
+               static_cast<const __half*>(xr), static_cast<const __half*>(suh_stack), problems, n_problems, afrag, blocksum,
+               8 * tg, size_k, max_problems, n_experts, max_rows);
     GemvArgs args;
     args.afrag = afrag;
     args.blocksum = blocksum;

@@ -142,6 +142,8 @@ __device__ __forceinline__ __half silu_mul_one(__half g, __half u, float limit)
 __global__ void __launch_bounds__(256) k_silu_mul(const __half2* gate, const __half2* up,
                                                   __half2* out, long long pairs, float limit)
 {
+    pdl_wait();
+    pdl_trigger();
     for (long long i = (long long) blockIdx.x * 256 + threadIdx.x; i < pairs; i += (long long) gridDim.x * 256) {
         __half2 g = gate[i], u = up[i];
         out[i] = __halves2half2(silu_mul_one(__low2half(g), __low2half(u), limit),
@@ -151,6 +153,8 @@ __global__ void __launch_bounds__(256) k_silu_mul(const __half2* gate, const __h
 
 __global__ void __launch_bounds__(256) k_add_f32(const float* a, const float* b, float* c, int n)
 {
+    pdl_wait();
+    pdl_trigger();
     int i = blockIdx.x * 256 + threadIdx.x;
     if (i < n) c[i] = __fadd_rn(a[i], b[i]);
 }
@@ -242,9 +246,8 @@ extern "C" int berth_ops_silu_mul(const void* gate, const void* up, void* out, i
         if (numel < 2 || (numel & 1)) throw std::runtime_error("silu_mul: numel must be positive and even");
         long long pairs = numel / 2;
         int grid = int(std::min<long long>((pairs + 255) / 256, 148LL * 8));
-        k_silu_mul<<<grid, 256, 0, (cudaStream_t) stream>>>((const __half2*) gate, (const __half2*) up, (__half2*) out,
-                                                            pairs, act_limit);
-        cuda_ok(cudaGetLastError(), "silu_mul launch");
+        launch_pdl(k_silu_mul, dim3(grid), dim3(256), 0, (cudaStream_t) stream, "silu_mul launch", (const __half2*) gate,
+                   (const __half2*) up, (__half2*) out, pairs, act_limit);
         st.launch = "k_silu_mul block=256 grid=" + std::to_string(grid);
     });
 }
@@ -256,8 +259,8 @@ extern "C" int berth_ops_add_f32(const void* a, const void* b, void* c, int n, v
         if (!a || !b || !c) throw std::runtime_error("add_f32: null device pointer");
         if (n < 1) throw std::runtime_error("add_f32: n must be positive");
         int grid = (n + 255) / 256;
-        k_add_f32<<<grid, 256, 0, (cudaStream_t) stream>>>((const float*) a, (const float*) b, (float*) c, n);
-        cuda_ok(cudaGetLastError(), "add_f32 launch");
+        launch_pdl(k_add_f32, dim3(grid), dim3(256), 0, (cudaStream_t) stream, "add_f32 launch", (const float*) a,
+                   (const float*) b, (float*) c, n);
         st.launch = "k_add_f32 block=256 grid=" + std::to_string(grid);
     });
 }
