@@ -149,7 +149,7 @@ class DecodeStack:
         self.h_o = torch.empty((m, HIDDEN), dtype=f32).pin_memory()
         self.h2d_bytes = 2 * m * (HIDDEN + HIDDEN + QDIM)
         self.d2h_bytes = m * (4 * HIDDEN + 2 * QDIM + 4 * KVDIM + 4 * HIDDEN)
-        self.launches_per_step = 15   # 7 x (k_rotate_in + k_exl3_gemv) + 1 x k_silu_mul
+        self.launches_per_step = 22   # 7 x (k_rotate_in + k_exl3_gemv + k_gemv_finish) + 1 x k_silu_mul
 
     def step(self, i: int) -> None:
         from berth_b200.kernels import OutDtype

@@ -87,14 +87,12 @@ struct DeviceInfo {
 const DeviceInfo& device_info(int device);
 int current_device();
 
-// Scratch of the decode GEMV: fp32 partial-sum slabs (two [m][128] slabs per CTA), arrival counters
-// (four per band group, zero between launches), one fp32 sum per (row, 128 rotated
-// inputs), and a status word that collects bounded-wait failures.
+// Scratch of the decode GEMV: fp32 partial-sum slabs (two [m][BU*128] slabs per CTA), the rotated
+// activations in fragment order, one fp32 sum per (row, 128 rotated inputs), and a status word
+// that collects bounded-wait failures.
 struct GemvScratch {
     float* slabs = nullptr;
     size_t slab_bytes = 0;
-    unsigned* counters = nullptr;
-    int counter_slots = 0;
     uint32_t* afrag = nullptr;     // rotated activations in MMA fragment order
     size_t afrag_bytes = 0;
     float* blocksum = nullptr;
@@ -104,7 +102,6 @@ struct GemvScratch {
 // The library's own scratch: allocated once per device at first use, never grown, never freed
 // (cf. crates/berth-kernels/csrc/int8_sq.cu:20-47 of berth).
 constexpr size_t kGemvSlabBytes = size_t(32) << 20;
-constexpr int kGemvCounterSlots = 1 << 16;
 constexpr size_t kGemvBlocksumFloats = size_t(32) * 4096;
 constexpr size_t kGemvAfragBytes = size_t(8) << 20;   // size_k * ceil(size_m / 8) <= 524288
 GemvScratch gemv_workspace(int device);

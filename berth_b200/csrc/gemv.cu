@@ -1,7 +1,7 @@
-// Fused EXL3 decode GEMV (size_m <= 32): trellis tiles streamed through shared memory by TMA,
-// decoded in registers, accumulated on the tensor cores, split-K reduced by whoever arrives
-// last, rotated back (128-wide Hadamard) and scaled -- one persistent launch, preceded by a
-// tiny rotation kernel for the activations.
+// EXL3 decode GEMV (size_m <= 32): trellis tiles streamed through shared memory by TMA, decoded
+// in registers and accumulated on the tensor cores by one persistent launch; a tiny rotation
+// kernel for the activations runs before it and a wide finishing kernel (split-K sum, 128-wide
+// Hadamard, output scale) after it, the three chained by programmatic dependent launch.
 //
 // Roofline: HBM.  Algorithmic bytes per launch = K*N*BITS/8 + 2K + 2N + 2MK + out_bytes*M*N.
 // At 4 bits per weight the roofline asks for ~36 weights per cycle per SM, while the two
@@ -21,8 +21,9 @@
 // engine needs to stream near HBM speed) ordered band-group-major; CTA c of G (= number of SMs)
 // takes the contiguous unit range [c*U/G, (c+1)*U/G), so every SM streams the same number of
 // bytes with no tail wave.  A range covers at most one partial band group at its head and one
-// at its tail; those are reduced through slabs (2 per CTA) and arrival counters: whoever
-// arrives last sums the slabs in CTA order -- deterministic, and nothing ever waits on a peer.
+// at its tail; their partial sums go to slabs (2 per CTA) which k_gemv_finish, one warp per
+// (band, row), sums in CTA order -- deterministic, nothing ever waits on a peer, and the loads
+// of that sum are spread over the whole GPU instead of trailing behind the last CTA to arrive.
 //
 // Inside a CTA (21 warps, one CTA per SM):
 //   warp 16      producer: one lane issues one 2-D TMA copy (8 rows x one run) per unit into a
@@ -31,9 +32,9 @@
 //                unit, keeping NT*TG*4 fp32 accumulators per lane (TG token groups of 8 for
 //                m <= 8, 16, 32); at the end of a segment it dumps them into a double-buffered
 //                shared slab and carries on -- consumers never meet at a barrier;
-//   warps 17..20 epilogue: reduce the dumped slabs in fixed order, write/arrive on the split-K
-//                slabs or finish the bands (MUL1 affine correction, Hadamard, svh, store), in
-//                the background of the streaming warps.
+//   warps 17..20 epilogue: reduce the dumped slabs in fixed order and write the split-K slab, or,
+//                when the CTA holds a band group's whole K, finish the bands themselves (MUL1
+//                affine correction, Hadamard, svh, store), in the background of the streaming warps.
 // Every mbarrier wait is bounded; a wait that runs out sets a status bit and carries on.
 #include "exl3_decode.cuh"
 #include "../../include/berth_b200.h"
@@ -91,7 +92,6 @@ struct GemvArgs {
     const int* n_problems;         // grouped launch: device-side count
     int max_problems, n_matrices, max_rows;   // bounds the table entries are clamped to
     float* slabs;             // [2*G][m][BU*128]
-    unsigned* counters;       // [band groups][kEpiWarps], zero between launches
     unsigned* status;
     int m, k, n, out_fp32;
 };
@@ -297,11 +297,52 @@ __device__ __forceinline__ void tile_mma(const uint32_t (&s)[8], float (&acc)[TG
     }
 }
 
+// Sum over a row's block sums (the MUL1 epilogue's sum of the rotated activations), whole warp.
+__device__ __forceinline__ float row_sum(const float* bsum, int kblocks, int lane)
+{
+    float sx = 0.f;
+    for (int b = lane; b < kblocks; b += 32) sx = __fadd_rn(sx, __ldg(bsum + b));
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) sx = __fadd_rn(sx, __shfl_xor_sync(dq::kFull, sx, off));
+    return sx;
+}
+
+// Last steps of one output band of one row: v = the lane's four fp32 dot products (columns
+// band*128 + 4*lane ..).  MUL1: w = S*h + B per weight  =>  sum_k x_k w_k = S*acc + B*sum_k x_k.
+template <bool MUL1>
+__device__ __forceinline__ void finish_band(float (&v)[4], float sx, int lane, const __half* svh, int band, void* c,
+                                            size_t out_row, int n, int out_fp32)
+{
+    const int col = band * 128 + lane * 4;
+    const uint2 sr = __ldg(reinterpret_cast<const uint2*>(svh + col));
+    if constexpr (MUL1) {
+        const float S1 = __half2float(__ushort_as_half(dq::kMul1S));
+        const float bsx = __fmul_rn(__half2float(__ushort_as_half(dq::kMul1B)), sx);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = __fmaf_rn(S1, v[i], bsx);
+    }
+    dq::had128_warp(v, lane);
+    uint2 srm = sr;
+    __half2 s0 = *reinterpret_cast<__half2*>(&srm.x), s1 = *reinterpret_cast<__half2*>(&srm.y);
+    v[0] = __fmul_rn(__fmul_rn(v[0], kRScale), __low2float(s0));
+    v[1] = __fmul_rn(__fmul_rn(v[1], kRScale), __high2float(s0));
+    v[2] = __fmul_rn(__fmul_rn(v[2], kRScale), __low2float(s1));
+    v[3] = __fmul_rn(__fmul_rn(v[3], kRScale), __high2float(s1));
+    if (out_fp32) {
+        *reinterpret_cast<float4*>(static_cast<float*>(c) + out_row * n + col) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        uint2 o;
+        o.x = dq::pack_half2(__float2half_rn(v[0]), __float2half_rn(v[1]));
+        o.y = dq::pack_half2(__float2half_rn(v[2]), __float2half_rn(v[3]));
+        *reinterpret_cast<uint2*>(static_cast<__half*>(c) + out_row * n + col) = o;
+    }
+}
+
 // One segment (part of one band group) of a CTA's unit range.
 struct Segment {
     int bg, kb_begin, units;
     bool head;       // starts at the CTA's first unit (slab 2c) or later (slab 2c+1)
-    bool whole;      // covers the band group's whole K: no slab, no counter
+    bool whole;      // covers the band group's whole K: finished in the decode kernel, no slab
 };
 __device__ __forceinline__ Segment segment_at(long long u, long long u0, long long u1, int kblocks)
 {
@@ -342,7 +383,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
     const long long U = (long long) nprob * bgroups * kblocks;
     const int cta = blockIdx.x;
     const int G = U < (long long) gridDim.x ? int(U) : int(gridDim.x);   // CTAs that own units
-    if (cta >= G) return;
+    if (cta >= G) {
+        grid_dependency_wait();   // a grid must not complete before its predecessors: its successor relies on that
+        return;
+    }
     const long long u0 = unit_begin(cta, U, G), u1 = unit_begin(cta + 1, U, G);
     const int nunits = int(u1 - u0);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + S);
@@ -458,7 +502,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
     {
         const int ew = warp - kProducerWarp - 1;      // 0..3
         const int et = threadIdx.x - (kProducerWarp + 1) * 32;   // 0..127 = column inside a band
-        grid_dependency_wait();                       // block sums and problem table come from the preceding kernels
+        // Block sums and the problem table come from the preceding kernels, and the slabs may still be
+        // read by the finishing kernel of the previous linear.
+        grid_dependency_wait();
         const int slab_rows = grouped ? TOK : p.m;
         const size_t slab_floats = size_t(slab_rows) * BU * 128;
         int flush = 0;
@@ -472,115 +518,115 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
                 const GemvProblem pr = load_problem(p.problems, pi, p.n_matrices, TOK, p.max_rows);
                 rows = pr.rows; row0 = pr.row0; z = pr.z;
             }
-            const __half* svh = p.svh + size_t(z) * p.n;
-            const float* bsum = p.blocksum + size_t(pi) * slab_rows * kblocks;
             const int buf = flush & 1;
             handover_wait(2 + buf);
             // fixed-order reduction over the row streams: thread et owns column et of every band
+            float* dst = sg.whole ? outbuf : p.slabs + size_t(sg.head ? 2 * cta : 2 * cta + 1) * slab_floats;
+            const int dpitch = sg.whole ? PITCH : BU * 128;
             for (int tok = 0; tok < TOK && tok < rows; ++tok) {
 #pragma unroll
                 for (int b = 0; b < BU; ++b) {
                     float v = 0.f;
 #pragma unroll
                     for (int w = 0; w < RW; ++w) v = __fadd_rn(v, red[(buf * RW + w) * RED_SLAB + tok * PITCH + b * 128 + et]);
-                    outbuf[tok * PITCH + b * 128 + et] = v;
+                    if (sg.whole) dst[tok * dpitch + b * 128 + et] = v;
+                    else __stcg(dst + tok * dpitch + b * 128 + et, v);
                 }
             }
             handover_signal(4 + buf);   // the streaming warps may refill this buffer
-            epi_sync();   // outbuf complete
-
-            bool finish = true;
-            int first_cta = cta, last_cta = cta, first_slab = 0;
-            if (!sg.whole && ew < rows) {
-                const int slab = sg.head ? 2 * cta : 2 * cta + 1;
-                for (int row = ew; row < rows; row += kEpiWarps)
-#pragma unroll
-                    for (int b = 0; b < BU; ++b) {
-                        float4 v = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
-                        __stcg(reinterpret_cast<float4*>(p.slabs + size_t(slab) * slab_floats + (size_t(row) * BU + b) * 128 + lane * 4), v);
-                    }
-                first_cta = unit_owner((long long) sg.bg * kblocks, U, G);
-                last_cta = unit_owner((long long) (sg.bg + 1) * kblocks - 1, U, G);
-                // slabs of this band group, in CTA order: the first CTA's tail (or head, if its range
-                // starts exactly here), then the heads of the following CTAs
-                first_slab = (unit_begin(first_cta, U, G) >= (long long) sg.bg * kblocks) ? 2 * first_cta : 2 * first_cta + 1;
-                __threadfence();
-                __syncwarp();
-                unsigned old = 0;
-                if (lane == 0) old = atomicAdd(p.counters + sg.bg * kEpiWarps + ew, 1u);
-                old = __shfl_sync(dq::kFull, old, 0);
-                finish = (old == unsigned(last_cta - first_cta));
-                if (finish) __threadfence();
-            }
-
-            if (finish) {
+            if (sg.whole) {
+                epi_sync();   // outbuf complete
+                const __half* svh = p.svh + size_t(z) * p.n;
+                const float* bsum = p.blocksum + size_t(pi) * slab_rows * kblocks;
                 for (int row = ew; row < rows; row += kEpiWarps) {
-                    float sx = 0.f;
-                    if constexpr (CB == 2) {
-                        // w = S*h + B per weight  =>  sum_k x_k w_k = S*acc + B*sum_k x_k
-                        for (int b = lane; b < kblocks; b += 32) sx = __fadd_rn(sx, __ldg(bsum + size_t(row) * kblocks + b));
-#pragma unroll
-                        for (int off = 16; off >= 1; off >>= 1) sx = __fadd_rn(sx, __shfl_xor_sync(dq::kFull, sx, off));
-                    }
+                    const float sx = (CB == 2) ? row_sum(bsum + size_t(row) * kblocks, kblocks, lane) : 0.f;
                     for (int b = 0; b < BU; ++b) {
                         const int band = lbg * BU + b;
                         if (band >= bands) break;   // ragged last band group
-                        float v[4];
-                        if (sg.whole) {
-                            float4 t = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
-                            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-                        } else {
-                            v[0] = v[1] = v[2] = v[3] = 0.f;
-                            const float* base = p.slabs + (size_t(row) * BU + b) * 128 + lane * 4;
-                            const int nsl = last_cta - first_cta + 1;
-                            for (int i0 = 0; i0 < nsl; i0 += 8) {
-                                float4 t[8];
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) {   // eight independent loads in flight, summed in CTA order
-                                    const int si = i0 + i;
-                                    const int slab = si == 0 ? first_slab : 2 * (first_cta + si);
-                                    t[i] = si < nsl ? __ldcg(reinterpret_cast<const float4*>(base + size_t(slab) * slab_floats))
-                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
-                                }
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) {
-                                    if (i0 + i < nsl) {
-                                        v[0] = __fadd_rn(v[0], t[i].x); v[1] = __fadd_rn(v[1], t[i].y);
-                                        v[2] = __fadd_rn(v[2], t[i].z); v[3] = __fadd_rn(v[3], t[i].w);
-                                    }
-                                }
-                            }
-                        }
-                        if constexpr (CB == 2) {
-                            const float S1 = __half2float(__ushort_as_half(dq::kMul1S));
-                            const float bsx = __fmul_rn(__half2float(__ushort_as_half(dq::kMul1B)), sx);
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) v[i] = __fmaf_rn(S1, v[i], bsx);
-                        }
-                        dq::had128_warp(v, lane);
-                        const int col = band * 128 + lane * 4;
-                        uint2 sr = *reinterpret_cast<const uint2*>(svh + col);
-                        __half2 s0 = *reinterpret_cast<__half2*>(&sr.x), s1 = *reinterpret_cast<__half2*>(&sr.y);
-                        v[0] = __fmul_rn(__fmul_rn(v[0], kRScale), __low2float(s0));
-                        v[1] = __fmul_rn(__fmul_rn(v[1], kRScale), __high2float(s0));
-                        v[2] = __fmul_rn(__fmul_rn(v[2], kRScale), __low2float(s1));
-                        v[3] = __fmul_rn(__fmul_rn(v[3], kRScale), __high2float(s1));
-                        if (p.out_fp32) {
-                            *reinterpret_cast<float4*>(static_cast<float*>(p.c) + size_t(row0 + row) * p.n + col) = make_float4(v[0], v[1], v[2], v[3]);
-                        } else {
-                            uint2 o;
-                            o.x = dq::pack_half2(__float2half_rn(v[0]), __float2half_rn(v[1]));
-                            o.y = dq::pack_half2(__float2half_rn(v[2]), __float2half_rn(v[3]));
-                            *reinterpret_cast<uint2*>(static_cast<__half*>(p.c) + size_t(row0 + row) * p.n + col) = o;
-                        }
+                        float4 t = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
+                        float v[4] = {t.x, t.y, t.z, t.w};
+                        finish_band<CB == 2>(v, sx, lane, svh, band, p.c, size_t(row0 + row), p.n, p.out_fp32);
                     }
                 }
-                if (!sg.whole && ew < rows && lane == 0) p.counters[sg.bg * kEpiWarps + ew] = 0;   // self-resetting
+                epi_sync();   // outbuf is free again
             }
-            epi_sync();   // outbuf is free again
             ++flush;
             u += sg.units;
         }
+    }
+}
+
+// Finishing kernel of the decode GEMV: one warp per (band group, band, row) sums that row's
+// split-K slabs in CTA order (eight independent loads in flight), applies the MUL1 affine
+// correction, the 128-wide Hadamard and the output scale, and stores.  Band groups whose whole K
+// sat in one CTA were finished by the decode kernel itself and are skipped.
+struct FinishArgs {
+    const float* slabs;
+    const float* blocksum;
+    void* c;
+    const __half* svh;
+    const GemvProblem* problems;
+    const int* n_problems;
+    int max_problems, n_matrices, max_rows;
+    int m, k, n, out_fp32, bu, tok, main_grid, mul1;
+};
+
+__global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int lane = threadIdx.x & 31;
+    const int bands = p.n >> 7, kblocks = p.k >> 7, bu = p.bu;
+    const int bgroups = (bands + bu - 1) / bu;
+    const bool grouped = p.problems != nullptr;
+    const int nprob = grouped ? min(max(__ldg(p.n_problems), 0), p.max_problems) : 1;
+    const long long U = (long long) nprob * bgroups * kblocks;
+    const int G = U < (long long) p.main_grid ? int(U) : p.main_grid;
+    const int slab_rows = grouped ? p.tok : p.m;
+    const size_t slab_floats = size_t(slab_rows) * bu * 128;
+    const long long total = (long long) nprob * bgroups * bu * slab_rows;
+    for (long long task = (long long) blockIdx.x * 8 + (threadIdx.x >> 5); task < total; task += (long long) gridDim.x * 8) {
+        const int row = int(task % slab_rows);
+        const int b = int((task / slab_rows) % bu);
+        const int gbg = int(task / ((long long) slab_rows * bu));
+        const int pi = gbg / bgroups, lbg = gbg - pi * bgroups, band = lbg * bu + b;
+        if (band >= bands) continue;   // ragged last band group
+        int rows = p.m, row0 = 0, z = 0;
+        if (grouped) {
+            const GemvProblem pr = load_problem(p.problems, pi, p.n_matrices, p.tok, p.max_rows);
+            rows = pr.rows; row0 = pr.row0; z = pr.z;
+        }
+        if (row >= rows) continue;
+        const int first_cta = unit_owner((long long) gbg * kblocks, U, G);
+        const int last_cta = unit_owner((long long) (gbg + 1) * kblocks - 1, U, G);
+        if (first_cta == last_cta) continue;   // one CTA held the whole K and finished the band itself
+        // slabs of this band group, in CTA order: the first CTA's tail (or head, if its range starts
+        // exactly here), then the heads of the following CTAs
+        const int first_slab = (unit_begin(first_cta, U, G) >= (long long) gbg * kblocks) ? 2 * first_cta : 2 * first_cta + 1;
+        const int nsl = last_cta - first_cta + 1;
+        const float sx = p.mul1 ? row_sum(p.blocksum + (size_t(pi) * slab_rows + row) * kblocks, kblocks, lane) : 0.f;
+        const float* base = p.slabs + (size_t(row) * bu + b) * 128 + lane * 4;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int i0 = 0; i0 < nsl; i0 += 8) {
+            float4 t[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int si = i0 + i;
+                const int slab = si == 0 ? first_slab : 2 * (first_cta + si);
+                t[i] = si < nsl ? __ldcg(reinterpret_cast<const float4*>(base + size_t(slab) * slab_floats))
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (i0 + i < nsl) {
+                    v[0] = __fadd_rn(v[0], t[i].x); v[1] = __fadd_rn(v[1], t[i].y);
+                    v[2] = __fadd_rn(v[2], t[i].z); v[3] = __fadd_rn(v[3], t[i].w);
+                }
+            }
+        }
+        const __half* svh = p.svh + size_t(z) * p.n;
+        if (p.mul1) finish_band<true>(v, sx, lane, svh, band, p.c, size_t(row0 + row), p.n, p.out_fp32);
+        else finish_band<false>(v, sx, lane, svh, band, p.c, size_t(row0 + row), p.n, p.out_fp32);
     }
 }
 
@@ -594,8 +640,11 @@ __global__ void __launch_bounds__(128) k_rotate_in(const __half* __restrict__ a,
                                                    __half* __restrict__ a_had, uint32_t* __restrict__ afrag,
                                                    float* __restrict__ blocksum, int rows, int rows_pad, int k)
 {
-    grid_dependency_wait();      // the activations (and the scratch this kernel overwrites) belong to the preceding kernels
+    // Trigger first: the decode kernel behind this one may then take each SM as the previous decode
+    // kernel leaves it and prefetch its weights; it still waits for this grid, which itself waits here
+    // for everything before it (the activations and the scratch this kernel overwrites).
     grid_launch_dependents();
+    grid_dependency_wait();
     const int lane = threadIdx.x & 31, kblocks = k >> 7, tgs = rows_pad >> 3;
     const int total = rows_pad * kblocks;
     for (int idx = blockIdx.x * 4 + (threadIdx.x >> 5); idx < total; idx += gridDim.x * 4) {
@@ -772,6 +821,19 @@ __global__ void __launch_bounds__(128) k_rotate_rows(const __half* __restrict__ 
     }
 }
 
+// The finishing kernel behind a decode launch of `main_grid` CTAs; `warps` = (band, row) tasks at most.
+void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int codebook, long long warps, int sms, cudaStream_t stream)
+{
+    FinishArgs f;
+    f.slabs = a.slabs; f.blocksum = a.blocksum; f.c = a.c; f.svh = a.svh;
+    f.problems = a.problems; f.n_problems = a.n_problems;
+    f.max_problems = a.max_problems; f.n_matrices = a.n_matrices; f.max_rows = a.max_rows;
+    f.m = a.m; f.k = a.k; f.n = a.n; f.out_fp32 = a.out_fp32;
+    f.bu = bu; f.tok = tok; f.main_grid = main_grid; f.mul1 = codebook == 2;
+    const int grid = int(std::max<long long>(1, std::min<long long>((warps + 7) / 8, 8LL * sms)));
+    launch_pdl(k_gemv_finish, dim3(grid), dim3(256), 0, stream, "k_gemv_finish launch", f);
+}
+
 }  // namespace
 
 // Launches rotation + decode GEMV for up to 32 rows.  `sc` is the split-K scratch: the library's
@@ -787,7 +849,6 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     const int tg = size_m <= 8 ? 1 : (size_m <= 16 ? 2 : 4);
     const int bu = k_bits <= 4 ? 2 : 1;   // bands per unit, as Geo<BITS, TG>::BU
     const int bands = size_n / 128, kblocks = size_k / 128, bgroups = (bands + bu - 1) / bu;
-    if (bgroups * kEpiWarps > sc.counter_slots) throw std::runtime_error("exl3 gemv: size_n exceeds the counter table of the scratch");
     if (size_t(size_m) * kblocks > sc.blocksum_floats)
         throw std::runtime_error("exl3 gemv: size_m * size_k / 128 exceeds the block-sum table of the scratch");
     const long long units = (long long) bgroups * kblocks;
@@ -813,7 +874,6 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     args.c = c;
     args.svh = static_cast<const __half*>(svh);
     args.slabs = sc.slabs;
-    args.counters = sc.counters;
     args.status = sc.status;
     args.m = size_m; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
@@ -821,8 +881,10 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     args.n_problems = nullptr;
     args.max_problems = 1; args.n_matrices = 1; args.max_rows = size_m;
     const size_t smem = launch_bits(k_bits, codebook, tg, trellis, 1, args, grid, stream);
+    launch_finish(args, bu, 8 * tg, grid, codebook, (long long) bgroups * bu * size_m, sms, stream);
     return "k_rotate_in + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," + std::to_string(tg) +
-           "> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem);
+           "> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem) +
+           " + k_gemv_finish";
 }
 
 std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n_experts, void* c, const void* suh_stack,
@@ -835,8 +897,6 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
     if (tg != 1 && tg != 2 && tg != 4) throw std::runtime_error("exl3 grouped gemv: token groups must be 1, 2 or 4");
     const int bu = k_bits <= 4 ? 2 : 1;
     const int bands = size_n / 128, bgroups = (bands + bu - 1) / bu;
-    if ((long long) max_problems * bgroups * kEpiWarps > sc.counter_slots)
-        throw std::runtime_error("exl3 grouped gemv: problems x band groups exceed the counter table of the scratch");
     int grid = sms;
     const size_t per_cta = size_t(2) * 8 * tg * bu * 128 * sizeof(float);
     if (size_t(grid) * per_cta > sc.slab_bytes) grid = int(sc.slab_bytes / per_cta);
@@ -856,13 +916,14 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
     args.n_matrices = n_experts;
     args.max_rows = max_rows;
     args.slabs = sc.slabs;
-    args.counters = sc.counters;
     args.status = sc.status;
     args.m = 8 * tg; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
     const size_t smem = launch_bits(k_bits, codebook, tg, trellis_stack, n_experts, args, grid, stream);
+    launch_finish(args, bu, 8 * tg, grid, codebook, (long long) max_problems * bgroups * bu * 8 * tg, sms, stream);
     return "k_rotate_rows + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," + std::to_string(tg) +
-           ",grouped> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem);
+           ",grouped> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem) +
+           " + k_gemv_finish";
 }
 
 }  // namespace berth
@@ -878,12 +939,11 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
 // cudaFree or any allocating routine.
 //
 // The scratch is one file-scope __device__ array: 4 MiB of fp32 partial-sum slabs, 2 MiB for the
-// rotated activations in fragment order, arrival counters (16 KiB), one fp32 block sum per
-// (row, 128 inputs) (128 KiB) and a status word.  Every
-// GPU that loads the library carries it until the process exits.  All calls on a device share it
-// and it keeps whatever the previous call left behind: the counters are cleared on the stream
-// before each launch; slabs, fragments and block sums are fully overwritten before they are read.  Two
-// calls that overlap on the GPU (different streams) race on it; issue them on one stream.
+// rotated activations in fragment order, one fp32 block sum per (row, 128 inputs) (128 KiB) and a
+// status word.  Every GPU that loads the library carries it until the process exits.  All calls on
+// a device share it and it keeps whatever the previous call left behind: nothing needs clearing,
+// slabs, fragments and block sums are fully overwritten before they are read.  Two calls that
+// overlap on the GPU (different streams) race on it; issue them on one stream.
 namespace berth {
 namespace {
 
@@ -891,11 +951,10 @@ constexpr size_t kStaticSlabBytes = size_t(4) << 20;   // 4 MiB of split-K parti
 constexpr int kStaticMaxBands = 1024;                  // size_n <= 131072
 constexpr int kStaticMaxRows = 32;
 constexpr int kStaticMaxKBlocks = 1024;                // size_k <= 131072
-constexpr size_t kStaticCounterBytes = size_t(kStaticMaxBands) * kEpiWarps * sizeof(unsigned);
 constexpr size_t kStaticBlocksumBytes = size_t(kStaticMaxRows) * kStaticMaxKBlocks * sizeof(float);
 constexpr size_t kStaticAfragBytes = size_t(2) << 20;   // size_k * ceil(size_m / 8) <= 131072
 
-static __device__ __align__(256) unsigned char g_static_scratch[kStaticSlabBytes + kStaticAfragBytes + kStaticCounterBytes + kStaticBlocksumBytes + 256];
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticSlabBytes + kStaticAfragBytes + kStaticBlocksumBytes + 256];
 
 GemvScratch g_static_ptr[kMaxDevices];
 std::mutex g_static_mu;
@@ -917,9 +976,6 @@ GemvScratch static_scratch(int device)
         s.afrag = reinterpret_cast<uint32_t*>(b);
         s.afrag_bytes = kStaticAfragBytes;
         b += kStaticAfragBytes;
-        s.counters = reinterpret_cast<unsigned*>(b);
-        s.counter_slots = kStaticMaxBands * kEpiWarps;
-        b += kStaticCounterBytes;
         s.blocksum = reinterpret_cast<float*>(b);
         s.blocksum_floats = size_t(kStaticMaxRows) * kStaticMaxKBlocks;
         b += kStaticBlocksumBytes;
@@ -960,8 +1016,6 @@ extern "C" int berth_exl3_linear_static_scratch(const void* a, const void* trell
             throw std::runtime_error("exl3 linear: no linked kernel for this GPU (library is built for sm_100a only)");
         GemvScratch s = static_scratch(device);
         cudaStream_t cs = (cudaStream_t) stream;
-        // Arrival counters must start at zero; slabs and block sums need no clearing.
-        cuda_ok(cudaMemsetAsync(s.counters, 0, kStaticCounterBytes, cs), "static scratch counter reset");
         st.launch = launch_gemv(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, out_fp32, s,
                                 info.sms, cs) + " static-scratch";
     });

@@ -142,8 +142,8 @@ __device__ __forceinline__ __half silu_mul_one(__half g, __half u, float limit)
 __global__ void __launch_bounds__(256) k_silu_mul(const __half2* gate, const __half2* up,
                                                   __half2* out, long long pairs, float limit)
 {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     for (long long i = (long long) blockIdx.x * 256 + threadIdx.x; i < pairs; i += (long long) gridDim.x * 256) {
         __half2 g = gate[i], u = up[i];
         out[i] = __halves2half2(silu_mul_one(__low2half(g), __low2half(u), limit),
@@ -153,8 +153,8 @@ __global__ void __launch_bounds__(256) k_silu_mul(const __half2* gate, const __h
 
 __global__ void __launch_bounds__(256) k_add_f32(const float* a, const float* b, float* c, int n)
 {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     int i = blockIdx.x * 256 + threadIdx.x;
     if (i < n) c[i] = __fadd_rn(a[i], b[i]);
 }

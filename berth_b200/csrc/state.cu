@@ -57,9 +57,8 @@ GemvScratch gemv_workspace(int device)
     if (device < 0 || device >= kMaxDevices) throw std::runtime_error("device index out of range");
     GemvScratch& w = g_ws[device];
     if (!w.slabs) {
-        const size_t counters = size_t(kGemvCounterSlots) * sizeof(unsigned);
         const size_t blocksum = kGemvBlocksumFloats * sizeof(float);
-        const size_t total = kGemvSlabBytes + kGemvAfragBytes + counters + blocksum + 256;
+        const size_t total = kGemvSlabBytes + kGemvAfragBytes + blocksum + 256;
         void* p = nullptr;
         cuda_ok(cudaMalloc(&p, total), "gemv workspace");
         cuda_ok(cudaMemset(p, 0, total), "gemv workspace memset");
@@ -70,9 +69,6 @@ GemvScratch gemv_workspace(int device)
         w.afrag = reinterpret_cast<uint32_t*>(b);
         w.afrag_bytes = kGemvAfragBytes;
         b += kGemvAfragBytes;
-        w.counters = reinterpret_cast<unsigned*>(b);
-        w.counter_slots = kGemvCounterSlots;
-        b += counters;
         w.blocksum = reinterpret_cast<float*>(b);
         w.blocksum_floats = kGemvBlocksumFloats;
         b += blocksum;
