@@ -149,7 +149,8 @@ class DecodeStack:
         self.h_o = torch.empty((m, HIDDEN), dtype=f32).pin_memory()
         self.h2d_bytes = 2 * m * (HIDDEN + HIDDEN + QDIM)
         self.d2h_bytes = m * (4 * HIDDEN + 2 * QDIM + 4 * KVDIM + 4 * HIDDEN)
-        self.launches_per_step = 22   # 7 x (k_rotate_in + k_exl3_gemv + k_gemv_finish) + 1 x k_silu_mul
+        # 7 x (k_exl3_gemv + k_gemv_finish) + k_silu_mul; above two rows every linear also launches k_rotate_in
+        self.launches_per_step = 15 if m <= 2 else 22
 
     def step(self, i: int) -> None:
         from berth_b200.kernels import OutDtype
@@ -249,7 +250,7 @@ def bench_prefill(rank: int, reps: int = 5) -> dict:
 MOE = dict(hidden=2048, inter=512, n_experts=256, top_k=8, shared_inter=512)
 
 
-def bench_moe(rank: int, world: int, steps: int = 20) -> dict:
+def bench_moe(rank: int, world: int, steps: int = 20, tokens=(1, 64, 1024)) -> dict:
     """A3B MoE layer (256 experts + shared, top-8, 4 bpw) at 1, 64 and 1024 tokens in total.  One GPU: the
     fused berth_moe_layer.  N GPUs: experts sharded in blocks of 256/N, tokens split evenly, two NCCL
     all-to-alls per layer (expert parallelism); time = max over ranks."""
@@ -280,7 +281,7 @@ def bench_moe(rank: int, world: int, steps: int = 20) -> dict:
     else:
         stages = moe.GpuStages(dev, w, E, max_rows=1024 * K, max_rows_per_expert=1024)
         layer = moe.EpMoeLayer(stages, dist.group.WORLD, E, K)
-    for T in (1, 64, 1024):
+    for T in tokens:
         t_loc = T // world if T >= world else (1 if rank < T else 0)    # tokens of this rank
         x = torch.from_numpy(synth.activations(1234, f"c3.x{T}.r{rank}", max(t_loc, 1), H)).to(dev)[:t_loc]
         if world == 1:
@@ -369,6 +370,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill (configuration 2) and MoE (configuration 3) measurements")
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "moe"],
+                    help="run one of the extra measurements alone and print its record (for profiling; not the contract line)")
+    ap.add_argument("--moe-tokens", type=int, nargs="*", default=[1, 64, 1024], help="token counts of the MoE measurement")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 10:
@@ -388,6 +392,14 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     warmup = max(args.warmup, 3)
+    if args.only != "all":
+        rec = bench_prefill(rank, reps=max(1, min(args.steps, 5))) if args.only == "prefill" \
+            else bench_moe(rank, world, steps=args.steps, tokens=tuple(args.moe_tokens))
+        if rank == 0:
+            print(json.dumps(rec))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     stack = DecodeStack(args.m, rank)
 

@@ -22,7 +22,7 @@
 // takes the contiguous unit range [c*U/G, (c+1)*U/G), so every SM streams the same number of
 // bytes with no tail wave.  A range covers at most one partial band group at its head and one
 // at its tail; their partial sums go to slabs (2 per CTA) which k_gemv_finish, one warp per
-// (band, row), sums in CTA order -- deterministic, nothing ever waits on a peer, and the loads
+// (straddled band, row), sums in CTA order -- deterministic, nothing ever waits on a peer, and the loads
 // of that sum are spread over the whole GPU instead of trailing behind the last CTA to arrive.
 //
 // Inside a CTA (21 warps, one CTA per SM):
@@ -58,6 +58,7 @@ constexpr int kProducerWarp = kConsumerWarps;
 constexpr int kThreads = (kConsumerWarps + 1 + kEpiWarps) * 32;
 constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kRingBytes = 96 * 1024;
+constexpr int kFusedUnits = 26;   // most units per CTA for which the rotated activations fit in shared memory
 
 enum StatusBits : unsigned { kStFullTimeout = 1u, kStEmptyTimeout = 2u };
 
@@ -80,12 +81,18 @@ struct Geo {
     static constexpr int PITCH = BU * 128 + 4;                // floats per token row in shared slabs
     static constexpr int RED_SLAB = TOK * PITCH;
     static constexpr size_t SMEM = size_t(kRingBytes) + size_t(2 * RW + 1) * RED_SLAB * 4 + size_t(2 * S) * 8;
+    // in-kernel rotation (TG == 1): the CTA's own rotated activations, one 2 KiB block per unit
+    static constexpr size_t SMEM_FUSED = SMEM + size_t(kFusedUnits) * ACT_BYTES;
+    static_assert(TG != 1 || SMEM_FUSED <= 227 * 1024, "shared memory of the in-kernel rotation variant");
     static_assert(S >= 2 && RW >= 1 && RW * RPW == 8 && CG * RW == kConsumerWarps, "geometry");
 };
 
 struct GemvArgs {
     const uint32_t* afrag;    // rotated activations in MMA fragment order [problem][k/16][TG][2][8][4] words
-    const float* blocksum;    // [problem][8*TG or m][k/128]: sum of each rotated 128-block (MUL1 epilogue)
+    float* blocksum;          // [problem][8*TG or m][k/128]: sum of each rotated 128-block (MUL1 epilogue)
+    const __half* a;          // in-kernel rotation only: activations [m][k], input sign-scale [k], and the
+    const __half* suh;        //   caller's buffer for the rotated activations [m][k]
+    __half* a_had;
     void* c;                  // output rows [rows][n]
     const __half* svh;        // [n], or the stack [experts][n] when grouped
     const GemvProblem* problems;   // grouped launch: one entry per (expert, chunk of <= 8*TG rows); else null
@@ -188,6 +195,10 @@ __device__ __forceinline__ void handover_signal(int id)
 __device__ __forceinline__ void handover_wait(int id)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(kHandoverThreads) : "memory");
+}
+__device__ __forceinline__ void consumer_sync()
+{
+    asm volatile("bar.sync 6, %0;" ::"n"(kConsumerWarps * 32) : "memory");
 }
 __device__ __forceinline__ void grid_dependency_wait() { pdl_wait(); }
 __device__ __forceinline__ void grid_launch_dependents() { pdl_trigger(); }
@@ -297,6 +308,38 @@ __device__ __forceinline__ void tile_mma(const uint32_t (&s)[8], float (&acc)[TG
     }
 }
 
+// One 128-block of one activation row, whole warp: fp16(H128(x * suh) / sqrt(128)); the lane gets
+// elements 4*lane .. 4*lane+3 packed as two half pairs.  SUM: `sx` = sum of the 128 rounded values
+// (every lane), which the MUL1 epilogue needs.
+template <bool SUM>
+__device__ __forceinline__ uint2 rotate_block(const __half* __restrict__ xrow, const __half* __restrict__ suh, int kb, int lane, float& sx)
+{
+    const int kcol = kb * 128 + lane * 4;
+    uint2 xr = *reinterpret_cast<const uint2*>(xrow + kcol);
+    uint2 sr = *reinterpret_cast<const uint2*>(suh + kcol);
+    __half2 x0 = *reinterpret_cast<__half2*>(&xr.x), x1 = *reinterpret_cast<__half2*>(&xr.y);
+    __half2 s0 = *reinterpret_cast<__half2*>(&sr.x), s1 = *reinterpret_cast<__half2*>(&sr.y);
+    float v[4];
+    v[0] = __fmul_rn(__low2float(x0), __low2float(s0));
+    v[1] = __fmul_rn(__high2float(x0), __high2float(s0));
+    v[2] = __fmul_rn(__low2float(x1), __low2float(s1));
+    v[3] = __fmul_rn(__high2float(x1), __high2float(s1));
+    dq::had128_warp(v, lane);
+    __half h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __float2half_rn(__fmul_rn(v[i], kRScale));
+    uint2 o;
+    o.x = dq::pack_half2(h[0], h[1]);
+    o.y = dq::pack_half2(h[2], h[3]);
+    sx = 0.f;
+    if constexpr (SUM) {
+        sx = __fadd_rn(__fadd_rn(__half2float(h[0]), __half2float(h[1])), __fadd_rn(__half2float(h[2]), __half2float(h[3])));
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) sx = __fadd_rn(sx, __shfl_xor_sync(dq::kFull, sx, off));
+    }
+    return o;
+}
+
 // Sum over a row's block sums (the MUL1 epilogue's sum of the rotated activations), whole warp.
 __device__ __forceinline__ float row_sum(const float* bsum, int kblocks, int lane)
 {
@@ -310,11 +353,10 @@ __device__ __forceinline__ float row_sum(const float* bsum, int kblocks, int lan
 // Last steps of one output band of one row: v = the lane's four fp32 dot products (columns
 // band*128 + 4*lane ..).  MUL1: w = S*h + B per weight  =>  sum_k x_k w_k = S*acc + B*sum_k x_k.
 template <bool MUL1>
-__device__ __forceinline__ void finish_band(float (&v)[4], float sx, int lane, const __half* svh, int band, void* c,
+__device__ __forceinline__ void finish_band(float (&v)[4], float sx, int lane, uint2 sr, int band, void* c,
                                             size_t out_row, int n, int out_fp32)
 {
     const int col = band * 128 + lane * 4;
-    const uint2 sr = __ldg(reinterpret_cast<const uint2*>(svh + col));
     if constexpr (MUL1) {
         const float S1 = __half2float(__ushort_as_half(dq::kMul1S));
         const float bsx = __fmul_rn(__half2float(__ushort_as_half(dq::kMul1B)), sx);
@@ -357,9 +399,15 @@ __device__ __forceinline__ Segment segment_at(long long u, long long u0, long lo
 }
 
 // ---------------------------------------------------------------- the kernel
-template <int BITS, int CB, int TG>
+// FUSED (TG == 1, dense launches whose CTAs take at most kFusedUnits units and never a whole band
+// group): no rotation kernel runs before this one; the streaming warps rotate the 128-blocks of the
+// CTA's own units into shared memory while the first weight stages are in flight, and the CTAs
+// that hold band group 0 also write the rotated activations and their block sums for the caller
+// and the finishing kernel.
+template <int BITS, int CB, int TG, bool FUSED>
 __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant__ CUtensorMap tmap, const GemvArgs p)
 {
+    static_assert(!FUSED || TG == 1, "in-kernel rotation is built for one token group");
     using G_ = Geo<BITS, TG>;
     constexpr int NW = G_::NW, BU = G_::BU, ROW_BYTES = G_::ROW_BYTES, W_BYTES = G_::W_BYTES, ACT_BYTES = G_::ACT_BYTES;
     constexpr int STAGE_BYTES = G_::STAGE_BYTES, S = G_::S;
@@ -371,6 +419,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
     float* red = reinterpret_cast<float*>(smem + kRingBytes);                 // [2][RW][TOK][PITCH]
     float* outbuf = red + 2 * RW * RED_SLAB;                                  // [TOK][PITCH]
     uint64_t* bars = reinterpret_cast<uint64_t*>(outbuf + RED_SLAB);
+    uint32_t* actbuf = reinterpret_cast<uint32_t*>(smem + G_::SMEM);          // FUSED: [kFusedUnits][ACT_BYTES / 4]
 
     // Let the next kernel on the stream (normally the next linear's rotation) become resident now; it
     // waits for this grid's completion before it touches memory.
@@ -423,19 +472,22 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
             const int pre = nunits < S ? nunits : S;
             // (a grouped launch's problem table was written before the rotation kernel started, so it
             // is already visible here)
+            constexpr uint32_t kStageTx = FUSED ? W_BYTES : STAGE_BYTES;
             for (int i = 0; i < pre; ++i) {
-                mbar_arrive_expect_tx(full0 + 8 * i, STAGE_BYTES);
+                mbar_arrive_expect_tx(full0 + 8 * i, kStageTx);
                 issue_weights(i, smem_u32(ring + i * STAGE_BYTES), full0 + 8 * i);
             }
-            grid_dependency_wait();
-            for (int i = 0; i < pre; ++i) issue_acts(i, smem_u32(ring + i * STAGE_BYTES + W_BYTES), full0 + 8 * i);
+            if constexpr (!FUSED) {
+                grid_dependency_wait();
+                for (int i = 0; i < pre; ++i) issue_acts(i, smem_u32(ring + i * STAGE_BYTES + W_BYTES), full0 + 8 * i);
+            }
             int s = 0, lap = 1;
             for (int i = pre; i < nunits; ++i) {
                 mbar_wait_parked(empty0 + 8 * s, (lap - 1) & 1, p.status, kStEmptyTimeout);
-                mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                mbar_arrive_expect_tx(full0 + 8 * s, kStageTx);
                 const uint32_t dst = smem_u32(ring + s * STAGE_BYTES);
                 issue_weights(i, dst, full0 + 8 * s);
-                issue_acts(i, dst + W_BYTES, full0 + 8 * s);
+                if constexpr (!FUSED) issue_acts(i, dst + W_BYTES, full0 + 8 * s);
                 if (++s == S) { s = 0; ++lap; }
             }
         }
@@ -446,7 +498,27 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
         // ------------------------------------------------------------ consumers
         const int cg = warp % CG, rs = warp / CG;
         const int g = lane >> 2, q = lane & 3, lane1 = (lane + 1) & 31;
-        int s = 0, phase = 0, flush = 0;
+        if constexpr (FUSED) {
+            grid_dependency_wait();   // the activations come from the preceding kernels
+            for (int i = threadIdx.x; i < nunits * (ACT_BYTES / 4); i += kConsumerWarps * 32) actbuf[i] = 0u;   // rows >= m stay zero
+            consumer_sync();
+            const int ntask = nunits * p.m;
+            for (int task = warp; task < ntask; task += kConsumerWarps) {
+                const int i = task / p.m, t = task - i * p.m;
+                const long long uu = u0 + i;
+                const int gbg = int(uu / kblocks), kb = int(uu - (long long) gbg * kblocks);
+                float sx;
+                const uint2 o = rotate_block<CB == 2>(p.a + size_t(t) * p.k, p.suh, kb, lane, sx);
+                // lane holds k_in = 4*(lane&3) .. +3 of k-tile (lane/4) of the block: half h = k_in/8, pair index (k_in%8)/2
+                *reinterpret_cast<uint2*>(actbuf + i * (ACT_BYTES / 4) + ((lane >> 2) * 2 + ((lane & 3) >> 1)) * 32 + t * 4 + 2 * (lane & 1)) = o;
+                if (gbg == 0) {   // band group 0 meets every 128-block exactly once
+                    *reinterpret_cast<uint2*>(p.a_had + size_t(t) * p.k + kb * 128 + lane * 4) = o;
+                    if (CB == 2 && lane == 0) p.blocksum[t * kblocks + kb] = sx;
+                }
+            }
+            consumer_sync();
+        }
+        int s = 0, phase = 0, flush = 0, ui = 0;
         long long u = u0;
         while (u < u1) {
             const Segment sg = segment_at(u, u0, u1, kblocks);
@@ -459,7 +531,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
             for (int j = 0; j < sg.units; ++j) {
                 mbar_wait(full0 + 8 * s, phase, p.status, kStFullTimeout);
                 const uint32_t* stage = reinterpret_cast<const uint32_t*>(ring + s * STAGE_BYTES) + cg * NT * NW;
-                const uint32_t* act = reinterpret_cast<const uint32_t*>(ring + s * STAGE_BYTES + W_BYTES);
+                const uint32_t* act = FUSED ? actbuf + ui * (ACT_BYTES / 4)
+                                            : reinterpret_cast<const uint32_t*>(ring + s * STAGE_BYTES + W_BYTES);
+                ++ui;
 #pragma unroll
                 for (int i = 0; i < RPW; ++i) {
                     RowFrag<CB, TG> f;
@@ -519,6 +593,25 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
                 rows = pr.rows; row0 = pr.row0; z = pr.z;
             }
             const int buf = flush & 1;
+            // A whole band group is finished here: fetch what that needs (the row sums of the rotated
+            // activations, the output scales) while the streaming warps are still busy with the segment.
+            constexpr int kRowsPerWarp = TOK / kEpiWarps;
+            float sxr[kRowsPerWarp];
+            uint2 svr[BU];
+            if (sg.whole) {
+                const float* bsum = p.blocksum + size_t(pi) * slab_rows * kblocks;
+#pragma unroll
+                for (int r = 0; r < kRowsPerWarp; ++r) {
+                    const int row = ew + r * kEpiWarps;
+                    sxr[r] = (CB == 2 && row < rows) ? row_sum(bsum + size_t(row) * kblocks, kblocks, lane) : 0.f;
+                }
+#pragma unroll
+                for (int b = 0; b < BU; ++b) {
+                    const int band = lbg * BU + b;
+                    svr[b] = band < bands ? __ldg(reinterpret_cast<const uint2*>(p.svh + size_t(z) * p.n + band * 128 + lane * 4))
+                                          : make_uint2(0u, 0u);
+                }
+            }
             handover_wait(2 + buf);
             // fixed-order reduction over the row streams: thread et owns column et of every band
             float* dst = sg.whole ? outbuf : p.slabs + size_t(sg.head ? 2 * cta : 2 * cta + 1) * slab_floats;
@@ -536,16 +629,19 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
             handover_signal(4 + buf);   // the streaming warps may refill this buffer
             if (sg.whole) {
                 epi_sync();   // outbuf complete
-                const __half* svh = p.svh + size_t(z) * p.n;
-                const float* bsum = p.blocksum + size_t(pi) * slab_rows * kblocks;
-                for (int row = ew; row < rows; row += kEpiWarps) {
-                    const float sx = (CB == 2) ? row_sum(bsum + size_t(row) * kblocks, kblocks, lane) : 0.f;
-                    for (int b = 0; b < BU; ++b) {
-                        const int band = lbg * BU + b;
-                        if (band >= bands) break;   // ragged last band group
-                        float4 t = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
-                        float v[4] = {t.x, t.y, t.z, t.w};
-                        finish_band<CB == 2>(v, sx, lane, svh, band, p.c, size_t(row0 + row), p.n, p.out_fp32);
+#pragma unroll
+                for (int r = 0; r < kRowsPerWarp; ++r) {
+                    const int row = ew + r * kEpiWarps;
+                    if (row < rows) {
+#pragma unroll
+                        for (int b = 0; b < BU; ++b) {
+                            const int band = lbg * BU + b;
+                            if (band < bands) {   // ragged last band group
+                                float4 t = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
+                                float v[4] = {t.x, t.y, t.z, t.w};
+                                finish_band<CB == 2>(v, sxr[r], lane, svr[b], band, p.c, size_t(row0 + row), p.n, p.out_fp32);
+                            }
+                        }
                     }
                 }
                 epi_sync();   // outbuf is free again
@@ -556,10 +652,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
     }
 }
 
-// Finishing kernel of the decode GEMV: one warp per (band group, band, row) sums that row's
-// split-K slabs in CTA order (eight independent loads in flight), applies the MUL1 affine
-// correction, the 128-wide Hadamard and the output scale, and stores.  Band groups whose whole K
-// sat in one CTA were finished by the decode kernel itself and are skipped.
+// Finishing kernel of the decode GEMV.  A band group whose K was split over several CTAs straddles
+// at least one boundary between consecutive CTA ranges, so the grid is (boundary, chunk of eight
+// (band, row) tasks): the block of the first boundary inside a band group takes that band group, one
+// warp per task sums the row's split-K slabs in CTA order (eight independent loads in flight),
+// applies the MUL1 affine correction, the 128-wide Hadamard and the output scale, and stores.  Band
+// groups whose whole K sat in one CTA straddle no boundary; the decode kernel finished those.
 struct FinishArgs {
     const float* slabs;
     const float* blocksum;
@@ -582,52 +680,55 @@ __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
     const int nprob = grouped ? min(max(__ldg(p.n_problems), 0), p.max_problems) : 1;
     const long long U = (long long) nprob * bgroups * kblocks;
     const int G = U < (long long) p.main_grid ? int(U) : p.main_grid;
+    const int c = blockIdx.x + 1;                      // the boundary between the ranges of CTA c-1 and CTA c
+    if (c >= G) return;
+    const long long ub = unit_begin(c, U, G);
+    const int gbg = int(ub / kblocks);
+    const long long g0 = (long long) gbg * kblocks;    // first unit of the band group around the boundary
+    if (ub == g0) return;                              // the boundary is a band-group start: nothing straddles it
+    if (unit_begin(c - 1, U, G) > g0) return;          // an earlier boundary lies inside the same band group
     const int slab_rows = grouped ? p.tok : p.m;
-    const size_t slab_floats = size_t(slab_rows) * bu * 128;
-    const long long total = (long long) nprob * bgroups * bu * slab_rows;
-    for (long long task = (long long) blockIdx.x * 8 + (threadIdx.x >> 5); task < total; task += (long long) gridDim.x * 8) {
-        const int row = int(task % slab_rows);
-        const int b = int((task / slab_rows) % bu);
-        const int gbg = int(task / ((long long) slab_rows * bu));
-        const int pi = gbg / bgroups, lbg = gbg - pi * bgroups, band = lbg * bu + b;
-        if (band >= bands) continue;   // ragged last band group
-        int rows = p.m, row0 = 0, z = 0;
-        if (grouped) {
-            const GemvProblem pr = load_problem(p.problems, pi, p.n_matrices, p.tok, p.max_rows);
-            rows = pr.rows; row0 = pr.row0; z = pr.z;
-        }
-        if (row >= rows) continue;
-        const int first_cta = unit_owner((long long) gbg * kblocks, U, G);
-        const int last_cta = unit_owner((long long) (gbg + 1) * kblocks - 1, U, G);
-        if (first_cta == last_cta) continue;   // one CTA held the whole K and finished the band itself
-        // slabs of this band group, in CTA order: the first CTA's tail (or head, if its range starts
-        // exactly here), then the heads of the following CTAs
-        const int first_slab = (unit_begin(first_cta, U, G) >= (long long) gbg * kblocks) ? 2 * first_cta : 2 * first_cta + 1;
-        const int nsl = last_cta - first_cta + 1;
-        const float sx = p.mul1 ? row_sum(p.blocksum + (size_t(pi) * slab_rows + row) * kblocks, kblocks, lane) : 0.f;
-        const float* base = p.slabs + (size_t(row) * bu + b) * 128 + lane * 4;
-        float v[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int i0 = 0; i0 < nsl; i0 += 8) {
-            float4 t[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int si = i0 + i;
-                const int slab = si == 0 ? first_slab : 2 * (first_cta + si);
-                t[i] = si < nsl ? __ldcg(reinterpret_cast<const float4*>(base + size_t(slab) * slab_floats))
-                                : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                if (i0 + i < nsl) {
-                    v[0] = __fadd_rn(v[0], t[i].x); v[1] = __fadd_rn(v[1], t[i].y);
-                    v[2] = __fadd_rn(v[2], t[i].z); v[3] = __fadd_rn(v[3], t[i].w);
-                }
-            }
-        }
-        const __half* svh = p.svh + size_t(z) * p.n;
-        if (p.mul1) finish_band<true>(v, sx, lane, svh, band, p.c, size_t(row0 + row), p.n, p.out_fp32);
-        else finish_band<false>(v, sx, lane, svh, band, p.c, size_t(row0 + row), p.n, p.out_fp32);
+    const int task = blockIdx.y * 8 + (threadIdx.x >> 5);
+    if (task >= bu * slab_rows) return;
+    const int b = task / slab_rows, row = task - b * slab_rows;
+    const int pi = gbg / bgroups, lbg = gbg - pi * bgroups, band = lbg * bu + b;
+    if (band >= bands) return;   // ragged last band group
+    int rows = p.m, row0 = 0, z = 0;
+    if (grouped) {
+        const GemvProblem pr = load_problem(p.problems, pi, p.n_matrices, p.tok, p.max_rows);
+        rows = pr.rows; row0 = pr.row0; z = pr.z;
     }
+    if (row >= rows) return;
+    // slabs of this band group, in CTA order: the first CTA's tail (or head, if its range starts
+    // exactly here), then the heads of the following CTAs
+    const int first_cta = c - 1;
+    const int last_cta = unit_owner(g0 + kblocks - 1, U, G);
+    const int first_slab = (unit_begin(first_cta, U, G) >= g0) ? 2 * first_cta : 2 * first_cta + 1;
+    const int nsl = last_cta - first_cta + 1;
+    const size_t slab_floats = size_t(slab_rows) * bu * 128;
+    const uint2 sr = __ldg(reinterpret_cast<const uint2*>(p.svh + size_t(z) * p.n + band * 128 + lane * 4));
+    const float sx = p.mul1 ? row_sum(p.blocksum + (size_t(pi) * slab_rows + row) * kblocks, kblocks, lane) : 0.f;
+    const float* base = p.slabs + (size_t(row) * bu + b) * 128 + lane * 4;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i0 = 0; i0 < nsl; i0 += 8) {
+        float4 t[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int si = i0 + i;
+            const int slab = si == 0 ? first_slab : 2 * (first_cta + si);
+            t[i] = si < nsl ? __ldcg(reinterpret_cast<const float4*>(base + size_t(slab) * slab_floats))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (i0 + i < nsl) {
+                v[0] = __fadd_rn(v[0], t[i].x); v[1] = __fadd_rn(v[1], t[i].y);
+                v[2] = __fadd_rn(v[2], t[i].z); v[3] = __fadd_rn(v[3], t[i].w);
+            }
+        }
+    }
+    if (p.mul1) finish_band<true>(v, sx, lane, sr, band, p.c, size_t(row0 + row), p.n, p.out_fp32);
+    else finish_band<false>(v, sx, lane, sr, band, p.c, size_t(row0 + row), p.n, p.out_fp32);
 }
 
 // ---------------------------------------------------------------- rotation of the activations
@@ -649,28 +750,11 @@ __global__ void __launch_bounds__(128) k_rotate_in(const __half* __restrict__ a,
     const int total = rows_pad * kblocks;
     for (int idx = blockIdx.x * 4 + (threadIdx.x >> 5); idx < total; idx += gridDim.x * 4) {
         const int row = idx / kblocks, b = idx - row * kblocks;
-        const int kcol = b * 128 + lane * 4;
         uint2 o = make_uint2(0u, 0u);
         if (row < rows) {
-            uint2 xr = *reinterpret_cast<const uint2*>(a + size_t(row) * k + kcol);
-            uint2 sr = *reinterpret_cast<const uint2*>(suh + kcol);
-            __half2 x0 = *reinterpret_cast<__half2*>(&xr.x), x1 = *reinterpret_cast<__half2*>(&xr.y);
-            __half2 s0 = *reinterpret_cast<__half2*>(&sr.x), s1 = *reinterpret_cast<__half2*>(&sr.y);
-            float v[4];
-            v[0] = __fmul_rn(__low2float(x0), __low2float(s0));
-            v[1] = __fmul_rn(__high2float(x0), __high2float(s0));
-            v[2] = __fmul_rn(__low2float(x1), __low2float(s1));
-            v[3] = __fmul_rn(__high2float(x1), __high2float(s1));
-            dq::had128_warp(v, lane);
-            __half h[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) h[i] = __float2half_rn(__fmul_rn(v[i], kRScale));
-            o.x = dq::pack_half2(h[0], h[1]);
-            o.y = dq::pack_half2(h[2], h[3]);
-            *reinterpret_cast<uint2*>(a_had + size_t(row) * k + kcol) = o;
-            float sx = __fadd_rn(__fadd_rn(__half2float(h[0]), __half2float(h[1])), __fadd_rn(__half2float(h[2]), __half2float(h[3])));
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) sx = __fadd_rn(sx, __shfl_xor_sync(dq::kFull, sx, off));
+            float sx;
+            o = rotate_block<true>(a + size_t(row) * k, suh, b, lane, sx);
+            *reinterpret_cast<uint2*>(a_had + size_t(row) * k + b * 128 + lane * 4) = o;
             if (lane == 0) blocksum[row * kblocks + b] = sx;
         }
         // lane holds k_in = 4*(lane&3) .. +3 of k-tile (8*b + lane/4): half h = k_in/8, pair index q = (k_in%8)/2
@@ -715,22 +799,23 @@ CUtensorMap trellis_map(const void* trellis, int n_matrices, int size_k, int siz
     return map;
 }
 
-template <int BITS, int CB, int TG>
+template <int BITS, int CB, int TG, bool FUSED>
 size_t launch_one(const void* trellis, int n_matrices, const GemvArgs& args, int grid, cudaStream_t stream)
 {
     using G_ = Geo<BITS, TG>;
-    auto kern = k_exl3_gemv<BITS, CB, TG>;
+    auto kern = k_exl3_gemv<BITS, CB, TG, FUSED>;
+    constexpr size_t kSmem = FUSED ? G_::SMEM_FUSED : G_::SMEM;
     static bool attr_set[kMaxDevices] = {};
     const int dev = current_device();
     if (!attr_set[dev]) {
-        cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(G_::SMEM)), "gemv smem attribute");
+        cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmem)), "gemv smem attribute");
         attr_set[dev] = true;
     }
     const CUtensorMap map = trellis_map(trellis, n_matrices, args.k, args.n, BITS, G_::ROW_BYTES);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = G_::SMEM;
+    cfg.dynamicSmemBytes = kSmem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -738,100 +823,86 @@ size_t launch_one(const void* trellis, int n_matrices, const GemvArgs& args, int
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cuda_ok(cudaLaunchKernelEx(&cfg, kern, map, args), "k_exl3_gemv launch");
-    return G_::SMEM;
+    return kSmem;
 }
 
 template <int BITS, int CB>
-size_t launch_tg(int tg, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
+size_t launch_tg(int tg, bool fused, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
 {
     switch (tg) {
-        case 1: return launch_one<BITS, CB, 1>(t, nm, a, grid, st);
-        case 2: return launch_one<BITS, CB, 2>(t, nm, a, grid, st);
-        default: return launch_one<BITS, CB, 4>(t, nm, a, grid, st);
+        case 1: return fused ? launch_one<BITS, CB, 1, true>(t, nm, a, grid, st) : launch_one<BITS, CB, 1, false>(t, nm, a, grid, st);
+        case 2: return launch_one<BITS, CB, 2, false>(t, nm, a, grid, st);
+        default: return launch_one<BITS, CB, 4, false>(t, nm, a, grid, st);
     }
 }
 
 template <int BITS>
-size_t launch_cb(int cb, int tg, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
+size_t launch_cb(int cb, int tg, bool fused, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
 {
     switch (cb) {
-        case 0: return launch_tg<BITS, 0>(tg, t, nm, a, grid, st);
-        case 1: return launch_tg<BITS, 1>(tg, t, nm, a, grid, st);
-        default: return launch_tg<BITS, 2>(tg, t, nm, a, grid, st);
+        case 0: return launch_tg<BITS, 0>(tg, fused, t, nm, a, grid, st);
+        case 1: return launch_tg<BITS, 1>(tg, fused, t, nm, a, grid, st);
+        default: return launch_tg<BITS, 2>(tg, fused, t, nm, a, grid, st);
     }
 }
 
-size_t launch_bits(int k_bits, int cb, int tg, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
+size_t launch_bits(int k_bits, int cb, int tg, bool fused, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
 {
     switch (k_bits) {
-        case 1: return launch_cb<1>(cb, tg, t, nm, a, grid, st);
-        case 2: return launch_cb<2>(cb, tg, t, nm, a, grid, st);
-        case 3: return launch_cb<3>(cb, tg, t, nm, a, grid, st);
-        case 4: return launch_cb<4>(cb, tg, t, nm, a, grid, st);
-        case 5: return launch_cb<5>(cb, tg, t, nm, a, grid, st);
-        case 6: return launch_cb<6>(cb, tg, t, nm, a, grid, st);
-        case 7: return launch_cb<7>(cb, tg, t, nm, a, grid, st);
-        case 8: return launch_cb<8>(cb, tg, t, nm, a, grid, st);
+        case 1: return launch_cb<1>(cb, tg, fused, t, nm, a, grid, st);
+        case 2: return launch_cb<2>(cb, tg, fused, t, nm, a, grid, st);
+        case 3: return launch_cb<3>(cb, tg, fused, t, nm, a, grid, st);
+        case 4: return launch_cb<4>(cb, tg, fused, t, nm, a, grid, st);
+        case 5: return launch_cb<5>(cb, tg, fused, t, nm, a, grid, st);
+        case 6: return launch_cb<6>(cb, tg, fused, t, nm, a, grid, st);
+        case 7: return launch_cb<7>(cb, tg, fused, t, nm, a, grid, st);
+        case 8: return launch_cb<8>(cb, tg, fused, t, nm, a, grid, st);
         default: throw std::runtime_error("exl3 linear: K must be in 1..=8");
     }
 }
 
-// Rotation for a grouped launch: routed rows xr [R][k], one warp per (problem, padded row, 128-block);
-// the row's expert picks the sign-scale vector.  Rows past a problem's count are written as zeros.
-__global__ void __launch_bounds__(128) k_rotate_rows(const __half* __restrict__ xr, const __half* __restrict__ suh_stack,
+// Rotation for a grouped launch: routed rows xr [R][k]; one block per problem, its warps share the
+// (row, 128-block) pairs of the problem's real rows; the row's expert picks the sign-scale vector.
+// Rows past the problem's count are left as they are: a token is a column of the MMA, so whatever
+// sits there reaches only accumulators that nobody stores.
+__global__ void __launch_bounds__(256) k_rotate_rows(const __half* __restrict__ xr, const __half* __restrict__ suh_stack,
                                                      const GemvProblem* __restrict__ problems, const int* __restrict__ n_problems,
                                                      uint32_t* __restrict__ afrag, float* __restrict__ blocksum, int tok, int k,
                                                      int max_problems, int n_matrices, int max_rows)
 {
     grid_dependency_wait();      // the problem table comes from the preceding kernel
     grid_launch_dependents();
-    const int lane = threadIdx.x & 31, kblocks = k >> 7, tgs = tok >> 3;
-    const long long total = (long long) min(max(__ldg(n_problems), 0), max_problems) * tok * kblocks;
-    for (long long idx = (long long) blockIdx.x * 4 + (threadIdx.x >> 5); idx < total; idx += (long long) gridDim.x * 4) {
-        const int b = int(idx % kblocks);
-        const int lr = int((idx / kblocks) % tok);
-        const int pi = int(idx / ((long long) kblocks * tok));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, kblocks = k >> 7, tgs = tok >> 3;
+    const int nprob = min(max(__ldg(n_problems), 0), max_problems);
+    for (int pi = blockIdx.x; pi < nprob; pi += gridDim.x) {
         const GemvProblem pr = load_problem(problems, pi, n_matrices, tok, max_rows);
-        const int kcol = b * 128 + lane * 4;
-        uint2 o = make_uint2(0u, 0u);
-        if (lr < pr.rows) {
-            uint2 xw = *reinterpret_cast<const uint2*>(xr + size_t(pr.row0 + lr) * k + kcol);
-            uint2 sr = *reinterpret_cast<const uint2*>(suh_stack + size_t(pr.z) * k + kcol);
-            __half2 x0 = *reinterpret_cast<__half2*>(&xw.x), x1 = *reinterpret_cast<__half2*>(&xw.y);
-            __half2 s0 = *reinterpret_cast<__half2*>(&sr.x), s1 = *reinterpret_cast<__half2*>(&sr.y);
-            float v[4];
-            v[0] = __fmul_rn(__low2float(x0), __low2float(s0));
-            v[1] = __fmul_rn(__high2float(x0), __high2float(s0));
-            v[2] = __fmul_rn(__low2float(x1), __low2float(s1));
-            v[3] = __fmul_rn(__high2float(x1), __high2float(s1));
-            dq::had128_warp(v, lane);
-            __half h[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) h[i] = __float2half_rn(__fmul_rn(v[i], kRScale));
-            o.x = dq::pack_half2(h[0], h[1]);
-            o.y = dq::pack_half2(h[2], h[3]);
-            float sx = __fadd_rn(__fadd_rn(__half2float(h[0]), __half2float(h[1])), __fadd_rn(__half2float(h[2]), __half2float(h[3])));
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) sx = __fadd_rn(sx, __shfl_xor_sync(dq::kFull, sx, off));
+        const __half* suh = suh_stack + size_t(pr.z) * k;
+        const int pairs = pr.rows * kblocks;
+#pragma unroll 4
+        for (int pair = warp; pair < pairs; pair += 8) {
+            const int lr = pair / kblocks, b = pair - lr * kblocks;
+            float sx;
+            const uint2 o = rotate_block<true>(xr + size_t(pr.row0 + lr) * k, suh, b, lane, sx);
             if (lane == 0) blocksum[(size_t(pi) * tok + lr) * kblocks + b] = sx;
+            const int ktile = b * 8 + (lane >> 2), hsel = (lane & 3) >> 1, q = 2 * (lane & 1);
+            const size_t w = (((size_t(pi) * (k >> 4) + ktile) * tgs + (lr >> 3)) * 2 + hsel) * 32 + (lr & 7) * 4 + q;
+            *reinterpret_cast<uint2*>(afrag + w) = o;
         }
-        const int ktile = b * 8 + (lane >> 2), hsel = (lane & 3) >> 1, q = 2 * (lane & 1);
-        const size_t w = (((size_t(pi) * (k >> 4) + ktile) * tgs + (lr >> 3)) * 2 + hsel) * 32 + (lr & 7) * 4 + q;
-        *reinterpret_cast<uint2*>(afrag + w) = o;
     }
 }
 
-// The finishing kernel behind a decode launch of `main_grid` CTAs; `warps` = (band, row) tasks at most.
-void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int codebook, long long warps, int sms, cudaStream_t stream)
+// The finishing kernel behind a decode launch of `main_grid` CTAs (nothing to do behind a single CTA).
+void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int codebook, cudaStream_t stream)
 {
+    if (main_grid < 2) return;
     FinishArgs f;
     f.slabs = a.slabs; f.blocksum = a.blocksum; f.c = a.c; f.svh = a.svh;
     f.problems = a.problems; f.n_problems = a.n_problems;
     f.max_problems = a.max_problems; f.n_matrices = a.n_matrices; f.max_rows = a.max_rows;
     f.m = a.m; f.k = a.k; f.n = a.n; f.out_fp32 = a.out_fp32;
     f.bu = bu; f.tok = tok; f.main_grid = main_grid; f.mul1 = codebook == 2;
-    const int grid = int(std::max<long long>(1, std::min<long long>((warps + 7) / 8, 8LL * sms)));
-    launch_pdl(k_gemv_finish, dim3(grid), dim3(256), 0, stream, "k_gemv_finish launch", f);
+    const int slab_rows = a.problems ? tok : a.m;
+    launch_pdl(k_gemv_finish, dim3(main_grid - 1, (bu * slab_rows + 7) / 8), dim3(256), 0, stream, "k_gemv_finish launch", f);
 }
 
 }  // namespace
@@ -863,14 +934,24 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     const size_t afrag_bytes = size_t(size_k / 16) * tg * 256;
     if (afrag_bytes > sc.afrag_bytes)
         throw std::runtime_error("exl3 gemv: size_k * ceil(size_m / 8) exceeds the activation-fragment area of the scratch");
-    const int rot_total = 8 * tg * kblocks;
-    launch_pdl(k_rotate_in, dim3(std::min((rot_total + 3) / 4, 4 * sms)), dim3(128), 0, stream, "k_rotate_in launch",
-               static_cast<const __half*>(a), static_cast<const __half*>(suh), static_cast<__half*>(a_had), sc.afrag, sc.blocksum,
-               size_m, 8 * tg, size_k);
+    // In-kernel rotation for one or two rows (with more, the per-CTA repetition of the rotation costs more
+    // than the separate kernel), when every CTA's units fit its shared-memory block and no CTA holds a
+    // whole band group.
+    const long long units_per_cta = (units + grid - 1) / grid;
+    const bool fused = size_m <= 2 && units_per_cta <= kFusedUnits && units_per_cta < kblocks;
+    if (!fused) {
+        const int rot_total = 8 * tg * kblocks;
+        launch_pdl(k_rotate_in, dim3(std::min((rot_total + 3) / 4, 4 * sms)), dim3(128), 0, stream, "k_rotate_in launch",
+                   static_cast<const __half*>(a), static_cast<const __half*>(suh), static_cast<__half*>(a_had), sc.afrag,
+                   sc.blocksum, size_m, 8 * tg, size_k);
+    }
 
     GemvArgs args;
     args.afrag = sc.afrag;
     args.blocksum = sc.blocksum;
+    args.a = static_cast<const __half*>(a);
+    args.suh = static_cast<const __half*>(suh);
+    args.a_had = static_cast<__half*>(a_had);
     args.c = c;
     args.svh = static_cast<const __half*>(svh);
     args.slabs = sc.slabs;
@@ -880,10 +961,10 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     args.problems = nullptr;
     args.n_problems = nullptr;
     args.max_problems = 1; args.n_matrices = 1; args.max_rows = size_m;
-    const size_t smem = launch_bits(k_bits, codebook, tg, trellis, 1, args, grid, stream);
-    launch_finish(args, bu, 8 * tg, grid, codebook, (long long) bgroups * bu * size_m, sms, stream);
-    return "k_rotate_in + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," + std::to_string(tg) +
-           "> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem) +
+    const size_t smem = launch_bits(k_bits, codebook, tg, fused, trellis, 1, args, grid, stream);
+    launch_finish(args, bu, 8 * tg, grid, codebook, stream);
+    return std::string(fused ? "" : "k_rotate_in + ") + "k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," +
+           std::to_string(tg) + (fused ? ",fused" : "") + "> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem) +
            " + k_gemv_finish";
 }
 
@@ -901,13 +982,13 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
     const size_t per_cta = size_t(2) * 8 * tg * bu * 128 * sizeof(float);
     if (size_t(grid) * per_cta > sc.slab_bytes) grid = int(sc.slab_bytes / per_cta);
     if (grid < 1) throw std::runtime_error("exl3 grouped gemv: split-K scratch is too small");
-    const long long warps = (long long) max_problems * 8 * tg * (size_k / 128);
-    launch_pdl(k_rotate_rows, dim3(int(std::min<long long>((warps + 3) / 4, 8LL * sms))), dim3(128), 0, stream, "k_rotate_rows launch",
+    launch_pdl(k_rotate_rows, dim3(std::max(1, std::min(max_problems, 16 * sms))), dim3(256), 0, stream, "k_rotate_rows launch",
                static_cast<const __half*>(xr), static_cast<const __half*>(suh_stack), problems, n_problems, afrag, blocksum,
                8 * tg, size_k, max_problems, n_experts, max_rows);
     GemvArgs args;
     args.afrag = afrag;
     args.blocksum = blocksum;
+    args.a = nullptr; args.suh = nullptr; args.a_had = nullptr;
     args.c = c;
     args.svh = static_cast<const __half*>(svh_stack);
     args.problems = problems;
@@ -919,8 +1000,8 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
     args.status = sc.status;
     args.m = 8 * tg; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
-    const size_t smem = launch_bits(k_bits, codebook, tg, trellis_stack, n_experts, args, grid, stream);
-    launch_finish(args, bu, 8 * tg, grid, codebook, (long long) max_problems * bgroups * bu * 8 * tg, sms, stream);
+    const size_t smem = launch_bits(k_bits, codebook, tg, false, trellis_stack, n_experts, args, grid, stream);
+    launch_finish(args, bu, 8 * tg, grid, codebook, stream);
     return "k_rotate_rows + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," + std::to_string(tg) +
            ",grouped> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem) +
            " + k_gemv_finish";

@@ -22,25 +22,51 @@ namespace {
 // compared bit for bit.  Block = 32 chunk-warps x 32 experts for kRouterTok tokens: warp j
 // accumulates chunk j with coalesced reads of the router rows (each row read once per token tile).
 constexpr int kRouterTok = 8;
+// Dynamic shared memory: the token tile as fp32 [kRouterTok][H], then the chunk sums [32][kRouterTok][33].
 __global__ void __launch_bounds__(1024) k_moe_router_logits(const __half* __restrict__ x, const __half* __restrict__ w,
                                                             const float* __restrict__ bias, float* __restrict__ logits,
                                                             int T, int H, int E)
 {
-    __shared__ float part[32][kRouterTok][33];
+    extern __shared__ __align__(16) float rsm[];
+    float* xs = rsm;                                                    // [kRouterTok][H]
+    float (*part)[kRouterTok][33] = reinterpret_cast<float (*)[kRouterTok][33]>(rsm + kRouterTok * H);
     const int j = threadIdx.x >> 5, el = threadIdx.x & 31;
     const int e = blockIdx.x * 32 + el, t0 = blockIdx.y * kRouterTok;
     const int chunk = H / 32;
+    // the tile's activations, converted once (rows past T repeat the last token; their sums are never stored)
+    for (int i = threadIdx.x * 2; i < kRouterTok * H; i += 2048) {
+        const int tt = i / H, h = i - tt * H;
+        const __half2 v = *reinterpret_cast<const __half2*>(x + size_t(min(t0 + tt, T - 1)) * H + h);
+        xs[i] = __low2float(v);
+        xs[i + 1] = __high2float(v);
+    }
+    __syncthreads();
     const __half* wr = w + size_t(j) * chunk * E + e;
+    const float* xj = xs + j * chunk;
     float acc[kRouterTok];
 #pragma unroll
     for (int tt = 0; tt < kRouterTok; ++tt) acc[tt] = 0.f;
-    for (int i = 0; i < chunk; ++i) {
-        const float wv = __half2float(wr[size_t(i) * E]);
+    // eight router rows in flight per pass; the products are still added one by one in k order
+    int i0 = 0;
+    const int vec_end = (chunk & 3) == 0 ? chunk : 0;   // quads are 16-byte aligned only if the chunk is a multiple of 4
+    for (; i0 + 8 <= vec_end; i0 += 8) {
+        float wv[8];
+#pragma unroll
+        for (int ii = 0; ii < 8; ++ii) wv[ii] = __half2float(wr[size_t(i0 + ii) * E]);
 #pragma unroll
         for (int tt = 0; tt < kRouterTok; ++tt) {
-            const int t = min(t0 + tt, T - 1);
-            acc[tt] = __fmaf_rn(__half2float(x[size_t(t) * H + j * chunk + i]), wv, acc[tt]);
+            const float4 a = *reinterpret_cast<const float4*>(xj + tt * H + i0);
+            const float4 b = *reinterpret_cast<const float4*>(xj + tt * H + i0 + 4);
+            acc[tt] = __fmaf_rn(a.x, wv[0], acc[tt]); acc[tt] = __fmaf_rn(a.y, wv[1], acc[tt]);
+            acc[tt] = __fmaf_rn(a.z, wv[2], acc[tt]); acc[tt] = __fmaf_rn(a.w, wv[3], acc[tt]);
+            acc[tt] = __fmaf_rn(b.x, wv[4], acc[tt]); acc[tt] = __fmaf_rn(b.y, wv[5], acc[tt]);
+            acc[tt] = __fmaf_rn(b.z, wv[6], acc[tt]); acc[tt] = __fmaf_rn(b.w, wv[7], acc[tt]);
         }
+    }
+    for (; i0 < chunk; ++i0) {   // the rest, or all of it for an odd chunk
+        const float wv = __half2float(wr[size_t(i0) * E]);
+#pragma unroll
+        for (int tt = 0; tt < kRouterTok; ++tt) acc[tt] = __fmaf_rn(xj[tt * H + i0], wv, acc[tt]);
     }
 #pragma unroll
     for (int tt = 0; tt < kRouterTok; ++tt) part[j][tt][el] = acc[tt];
@@ -239,6 +265,14 @@ inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
 int token_groups(int max_rows_per_expert) { return max_rows_per_expert <= 8 ? 1 : (max_rows_per_expert <= 16 ? 2 : 4); }
 
+// Token groups for T tokens routed top_k ways over n_experts: sized for twice the mean rows per expert
+// (an expert with more rows takes several chunks), never beyond what one expert can receive.
+int token_groups_routed(int T, int top_k, int n_experts)
+{
+    const long long twice_mean = (2LL * T * top_k + n_experts - 1) / n_experts;
+    return token_groups(int(std::min<long long>(T, std::max<long long>(twice_mean, 1))));
+}
+
 // Workspace carve-up of the expert stage for up to R routed rows.
 struct ExpertScratch {
     int* counts; int* offsets; int* n_problems; GemvProblem* problems;
@@ -286,8 +320,16 @@ void check_moe_shapes(const berth_moe_weights* w, int T)
 void router_topk(const void* x, const void* w_router, const float* bias, int32_t* topk_idx, float* topk_w, float* logits,
                  int T, int H, int E, int k, cudaStream_t st)
 {
-    k_moe_router_logits<<<dim3(E / 32, (T + kRouterTok - 1) / kRouterTok), 1024, 0, st>>>((const __half*) x, (const __half*) w_router,
-                                                                                        bias, logits, T, H, E);
+    const size_t smem = size_t(kRouterTok) * H * 4 + size_t(32) * kRouterTok * 33 * 4;
+    if (smem > 200 * 1024) throw std::runtime_error("moe router: hidden is too large for the router's shared-memory tile");
+    static bool attr_set[kMaxDevices] = {};
+    const int dev = current_device();
+    if (!attr_set[dev]) {
+        cuda_ok(cudaFuncSetAttribute(k_moe_router_logits, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "router smem attribute");
+        attr_set[dev] = true;
+    }
+    k_moe_router_logits<<<dim3(E / 32, (T + kRouterTok - 1) / kRouterTok), 1024, smem, st>>>((const __half*) x, (const __half*) w_router,
+                                                                                           bias, logits, T, H, E);
     cuda_ok(cudaGetLastError(), "k_moe_router_logits launch");
     k_moe_topk<<<(T + 3) / 4, 128, 0, st>>>(logits, topk_idx, topk_w, T, E, k);
     cuda_ok(cudaGetLastError(), "k_moe_topk launch");
@@ -434,7 +476,7 @@ extern "C" size_t berth_moe_workspace_bytes(int T, int hidden, int inter, int sh
 {
     if (T < 1 || hidden < 128 || inter < 128 || n_experts < 1 || top_k < 1) return 0;
     const int R = T * top_k;
-    const int tg = token_groups(T);
+    const int tg = token_groups_routed(T, top_k, n_experts);
     const ExpertScratch es = carve_experts(nullptr, R, n_experts, hidden, inter, tg);
     size_t total = 0;
     total += align256(size_t(T) * n_experts * 4);            // logits
@@ -468,7 +510,7 @@ extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T,
         GemvScratch sc = gemv_workspace(device);
         cudaStream_t cs = (cudaStream_t) stream;
         const int H = w->hidden, I = w->inter, E = w->n_experts, K = w->top_k, R = T * K, SI = w->shared_inter;
-        const int tg = token_groups(T);
+        const int tg = token_groups_routed(T, K, E);
 
         char* b = static_cast<char*>(workspace);
         b = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(b) + 255) & ~uintptr_t(255));
