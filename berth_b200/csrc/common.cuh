@@ -112,6 +112,27 @@ struct GemvProblem {
     int z, row0, rows, pad;
 };
 
+// Grouped prefill launch over a stack of equally shaped matrices on the tensor cores: problem i applies
+// matrix z_i to rows [row0_i, row0_i + rows_i) of xr, rows_i <= 128 * nsub; xr_had [max_rows][k] fp16
+// receives the rotated rows.
+std::string launch_gemm_tc_grouped(const void* xr, void* xr_had, const void* trellis_stack, int n_matrices, void* c,
+                                   const void* suh_stack, const void* svh_stack, const GemvProblem* problems, const int* n_problems,
+                                   int max_problems, int max_rows, int nsub, int size_k, int size_n, int k_bits, int codebook,
+                                   int out_fp32, unsigned* status, int sms, cudaStream_t stream);
+
+#ifdef __CUDACC__
+// A problem-table entry with every field forced into range, so that a table the caller forgot to
+// build (or built for another shape) yields wrong numbers, never a wild address.
+__device__ __forceinline__ GemvProblem load_problem(const GemvProblem* table, int i, int n_matrices, int tok, int max_rows)
+{
+    GemvProblem pr = table[i];
+    pr.z = min(max(pr.z, 0), n_matrices - 1);
+    pr.rows = min(max(pr.rows, 0), tok);
+    pr.row0 = min(max(pr.row0, 0), max(max_rows - pr.rows, 0));
+    return pr;
+}
+#endif
+
 // Grouped decode launch over a stack of equally shaped matrices (the experts of an MoE layer):
 // `problems` / `n_problems` live on the device (built by the dispatch kernels), xr fp16 [R][k] are
 // the routed rows, c the outputs [R][n]; suh_stack [experts][k], svh_stack [experts][n].

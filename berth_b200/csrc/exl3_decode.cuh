@@ -141,6 +141,43 @@ __device__ __forceinline__ void lane_states_regs(uint32_t r0, uint32_t r1, uint3
     states_aligned<BITS>(a0, a1, a2, s);
 }
 
+// Half-word selection on the FMA-heavy pipe: dp2a.lo(a, b) = a.h0*b.byte0 + a.h1*b.byte1.
+__device__ __forceinline__ uint32_t lo16_heavy(uint32_t a)
+{
+    uint32_t d;
+    asm("dp2a.lo.u32.u32 %0, %1, 0x0001, 0;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ uint32_t hi16_heavy(uint32_t a)
+{
+    uint32_t d;
+    asm("dp2a.lo.u32.u32 %0, %1, 0x0100, 0;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+// 4-bit tiles: eight 16-bit windows from the lane's raw word r0 and the next lane's r1
+// (13 integer operations).  Stream bytes in order: r0.b1 r0.b0 r0.b3 r0.b2 r1.b1 r1.b0.
+// HEAVY = true moves the six half-word selections to the FMA-heavy pipe (for the codebooks whose
+// arithmetic leans on the ALU pipe).
+template <bool HEAVY>
+__device__ __forceinline__ void states_4bit(uint32_t r0, uint32_t r1, uint32_t (&s)[8])
+{
+    s[2] = __byte_perm(r0, 0u, 0x4403);
+    const uint32_t z = r1 & 0xff00u;
+    s[6] = __byte_perm(r0, z, 0x4425);
+    const uint32_t a0 = __byte_perm(r0, 0u, 0x1032), a1 = __byte_perm(r1, 0u, 0x1032);
+    const uint32_t c4 = __funnelshift_l(a1, a0, 4), c12 = __funnelshift_l(a1, a0, 12);
+    if constexpr (HEAVY) {
+        s[0] = lo16_heavy(r0); s[4] = hi16_heavy(r0);
+        s[1] = hi16_heavy(c4); s[3] = hi16_heavy(c12);
+        s[5] = lo16_heavy(c4); s[7] = lo16_heavy(c12);
+    } else {
+        s[0] = r0 & 0xffffu; s[4] = r0 >> 16;
+        s[1] = c4 >> 16; s[3] = c12 >> 16;
+        s[5] = c4 & 0xffffu; s[7] = c12 & 0xffffu;
+    }
+}
+
 // Eight states -> the four packed fp16 pairs (j=0,1), (2,3), (4,5), (6,7): the A fragment
 // a0..a3 of mma.m16n8k16 for the transposed tile.
 template <int CB>

@@ -1,22 +1,34 @@
 // Prefill EXL3 linear on the 5th-generation tensor cores (size_m > 32):
 //   C = H128( a_had . W ) * svh,  a_had = H128(A * suh) (rotated beforehand by k_had128),
-// with W never materialised in HBM: trellis tiles arrive by TMA, eight decode warps expand
-// them (bit-exact fp16 weights) straight into the swizzled K-major shared-memory operand of
-// tcgen05.mma, the fp32 accumulators live in tensor memory, and the epilogue applies the
-// output Hadamard and the svh sign-scale before the only write of C.
+// with W never materialised in HBM, nor in shared memory: trellis tiles arrive by TMA, sixteen
+// decode warps expand them (bit-exact fp16 weights) and store the fragments straight into TENSOR
+// MEMORY, which is where tcgen05.mma takes its A operand from.  The product is computed transposed,
+//   D[n][row] = sum_k W[k][n] * a_had[row][k],
+// so the weights are the 128-row A operand (tensor memory), the activations the B operand (shared
+// memory, K-major, 128-byte swizzle, up to 256 rows per instruction) and the fp32 accumulator holds
+// one output column per TMEM lane.  Why: with both operands in shared memory a 128x128x16 MMA reads
+// 8 KiB per 64 cycles, which is all the shared-memory bandwidth of an SM, and the TMA writes and the
+// decode warps' traffic come on top (measured: 1815 cycles per 64-deep stage of a 512-row tile against
+// 1084 for the tensor pipe).  With the weights in tensor memory the activations are read from shared
+// memory once per stage and nothing else.  The MMA fragment layout of the decoder (lane = 4*g + q holds
+// (n = g, g+8; k = 2q, 2q+1, 2q+8, 2q+9)) is exactly the 16x128b store shape of tensor memory, so a tile
+// costs one tcgen05.st.
 //
-// Tile: one CTA owns 128 output columns (one Hadamard band) for up to 512 token rows -- four
-// 128x128 fp32 accumulators, all 512 TMEM columns -- so every decoded weight feeds 512 tokens:
-// per 64-deep k stage the tensor pipe needs 4 x (128x128x64) MACs = 1024 cycles while the decode
-// warps expand 32 tiles (~1600 warp instructions), which keeps the kernel MMA bound.
+// Tile: one CTA owns 128 output columns (one Hadamard band) for up to 384 token rows (384 fp32
+// accumulator columns; the other 128 TMEM columns hold four 64-deep weight stages).
 // Roofline: tensor pipe; FLOPs = 2*M*K*N.
 //
-// Warp roles (16 warps, one CTA per SM):
-//   warp 0      TMA producer: A stages (4 boxes of 128 rows x 64 k, 128-byte swizzle) and raw
-//               trellis stages (4 k-tile rows x 8 tiles);
+// Warp roles (24 warps, one CTA per SM):
+//   warp 0      TMA producer: activation stages (boxes of 128 rows x 64 k) and raw trellis stages
+//               (4 k-tile rows x 8 tiles);
 //   warp 1      TMEM allocation + the single MMA-issuing thread;
-//   warps 4..7  epilogue: tcgen05.ld, Hadamard, scale, store (warp w reads TMEM lanes 32*(w%4)..);
-//   warps 8..15 decode: trellis words -> fp16 pairs -> swizzled B stage.
+//   warps 4..7  epilogue: the thread owns output column n = its TMEM lane; 128-point Hadamard over n by
+//               warp shuffles (strides 1..16) and a shared-memory exchange between the four warps (32, 64),
+//               output scale, coalesced stores;
+//   warps 8..23 decode: trellis words -> fp16 pairs -> tensor memory, two tiles per warp and stage.
+// Grouped launches (the experts of an MoE layer) take blockIdx.y as an index into a device-side
+// problem table {matrix of the stack, first row, rows}; the MMA then covers only the problem's rows
+// (rounded up to 16), which is what makes small per-expert batches cheap.
 // All waits are bounded: a wait that runs out sets a status bit and the kernel carries on and
 // exits (wrong output, no hang).
 #include "exl3_decode.cuh"
@@ -28,16 +40,16 @@
 namespace berth {
 namespace {
 
-constexpr int kThreads = 512;
-constexpr int kDecodeWarp0 = 8, kDecodeWarps = 8;
+constexpr int kThreads = 768;
+constexpr int kDecodeWarp0 = 8, kDecodeWarps = 16;
 constexpr int kEpiWarp0 = 4;
-constexpr int BN = 128, BK = 64, SUB = 128, MAX_SUB = 4;
-constexpr int SA = 2;   // A stages
-constexpr int SB = 3;   // decoded-B stages
+constexpr int BN = 128, BK = 64, SUB = 128, MAX_SUB = 3;
+constexpr int SA = 3;   // activation stages
+constexpr int SW = 4;   // decoded-weight stages in tensor memory (32 columns each)
 constexpr int ST = 4;   // raw trellis stages
 constexpr int A_SUB_BYTES = SUB * BK * 2;          // 16 KiB
 constexpr int A_STAGE_BYTES = MAX_SUB * A_SUB_BYTES;
-constexpr int B_STAGE_BYTES = BN * BK * 2;         // 16 KiB
+constexpr int kAccCols = MAX_SUB * SUB;            // accumulator columns; weight stages follow
 constexpr long long kWaitCycles = 500000000LL;
 
 enum : unsigned { kStGemmTimeout = 16u };
@@ -47,16 +59,18 @@ struct TGeo {
     static constexpr int NW = 8 * BITS;
     static constexpr int TROW_BYTES = 8 * NW * 4;          // one k-tile row of the band
     static constexpr int T_STAGE_BYTES = 4 * TROW_BYTES;   // 64 k rows
-    static constexpr size_t SMEM = 1024 /*align slack*/ + size_t(SA) * A_STAGE_BYTES + size_t(SB) * B_STAGE_BYTES +
-                                   size_t(ST) * T_STAGE_BYTES + 256 /*barriers*/;
+    static constexpr size_t SMEM = 1024 /*align slack*/ + size_t(SA) * A_STAGE_BYTES + size_t(ST) * T_STAGE_BYTES + 256 /*barriers*/;
 };
 
 struct GemmArgs {
     void* c;
-    const __half* svh;
+    const __half* svh;       // [n], or the stack [matrices][n] of a grouped launch
     unsigned* status;
-    int m, k, n, out_fp32;
-    int nsub_max;   // 128-row sub-tiles per CTA (1..4): the row block of a CTA is nsub_max*128 tokens
+    int m, k, n, out_fp32;   // m = rows of the activation / output arrays
+    int nsub_max;   // 128-row sub-tiles per CTA (1..3): the row block of a CTA is nsub_max*128 tokens
+    const GemvProblem* problems;   // grouped launch: one entry per (matrix, chunk of <= nsub_max*128 rows); else null
+    const int* n_problems;
+    int max_problems, n_matrices;
 };
 
 // ---------------------------------------------------------------- PTX helpers
@@ -97,10 +111,31 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
     }
     return true;
 }
+// The same for warps that wait long (producer, decode, epilogue): sleep between polls, so that the one
+// thread that issues the MMAs is not competing for issue slots with spinning warps.
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, unsigned* status, unsigned ns)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(ns);
+        if (clock64() - t0 > kWaitCycles) {
+            atomicOr(status, kStGemmTimeout);
+            return false;
+        }
+    }
+    return true;
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
 {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
                  : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -110,16 +145,27 @@ __device__ __forceinline__ void tc_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-// D[tmem] (+)= A[smem desc] * B[smem desc]^T, fp16 in, fp32 out, 128 x 128 x 16.
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+// D[tmem] (+)= A[tmem] * B[smem desc]^T: A = 128 rows x 16 k fp16 in tensor memory (lane = row, two k per
+// 32-bit column), B = N rows x 16 k K-major in shared memory, D = 128 lanes x N fp32 columns.
+__device__ __forceinline__ void tc_mma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
 {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Instruction descriptor: D fp32, A/B fp16, both K-major, M = 128, N = n (a multiple of 16 up to 256).
+__device__ __forceinline__ uint32_t idesc_n(int n) { return (1u << 4) | (uint32_t(n >> 3) << 17) | (uint32_t(128 >> 4) << 24); }
+// One decoded 16x16 tile (the four fragment registers of mma.m16n8k16's A operand) into tensor memory:
+// 16 lanes x 8 columns starting at taddr; thread 4*g+q supplies (lane g | g+8, columns q | q+4).
+__device__ __forceinline__ void tc_st_frag(uint32_t taddr, const uint32_t (&w)[4])
+{
+    asm volatile("tcgen05.st.sync.aligned.16x128b.x2.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                 : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // 32 lanes x 32 consecutive fp32 columns of this warp's TMEM lane quarter.
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32])
 {
@@ -136,23 +182,6 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32])
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const float (&v)[32])
-{
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
-          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
-          "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
-          "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
-          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
-          "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
-          "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
-          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
-          "r"(__float_as_uint(v[31]))
-        : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
 
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, groups
 // of 8 rows 1024 bytes apart (start address and offsets in 16-byte units; version 1 = sm_100).
@@ -166,22 +195,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
     d |= uint64_t(2) << 61;                      // SWIZZLE_128B
     return d;
 }
-// Instruction descriptor: D fp32, A/B fp16, both K-major, M = 128, N = 128.
-constexpr uint32_t kIdesc = (1u << 4) | (uint32_t(BN >> 3) << 17) | (uint32_t(SUB >> 4) << 24);
-
-// 32-point Hadamard butterfly (strides 1..16) on registers.
-__device__ __forceinline__ void had32_regs(float (&v)[32])
-{
-#pragma unroll
-    for (int s = 1; s < 32; s <<= 1)
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-            if (!(i & s)) {
-                const float a = v[i], b = v[i | s];
-                v[i] = a + b;
-                v[i | s] = a - b;
-            }
-}
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // ---------------------------------------------------------------- the kernel
 template <int BITS, int CB>
@@ -191,28 +205,37 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
     using TG_ = TGeo<BITS>;
     constexpr int NW = TG_::NW, TROW_BYTES = TG_::TROW_BYTES, T_STAGE_BYTES = TG_::T_STAGE_BYTES;
 
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int band = blockIdx.x;
+    int z = 0, m0 = blockIdx.y * (p.nsub_max * SUB), rows_here = min(p.m - m0, p.nsub_max * SUB);
+    if (p.problems) {
+        // (the table was written by kernels that completed before this launch)
+        if (int(blockIdx.y) >= min(max(__ldg(p.n_problems), 0), p.max_problems)) return;
+        const GemvProblem pr = load_problem(p.problems, blockIdx.y, p.n_matrices, p.nsub_max * SUB, p.m);
+        z = pr.z; m0 = pr.row0; rows_here = pr.rows;
+        if (rows_here < 1) return;
+    }
+    const int row_end = m0 + rows_here;
+    const int nsub = (rows_here + SUB - 1) / SUB;
+    const int rows_pad = (rows_here + 15) & ~15;          // MMA N granularity
+    const int n1 = min(rows_pad, 256), n2 = rows_pad - n1;   // rows of the first / second MMA of a k step
+    const int kstages = p.k / BK;
+
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* a_ring = smem;
-    unsigned char* b_ring = a_ring + SA * A_STAGE_BYTES;
-    unsigned char* t_ring = b_ring + SB * B_STAGE_BYTES;
+    unsigned char* t_ring = a_ring + SA * A_STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(t_ring + ST * T_STAGE_BYTES);
     __shared__ uint32_t s_tmem_base;
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int band = blockIdx.x, m0 = blockIdx.y * (p.nsub_max * SUB);
-    const int rows_here = min(p.m - m0, p.nsub_max * SUB);
-    const int nsub = (rows_here + SUB - 1) / SUB;
-    const int kstages = p.k / BK;
-
     const uint32_t full_a = smem_u32(bars), empty_a = full_a + 8 * SA;
-    const uint32_t full_b = empty_a + 8 * SA, empty_b = full_b + 8 * SB;
-    const uint32_t full_t = empty_b + 8 * SB, empty_t = full_t + 8 * ST;
+    const uint32_t full_w = empty_a + 8 * SA, empty_w = full_w + 8 * SW;
+    const uint32_t full_t = empty_w + 8 * SW, empty_t = full_t + 8 * ST;
     const uint32_t acc_full = empty_t + 8 * ST;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SA; ++s) { mbar_init(full_a + 8 * s, 1); mbar_init(empty_a + 8 * s, 1); }
-        for (int s = 0; s < SB; ++s) { mbar_init(full_b + 8 * s, kDecodeWarps); mbar_init(empty_b + 8 * s, 1); }
+        for (int s = 0; s < SW; ++s) { mbar_init(full_w + 8 * s, kDecodeWarps); mbar_init(empty_w + 8 * s, 1); }
         for (int s = 0; s < ST; ++s) { mbar_init(full_t + 8 * s, 1); mbar_init(empty_t + 8 * s, kDecodeWarps); }
         mbar_init(acc_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -225,6 +248,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem_base;
+    const uint32_t tmem_w = tmem + kAccCols;   // weight stages: 32 columns (64 k) each
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -234,12 +258,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
             int sa = 0, pa = 0, st = 0, pt = 0;
             for (int ks = 0; ks < kstages; ++ks) {
                 // raw trellis: 4 k-tile rows of this band
-                if (ks >= ST) mbar_wait(empty_t + 8 * st, pt ^ 1, p.status);
+                if (ks >= ST) mbar_wait_parked(empty_t + 8 * st, pt ^ 1, p.status, 100);
                 mbar_arrive_expect_tx(full_t + 8 * st, T_STAGE_BYTES);
-                tma_load_2d(smem_u32(t_ring + st * T_STAGE_BYTES), &tmap_t, band * (TROW_BYTES / 8), ks * 4, full_t + 8 * st);
+                tma_load_3d(smem_u32(t_ring + st * T_STAGE_BYTES), &tmap_t, band * (TROW_BYTES / 8), ks * 4, z, full_t + 8 * st);
                 if (++st == ST) { st = 0; pt ^= 1; }
-                // activations: nsub boxes of 128 rows x 64 k
-                if (ks >= SA) mbar_wait(empty_a + 8 * sa, pa ^ 1, p.status);
+                // activations: nsub boxes of 128 rows x 64 k (rows past the array read as zero)
+                if (ks >= SA) mbar_wait_parked(empty_a + 8 * sa, pa ^ 1, p.status, 100);
                 mbar_arrive_expect_tx(full_a + 8 * sa, nsub * A_SUB_BYTES);
                 for (int sub = 0; sub < nsub; ++sub)
                     tma_load_2d(smem_u32(a_ring + sa * A_STAGE_BYTES + sub * A_SUB_BYTES), &tmap_a, ks * BK, m0 + sub * SUB,
@@ -250,118 +274,106 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            int sa = 0, pa = 0, sb = 0, pb = 0;
+            const uint32_t id1 = idesc_n(n1), id2 = idesc_n(n2 > 0 ? n2 : 16);
+            int sa = 0, pa = 0, sw = 0, pw = 0;
             for (int ks = 0; ks < kstages; ++ks) {
                 mbar_wait(full_a + 8 * sa, pa, p.status);
-                mbar_wait(full_b + 8 * sb, pb, p.status);
+                mbar_wait(full_w + 8 * sw, pw, p.status);
                 tc_fence_after();
-                const uint32_t a_base = smem_u32(a_ring + sa * A_STAGE_BYTES);
-                const uint64_t b_desc0 = smem_desc_sw128(smem_u32(b_ring + sb * B_STAGE_BYTES));
-                for (int sub = 0; sub < nsub; ++sub) {
-                    const uint64_t a_desc0 = smem_desc_sw128(a_base + sub * A_SUB_BYTES);
+                const uint32_t x_base = smem_u32(a_ring + sa * A_STAGE_BYTES);
+                const uint64_t x_desc1 = smem_desc_sw128(x_base), x_desc2 = smem_desc_sw128(x_base + 2 * A_SUB_BYTES);
 #pragma unroll
-                    for (int k16 = 0; k16 < BK / 16; ++k16)   // +32 bytes (2 x 16-byte units) per 16 k inside the swizzle atom
-                        tc_mma_f16(tmem + sub * BN, a_desc0 + 2 * k16, b_desc0 + 2 * k16, kIdesc, (ks | k16) ? 1u : 0u);
+                for (int k16 = 0; k16 < BK / 16; ++k16) {   // +32 bytes (2 x 16-byte units) per 16 k inside the swizzle atom
+                    const uint32_t w_t = tmem_w + sw * 32 + 8 * k16;
+                    tc_mma_ts_f16(tmem, w_t, x_desc1 + 2 * k16, id1, (ks | k16) ? 1u : 0u);
+                    if (n2 > 0) tc_mma_ts_f16(tmem + 256, w_t, x_desc2 + 2 * k16, id2, (ks | k16) ? 1u : 0u);
                 }
                 tc_commit(empty_a + 8 * sa);   // both arrive when the MMAs above have read their operands
-                tc_commit(empty_b + 8 * sb);
+                tc_commit(empty_w + 8 * sw);
                 if (++sa == SA) { sa = 0; pa ^= 1; }
-                if (++sb == SB) { sb = 0; pb ^= 1; }
+                if (++sw == SW) { sw = 0; pw ^= 1; }
             }
             tc_commit(acc_full);
         }
     } else if (warp >= kDecodeWarp0) {
         // ------------------------------------------------------------ decode warps
+        // warp d: k-tile row d/4 of the stage, tile columns 2*(d%4), 2*(d%4)+1 = output columns 32*(d%4) .. +31,
+        // which are the TMEM lanes this warp may access (warp index % 4 == d % 4).
         const int d = warp - kDecodeWarp0;
-        const int krow = d >> 1, col0 = (d & 1) * 4;   // this warp: k-tile row krow of the stage, tile columns col0..col0+3
-        const int g = lane >> 2, q = lane & 3;
-        int st = 0, pt = 0, sb = 0, pb = 0;
+        const int krow = d >> 2, quarter = d & 3;
+        int st = 0, pt = 0, sw = 0, pw = 0;
         for (int ks = 0; ks < kstages; ++ks) {
-            mbar_wait(full_t + 8 * st, pt, p.status);
-            if (ks >= SB) mbar_wait(empty_b + 8 * sb, pb ^ 1, p.status);
+            mbar_wait_parked(full_t + 8 * st, pt, p.status, 40);
             const uint32_t* trow = reinterpret_cast<const uint32_t*>(t_ring + st * T_STAGE_BYTES + krow * TROW_BYTES);
-            unsigned char* bst = b_ring + sb * B_STAGE_BYTES;
+            uint32_t w[2][4];
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                uint32_t s[8], w[4];
-                dq::lane_states<BITS>(trow + (col0 + t) * NW, lane, s);
-                dq::decode_frag<CB>(s, w);
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const int n = (col0 + t) * 16 + g + 8 * (r & 1);
-                    const int chunk = 2 * krow + (r >> 1);           // 16-byte chunk of k = 16*krow + 8*(r>>1) + 2q
-                    *reinterpret_cast<uint32_t*>(bst + n * 128 + ((chunk ^ (n & 7)) << 4) + 4 * q) = w[r];
-                }
+            for (int t = 0; t < 2; ++t) {
+                uint32_t s[8];
+                const uint32_t* tile = trow + (2 * quarter + t) * NW;
+                if constexpr (BITS == 4) dq::states_4bit<CB != 2>(tile[lane], tile[(lane + 1) & 31], s);
+                else dq::lane_states<BITS>(tile, lane, s);
+                dq::decode_frag<CB>(s, w[t]);
             }
-            fence_proxy_async();   // generic-proxy stores -> visible to the tensor core's async proxy
+            if (ks >= SW) {
+                mbar_wait_parked(empty_w + 8 * sw, pw ^ 1, p.status, 40);   // the MMAs that read this weight stage are done
+                tc_fence_after();
+            }
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+                tc_st_frag(tmem_w + (uint32_t(32 * quarter + 16 * t) << 16) + sw * 32 + 8 * krow, w[t]);
+            tc_wait_st();
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(full_b + 8 * sb);
+                mbar_arrive(full_w + 8 * sw);
                 mbar_arrive(empty_t + 8 * st);
             }
             if (++st == ST) { st = 0; pt ^= 1; }
-            if (++sb == SB) { sb = 0; pb ^= 1; }
+            if (++sw == SW) { sw = 0; pw ^= 1; }
         }
     } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + 4) {
         // ------------------------------------------------------------ epilogue
+        // Thread = output column n = 32*quarter + lane (its TMEM lane), 32 token rows per pass.
         const int quarter = warp & 3;
-        mbar_wait(acc_full, 0, p.status);
+        const int n = quarter * 32 + lane;
+        const float scale = __half2float(p.svh[size_t(z) * p.n + band * BN + n]);
+        float* xch = reinterpret_cast<float*>(a_ring);    // [4 quarters][32 rows][32 lanes]: the activation ring is idle by now
+        mbar_wait_parked(acc_full, 0, p.status, 1000);
         tc_fence_after();
-        const float* dummy = nullptr; (void) dummy;
-        for (int sub = 0; sub < nsub; ++sub) {
-            const uint32_t tbase = tmem + (uint32_t(quarter * 32) << 16) + sub * BN;
-            // strides 64 and 32 across the four 32-column blocks, in place in tensor memory
-            {
-                float x0[32], x2[32];
-                tc_ld32(tbase + 0, x0); tc_ld32(tbase + 64, x2);
+        for (int c0 = 0; c0 < rows_pad; c0 += 32) {
+            float v[32];
+            tc_ld32(tmem + (uint32_t(quarter * 32) << 16) + c0, v);
+            // 128-point Hadamard over n, strides ascending: 1..16 between the lanes of the warp ...
 #pragma unroll
-                for (int i = 0; i < 32; ++i) { const float a = x0[i], b = x2[i]; x0[i] = a + b; x2[i] = a - b; }
-                tc_st32(tbase + 0, x0); tc_st32(tbase + 64, x2);
-                tc_ld32(tbase + 32, x0); tc_ld32(tbase + 96, x2);
+            for (int s = 1; s < 32; s <<= 1) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) { const float a = x0[i], b = x2[i]; x0[i] = a + b; x2[i] = a - b; }
-                tc_st32(tbase + 32, x0); tc_st32(tbase + 96, x2);
+                for (int j = 0; j < 32; ++j) {
+                    const float o = __shfl_xor_sync(dq::kFull, v[j], s);
+                    v[j] = (lane & s) ? __fsub_rn(o, v[j]) : __fadd_rn(v[j], o);
+                }
             }
-            const int row = m0 + sub * SUB + quarter * 32 + lane;
+            // ... 32 and 64 between the four warps, through shared memory
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                float y0[32], y1[32];
-                tc_ld32(tbase + half * 64, y0); tc_ld32(tbase + half * 64 + 32, y1);
+            for (int j = 0; j < 32; ++j) xch[(quarter * 32 + j) * 32 + lane] = v[j];
+            epi_sync();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) { const float a = y0[i], b = y1[i]; y0[i] = a + b; y1[i] = a - b; }
-                had32_regs(y0);
-                had32_regs(y1);
-                if (row < p.m) {
+            for (int j = 0; j < 32; ++j) {
+                const float p1 = xch[((quarter ^ 1) * 32 + j) * 32 + lane];
+                const float p2 = xch[((quarter ^ 2) * 32 + j) * 32 + lane];
+                const float p3 = xch[((quarter ^ 3) * 32 + j) * 32 + lane];
+                const float a = (quarter & 1) ? __fsub_rn(p1, v[j]) : __fadd_rn(v[j], p1);      // stride 32: this quarter's pair
+                const float b = (quarter & 1) ? __fsub_rn(p3, p2) : __fadd_rn(p2, p3);          // stride 32: the pair 64 away
+                v[j] = (quarter & 2) ? __fsub_rn(b, a) : __fadd_rn(a, b);                       // stride 64
+            }
+            epi_sync();   // xch may be overwritten by the next pass
+            const int col = band * BN + n;
 #pragma unroll
-                    for (int blk = 0; blk < 2; ++blk) {
-                        float (&y)[32] = blk ? y1 : y0;
-                        const int col = band * BN + half * 64 + blk * 32;
-                        if (p.out_fp32) {
-                            float* dst = static_cast<float*>(p.c) + size_t(row) * p.n + col;
-#pragma unroll
-                            for (int i = 0; i < 32; i += 4) {
-                                float4 o;
-                                o.x = y[i] * kRScale * __half2float(p.svh[col + i]);
-                                o.y = y[i + 1] * kRScale * __half2float(p.svh[col + i + 1]);
-                                o.z = y[i + 2] * kRScale * __half2float(p.svh[col + i + 2]);
-                                o.w = y[i + 3] * kRScale * __half2float(p.svh[col + i + 3]);
-                                *reinterpret_cast<float4*>(dst + i) = o;
-                            }
-                        } else {
-                            __half* dst = static_cast<__half*>(p.c) + size_t(row) * p.n + col;
-#pragma unroll
-                            for (int i = 0; i < 32; i += 8) {
-                                uint4 o;
-                                uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-                                for (int j = 0; j < 4; ++j)
-                                    ow[j] = dq::pack_half2(
-                                        __float2half_rn(y[i + 2 * j] * kRScale * __half2float(p.svh[col + i + 2 * j])),
-                                        __float2half_rn(y[i + 2 * j + 1] * kRScale * __half2float(p.svh[col + i + 2 * j + 1])));
-                                *reinterpret_cast<uint4*>(dst + i) = o;
-                            }
-                        }
-                    }
+            for (int j = 0; j < 32; ++j) {
+                const int row = m0 + c0 + j;
+                if (row < row_end) {
+                    const float y = __fmul_rn(__fmul_rn(v[j], kRScale), scale);
+                    if (p.out_fp32) static_cast<float*>(p.c)[size_t(row) * p.n + col] = y;
+                    else static_cast<__half*>(p.c)[size_t(row) * p.n + col] = __float2half_rn(y);
                 }
             }
         }
@@ -405,6 +417,24 @@ CUtensorMap make_map(CUtensorMapDataType type, const void* base, cuuint64_t inne
     return map;
 }
 
+// 3-D view of a trellis stack: z = matrix, y = k-tile row (K/16), x = the row in 8-byte elements;
+// box = 4 k-tile rows x 8 tiles (one 64 x 128 weight stage) of one matrix.
+CUtensorMap make_trellis_map(const void* base, int n_matrices, int size_k, int size_n, int bits, int trow_bytes)
+{
+    if (reinterpret_cast<uintptr_t>(base) % 16 != 0) throw std::runtime_error("exl3 linear: tensors must be 16-byte aligned");
+    CUtensorMap map;
+    const cuuint64_t row_bytes = cuuint64_t(size_n / 16) * 32 * bits;
+    const cuuint64_t dims[3] = {row_bytes / 8, cuuint64_t(size_k / 16), cuuint64_t(n_matrices)};
+    const cuuint64_t strides[2] = {row_bytes, row_bytes * cuuint64_t(size_k / 16)};
+    const cuuint32_t box[3] = {cuuint32_t(trow_bytes / 8), 4, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void*>(base), dims, strides, box, elem,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw std::runtime_error("exl3 linear: cuTensorMapEncodeTiled failed (" + std::to_string(int(r)) + ")");
+    return map;
+}
+
 template <int BITS, int CB>
 void launch_tc(const void* a_had, const void* trellis, const GemmArgs& args, cudaStream_t stream)
 {
@@ -419,11 +449,8 @@ void launch_tc(const void* a_had, const void* trellis, const GemmArgs& args, cud
     // activations [m][k] fp16: box 64 k x 128 rows, 128-byte swizzle (the tensor core's K-major layout)
     const CUtensorMap map_a = make_map(CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a_had, cuuint64_t(args.k), cuuint64_t(args.m),
                                        cuuint64_t(args.k) * 2, BK, SUB, CU_TENSOR_MAP_SWIZZLE_128B);
-    // trellis as [k/16][row bytes / 8] 8-byte elements: box = 8 tiles x 4 k-tile rows
-    const cuuint64_t row_bytes = cuuint64_t(args.n / 16) * 32 * BITS;
-    const CUtensorMap map_t = make_map(CU_TENSOR_MAP_DATA_TYPE_UINT64, trellis, row_bytes / 8, cuuint64_t(args.k / 16), row_bytes,
-                                       TG_::TROW_BYTES / 8, 4, CU_TENSOR_MAP_SWIZZLE_NONE);
-    dim3 grid(args.n / BN, (args.m + args.nsub_max * SUB - 1) / (args.nsub_max * SUB));
+    const CUtensorMap map_t = make_trellis_map(trellis, args.problems ? args.n_matrices : 1, args.k, args.n, BITS, TG_::TROW_BYTES);
+    dim3 grid(args.n / BN, args.problems ? args.max_problems : (args.m + args.nsub_max * SUB - 1) / (args.nsub_max * SUB));
     kern<<<grid, kThreads, TG_::SMEM, stream>>>(map_a, map_t, args);
     cuda_ok(cudaGetLastError(), "k_exl3_gemm_tc launch");
 }
@@ -435,6 +462,57 @@ void launch_tc_cb(int cb, const void* a_had, const void* trellis, const GemmArgs
         case 0: launch_tc<BITS, 0>(a_had, trellis, a, st); break;
         case 1: launch_tc<BITS, 1>(a_had, trellis, a, st); break;
         default: launch_tc<BITS, 2>(a_had, trellis, a, st); break;
+    }
+}
+
+void launch_tc_bits(int k_bits, int codebook, const void* a_had, const void* trellis, const GemmArgs& args, cudaStream_t stream)
+{
+    switch (k_bits) {
+        case 1: launch_tc_cb<1>(codebook, a_had, trellis, args, stream); break;
+        case 2: launch_tc_cb<2>(codebook, a_had, trellis, args, stream); break;
+        case 3: launch_tc_cb<3>(codebook, a_had, trellis, args, stream); break;
+        case 4: launch_tc_cb<4>(codebook, a_had, trellis, args, stream); break;
+        case 5: launch_tc_cb<5>(codebook, a_had, trellis, args, stream); break;
+        case 6: launch_tc_cb<6>(codebook, a_had, trellis, args, stream); break;
+        case 7: launch_tc_cb<7>(codebook, a_had, trellis, args, stream); break;
+        case 8: launch_tc_cb<8>(codebook, a_had, trellis, args, stream); break;
+        default: throw std::runtime_error("exl3 linear: K must be in 1..=8");
+    }
+}
+
+// Rotation of the routed rows of a grouped launch: a_had[row] = fp16(H128(x[row] * suh[matrix of the row]) / sqrt(128)).
+// One block per problem, its warps share the (row, 128-block) pairs.
+__global__ void __launch_bounds__(256) k_rotate_rows_plain(const __half* __restrict__ xr, const __half* __restrict__ suh_stack,
+                                                           const GemvProblem* __restrict__ problems, const int* __restrict__ n_problems,
+                                                           __half* __restrict__ a_had, int chunk, int k, int max_problems,
+                                                           int n_matrices, int max_rows)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, kblocks = k >> 7;
+    const int nprob = min(max(__ldg(n_problems), 0), max_problems);
+    for (int pi = blockIdx.x; pi < nprob; pi += gridDim.x) {
+        const GemvProblem pr = load_problem(problems, pi, n_matrices, chunk, max_rows);
+        const __half* suh = suh_stack + size_t(pr.z) * k;
+        const int pairs = pr.rows * kblocks;
+#pragma unroll 4
+        for (int pair = warp; pair < pairs; pair += 8) {
+            const int lr = pair / kblocks, b = pair - lr * kblocks;
+            const size_t off = size_t(pr.row0 + lr) * k + b * 128 + lane * 4;
+            const uint2 xw = *reinterpret_cast<const uint2*>(xr + off);
+            const uint2 sr = *reinterpret_cast<const uint2*>(suh + b * 128 + lane * 4);
+            uint2 xm = xw, sm = sr;
+            const __half2 x0 = *reinterpret_cast<__half2*>(&xm.x), x1 = *reinterpret_cast<__half2*>(&xm.y);
+            const __half2 s0 = *reinterpret_cast<__half2*>(&sm.x), s1 = *reinterpret_cast<__half2*>(&sm.y);
+            float v[4];
+            v[0] = __fmul_rn(__low2float(x0), __low2float(s0));
+            v[1] = __fmul_rn(__high2float(x0), __high2float(s0));
+            v[2] = __fmul_rn(__low2float(x1), __low2float(s1));
+            v[3] = __fmul_rn(__high2float(x1), __high2float(s1));
+            dq::had128_warp(v, lane);
+            uint2 o;
+            o.x = dq::pack_half2(__float2half_rn(__fmul_rn(v[0], kRScale)), __float2half_rn(__fmul_rn(v[1], kRScale)));
+            o.y = dq::pack_half2(__float2half_rn(__fmul_rn(v[2], kRScale)), __float2half_rn(__fmul_rn(v[3], kRScale)));
+            *reinterpret_cast<uint2*>(a_had + off) = o;
+        }
     }
 }
 
@@ -457,9 +535,10 @@ std::string launch_gemm_tc(const void* a, const void* trellis, void* c, const vo
     args.status = status;
     args.m = size_m; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
-    // Rows per CTA: 128..512.  More rows per decoded weight keep the kernel MMA bound (the decode
-    // warps need ~640 cycles per 64-deep stage, one 128-row sub-tile 256), fewer rows give more
-    // CTAs; pick the count with the fewest (waves x stage time) on this device.
+    args.problems = nullptr; args.n_problems = nullptr; args.max_problems = 0; args.n_matrices = 1;
+    // Rows per CTA: 128, 256 or 384.  More rows per decoded weight keep the kernel MMA bound (the decode
+    // warps need ~700 cycles per 64-deep stage, 128 rows of MMA ~370), fewer rows give more CTAs; pick the
+    // count with the fewest (waves x stage time) on this device.
     {
         const int sms = device_info(current_device()).sms;
         const int bands = size_n / BN;
@@ -467,24 +546,43 @@ std::string launch_gemm_tc(const void* a, const void* trellis, void* c, const vo
         for (int ns = 1; ns <= MAX_SUB; ++ns) {
             const long long ctas = (long long) bands * ((size_m + ns * SUB - 1) / (ns * SUB));
             const long long waves = (ctas + sms - 1) / sms;
-            const long long cost = waves * std::max(ns * 256, 640);
+            const long long cost = waves * std::max(ns * 370, 700);
             if (best < 0 || cost <= best) { best = cost; args.nsub_max = ns; }   // ties: more rows per CTA
         }
     }
-    switch (k_bits) {
-        case 1: launch_tc_cb<1>(codebook, a_had, trellis, args, stream); break;
-        case 2: launch_tc_cb<2>(codebook, a_had, trellis, args, stream); break;
-        case 3: launch_tc_cb<3>(codebook, a_had, trellis, args, stream); break;
-        case 4: launch_tc_cb<4>(codebook, a_had, trellis, args, stream); break;
-        case 5: launch_tc_cb<5>(codebook, a_had, trellis, args, stream); break;
-        case 6: launch_tc_cb<6>(codebook, a_had, trellis, args, stream); break;
-        case 7: launch_tc_cb<7>(codebook, a_had, trellis, args, stream); break;
-        case 8: launch_tc_cb<8>(codebook, a_had, trellis, args, stream); break;
-        default: throw std::runtime_error("exl3 linear: K must be in 1..=8");
-    }
+    launch_tc_bits(k_bits, codebook, a_had, trellis, args, stream);
     return "k_had128<f16,pre> + k_exl3_gemm_tc<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "> grid=" +
            std::to_string(size_n / BN) + "x" + std::to_string((size_m + args.nsub_max * SUB - 1) / (args.nsub_max * SUB)) +
            " block=" + std::to_string(kThreads) + " tile=" + std::to_string(args.nsub_max * SUB) + "x128x64 tmem=512";
+}
+
+// Grouped prefill linear over a stack of equally shaped matrices: problem i applies matrix z_i to rows
+// [row0_i, row0_i + rows_i) of xr (rows_i <= 128 * nsub); xr_had [max_rows][k] receives the rotated rows.
+std::string launch_gemm_tc_grouped(const void* xr, void* xr_had, const void* trellis_stack, int n_matrices, void* c,
+                                   const void* suh_stack, const void* svh_stack, const GemvProblem* problems, const int* n_problems,
+                                   int max_problems, int max_rows, int nsub, int size_k, int size_n, int k_bits, int codebook,
+                                   int out_fp32, unsigned* status, int sms, cudaStream_t stream)
+{
+    if (size_k % 128 != 0 || size_n % 128 != 0)
+        throw std::runtime_error("exl3 grouped gemm: size_k and size_n must be multiples of 128");
+    if (nsub < 1 || nsub > MAX_SUB) throw std::runtime_error("exl3 grouped gemm: row chunks must be 128, 256 or 384 rows");
+    if (max_problems < 1 || max_problems > 65535) throw std::runtime_error("exl3 grouped gemm: problem count out of range");
+    k_rotate_rows_plain<<<std::min(max_problems, 16 * sms), 256, 0, stream>>>(
+        static_cast<const __half*>(xr), static_cast<const __half*>(suh_stack), problems, n_problems, static_cast<__half*>(xr_had),
+        nsub * SUB, size_k, max_problems, n_matrices, max_rows);
+    cuda_ok(cudaGetLastError(), "k_rotate_rows_plain launch");
+    GemmArgs args;
+    args.c = c;
+    args.svh = static_cast<const __half*>(svh_stack);
+    args.status = status;
+    args.m = max_rows; args.k = size_k; args.n = size_n;
+    args.out_fp32 = out_fp32;
+    args.nsub_max = nsub;
+    args.problems = problems; args.n_problems = n_problems; args.max_problems = max_problems; args.n_matrices = n_matrices;
+    launch_tc_bits(k_bits, codebook, xr_had, trellis_stack, args, stream);
+    return "k_rotate_rows_plain + k_exl3_gemm_tc<" + std::to_string(k_bits) + "," + std::to_string(codebook) + ",grouped> grid=" +
+           std::to_string(size_n / BN) + "x" + std::to_string(max_problems) + " block=" + std::to_string(kThreads) + " tile=" +
+           std::to_string(nsub * SUB) + "x128x64 tmem=512";
 }
 
 }  // namespace berth

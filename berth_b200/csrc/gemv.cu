@@ -103,17 +103,6 @@ struct GemvArgs {
     int m, k, n, out_fp32;
 };
 
-// A problem-table entry with every field forced into range, so that a table the caller forgot to
-// build (or built for another shape) yields wrong numbers, never a wild address.
-__device__ __forceinline__ GemvProblem load_problem(const GemvProblem* table, int i, int n_matrices, int tok, int max_rows)
-{
-    GemvProblem pr = table[i];
-    pr.z = min(max(pr.z, 0), n_matrices - 1);
-    pr.rows = min(max(pr.rows, 0), tok);
-    pr.row0 = min(max(pr.row0, 0), max(max_rows - pr.rows, 0));
-    return pr;
-}
-
 // ---------------------------------------------------------------- mbarrier / TMA PTX
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
 
@@ -204,52 +193,12 @@ __device__ __forceinline__ void grid_dependency_wait() { pdl_wait(); }
 __device__ __forceinline__ void grid_launch_dependents() { pdl_trigger(); }
 
 // ---------------------------------------------------------------- per-tile decode + MMA
-// Half-word selection on the FMA-heavy pipe: dp2a.lo(a, b) = a.h0*b.byte0 + a.h1*b.byte1.
-__device__ __forceinline__ uint32_t lo16_heavy(uint32_t a)
-{
-    uint32_t d;
-    asm("dp2a.lo.u32.u32 %0, %1, 0x0001, 0;" : "=r"(d) : "r"(a));
-    return d;
-}
-__device__ __forceinline__ uint32_t hi16_heavy(uint32_t a)
-{
-    uint32_t d;
-    asm("dp2a.lo.u32.u32 %0, %1, 0x0100, 0;" : "=r"(d) : "r"(a));
-    return d;
-}
-
-// 4-bit tiles: eight 16-bit windows from the lane's raw word r0 and the next lane's r1
-// (13 integer operations).  Stream bytes in order: r0.b1 r0.b0 r0.b3 r0.b2 r1.b1 r1.b0.
-// HEAVY = true moves the six half-word selections to the FMA-heavy pipe (for the codebooks whose
-// arithmetic leans on the ALU pipe).
-template <bool HEAVY>
-__device__ __forceinline__ void states_4bit(uint32_t r0, uint32_t r1, uint32_t (&s)[8])
-{
-    s[2] = __byte_perm(r0, 0u, 0x4403);
-    const uint32_t z = r1 & 0xff00u;
-    s[6] = __byte_perm(r0, z, 0x4425);
-    const uint32_t a0 = __byte_perm(r0, 0u, 0x1032), a1 = __byte_perm(r1, 0u, 0x1032);
-    const uint32_t c4 = __funnelshift_l(a1, a0, 4), c12 = __funnelshift_l(a1, a0, 12);
-    if constexpr (HEAVY) {
-        s[0] = lo16_heavy(r0); s[4] = hi16_heavy(r0);
-        s[1] = hi16_heavy(c4); s[3] = hi16_heavy(c12);
-        s[5] = lo16_heavy(c4); s[7] = lo16_heavy(c12);
-    } else {
-        s[0] = r0 & 0xffffu; s[4] = r0 >> 16;
-        s[1] = c4 >> 16; s[3] = c12 >> 16;
-        s[5] = c4 & 0xffffu; s[7] = c12 & 0xffffu;
-    }
-}
-
 template <int BITS, int CB>
 __device__ __forceinline__ void tile_states(const uint32_t* tile, int lane, int lane1, uint32_t (&s)[8])
 {
-    if constexpr (BITS == 4) {
-        const uint32_t r0 = tile[lane], r1 = tile[lane1];
-        states_4bit<CB != 2>(r0, r1, s);
-    } else {
-        dq::lane_states<BITS>(tile, lane, s);
-    }
+    // the codebooks whose arithmetic leans on the ALU pipe take their half-word selections on the FMA-heavy pipe
+    if constexpr (BITS == 4) dq::states_4bit<CB != 2>(tile[lane], tile[lane1], s);
+    else dq::lane_states<BITS>(tile, lane, s);
 }
 
 // Duplicated activation pairs for the lo/hi-as-k-slots scheme: from b0 = (x[2q], x[2q+1]) and

@@ -263,14 +263,29 @@ __global__ void __launch_bounds__(256) k_moe_combine(const __half* __restrict__ 
 
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
-int token_groups(int max_rows_per_expert) { return max_rows_per_expert <= 8 ? 1 : (max_rows_per_expert <= 16 ? 2 : 4); }
+// How the expert stage cuts an expert's rows into problems: up to 32 rows per problem go through the
+// grouped decode GEMV (8, 16 or 32 rows = 1, 2 or 4 token groups), more through the grouped tensor-core
+// GEMM (128..384 rows = 1..3 sub-tiles).  An expert with more rows than one chunk takes several problems.
+struct ExpertPlan {
+    int chunk;   // rows per problem
+    int tg;      // token groups of the GEMV path, 0 on the GEMM path
+    int nsub;    // 128-row sub-tiles of the GEMM path, 0 on the GEMV path
+};
+ExpertPlan expert_plan(int rows_per_expert)
+{
+    if (rows_per_expert <= 8) return {8, 1, 0};
+    if (rows_per_expert <= 16) return {16, 2, 0};
+    if (rows_per_expert <= 32) return {32, 4, 0};
+    const int nsub = std::min(3, (rows_per_expert + 127) / 128);
+    return {128 * nsub, 0, nsub};
+}
 
-// Token groups for T tokens routed top_k ways over n_experts: sized for twice the mean rows per expert
-// (an expert with more rows takes several chunks), never beyond what one expert can receive.
-int token_groups_routed(int T, int top_k, int n_experts)
+// Rows-per-expert figure for T tokens routed top_k ways over n_experts: twice the mean, never beyond
+// what one expert can receive.
+int routed_rows_hint(int T, int top_k, int n_experts)
 {
     const long long twice_mean = (2LL * T * top_k + n_experts - 1) / n_experts;
-    return token_groups(int(std::min<long long>(T, std::max<long long>(twice_mean, 1))));
+    return int(std::min<long long>(T, std::max<long long>(twice_mean, 1)));   // the caller turns this into a plan
 }
 
 // Workspace carve-up of the expert stage for up to R routed rows.
@@ -279,18 +294,19 @@ struct ExpertScratch {
     uint32_t* afrag; float* blocksum; __half* g; __half* u; int max_problems;
     size_t bytes;
 };
-ExpertScratch carve_experts(void* base, int R, int n_local, int hidden, int inter, int tg)
+ExpertScratch carve_experts(void* base, int R, int n_local, int hidden, int inter, const ExpertPlan& plan)
 {
     ExpertScratch s{};
-    const int chunk = 8 * tg;
+    const int chunk = plan.chunk;
     s.max_problems = R / chunk + n_local;
     const int kmax = std::max(hidden, inter);
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += align256(bytes); return o; };
     const size_t o_counts = take(size_t(n_local) * 4), o_offsets = take(size_t(n_local + 1) * 4), o_np = take(4);
     const size_t o_prob = take(size_t(s.max_problems) * sizeof(GemvProblem));
-    const size_t o_afrag = take(size_t(s.max_problems) * (kmax / 16) * tg * 256);
-    const size_t o_bsum = take(size_t(s.max_problems) * chunk * (kmax / 128) * 4);
+    // rotated activations: fragment order per problem (GEMV) or plain rows (GEMM)
+    const size_t o_afrag = take(plan.tg ? size_t(s.max_problems) * (kmax / 16) * plan.tg * 256 : size_t(R) * kmax * 2);
+    const size_t o_bsum = take(plan.tg ? size_t(s.max_problems) * chunk * (kmax / 128) * 4 : 256);
     const size_t o_g = take(size_t(R) * inter * 2), o_u = take(size_t(R) * inter * 2);
     s.bytes = off;
     if (base) {
@@ -350,9 +366,21 @@ void dispatch(const int32_t* keys, int n, int e0, int n_local, int chunk, const 
 // Grouped gate/up -> silu*up -> down over routed rows xr [R][hidden]; yr fp16 [R][hidden].
 std::string experts(const berth_moe_weights* w, const void* gate_t, const void* up_t, const void* down_t, const void* gsuh,
                     const void* gsvh, const void* usuh, const void* usvh, const void* dsuh, const void* dsvh, int n_local,
-                    const void* xr, void* yr, int R, int max_rows, int tg, const ExpertScratch& s, const GemvScratch& sc, int sms, cudaStream_t st)
+                    const void* xr, void* yr, int R, int max_rows, const ExpertPlan& plan, const ExpertScratch& s, const GemvScratch& sc,
+                    int sms, cudaStream_t st)
 {
     const int H = w->hidden, I = w->inter;
+    if (plan.nsub) {
+        std::string d = launch_gemm_tc_grouped(xr, s.afrag, gate_t, n_local, s.g, gsuh, gsvh, s.problems, s.n_problems, s.max_problems,
+                                               max_rows, plan.nsub, H, I, w->k_bits, w->codebook, 0, sc.status, sms, st);
+        launch_gemm_tc_grouped(xr, s.afrag, up_t, n_local, s.u, usuh, usvh, s.problems, s.n_problems, s.max_problems, max_rows, plan.nsub,
+                               H, I, w->k_bits, w->codebook, 0, sc.status, sms, st);
+        if (berth_ops_silu_mul(s.g, s.u, s.g, int64_t(R) * I, 0.0f, st) != 0) throw std::runtime_error(berth_ops_last_error());
+        launch_gemm_tc_grouped(s.g, s.afrag, down_t, n_local, yr, dsuh, dsvh, s.problems, s.n_problems, s.max_problems, max_rows,
+                               plan.nsub, I, H, w->k_bits, w->codebook, 0, sc.status, sms, st);
+        return d;
+    }
+    const int tg = plan.tg;
     std::string d = launch_gemv_grouped(xr, gate_t, n_local, s.g, gsuh, gsvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag,
                                         s.blocksum, H, I, w->k_bits, w->codebook, 0, sc, sms, st);
     launch_gemv_grouped(xr, up_t, n_local, s.u, usuh, usvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag, s.blocksum, H, I,
@@ -394,7 +422,7 @@ extern "C" int berth_moe_router_topk(const void* x, const void* w_router, const 
 extern "C" size_t berth_moe_experts_workspace_bytes(int max_rows, int n_local, int hidden, int inter, int max_rows_per_expert)
 {
     if (max_rows < 1 || n_local < 1 || hidden < 128 || inter < 128) return 0;
-    return carve_experts(nullptr, max_rows, n_local, hidden, inter, token_groups(max_rows_per_expert)).bytes + 256;
+    return carve_experts(nullptr, max_rows, n_local, hidden, inter, expert_plan(max_rows_per_expert)).bytes + 256;
 }
 
 static ExpertScratch expert_scratch(void* ews, size_t ews_bytes, int max_rows, int n_local, int hidden, int inter, int mrpe)
@@ -405,7 +433,7 @@ static ExpertScratch expert_scratch(void* ews, size_t ews_bytes, int max_rows, i
         throw std::runtime_error("moe: expert workspace of " + std::to_string(ews_bytes) + " bytes is smaller than the " +
                                  std::to_string(need) + " required");
     void* b = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(ews) + 255) & ~uintptr_t(255));
-    return carve_experts(b, max_rows, n_local, hidden, inter, token_groups(mrpe));
+    return carve_experts(b, max_rows, n_local, hidden, inter, expert_plan(mrpe));
 }
 
 extern "C" int berth_moe_sort_rows(const int32_t* keys, int n, int e0, int n_local, int32_t* perm, int32_t* inv,
@@ -418,7 +446,7 @@ extern "C" int berth_moe_sort_rows(const int32_t* keys, int n, int e0, int n_loc
         if (n < 0 || n > max_rows) throw std::runtime_error("moe sort: n must be within 0..max_rows");
         if (n_local < 1 || n_local > 1024) throw std::runtime_error("moe sort: n_local must be in 1..=1024");
         ExpertScratch es = expert_scratch(ews, ews_bytes, max_rows, n_local, hidden, inter, max_rows_per_expert);
-        dispatch(keys, n, e0, n_local, 8 * token_groups(max_rows_per_expert), es, perm, inv, (cudaStream_t) stream);
+        dispatch(keys, n, e0, n_local, expert_plan(max_rows_per_expert).chunk, es, perm, inv, (cudaStream_t) stream);
         if (offsets_out)
             cuda_ok(cudaMemcpyAsync(offsets_out, es.offsets, size_t(n_local + 1) * 4, cudaMemcpyDeviceToDevice, (cudaStream_t) stream),
                     "moe sort offsets copy");
@@ -454,7 +482,7 @@ extern "C" int berth_moe_experts(const berth_moe_weights* w, const void* xr, voi
         ExpertScratch es = expert_scratch(ews, ews_bytes, max_rows, w->n_experts, w->hidden, w->inter, max_rows_per_expert);
         if (n_rows == 0) return;
         st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
-                            w->down_suh, w->down_svh, w->n_experts, xr, yr, n_rows, n_rows, token_groups(max_rows_per_expert), es,
+                            w->down_suh, w->down_svh, w->n_experts, xr, yr, n_rows, n_rows, expert_plan(max_rows_per_expert), es,
                             gemv_workspace(device), info.sms, (cudaStream_t) stream);
     });
 }
@@ -476,8 +504,7 @@ extern "C" size_t berth_moe_workspace_bytes(int T, int hidden, int inter, int sh
 {
     if (T < 1 || hidden < 128 || inter < 128 || n_experts < 1 || top_k < 1) return 0;
     const int R = T * top_k;
-    const int tg = token_groups_routed(T, top_k, n_experts);
-    const ExpertScratch es = carve_experts(nullptr, R, n_experts, hidden, inter, tg);
+    const ExpertScratch es = carve_experts(nullptr, R, n_experts, hidden, inter, expert_plan(routed_rows_hint(T, top_k, n_experts)));
     size_t total = 0;
     total += align256(size_t(T) * n_experts * 4);            // logits
     total += 2 * align256(size_t(R) * 4);                    // perm, inv
@@ -510,7 +537,7 @@ extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T,
         GemvScratch sc = gemv_workspace(device);
         cudaStream_t cs = (cudaStream_t) stream;
         const int H = w->hidden, I = w->inter, E = w->n_experts, K = w->top_k, R = T * K, SI = w->shared_inter;
-        const int tg = token_groups_routed(T, K, E);
+        const ExpertPlan plan = expert_plan(routed_rows_hint(T, K, E));
 
         char* b = static_cast<char*>(workspace);
         b = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(b) + 255) & ~uintptr_t(255));
@@ -520,15 +547,15 @@ extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T,
         int32_t* inv = (int32_t*) take(size_t(R) * 4);
         __half* xr = (__half*) take(size_t(R) * H * 2);
         __half* yr = (__half*) take(size_t(R) * H * 2);
-        ExpertScratch es = carve_experts(b, R, E, H, I, tg);
+        ExpertScratch es = carve_experts(b, R, E, H, I, plan);
         b += es.bytes;
 
         router_topk(x, w->w_router, w->router_bias, topk_idx, topk_w, logits, T, H, E, K, cs);
-        dispatch(topk_idx, R, 0, E, 8 * tg, es, perm, inv, cs);
+        dispatch(topk_idx, R, 0, E, plan.chunk, es, perm, inv, cs);
         k_moe_gather_rows<<<std::min(R, 148 * 8), 256, 0, cs>>>((const __half*) x, perm, es.offsets + E, K, xr, H);
         cuda_ok(cudaGetLastError(), "k_moe_gather_rows launch");
         st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
-                            w->down_suh, w->down_svh, E, xr, yr, R, R, tg, es, sc, info.sms, cs);
+                            w->down_suh, w->down_svh, E, xr, yr, R, R, plan, es, sc, info.sms, cs);
 
         __half* ysh = nullptr;
         if (SI > 0) {

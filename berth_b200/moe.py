@@ -102,11 +102,12 @@ class GpuStages:
         self.E = n_experts_total
         self.max_rows, self.mrpe = max_rows, max_rows_per_expert
         l = _lib.lib()
-        # one scratch for the send-side sort over all experts, one for the local experts
-        self.ews_all = torch.empty(l.berth_moe_experts_workspace_bytes(max_rows, self.E, self.d["hidden"], self.d["inter"], max_rows_per_expert),
-                                   dtype=torch.uint8, device=device)
-        self.ews_loc = torch.empty(l.berth_moe_experts_workspace_bytes(max_rows, self.d["n_experts"], self.d["hidden"], self.d["inter"],
-                                                                       max_rows_per_expert), dtype=torch.uint8, device=device)
+        # one scratch for the send-side sort over all experts, one for the local experts; the expert stage picks
+        # its row chunk per call (see rows_hint), so the scratch is sized for the largest of the possible plans
+        hints = [h for h in (8, 16, 32, 128, 256, 384, 512) if h <= max(8, max_rows_per_expert)] + [max_rows_per_expert]
+        size = lambda n_exp: max(l.berth_moe_experts_workspace_bytes(max_rows, n_exp, self.d["hidden"], self.d["inter"], h) for h in hints)
+        self.ews_all = torch.empty(size(self.E), dtype=torch.uint8, device=device)
+        self.ews_loc = torch.empty(size(self.d["n_experts"]), dtype=torch.uint8, device=device)
         from .engine import Exl3Linear, Gpu
         self.shared = None
         if self.d["shared_inter"]:
@@ -130,6 +131,12 @@ class GpuStages:
         router_topk(x, self.layer._keep["w_router"], self.layer._keep.get("router_bias"), idx, w, logits, T, H, self.E, k)
         return idx, w
 
+    def rows_hint(self, n_rows: int, n_local: int) -> int:
+        """Rows-per-expert figure the expert stage sizes its problems for: twice the mean, at least 1, at most
+        the construction-time bound.  sort(for_experts=True) and experts() of one layer call must agree on it,
+        which they do because both see the same row count."""
+        return max(1, min(self.mrpe, -(-2 * n_rows // max(n_local, 1))))
+
     def sort(self, keys, e0: int, n_local: int, for_experts: bool = False):
         """Stable sort by expert.  for_experts=True also leaves the problem table of the following
         experts() call in the local-expert scratch (n_local must then be this rank's expert count)."""
@@ -142,7 +149,7 @@ class GpuStages:
             keys = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._check(_lib.lib().berth_moe_sort_rows(keys.data_ptr(), n, e0, n_local, perm.data_ptr(), inv.data_ptr(), offsets.data_ptr(),
                                                    ews.data_ptr(), ews.numel(), self.max_rows, self.d["hidden"], self.d["inter"],
-                                                   self.mrpe, None))
+                                                   self.rows_hint(n, n_local), None))
         return perm[:n], inv[:n], offsets
 
     def gather(self, src, index, div: int):
@@ -156,7 +163,7 @@ class GpuStages:
         R = xr.shape[0]
         yr = torch.empty_like(xr)
         self._check(_lib.lib().berth_moe_experts(C.byref(self.layer.c), xr.data_ptr(), yr.data_ptr(), R, self.ews_loc.data_ptr(),
-                                                 self.ews_loc.numel(), self.max_rows, self.mrpe, None))
+                                                 self.ews_loc.numel(), self.max_rows, self.rows_hint(R, self.d["n_experts"]), None))
         return yr
 
     def shared_expert(self, x):
