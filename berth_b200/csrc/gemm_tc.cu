@@ -22,10 +22,11 @@
 //   warp 0      TMA producer: activation stages (boxes of 128 rows x 64 k) and raw trellis stages
 //               (4 k-tile rows x 8 tiles);
 //   warp 1      TMEM allocation + the single MMA-issuing thread;
-//   warps 4..7  epilogue: the thread owns output column n = its TMEM lane; 128-point Hadamard over n by
-//               warp shuffles (strides 1..16) and a shared-memory exchange between the four warps (32, 64),
-//               output scale, coalesced stores;
-//   warps 8..23 decode: trellis words -> fp16 pairs -> tensor memory, two tiles per warp and stage.
+//   warps 8..23 decode: trellis words -> fp16 pairs -> tensor memory, two tiles per warp and stage;
+//   warps 4..7 and, after their last stage, the decode warps: epilogue in five teams of four warps.  A thread
+//               owns output column n = its TMEM lane; 128-point Hadamard over n by warp shuffles (strides
+//               1..16) and a shared-memory exchange between the four warps of the team (32, 64), output
+//               scale, coalesced stores.
 // Grouped launches (the experts of an MoE layer) take blockIdx.y as an index into a device-side
 // problem table {matrix of the stack, first row, rows}; the MMA then covers only the problem's rows
 // (rounded up to 16), which is what makes small per-expert batches cheap.
@@ -195,7 +196,16 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
     d |= uint64_t(2) << 61;                      // SWIZZLE_128B
     return d;
 }
-__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+constexpr int kEpiTeams = 5;
+// Barrier of one epilogue team (four warps); ids 1..5.
+__device__ __forceinline__ void team_sync(int team) { asm volatile("bar.sync %0, 128;" ::"r"(team + 1) : "memory"); }
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 
 // ---------------------------------------------------------------- the kernel
 template <int BITS, int CB>
@@ -273,28 +283,34 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t id1 = idesc_n(n1), id2 = idesc_n(n2 > 0 ? n2 : 16);
-            int sa = 0, pa = 0, sw = 0, pw = 0;
-            for (int ks = 0; ks < kstages; ++ks) {
-                mbar_wait(full_a + 8 * sa, pa, p.status);
-                mbar_wait(full_w + 8 * sw, pw, p.status);
-                tc_fence_after();
-                const uint32_t x_base = smem_u32(a_ring + sa * A_STAGE_BYTES);
-                const uint64_t x_desc1 = smem_desc_sw128(x_base), x_desc2 = smem_desc_sw128(x_base + 2 * A_SUB_BYTES);
+        // The whole warp runs the loop and one elected lane issues: addresses and descriptors then live in
+        // uniform registers.  (Issued from a single-lane branch every operand was moved from the vector to
+        // the uniform register file first, about 160 cycles per 16-deep step, more than the MMA itself.)
+        const uint32_t id1 = idesc_n(n1), id2 = idesc_n(n2 > 0 ? n2 : 16);
+        int sa = 0, pa = 0, sw = 0, pw = 0;
+        for (int ks = 0; ks < kstages; ++ks) {
+            mbar_wait(full_a + 8 * sa, pa, p.status);
+            mbar_wait(full_w + 8 * sw, pw, p.status);
+            tc_fence_after();
+            const uint32_t x_base = smem_u32(a_ring + sa * A_STAGE_BYTES);
+            const uint64_t x_desc1 = smem_desc_sw128(x_base), x_desc2 = smem_desc_sw128(x_base + 2 * A_SUB_BYTES);
+            const uint32_t w_t = tmem_w + sw * 32;
+            const uint32_t bar_a = empty_a + 8 * sa, bar_w = empty_w + 8 * sw;
+            if (elect_one()) {
 #pragma unroll
                 for (int k16 = 0; k16 < BK / 16; ++k16) {   // +32 bytes (2 x 16-byte units) per 16 k inside the swizzle atom
-                    const uint32_t w_t = tmem_w + sw * 32 + 8 * k16;
-                    tc_mma_ts_f16(tmem, w_t, x_desc1 + 2 * k16, id1, (ks | k16) ? 1u : 0u);
-                    if (n2 > 0) tc_mma_ts_f16(tmem + 256, w_t, x_desc2 + 2 * k16, id2, (ks | k16) ? 1u : 0u);
+                    tc_mma_ts_f16(tmem, w_t + 8 * k16, x_desc1 + 2 * k16, id1, (ks | k16) ? 1u : 0u);
+                    if (n2 > 0) tc_mma_ts_f16(tmem + 256, w_t + 8 * k16, x_desc2 + 2 * k16, id2, (ks | k16) ? 1u : 0u);
                 }
-                tc_commit(empty_a + 8 * sa);   // both arrive when the MMAs above have read their operands
-                tc_commit(empty_w + 8 * sw);
-                if (++sa == SA) { sa = 0; pa ^= 1; }
-                if (++sw == SW) { sw = 0; pw ^= 1; }
+                tc_commit(bar_a);   // both arrive when the MMAs above have read their operands
+                tc_commit(bar_w);
             }
-            tc_commit(acc_full);
+            __syncwarp();
+            if (++sa == SA) { sa = 0; pa ^= 1; }
+            if (++sw == SW) { sw = 0; pw ^= 1; }
         }
+        if (elect_one()) tc_commit(acc_full);
+        __syncwarp();
     } else if (warp >= kDecodeWarp0) {
         // ------------------------------------------------------------ decode warps
         // warp d: k-tile row d/4 of the stage, tile columns 2*(d%4), 2*(d%4)+1 = output columns 32*(d%4) .. +31,
@@ -331,31 +347,40 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
             if (++st == ST) { st = 0; pt ^= 1; }
             if (++sw == SW) { sw = 0; pw ^= 1; }
         }
-    } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + 4) {
-        // ------------------------------------------------------------ epilogue
-        // Thread = output column n = 32*quarter + lane (its TMEM lane), 32 token rows per pass.
+    }
+
+    // ---------------------------------------------------------------- epilogue
+    // Five teams of four warps (one warp per TMEM lane quarter): the epilogue warps and, once their
+    // last stage is stored, the four decode groups.  Team i takes the 32-row passes i, i+5, ...
+    // Thread = output column n = 32*quarter + lane (its TMEM lane).
+    int team = -1;
+    if (warp >= kEpiWarp0 && warp < kEpiWarp0 + 4) team = 0;
+    else if (warp >= kDecodeWarp0) team = 1 + ((warp - kDecodeWarp0) >> 2);
+    if (team >= 0) {
         const int quarter = warp & 3;
         const int n = quarter * 32 + lane;
         const float scale = __half2float(p.svh[size_t(z) * p.n + band * BN + n]);
-        float* xch = reinterpret_cast<float*>(a_ring);    // [4 quarters][32 rows][32 lanes]: the activation ring is idle by now
-        mbar_wait_parked(acc_full, 0, p.status, 1000);
+        // exchange buffers [team][4 quarters][32 rows][32 lanes] in the activation ring, which is idle by then
+        float* xch = reinterpret_cast<float*>(a_ring) + team * (4 * 32 * 32);
+        float sgn[5];   // -1 where this lane is the upper element of the butterfly of stride 2^i
+#pragma unroll
+        for (int i = 0; i < 5; ++i) sgn[i] = (lane >> i) & 1 ? -1.f : 1.f;
+        mbar_wait_parked(acc_full, 0, p.status, team == 0 ? 1000 : 100);
         tc_fence_after();
-        for (int c0 = 0; c0 < rows_pad; c0 += 32) {
+        for (int c0 = 32 * team; c0 < rows_pad; c0 += 32 * kEpiTeams) {
             float v[32];
             tc_ld32(tmem + (uint32_t(quarter * 32) << 16) + c0, v);
-            // 128-point Hadamard over n, strides ascending: 1..16 between the lanes of the warp ...
+            // 128-point Hadamard over n, strides ascending: 1..16 between the lanes of the warp
+            // (sgn * v + o is o - v or v + o, rounded once) ...
 #pragma unroll
-            for (int s = 1; s < 32; s <<= 1) {
+            for (int i = 0; i < 5; ++i) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float o = __shfl_xor_sync(dq::kFull, v[j], s);
-                    v[j] = (lane & s) ? __fsub_rn(o, v[j]) : __fadd_rn(v[j], o);
-                }
+                for (int j = 0; j < 32; ++j) v[j] = __fmaf_rn(sgn[i], v[j], __shfl_xor_sync(dq::kFull, v[j], 1 << i));
             }
-            // ... 32 and 64 between the four warps, through shared memory
+            // ... 32 and 64 between the four warps of the team, through shared memory
 #pragma unroll
             for (int j = 0; j < 32; ++j) xch[(quarter * 32 + j) * 32 + lane] = v[j];
-            epi_sync();
+            team_sync(team);
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
                 const float p1 = xch[((quarter ^ 1) * 32 + j) * 32 + lane];
@@ -365,7 +390,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
                 const float b = (quarter & 1) ? __fsub_rn(p3, p2) : __fadd_rn(p2, p3);          // stride 32: the pair 64 away
                 v[j] = (quarter & 2) ? __fsub_rn(b, a) : __fadd_rn(a, b);                       // stride 64
             }
-            epi_sync();   // xch may be overwritten by the next pass
+            team_sync(team);   // xch may be overwritten by the next pass
             const int col = band * BN + n;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
