@@ -506,25 +506,32 @@ void launch_tc_bits(int k_bits, int codebook, const void* a_had, const void* tre
 }
 
 // Rotation of the routed rows of a grouped launch: a_had[row] = fp16(H128(x[row] * suh[matrix of the row]) / sqrt(128)).
-// One block per problem, its warps share the (row, 128-block) pairs.
+// One warp per row: it finds the row's problem by bisection over the table (problems are sorted by first
+// row and cover [0, total rows) without gaps), then walks the row's 128-blocks.
 __global__ void __launch_bounds__(256) k_rotate_rows_plain(const __half* __restrict__ xr, const __half* __restrict__ suh_stack,
                                                            const GemvProblem* __restrict__ problems, const int* __restrict__ n_problems,
                                                            __half* __restrict__ a_had, int chunk, int k, int max_problems,
                                                            int n_matrices, int max_rows)
 {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, kblocks = k >> 7;
+    const int lane = threadIdx.x & 31, kblocks = k >> 7;
     const int nprob = min(max(__ldg(n_problems), 0), max_problems);
-    for (int pi = blockIdx.x; pi < nprob; pi += gridDim.x) {
-        const GemvProblem pr = load_problem(problems, pi, n_matrices, chunk, max_rows);
+    if (nprob < 1) return;
+    const GemvProblem last = load_problem(problems, nprob - 1, n_matrices, chunk, max_rows);
+    const int total_rows = min(last.row0 + last.rows, max_rows);
+    for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < total_rows; row += gridDim.x * 8) {
+        int lo = 0, hi = nprob - 1;   // the last problem whose first row is <= row
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (__ldg(&problems[mid].row0) <= row) lo = mid; else hi = mid - 1;
+        }
+        const GemvProblem pr = load_problem(problems, lo, n_matrices, chunk, max_rows);
+        if (row < pr.row0 || row >= pr.row0 + pr.rows) continue;   // a table with gaps: leave the row alone
         const __half* suh = suh_stack + size_t(pr.z) * k;
-        const int pairs = pr.rows * kblocks;
 #pragma unroll 4
-        for (int pair = warp; pair < pairs; pair += 8) {
-            const int lr = pair / kblocks, b = pair - lr * kblocks;
-            const size_t off = size_t(pr.row0 + lr) * k + b * 128 + lane * 4;
-            const uint2 xw = *reinterpret_cast<const uint2*>(xr + off);
-            const uint2 sr = *reinterpret_cast<const uint2*>(suh + b * 128 + lane * 4);
-            uint2 xm = xw, sm = sr;
+        for (int b = 0; b < kblocks; ++b) {
+            const size_t off = size_t(row) * k + b * 128 + lane * 4;
+            uint2 xm = *reinterpret_cast<const uint2*>(xr + off);
+            uint2 sm = __ldg(reinterpret_cast<const uint2*>(suh + b * 128 + lane * 4));
             const __half2 x0 = *reinterpret_cast<__half2*>(&xm.x), x1 = *reinterpret_cast<__half2*>(&xm.y);
             const __half2 s0 = *reinterpret_cast<__half2*>(&sm.x), s1 = *reinterpret_cast<__half2*>(&sm.y);
             float v[4];
@@ -592,7 +599,7 @@ std::string launch_gemm_tc_grouped(const void* xr, void* xr_had, const void* tre
         throw std::runtime_error("exl3 grouped gemm: size_k and size_n must be multiples of 128");
     if (nsub < 1 || nsub > MAX_SUB) throw std::runtime_error("exl3 grouped gemm: row chunks must be 128, 256 or 384 rows");
     if (max_problems < 1 || max_problems > 65535) throw std::runtime_error("exl3 grouped gemm: problem count out of range");
-    k_rotate_rows_plain<<<std::min(max_problems, 16 * sms), 256, 0, stream>>>(
+    k_rotate_rows_plain<<<std::max(1, std::min((max_rows + 7) / 8, 8 * sms)), 256, 0, stream>>>(
         static_cast<const __half*>(xr), static_cast<const __half*>(suh_stack), problems, n_problems, static_cast<__half*>(xr_had),
         nsub * SUB, size_k, max_problems, n_matrices, max_rows);
     cuda_ok(cudaGetLastError(), "k_rotate_rows_plain launch");

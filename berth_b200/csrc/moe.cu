@@ -19,68 +19,83 @@ namespace {
 // ---------------------------------------------------------------- router
 // logits[t][e] = sum over 32 chunks of H/32 sequential fmaf, chunks combined by a halving tree
 // ((p0+p16)+(p8+p24))+...: the summation order of the CPU checker, so the top-k indices can be
-// compared bit for bit.  Block = 32 chunk-warps x 32 experts for kRouterTok tokens: warp j
-// accumulates chunk j with coalesced reads of the router rows (each row read once per token tile).
+// compared bit for bit.  Block = 16 warps x 32 experts for kRouterTok tokens: a warp accumulates
+// chunks j and j+16 with coalesced reads of the router rows (each row read once per token tile).
 constexpr int kRouterTok = 8;
+constexpr int kRouterWarps = 16;   // each warp accumulates two of the 32 chunks, one after the other
 // Dynamic shared memory: the token tile as fp32 [kRouterTok][H], then the chunk sums [32][kRouterTok][33].
-__global__ void __launch_bounds__(1024) k_moe_router_logits(const __half* __restrict__ x, const __half* __restrict__ w,
-                                                            const float* __restrict__ bias, float* __restrict__ logits,
-                                                            int T, int H, int E)
+// 512 threads and ~97 KiB per block, so that two blocks share an SM and one block's load and reduction
+// phases overlap the other's arithmetic.
+__global__ void __launch_bounds__(kRouterWarps * 32, 2) k_moe_router_logits(const __half* __restrict__ x, const __half* __restrict__ w,
+                                                                            const float* __restrict__ bias, float* __restrict__ logits,
+                                                                            int T, int H, int E)
 {
     extern __shared__ __align__(16) float rsm[];
     float* xs = rsm;                                                    // [kRouterTok][H]
     float (*part)[kRouterTok][33] = reinterpret_cast<float (*)[kRouterTok][33]>(rsm + kRouterTok * H);
-    const int j = threadIdx.x >> 5, el = threadIdx.x & 31;
+    const int wq = threadIdx.x >> 5, el = threadIdx.x & 31;
     const int e = blockIdx.x * 32 + el, t0 = blockIdx.y * kRouterTok;
     const int chunk = H / 32;
     // the tile's activations, converted once (rows past T repeat the last token; their sums are never stored)
-    for (int i = threadIdx.x * 2; i < kRouterTok * H; i += 2048) {
+    for (int i = threadIdx.x * 2; i < kRouterTok * H; i += kRouterWarps * 64) {
         const int tt = i / H, h = i - tt * H;
         const __half2 v = *reinterpret_cast<const __half2*>(x + size_t(min(t0 + tt, T - 1)) * H + h);
         xs[i] = __low2float(v);
         xs[i + 1] = __high2float(v);
     }
     __syncthreads();
-    const __half* wr = w + size_t(j) * chunk * E + e;
-    const float* xj = xs + j * chunk;
-    float acc[kRouterTok];
-#pragma unroll
-    for (int tt = 0; tt < kRouterTok; ++tt) acc[tt] = 0.f;
-    // eight router rows in flight per pass; the products are still added one by one in k order
-    int i0 = 0;
     const int vec_end = (chunk & 3) == 0 ? chunk : 0;   // quads are 16-byte aligned only if the chunk is a multiple of 4
-    for (; i0 + 8 <= vec_end; i0 += 8) {
-        float wv[8];
+    for (int j = wq; j < 32; j += kRouterWarps) {
+        const __half* wr = w + size_t(j) * chunk * E + e;
+        const float* xj = xs + j * chunk;
+        float acc[kRouterTok];
 #pragma unroll
-        for (int ii = 0; ii < 8; ++ii) wv[ii] = __half2float(wr[size_t(i0 + ii) * E]);
+        for (int tt = 0; tt < kRouterTok; ++tt) acc[tt] = 0.f;
+        // eight router rows in flight per pass, the next eight already requested; the products are still
+        // added one by one in k order
+        int i0 = 0;
+        __half nxt[8];
+        if (8 <= vec_end) {
 #pragma unroll
-        for (int tt = 0; tt < kRouterTok; ++tt) {
-            const float4 a = *reinterpret_cast<const float4*>(xj + tt * H + i0);
-            const float4 b = *reinterpret_cast<const float4*>(xj + tt * H + i0 + 4);
-            acc[tt] = __fmaf_rn(a.x, wv[0], acc[tt]); acc[tt] = __fmaf_rn(a.y, wv[1], acc[tt]);
-            acc[tt] = __fmaf_rn(a.z, wv[2], acc[tt]); acc[tt] = __fmaf_rn(a.w, wv[3], acc[tt]);
-            acc[tt] = __fmaf_rn(b.x, wv[4], acc[tt]); acc[tt] = __fmaf_rn(b.y, wv[5], acc[tt]);
-            acc[tt] = __fmaf_rn(b.z, wv[6], acc[tt]); acc[tt] = __fmaf_rn(b.w, wv[7], acc[tt]);
+            for (int ii = 0; ii < 8; ++ii) nxt[ii] = wr[size_t(ii) * E];
         }
-    }
-    for (; i0 < chunk; ++i0) {   // the rest, or all of it for an odd chunk
-        const float wv = __half2float(wr[size_t(i0) * E]);
+        for (; i0 + 8 <= vec_end; i0 += 8) {
+            float wv[8];
 #pragma unroll
-        for (int tt = 0; tt < kRouterTok; ++tt) acc[tt] = __fmaf_rn(xj[tt * H + i0], wv, acc[tt]);
-    }
+            for (int ii = 0; ii < 8; ++ii) wv[ii] = __half2float(nxt[ii]);
+            if (i0 + 16 <= vec_end) {
 #pragma unroll
-    for (int tt = 0; tt < kRouterTok; ++tt) part[j][tt][el] = acc[tt];
+                for (int ii = 0; ii < 8; ++ii) nxt[ii] = wr[size_t(i0 + 8 + ii) * E];
+            }
+#pragma unroll
+            for (int tt = 0; tt < kRouterTok; ++tt) {
+                const float4 a = *reinterpret_cast<const float4*>(xj + tt * H + i0);
+                const float4 b = *reinterpret_cast<const float4*>(xj + tt * H + i0 + 4);
+                acc[tt] = __fmaf_rn(a.x, wv[0], acc[tt]); acc[tt] = __fmaf_rn(a.y, wv[1], acc[tt]);
+                acc[tt] = __fmaf_rn(a.z, wv[2], acc[tt]); acc[tt] = __fmaf_rn(a.w, wv[3], acc[tt]);
+                acc[tt] = __fmaf_rn(b.x, wv[4], acc[tt]); acc[tt] = __fmaf_rn(b.y, wv[5], acc[tt]);
+                acc[tt] = __fmaf_rn(b.z, wv[6], acc[tt]); acc[tt] = __fmaf_rn(b.w, wv[7], acc[tt]);
+            }
+        }
+        for (; i0 < chunk; ++i0) {   // the rest, or all of it for an odd chunk
+            const float wv = __half2float(wr[size_t(i0) * E]);
+#pragma unroll
+            for (int tt = 0; tt < kRouterTok; ++tt) acc[tt] = __fmaf_rn(xj[tt * H + i0], wv, acc[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < kRouterTok; ++tt) part[j][tt][el] = acc[tt];
+    }
     __syncthreads();
     // warp tt reduces token tt: lane = expert; the same halving tree as a 32-lane xor butterfly's lane 0
-    if (j < kRouterTok && t0 + j < T) {
+    if (wq < kRouterTok && t0 + wq < T) {
         float p[32];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) p[c] = part[c][j][el];
+        for (int c = 0; c < 32; ++c) p[c] = part[c][wq][el];
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1)
 #pragma unroll
             for (int c = 0; c < off; ++c) p[c] = __fadd_rn(p[c], p[c + off]);
-        logits[size_t(t0 + j) * E + e] = __fadd_rn(p[0], bias ? bias[e] : 0.f);
+        logits[size_t(t0 + wq) * E + e] = __fadd_rn(p[0], bias ? bias[e] : 0.f);
     }
 }
 
@@ -344,7 +359,7 @@ void router_topk(const void* x, const void* w_router, const float* bias, int32_t
         cuda_ok(cudaFuncSetAttribute(k_moe_router_logits, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "router smem attribute");
         attr_set[dev] = true;
     }
-    k_moe_router_logits<<<dim3(E / 32, (T + kRouterTok - 1) / kRouterTok), 1024, smem, st>>>((const __half*) x, (const __half*) w_router,
+    k_moe_router_logits<<<dim3(E / 32, (T + kRouterTok - 1) / kRouterTok), kRouterWarps * 32, smem, st>>>((const __half*) x, (const __half*) w_router,
                                                                                            bias, logits, T, H, E);
     cuda_ok(cudaGetLastError(), "k_moe_router_logits launch");
     k_moe_topk<<<(T + 3) / 4, 128, 0, st>>>(logits, topk_idx, topk_w, T, E, k);
