@@ -207,6 +207,76 @@ __device__ __forceinline__ bool elect_one()
     return pred != 0;
 }
 
+// One epilogue pass of a team of four warps (one per TMEM lane quarter; barrier id `team` + 1): 32 token
+// rows (accumulator columns tacc .. tacc+31 of the warp's lanes) of one band.  A thread owns output column
+// n = 32*quarter + lane: 128-point Hadamard over n with ascending strides -- 1..16 between the lanes of
+// the warp (sgn * v + o is o - v or v + o, rounded once), 32 and 64 between the four warps through the
+// 16 KiB exchange buffer xch -- then the output scale and the stores of rows row0 .. row0+31 below row_end.
+__device__ __noinline__ void epilogue_pass(uint32_t tacc, float* xch, int team, int quarter, int lane, float scale, void* c,
+                                              int out_fp32, int ldc, int col, int row0, int row_end)
+{
+    float v[32];
+    tc_ld32(tacc, v);
+#pragma unroll
+    for (int i = 0; i < 5; ++i) {
+        const float sgn = (lane >> i) & 1 ? -1.f : 1.f;   // -1 where this lane is the upper element of the butterfly
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __fmaf_rn(sgn, v[j], __shfl_xor_sync(dq::kFull, v[j], 1 << i));
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) xch[(quarter * 32 + j) * 32 + lane] = v[j];
+    team_sync(team);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const float p1 = xch[((quarter ^ 1) * 32 + j) * 32 + lane];
+        const float p2 = xch[((quarter ^ 2) * 32 + j) * 32 + lane];
+        const float p3 = xch[((quarter ^ 3) * 32 + j) * 32 + lane];
+        const float a = (quarter & 1) ? __fsub_rn(p1, v[j]) : __fadd_rn(v[j], p1);      // stride 32: this quarter's pair
+        const float b = (quarter & 1) ? __fsub_rn(p3, p2) : __fadd_rn(p2, p3);          // stride 32: the pair 64 away
+        v[j] = (quarter & 2) ? __fsub_rn(b, a) : __fadd_rn(a, b);                       // stride 64
+    }
+    team_sync(team);   // xch may be overwritten by the next pass
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const int row = row0 + j;
+        if (row < row_end) {
+            const float y = __fmul_rn(__fmul_rn(v[j], kRScale), scale);
+            if (out_fp32) static_cast<float*>(c)[size_t(row) * ldc + col] = y;
+            else static_cast<__half*>(c)[size_t(row) * ldc + col] = __float2half_rn(y);
+        }
+    }
+}
+
+// One 64-deep stage of one band decoded into tensor memory by the sixteen decode warps: warp d takes k-tile row
+// d/4 of the stage and tile columns 2*(d%4), 2*(d%4)+1 = output columns 32*(d%4) .. +31, which are the TMEM lanes
+// it may access (warp index % 4 == d % 4).  `wait_w` = the stage of tensor memory must first be released.
+template <int BITS, int CB>
+__device__ __forceinline__ void decode_stage(const unsigned char* tstage, uint32_t tmem_wstage, int d, int lane, bool wait_w,
+                                             uint32_t empty_w_bar, uint32_t empty_w_parity, unsigned* status)
+{
+    constexpr int NW = 8 * BITS, TROW_BYTES = 8 * NW * 4;
+    const int krow = d >> 2, quarter = d & 3;
+    const uint32_t* trow = reinterpret_cast<const uint32_t*>(tstage + krow * TROW_BYTES);
+    uint32_t w[2][4];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        uint32_t s[8];
+        const uint32_t* tile = trow + (2 * quarter + t) * NW;
+        if constexpr (BITS == 4) dq::states_4bit<CB != 2>(tile[lane], tile[(lane + 1) & 31], s);
+        else dq::lane_states<BITS>(tile, lane, s);
+        dq::decode_frag<CB>(s, w[t]);
+    }
+    if (wait_w) {
+        mbar_wait_parked(empty_w_bar, empty_w_parity, status, 40);   // the MMAs that read this weight stage are done
+        tc_fence_after();
+    }
+#pragma unroll
+    for (int t = 0; t < 2; ++t) tc_st_frag(tmem_wstage + (uint32_t(32 * quarter + 16 * t) << 16) + 8 * krow, w[t]);
+    tc_wait_st();
+    tc_fence_before();
+    __syncwarp();
+}
+
 // ---------------------------------------------------------------- the kernel
 template <int BITS, int CB>
 __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_constant__ CUtensorMap tmap_a,
@@ -313,33 +383,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
         __syncwarp();
     } else if (warp >= kDecodeWarp0) {
         // ------------------------------------------------------------ decode warps
-        // warp d: k-tile row d/4 of the stage, tile columns 2*(d%4), 2*(d%4)+1 = output columns 32*(d%4) .. +31,
-        // which are the TMEM lanes this warp may access (warp index % 4 == d % 4).
         const int d = warp - kDecodeWarp0;
-        const int krow = d >> 2, quarter = d & 3;
         int st = 0, pt = 0, sw = 0, pw = 0;
         for (int ks = 0; ks < kstages; ++ks) {
             mbar_wait_parked(full_t + 8 * st, pt, p.status, 40);
-            const uint32_t* trow = reinterpret_cast<const uint32_t*>(t_ring + st * T_STAGE_BYTES + krow * TROW_BYTES);
-            uint32_t w[2][4];
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-                uint32_t s[8];
-                const uint32_t* tile = trow + (2 * quarter + t) * NW;
-                if constexpr (BITS == 4) dq::states_4bit<CB != 2>(tile[lane], tile[(lane + 1) & 31], s);
-                else dq::lane_states<BITS>(tile, lane, s);
-                dq::decode_frag<CB>(s, w[t]);
-            }
-            if (ks >= SW) {
-                mbar_wait_parked(empty_w + 8 * sw, pw ^ 1, p.status, 40);   // the MMAs that read this weight stage are done
-                tc_fence_after();
-            }
-#pragma unroll
-            for (int t = 0; t < 2; ++t)
-                tc_st_frag(tmem_w + (uint32_t(32 * quarter + 16 * t) << 16) + sw * 32 + 8 * krow, w[t]);
-            tc_wait_st();
-            tc_fence_before();
-            __syncwarp();
+            decode_stage<BITS, CB>(t_ring + st * T_STAGE_BYTES, tmem_w + sw * 32, d, lane, ks >= SW, empty_w + 8 * sw, pw ^ 1, p.status);
             if (lane == 0) {
                 mbar_arrive(full_w + 8 * sw);
                 mbar_arrive(empty_t + 8 * st);
@@ -362,49 +410,189 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
         const float scale = __half2float(p.svh[size_t(z) * p.n + band * BN + n]);
         // exchange buffers [team][4 quarters][32 rows][32 lanes] in the activation ring, which is idle by then
         float* xch = reinterpret_cast<float*>(a_ring) + team * (4 * 32 * 32);
-        float sgn[5];   // -1 where this lane is the upper element of the butterfly of stride 2^i
-#pragma unroll
-        for (int i = 0; i < 5; ++i) sgn[i] = (lane >> i) & 1 ? -1.f : 1.f;
         mbar_wait_parked(acc_full, 0, p.status, team == 0 ? 1000 : 100);
         tc_fence_after();
-        for (int c0 = 32 * team; c0 < rows_pad; c0 += 32 * kEpiTeams) {
-            float v[32];
-            tc_ld32(tmem + (uint32_t(quarter * 32) << 16) + c0, v);
-            // 128-point Hadamard over n, strides ascending: 1..16 between the lanes of the warp
-            // (sgn * v + o is o - v or v + o, rounded once) ...
-#pragma unroll
-            for (int i = 0; i < 5; ++i) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __fmaf_rn(sgn[i], v[j], __shfl_xor_sync(dq::kFull, v[j], 1 << i));
-            }
-            // ... 32 and 64 between the four warps of the team, through shared memory
-#pragma unroll
-            for (int j = 0; j < 32; ++j) xch[(quarter * 32 + j) * 32 + lane] = v[j];
-            team_sync(team);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const float p1 = xch[((quarter ^ 1) * 32 + j) * 32 + lane];
-                const float p2 = xch[((quarter ^ 2) * 32 + j) * 32 + lane];
-                const float p3 = xch[((quarter ^ 3) * 32 + j) * 32 + lane];
-                const float a = (quarter & 1) ? __fsub_rn(p1, v[j]) : __fadd_rn(v[j], p1);      // stride 32: this quarter's pair
-                const float b = (quarter & 1) ? __fsub_rn(p3, p2) : __fadd_rn(p2, p3);          // stride 32: the pair 64 away
-                v[j] = (quarter & 2) ? __fsub_rn(b, a) : __fadd_rn(a, b);                       // stride 64
-            }
-            team_sync(team);   // xch may be overwritten by the next pass
-            const int col = band * BN + n;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int row = m0 + c0 + j;
-                if (row < row_end) {
-                    const float y = __fmul_rn(__fmul_rn(v[j], kRScale), scale);
-                    if (p.out_fp32) static_cast<float*>(p.c)[size_t(row) * p.n + col] = y;
-                    else static_cast<__half*>(p.c)[size_t(row) * p.n + col] = __float2half_rn(y);
-                }
-            }
-        }
+        for (int c0 = 32 * team; c0 < rows_pad; c0 += 32 * kEpiTeams)
+            epilogue_pass(tmem + (uint32_t(quarter * 32) << 16) + c0, xch, team, quarter, lane, scale, p.c, p.out_fp32, p.n,
+                          band * BN + n, m0 + c0, row_end);
         tc_fence_before();
     }
 
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- the grouped kernel
+// Persistent variant for the expert stacks of an MoE layer: work items are (problem, band) pairs, band
+// fastest; CTA c takes items c, c + gridDim.x, ...  The rings and the decode / MMA pipeline run on across
+// item boundaries, and with one 128-row sub-tile per problem the accumulator is double buffered, so the
+// epilogue of an item (four dedicated warps) overlaps the main loop of the next.  Per item the MMA covers
+// only the problem's rows (rounded up to 16).
+template <int BITS>
+struct GGeo {
+    static constexpr int T_STAGE_BYTES = TGeo<BITS>::T_STAGE_BYTES;
+    static constexpr size_t SMEM = TGeo<BITS>::SMEM + 4 * 32 * 32 * 4 /*exchange buffer of the epilogue*/;
+};
+
+template <int BITS, int CB>
+__global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __grid_constant__ CUtensorMap tmap_a,
+                                                                      const __grid_constant__ CUtensorMap tmap_t, const GemmArgs p)
+{
+    using TG_ = TGeo<BITS>;
+    constexpr int TROW_BYTES = TG_::TROW_BYTES, T_STAGE_BYTES = TG_::T_STAGE_BYTES;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int bands = p.n / BN;
+    const int chunk = p.nsub_max * SUB;
+    // (the table was written by kernels that completed before this launch)
+    const int nprob = min(max(__ldg(p.n_problems), 0), p.max_problems);
+    const int n_items = nprob * bands;
+    if (int(blockIdx.x) >= n_items) return;
+    const int my_items = (n_items - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
+    const int nbuf = p.nsub_max == 1 ? 2 : 1;           // accumulator buffers of `chunk` columns each
+    const int kstages = p.k / BK;
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* a_ring = smem;
+    unsigned char* t_ring = a_ring + SA * A_STAGE_BYTES;
+    float* xch = reinterpret_cast<float*>(t_ring + ST * T_STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(xch + 4 * 32 * 32);
+    __shared__ uint32_t s_tmem_base;
+
+    const uint32_t full_a = smem_u32(bars), empty_a = full_a + 8 * SA;
+    const uint32_t full_w = empty_a + 8 * SA, empty_w = full_w + 8 * SW;
+    const uint32_t full_t = empty_w + 8 * SW, empty_t = full_t + 8 * ST;
+    const uint32_t acc_full = empty_t + 8 * ST, acc_empty = acc_full + 16;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < SA; ++s) { mbar_init(full_a + 8 * s, 1); mbar_init(empty_a + 8 * s, 1); }
+        for (int s = 0; s < SW; ++s) { mbar_init(full_w + 8 * s, kDecodeWarps); mbar_init(empty_w + 8 * s, 1); }
+        for (int s = 0; s < ST; ++s) { mbar_init(full_t + 8 * s, 1); mbar_init(empty_t + 8 * s, kDecodeWarps); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full + 8 * b, 1); mbar_init(acc_empty + 8 * b, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem_base;
+    const uint32_t tmem_w = tmem + kAccCols;   // weight stages: 32 columns (64 k) each
+
+    // item `it` of this CTA -> its problem and band
+    auto item_at = [&](int it, int& band, GemvProblem& pr) {
+        const int item = int(blockIdx.x) + it * int(gridDim.x);
+        const int pi = item / bands;
+        band = item - pi * bands;
+        pr = load_problem(p.problems, pi, p.n_matrices, chunk, p.m);
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_t) : "memory");
+            int sa = 0, pa = 0, st = 0, pt = 0, cnt = 0;
+            for (int it = 0; it < my_items; ++it) {
+                int band; GemvProblem pr;
+                item_at(it, band, pr);
+                const int nsub = (pr.rows + SUB - 1) / SUB;
+                for (int ks = 0; ks < kstages; ++ks, ++cnt) {
+                    if (cnt >= ST) mbar_wait_parked(empty_t + 8 * st, pt ^ 1, p.status, 100);
+                    mbar_arrive_expect_tx(full_t + 8 * st, T_STAGE_BYTES);
+                    tma_load_3d(smem_u32(t_ring + st * T_STAGE_BYTES), &tmap_t, band * (TROW_BYTES / 8), ks * 4, pr.z, full_t + 8 * st);
+                    if (++st == ST) { st = 0; pt ^= 1; }
+                    if (cnt >= SA) mbar_wait_parked(empty_a + 8 * sa, pa ^ 1, p.status, 100);
+                    mbar_arrive_expect_tx(full_a + 8 * sa, max(nsub, 1) * A_SUB_BYTES);
+                    for (int sub = 0; sub < max(nsub, 1); ++sub)
+                        tma_load_2d(smem_u32(a_ring + sa * A_STAGE_BYTES + sub * A_SUB_BYTES), &tmap_a, ks * BK, pr.row0 + sub * SUB,
+                                    full_a + 8 * sa);
+                    if (++sa == SA) { sa = 0; pa ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (whole warp, one elected lane issues)
+        int sa = 0, pa = 0, sw = 0, pw = 0;
+        for (int it = 0; it < my_items; ++it) {
+            int band; GemvProblem pr;
+            item_at(it, band, pr);
+            const int rows_pad = max((pr.rows + 15) & ~15, 16);
+            const int n1 = min(rows_pad, 256), n2 = rows_pad - n1;
+            const uint32_t id1 = idesc_n(n1), id2 = idesc_n(n2 > 0 ? n2 : 16);
+            const int buf = it % nbuf;
+            const uint32_t tacc = tmem + buf * chunk;
+            if (it >= nbuf) {   // the epilogue has drained this accumulator
+                mbar_wait(acc_empty + 8 * buf, ((it / nbuf) - 1) & 1, p.status);
+                tc_fence_after();
+            }
+            for (int ks = 0; ks < kstages; ++ks) {
+                mbar_wait(full_a + 8 * sa, pa, p.status);
+                mbar_wait(full_w + 8 * sw, pw, p.status);
+                tc_fence_after();
+                const uint32_t x_base = smem_u32(a_ring + sa * A_STAGE_BYTES);
+                const uint64_t x_desc1 = smem_desc_sw128(x_base), x_desc2 = smem_desc_sw128(x_base + 2 * A_SUB_BYTES);
+                const uint32_t w_t = tmem_w + sw * 32;
+                const uint32_t bar_a = empty_a + 8 * sa, bar_w = empty_w + 8 * sw;
+                if (elect_one()) {
+#pragma unroll
+                    for (int k16 = 0; k16 < BK / 16; ++k16) {
+                        tc_mma_ts_f16(tacc, w_t + 8 * k16, x_desc1 + 2 * k16, id1, (ks | k16) ? 1u : 0u);
+                        if (n2 > 0) tc_mma_ts_f16(tacc + 256, w_t + 8 * k16, x_desc2 + 2 * k16, id2, (ks | k16) ? 1u : 0u);
+                    }
+                    tc_commit(bar_a);
+                    tc_commit(bar_w);
+                }
+                __syncwarp();
+                if (++sa == SA) { sa = 0; pa ^= 1; }
+                if (++sw == SW) { sw = 0; pw ^= 1; }
+            }
+            if (elect_one()) tc_commit(acc_full + 8 * buf);
+            __syncwarp();
+        }
+    } else if (warp >= kDecodeWarp0) {
+        // ------------------------------------------------------------ decode warps
+        const int d = warp - kDecodeWarp0;
+        int st = 0, pt = 0, sw = 0, pw = 0;
+        const int total = my_items * kstages;
+        for (int cnt = 0; cnt < total; ++cnt) {
+            mbar_wait_parked(full_t + 8 * st, pt, p.status, 40);
+            decode_stage<BITS, CB>(t_ring + st * T_STAGE_BYTES, tmem_w + sw * 32, d, lane, cnt >= SW, empty_w + 8 * sw, pw ^ 1, p.status);
+            if (lane == 0) {
+                mbar_arrive(full_w + 8 * sw);
+                mbar_arrive(empty_t + 8 * st);
+            }
+            if (++st == ST) { st = 0; pt ^= 1; }
+            if (++sw == SW) { sw = 0; pw ^= 1; }
+        }
+    } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + 4) {
+        // ------------------------------------------------------------ epilogue warps
+        const int quarter = warp & 3;
+        const int n = quarter * 32 + lane;
+        for (int it = 0; it < my_items; ++it) {
+            int band; GemvProblem pr;
+            item_at(it, band, pr);
+            const float scale = __half2float(p.svh[size_t(pr.z) * p.n + band * BN + n]);
+            const int buf = it % nbuf;
+            mbar_wait_parked(acc_full + 8 * buf, (it / nbuf) & 1, p.status, 200);
+            tc_fence_after();
+            const int rows_pad = (pr.rows + 15) & ~15;
+            for (int c0 = 0; c0 < rows_pad; c0 += 32)
+                epilogue_pass(tmem + buf * chunk + (uint32_t(quarter * 32) << 16) + c0, xch, 0, quarter, lane, scale, p.c, p.out_fp32,
+                              p.n, band * BN + n, pr.row0 + c0, pr.row0 + pr.rows);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + 8 * buf);
+        }
+    }
+
+    tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
@@ -475,7 +663,20 @@ void launch_tc(const void* a_had, const void* trellis, const GemmArgs& args, cud
     const CUtensorMap map_a = make_map(CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a_had, cuuint64_t(args.k), cuuint64_t(args.m),
                                        cuuint64_t(args.k) * 2, BK, SUB, CU_TENSOR_MAP_SWIZZLE_128B);
     const CUtensorMap map_t = make_trellis_map(trellis, args.problems ? args.n_matrices : 1, args.k, args.n, BITS, TG_::TROW_BYTES);
-    dim3 grid(args.n / BN, args.problems ? args.max_problems : (args.m + args.nsub_max * SUB - 1) / (args.nsub_max * SUB));
+    if (args.problems) {
+        auto gk = k_exl3_gemm_tc_grouped<BITS, CB>;
+        static bool gattr_set[kMaxDevices] = {};
+        if (!gattr_set[dev]) {
+            cuda_ok(cudaFuncSetAttribute(gk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(GGeo<BITS>::SMEM)), "grouped gemm smem attribute");
+            gattr_set[dev] = true;
+        }
+        const long long items = (long long) args.max_problems * (args.n / BN);
+        const int grid = int(std::min<long long>(items, device_info(dev).sms));
+        gk<<<grid, kThreads, GGeo<BITS>::SMEM, stream>>>(map_a, map_t, args);
+        cuda_ok(cudaGetLastError(), "k_exl3_gemm_tc_grouped launch");
+        return;
+    }
+    dim3 grid(args.n / BN, (args.m + args.nsub_max * SUB - 1) / (args.nsub_max * SUB));
     kern<<<grid, kThreads, TG_::SMEM, stream>>>(map_a, map_t, args);
     cuda_ok(cudaGetLastError(), "k_exl3_gemm_tc launch");
 }
@@ -612,7 +813,7 @@ std::string launch_gemm_tc_grouped(const void* xr, void* xr_had, const void* tre
     args.nsub_max = nsub;
     args.problems = problems; args.n_problems = n_problems; args.max_problems = max_problems; args.n_matrices = n_matrices;
     launch_tc_bits(k_bits, codebook, xr_had, trellis_stack, args, stream);
-    return "k_rotate_rows_plain + k_exl3_gemm_tc<" + std::to_string(k_bits) + "," + std::to_string(codebook) + ",grouped> grid=" +
+    return "k_rotate_rows_plain + k_exl3_gemm_tc_grouped<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "> persistent items<=" +
            std::to_string(size_n / BN) + "x" + std::to_string(max_problems) + " block=" + std::to_string(kThreads) + " tile=" +
            std::to_string(nsub * SUB) + "x128x64 tmem=512";
 }

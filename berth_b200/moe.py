@@ -166,12 +166,21 @@ class GpuStages:
                                                  self.ews_loc.numel(), self.max_rows, self.rows_hint(R, self.d["n_experts"]), None))
         return yr
 
-    def shared_expert(self, x):
+    def shared_expert(self, x, stream=None):
+        """Shared expert of x on the current stream, or on `stream` (only for more than 32 rows: the decode
+        kernels share one per-device scratch, so they must stay on one stream; the prefill kernels do not)."""
         if self.shared is None:
             return None
         from .kernels import OutDtype, ops
         g, gate, up, down = self.shared
         T = x.shape[0]
+        if stream is not None:
+            if T <= 32:
+                raise Error("shared expert: the decode kernels must stay on the layer's stream")
+            if getattr(self, "_side_gpu", None) is None or self._side_gpu.stream is not stream:
+                from .engine import Gpu
+                self._side_gpu = Gpu(g.device.index if hasattr(g.device, "index") else g.device, stream=stream)
+            g = self._side_gpu
         si, H = self.d["shared_inter"], self.d["hidden"]
         a = torch.empty((T, si), dtype=torch.float16, device=self.device)
         b = torch.empty((T, si), dtype=torch.float16, device=self.device)
@@ -183,7 +192,7 @@ class GpuStages:
             fwd = lambda lin, i, o: lin.forward_rows(g, T, i, o, OutDtype.F16, sc)
         fwd(gate, x, a)
         fwd(up, x, b)
-        ops.silu_mul(a, b, a, T * si, 0.0)
+        ops.silu_mul(a, b, a, T * si, 0.0, g.stream)
         fwd(down, a, y)
         return y
 
@@ -219,35 +228,69 @@ class EpMoeLayer:
         self.last_stats = {}
 
     def forward(self, x: torch.Tensor):
-        """x fp16 [T_local][hidden] -> (out fp32 [T_local][hidden], topk_idx, topk_w)."""
+        """x fp16 [T_local][hidden] -> (out fp32 [T_local][hidden], topk_idx, topk_w).
+
+        Exchange steps per layer: one all-to-all of per-expert row counts (fixed size, so it needs nothing
+        from the host), ONE host read of the resulting send/receive sizes, one all-to-all of the routed rows
+        and one of the expert outputs.  The expert id of every received row follows from the counts (a
+        source sends its rows sorted by expert), so no key travels with the rows.  The shared expert runs on
+        a side stream while the rows are away."""
         dist, st = self.dist, self.stages
-        T, k, W = x.shape[0], self.k, self.world
+        T, k, W, nl = x.shape[0], self.k, self.world, self.n_local
+        dev = x.device
         if T:
             idx, w = st.route(x)
         else:   # a rank without tokens still takes part in the exchanges
-            idx = torch.empty((0, k), dtype=torch.int32, device=x.device)
-            w = torch.empty((0, k), dtype=torch.float32, device=x.device)
+            idx = torch.empty((0, k), dtype=torch.int32, device=dev)
+            w = torch.empty((0, k), dtype=torch.float32, device=dev)
         keys = idx.reshape(-1)
         perm, inv, offsets = st.sort(keys, 0, self.E)                     # rows sorted by expert = by rank
+        ysh = self._shared_async(x) if T else None
         send_rows = st.gather(x, perm, k)
-        send_keys = keys[perm.long()].contiguous()
-        bounds = offsets[:: self.n_local].to("cpu", torch.int64)          # first row of every rank's block (host sync)
-        send_counts = (bounds[1:] - bounds[:-1]).tolist()
-        counts_dev = torch.tensor(send_counts, dtype=torch.int64, device=x.device)
-        recv_dev = torch.empty_like(counts_dev)
-        dist.all_to_all_single(recv_dev, counts_dev, group=self.group)
-        recv_counts = recv_dev.tolist()
+        cnt_send = (offsets[1:] - offsets[:-1]).contiguous()             # rows per expert, [W * n_local]
+        cnt_recv = torch.empty_like(cnt_send)                              # [source rank][local expert]
+        dist.all_to_all_single(cnt_recv, cnt_send, group=self.group)
+        sizes = torch.stack((cnt_send.view(W, nl).sum(1), cnt_recv.view(W, nl).sum(1))).to("cpu")   # the one host sync
+        send_counts, recv_counts = sizes[0].tolist(), sizes[1].tolist()
         R = sum(recv_counts)
-        recv_rows = torch.empty((R, x.shape[1]), dtype=x.dtype, device=x.device)
-        recv_keys = torch.empty(R, dtype=torch.int32, device=x.device)
+        recv_rows = torch.empty((R, x.shape[1]), dtype=x.dtype, device=dev)
         dist.all_to_all_single(recv_rows, send_rows, recv_counts, send_counts, group=self.group)
-        dist.all_to_all_single(recv_keys, send_keys, recv_counts, send_counts, group=self.group)
-        perm2, inv2, _ = st.sort(recv_keys, self.e0, self.n_local, for_experts=True)   # regroup by local expert
+        # expert of every received row: source by source, experts ascending, cnt_recv[s][e] rows each
+        local_ids = (torch.arange(nl, dtype=torch.int32, device=dev) + self.e0).repeat(W)
+        recv_keys = torch.repeat_interleave(local_ids, cnt_recv.long(), output_size=R) if R else \
+            torch.empty(0, dtype=torch.int32, device=dev)
+        perm2, inv2, _ = st.sort(recv_keys, self.e0, nl, for_experts=True)   # regroup by local expert
         xr = st.gather(recv_rows, perm2, 1)
         yr = st.experts(xr)
         back = st.gather(yr, inv2, 1)                                      # expert outputs in arrival order
         y_sorted = torch.empty_like(send_rows)
         dist.all_to_all_single(y_sorted, back, send_counts, recv_counts, group=self.group)
-        out = st.combine(y_sorted, inv, w, st.shared_expert(x)) if T else torch.empty((0, x.shape[1]), dtype=torch.float32, device=x.device)
+        if T:
+            if ysh is not None and not self._shared_inline:
+                torch.cuda.current_stream(dev).wait_event(self._shared_done)
+            out = st.combine(y_sorted, inv, w, ysh)
+        else:
+            out = torch.empty((0, x.shape[1]), dtype=torch.float32, device=dev)
         self.last_stats = {"sent_rows": T * k, "recv_rows": R, "send_counts": send_counts, "recv_counts": recv_counts}
         return out, idx, w
+
+    def _shared_async(self, x):
+        """Shared expert of the local tokens; on a CUDA device on a side stream, so that it overlaps the
+        exchange and the routed experts (the caller waits for self._shared_done before the combine)."""
+        st = self.stages
+        if x.device.type != "cuda" or getattr(st, "shared", None) is None or x.shape[0] <= 32:
+            self._shared_inline = True
+            return st.shared_expert(x)
+        self._shared_inline = False
+        if not hasattr(self, "_side"):
+            self._side = torch.cuda.Stream(device=x.device)
+            self._shared_done = torch.cuda.Event()
+        main = torch.cuda.current_stream(x.device)
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            ysh = st.shared_expert(x, stream=self._side)
+            self._shared_done.record(self._side)
+        x.record_stream(self._side)
+        if ysh is not None:
+            ysh.record_stream(main)
+        return ysh
