@@ -159,13 +159,16 @@ __global__ void __launch_bounds__(256) k_moe_count(const int32_t* __restrict__ k
 
 // offsets[0..n_local] = exclusive scan of counts; problem table: every expert's rows in chunks of
 // `chunk` rows, experts in ascending order.  One block of 1024 threads, one expert per thread.
+// With extra_rows > 0 one more matrix (index n_local, the shared expert held behind the stack) takes
+// extra_rows rows after the routed ones: offsets[n_local + 1] then ends the table.
 __global__ void __launch_bounds__(1024) k_moe_scan(const int* __restrict__ counts, int* __restrict__ offsets,
                                                    GemvProblem* __restrict__ problems, int* __restrict__ n_problems,
-                                                   int n_local, int chunk)
+                                                   int n_routed, int chunk, int extra_rows)
 {
     __shared__ int wrows[32], wprob[32];
     const int j = threadIdx.x, lane = j & 31, warp = j >> 5;
-    const int c = j < n_local ? counts[j] : 0;
+    const int n_local = n_routed + (extra_rows > 0 ? 1 : 0);
+    const int c = j < n_routed ? counts[j] : (j < n_local ? extra_rows : 0);
     const int np = (c + chunk - 1) / chunk;
     int prow = c, pprob = np;     // inclusive warp scans
 #pragma unroll
@@ -317,7 +320,7 @@ ExpertScratch carve_experts(void* base, int R, int n_local, int hidden, int inte
     const int kmax = std::max(hidden, inter);
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += align256(bytes); return o; };
-    const size_t o_counts = take(size_t(n_local) * 4), o_offsets = take(size_t(n_local + 1) * 4), o_np = take(4);
+    const size_t o_counts = take(size_t(n_local) * 4), o_offsets = take(size_t(n_local + 2) * 4), o_np = take(4);
     const size_t o_prob = take(size_t(s.max_problems) * sizeof(GemvProblem));
     // rotated activations: fragment order per problem (GEMV) or plain rows (GEMM)
     const size_t o_afrag = take(plan.tg ? size_t(s.max_problems) * (kmax / 16) * plan.tg * 256 : size_t(R) * kmax * 2);
@@ -331,6 +334,21 @@ ExpertScratch carve_experts(void* base, int R, int n_local, int hidden, int inte
         s.g = (__half*) (b + o_g); s.u = (__half*) (b + o_u);
     }
     return s;
+}
+
+// True if the shared expert has the experts' shape and each of its nine tensors starts exactly where the
+// corresponding stack of n_experts matrices ends, i.e. the stacks really hold n_experts + 1 matrices.
+bool shared_behind_stacks(const berth_moe_weights* w)
+{
+    if (w->shared_inter <= 0 || w->shared_inter != w->inter) return false;
+    const size_t E = size_t(w->n_experts), H = size_t(w->hidden), I = size_t(w->inter);
+    const size_t t_hi = H / 16 * (I / 16) * 16 * size_t(w->k_bits) * 2;   // bytes of one hidden x inter trellis
+    auto at = [](const void* base, size_t bytes) { return static_cast<const void*>(static_cast<const char*>(base) + bytes); };
+    return w->sh_gate_trellis == at(w->gate_trellis, E * t_hi) && w->sh_up_trellis == at(w->up_trellis, E * t_hi) &&
+           w->sh_down_trellis == at(w->down_trellis, E * t_hi) && w->sh_gate_suh == at(w->gate_suh, E * H * 2) &&
+           w->sh_gate_svh == at(w->gate_svh, E * I * 2) && w->sh_up_suh == at(w->up_suh, E * H * 2) &&
+           w->sh_up_svh == at(w->up_svh, E * I * 2) && w->sh_down_suh == at(w->down_suh, E * I * 2) &&
+           w->sh_down_svh == at(w->down_svh, E * H * 2);
 }
 
 void check_moe_shapes(const berth_moe_weights* w, int T)
@@ -368,11 +386,12 @@ void router_topk(const void* x, const void* w_router, const float* bias, int32_t
 
 // keys[n] -> counts/offsets/problems + perm/inv; experts [e0, e0 + n_local).
 void dispatch(const int32_t* keys, int n, int e0, int n_local, int chunk, const ExpertScratch& s, int32_t* perm, int32_t* inv,
-              cudaStream_t st)
+              cudaStream_t st, int extra_rows = 0)
 {
+    if (n_local + (extra_rows > 0 ? 1 : 0) > 1024) throw std::runtime_error("moe: too many local experts for the scan kernel");
     k_moe_count<<<n_local, 256, 0, st>>>(keys, n, e0, s.counts);
     cuda_ok(cudaGetLastError(), "k_moe_count launch");
-    k_moe_scan<<<1, 1024, 0, st>>>(s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk);
+    k_moe_scan<<<1, 1024, 0, st>>>(s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows);
     cuda_ok(cudaGetLastError(), "k_moe_scan launch");
     k_moe_scatter<<<n_local, 256, 0, st>>>(keys, n, e0, s.offsets, perm, inv);
     cuda_ok(cudaGetLastError(), "k_moe_scatter launch");
@@ -519,11 +538,12 @@ extern "C" size_t berth_moe_workspace_bytes(int T, int hidden, int inter, int sh
 {
     if (T < 1 || hidden < 128 || inter < 128 || n_experts < 1 || top_k < 1) return 0;
     const int R = T * top_k;
-    const ExpertScratch es = carve_experts(nullptr, R, n_experts, hidden, inter, expert_plan(routed_rows_hint(T, top_k, n_experts)));
+    // sized for the layout with the shared expert's rows behind the routed ones (T more rows, one more matrix)
+    const ExpertScratch es = carve_experts(nullptr, R + T, n_experts + 1, hidden, inter, expert_plan(routed_rows_hint(T, top_k, n_experts)));
     size_t total = 0;
     total += align256(size_t(T) * n_experts * 4);            // logits
     total += 2 * align256(size_t(R) * 4);                    // perm, inv
-    total += 2 * align256(size_t(R) * hidden * 2);           // xr, yr
+    total += 2 * align256(size_t(R + T) * hidden * 2);       // xr, yr
     total += es.bytes;
     if (shared_inter > 0) {
         total += 3 * align256(size_t(T) * shared_inter * 2);                 // shared gate, up outputs + rotated
@@ -560,20 +580,26 @@ extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T,
         float* logits = (float*) take(size_t(T) * E * 4);
         int32_t* perm = (int32_t*) take(size_t(R) * 4);
         int32_t* inv = (int32_t*) take(size_t(R) * 4);
-        __half* xr = (__half*) take(size_t(R) * H * 2);
-        __half* yr = (__half*) take(size_t(R) * H * 2);
-        ExpertScratch es = carve_experts(b, R, E, H, I, plan);
-        b += es.bytes;
+        // A shared expert whose tensors sit directly behind the expert stacks (and has the experts' shape) is
+        // run as matrix E of the grouped launches: its rows are the layer's own tokens, appended to the routed rows.
+        const bool fused_shared = shared_behind_stacks(w);
+        const int RT = fused_shared ? R + T : R, NM = fused_shared ? E + 1 : E;
+        __half* xr = (__half*) take(size_t(R + T) * H * 2);
+        __half* yr = (__half*) take(size_t(R + T) * H * 2);
+        ExpertScratch es = carve_experts(b, RT, NM, H, I, plan);
+        b += carve_experts(nullptr, R + T, E + 1, H, I, plan).bytes;
 
         router_topk(x, w->w_router, w->router_bias, topk_idx, topk_w, logits, T, H, E, K, cs);
-        dispatch(topk_idx, R, 0, E, plan.chunk, es, perm, inv, cs);
+        dispatch(topk_idx, R, 0, E, plan.chunk, es, perm, inv, cs, fused_shared ? T : 0);
         k_moe_gather_rows<<<std::min(R, 148 * 8), 256, 0, cs>>>((const __half*) x, perm, es.offsets + E, K, xr, H);
         cuda_ok(cudaGetLastError(), "k_moe_gather_rows launch");
+        if (fused_shared)
+            cuda_ok(cudaMemcpyAsync(xr + size_t(R) * H, x, size_t(T) * H * 2, cudaMemcpyDeviceToDevice, cs), "moe layer: shared rows copy");
         st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
-                            w->down_suh, w->down_svh, E, xr, yr, R, R, plan, es, sc, info.sms, cs);
+                            w->down_suh, w->down_svh, NM, xr, yr, RT, RT, plan, es, sc, info.sms, cs);
 
-        __half* ysh = nullptr;
-        if (SI > 0) {
+        __half* ysh = fused_shared ? yr + size_t(R) * H : nullptr;
+        if (SI > 0 && !fused_shared) {
             if (!w->sh_gate_trellis || !w->sh_up_trellis || !w->sh_down_trellis) throw std::runtime_error("moe layer: null shared-expert pointer");
             __half* sg = (__half*) take(size_t(T) * SI * 2);
             __half* su = (__half*) take(size_t(T) * SI * 2);
@@ -588,6 +614,6 @@ extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T,
         k_moe_combine<<<T, 256, 0, cs>>>(yr, inv, topk_w, ysh, (float*) out, H, K);
         cuda_ok(cudaGetLastError(), "k_moe_combine launch");
         st.launch = "k_moe_router_logits + k_moe_topk + k_moe_count/scan/scatter + k_moe_gather_rows + 3 x (" + st.launch +
-                    ") + k_silu_mul + k_moe_combine";
+                    ") + k_silu_mul + k_moe_combine" + (fused_shared ? " [shared expert as matrix E of the grouped launches]" : "");
     });
 }

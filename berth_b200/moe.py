@@ -39,7 +39,7 @@ class MoeLayer:
     """One MoE layer resident on a GPU.  ``weights`` is the dict of ``berth_b200.synth.moe_layer_weights``
     (or the same keys filled from a checkpoint): numpy arrays are uploaded, torch tensors are kept."""
 
-    def __init__(self, device: torch.device, weights: dict, max_tokens: int):
+    def __init__(self, device: torch.device, weights: dict, max_tokens: int, fuse_shared: bool = True):
         self.device = device
         self.dims = {k: int(weights[k]) for k in ("hidden", "inter", "shared_inter", "n_experts", "top_k", "bits", "cb")}
         self._keep = {}
@@ -47,16 +47,36 @@ class MoeLayer:
         self.c.hidden, self.c.inter, self.c.shared_inter = self.dims["hidden"], self.dims["inter"], self.dims["shared_inter"]
         self.c.n_experts, self.c.top_k = self.dims["n_experts"], self.dims["top_k"]
         self.c.k_bits, self.c.codebook = self.dims["bits"], self.dims["cb"]
+        def on_device(v):
+            if isinstance(v, torch.Tensor):
+                return v.to(device)
+            a = np.ascontiguousarray(v)
+            if a.dtype == np.uint16:
+                a = a.view(np.int16)
+            return torch.from_numpy(a).to(device)
+
+        # A shared expert of the experts' shape is stored as matrix n_experts of every stack: the library then
+        # runs it inside the grouped expert launches instead of three launches of its own.
+        stacked = set()
+        if self.dims["shared_inter"] == self.dims["inter"] and fuse_shared and \
+                all(weights.get(f"sh_{p}_{k}") is not None for p in ("gate", "up", "down") for k in ("trellis", "suh", "svh")):
+            E = self.dims["n_experts"]
+            for p in ("gate", "up", "down"):
+                for k in ("trellis", "suh", "svh"):
+                    both = torch.cat((on_device(weights[f"{p}_{k}"]), on_device(weights[f"sh_{p}_{k}"]).unsqueeze(0)))
+                    self._keep[f"{p}_{k}"] = both
+                    self._keep[f"sh_{p}_{k}"] = both[E]
+                    setattr(self.c, f"{p}_{k}", both.data_ptr())
+                    setattr(self.c, f"sh_{p}_{k}", both[E].data_ptr())
+                    stacked.update((f"{p}_{k}", f"sh_{p}_{k}"))
         for name in _PTR_FIELDS:
+            if name in stacked:
+                continue
             v = weights.get(name)
             if v is None:
                 setattr(self.c, name, None)
                 continue
-            if not isinstance(v, torch.Tensor):
-                a = np.ascontiguousarray(v)
-                if a.dtype == np.uint16:
-                    a = a.view(np.int16)
-                v = torch.from_numpy(a).to(device)
+            v = on_device(v)
             self._keep[name] = v
             setattr(self.c, name, v.data_ptr())
         self.max_tokens = 0

@@ -52,9 +52,9 @@ def test_router_ties_and_bias(oracle):
     assert (idx == exp_idx).all()
 
 
-def _run_layer(wts, x):
+def _run_layer(wts, x, fuse_shared=True):
     T = x.shape[0]
-    layer = moe.MoeLayer(torch.device("cuda"), wts, T)
+    layer = moe.MoeLayer(torch.device("cuda"), wts, T, fuse_shared=fuse_shared)
     out = torch.full((T, wts["hidden"]), float("nan"), dtype=torch.float32, device="cuda")
     idx = torch.empty((T, wts["top_k"]), dtype=torch.int32, device="cuda")
     w = torch.empty((T, wts["top_k"]), dtype=torch.float32, device="cuda")
@@ -135,7 +135,7 @@ def test_expert_parallel_stages_match_fused_layer(T):
     H, I, E, k, bits, cb = 256, 128, 32, 4, 4, 2
     wts = synth.moe_layer_weights(1234, "ep1", H, I, E, k, bits, cb, shared_inter=128)
     x = synth.activations(1234, f"ep1.x{T}", T, H)
-    ref, ref_idx, _ = _run_layer(wts, x)
+    ref, ref_idx, _ = _run_layer(wts, x, fuse_shared=False)   # the staged host runs the shared expert through its own linears
     stages = moe.GpuStages(torch.device("cuda", torch.cuda.current_device()), wts, E, max_rows=T * k, max_rows_per_expert=T)
     layer = moe.EpMoeLayer.__new__(moe.EpMoeLayer)
     layer.dist, layer.group, layer.stages = _OneRankDist, None, stages
@@ -146,3 +146,18 @@ def test_expert_parallel_stages_match_fused_layer(T):
     rms = np.sqrt((ref.astype(np.float64) ** 2).mean())
     assert np.abs(out.cpu().numpy() - ref).max() <= 1e-3 * rms
     assert layer.last_stats["recv_rows"] == T * k
+
+
+@pytest.mark.parametrize("T", [1, 40, 130])
+def test_shared_expert_inside_the_grouped_launches(T):
+    """A shared expert stored behind the expert stacks runs as matrix E of the grouped launches; the result
+    agrees with the layer that runs it through three linears of its own (same routing, outputs within the
+    fp16 rounding of the intermediate activations)."""
+    H, I, E, k = 256, 128, 32, 4
+    wts = synth.moe_layer_weights(1234, "fuse", H, I, E, k, 4, 2, shared_inter=I)
+    x = synth.activations(1234, f"fuse.x{T}", T, H)
+    fused, idx_f, w_f = _run_layer(wts, x, fuse_shared=True)
+    plain, idx_p, w_p = _run_layer(wts, x, fuse_shared=False)
+    assert (idx_f == idx_p).all() and (w_f == w_p).all()
+    rms = np.sqrt((plain.astype(np.float64) ** 2).mean())
+    assert np.abs(fused - plain).max() <= 5e-3 * rms
