@@ -208,41 +208,73 @@ __device__ __forceinline__ bool elect_one()
 }
 
 // One epilogue pass of a team of four warps (one per TMEM lane quarter; barrier id `team` + 1): 32 token
-// rows (accumulator columns tacc .. tacc+31 of the warp's lanes) of one band.  A thread owns output column
-// n = 32*quarter + lane: 128-point Hadamard over n with ascending strides -- 1..16 between the lanes of
-// the warp (sgn * v + o is o - v or v + o, rounded once), 32 and 64 between the four warps through the
-// 16 KiB exchange buffer xch -- then the output scale and the stores of rows row0 .. row0+31 below row_end.
-__device__ __noinline__ void epilogue_pass(uint32_t tacc, float* xch, int team, int quarter, int lane, float scale, void* c,
-                                              int out_fp32, int ldc, int col, int row0, int row_end)
+// rows (accumulator columns tacc .. tacc+31 of the warp's lanes) of one band.  The accumulator has one
+// output column n per TMEM lane, so a thread first holds 32 rows of one n; the tile is transposed through
+// shared memory (xch, kXchFloats floats, rows of 129 with the 32-blocks rotated by 8 per block: no bank
+// conflict on either side) so that thread t then holds the 32 consecutive n of block t%4 of row t/4.
+// 128-point Hadamard over n with ascending strides: 1..16 in registers, 32 and 64 between the four
+// threads of a row by shuffles (sgn * v + o is o - v or v + o, rounded once); then the output scale
+// (svh_s: the band's 128 scales as fp32) and 16-byte stores of rows row0 .. row0+31 below row_end.
+constexpr int kXchPitch = 129;
+constexpr int kXchFloats = 32 * kXchPitch;
+__device__ __noinline__ void epilogue_pass(uint32_t tacc, float* xch, const float* svh_s, int team, int quarter, int lane, void* c,
+                                           int out_fp32, int ldc, int col0, int row0, int row_end)
 {
     float v[32];
     tc_ld32(tacc, v);
+    {
+        float* wp = xch + 32 * quarter + ((lane - 8 * quarter) & 31);
 #pragma unroll
-    for (int i = 0; i < 5; ++i) {
-        const float sgn = (lane >> i) & 1 ? -1.f : 1.f;   // -1 where this lane is the upper element of the butterfly
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __fmaf_rn(sgn, v[j], __shfl_xor_sync(dq::kFull, v[j], 1 << i));
+        for (int j = 0; j < 32; ++j) wp[j * kXchPitch] = v[j];
     }
-#pragma unroll
-    for (int j = 0; j < 32; ++j) xch[(quarter * 32 + j) * 32 + lane] = v[j];
     team_sync(team);
+    const int t = quarter * 32 + lane, r = t >> 2, cc = t & 3;
+    {
+        const float* rp = xch + r * kXchPitch + 32 * cc;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        const float p1 = xch[((quarter ^ 1) * 32 + j) * 32 + lane];
-        const float p2 = xch[((quarter ^ 2) * 32 + j) * 32 + lane];
-        const float p3 = xch[((quarter ^ 3) * 32 + j) * 32 + lane];
-        const float a = (quarter & 1) ? __fsub_rn(p1, v[j]) : __fadd_rn(v[j], p1);      // stride 32: this quarter's pair
-        const float b = (quarter & 1) ? __fsub_rn(p3, p2) : __fadd_rn(p2, p3);          // stride 32: the pair 64 away
-        v[j] = (quarter & 2) ? __fsub_rn(b, a) : __fadd_rn(a, b);                       // stride 64
+        for (int i = 0; i < 32; ++i) v[i] = rp[(i - 8 * cc) & 31];
     }
     team_sync(team);   // xch may be overwritten by the next pass
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        const int row = row0 + j;
-        if (row < row_end) {
-            const float y = __fmul_rn(__fmul_rn(v[j], kRScale), scale);
-            if (out_fp32) static_cast<float*>(c)[size_t(row) * ldc + col] = y;
-            else static_cast<__half*>(c)[size_t(row) * ldc + col] = __float2half_rn(y);
+    for (int s = 1; s < 32; s <<= 1)
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (!(i & s)) {
+                const float a = v[i], b = v[i | s];
+                v[i] = __fadd_rn(a, b);
+                v[i | s] = __fsub_rn(a, b);
+            }
+#pragma unroll
+    for (int bit = 0; bit < 2; ++bit) {
+        const float sgn = (cc >> bit) & 1 ? -1.f : 1.f;   // -1 where this thread holds the upper block of the butterfly
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __fmaf_rn(sgn, v[i], __shfl_xor_sync(dq::kFull, v[i], 1 << bit));
+    }
+    const int row = row0 + r;
+    if (row < row_end) {
+        const float* sp = svh_s + 32 * cc;
+        if (out_fp32) {
+            float* dst = static_cast<float*>(c) + size_t(row) * ldc + col0 + 32 * cc;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                const float4 sc = *reinterpret_cast<const float4*>(sp + i);
+                float4 o;
+                o.x = __fmul_rn(__fmul_rn(v[i], kRScale), sc.x); o.y = __fmul_rn(__fmul_rn(v[i + 1], kRScale), sc.y);
+                o.z = __fmul_rn(__fmul_rn(v[i + 2], kRScale), sc.z); o.w = __fmul_rn(__fmul_rn(v[i + 3], kRScale), sc.w);
+                *reinterpret_cast<float4*>(dst + i) = o;
+            }
+        } else {
+            __half* dst = static_cast<__half*>(c) + size_t(row) * ldc + col0 + 32 * cc;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                const float4 s0 = *reinterpret_cast<const float4*>(sp + i), s1 = *reinterpret_cast<const float4*>(sp + i + 4);
+                uint4 o;
+                o.x = dq::pack_half2(__float2half_rn(__fmul_rn(__fmul_rn(v[i], kRScale), s0.x)), __float2half_rn(__fmul_rn(__fmul_rn(v[i + 1], kRScale), s0.y)));
+                o.y = dq::pack_half2(__float2half_rn(__fmul_rn(__fmul_rn(v[i + 2], kRScale), s0.z)), __float2half_rn(__fmul_rn(__fmul_rn(v[i + 3], kRScale), s0.w)));
+                o.z = dq::pack_half2(__float2half_rn(__fmul_rn(__fmul_rn(v[i + 4], kRScale), s1.x)), __float2half_rn(__fmul_rn(__fmul_rn(v[i + 5], kRScale), s1.y)));
+                o.w = dq::pack_half2(__float2half_rn(__fmul_rn(__fmul_rn(v[i + 6], kRScale), s1.z)), __float2half_rn(__fmul_rn(__fmul_rn(v[i + 7], kRScale), s1.w)));
+                *reinterpret_cast<uint4*>(dst + i) = o;
+            }
         }
     }
 }
@@ -408,13 +440,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
         const int quarter = warp & 3;
         const int n = quarter * 32 + lane;
         const float scale = __half2float(p.svh[size_t(z) * p.n + band * BN + n]);
-        // exchange buffers [team][4 quarters][32 rows][32 lanes] in the activation ring, which is idle by then
-        float* xch = reinterpret_cast<float*>(a_ring) + team * (4 * 32 * 32);
         mbar_wait_parked(acc_full, 0, p.status, team == 0 ? 1000 : 100);
         tc_fence_after();
+        // per team: transposition buffer and the band's scales, in the activation ring, which is idle by now
+        float* xch = reinterpret_cast<float*>(a_ring) + team * (kXchFloats + 128);
+        float* svh_s = xch + kXchFloats;
+        svh_s[n] = scale;
+        team_sync(team);
         for (int c0 = 32 * team; c0 < rows_pad; c0 += 32 * kEpiTeams)
-            epilogue_pass(tmem + (uint32_t(quarter * 32) << 16) + c0, xch, team, quarter, lane, scale, p.c, p.out_fp32, p.n,
-                          band * BN + n, m0 + c0, row_end);
+            epilogue_pass(tmem + (uint32_t(quarter * 32) << 16) + c0, xch, svh_s, team, quarter, lane, p.c, p.out_fp32, p.n, band * BN,
+                          m0 + c0, row_end);
         tc_fence_before();
     }
 
@@ -434,7 +469,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
 template <int BITS>
 struct GGeo {
     static constexpr int T_STAGE_BYTES = TGeo<BITS>::T_STAGE_BYTES;
-    static constexpr size_t SMEM = TGeo<BITS>::SMEM + 4 * 32 * 32 * 4 /*exchange buffer of the epilogue*/;
+    static constexpr size_t SMEM = TGeo<BITS>::SMEM + (kXchFloats + 2 * 128) * 4 /*transposition buffer and scales of the epilogue*/;
 };
 
 template <int BITS, int CB>
@@ -460,7 +495,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
     unsigned char* a_ring = smem;
     unsigned char* t_ring = a_ring + SA * A_STAGE_BYTES;
     float* xch = reinterpret_cast<float*>(t_ring + ST * T_STAGE_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(xch + 4 * 32 * 32);
+    float* svh_s = xch + kXchFloats;                   // two buffers of 128 scales, alternating between items
+    uint64_t* bars = reinterpret_cast<uint64_t*>(svh_s + 2 * 128);
     __shared__ uint32_t s_tmem_base;
 
     const uint32_t full_a = smem_u32(bars), empty_a = full_a + 8 * SA;
@@ -479,6 +515,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // the problems of this CTA's first items, so that no role waits for the table at an item boundary
+    constexpr int kCachedItems = 64;
+    __shared__ GemvProblem s_prob[kCachedItems];
+    if (int(threadIdx.x) >= 64 && int(threadIdx.x) < 64 + min(my_items, kCachedItems)) {
+        const int item = int(blockIdx.x) + (int(threadIdx.x) - 64) * int(gridDim.x);
+        s_prob[threadIdx.x - 64] = load_problem(p.problems, item / bands, p.n_matrices, chunk, p.m);
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -490,7 +533,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
         const int item = int(blockIdx.x) + it * int(gridDim.x);
         const int pi = item / bands;
         band = item - pi * bands;
-        pr = load_problem(p.problems, pi, p.n_matrices, chunk, p.m);
+        pr = it < kCachedItems ? s_prob[it] : load_problem(p.problems, pi, p.n_matrices, chunk, p.m);
     };
 
     if (warp == 0) {
@@ -578,14 +621,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
         for (int it = 0; it < my_items; ++it) {
             int band; GemvProblem pr;
             item_at(it, band, pr);
-            const float scale = __half2float(p.svh[size_t(pr.z) * p.n + band * BN + n]);
+            float* sv = svh_s + (it & 1) * 128;   // (the other buffer may still be read by a slower warp of the previous item)
+            sv[n] = __half2float(p.svh[size_t(pr.z) * p.n + band * BN + n]);
             const int buf = it % nbuf;
             mbar_wait_parked(acc_full + 8 * buf, (it / nbuf) & 1, p.status, 200);
             tc_fence_after();
+            team_sync(0);   // the scales are in place
             const int rows_pad = (pr.rows + 15) & ~15;
             for (int c0 = 0; c0 < rows_pad; c0 += 32)
-                epilogue_pass(tmem + buf * chunk + (uint32_t(quarter * 32) << 16) + c0, xch, 0, quarter, lane, scale, p.c, p.out_fp32,
-                              p.n, band * BN + n, pr.row0 + c0, pr.row0 + pr.rows);
+                epilogue_pass(tmem + buf * chunk + (uint32_t(quarter * 32) << 16) + c0, xch, sv, 0, quarter, lane, p.c, p.out_fp32, p.n,
+                              band * BN, pr.row0 + c0, pr.row0 + pr.rows);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty + 8 * buf);
