@@ -814,17 +814,18 @@ std::string launch_gemm_tc(const void* a, const void* trellis, void* c, const vo
     args.m = size_m; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
     args.problems = nullptr; args.n_problems = nullptr; args.max_problems = 0; args.n_matrices = 1;
-    // Rows per CTA: 128, 256 or 384.  More rows per decoded weight keep the kernel MMA bound (the decode
-    // warps need ~700 cycles per 64-deep stage, 128 rows of MMA ~370), fewer rows give more CTAs; pick the
-    // count with the fewest (waves x stage time) on this device.
+    // Rows per CTA: 128, 256 or 384.  More rows per decoded weight keep the kernel MMA bound, fewer rows give
+    // more CTAs; pick the count with the least (waves x time of one CTA), the latter from the measured stage
+    // and epilogue times of the three tile heights (ns per 64-deep stage; ns per epilogue; 1.2 us to start).
     {
+        static const int kStageNs[MAX_SUB] = {430, 490, 540}, kEpilogueNs[MAX_SUB] = {4000, 7400, 10300};
         const int sms = device_info(current_device()).sms;
         const int bands = size_n / BN;
         long long best = -1;
         for (int ns = 1; ns <= MAX_SUB; ++ns) {
             const long long ctas = (long long) bands * ((size_m + ns * SUB - 1) / (ns * SUB));
             const long long waves = (ctas + sms - 1) / sms;
-            const long long cost = waves * std::max(ns * 370, 700);
+            const long long cost = waves * ((long long) (size_k / BK) * kStageNs[ns - 1] + kEpilogueNs[ns - 1] + 1200);
             if (best < 0 || cost <= best) { best = cost; args.nsub_max = ns; }   // ties: more rows per CTA
         }
     }
