@@ -340,6 +340,42 @@ __global__ void __launch_bounds__(256) k_moe_combine(const __half* __restrict__ 
     }
 }
 
+// Expert-parallel receive side: the rows of source s arrive sorted by local expert, cnt[s][e] of them per
+// expert.  seg_off[i] = first row of segment i = s * n_local + e (exclusive scan, one block, up to 1024 segments).
+__global__ void __launch_bounds__(1024) k_moe_segment_scan(const int32_t* __restrict__ cnt, int n_seg, int* __restrict__ seg_off)
+{
+    __shared__ int wsum[32];
+    const int j = threadIdx.x, lane = j & 31, warp = j >> 5;
+    const int c = j < n_seg ? max(cnt[j], 0) : 0;
+    int incl = c;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int a = __shfl_up_sync(dq::kFull, incl, off);
+        if (lane >= off) incl += a;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int a = wsum[lane];
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int u = __shfl_up_sync(dq::kFull, a, off);
+            if (lane >= off) a += u;
+        }
+        wsum[lane] = a;
+    }
+    __syncthreads();
+    if (j < n_seg) seg_off[j] = incl - c + (warp ? wsum[warp - 1] : 0);
+    if (j == 0) seg_off[n_seg] = wsum[31];
+}
+// keys[row] = local expert of the row: block = segment.
+__global__ void __launch_bounds__(128) k_moe_segment_keys(const int* __restrict__ seg_off, int n_local, int max_rows, int32_t* __restrict__ keys)
+{
+    const int seg = blockIdx.x, e = seg % n_local;
+    const int r0 = seg_off[seg], r1 = min(seg_off[seg + 1], max_rows);
+    for (int r = r0 + threadIdx.x; r < r1; r += 128) keys[r] = e;
+}
+
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
 // How the expert stage cuts an expert's rows into problems: up to 32 rows per problem go through the
@@ -604,6 +640,116 @@ extern "C" int berth_moe_combine(const void* y, const int32_t* inv, const float*
         k_moe_combine<<<T, 256, 0, (cudaStream_t) stream>>>((const __half*) y, inv, topk_w, (const __half*) ysh, (float*) out, hidden, top_k);
         cuda_ok(cudaGetLastError(), "k_moe_combine launch");
         st.launch = "k_moe_combine grid=" + std::to_string(T);
+    });
+}
+
+// ---- expert parallelism with one library call per side of the exchange
+
+extern "C" size_t berth_moe_ep_send_workspace_bytes(int T, int n_experts, int top_k)
+{
+    if (T < 1 || n_experts < 1 || top_k < 1) return 0;
+    const size_t R = size_t(T) * top_k;
+    return align256(size_t(T) * n_experts * 4) + align256(R * 4) + align256(size_t(n_experts + 2) * 4) + 256 +
+           align256((R / 8 + n_experts + 1) * sizeof(GemvProblem)) + 512;
+}
+
+extern "C" int berth_moe_ep_send(const void* x, int T, const void* w_router, const float* router_bias, int hidden, int n_experts,
+                                 int top_k, int32_t* topk_idx, float* topk_w, int32_t* inv, void* send_rows, int32_t* counts,
+                                 void* ws, size_t ws_bytes, void* stream)
+{
+    CallState& st = moe_state();
+    return guarded(st, [&] {
+        if (!x || !w_router || !topk_idx || !topk_w || !inv || !send_rows || !counts || !ws)
+            throw std::runtime_error("moe ep send: null device pointer");
+        if (T < 1) throw std::runtime_error("moe ep send: T must be positive");
+        if (hidden < 32 || hidden % 32) throw std::runtime_error("moe ep send: hidden must be a multiple of 32");
+        if (n_experts < 32 || n_experts % 32 || n_experts > 1024)
+            throw std::runtime_error("moe ep send: n_experts must be a multiple of 32 up to 1024");
+        if (top_k < 1 || top_k > 32 || top_k > n_experts) throw std::runtime_error("moe ep send: top_k must be in 1..=32");
+        if (ws_bytes < berth_moe_ep_send_workspace_bytes(T, n_experts, top_k)) throw std::runtime_error("moe ep send: workspace too small");
+        cudaStream_t cs = (cudaStream_t) stream;
+        const int R = T * top_k;
+        char* b = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(ws) + 255) & ~uintptr_t(255));
+        auto take = [&](size_t bytes) { char* p = b; b += align256(bytes); return p; };
+        float* logits = (float*) take(size_t(T) * n_experts * 4);
+        int32_t* perm = (int32_t*) take(size_t(R) * 4);
+        ExpertScratch es{};
+        es.counts = counts;
+        es.offsets = (int*) take(size_t(n_experts + 2) * 4);
+        es.n_problems = (int*) take(4);
+        es.problems = (GemvProblem*) take((size_t(R) / 8 + n_experts + 1) * sizeof(GemvProblem));
+        router_topk(x, w_router, router_bias, topk_idx, topk_w, logits, T, hidden, n_experts, top_k, cs);
+        dispatch(topk_idx, R, 0, n_experts, 8, es, perm, inv, cs);
+        k_moe_gather_rows<<<std::min(R, 148 * 8), 256, 0, cs>>>((const __half*) x, perm, es.offsets + n_experts, top_k, (__half*) send_rows, hidden);
+        cuda_ok(cudaGetLastError(), "k_moe_gather_rows launch");
+        st.launch = "k_moe_router_logits + k_moe_topk + k_moe_count/scan/scatter + k_moe_gather_rows";
+    });
+}
+
+static const int kPlanHints[] = {8, 16, 32, 128, 256, 384};
+
+extern "C" size_t berth_moe_ep_experts_workspace_bytes(int max_rows, int max_tokens, int world, int n_local, int hidden, int inter)
+{
+    if (max_rows < 1 || max_tokens < 0 || world < 1 || n_local < 1 || hidden < 128 || inter < 128) return 0;
+    size_t es = 0;
+    for (int h : kPlanHints) es = std::max(es, carve_experts(nullptr, max_rows + max_tokens, n_local + 1, hidden, inter, expert_plan(h)).bytes);
+    return 3 * align256(size_t(max_rows) * 4) + align256(size_t(world * n_local + 1) * 4) +
+           2 * align256(size_t(max_rows + max_tokens) * hidden * 2) + es + 1024;
+}
+
+extern "C" int berth_moe_ep_experts(const berth_moe_weights* w, const void* recv_rows, int n_rows, const int32_t* cnt_recv, int world,
+                                    const void* x_local, int T_local, void* back, void* ysh, void* ws, size_t ws_bytes, int max_rows,
+                                    int max_tokens, int rows_hint, void* stream)
+{
+    CallState& st = moe_state();
+    return guarded(st, [&] {
+        check_moe_shapes(w, 1);
+        if (!cnt_recv || !ws || (n_rows > 0 && (!recv_rows || !back))) throw std::runtime_error("moe ep experts: null device pointer");
+        if (n_rows < 0 || n_rows > max_rows) throw std::runtime_error("moe ep experts: n_rows must be within 0..max_rows");
+        if (T_local < 0 || T_local > max_tokens) throw std::runtime_error("moe ep experts: T_local must be within 0..max_tokens");
+        const int NL = w->n_experts, H = w->hidden, I = w->inter;
+        if (world < 1 || world * NL > 1024) throw std::runtime_error("moe ep experts: world x local experts must be at most 1024");
+        const bool with_shared = ysh != nullptr && T_local > 0;
+        if (with_shared && (!x_local || !shared_behind_stacks(w)))
+            throw std::runtime_error("moe ep experts: the shared expert must be stored behind the expert stacks to run here");
+        if (ws_bytes < berth_moe_ep_experts_workspace_bytes(max_rows, max_tokens, world, NL, H, I))
+            throw std::runtime_error("moe ep experts: workspace too small");
+        const int device = current_device();
+        const DeviceInfo& info = device_info(device);
+        if (info.major != 10) throw std::runtime_error("moe ep experts: no linked kernel for this GPU (library is built for sm_100a only)");
+        cudaStream_t cs = (cudaStream_t) stream;
+        const int TS = with_shared ? T_local : 0;
+        const int RT = n_rows + TS, NM = with_shared ? NL + 1 : NL;
+        if (RT == 0) return;
+        const ExpertPlan plan = expert_plan(std::max(rows_hint, 1));
+        char* b = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(ws) + 255) & ~uintptr_t(255));
+        auto take = [&](size_t bytes) { char* p = b; b += align256(bytes); return p; };
+        int32_t* keys = (int32_t*) take(size_t(max_rows) * 4);
+        int32_t* perm = (int32_t*) take(size_t(max_rows) * 4);
+        int32_t* inv = (int32_t*) take(size_t(max_rows) * 4);
+        int* seg_off = (int*) take(size_t(world * NL + 1) * 4);
+        __half* xr = (__half*) take(size_t(max_rows + max_tokens) * H * 2);
+        __half* yr = (__half*) take(size_t(max_rows + max_tokens) * H * 2);
+        ExpertScratch es = carve_experts(b, RT, NM, H, I, plan);
+        if (n_rows > 0) {
+            k_moe_segment_scan<<<1, 1024, 0, cs>>>(cnt_recv, world * NL, seg_off);
+            k_moe_segment_keys<<<world * NL, 128, 0, cs>>>(seg_off, NL, n_rows, keys);
+            cuda_ok(cudaGetLastError(), "k_moe_segment_keys launch");
+        }
+        dispatch(keys, n_rows, 0, NL, plan.chunk, es, perm, inv, cs, TS);
+        if (n_rows > 0) {
+            k_moe_gather_rows<<<std::min(n_rows, 148 * 8), 256, 0, cs>>>((const __half*) recv_rows, perm, es.offsets + NL, 1, xr, H);
+            cuda_ok(cudaGetLastError(), "k_moe_gather_rows launch");
+        }
+        if (TS) cuda_ok(cudaMemcpyAsync(xr + size_t(n_rows) * H, x_local, size_t(TS) * H * 2, cudaMemcpyDeviceToDevice, cs), "moe ep experts: shared rows copy");
+        st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
+                            w->down_suh, w->down_svh, NM, xr, yr, RT, RT, plan, es, gemv_workspace(device), info.sms, cs);
+        if (n_rows > 0) {
+            k_moe_gather_n<<<std::min(n_rows, 148 * 8), 256, 0, cs>>>(yr, inv, n_rows, 1, (__half*) back, H);
+            cuda_ok(cudaGetLastError(), "k_moe_gather launch");
+        }
+        if (TS) cuda_ok(cudaMemcpyAsync(ysh, yr + size_t(n_rows) * H, size_t(TS) * H * 2, cudaMemcpyDeviceToDevice, cs), "moe ep experts: shared output copy");
+        st.launch = "k_moe_segment_scan/keys + k_moe_count/scan/scatter + k_moe_gather_rows + 3 x (" + st.launch + ") + k_silu_mul + k_moe_gather_n";
     });
 }
 

@@ -216,6 +216,54 @@ class GpuStages:
         fwd(down, a, y)
         return y
 
+    # ---- one library call per side of the exchange
+    def ep_send(self, x, max_tokens: int):
+        """Route, sort and gather the local tokens: (topk_idx, topk_w, inv, send_rows, counts per expert)."""
+        l = _lib.lib()
+        T, H = x.shape
+        k, E = self.d["top_k"], self.E
+        if getattr(self, "_send_ws", None) is None or self._send_cap < T:
+            self._send_cap = max(T, max_tokens)
+            self._send_ws = torch.empty(l.berth_moe_ep_send_workspace_bytes(self._send_cap, E, k), dtype=torch.uint8, device=self.device)
+        idx = torch.empty((T, k), dtype=torch.int32, device=self.device)
+        w = torch.empty((T, k), dtype=torch.float32, device=self.device)
+        inv = torch.empty(T * k, dtype=torch.int32, device=self.device)
+        rows = torch.empty((T * k, H), dtype=torch.float16, device=self.device)
+        counts = torch.empty(E, dtype=torch.int32, device=self.device)
+        kp = self.layer._keep
+        bias = kp.get("router_bias")
+        self._check(l.berth_moe_ep_send(x.data_ptr(), T, kp["w_router"].data_ptr(), None if bias is None else bias.data_ptr(), H, E, k,
+                                        idx.data_ptr(), w.data_ptr(), inv.data_ptr(), rows.data_ptr(), counts.data_ptr(),
+                                        self._send_ws.data_ptr(), self._send_ws.numel(), None))
+        return idx, w, inv, rows, counts
+
+    def shared_is_stacked(self) -> bool:
+        """True if the shared expert sits behind the local expert stacks (MoeLayer puts it there when it has the
+        experts' shape), so that ep_experts can run it inside the grouped launches."""
+        d, kp = self.d, self.layer._keep
+        return bool(d["shared_inter"]) and d["shared_inter"] == d["inter"] and "sh_gate_trellis" in kp and \
+            kp["sh_gate_trellis"].data_ptr() == kp["gate_trellis"].data_ptr() + d["n_experts"] * kp["gate_trellis"][0].numel() * 2
+
+    def ep_experts(self, recv_rows, cnt_recv, world: int, x_local, max_tokens: int):
+        """Received rows -> expert outputs in arrival order (+ the shared expert's output for the local tokens
+        when it is stacked behind the experts)."""
+        l = _lib.lib()
+        R, H = recv_rows.shape
+        T = x_local.shape[0]
+        nl = self.d["n_experts"]
+        if getattr(self, "_exp_ws", None) is None:
+            self._exp_tokens = max(T, max_tokens)
+            self._exp_ws = torch.empty(l.berth_moe_ep_experts_workspace_bytes(self.max_rows, self._exp_tokens, world, nl, H, self.d["inter"]),
+                                       dtype=torch.uint8, device=self.device)
+        back = torch.empty((R, H), dtype=torch.float16, device=self.device)
+        stacked = self.shared_is_stacked() and T > 0
+        ysh = torch.empty((T, H), dtype=torch.float16, device=self.device) if stacked else None
+        self._check(l.berth_moe_ep_experts(C.byref(self.layer.c), recv_rows.data_ptr() if R else None, R, cnt_recv.data_ptr(), world,
+                                           x_local.data_ptr() if T else None, T, back.data_ptr() if R else None,
+                                           None if ysh is None else ysh.data_ptr(), self._exp_ws.data_ptr(), self._exp_ws.numel(),
+                                           self.max_rows, self._exp_tokens, self.rows_hint(R, nl), None))
+        return back, ysh
+
     def combine(self, y, inv, w, ysh):
         T, k = w.shape
         H = y.shape[1]
@@ -258,6 +306,8 @@ class EpMoeLayer:
         dist, st = self.dist, self.stages
         T, k, W, nl = x.shape[0], self.k, self.world, self.n_local
         dev = x.device
+        if hasattr(st, "ep_send") and T:
+            return self._forward_fused(x)
         if T:
             idx, w = st.route(x)
         else:   # a rank without tokens still takes part in the exchanges
@@ -291,6 +341,28 @@ class EpMoeLayer:
             out = st.combine(y_sorted, inv, w, ysh)
         else:
             out = torch.empty((0, x.shape[1]), dtype=torch.float32, device=dev)
+        self.last_stats = {"sent_rows": T * k, "recv_rows": R, "send_counts": send_counts, "recv_counts": recv_counts}
+        return out, idx, w
+
+    def _forward_fused(self, x: torch.Tensor):
+        """The same exchange with one library call on each side of it (GPU stages)."""
+        dist, st = self.dist, self.stages
+        T, k, W, nl = x.shape[0], self.k, self.world, self.n_local
+        dev = x.device
+        idx, w, inv, send_rows, cnt_send = st.ep_send(x, T)
+        cnt_recv = torch.empty_like(cnt_send)                              # [source rank][local expert]
+        dist.all_to_all_single(cnt_recv, cnt_send, group=self.group)
+        sizes = torch.stack((cnt_send.view(W, nl).sum(1), cnt_recv.view(W, nl).sum(1))).to("cpu")   # the one host sync
+        send_counts, recv_counts = sizes[0].tolist(), sizes[1].tolist()
+        R = sum(recv_counts)
+        recv_rows = torch.empty((R, x.shape[1]), dtype=x.dtype, device=dev)
+        dist.all_to_all_single(recv_rows, send_rows, recv_counts, send_counts, group=self.group)
+        back, ysh = st.ep_experts(recv_rows, cnt_recv, W, x, T)
+        if ysh is None and getattr(st, "shared", None) is not None:
+            ysh = st.shared_expert(x)
+        y_sorted = torch.empty_like(send_rows)
+        dist.all_to_all_single(y_sorted, back, send_counts, recv_counts, group=self.group)
+        out = st.combine(y_sorted, inv, w, ysh)
         self.last_stats = {"sent_rows": T * k, "recv_rows": R, "send_counts": send_counts, "recv_counts": recv_counts}
         return out, idx, w
 

@@ -184,6 +184,29 @@ int berth_moe_experts(const berth_moe_weights* w, const void* xr, void* yr, int 
                       size_t ews_bytes, int max_rows, int max_rows_per_expert, void* stream);
 int berth_moe_combine(const void* y, const int32_t* inv, const float* topk_w, const void* ysh,
                       void* out, int T, int hidden, int top_k, void* stream);
+/* The two compute sides of an expert-parallel layer as one call each (the host puts its all-to-alls
+ * between them; no counterpart in berth).
+ *   ep_send:    route the T local tokens over all n_experts, sort the (token, slot) pairs by expert
+ *               (= by destination rank, experts being split in contiguous blocks) and gather their
+ *               rows.  Out: topk_idx/topk_w [T][k]; inv[T*k] = position of pair (t, s) in the sorted
+ *               order; send_rows fp16 [T*k][hidden] in that order; counts[n_experts] rows per expert.
+ *   ep_experts: recv_rows fp16 [n_rows][hidden] = the rows of source 0, 1, .. world-1, each source's
+ *               rows sorted by local expert, cnt_recv[world][n_local] of them per (source, expert).
+ *               Regroups by local expert, runs the experts (w holds the LOCAL stacks) and writes the
+ *               outputs in arrival order to back [n_rows][hidden].  With ysh != NULL the shared expert,
+ *               which must then be stored behind the stacks as matrix n_local, runs in the same
+ *               launches on x_local [T_local][hidden] -> ysh [T_local][hidden].  rows_hint = the rows
+ *               per expert to size the problems for (see berth_moe_experts). */
+size_t berth_moe_ep_send_workspace_bytes(int T, int n_experts, int top_k);
+int berth_moe_ep_send(const void* x, int T, const void* w_router, const float* router_bias, int hidden,
+                      int n_experts, int top_k, int32_t* topk_idx, float* topk_w, int32_t* inv,
+                      void* send_rows, int32_t* counts, void* ws, size_t ws_bytes, void* stream);
+size_t berth_moe_ep_experts_workspace_bytes(int max_rows, int max_tokens, int world, int n_local,
+                                            int hidden, int inter);
+int berth_moe_ep_experts(const berth_moe_weights* w, const void* recv_rows, int n_rows,
+                         const int32_t* cnt_recv, int world, const void* x_local, int T_local, void* back,
+                         void* ysh, void* ws, size_t ws_bytes, int max_rows, int max_tokens, int rows_hint,
+                         void* stream);
 const char* berth_moe_last_error(void);
 const char* berth_moe_last_launch(void);
 

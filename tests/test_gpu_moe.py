@@ -135,7 +135,7 @@ def test_expert_parallel_stages_match_fused_layer(T):
     H, I, E, k, bits, cb = 256, 128, 32, 4, 4, 2
     wts = synth.moe_layer_weights(1234, "ep1", H, I, E, k, bits, cb, shared_inter=128)
     x = synth.activations(1234, f"ep1.x{T}", T, H)
-    ref, ref_idx, _ = _run_layer(wts, x, fuse_shared=False)   # the staged host runs the shared expert through its own linears
+    ref, ref_idx, _ = _run_layer(wts, x)
     stages = moe.GpuStages(torch.device("cuda", torch.cuda.current_device()), wts, E, max_rows=T * k, max_rows_per_expert=T)
     layer = moe.EpMoeLayer.__new__(moe.EpMoeLayer)
     layer.dist, layer.group, layer.stages = _OneRankDist, None, stages
