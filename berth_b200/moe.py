@@ -251,7 +251,7 @@ class GpuStages:
         R, H = recv_rows.shape
         T = x_local.shape[0]
         nl = self.d["n_experts"]
-        if getattr(self, "_exp_ws", None) is None:
+        if getattr(self, "_exp_ws", None) is None or self._exp_tokens < T:
             self._exp_tokens = max(T, max_tokens)
             self._exp_ws = torch.empty(l.berth_moe_ep_experts_workspace_bytes(self.max_rows, self._exp_tokens, world, nl, H, self.d["inter"]),
                                        dtype=torch.uint8, device=self.device)
