@@ -55,6 +55,11 @@ SIGNATURES = {
     "berth_moe_ep_send": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
     "berth_moe_ep_experts_workspace_bytes": (C.c_size_t, [_i, _i, _i, _i, _i, _i]),
     "berth_moe_ep_experts": (_i, [C.POINTER(MoeWeights), _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, C.c_size_t, _i, _i, _i, _vp]),
+    "berth_moe_p2p_send_workspace_bytes": (C.c_size_t, [_i, _i, _i, _i]),
+    "berth_moe_p2p_send": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, C.c_uint, _vp, _vp, _vp, _i, _vp, C.c_size_t, _vp]),
+    "berth_moe_p2p_experts_workspace_bytes": (C.c_size_t, [_i, _i, _i, _i]),
+    "berth_moe_p2p_experts": (_i, [C.POINTER(MoeWeights), _vp, _i, _vp, _i, _i, C.c_uint, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp,
+                                   _vp, C.c_size_t, _vp]),
     "berth_moe_last_error": (C.c_char_p, []),
     "berth_moe_last_launch": (C.c_char_p, []),
     "berth_ops_last_error": (C.c_char_p, []),

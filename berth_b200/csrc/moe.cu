@@ -13,6 +13,7 @@ namespace berth {
 
 std::string linear_rows(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, cudaStream_t stream);
+void silu_mul_rows(const void* gate, const void* up, void* out, const int* n_rows, int max_rows, int row_elems, cudaStream_t stream);
 
 namespace {
 
@@ -376,6 +377,191 @@ __global__ void __launch_bounds__(128) k_moe_segment_keys(const int* __restrict_
     for (int r = r0 + threadIdx.x; r < r1; r += 128) keys[r] = e;
 }
 
+// ---------------------------------------------------------------- expert parallelism over peer memory
+// The ranks of one NVSwitch box exchange routed rows and expert outputs with plain stores into each other's
+// memory (symmetric buffers whose per-rank addresses the host passes in) and three flag barriers per layer;
+// no collective library call and no host synchronisation.  Every wait on a peer is bounded: when it runs out
+// it sets a status bit and the layer carries on with whatever is there.
+constexpr int kMaxPeers = 8;
+struct PeerPtrs { void* p[kMaxPeers]; };
+enum : unsigned { kStEpTimeout = 32u, kStEpOverflow = 64u };
+
+// Thread s < W: tell rank s that this rank has reached `phase` of layer call `epoch`, then wait for rank s to
+// say the same.  flags: uint32 [3 phases][kMaxPeers sources] on every rank.  Everything this block wrote to
+// peer memory before the call is visible to a peer that has seen the flag.
+__device__ __forceinline__ void ep_signal_and_wait(const PeerPtrs& flags, int phase, int rank, int W, unsigned epoch, unsigned* status)
+{
+    __threadfence_system();
+    __syncthreads();
+    const int s = threadIdx.x;
+    if (s < W) {
+        volatile unsigned* remote = static_cast<volatile unsigned*>(flags.p[s]) + phase * kMaxPeers + rank;
+        *remote = epoch;
+        volatile unsigned* mine = static_cast<volatile unsigned*>(flags.p[rank]) + phase * kMaxPeers + s;
+        bool ok = false;
+        for (unsigned i = 0; i < (1u << 22); ++i) {
+            if (int(*mine - epoch) >= 0) { ok = true; break; }
+            __nanosleep(100);
+        }
+        if (!ok) atomicOr(status, kStEpTimeout);
+        __threadfence_system();
+    }
+    __syncthreads();
+}
+
+// Exclusive scan of one value per thread over a block of 1024 (value 0 beyond n); returns the prefix, total in *total.
+__device__ __forceinline__ int block_exclusive_scan(int v, int* wsum /*[32] shared*/, int* total)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int a = __shfl_up_sync(dq::kFull, incl, off);
+        if (lane >= off) incl += a;
+    }
+    __syncthreads();   // wsum may still be read from an earlier call
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int a = wsum[lane];
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int u = __shfl_up_sync(dq::kFull, a, off);
+            if (lane >= off) a += u;
+        }
+        wsum[lane] = a;
+    }
+    __syncthreads();
+    if (total) *total = wsum[31];
+    return incl - v + (warp ? wsum[warp - 1] : 0);
+}
+
+// Publish this rank's rows-per-expert to every rank (cnt_all [W][E] on each), barrier 0, then build from the
+// full matrix (one block of 1024 threads, E <= 1024):
+//   dst0[e]         first row, in the owner's receive buffer, of this rank's rows for expert e
+//                   (the owner holds expert blocks in order, each block source by source);
+//   counts_local[j] rows arriving here for local expert j, from all sources;
+//   send_off[s][j]  position of source s's first row for local expert j in s's own sorted send order.
+__global__ void __launch_bounds__(1024) k_ep_publish_tables(const int* __restrict__ counts, PeerPtrs cnt_all, PeerPtrs flags, int rank, int W,
+                                                            int E, int n_local, unsigned epoch, int* __restrict__ dst0,
+                                                            int* __restrict__ counts_local, int* __restrict__ send_off, unsigned* status)
+{
+    __shared__ int wsum[32];
+    __shared__ int prefix[1025];
+    const int e = threadIdx.x;
+    if (e < E) {
+        const int c = max(counts[e], 0);
+        for (int d = 0; d < W; ++d) static_cast<int*>(cnt_all.p[d])[rank * E + e] = c;
+    }
+    ep_signal_and_wait(flags, 0, rank, W, epoch, status);
+    const volatile int* cnt = static_cast<const volatile int*>(cnt_all.p[rank]);
+    int tot = 0, before = 0;
+    if (e < E)
+        for (int s = 0; s < W; ++s) {
+            const int c = cnt[s * E + e];
+            if (s < rank) before += c;
+            tot += c;
+        }
+    const int pre = block_exclusive_scan(e < E ? tot : 0, wsum, nullptr);
+    if (e <= E) prefix[e] = pre;
+    __syncthreads();
+    if (e < E) {
+        const int owner0 = (e / n_local) * n_local;          // first expert of the owner's block
+        dst0[e] = pre - prefix[owner0] + before;
+        const int e0 = rank * n_local;
+        if (e >= e0 && e < e0 + n_local) counts_local[e - e0] = tot;
+    }
+    for (int s = 0; s < W; ++s) {
+        const int ps = block_exclusive_scan(e < E ? cnt[s * E + e] : 0, wsum, nullptr);
+        const int e0 = rank * n_local;
+        if (e >= e0 && e < e0 + n_local) send_off[s * n_local + (e - e0)] = ps;
+    }
+}
+
+// Row pos of this rank's sorted send order -> the receive buffer of the rank that owns its expert.
+__global__ void __launch_bounds__(256) k_ep_dispatch(const __half* __restrict__ x, const int32_t* __restrict__ perm,
+                                                     const int* __restrict__ offsets_send, const int* __restrict__ dst0, PeerPtrs recv_rows,
+                                                     int E, int n_local, int top_k, int H, int n_send, int max_rows, unsigned* status)
+{
+    for (int pos = blockIdx.x; pos < n_send; pos += gridDim.x) {
+        int lo = 0, hi = E - 1;   // the last expert whose first position is <= pos and that has rows there
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (__ldg(offsets_send + mid) <= pos) lo = mid; else hi = mid - 1;
+        }
+        const int e = lo;
+        const int dst = __ldg(dst0 + e) + pos - __ldg(offsets_send + e);
+        if (dst < 0 || dst >= max_rows) {
+            if (threadIdx.x == 0) atomicOr(status, kStEpOverflow);
+            continue;
+        }
+        const uint4* src = reinterpret_cast<const uint4*>(x + size_t(perm[pos] / top_k) * H);
+        uint4* out = reinterpret_cast<uint4*>(static_cast<__half*>(recv_rows.p[e / n_local]) + size_t(dst) * H);
+        for (int i = threadIdx.x; i < H / 8; i += 256) out[i] = src[i];
+    }
+    __threadfence_system();
+}
+
+__global__ void __launch_bounds__(32) k_ep_barrier(PeerPtrs flags, int phase, int rank, int W, unsigned epoch, unsigned* status)
+{
+    ep_signal_and_wait(flags, phase, rank, W, epoch, status);
+}
+
+// dst[*row_off + r] = src[r] for r < rows (rows of H halves): the local tokens behind the received rows.
+__global__ void __launch_bounds__(256) k_rows_to_offset(const __half* __restrict__ src, __half* __restrict__ dst, const int* __restrict__ row_off,
+                                                        int rows, int H, int max_rows)
+{
+    const int off = min(max(__ldg(row_off), 0), max_rows - rows);
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        const uint4* s = reinterpret_cast<const uint4*>(src + size_t(r) * H);
+        uint4* d = reinterpret_cast<uint4*>(dst + size_t(off + r) * H);
+        for (int i = threadIdx.x; i < H / 8; i += 256) d[i] = s[i];
+    }
+}
+__global__ void __launch_bounds__(256) k_rows_from_offset(const __half* __restrict__ src, __half* __restrict__ dst, const int* __restrict__ row_off,
+                                                          int rows, int H, int max_rows)
+{
+    const int off = min(max(__ldg(row_off), 0), max_rows - rows);
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        const uint4* s = reinterpret_cast<const uint4*>(src + size_t(off + r) * H);
+        uint4* d = reinterpret_cast<uint4*>(dst + size_t(r) * H);
+        for (int i = threadIdx.x; i < H / 8; i += 256) d[i] = s[i];
+    }
+}
+
+// Expert output row p (rows sorted by local expert, inside an expert source by source) -> the source's return
+// buffer at the position the row had in the source's sorted send order.
+__global__ void __launch_bounds__(256) k_ep_return(const __half* __restrict__ yr, const int* __restrict__ offsets, PeerPtrs cnt_all,
+                                                   const int* __restrict__ send_off, PeerPtrs ret_rows, int rank, int W, int E, int n_local,
+                                                   int H, int max_rows, int max_send, unsigned* status)
+{
+    const int R = min(max(__ldg(offsets + n_local), 0), max_rows);
+    const int* cnt = static_cast<const int*>(cnt_all.p[rank]);
+    for (int p = blockIdx.x; p < R; p += gridDim.x) {
+        int lo = 0, hi = n_local - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (__ldg(offsets + mid) <= p) lo = mid; else hi = mid - 1;
+        }
+        const int j = lo, e = rank * n_local + j;
+        int q = p - __ldg(offsets + j), s = 0;
+        for (; s < W - 1; ++s) {
+            const int c = cnt[s * E + e];
+            if (q < c) break;
+            q -= c;
+        }
+        const int srcpos = __ldg(send_off + s * n_local + j) + q;
+        if (srcpos < 0 || srcpos >= max_send) {
+            if (threadIdx.x == 0) atomicOr(status, kStEpOverflow);
+            continue;
+        }
+        const uint4* src = reinterpret_cast<const uint4*>(yr + size_t(p) * H);
+        uint4* out = reinterpret_cast<uint4*>(static_cast<__half*>(ret_rows.p[s]) + size_t(srcpos) * H);
+        for (int i = threadIdx.x; i < H / 8; i += 256) out[i] = src[i];
+    }
+    __threadfence_system();
+}
+
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
 // How the expert stage cuts an expert's rows into problems: up to 32 rows per problem go through the
@@ -510,15 +696,20 @@ void dispatch(const int32_t* keys, int n, int e0, int n_local, int chunk, const 
 std::string experts(const berth_moe_weights* w, const void* gate_t, const void* up_t, const void* down_t, const void* gsuh,
                     const void* gsvh, const void* usuh, const void* usvh, const void* dsuh, const void* dsvh, int n_local,
                     const void* xr, void* yr, int R, int max_rows, const ExpertPlan& plan, const ExpertScratch& s, const GemvScratch& sc,
-                    int sms, cudaStream_t st)
+                    int sms, cudaStream_t st, const int* rows_dev = nullptr)
 {
     const int H = w->hidden, I = w->inter;
+    // the activation between the projections: over R rows, or over the device-side count (at most max_rows)
+    auto act = [&] {
+        if (rows_dev) silu_mul_rows(s.g, s.u, s.g, rows_dev, max_rows, I, st);
+        else if (berth_ops_silu_mul(s.g, s.u, s.g, int64_t(R) * I, 0.0f, st) != 0) throw std::runtime_error(berth_ops_last_error());
+    };
     if (plan.nsub) {
         std::string d = launch_gemm_tc_grouped(xr, s.afrag, gate_t, n_local, s.g, gsuh, gsvh, s.problems, s.n_problems, s.max_problems,
                                                max_rows, plan.nsub, H, I, w->k_bits, w->codebook, 0, sc.status, sms, st);
         launch_gemm_tc_grouped(xr, s.afrag, up_t, n_local, s.u, usuh, usvh, s.problems, s.n_problems, s.max_problems, max_rows, plan.nsub,
                                H, I, w->k_bits, w->codebook, 0, sc.status, sms, st);
-        if (berth_ops_silu_mul(s.g, s.u, s.g, int64_t(R) * I, 0.0f, st) != 0) throw std::runtime_error(berth_ops_last_error());
+        act();
         launch_gemm_tc_grouped(s.g, s.afrag, down_t, n_local, yr, dsuh, dsvh, s.problems, s.n_problems, s.max_problems, max_rows,
                                plan.nsub, I, H, w->k_bits, w->codebook, 0, sc.status, sms, st);
         return d;
@@ -528,7 +719,7 @@ std::string experts(const berth_moe_weights* w, const void* gate_t, const void* 
                                         s.blocksum, H, I, w->k_bits, w->codebook, 0, sc, sms, st);
     launch_gemv_grouped(xr, up_t, n_local, s.u, usuh, usvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag, s.blocksum, H, I,
                         w->k_bits, w->codebook, 0, sc, sms, st);
-    if (berth_ops_silu_mul(s.g, s.u, s.g, int64_t(R) * I, 0.0f, st) != 0) throw std::runtime_error(berth_ops_last_error());
+    act();
     launch_gemv_grouped(s.g, down_t, n_local, yr, dsuh, dsvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag, s.blocksum, I, H,
                         w->k_bits, w->codebook, 0, sc, sms, st);
     return d;
@@ -750,6 +941,160 @@ extern "C" int berth_moe_ep_experts(const berth_moe_weights* w, const void* recv
         }
         if (TS) cuda_ok(cudaMemcpyAsync(ysh, yr + size_t(n_rows) * H, size_t(TS) * H * 2, cudaMemcpyDeviceToDevice, cs), "moe ep experts: shared output copy");
         st.launch = "k_moe_segment_scan/keys + k_moe_count/scan/scatter + k_moe_gather_rows + 3 x (" + st.launch + ") + k_silu_mul + k_moe_gather_n";
+    });
+}
+
+// ---- expert parallelism over peer memory: two calls per layer, no collective, no host synchronisation
+
+namespace {
+struct P2pSendWs {
+    float* logits; int32_t* perm; int* counts; int* offsets; int* n_problems; GemvProblem* problems;
+    int* dst0; int* counts_local; int* send_off; size_t bytes;
+};
+P2pSendWs carve_p2p_send(void* base, int T, int E, int top_k, int world, int n_local)
+{
+    P2pSendWs s{};
+    const size_t R = size_t(T) * top_k;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off += align256(bytes); return o; };
+    const size_t o_log = take(size_t(T) * E * 4), o_perm = take(R * 4), o_cnt = take(size_t(E) * 4), o_off = take(size_t(E + 2) * 4);
+    const size_t o_np = take(4), o_prob = take((R / 8 + E + 1) * sizeof(GemvProblem)), o_dst = take(size_t(E) * 4);
+    const size_t o_cl = take(size_t(n_local + 1) * 4), o_so = take(size_t(world) * n_local * 4);
+    s.bytes = off;
+    if (base) {
+        char* b = static_cast<char*>(base);
+        s.logits = (float*) (b + o_log); s.perm = (int32_t*) (b + o_perm); s.counts = (int*) (b + o_cnt); s.offsets = (int*) (b + o_off);
+        s.n_problems = (int*) (b + o_np); s.problems = (GemvProblem*) (b + o_prob); s.dst0 = (int*) (b + o_dst);
+        s.counts_local = (int*) (b + o_cl); s.send_off = (int*) (b + o_so);
+    }
+    return s;
+}
+PeerPtrs peer_ptrs(const void* const* ptrs, int world, const char* what)
+{
+    PeerPtrs p{};
+    if (!ptrs) throw std::runtime_error(std::string("moe p2p: null ") + what + " pointer list");
+    for (int i = 0; i < world; ++i) {
+        if (!ptrs[i]) throw std::runtime_error(std::string("moe p2p: null ") + what + " pointer of a rank");
+        p.p[i] = const_cast<void*>(ptrs[i]);
+    }
+    return p;
+}
+void check_p2p_world(int rank, int world, int n_experts, int n_local)
+{
+    if (world < 1 || world > kMaxPeers) throw std::runtime_error("moe p2p: world must be in 1..=8");
+    if (rank < 0 || rank >= world) throw std::runtime_error("moe p2p: rank out of range");
+    if (n_local < 1 || n_local * world != n_experts) throw std::runtime_error("moe p2p: experts must split evenly over the ranks");
+    if (n_experts > 1024 || n_experts % 32) throw std::runtime_error("moe p2p: n_experts must be a multiple of 32 up to 1024");
+}
+}  // namespace
+
+extern "C" size_t berth_moe_p2p_send_workspace_bytes(int T, int n_experts, int top_k, int world)
+{
+    if (T < 1 || n_experts < 1 || top_k < 1 || world < 1 || n_experts % world) return 0;
+    return carve_p2p_send(nullptr, T, n_experts, top_k, world, n_experts / world).bytes + 512;
+}
+
+extern "C" int berth_moe_p2p_send(const void* x, int T, const void* w_router, const float* router_bias, int hidden, int n_experts,
+                                  int top_k, int32_t* topk_idx, float* topk_w, int32_t* inv, int rank, int world, unsigned epoch,
+                                  const void* const* cnt_all, const void* const* flags, const void* const* recv_rows, int max_rows,
+                                  void* ws, size_t ws_bytes, void* stream)
+{
+    CallState& st = moe_state();
+    return guarded(st, [&] {
+        if (!w_router || !ws || (T > 0 && (!x || !topk_idx || !topk_w || !inv))) throw std::runtime_error("moe p2p send: null device pointer");
+        if (T < 0) throw std::runtime_error("moe p2p send: T must not be negative");   // a rank without tokens still joins the exchange
+        if (hidden < 32 || hidden % 32) throw std::runtime_error("moe p2p send: hidden must be a multiple of 32");
+        if (top_k < 1 || top_k > 32 || top_k > n_experts) throw std::runtime_error("moe p2p send: top_k must be in 1..=32");
+        const int n_local = world > 0 ? n_experts / world : 0;
+        check_p2p_world(rank, world, n_experts, n_local);
+        if (ws_bytes < berth_moe_p2p_send_workspace_bytes(std::max(T, 1), n_experts, top_k, world))
+            throw std::runtime_error("moe p2p send: workspace too small");
+        const PeerPtrs pc = peer_ptrs(cnt_all, world, "count table"), pf = peer_ptrs(flags, world, "flag"), pr = peer_ptrs(recv_rows, world, "receive buffer");
+        const int device = current_device();
+        unsigned* status = gemv_workspace(device).status;
+        cudaStream_t cs = (cudaStream_t) stream;
+        const int R = T * top_k;
+        void* base = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(ws) + 255) & ~uintptr_t(255));
+        const P2pSendWs s = carve_p2p_send(base, std::max(T, 1), n_experts, top_k, world, n_local);
+        ExpertScratch es{};
+        es.counts = s.counts; es.offsets = s.offsets; es.n_problems = s.n_problems; es.problems = s.problems;
+        if (T > 0) {
+            router_topk(x, w_router, router_bias, topk_idx, topk_w, s.logits, T, hidden, n_experts, top_k, cs);
+            dispatch(topk_idx, R, 0, n_experts, 8, es, s.perm, inv, cs);
+        } else {
+            cuda_ok(cudaMemsetAsync(s.counts, 0, size_t(n_experts) * 4, cs), "moe p2p send: clear counts");
+        }
+        k_ep_publish_tables<<<1, 1024, 0, cs>>>(s.counts, pc, pf, rank, world, n_experts, n_local, epoch, s.dst0, s.counts_local, s.send_off, status);
+        cuda_ok(cudaGetLastError(), "k_ep_publish_tables launch");
+        if (R > 0) {
+            k_ep_dispatch<<<std::min(R, 148 * 8), 256, 0, cs>>>((const __half*) x, s.perm, s.offsets, s.dst0, pr, n_experts, n_local, top_k, hidden, R,
+                                                               max_rows, status);
+            cuda_ok(cudaGetLastError(), "k_ep_dispatch launch");
+        }
+        k_ep_barrier<<<1, 32, 0, cs>>>(pf, 1, rank, world, epoch, status);
+        cuda_ok(cudaGetLastError(), "k_ep_barrier launch");
+        st.launch = "k_moe_router_logits + k_moe_topk + k_moe_count/scan/scatter + k_ep_publish_tables + k_ep_dispatch + k_ep_barrier";
+    });
+}
+
+extern "C" size_t berth_moe_p2p_experts_workspace_bytes(int max_rows, int n_local, int hidden, int inter)
+{
+    if (max_rows < 1 || n_local < 1 || hidden < 128 || inter < 128) return 0;
+    size_t es = 0;
+    for (int h : kPlanHints) es = std::max(es, carve_experts(nullptr, max_rows, n_local + 1, hidden, inter, expert_plan(h)).bytes);
+    return align256(size_t(max_rows) * hidden * 2) + es + 1024;
+}
+
+extern "C" int berth_moe_p2p_experts(const berth_moe_weights* w, const void* x_local, int T_local, void* ysh, int rank, int world,
+                                     unsigned epoch, int n_experts_total, int top_k, int send_tokens, const void* const* cnt_all,
+                                     const void* const* flags, const void* const* recv_rows, const void* const* ret_rows, int max_rows,
+                                     int max_send, int rows_hint, void* send_ws, void* ws, size_t ws_bytes, void* stream)
+{
+    CallState& st = moe_state();
+    return guarded(st, [&] {
+        check_moe_shapes(w, 1);
+        if (!send_ws || !ws) throw std::runtime_error("moe p2p experts: null workspace");
+        const int NL = w->n_experts, H = w->hidden, I = w->inter;
+        check_p2p_world(rank, world, n_experts_total, NL);
+        if (T_local < 0 || T_local >= max_rows) throw std::runtime_error("moe p2p experts: T_local must be below max_rows");
+        const bool with_shared = ysh != nullptr && T_local > 0;
+        if (with_shared && (!x_local || !shared_behind_stacks(w)))
+            throw std::runtime_error("moe p2p experts: the shared expert must be stored behind the expert stacks to run here");
+        if (ws_bytes < berth_moe_p2p_experts_workspace_bytes(max_rows, NL, H, I)) throw std::runtime_error("moe p2p experts: workspace too small");
+        const PeerPtrs pc = peer_ptrs(cnt_all, world, "count table"), pf = peer_ptrs(flags, world, "flag");
+        const PeerPtrs pr = peer_ptrs(recv_rows, world, "receive buffer"), pt = peer_ptrs(ret_rows, world, "return buffer");
+        const int device = current_device();
+        const DeviceInfo& info = device_info(device);
+        if (info.major != 10) throw std::runtime_error("moe p2p experts: no linked kernel for this GPU (library is built for sm_100a only)");
+        const GemvScratch sc = gemv_workspace(device);
+        cudaStream_t cs = (cudaStream_t) stream;
+        void* sbase = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(send_ws) + 255) & ~uintptr_t(255));
+        const P2pSendWs sw = carve_p2p_send(sbase, std::max(send_tokens, 1), n_experts_total, top_k, world, NL);
+        const int TS = with_shared ? T_local : 0, NM = with_shared ? NL + 1 : NL;
+        const ExpertPlan plan = expert_plan(std::max(rows_hint, 1));
+        char* b = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(ws) + 255) & ~uintptr_t(255));
+        __half* yr = reinterpret_cast<__half*>(b);
+        b += align256(size_t(max_rows) * H * 2);
+        ExpertScratch es = carve_experts(b, max_rows, NM, H, I, plan);
+        es.counts = sw.counts_local;
+        __half* xr = static_cast<__half*>(pr.p[rank]);
+        k_moe_scan<<<1, 1024, 0, cs>>>(es.counts, es.offsets, es.problems, es.n_problems, NL, plan.chunk, TS);
+        cuda_ok(cudaGetLastError(), "k_moe_scan launch");
+        if (TS) {
+            k_rows_to_offset<<<std::min(TS, 148 * 8), 256, 0, cs>>>((const __half*) x_local, xr, es.offsets + NL, TS, H, max_rows);
+            cuda_ok(cudaGetLastError(), "k_rows_to_offset launch");
+        }
+        st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
+                            w->down_suh, w->down_svh, NM, xr, yr, 0, max_rows, plan, es, sc, info.sms, cs, es.offsets + NM);
+        k_ep_return<<<148 * 8, 256, 0, cs>>>(yr, es.offsets, pc, sw.send_off, pt, rank, world, n_experts_total, NL, H, max_rows, max_send, sc.status);
+        cuda_ok(cudaGetLastError(), "k_ep_return launch");
+        k_ep_barrier<<<1, 32, 0, cs>>>(pf, 2, rank, world, epoch, sc.status);
+        cuda_ok(cudaGetLastError(), "k_ep_barrier launch");
+        if (TS) {
+            k_rows_from_offset<<<std::min(TS, 148 * 8), 256, 0, cs>>>(yr, (__half*) ysh, es.offsets + NL, TS, H, max_rows);
+            cuda_ok(cudaGetLastError(), "k_rows_from_offset launch");
+        }
+        st.launch = "k_moe_scan + 3 x (" + st.launch + ") + k_silu_mul_rows + k_ep_return + k_ep_barrier";
     });
 }
 

@@ -151,6 +151,18 @@ __global__ void __launch_bounds__(256) k_silu_mul(const __half2* gate, const __h
     }
 }
 
+// The same over the first *n_rows rows of `row_pairs` half pairs each (row count known on the device only).
+__global__ void __launch_bounds__(256) k_silu_mul_rows(const __half2* gate, const __half2* up, __half2* out,
+                                                       const int* __restrict__ n_rows, int max_rows, int row_pairs, float limit)
+{
+    const long long pairs = (long long) min(max(__ldg(n_rows), 0), max_rows) * row_pairs;
+    for (long long i = (long long) blockIdx.x * 256 + threadIdx.x; i < pairs; i += (long long) gridDim.x * 256) {
+        __half2 g = gate[i], u = up[i];
+        out[i] = __halves2half2(silu_mul_one(__low2half(g), __low2half(u), limit),
+                                silu_mul_one(__high2half(g), __high2half(u), limit));
+    }
+}
+
 __global__ void __launch_bounds__(256) k_add_f32(const float* a, const float* b, float* c, int n)
 {
     pdl_trigger();
@@ -160,6 +172,15 @@ __global__ void __launch_bounds__(256) k_add_f32(const float* a, const float* b,
 }
 
 }  // namespace
+
+// SiLU(gate) * up over the first *n_rows rows (device-side count, at most max_rows) of row_elems fp16 each.
+void silu_mul_rows(const void* gate, const void* up, void* out, const int* n_rows, int max_rows, int row_elems, cudaStream_t stream)
+{
+    const long long pairs = (long long) max_rows * (row_elems / 2);
+    const int grid = int(std::max<long long>(1, std::min<long long>((pairs + 255) / 256, 148LL * 8)));
+    k_silu_mul_rows<<<grid, 256, 0, stream>>>((const __half2*) gate, (const __half2*) up, (__half2*) out, n_rows, max_rows, row_elems / 2, 0.0f);
+    cuda_ok(cudaGetLastError(), "silu_mul_rows launch");
+}
 
 // Internal C++ entry points (shared with the prefill path).
 void reconstruct(void* unpacked, const void* packed, int size_k, int slice_n, int full_n, int n_offset,

@@ -386,3 +386,79 @@ class EpMoeLayer:
         if ysh is not None:
             ysh.record_stream(main)
         return ysh
+
+
+class P2pMoeLayer:
+    """Expert-parallel MoE layer whose exchange is done by the kernels themselves over peer memory: routed
+    rows are stored straight into the owning rank's buffer at their final, expert-sorted position, expert
+    outputs straight back into the sender's buffer, with three flag barriers per layer.  No collective call
+    and no host synchronisation inside a layer.  The symmetric buffers come from
+    ``torch.distributed._symmetric_memory`` (one allocation per buffer, rendezvous over `group`); the ranks
+    must share one NVSwitch box.  ``stages`` is this rank's ``GpuStages`` (local expert stacks)."""
+
+    def __init__(self, stages: GpuStages, group, n_experts: int, top_k: int, max_tokens: int, max_rows: int):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.dist, self.group, self.stages = dist, group, stages
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise Error("P2pMoeLayer: at most 8 ranks")
+        if n_experts % self.world:
+            raise Error(f"{n_experts} experts do not split evenly over {self.world} ranks")
+        self.E, self.k, self.n_local = n_experts, top_k, n_experts // self.world
+        self.max_tokens, self.max_rows, self.max_send = max_tokens, max_rows, max_tokens * top_k
+        d, dev, l = stages.d, stages.device, _lib.lib()
+        H = d["hidden"]
+        gname = group.group_name if hasattr(group, "group_name") else group
+
+        def symmetric(nbytes):
+            t = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+            t.zero_()
+            h = symm_mem.rendezvous(t, gname)
+            ptrs = (C.c_void_p * self.world)(*[int(p) for p in h.buffer_ptrs])
+            return t, h, ptrs
+
+        self._cnt, self._cnt_h, self.cnt_ptrs = symmetric(self.world * n_experts * 4)
+        self._flags, self._flags_h, self.flag_ptrs = symmetric(3 * 8 * 4)
+        self._recv, self._recv_h, self.recv_ptrs = symmetric(max_rows * H * 2)
+        self._ret, self._ret_h, self.ret_ptrs = symmetric(max(self.max_send, 1) * H * 2)
+        torch.cuda.synchronize(dev)
+        dist.barrier(group)          # every rank's flags are zero before the first epoch
+        self.epoch = 0
+        self.send_ws = torch.empty(l.berth_moe_p2p_send_workspace_bytes(max(max_tokens, 1), n_experts, top_k, self.world), dtype=torch.uint8, device=dev)
+        self.exp_ws = torch.empty(l.berth_moe_p2p_experts_workspace_bytes(max_rows, self.n_local, H, d["inter"]), dtype=torch.uint8, device=dev)
+        self.ret_rows = self._ret.view(torch.float16).view(-1, H)
+        self.last_stats = {}
+
+    def forward(self, x: torch.Tensor):
+        """x fp16 [T_local][hidden] -> (out fp32 [T_local][hidden], topk_idx, topk_w).  Asynchronous on the
+        current stream; all ranks must call it the same number of times."""
+        st, l = self.stages, _lib.lib()
+        T, H = x.shape
+        if T > self.max_tokens:
+            raise Error(f"P2pMoeLayer: {T} tokens exceed max_tokens = {self.max_tokens}")
+        dev, k = x.device, self.k
+        self.epoch += 1
+        idx = torch.empty((T, k), dtype=torch.int32, device=dev)
+        w = torch.empty((T, k), dtype=torch.float32, device=dev)
+        inv = torch.empty(max(T * k, 1), dtype=torch.int32, device=dev)
+        kp = st.layer._keep
+        bias = kp.get("router_bias")
+        p = lambda t: t.data_ptr() if t.numel() else None
+        st._check(l.berth_moe_p2p_send(p(x), T, kp["w_router"].data_ptr(), None if bias is None else bias.data_ptr(), H, self.E, k,
+                                       p(idx), p(w), inv.data_ptr(), self.rank, self.world, self.epoch, self.cnt_ptrs, self.flag_ptrs,
+                                       self.recv_ptrs, self.max_rows, self.send_ws.data_ptr(), self.send_ws.numel(), None))
+        stacked = st.shared_is_stacked() and T > 0
+        ysh = torch.empty((T, H), dtype=torch.float16, device=dev) if stacked else None
+        # rows per local expert to size the problems for: twice the mean if every rank holds as many tokens as this one
+        hint = max(1, min(1024, -(-2 * max(T, 1) * self.world * k // self.E)))
+        st._check(l.berth_moe_p2p_experts(C.byref(st.layer.c), p(x), T, None if ysh is None else ysh.data_ptr(), self.rank, self.world,
+                                          self.epoch, self.E, k, T, self.cnt_ptrs, self.flag_ptrs, self.recv_ptrs, self.ret_ptrs,
+                                          self.max_rows, max(self.max_send, 1), hint, self.send_ws.data_ptr(), self.exp_ws.data_ptr(),
+                                          self.exp_ws.numel(), None))
+        if T == 0:
+            return torch.empty((0, H), dtype=torch.float32, device=dev), idx, w
+        if ysh is None and getattr(st, "shared", None) is not None:
+            ysh = st.shared_expert(x)
+        out = st.combine(self.ret_rows[: T * k], inv[: T * k], w, ysh)
+        return out, idx, w

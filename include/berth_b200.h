@@ -207,6 +207,32 @@ int berth_moe_ep_experts(const berth_moe_weights* w, const void* recv_rows, int 
                          const int32_t* cnt_recv, int world, const void* x_local, int T_local, void* back,
                          void* ysh, void* ws, size_t ws_bytes, int max_rows, int max_tokens, int rows_hint,
                          void* stream);
+/* The same two sides with the exchange done by the kernels themselves, over peer memory (the ranks of
+ * one NVSwitch box; no collective library call, no host synchronisation; no counterpart in berth).
+ * The host allocates four symmetric buffers on every rank and passes the per-rank device addresses
+ * (host arrays of `world` pointers, world <= 8):
+ *   cnt_all    int32 [world][n_experts]      rows per expert of every rank (each rank writes its row everywhere)
+ *   flags      uint32 [3][8], zero at start  flag barriers: counts published / rows delivered / outputs returned
+ *   recv_rows  fp16 [max_rows][hidden]       routed rows, written by their sources at their final, expert-sorted place
+ *   ret_rows   fp16 [max_send][hidden]       expert outputs, written by the experts' ranks at the row's send position
+ * `epoch` must grow by one with every layer call, the same on all ranks.  A rank calls p2p_send (route,
+ * sort, publish counts, deliver rows), then p2p_experts (experts on what arrived, plus the shared expert
+ * of its own T_local tokens when ysh != NULL -- it must then sit behind the stacks as matrix n_local --,
+ * return the outputs), then berth_moe_combine on its own ret_rows with the inv / topk_w of p2p_send.
+ * max_rows bounds the rows a rank can receive plus its own T_local; a row that would not fit is dropped
+ * and reported in berth_device_status (bit 64); a peer that never arrives ends the wait after about half
+ * a second (bit 32). */
+size_t berth_moe_p2p_send_workspace_bytes(int T, int n_experts, int top_k, int world);
+int berth_moe_p2p_send(const void* x, int T, const void* w_router, const float* router_bias, int hidden,
+                       int n_experts, int top_k, int32_t* topk_idx, float* topk_w, int32_t* inv, int rank,
+                       int world, unsigned epoch, const void* const* cnt_all, const void* const* flags,
+                       const void* const* recv_rows, int max_rows, void* ws, size_t ws_bytes, void* stream);
+size_t berth_moe_p2p_experts_workspace_bytes(int max_rows, int n_local, int hidden, int inter);
+int berth_moe_p2p_experts(const berth_moe_weights* w, const void* x_local, int T_local, void* ysh, int rank,
+                          int world, unsigned epoch, int n_experts_total, int top_k, int send_tokens,
+                          const void* const* cnt_all, const void* const* flags, const void* const* recv_rows,
+                          const void* const* ret_rows, int max_rows, int max_send, int rows_hint, void* send_ws,
+                          void* ws, size_t ws_bytes, void* stream);
 const char* berth_moe_last_error(void);
 const char* berth_moe_last_launch(void);
 
