@@ -281,7 +281,12 @@ def bench_moe(rank: int, world: int, steps: int = 20, tokens=(1, 64, 1024)) -> d
     else:
         # a rank may receive more rows than it sends (skewed routing): room for four times the mean
         stages = moe.GpuStages(dev, w, E, max_rows=4 * 1024 * K, max_rows_per_expert=1024)
-        layer = moe.EpMoeLayer(stages, dist.group.WORLD, E, K)
+        try:    # exchange by the kernels themselves over peer memory; NCCL all-to-alls if symmetric memory is not to be had
+            layer = moe.P2pMoeLayer(stages, dist.group.WORLD, E, K, max_tokens=1024, max_rows=4 * 1024 * K)
+            out["exchange"] = "peer-memory stores + flag barriers (no collective, no host sync)"
+        except Exception as exc:   # noqa: BLE001 - any failure of the symmetric allocation
+            layer = moe.EpMoeLayer(stages, dist.group.WORLD, E, K)
+            out["exchange"] = f"NCCL all_to_all_single (symmetric memory unavailable: {type(exc).__name__})"
     # global batches (the batch is split over the ranks), then, on several GPUs, 1024 tokens on every rank
     cases = [(T, False) for T in tokens] + ([(1024 * world, True)] if world > 1 and 1024 in tokens else [])
     for T, weak in cases:

@@ -161,3 +161,38 @@ def test_shared_expert_inside_the_grouped_launches(T):
     assert (idx_f == idx_p).all() and (w_f == w_p).all()
     rms = np.sqrt((plain.astype(np.float64) ** 2).mean())
     assert np.abs(fused - plain).max() <= 5e-3 * rms
+
+
+def test_peer_memory_layer_on_one_rank():
+    """P2pMoeLayer (exchange by peer-memory stores and flag barriers inside the kernels) on a single-rank
+    group: the rank is its own peer, so the whole send / deliver / experts / return / combine chain runs,
+    and the result equals the fused single-GPU layer's."""
+    import torch.distributed as dist
+    if not dist.is_available() or not dist.is_nccl_available():
+        pytest.skip("torch.distributed with NCCL is not available")
+    H, I, E, k, bits, cb = 256, 128, 32, 4, 4, 2
+    wts = synth.moe_layer_weights(1234, "p2p1", H, I, E, k, bits, cb, shared_inter=128)
+    own_group = not dist.is_initialized()
+    if own_group:
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29533", rank=0, world_size=1,
+                                device_id=torch.device("cuda", torch.cuda.current_device()))
+    try:
+        device = torch.device("cuda", torch.cuda.current_device())
+        stages = moe.GpuStages(device, wts, E, max_rows=64 * k + 64, max_rows_per_expert=64)
+        try:
+            layer = moe.P2pMoeLayer(stages, dist.group.WORLD, E, k, max_tokens=64, max_rows=64 * k + 64)
+        except Exception as exc:   # symmetric memory needs driver support that not every box has
+            pytest.skip(f"symmetric memory unavailable: {exc!r}")
+        for T in (1, 48):
+            x = synth.activations(1234, f"p2p1.x{T}", T, H)
+            ref, ref_idx, _ = _run_layer(wts, x)
+            for _ in range(2):    # twice: the epochs of the flag barriers advance
+                out, idx, w = layer.forward(dev(x))
+            torch.cuda.synchronize()
+            assert kernels.device_status(torch.cuda.current_device()) == 0
+            assert (idx.cpu().numpy() == ref_idx).all()
+            rms = np.sqrt((ref.astype(np.float64) ** 2).mean())
+            assert np.abs(out.cpu().numpy() - ref).max() <= 1e-3 * rms
+    finally:
+        if own_group:
+            dist.destroy_process_group()
