@@ -28,9 +28,12 @@
  * Per-device state owned by the library, allocated at the first launch on a device and kept
  * until exit (the counterpart of the lock buffer and 16 MiB split-K workspace of
  * crates/berth-kernels/csrc/linear.cu:334-345 and csrc/int8_sq.cu:20-47): about 40 MiB (split-K
- * partial-sum slabs, rotated activations, self-resetting arrival counters, block sums).  Launches that overlap on one device
- * (different streams) must not share it: berth drives one stream per device, and so must
- * every other caller.
+ * partial-sum slabs, rotated activations, block sums).  Launches of the decode kernels (up to 32
+ * rows, and the grouped decode launches of the MoE layer) that overlap on one device (different
+ * streams) must not share it: berth drives one stream per device, and so must every other caller.
+ * The prefill kernels use none of it.  The kernels of one linear are chained by programmatic
+ * dependent launch: a decode kernel may prefetch weights while the kernel before it on the stream
+ * still runs, so the trellis must not be written by the kernel that directly precedes a linear.
  */
 #ifndef BERTH_B200_H
 #define BERTH_B200_H
@@ -56,14 +59,13 @@ const char* berth_exl3_last_launch(void);   /* crates/berth-kernels/csrc/linear.
  * every byte of HBM, or a decode loop that cannot take cudaMalloc's device-wide synchronisation).
  * No counterpart in berth: its library allocates its workspaces with cudaMalloc at first use.
  * The scratch is a fixed __device__ array of about 6.1 MiB inside the library image (4 MiB
- * partial-sum slabs, 2 MiB rotated activations, 16 KiB counters, 128 KiB block sums, a status
- * word), held by every GPU that loads the library until the process exits; nothing is allocated
- * or freed.  Limits: size_m <= 32, size_n <= 131072 and size_k * ceil(size_m / 8) <= 131072;
+ * partial-sum slabs, 2 MiB rotated activations, 128 KiB block sums, a status word), held by
+ * every GPU that loads the library until the process exits; nothing is allocated or freed.  Limits: size_m <= 32, size_n <= 131072 and size_k * ceil(size_m / 8) <= 131072;
  * larger sizes are rejected with an error.  The first
  * call on a device looks the array's device address up (cudaGetSymbolAddress); make that first
  * call before any stream capture begins.  All calls on a device share the scratch, which keeps
- * the previous call's contents (the counters are cleared on `stream` before each launch): calls
- * that overlap on the GPU race, so issue them on one stream. */
+ * the previous call's contents (every part is overwritten before it is read): calls that overlap
+ * on the GPU race, so issue them on one stream. */
 int berth_exl3_linear_static_scratch(const void* a, const void* trellis, void* c, const void* suh,
                                      void* a_had, const void* svh, int size_m, int size_k,
                                      int size_n, int k_bits, int codebook, int out_fp32,
