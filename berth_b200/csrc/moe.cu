@@ -101,66 +101,6 @@ __global__ void __launch_bounds__(kRouterWarps * 32, 2) k_moe_router_logits(cons
     }
 }
 
-// The same logits for hidden = 2048 (chunks of 64): 16 warps, each owning chunks j and j + 16, lane = expert,
-// and the thread's 128 router weights stay in registers while the block walks over its token tiles (tile =
-// blockIdx.y, + gridDim.y, ...), so the router matrix is read from L2 once per block instead of once per
-// token tile.  Same summation order, bit for bit.
-__global__ void __launch_bounds__(512, 1) k_moe_router_logits_2048(const __half* __restrict__ x, const __half* __restrict__ w,
-                                                                   const float* __restrict__ bias, float* __restrict__ logits,
-                                                                   int T, int E)
-{
-    constexpr int H = 2048, CH = 64;
-    extern __shared__ __align__(16) float rsm[];
-    float* xs = rsm;                                                    // [kRouterTok][H]
-    float (*part)[kRouterTok][33] = reinterpret_cast<float (*)[kRouterTok][33]>(rsm + kRouterTok * H);
-    const int wq = threadIdx.x >> 5, el = threadIdx.x & 31;
-    const int e = blockIdx.x * 32 + el;
-    __half2 wreg[2][CH / 2];
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-        const __half* wr = w + size_t(wq + 16 * c) * CH * E + e;
-#pragma unroll
-        for (int i = 0; i < CH / 2; ++i) wreg[c][i] = __halves2half2(wr[size_t(2 * i) * E], wr[size_t(2 * i + 1) * E]);
-    }
-    const float bias_e = bias ? bias[e] : 0.f;
-    const int ntiles = (T + kRouterTok - 1) / kRouterTok;
-    for (int tile = blockIdx.y; tile < ntiles; tile += gridDim.y) {
-        const int t0 = tile * kRouterTok;
-        __syncthreads();   // the previous tile's sums have been read
-        for (int i = threadIdx.x * 2; i < kRouterTok * H; i += 1024) {
-            const int tt = i >> 11, h = i & (H - 1);
-            const __half2 v = *reinterpret_cast<const __half2*>(x + size_t(min(t0 + tt, T - 1)) * H + h);
-            xs[i] = __low2float(v);
-            xs[i + 1] = __high2float(v);
-        }
-        __syncthreads();
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            const int j = wq + 16 * c;
-            const float* xj = xs + j * CH;
-            float acc[kRouterTok];
-#pragma unroll
-            for (int tt = 0; tt < kRouterTok; ++tt) acc[tt] = 0.f;
-#pragma unroll
-            for (int q = 0; q < CH / 4; ++q) {
-                const float w0 = __low2float(wreg[c][2 * q]), w1 = __high2float(wreg[c][2 * q]);
-                const float w2 = __low2float(wreg[c][2 * q + 1]), w3 = __high2float(wreg[c][2 * q + 1]);
-#pragma unroll
-                for (int tt = 0; tt < kRouterTok; ++tt) {
-                    const float4 a = *reinterpret_cast<const float4*>(xj + tt * H + 4 * q);
-                    acc[tt] = __fmaf_rn(a.x, w0, acc[tt]); acc[tt] = __fmaf_rn(a.y, w1, acc[tt]);
-                    acc[tt] = __fmaf_rn(a.z, w2, acc[tt]); acc[tt] = __fmaf_rn(a.w, w3, acc[tt]);
-                }
-                asm volatile("" ::: "memory");   // keep the loads of the next quad behind this one (register budget)
-            }
-#pragma unroll
-            for (int tt = 0; tt < kRouterTok; ++tt) part[j][tt][el] = acc[tt];
-        }
-        __syncthreads();
-        if (wq < kRouterTok && t0 + wq < T) logits[size_t(t0 + wq) * E + e] = __fadd_rn(chunk_tree<1>(&part[0][wq][el], 0), bias_e);
-    }
-}
-
 // One warp per token: k rounds of arg-max, value descending then index ascending.
 __global__ void __launch_bounds__(128) k_moe_topk(const float* __restrict__ logits, int32_t* __restrict__ topk_idx,
                                                   float* __restrict__ topk_w, int T, int E, int k)
@@ -660,20 +600,8 @@ void router_topk(const void* x, const void* w_router, const float* bias, int32_t
         cuda_ok(cudaFuncSetAttribute(k_moe_router_logits, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "router smem attribute");
         attr_set[dev] = true;
     }
-    const int ntiles = (T + kRouterTok - 1) / kRouterTok;
-    if (H == 2048 && ntiles > 1) {
-        // one block per SM: expert groups x as many token partitions as fill the device
-        static bool attr2_set[kMaxDevices] = {};
-        if (!attr2_set[dev]) {
-            cuda_ok(cudaFuncSetAttribute(k_moe_router_logits_2048, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "router smem attribute");
-            attr2_set[dev] = true;
-        }
-        const int parts = std::max(1, std::min(ntiles, device_info(dev).sms / (E / 32)));
-        k_moe_router_logits_2048<<<dim3(E / 32, parts), 512, smem, st>>>((const __half*) x, (const __half*) w_router, bias, logits, T, E);
-    } else {
-        k_moe_router_logits<<<dim3(E / 32, ntiles), kRouterWarps * 32, smem, st>>>((const __half*) x, (const __half*) w_router, bias, logits,
-                                                                                  T, H, E);
-    }
+    k_moe_router_logits<<<dim3(E / 32, (T + kRouterTok - 1) / kRouterTok), kRouterWarps * 32, smem, st>>>((const __half*) x, (const __half*) w_router,
+                                                                                           bias, logits, T, H, E);
     cuda_ok(cudaGetLastError(), "k_moe_router_logits launch");
     k_moe_topk<<<(T + 3) / 4, 128, 0, st>>>(logits, topk_idx, topk_w, T, E, k);
     cuda_ok(cudaGetLastError(), "k_moe_topk launch");
