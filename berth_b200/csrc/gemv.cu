@@ -101,7 +101,43 @@ struct GemvArgs {
     float* slabs;             // [2*G][m][BU*128]
     unsigned* status;
     int m, k, n, out_fp32;
+    // Sliced multi-linear (several column slices of several matrices applied to one input): device arrays
+    // with one entry per slice -- trellis address of the slice's first tile, its output scales, its
+    // output address, the full width of the matrix it was cut from (row stride of trellis and output),
+    // and which of the rotated inputs it takes.  Null b_list = not sliced.
+    const unsigned long long* b_list;
+    const unsigned long long* svh_list;
+    const unsigned long long* c_list;
+    const int* n_stride_list;
+    const int* had_src_list;
+    int n_slices;
 };
+
+// What the roles of the decode kernel need to know about problem pi of a launch.
+struct ProblemView {
+    int rows, row0, z;       // rows of the problem, first row in the activation / output arrays, matrix of the stack
+    int act;                 // which rotated-activation block set and block-sum table it reads
+    const __half* svh;       // output scales of the problem's matrix (column 0 of the problem)
+    void* c;                 // output base (row 0, column 0 of the problem)
+    int ldc;                 // output row stride in elements
+};
+template <typename Args>
+__device__ __forceinline__ ProblemView problem_view(const Args& p, int pi, int tok)
+{
+    ProblemView v;
+    v.rows = p.m; v.row0 = 0; v.z = 0; v.act = 0; v.svh = p.svh; v.c = p.c; v.ldc = p.n;
+    if (p.b_list) {
+        v.act = __ldg(p.had_src_list + pi);
+        v.svh = reinterpret_cast<const __half*>(__ldg(p.svh_list + pi));
+        v.c = reinterpret_cast<void*>(__ldg(p.c_list + pi));
+        v.ldc = __ldg(p.n_stride_list + pi);
+    } else if (p.problems) {
+        const GemvProblem pr = load_problem(p.problems, pi, p.n_matrices, tok, p.max_rows);
+        v.rows = pr.rows; v.row0 = pr.row0; v.z = pr.z; v.act = pi;
+        v.svh = p.svh + size_t(pr.z) * p.n;
+    }
+    return v;
+}
 
 // ---------------------------------------------------------------- mbarrier / TMA PTX
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
@@ -376,8 +412,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bands = p.n >> 7, kblocks = p.k >> 7;
     const int bgroups = (bands + BU - 1) / BU;          // band groups of one problem
-    const bool grouped = p.problems != nullptr;
-    const int nprob = grouped ? min(max(__ldg(p.n_problems), 0), p.max_problems) : 1;
+    const bool sliced = p.b_list != nullptr;
+    const bool grouped = p.problems != nullptr || sliced;
+    const int nprob = sliced ? p.n_slices : (p.problems ? min(max(__ldg(p.n_problems), 0), p.max_problems) : 1);
     const long long U = (long long) nprob * bgroups * kblocks;
     const int cta = blockIdx.x;
     const int G = U < (long long) gridDim.x ? int(U) : int(gridDim.x);   // CTAs that own units
@@ -401,20 +438,30 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
+            if (!sliced) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
             // unit -> TMA coordinates of the weights and source of the activation block
             auto issue_weights = [&](int i, uint32_t dst, uint32_t bar) {
                 const long long u = u0 + i;
                 const int gbg = int(u / kblocks), kb = int(u - (long long) gbg * kblocks);
                 const int pi = gbg / bgroups, lbg = gbg - pi * bgroups;
-                const int z = grouped ? load_problem(p.problems, pi, p.n_matrices, TOK, p.max_rows).z : 0;
+                if (sliced) {
+                    // the slice's address comes from a device array, so no tensor map: one bulk copy per k-tile row
+                    const unsigned char* base = reinterpret_cast<const unsigned char*>(__ldg(p.b_list + pi));
+                    const size_t row_stride = size_t(__ldg(p.n_stride_list + pi) / 16) * (NW * 4);
+#pragma unroll
+                    for (int r = 0; r < 8; ++r)
+                        bulk_load_1d(dst + r * ROW_BYTES, base + size_t(kb * 8 + r) * row_stride + size_t(lbg) * ROW_BYTES, ROW_BYTES, bar);
+                    return;
+                }
+                const int z = p.problems ? load_problem(p.problems, pi, p.n_matrices, TOK, p.max_rows).z : 0;
                 tma_load_3d(dst, &tmap, lbg * (ROW_BYTES / 8), kb * 8, z, bar);
             };
             auto issue_acts = [&](int i, uint32_t dst, uint32_t bar) {
                 const long long u = u0 + i;
                 const int gbg = int(u / kblocks), kb = int(u - (long long) gbg * kblocks);
                 const int pi = gbg / bgroups;
-                bulk_load_1d(dst, p.afrag + (size_t(pi) * kblocks + kb) * (ACT_BYTES / 4), ACT_BYTES, bar);
+                const int act = sliced ? __ldg(p.had_src_list + pi) : pi;
+                bulk_load_1d(dst, p.afrag + (size_t(act) * kblocks + kb) * (ACT_BYTES / 4), ACT_BYTES, bar);
             };
             // The weights do not depend on the rotation kernel: fill the ring with them first,
             // then wait for the activations and complete those stages.
@@ -528,7 +575,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
         // Block sums and the problem table come from the preceding kernels, and the slabs may still be
         // read by the finishing kernel of the previous linear.
         grid_dependency_wait();
-        const int slab_rows = grouped ? TOK : p.m;
+        const int slab_rows = p.problems ? TOK : p.m;
         const size_t slab_floats = size_t(slab_rows) * BU * 128;
         int flush = 0;
         long long u = u0;
@@ -536,11 +583,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
             const Segment sg = segment_at(u, u0, u1, kblocks);
             // the problem this band group belongs to: its rows, output rows, sign-scale vector
             const int pi = sg.bg / bgroups, lbg = sg.bg - pi * bgroups;
-            int rows = p.m, row0 = 0, z = 0;
-            if (grouped) {
-                const GemvProblem pr = load_problem(p.problems, pi, p.n_matrices, TOK, p.max_rows);
-                rows = pr.rows; row0 = pr.row0; z = pr.z;
-            }
+            const ProblemView pv = problem_view(p, pi, TOK);
+            const int rows = pv.rows, row0 = pv.row0;
             const int buf = flush & 1;
             // A whole band group is finished here: fetch what that needs (the row sums of the rotated
             // activations, the output scales) while the streaming warps are still busy with the segment.
@@ -548,7 +592,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
             float sxr[kRowsPerWarp];
             uint2 svr[BU];
             if (sg.whole) {
-                const float* bsum = p.blocksum + size_t(pi) * slab_rows * kblocks;
+                const float* bsum = p.blocksum + size_t(pv.act) * slab_rows * kblocks;
 #pragma unroll
                 for (int r = 0; r < kRowsPerWarp; ++r) {
                     const int row = ew + r * kEpiWarps;
@@ -557,8 +601,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
 #pragma unroll
                 for (int b = 0; b < BU; ++b) {
                     const int band = lbg * BU + b;
-                    svr[b] = band < bands ? __ldg(reinterpret_cast<const uint2*>(p.svh + size_t(z) * p.n + band * 128 + lane * 4))
-                                          : make_uint2(0u, 0u);
+                    svr[b] = band < bands ? __ldg(reinterpret_cast<const uint2*>(pv.svh + band * 128 + lane * 4)) : make_uint2(0u, 0u);
                 }
             }
             handover_wait(2 + buf);
@@ -588,7 +631,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
                             if (band < bands) {   // ragged last band group
                                 float4 t = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
                                 float v[4] = {t.x, t.y, t.z, t.w};
-                                finish_band<CB == 2>(v, sxr[r], lane, svr[b], band, p.c, size_t(row0 + row), p.n, p.out_fp32);
+                                finish_band<CB == 2>(v, sxr[r], lane, svr[b], band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32);
                             }
                         }
                     }
@@ -616,6 +659,12 @@ struct FinishArgs {
     const int* n_problems;
     int max_problems, n_matrices, max_rows;
     int m, k, n, out_fp32, bu, tok, main_grid, mul1;
+    const unsigned long long* b_list;      // sliced launch (see GemvArgs), else null
+    const unsigned long long* svh_list;
+    const unsigned long long* c_list;
+    const int* n_stride_list;
+    const int* had_src_list;
+    int n_slices;
 };
 
 __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
@@ -625,8 +674,7 @@ __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
     const int lane = threadIdx.x & 31;
     const int bands = p.n >> 7, kblocks = p.k >> 7, bu = p.bu;
     const int bgroups = (bands + bu - 1) / bu;
-    const bool grouped = p.problems != nullptr;
-    const int nprob = grouped ? min(max(__ldg(p.n_problems), 0), p.max_problems) : 1;
+    const int nprob = p.b_list ? p.n_slices : (p.problems ? min(max(__ldg(p.n_problems), 0), p.max_problems) : 1);
     const long long U = (long long) nprob * bgroups * kblocks;
     const int G = U < (long long) p.main_grid ? int(U) : p.main_grid;
     const int c = blockIdx.x + 1;                      // the boundary between the ranges of CTA c-1 and CTA c
@@ -636,17 +684,14 @@ __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
     const long long g0 = (long long) gbg * kblocks;    // first unit of the band group around the boundary
     if (ub == g0) return;                              // the boundary is a band-group start: nothing straddles it
     if (unit_begin(c - 1, U, G) > g0) return;          // an earlier boundary lies inside the same band group
-    const int slab_rows = grouped ? p.tok : p.m;
+    const int slab_rows = p.problems ? p.tok : p.m;
     const int task = blockIdx.y * 8 + (threadIdx.x >> 5);
     if (task >= bu * slab_rows) return;
     const int b = task / slab_rows, row = task - b * slab_rows;
     const int pi = gbg / bgroups, lbg = gbg - pi * bgroups, band = lbg * bu + b;
     if (band >= bands) return;   // ragged last band group
-    int rows = p.m, row0 = 0, z = 0;
-    if (grouped) {
-        const GemvProblem pr = load_problem(p.problems, pi, p.n_matrices, p.tok, p.max_rows);
-        rows = pr.rows; row0 = pr.row0; z = pr.z;
-    }
+    const ProblemView pv = problem_view(p, pi, p.tok);
+    const int rows = pv.rows, row0 = pv.row0;
     if (row >= rows) return;
     // slabs of this band group, in CTA order: the first CTA's tail (or head, if its range starts
     // exactly here), then the heads of the following CTAs
@@ -655,8 +700,8 @@ __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
     const int first_slab = (unit_begin(first_cta, U, G) >= g0) ? 2 * first_cta : 2 * first_cta + 1;
     const int nsl = last_cta - first_cta + 1;
     const size_t slab_floats = size_t(slab_rows) * bu * 128;
-    const uint2 sr = __ldg(reinterpret_cast<const uint2*>(p.svh + size_t(z) * p.n + band * 128 + lane * 4));
-    const float sx = p.mul1 ? row_sum(p.blocksum + (size_t(pi) * slab_rows + row) * kblocks, kblocks, lane) : 0.f;
+    const uint2 sr = __ldg(reinterpret_cast<const uint2*>(pv.svh + band * 128 + lane * 4));
+    const float sx = p.mul1 ? row_sum(p.blocksum + (size_t(pv.act) * slab_rows + row) * kblocks, kblocks, lane) : 0.f;
     const float* base = p.slabs + (size_t(row) * bu + b) * 128 + lane * 4;
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     for (int i0 = 0; i0 < nsl; i0 += 8) {
@@ -676,8 +721,8 @@ __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
             }
         }
     }
-    if (p.mul1) finish_band<true>(v, sx, lane, sr, band, p.c, size_t(row0 + row), p.n, p.out_fp32);
-    else finish_band<false>(v, sx, lane, sr, band, p.c, size_t(row0 + row), p.n, p.out_fp32);
+    if (p.mul1) finish_band<true>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32);
+    else finish_band<false>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32);
 }
 
 // ---------------------------------------------------------------- rotation of the activations
@@ -686,15 +731,18 @@ __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
 // (k = 16*ktile + 8*h + 2*q, +1) of token 8*tg + t at word ((ktile*TG + tg)*2 + h)*32 + 4*t + q, zero
 // for tokens >= m); blocksum[row][b] = sum of the 128 rounded values of a block.
 // One warp per (token row, 128-block).  Lets the dependent GEMV start early (programmatic launch).
-__global__ void __launch_bounds__(128) k_rotate_in(const __half* __restrict__ a, const __half* __restrict__ suh,
+// With suh_list the sign-scale vector is entry `src` of that device array of addresses (sliced multi-linear).
+__global__ void __launch_bounds__(128) k_rotate_in(const __half* __restrict__ a, const __half* __restrict__ suh_in,
                                                    __half* __restrict__ a_had, uint32_t* __restrict__ afrag,
-                                                   float* __restrict__ blocksum, int rows, int rows_pad, int k)
+                                                   float* __restrict__ blocksum, int rows, int rows_pad, int k,
+                                                   const unsigned long long* __restrict__ suh_list, int src)
 {
     // Trigger first: the decode kernel behind this one may then take each SM as the previous decode
     // kernel leaves it and prefetch its weights; it still waits for this grid, which itself waits here
     // for everything before it (the activations and the scratch this kernel overwrites).
     grid_launch_dependents();
     grid_dependency_wait();
+    const __half* suh = suh_list ? reinterpret_cast<const __half*>(__ldg(suh_list + src)) : suh_in;
     const int lane = threadIdx.x & 31, kblocks = k >> 7, tgs = rows_pad >> 3;
     const int total = rows_pad * kblocks;
     for (int idx = blockIdx.x * 4 + (threadIdx.x >> 5); idx < total; idx += gridDim.x * 4) {
@@ -760,7 +808,8 @@ size_t launch_one(const void* trellis, int n_matrices, const GemvArgs& args, int
         cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmem)), "gemv smem attribute");
         attr_set[dev] = true;
     }
-    const CUtensorMap map = trellis_map(trellis, n_matrices, args.k, args.n, BITS, G_::ROW_BYTES);
+    CUtensorMap map = {};   // a sliced launch addresses its weights through a device array, not through this map
+    if (!args.b_list) map = trellis_map(trellis, n_matrices, args.k, args.n, BITS, G_::ROW_BYTES);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);
@@ -850,6 +899,8 @@ void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int codebo
     f.max_problems = a.max_problems; f.n_matrices = a.n_matrices; f.max_rows = a.max_rows;
     f.m = a.m; f.k = a.k; f.n = a.n; f.out_fp32 = a.out_fp32;
     f.bu = bu; f.tok = tok; f.main_grid = main_grid; f.mul1 = codebook == 2;
+    f.b_list = a.b_list; f.svh_list = a.svh_list; f.c_list = a.c_list; f.n_stride_list = a.n_stride_list; f.had_src_list = a.had_src_list;
+    f.n_slices = a.n_slices;
     const int slab_rows = a.problems ? tok : a.m;
     launch_pdl(k_gemv_finish, dim3(main_grid - 1, (bu * slab_rows + 7) / 8), dim3(256), 0, stream, "k_gemv_finish launch", f);
 }
@@ -892,7 +943,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
         const int rot_total = 8 * tg * kblocks;
         launch_pdl(k_rotate_in, dim3(std::min((rot_total + 3) / 4, 4 * sms)), dim3(128), 0, stream, "k_rotate_in launch",
                    static_cast<const __half*>(a), static_cast<const __half*>(suh), static_cast<__half*>(a_had), sc.afrag,
-                   sc.blocksum, size_m, 8 * tg, size_k);
+                   sc.blocksum, size_m, 8 * tg, size_k, (const unsigned long long*) nullptr, 0);
     }
 
     GemvArgs args;
@@ -910,6 +961,8 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     args.problems = nullptr;
     args.n_problems = nullptr;
     args.max_problems = 1; args.n_matrices = 1; args.max_rows = size_m;
+    args.b_list = nullptr; args.svh_list = nullptr; args.c_list = nullptr; args.n_stride_list = nullptr; args.had_src_list = nullptr;
+    args.n_slices = 0;
     const size_t smem = launch_bits(k_bits, codebook, tg, fused, trellis, 1, args, grid, stream);
     launch_finish(args, bu, 8 * tg, grid, codebook, stream);
     return std::string(fused ? "" : "k_rotate_in + ") + "k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," +
@@ -949,11 +1002,70 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
     args.status = sc.status;
     args.m = 8 * tg; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
+    args.b_list = nullptr; args.svh_list = nullptr; args.c_list = nullptr; args.n_stride_list = nullptr; args.had_src_list = nullptr;
+    args.n_slices = 0;
     const size_t smem = launch_bits(k_bits, codebook, tg, false, trellis_stack, n_experts, args, grid, stream);
     launch_finish(args, bu, 8 * tg, grid, codebook, stream);
     return "k_rotate_rows + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," + std::to_string(tg) +
            ",grouped> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem) +
            " + k_gemv_finish";
+}
+
+// Sliced multi-linear on the decode kernel: `n_slices` column slices of width size_n, cut from `num_had_src`
+// matrices, all applied to the same size_m rows of `a`.  Every list is a DEVICE array (see GemvArgs).
+std::string launch_gemv_sliced(const void* a, const void* b_list, const void* suh_list, void* a_had, const void* svh_list,
+                               const void* c_list, const int* n_stride_list, const int* had_src_list, int num_had_src, int n_slices,
+                               int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, const GemvScratch& sc,
+                               int sms, cudaStream_t stream)
+{
+    if (size_m > 32) throw std::runtime_error("exl3_mgemm: no linked kernel for size_m above 32");
+    if (size_k % 128 != 0)
+        throw std::runtime_error("exl3_mgemm: no linked kernel for size_k that is not a multiple of 128 (128-wide Hadamard)");
+    const int tg = size_m <= 8 ? 1 : (size_m <= 16 ? 2 : 4);
+    const int bu = k_bits <= 4 ? 2 : 1;
+    if (size_n % (bu * 128) != 0)
+        throw std::runtime_error("exl3_mgemm: no linked kernel for a slice width that is not a multiple of " + std::to_string(bu * 128));
+    const int bands = size_n / 128, kblocks = size_k / 128, bgroups = bands / bu;
+    if (size_t(num_had_src) * size_m * kblocks > sc.blocksum_floats)
+        throw std::runtime_error("exl3_mgemm: sources x size_m x size_k / 128 exceed the block-sum table of the scratch");
+    const size_t afrag_bytes = size_t(size_k / 16) * tg * 256;
+    if (afrag_bytes * num_had_src > sc.afrag_bytes)
+        throw std::runtime_error("exl3_mgemm: sources x size_k x ceil(size_m / 8) exceed the activation-fragment area of the scratch");
+    const long long units = (long long) n_slices * bgroups * kblocks;
+    int grid = int(std::min<long long>(sms, units));
+    const size_t per_cta = size_t(2) * size_m * bu * 128 * sizeof(float);
+    if (size_t(grid) * per_cta > sc.slab_bytes) grid = int(sc.slab_bytes / per_cta);
+    if (grid < 1) throw std::runtime_error("exl3_mgemm: split-K scratch is too small for this shape");
+    const int rot_total = 8 * tg * kblocks;
+    for (int src = 0; src < num_had_src; ++src)
+        launch_pdl(k_rotate_in, dim3(std::min((rot_total + 3) / 4, 4 * sms)), dim3(128), 0, stream, "k_rotate_in launch",
+                   static_cast<const __half*>(a), (const __half*) nullptr, static_cast<__half*>(a_had) + size_t(src) * size_m * size_k,
+                   sc.afrag + size_t(src) * (afrag_bytes / 4), sc.blocksum + size_t(src) * size_m * kblocks, size_m, 8 * tg, size_k,
+                   static_cast<const unsigned long long*>(suh_list), src);
+    GemvArgs args;
+    args.afrag = sc.afrag;
+    args.blocksum = sc.blocksum;
+    args.a = nullptr; args.suh = nullptr; args.a_had = nullptr;
+    args.c = nullptr;
+    args.svh = nullptr;
+    args.problems = nullptr;
+    args.n_problems = nullptr;
+    args.max_problems = n_slices; args.n_matrices = 1; args.max_rows = size_m;
+    args.slabs = sc.slabs;
+    args.status = sc.status;
+    args.m = size_m; args.k = size_k; args.n = size_n;
+    args.out_fp32 = out_fp32;
+    args.b_list = static_cast<const unsigned long long*>(b_list);
+    args.svh_list = static_cast<const unsigned long long*>(svh_list);
+    args.c_list = static_cast<const unsigned long long*>(c_list);
+    args.n_stride_list = n_stride_list;
+    args.had_src_list = had_src_list;
+    args.n_slices = n_slices;
+    const size_t smem = launch_bits(k_bits, codebook, tg, false, nullptr, 1, args, grid, stream);
+    launch_finish(args, bu, 8 * tg, grid, codebook, stream);
+    return std::to_string(num_had_src) + " x k_rotate_in + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," +
+           std::to_string(tg) + ",sliced> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" +
+           std::to_string(smem) + " + k_gemv_finish";
 }
 
 }  // namespace berth

@@ -112,3 +112,52 @@ extern "C" int berth_prefill_exl3_linear(const void* a, const void* trellis, voi
 // Smallest shapes of the two regimes berth's self tests exercise (csrc/linear.cu:406-465 of berth-kernels).
 extern "C" int berth_exl3_smoke_int8(int out_fp32) { return smoke(1, 128, 256, 4, 2, out_fp32); }
 extern "C" int berth_exl3_smoke_gemm(void) { return smoke(1, 128, 512, 6, 2, 0); }
+
+// ------------------------------------------------------------------------------------------
+// Sliced multi-linear (crates/berth-kernels/src/ops.rs:247-367, csrc/ops/mgemm.cu:125-334 of berth): several
+// column slices of several trellis matrices applied to one input in one decode launch.  Host checks in
+// berth's order and wording; every K and codebook is linked here, only the sliced mode is.
+namespace berth {
+std::string launch_gemv_sliced(const void* a, const void* b_list, const void* suh_list, void* a_had, const void* svh_list,
+                               const void* c_list, const int* n_stride_list, const int* had_src_list, int num_had_src, int n_slices,
+                               int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, const GemvScratch& sc,
+                               int sms, cudaStream_t stream);
+}
+
+extern "C" int berth_ops_mgemm(const void* a, const void* b_list, void* c, const void* suh_list, void* a_had, const void* svh_list,
+                               int size_m, int size_k, int size_n, int k_bits, int codebook, int c_fp32, int bszm_in, int bszm_out,
+                               const int* size_n_list, const void* c_ptrs, const int* n_stride_list, const int* had_src_list,
+                               int num_had_src, void* stream)
+{
+    using namespace berth;
+    CallState& st = ops_state();
+    int tag = 0;
+    const int rc = guarded(st, [&] {
+        if (!a || !b_list || !c || !suh_list || !a_had || !svh_list) throw std::runtime_error("exl3_mgemm: null device pointer");
+        if (size_m < 1 || size_k < 1 || size_n < 1 || bszm_in < 1 || bszm_out < 1)
+            throw std::runtime_error("exl3_mgemm: sizes must be positive");
+        if (size_k % 16 != 0) throw std::runtime_error("exl3_mgemm: size_k must be a multiple of 16");
+        if (size_n % 128 != 0) throw std::runtime_error("exl3_mgemm: size_n must be a multiple of 128");
+        if (k_bits < 1 || k_bits > 8 || codebook < 0 || codebook > 2)
+            throw std::runtime_error("exl3_mgemm: no linked kernel for K=" + std::to_string(k_bits) + " codebook=" + std::to_string(codebook));
+        if (c_fp32 != 0 && c_fp32 != 1) throw std::runtime_error("exl3_mgemm: c_fp32 must be 0 (fp16) or 1 (fp32)");
+        const bool any_list = size_n_list || c_ptrs || n_stride_list || had_src_list;
+        if (any_list) {
+            if (!size_n_list || !c_ptrs || !n_stride_list || !had_src_list)
+                throw std::runtime_error("exl3_mgemm: sliced mode requires size_n_list, c_ptrs, n_stride_list, and had_src_list");
+            if (num_had_src < 1) throw std::runtime_error("exl3_mgemm: sliced mode needs one suh entry per source");
+            if (bszm_in != 1) throw std::runtime_error("exl3_mgemm: sliced mode is single-input");
+        } else {
+            if (num_had_src != 0) throw std::runtime_error("exl3_mgemm: num_had_src requires had_src_list");
+            throw std::runtime_error("exl3_mgemm: no linked kernel for the uniform mode (sliced launches only)");
+        }
+        const int device = current_device();
+        const DeviceInfo& info = device_info(device);
+        if (info.major != 10) throw std::runtime_error("exl3_mgemm: no linked kernel for this GPU (library is built for sm_100a only)");
+        st.launch = launch_gemv_sliced(a, b_list, suh_list, a_had, svh_list, c_ptrs, n_stride_list, had_src_list, num_had_src, bszm_out,
+                                       size_m, size_k, size_n, k_bits, codebook, c_fp32, gemv_workspace(device), info.sms,
+                                       (cudaStream_t) stream);
+        tag = size_m <= 8 ? 1 : (size_m <= 16 ? 2 : 4);   // the token groups of the launch, as the positive "shape tag"
+    });
+    return rc == 0 ? tag : rc;
+}

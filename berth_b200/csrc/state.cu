@@ -1,6 +1,8 @@
 // Host-side state of the library: per-thread status strings, per-device facts and the
 // split-K workspace of the decode GEMV; plus the pure-integer entry points berth's tests pin.
 #include "common.cuh"
+
+#include <algorithm>
 #include "../../include/berth_b200.h"
 
 #include <mutex>
@@ -134,6 +136,25 @@ extern "C" uint64_t berth_exl3_gemm_tune_key(int size_m, int size_k, int size_n,
     const uint64_t v[9] = {mk, (uint64_t) size_k, (uint64_t) size_n, (uint64_t) k_bits, out_fp32 ? 1ull : 0ull,
                            (uint64_t) device, (uint64_t) cc, (uint64_t) sms, (uint64_t) cb};
     for (uint64_t x : v) { h ^= x; h *= 1099511628211ull; }
+    return h;
+}
+
+// FNV-1a key of the fork's multi-linear autotune cache (csrc/ops/mgemm.cu:40-91,277-294 of berth-kernels):
+// m bucketed to a power of two up to 16 (m = 1 stays 1), batch sizes capped at 24, sliced launches salted.
+extern "C" uint64_t berth_ops_mgemm_tune_key(int size_m, int size_k, int size_n, int k_bits, int c_fp32, int device, int cc,
+                                             int sms, int cb, int bszm_in, int bszm_out, int sliced)
+{
+    uint64_t mk;
+    if (size_m <= 16) { mk = 1; while (mk < (uint64_t) std::max(size_m, 1)) mk <<= 1; if (mk > 16) mk = 16; }
+    else if (size_m <= 31) mk = 32;
+    else if (size_m <= 63) mk = 64;
+    else if (size_m <= 127) mk = 128;
+    else mk = 512;
+    uint64_t h = 1469598103934665603ull;
+    const uint64_t v[11] = {mk, (uint64_t) size_k, (uint64_t) size_n, (uint64_t) k_bits, c_fp32 ? 1ull : 0ull, (uint64_t) device,
+                            (uint64_t) cc, (uint64_t) sms, (uint64_t) cb, (uint64_t) std::min(bszm_in, 24), (uint64_t) std::min(bszm_out, 24)};
+    for (uint64_t x : v) { h ^= x; h *= 1099511628211ull; }
+    if (sliced) h ^= 0x9e3779b97f4a7c15ull;
     return h;
 }
 

@@ -103,6 +103,52 @@ class Exl3Linear:
                                         self.k_bits, self.codebook, out, gpu.raw_stream())
 
 
+class SlicedMultiLinear:
+    """Several EXL3 linears that share one input, run as one launch over column slices of their greatest common
+    width (the fork's ``SlicedMultiLinear``, which berth drives through ``ops::exl3_mgemm``,
+    crates/berth-kernels/tests/ops.rs:250-345): the q / k / v projections of an attention layer, or the qkv and z
+    projections of a gated-delta-net layer.  All sources must share size_k, k_bits and codebook."""
+
+    def __init__(self, gpu: Gpu, sources: list, out: OutDtype, max_rows: int = 1):
+        import math
+        first = sources[0]
+        for s in sources:
+            if (s.size_k, s.k_bits, s.codebook) != (first.size_k, first.k_bits, first.codebook):
+                raise Error("SlicedMultiLinear: sources must share size_k, k_bits and codebook")
+        self.sources, self.out, self.max_rows = sources, out, max_rows
+        self.size_k, self.k_bits, self.codebook = first.size_k, first.k_bits, first.codebook
+        self.width = 0
+        for s in sources:
+            self.width = math.gcd(self.width, s.size_n)
+        elem = 2 if out == OutDtype.F16 else 4
+        dt = torch.float16 if out == OutDtype.F16 else torch.float32
+        self.outputs = [torch.empty((max_rows, s.size_n), dtype=dt, device=gpu.device) for s in sources]
+        b, svh, c, widths, strides, had = [], [], [], [], [], []
+        for i, s in enumerate(sources):
+            for n0 in range(0, s.size_n, self.width):
+                b.append(s.trellis.data_ptr() + (n0 // 16) * 16 * self.k_bits * 2)
+                svh.append(s.svh.data_ptr() + n0 * 2)
+                c.append(self.outputs[i].data_ptr() + n0 * elem)
+                widths.append(self.width); strides.append(s.size_n); had.append(i)
+        u64 = lambda v: torch.tensor(v, dtype=torch.int64, device=gpu.device)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=gpu.device)
+        self.b_list, self.svh_list, self.c_ptrs = u64(b), u64(svh), u64(c)
+        self.suh_list = u64([s.suh.data_ptr() for s in sources])
+        self.size_n_list, self.n_stride_list, self.had_src_list = i32(widths), i32(strides), i32(had)
+        self.slices = len(b)
+        self.a_had = torch.zeros(len(sources) * max_rows * self.size_k, dtype=torch.float16, device=gpu.device)
+        self.carrier = torch.empty(1, dtype=dt, device=gpu.device)
+
+    def forward_n(self, gpu: Gpu, rows: int, a: torch.Tensor) -> list:
+        """One launch; returns the per-source outputs ``[max_rows][size_n]`` (the first ``rows`` rows are written)."""
+        if rows > self.max_rows:
+            raise Error(f"SlicedMultiLinear: {rows} rows exceed max_rows = {self.max_rows}")
+        kernels.ops.exl3_mgemm(a, self.b_list, self.carrier, self.suh_list, self.a_had, self.svh_list, rows, self.size_k, self.width,
+                               self.k_bits, self.codebook, self.out, 1, self.slices, self.size_n_list, self.c_ptrs,
+                               self.n_stride_list, self.had_src_list, len(self.sources), gpu.stream)
+        return self.outputs
+
+
 class RowScratch:
     """Scratch shared by every linear of a prefill chunk.  ``weight`` is kept because the
     boundary requires a non-null pointer above 144 rows; the B200 kernels never write it, so it

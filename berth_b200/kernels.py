@@ -165,6 +165,25 @@ class ops:
             raise Error(ops.last_error() or f"silu_mul launch failed ({rc})")
 
     @staticmethod
+    def exl3_mgemm(a, b_list, c, suh_list, a_had, svh_list, size_m: int, size_k: int, size_n: int, k_bits: int, codebook,
+                   out, bszm_in: int, bszm_out: int, size_n_list, c_ptrs, n_stride_list, had_src_list, num_had_src: int,
+                   stream=None) -> int:
+        """``ops::exl3_mgemm`` (crates/berth-kernels/src/ops.rs:317-367): returns the positive shape tag."""
+        rc = _lib.lib().berth_ops_mgemm(_ptr(a), _ptr(b_list), _ptr(c), _ptr(suh_list), _ptr(a_had), _ptr(svh_list), size_m, size_k,
+                                        size_n, k_bits, int(codebook), int(out), bszm_in, bszm_out, _ptr(size_n_list), _ptr(c_ptrs),
+                                        _ptr(n_stride_list), _ptr(had_src_list), num_had_src, _stream(stream))
+        if rc > 0:
+            return rc
+        raise Error(ops.last_error() or f"exl3_mgemm launch failed ({rc})")
+
+    @staticmethod
+    def mgemm_tune_key(size_m: int, size_k: int, size_n: int, k_bits: int, out, device: int, cc: int, sms: int, codebook,
+                       bszm_in: int, bszm_out: int, sliced: bool) -> int:
+        """``ops::mgemm_tune_key`` (crates/berth-kernels/src/ops.rs:215-245)."""
+        return int(_lib.lib().berth_ops_mgemm_tune_key(size_m, size_k, size_n, k_bits, int(out), device, cc, sms, int(codebook),
+                                                       bszm_in, bszm_out, 1 if sliced else 0))
+
+    @staticmethod
     def add_f32(a, b, c, n: int, stream=None) -> None:
         rc = _lib.lib().berth_ops_add_f32(_ptr(a), _ptr(b), _ptr(c), n, _stream(stream))
         if rc != 0:

@@ -130,6 +130,28 @@ int berth_ops_add_f32(const void* a, const void* b, void* c, int n, void* stream
 const char* berth_ops_last_error(void);
 const char* berth_ops_last_launch(void);
 
+/* Several trellis linears that share one input in one decode launch, sliced mode
+ * (crates/berth-kernels/src/ops.rs:17-38,247-367, csrc/ops/mgemm.cu:125-334): slice i is a run of size_n
+ * columns of a matrix of n_stride_list[i] columns; b_list[i] = address of the slice's first tile
+ * (trellis + (n0 / 16) * 16 * k_bits * 2 bytes), svh_list[i] = svh + n0, c_ptrs[i] = out + n0 (row stride
+ * n_stride_list[i] elements), had_src_list[i] = which matrix it was cut from; suh_list[s] = suh of
+ * matrix s; a_had = num_had_src slabs of size_m * size_k fp16.  b_list, suh_list, svh_list, c_ptrs are
+ * DEVICE arrays of device addresses, size_n_list / n_stride_list / had_src_list DEVICE int arrays with
+ * one entry per slice (bszm_out of them); bszm_in = 1.  c carries only the output type.  Returns a
+ * positive tag (1, 2 or 4: the launch's token groups) or -1.  Differences from berth: every K and
+ * codebook is linked, size_m up to 32, no autotune; size_k must be a multiple of 128 and size_n of 256
+ * (128 above 4 bits); the uniform mode (all lists null) is not linked and fails closed. */
+int berth_ops_mgemm(const void* a, const void* b_list, void* c, const void* suh_list, void* a_had,
+                    const void* svh_list, int size_m, int size_k, int size_n, int k_bits,
+                    int codebook, int c_fp32, int bszm_in, int bszm_out, const int* size_n_list,
+                    const void* c_ptrs, const int* n_stride_list, const int* had_src_list,
+                    int num_had_src, void* stream);
+/* Key of berth's multi-linear autotune cache (csrc/ops/mgemm.cu:61-91,277-294), kept for tooling that
+ * reads that cache; nothing here autotunes. */
+uint64_t berth_ops_mgemm_tune_key(int size_m, int size_k, int size_n, int k_bits, int c_fp32,
+                                  int device, int cc, int sms, int cb, int bszm_in, int bszm_out,
+                                  int sliced);
+
 /* ------------------------------------------------------------------ MoE layer
  * berth has the shape contract of the A3B mixture-of-experts block (crates/berth-plan/src/plan.rs:43-57,
  * 204-219; crates/berth-plan/src/shape.rs:59-69) but no operator for it

@@ -94,6 +94,34 @@ def test_lm_head_tune_key_matches_berth(lib):
     assert kernels.gemm_tune_key(1, 5120, 248320, 6, 0, 0, 2, 82, int(Codebook.Mul1)) == 0x51F40C1BD7CAE3A7
 
 
+def test_mgemm_tune_keys_match_berth(lib):
+    # crates/berth-kernels/src/ops.rs:738-773: the two multi-linear bundles of the 27B decode (device 0, CC class 2, 82 SMs)
+    f = kernels.ops.mgemm_tune_key
+    assert f(1, 5120, 2048, 4, OutDtype.F32, 0, 2, 82, Codebook.Mul1, 1, 8, True) == 0xD2297A8A33A33F5B
+    assert f(1, 5120, 1024, 4, OutDtype.F16, 0, 2, 82, Codebook.Mul1, 1, 14, True) == 0x9C25A0752178FB4A
+
+
+def test_mgemm_rejected_launches_do_not_call_cuda(lib):
+    # crates/berth-kernels/src/ops.rs:775-857: null pointers, a K with no kernel, size_k not a multiple of 16
+    import ctypes as C
+    l = lib
+    null = None
+    p = C.c_void_p(8)     # never dereferenced: every case below fails before any CUDA call
+    rc = l.berth_ops_mgemm(null, null, null, null, null, null, 1, 5120, 2048, 4, 2, 1, 1, 8, null, null, null, null, 0, null)
+    assert rc == -1 and "null" in kernels.ops.last_error()
+    assert kernels.ops.last_launch() == ""
+    rc = l.berth_ops_mgemm(p, p, p, p, p, p, 1, 5120, 2048, 9, 2, 1, 1, 8, null, null, null, null, 0, null)
+    assert rc == -1 and "no linked kernel" in kernels.ops.last_error()
+    rc = l.berth_ops_mgemm(p, p, p, p, p, p, 1, 15, 2048, 4, 2, 0, 1, 1, null, null, null, null, 0, null)
+    assert rc == -1 and "multiple of 16" in kernels.ops.last_error()
+    rc = l.berth_ops_mgemm(p, p, p, p, p, p, 1, 5120, 2048, 4, 2, 0, 1, 8, p, null, p, p, 2, null)
+    assert rc == -1 and "sliced mode requires" in kernels.ops.last_error()
+    rc = l.berth_ops_mgemm(p, p, p, p, p, p, 1, 5120, 2048, 4, 2, 0, 2, 8, p, p, p, p, 2, null)
+    assert rc == -1 and "single-input" in kernels.ops.last_error()
+    rc = l.berth_ops_mgemm(p, p, p, p, p, p, 1, 5120, 2048, 4, 2, 0, 1, 8, null, null, null, null, 0, null)
+    assert rc == -1 and "uniform mode" in kernels.ops.last_error()
+
+
 def test_exl3_gemv_cfg_matches_27b_shapes(lib):
     # crates/berth-kernels/src/prefill_lin.rs:386-442
     f = kernels.prefill_lin.exl3_gemv_cfg

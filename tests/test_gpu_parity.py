@@ -273,3 +273,31 @@ def test_prefill_gemm_matches_decode_kernel():
     for r0 in (0, 32, 64):
         small, _ = run_linear(x[r0:r0 + 32], w, bits, cb, True)
         assert np.abs(big[r0:r0 + 32] - small).max() <= 1e-3 * rms
+
+
+# ---------------------------------------------------------------- sliced multi-linear (berth_ops_mgemm)
+@pytest.mark.parametrize("m,out_fp32", [(1, True), (1, False), (5, False), (20, True)])
+def test_sliced_multi_linear_vs_oracle(oracle, m, out_fp32):
+    """Three linears sharing one input in one launch (the q / k / v bundle of berth's attention layers,
+    crates/berth-kernels/tests/ops.rs:250-345, at reduced sizes): every source's output against the fp64
+    evaluation of that source alone, and the rotated input slab of every source bit for bit."""
+    from berth_b200.engine import Exl3Linear, Gpu, SlicedMultiLinear
+    K, bits, cb = 512, 4, 2
+    widths = (1536, 512, 256)
+    gpu = Gpu(torch.cuda.current_device())
+    ws = [synth.linear_weights(1234, f"mg{i}", K, n, bits) for i, n in enumerate(widths)]
+    lins = [Exl3Linear(gpu, f"mg{i}", w["trellis"], w["suh"], w["svh"], bits, Codebook(cb), max_rows=m) for i, w in enumerate(ws)]
+    out = OutDtype.F32 if out_fp32 else OutDtype.F16
+    ml = SlicedMultiLinear(gpu, lins, out, max_rows=m)
+    assert ml.width == 256 and ml.slices == 9
+    x = synth.activations(1234, f"mg.x{m}", m, K)
+    outs = ml.forward_n(gpu, m, dev(x))
+    torch.cuda.synchronize()
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+    assert "sliced" in kernels.ops.last_launch()
+    ah = host_u16(ml.a_had).reshape(len(ws), m, K)
+    for i, w in enumerate(ws):
+        y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, widths[i], bits, cb)
+        mx, mean = rel_errors(outs[i][:m].float().cpu().numpy(), y64)
+        assert mx <= MAX_REL and mean <= MEAN_REL, (i, mx, mean)
+        assert (ah[i] == oracle.had_r_128(x, w["suh"], True).view(np.uint16)).all()
