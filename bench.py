@@ -116,7 +116,8 @@ class DecodeStack:
         """m = token rows per step (buffers are sized for it)."""
         import torch
         from berth_b200 import synth
-        from berth_b200.engine import Exl3Linear, Gpu, MlpLayer
+        from berth_b200.engine import Exl3Linear, Gpu, MlpLayer, SlicedMultiLinear
+        from berth_b200.kernels import OutDtype
         from berth_b200.kernels import Codebook
         self.torch = torch
         self.m = m
@@ -129,6 +130,9 @@ class DecodeStack:
                 lin[name] = Exl3Linear(self.gpu, f"layers.{l}.{name}", w["trellis"], w["suh"], w["svh"], BITS,
                                        Codebook(CB), max_rows=m)
             mlp = MlpLayer(self.gpu, lin["gate"], lin["up"], lin["down"], max_rows=m)
+            # q, k and v share their input: one sliced multi-linear launch, as in berth's attention layers
+            # (berth_ops_mgemm; crates/berth-kernels/src/ops.rs:257-262)
+            lin["qkv"] = SlicedMultiLinear(self.gpu, [lin["q"], lin["k"], lin["v"]], OutDtype.F16, max_rows=m)
             self.layers.append((mlp, lin))
         dev = self.gpu.device
         f16, f32 = torch.float16, torch.float32
@@ -149,17 +153,16 @@ class DecodeStack:
         self.h_o = torch.empty((m, HIDDEN), dtype=f32).pin_memory()
         self.h2d_bytes = 2 * m * (HIDDEN + HIDDEN + QDIM)
         self.d2h_bytes = m * (4 * HIDDEN + 2 * QDIM + 4 * KVDIM + 4 * HIDDEN)
-        # 7 x (k_exl3_gemv + k_gemv_finish) + k_silu_mul; above two rows every linear also launches k_rotate_in
-        self.launches_per_step = 15 if m <= 2 else 22
+        # gate, up, down, o: k_exl3_gemv + k_gemv_finish each (k_rotate_in in front above two rows); q/k/v: one
+        # k_rotate_in + k_exl3_gemv + k_gemv_finish for the three; one k_silu_mul
+        self.launches_per_step = 12 if m <= 2 else 16
 
     def step(self, i: int) -> None:
         from berth_b200.kernels import OutDtype
         mlp, lin = self.layers[i % LAYERS]
         g, m = self.gpu, self.m
         mlp.forward_n(g, m, self.x, self.mlp_out)
-        lin["q"].forward_n(g, m, self.xa, self.q, OutDtype.F16)
-        lin["k"].forward_n(g, m, self.xa, self.k, OutDtype.F16)
-        lin["v"].forward_n(g, m, self.xa, self.v, OutDtype.F16)
+        self.q, self.k, self.v = lin["qkv"].forward_n(g, m, self.xa)
         lin["o"].forward_n(g, m, self.attn, self.o, OutDtype.F32)
 
     def step_e2e(self, i: int) -> None:
@@ -481,6 +484,7 @@ def main() -> None:
             "config": {"workload": "c1_dense_27b_decode_stack_4bpw", "m": args.m, "bits": BITS, "codebook": "mul1",
                        "bytes_per_step": sb, "layers_cycled": LAYERS,
                        "l2": f"{LAYERS} distinct layers ({LAYERS * sb / 1e6:.0f} MB) cycled; inputs larger than L2",
+                       "qkv": "one sliced multi-linear launch (berth_ops_mgemm), as berth's attention layers run them",
                        "parallelism": "replicas" if world > 1 else "single"},
             "frac_of_hbm_peak": value / world / peak, "peak_kind": peak_kind,
             "tokens_per_s": args.m * args.steps * world / (ms * 1e-3),

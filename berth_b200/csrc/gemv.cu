@@ -742,8 +742,15 @@ __global__ void __launch_bounds__(128) k_rotate_in(const __half* __restrict__ a,
     // for everything before it (the activations and the scratch this kernel overwrites).
     grid_launch_dependents();
     grid_dependency_wait();
-    const __half* suh = suh_list ? reinterpret_cast<const __half*>(__ldg(suh_list + src)) : suh_in;
     const int lane = threadIdx.x & 31, kblocks = k >> 7, tgs = rows_pad >> 3;
+    const __half* suh = suh_in;
+    if (suh_list) {   // blockIdx.y = source: its own sign-scale vector, rotated-input slab, fragment set and block sums
+        src += blockIdx.y;
+        suh = reinterpret_cast<const __half*>(__ldg(suh_list + src));
+        a_had += size_t(src) * rows * k;
+        afrag += size_t(src) * (k >> 4) * tgs * 64;
+        blocksum += size_t(src) * rows * kblocks;
+    }
     const int total = rows_pad * kblocks;
     for (int idx = blockIdx.x * 4 + (threadIdx.x >> 5); idx < total; idx += gridDim.x * 4) {
         const int row = idx / kblocks, b = idx - row * kblocks;
@@ -1037,11 +1044,9 @@ std::string launch_gemv_sliced(const void* a, const void* b_list, const void* su
     if (size_t(grid) * per_cta > sc.slab_bytes) grid = int(sc.slab_bytes / per_cta);
     if (grid < 1) throw std::runtime_error("exl3_mgemm: split-K scratch is too small for this shape");
     const int rot_total = 8 * tg * kblocks;
-    for (int src = 0; src < num_had_src; ++src)
-        launch_pdl(k_rotate_in, dim3(std::min((rot_total + 3) / 4, 4 * sms)), dim3(128), 0, stream, "k_rotate_in launch",
-                   static_cast<const __half*>(a), (const __half*) nullptr, static_cast<__half*>(a_had) + size_t(src) * size_m * size_k,
-                   sc.afrag + size_t(src) * (afrag_bytes / 4), sc.blocksum + size_t(src) * size_m * kblocks, size_m, 8 * tg, size_k,
-                   static_cast<const unsigned long long*>(suh_list), src);
+    launch_pdl(k_rotate_in, dim3(std::min((rot_total + 3) / 4, 4 * sms), num_had_src), dim3(128), 0, stream, "k_rotate_in launch",
+               static_cast<const __half*>(a), (const __half*) nullptr, static_cast<__half*>(a_had), sc.afrag, sc.blocksum, size_m, 8 * tg,
+               size_k, static_cast<const unsigned long long*>(suh_list), 0);
     GemvArgs args;
     args.afrag = sc.afrag;
     args.blocksum = sc.blocksum;
@@ -1063,7 +1068,7 @@ std::string launch_gemv_sliced(const void* a, const void* b_list, const void* su
     args.n_slices = n_slices;
     const size_t smem = launch_bits(k_bits, codebook, tg, false, nullptr, 1, args, grid, stream);
     launch_finish(args, bu, 8 * tg, grid, codebook, stream);
-    return std::to_string(num_had_src) + " x k_rotate_in + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," +
+    return "k_rotate_in x" + std::to_string(num_had_src) + " sources + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," +
            std::to_string(tg) + ",sliced> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" +
            std::to_string(smem) + " + k_gemv_finish";
 }
