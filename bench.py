@@ -324,7 +324,44 @@ def bench_moe(rank: int, world: int, steps: int = 20, tokens=(1, 64, 1024)) -> d
             out["tokens_1024_per_rank"] = dict(rec, total_tokens=total)
         else:
             out["by_tokens"][str(T)] = rec
+    if world > 1 and isinstance(layer, moe.P2pMoeLayer) and 1024 in tokens:
+        out["c4_zipf_1056_per_rank"] = bench_moe_skewed(rank, world, steps, w, dev)
     return out
+
+
+def bench_moe_skewed(rank: int, world: int, steps: int, w: dict, dev) -> dict:
+    """Configuration 4's layer: the same experts with a router bias that skews expert popularity (Zipf exponent
+    1.1 over a seeded rank order, strength 0.25 of the log-popularity), 1056 tokens on every rank (8448 on
+    8 GPUs = 8192 prefill + 256 decode tokens).  Reports the time of one layer and the load imbalance it ran under."""
+    import torch
+    import torch.distributed as dist
+    from berth_b200 import moe, synth
+    H, E, K = MOE["hidden"], MOE["n_experts"], MOE["top_k"]
+    T = 1056
+    bias = synth.zipf_router_bias(1234, "c4.bias", E, s=1.1, strength=0.25)
+    stages = moe.GpuStages(dev, dict(w, router_bias=bias), E, max_rows=8 * T * K, max_rows_per_expert=1024)
+    layer = moe.P2pMoeLayer(stages, dist.group.WORLD, E, K, max_tokens=T, max_rows=8 * T * K + T)
+    x = torch.from_numpy(synth.activations(1234, f"c4.x.r{rank}", T, H)).to(dev)
+    for _ in range(3):
+        layer.forward(x)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        layer.forward(x)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    cnt = layer._cnt.view(torch.int32).view(world, world, E // world).sum(dim=(0, 2)).to("cpu")   # rows received per rank
+    per_expert = layer._cnt.view(torch.int32).view(world, E).sum(0).to("cpu")
+    from berth_b200 import kernels
+    return {"us_per_layer": ms * 1e3, "tokens_per_s": T * world / ms * 1e3, "total_tokens": T * world,
+            "rows_per_rank_max_over_mean": float(cnt.max()) / max(float(cnt.float().mean()), 1.0),
+            "rows_per_expert_max_over_mean": float(per_expert.max()) / max(float(per_expert.float().mean()), 1.0),
+            "device_status": kernels.device_status(torch.cuda.current_device())}
 
 
 # ------------------------------------------------------------------ CPU arm
