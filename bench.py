@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the EXL3 decode hot path on B200.
 
-Workload (BASELINE configuration 1): the dense 27B-shaped decode stack at 4 bpw -- MLP
+Workload (benchmark configuration 1): the dense 27B-shaped decode stack at 4 bpw -- MLP
 gate/up 5120->17408 (fp16 out), silu*up, down 17408->5120 (fp32 out), and the attention
 projections q 5120->6144, k/v 5120->1024, o 6144->5120 -- for a batch of M fp16 token rows.
 One "step" is one pass over one layer's seven trellis matrices; LAYERS distinct seeded layers

@@ -60,6 +60,7 @@ SIGNATURES = {
     "berth_moe_p2p_experts_workspace_bytes": (C.c_size_t, [_i, _i, _i, _i]),
     "berth_moe_p2p_experts": (_i, [C.POINTER(MoeWeights), _vp, _i, _vp, _i, _i, C.c_uint, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp,
                                    _vp, C.c_size_t, _vp]),
+    "berth_prefill_hgemm": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "berth_ops_mgemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]),
     "berth_ops_mgemm_tune_key": (C.c_uint64, [_i] * 12),
     "berth_moe_last_error": (C.c_char_p, []),

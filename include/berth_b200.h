@@ -130,6 +130,14 @@ int berth_ops_add_f32(const void* a, const void* b, void* c, int n, void* stream
 const char* berth_ops_last_error(void);
 const char* berth_ops_last_launch(void);
 
+/* Plain fp16 GEMM c[m][n] = a[m][k] . b[k][n], row stride of c = ldc elements, fp32 accumulation
+ * (crates/berth-kernels/src/prefill_lin.rs:54-64,163-205, csrc/prefill_lin/hgemm.cu:192-268).  As in berth
+ * the work is cublasGemmEx; cuBLAS is loaded at the first call (dlopen of libcublas.so.12), the rest of
+ * the library does not depend on it.  The prefill linear above does not use it: it never
+ * materialises the fp16 weight. */
+int berth_prefill_hgemm(const void* a, const void* b, void* c, int size_m, int size_k, int size_n,
+                        int ldc, int c_fp32, void* stream);
+
 /* Several trellis linears that share one input in one decode launch, sliced mode
  * (crates/berth-kernels/src/ops.rs:17-38,247-367, csrc/ops/mgemm.cu:125-334): slice i is a run of size_n
  * columns of a matrix of n_stride_list[i] columns; b_list[i] = address of the slice's first tile

@@ -94,6 +94,15 @@ def test_lm_head_tune_key_matches_berth(lib):
     assert kernels.gemm_tune_key(1, 5120, 248320, 6, 0, 0, 2, 82, int(Codebook.Mul1)) == 0x51F40C1BD7CAE3A7
 
 
+def test_prefill_hgemm_rejected_launches(lib):
+    # crates/berth-kernels/csrc/prefill_lin/linear.cu:402-405
+    import ctypes as C
+    p = C.c_void_p(8)
+    assert lib.berth_prefill_hgemm(None, p, p, 4, 64, 64, 64, 0, None) == -1 and "null" in kernels.prefill_lin.last_error()
+    assert lib.berth_prefill_hgemm(p, p, p, 4, 64, 64, 32, 0, None) == -1 and "bad shape" in kernels.prefill_lin.last_error()
+    assert lib.berth_prefill_hgemm(p, p, p, 0, 64, 64, 64, 0, None) == -1 and "bad shape" in kernels.prefill_lin.last_error()
+
+
 def test_mgemm_tune_keys_match_berth(lib):
     # crates/berth-kernels/src/ops.rs:738-773: the two multi-linear bundles of the 27B decode (device 0, CC class 2, 82 SMs)
     f = kernels.ops.mgemm_tune_key

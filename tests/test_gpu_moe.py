@@ -83,7 +83,7 @@ def test_moe_layer_small_vs_oracle(oracle, T, bits, cb, shared):
 
 @pytest.mark.parametrize("T", [1, 64])
 def test_moe_layer_config3_vs_oracle(oracle, T):
-    """BASELINE configuration 3: hidden 2048, 256 experts + shared, top-8, intermediate 512, 4 bpw."""
+    """benchmark configuration 3: hidden 2048, 256 experts + shared, top-8, intermediate 512, 4 bpw."""
     H, I, E, k, bits, cb = 2048, 512, 256, 8, 4, 2
     wts = synth.moe_layer_weights(1234, "c3", H, I, E, k, bits, cb, shared_inter=512)
     x = synth.activations(1234, f"c3.x{T}", T, H)

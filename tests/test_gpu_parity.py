@@ -172,7 +172,7 @@ def test_linear_is_deterministic_and_counters_reset():
 
 @pytest.mark.parametrize("cb", [0, 2])
 def test_linear_config0_vs_oracle(oracle, cb):
-    """BASELINE configuration 0: in=5120, out=6144, 4 bpw, one fp16 row, fp16 out."""
+    """benchmark configuration 0: in=5120, out=6144, 4 bpw, one fp16 row, fp16 out."""
     K, N, bits = 5120, 6144, 4
     w = synth.linear_weights(1234, "c0", K, N, bits)
     x = synth.activations(1234, "c0.x", 1, K)
@@ -301,3 +301,20 @@ def test_sliced_multi_linear_vs_oracle(oracle, m, out_fp32):
         mx, mean = rel_errors(outs[i][:m].float().cpu().numpy(), y64)
         assert mx <= MAX_REL and mean <= MEAN_REL, (i, mx, mean)
         assert (ah[i] == oracle.had_r_128(x, w["suh"], True).view(np.uint16)).all()
+
+
+@pytest.mark.parametrize("m,k,n,ldc,out_fp32", [(5, 64, 48, 48, False), (130, 256, 512, 640, True), (47, 5120, 128, 128, False)])
+def test_prefill_hgemm_vs_numpy(m, k, n, ldc, out_fp32):
+    """berth_prefill_hgemm: c[m][ldc] = a[m][k] . b[k][n] in fp16 with fp32 accumulation; columns past n stay untouched."""
+    a = synth.activations(77, f"hg.a{m}", m, k)
+    b = (synth.activations(77, f"hg.b{k}", k, n).astype(np.float32) / np.sqrt(k)).astype(np.float16)
+    dt = torch.float32 if out_fp32 else torch.float16
+    c = torch.full((m, ldc), -7.0, dtype=dt, device="cuda")
+    kernels.prefill_lin.hgemm(dev(a), dev(b), c, m, k, n, ldc, OutDtype.F32 if out_fp32 else OutDtype.F16)
+    torch.cuda.synchronize()
+    assert kernels.prefill_lin.last_launch() == "cublasGemmEx"
+    got = c.float().cpu().numpy()
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    mx, mean = rel_errors(got[:, :n], ref)
+    assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
+    assert (got[:, n:] == -7.0).all()
