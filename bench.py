@@ -198,6 +198,37 @@ class DecodeStack:
         return e0.elapsed_time(e1) / (reps * len(mats))
 
 
+# ------------------------------------------------------------------ lm_head regime
+
+def bench_lm_head(rank: int, reps: int = 10) -> dict:
+    """berth's lm_head linear (6 bpw, 5120 -> 248320, one row; crates/berth-kernels/csrc/gemm_k6.cu:1-34): one
+    decode launch over 953 MB of trellis, far larger than L2."""
+    import torch
+    from berth_b200 import synth
+    from berth_b200.engine import Exl3Linear, Gpu
+    from berth_b200.kernels import Codebook, OutDtype
+    K, N, bits = HIDDEN, 248320, 6
+    gpu = Gpu(torch.cuda.current_device())
+    w = synth.linear_weights(synth.MASTER_SEED, f"r{rank}.lm_head", K, N, bits, fan_in_gain=True)
+    lin = Exl3Linear(gpu, "lm_head", w["trellis"], w["suh"], w["svh"], bits, Codebook(CB), max_rows=1)
+    x = torch.from_numpy(synth.activations(1234, f"r{rank}.lmh.x", 1, K)).to(gpu.device)
+    out = torch.empty((1, N), dtype=torch.float32, device=gpu.device)
+    for _ in range(3):
+        lin.forward_n(gpu, 1, x, out, OutDtype.F32)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        lin.forward_n(gpu, 1, x, out, OutDtype.F32)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    nbytes = linear_bytes(K, N, 1, 1, bits)
+    pk, _ = peaks()
+    return {"workload": "lm_head_6bpw_5120x248320_m1", "us": us, "gbs": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / pk,
+            "bytes": nbytes}
+
+
 # ------------------------------------------------------------------ configuration 2: prefill GEMM
 
 PREFILL_M = 4096
@@ -422,7 +453,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill (configuration 2) and MoE (configuration 3) measurements")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "moe"],
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "moe", "lm_head"],
                     help="run one of the extra measurements alone and print its record (for profiling; not the contract line)")
     ap.add_argument("--moe-tokens", type=int, nargs="*", default=[1, 64, 1024], help="token counts of the MoE measurement")
     args = ap.parse_args()
@@ -445,8 +476,12 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     warmup = max(args.warmup, 3)
     if args.only != "all":
-        rec = bench_prefill(rank, reps=max(1, min(args.steps, 5))) if args.only == "prefill" \
-            else bench_moe(rank, world, steps=args.steps, tokens=tuple(args.moe_tokens))
+        if args.only == "prefill":
+            rec = bench_prefill(rank, reps=max(1, min(args.steps, 5)))
+        elif args.only == "lm_head":
+            rec = bench_lm_head(rank, reps=max(1, min(args.steps, 20)))
+        else:
+            rec = bench_moe(rank, world, steps=args.steps, tokens=tuple(args.moe_tokens))
         if rank == 0:
             print(json.dumps(rec))
         if world > 1:
@@ -500,6 +535,7 @@ def main() -> None:
     if clocks is not None:
         clocks["window"] = "timed region + end-to-end region + 1.5 s repeat of the same step loop"
     prefill = bench_prefill(rank) if (rank == 0 and not args.no_extras) else None
+    lm_head = bench_lm_head(rank) if (rank == 0 and not args.no_extras) else None
     moe_res = None if args.no_extras else bench_moe(rank, world)
 
     if world > 1:
@@ -533,7 +569,7 @@ def main() -> None:
                     "d2h_bytes_per_step": stack.d2h_bytes, "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": stack.launches_per_step * args.steps,
             "clocks": clocks,
-            "prefill": prefill,
+            "prefill": prefill, "lm_head": lm_head,
             "moe": moe_res,
         }
         if not args.no_cpu_baseline and world == 1:

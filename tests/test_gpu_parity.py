@@ -318,3 +318,33 @@ def test_prefill_hgemm_vs_numpy(m, k, n, ldc, out_fp32):
     mx, mean = rel_errors(got[:, :n], ref)
     assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
     assert (got[:, n:] == -7.0).all()
+
+
+def test_lm_head_shape_6bpw_against_decoded_slices():
+    """The lm_head regime of berth (crates/berth-kernels/csrc/gemm_k6.cu:1-34: K = 6 bpw, N = 248320, one row): far
+    too large for the CPU checker, so three 128-column slices are decoded with berth_prefill_reconstruct (bit-exact
+    against the checker at small sizes) and multiplied in fp64 on the GPU; the full launch must agree on them."""
+    K, N, bits, cb = 5120, 248320, 6, 2
+    w = synth.linear_weights(1234, "lmh", K, N, bits)
+    x = synth.activations(1234, "lmh.x", 1, K)
+    c, ah = run_linear(x, w, bits, cb, True)
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+    assert np.isfinite(c).all()
+    td = dev(w["trellis"])
+    a_rot = torch.from_numpy(ah.view(np.float16).astype(np.float64)).cuda()          # H128(x * suh) / sqrt(128), [1][K]
+    hmat = torch.ones((1, 1), dtype=torch.float64, device="cuda")
+    for _ in range(7):
+        hmat = torch.cat((torch.cat((hmat, hmat), 1), torch.cat((hmat, -hmat), 1)), 0)
+    for n0 in (0, 128 * 977, N - 128):
+        wt = torch.empty((K, 128), dtype=torch.float16, device="cuda")
+        rc = _lib_reconstruct(wt, td, K, 128, N, n0, bits, cb)
+        assert rc == 0
+        y = (a_rot @ wt.double())                                                      # [1][128]
+        y = (y @ hmat) / np.sqrt(128.0) * torch.from_numpy(w["svh"][n0:n0 + 128].astype(np.float64)).cuda()
+        mx, mean = rel_errors(c[:, n0:n0 + 128], y.cpu().numpy())
+        assert mx <= MAX_REL and mean <= MEAN_REL, (n0, mx, mean)
+
+
+def _lib_reconstruct(out, trellis, size_k, slice_n, full_n, n_offset, bits, cb):
+    from berth_b200 import _lib
+    return _lib.lib().berth_prefill_reconstruct(out.data_ptr(), trellis.data_ptr(), size_k, slice_n, full_n, n_offset, bits, cb, None)
