@@ -122,6 +122,34 @@ class DecodeStack:
         self.torch = torch
         self.m = m
         self.gpu = Gpu(torch.cuda.current_device())
+        dev = self.gpu.device
+        f16, f32 = torch.float16, torch.float32
+        # One pinned host block and one device block each for the step's inputs and for its results, so that the
+        # end-to-end step is one copy in and one copy out (the tensors below are views into the device blocks).
+        self.h2d_bytes = 2 * m * (HIDDEN + HIDDEN + QDIM)
+        self.d2h_bytes = m * (4 * HIDDEN + 2 * QDIM + 4 * KVDIM + 4 * HIDDEN)
+        self.h_in = torch.empty(self.h2d_bytes, dtype=torch.uint8).pin_memory()
+        self.d_in = torch.empty(self.h2d_bytes, dtype=torch.uint8, device=dev)
+        self.h_out = torch.empty(self.d2h_bytes, dtype=torch.uint8).pin_memory()
+        self.d_out = torch.empty(self.d2h_bytes, dtype=torch.uint8, device=dev)
+
+        def carve(block, specs):
+            views, off = [], 0
+            for rows, cols, dt in specs:
+                nbytes = rows * cols * (2 if dt == f16 else 4)
+                views.append(block[off:off + nbytes].view(dt).view(rows, cols))
+                off += nbytes
+            return views
+
+        in_specs = [(m, HIDDEN, f16), (m, HIDDEN, f16), (m, QDIM, f16)]
+        hx, hxa, hattn = carve(self.h_in, in_specs)
+        hx.copy_(torch.from_numpy(synth.activations(1234, f"r{rank}.x", m, HIDDEN)))
+        hxa.copy_(torch.from_numpy(synth.activations(1234, f"r{rank}.xa", m, HIDDEN)))
+        hattn.copy_(torch.from_numpy(synth.activations(1234, f"r{rank}.attn", m, QDIM)))
+        self.x, self.xa, self.attn = carve(self.d_in, in_specs)
+        self.d_in.copy_(self.h_in)
+        out_specs = [(m, HIDDEN, f32), (m, HIDDEN, f32), (m, QDIM, f16), (m, KVDIM, f16), (m, KVDIM, f16)]
+        self.mlp_out, self.o, self.q, self.k, self.v = carve(self.d_out, out_specs)
         self.layers = []
         for l in range(LAYERS):
             lin = {}
@@ -132,27 +160,9 @@ class DecodeStack:
             mlp = MlpLayer(self.gpu, lin["gate"], lin["up"], lin["down"], max_rows=m)
             # q, k and v share their input: one sliced multi-linear launch, as in berth's attention layers
             # (berth_ops_mgemm; crates/berth-kernels/src/ops.rs:257-262)
-            lin["qkv"] = SlicedMultiLinear(self.gpu, [lin["q"], lin["k"], lin["v"]], OutDtype.F16, max_rows=m)
+            lin["qkv"] = SlicedMultiLinear(self.gpu, [lin["q"], lin["k"], lin["v"]], OutDtype.F16, max_rows=m,
+                                           outputs=[self.q, self.k, self.v])
             self.layers.append((mlp, lin))
-        dev = self.gpu.device
-        f16, f32 = torch.float16, torch.float32
-        # host inputs (pinned) and device activations
-        self.h_x = torch.from_numpy(synth.activations(1234, f"r{rank}.x", m, HIDDEN)).pin_memory()
-        self.h_xa = torch.from_numpy(synth.activations(1234, f"r{rank}.xa", m, HIDDEN)).pin_memory()
-        self.h_attn = torch.from_numpy(synth.activations(1234, f"r{rank}.attn", m, QDIM)).pin_memory()
-        self.x = self.h_x.to(dev); self.xa = self.h_xa.to(dev); self.attn = self.h_attn.to(dev)
-        self.mlp_out = torch.empty((m, HIDDEN), dtype=f32, device=dev)
-        self.q = torch.empty((m, QDIM), dtype=f16, device=dev)
-        self.k = torch.empty((m, KVDIM), dtype=f16, device=dev)
-        self.v = torch.empty((m, KVDIM), dtype=f16, device=dev)
-        self.o = torch.empty((m, HIDDEN), dtype=f32, device=dev)
-        self.h_mlp_out = torch.empty((m, HIDDEN), dtype=f32).pin_memory()
-        self.h_q = torch.empty((m, QDIM), dtype=f16).pin_memory()
-        self.h_k = torch.empty((m, KVDIM), dtype=f16).pin_memory()
-        self.h_v = torch.empty((m, KVDIM), dtype=f16).pin_memory()
-        self.h_o = torch.empty((m, HIDDEN), dtype=f32).pin_memory()
-        self.h2d_bytes = 2 * m * (HIDDEN + HIDDEN + QDIM)
-        self.d2h_bytes = m * (4 * HIDDEN + 2 * QDIM + 4 * KVDIM + 4 * HIDDEN)
         # gate, up, down, o: k_exl3_gemv + k_gemv_finish each (k_rotate_in in front above two rows); q/k/v: one
         # k_rotate_in + k_exl3_gemv + k_gemv_finish for the three; one k_silu_mul
         self.launches_per_step = 12 if m <= 2 else 16
@@ -162,20 +172,14 @@ class DecodeStack:
         mlp, lin = self.layers[i % LAYERS]
         g, m = self.gpu, self.m
         mlp.forward_n(g, m, self.x, self.mlp_out)
-        self.q, self.k, self.v = lin["qkv"].forward_n(g, m, self.xa)
+        lin["qkv"].forward_n(g, m, self.xa)
         lin["o"].forward_n(g, m, self.attn, self.o, OutDtype.F32)
 
     def step_e2e(self, i: int) -> None:
         """Host buffers in, host buffers out: what a caller without device residency pays."""
-        self.x.copy_(self.h_x, non_blocking=True)
-        self.xa.copy_(self.h_xa, non_blocking=True)
-        self.attn.copy_(self.h_attn, non_blocking=True)
+        self.d_in.copy_(self.h_in, non_blocking=True)
         self.step(i)
-        self.h_mlp_out.copy_(self.mlp_out, non_blocking=True)
-        self.h_q.copy_(self.q, non_blocking=True)
-        self.h_k.copy_(self.k, non_blocking=True)
-        self.h_v.copy_(self.v, non_blocking=True)
-        self.h_o.copy_(self.o, non_blocking=True)
+        self.h_out.copy_(self.d_out, non_blocking=True)
         self.torch.cuda.current_stream().synchronize()
 
     def time_gate_kernel(self, reps: int) -> float:

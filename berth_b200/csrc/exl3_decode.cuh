@@ -183,8 +183,27 @@ __device__ __forceinline__ void states_4bit(uint32_t r0, uint32_t r1, uint32_t (
 template <int CB>
 __device__ __forceinline__ void decode_frag(const uint32_t (&s)[8], uint32_t (&a)[4])
 {
+    if constexpr (CB == 2) {
+        // pack the two 16-bit patterns of 1024 + byte sum first, then one half2 fma per pair (the same
+        // per-element arithmetic as decode<2>, half the instructions)
+        const uint32_t sc = uint32_t(kMul1S) | (uint32_t(kMul1S) << 16), bi = uint32_t(kMul1B) | (uint32_t(kMul1B) << 16);
 #pragma unroll
-    for (int r = 0; r < 4; ++r) a[r] = pack_half2(decode<CB>(s[2 * r]), decode<CB>(s[2 * r + 1]));
+        for (int r = 0; r < 4; ++r) {
+            const uint32_t h = __byte_perm(mul1_h1024(s[2 * r]), mul1_h1024(s[2 * r + 1]), 0x5410);
+            const __half2 w = __hfma2(*reinterpret_cast<const __half2*>(&h), *reinterpret_cast<const __half2*>(&sc),
+                                      *reinterpret_cast<const __half2*>(&bi));
+            a[r] = *reinterpret_cast<const uint32_t*>(&w);
+        }
+    } else {
+        // 3INST / MCG: the weight is the sum of the two halves of the mixed word; add the words of two weights pairwise
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const uint32_t x0 = mix32<CB>(s[2 * r]), x1 = mix32<CB>(s[2 * r + 1]);
+            const uint32_t lo = __byte_perm(x0, x1, 0x5410), hi = __byte_perm(x0, x1, 0x7632);   // (lo0, lo1), (hi0, hi1)
+            const __half2 w = __hadd2(*reinterpret_cast<const __half2*>(&lo), *reinterpret_cast<const __half2*>(&hi));
+            a[r] = *reinterpret_cast<const uint32_t*>(&w);
+        }
+    }
 }
 
 // D(16x8, fp32) += A(16x16, fp16, row) * B(16x8, fp16, col)

@@ -109,7 +109,7 @@ class SlicedMultiLinear:
     crates/berth-kernels/tests/ops.rs:250-345): the q / k / v projections of an attention layer, or the qkv and z
     projections of a gated-delta-net layer.  All sources must share size_k, k_bits and codebook."""
 
-    def __init__(self, gpu: Gpu, sources: list, out: OutDtype, max_rows: int = 1):
+    def __init__(self, gpu: Gpu, sources: list, out: OutDtype, max_rows: int = 1, outputs: list | None = None):
         import math
         first = sources[0]
         for s in sources:
@@ -122,7 +122,12 @@ class SlicedMultiLinear:
             self.width = math.gcd(self.width, s.size_n)
         elem = 2 if out == OutDtype.F16 else 4
         dt = torch.float16 if out == OutDtype.F16 else torch.float32
-        self.outputs = [torch.empty((max_rows, s.size_n), dtype=dt, device=gpu.device) for s in sources]
+        if outputs is None:
+            outputs = [torch.empty((max_rows, s.size_n), dtype=dt, device=gpu.device) for s in sources]
+        for o, s in zip(outputs, sources):
+            if o.dtype != dt or tuple(o.shape) != (max_rows, s.size_n) or not o.is_contiguous():
+                raise Error("SlicedMultiLinear: an output must be a contiguous [max_rows][size_n] tensor of the output type")
+        self.outputs = list(outputs)
         b, svh, c, widths, strides, had = [], [], [], [], [], []
         for i, s in enumerate(sources):
             for n0 in range(0, s.size_n, self.width):
