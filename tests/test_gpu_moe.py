@@ -1,5 +1,7 @@
 """MoE layer parity: router top-k indices bit-exact against the CPU oracle (ties to the lower
 expert index), layer output within the fp32-accumulation tolerance of the fp64 evaluation."""
+import os
+
 import numpy as np
 import pytest
 
@@ -196,3 +198,16 @@ def test_peer_memory_layer_on_one_rank():
     finally:
         if own_group:
             dist.destroy_process_group()
+
+
+def test_peer_memory_layer_matches_nccl_layer():
+    """Two ranks on two GPUs (skipped on a one-GPU box): the peer-memory exchange against the NCCL exchange."""
+    import subprocess
+    import sys as _sys
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ep_p2p_worker.py")
+    r = subprocess.run([_sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+                        "127.0.0.1", "--master-port", "29541", worker], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "P2P-OK 0" in r.stdout and "P2P-OK 1" in r.stdout
