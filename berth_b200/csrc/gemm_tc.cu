@@ -47,7 +47,7 @@ constexpr int kEpiWarp0 = 4;
 constexpr int BN = 128, BK = 64, SUB = 128, MAX_SUB = 3;
 constexpr int SA = 3;   // activation stages
 constexpr int SW = 4;   // decoded-weight stages in tensor memory (32 columns each)
-constexpr int ST = 4;   // raw trellis stages
+constexpr int kBarrierBytes = 512;
 constexpr int A_SUB_BYTES = SUB * BK * 2;          // 16 KiB
 constexpr int A_STAGE_BYTES = MAX_SUB * A_SUB_BYTES;
 constexpr int kAccCols = MAX_SUB * SUB;            // accumulator columns; weight stages follow
@@ -60,7 +60,13 @@ struct TGeo {
     static constexpr int NW = 8 * BITS;
     static constexpr int TROW_BYTES = 8 * NW * 4;          // one k-tile row of the band
     static constexpr int T_STAGE_BYTES = 4 * TROW_BYTES;   // 64 k rows
-    static constexpr size_t SMEM = 1024 /*align slack*/ + size_t(SA) * A_STAGE_BYTES + size_t(ST) * T_STAGE_BYTES + 256 /*barriers*/;
+    // Raw trellis stages: as many as fit beside the activation ring (and the epilogue buffers of the grouped
+    // kernel), 4 to 16.  Weights that are read once come from DRAM, a microsecond or two away under load; four
+    // stages of 0.4 us each did not cover that.
+    static constexpr int kEpilogueExtra = (32 * 129 + 2 * 128) * 4;
+    static constexpr int kFree = 227 * 1024 - 1024 - SA * A_STAGE_BYTES - kEpilogueExtra - kBarrierBytes - 2048 /*static shared*/;
+    static constexpr int ST = kFree / T_STAGE_BYTES < 4 ? 4 : (kFree / T_STAGE_BYTES > 16 ? 16 : kFree / T_STAGE_BYTES);
+    static constexpr size_t SMEM = 1024 /*align slack*/ + size_t(SA) * A_STAGE_BYTES + size_t(ST) * T_STAGE_BYTES + kBarrierBytes;
 };
 
 struct GemmArgs {
@@ -315,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
                                                               const __grid_constant__ CUtensorMap tmap_t, const GemmArgs p)
 {
     using TG_ = TGeo<BITS>;
-    constexpr int NW = TG_::NW, TROW_BYTES = TG_::TROW_BYTES, T_STAGE_BYTES = TG_::T_STAGE_BYTES;
+    constexpr int NW = TG_::NW, TROW_BYTES = TG_::TROW_BYTES, T_STAGE_BYTES = TG_::T_STAGE_BYTES, ST = TG_::ST;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int band = blockIdx.x;
@@ -472,12 +478,17 @@ struct GGeo {
     static constexpr size_t SMEM = TGeo<BITS>::SMEM + (kXchFloats + 2 * 128) * 4 /*transposition buffer and scales of the epilogue*/;
 };
 
+// Three views of the activations (boxes of 32, 64 and 128 rows x 64 k): an item loads only as many rows as
+// its problem has, rounded up to a box; with 128-row boxes for 32-row problems the activation traffic of an
+// MoE layer at 1024 tokens was four times its weight traffic.
 template <int BITS, int CB>
 __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __grid_constant__ CUtensorMap tmap_a,
+                                                                      const __grid_constant__ CUtensorMap tmap_a64,
+                                                                      const __grid_constant__ CUtensorMap tmap_a32,
                                                                       const __grid_constant__ CUtensorMap tmap_t, const GemmArgs p)
 {
     using TG_ = TGeo<BITS>;
-    constexpr int TROW_BYTES = TG_::TROW_BYTES, T_STAGE_BYTES = TG_::T_STAGE_BYTES;
+    constexpr int TROW_BYTES = TG_::TROW_BYTES, T_STAGE_BYTES = TG_::T_STAGE_BYTES, ST = TG_::ST;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bands = p.n / BN;
@@ -499,13 +510,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
     uint64_t* bars = reinterpret_cast<uint64_t*>(svh_s + 2 * 128);
     __shared__ uint32_t s_tmem_base;
 
-    const uint32_t full_a = smem_u32(bars), empty_a = full_a + 8 * SA;
-    const uint32_t full_w = empty_a + 8 * SA, empty_w = full_w + 8 * SW;
+    // The activation ring holds as many stages as fit its 144 KiB: 9 of one 128-row sub-tile, 4 of two, 3 of three.
+    // With short stages (a 32-row problem's stage is 0.4 us of decode) three stages in flight did not cover an L2 miss.
+    constexpr int kMaxSA = 9;
+    const int a_stage = p.nsub_max * A_SUB_BYTES;
+    const int SAg = (SA * A_STAGE_BYTES) / a_stage;
+    const uint32_t full_a = smem_u32(bars), empty_a = full_a + 8 * kMaxSA;
+    const uint32_t full_w = empty_a + 8 * kMaxSA, empty_w = full_w + 8 * SW;
     const uint32_t full_t = empty_w + 8 * SW, empty_t = full_t + 8 * ST;
     const uint32_t acc_full = empty_t + 8 * ST, acc_empty = acc_full + 16;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < SA; ++s) { mbar_init(full_a + 8 * s, 1); mbar_init(empty_a + 8 * s, 1); }
+        for (int s = 0; s < kMaxSA; ++s) { mbar_init(full_a + 8 * s, 1); mbar_init(empty_a + 8 * s, 1); }
         for (int s = 0; s < SW; ++s) { mbar_init(full_w + 8 * s, kDecodeWarps); mbar_init(empty_w + 8 * s, 1); }
         for (int s = 0; s < ST; ++s) { mbar_init(full_t + 8 * s, 1); mbar_init(empty_t + 8 * s, kDecodeWarps); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full + 8 * b, 1); mbar_init(acc_empty + 8 * b, 4); }
@@ -540,23 +556,28 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a64) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a32) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_t) : "memory");
             int sa = 0, pa = 0, st = 0, pt = 0, cnt = 0;
             for (int it = 0; it < my_items; ++it) {
                 int band; GemvProblem pr;
                 item_at(it, band, pr);
                 const int nsub = (pr.rows + SUB - 1) / SUB;
+                // one box of 32 or 64 rows for a small problem, else 128-row boxes
+                const CUtensorMap* amap = pr.rows <= 32 ? &tmap_a32 : (pr.rows <= 64 ? &tmap_a64 : &tmap_a);
+                const int box_bytes = pr.rows <= 32 ? 32 * BK * 2 : (pr.rows <= 64 ? 64 * BK * 2 : A_SUB_BYTES);
                 for (int ks = 0; ks < kstages; ++ks, ++cnt) {
                     if (cnt >= ST) mbar_wait_parked(empty_t + 8 * st, pt ^ 1, p.status, 100);
                     mbar_arrive_expect_tx(full_t + 8 * st, T_STAGE_BYTES);
                     tma_load_3d(smem_u32(t_ring + st * T_STAGE_BYTES), &tmap_t, band * (TROW_BYTES / 8), ks * 4, pr.z, full_t + 8 * st);
                     if (++st == ST) { st = 0; pt ^= 1; }
-                    if (cnt >= SA) mbar_wait_parked(empty_a + 8 * sa, pa ^ 1, p.status, 100);
-                    mbar_arrive_expect_tx(full_a + 8 * sa, max(nsub, 1) * A_SUB_BYTES);
+                    if (cnt >= SAg) mbar_wait_parked(empty_a + 8 * sa, pa ^ 1, p.status, 100);
+                    mbar_arrive_expect_tx(full_a + 8 * sa, max(nsub, 1) * box_bytes);
                     for (int sub = 0; sub < max(nsub, 1); ++sub)
-                        tma_load_2d(smem_u32(a_ring + sa * A_STAGE_BYTES + sub * A_SUB_BYTES), &tmap_a, ks * BK, pr.row0 + sub * SUB,
+                        tma_load_2d(smem_u32(a_ring + sa * a_stage + sub * A_SUB_BYTES), amap, ks * BK, pr.row0 + sub * SUB,
                                     full_a + 8 * sa);
-                    if (++sa == SA) { sa = 0; pa ^= 1; }
+                    if (++sa == SAg) { sa = 0; pa ^= 1; }
                 }
             }
         }
@@ -579,7 +600,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
                 mbar_wait(full_a + 8 * sa, pa, p.status);
                 mbar_wait(full_w + 8 * sw, pw, p.status);
                 tc_fence_after();
-                const uint32_t x_base = smem_u32(a_ring + sa * A_STAGE_BYTES);
+                const uint32_t x_base = smem_u32(a_ring + sa * a_stage);
                 const uint64_t x_desc1 = smem_desc_sw128(x_base), x_desc2 = smem_desc_sw128(x_base + 2 * A_SUB_BYTES);
                 const uint32_t w_t = tmem_w + sw * 32;
                 const uint32_t bar_a = empty_a + 8 * sa, bar_w = empty_w + 8 * sw;
@@ -593,7 +614,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
                     tc_commit(bar_w);
                 }
                 __syncwarp();
-                if (++sa == SA) { sa = 0; pa ^= 1; }
+                if (++sa == SAg) { sa = 0; pa ^= 1; }
                 if (++sw == SW) { sw = 0; pw ^= 1; }
             }
             if (elect_one()) tc_commit(acc_full + 8 * buf);
@@ -717,7 +738,11 @@ void launch_tc(const void* a_had, const void* trellis, const GemmArgs& args, cud
         }
         const long long items = (long long) args.max_problems * (args.n / BN);
         const int grid = int(std::min<long long>(items, device_info(dev).sms));
-        gk<<<grid, kThreads, GGeo<BITS>::SMEM, stream>>>(map_a, map_t, args);
+        const CUtensorMap map_a64 = make_map(CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a_had, cuuint64_t(args.k), cuuint64_t(args.m),
+                                             cuuint64_t(args.k) * 2, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+        const CUtensorMap map_a32 = make_map(CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a_had, cuuint64_t(args.k), cuuint64_t(args.m),
+                                             cuuint64_t(args.k) * 2, BK, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+        gk<<<grid, kThreads, GGeo<BITS>::SMEM, stream>>>(map_a, map_a64, map_a32, map_t, args);
         cuda_ok(cudaGetLastError(), "k_exl3_gemm_tc_grouped launch");
         return;
     }
