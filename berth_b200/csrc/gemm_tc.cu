@@ -285,31 +285,36 @@ __device__ __noinline__ void epilogue_pass(uint32_t tacc, float* xch, const floa
     }
 }
 
-// One 64-deep stage of one band decoded into tensor memory by the sixteen decode warps: warp d takes k-tile row
-// d/4 of the stage and tile columns 2*(d%4), 2*(d%4)+1 = output columns 32*(d%4) .. +31, which are the TMEM lanes
-// it may access (warp index % 4 == d % 4).  `wait_w` = the stage of tensor memory must first be released.
+// One 64-deep stage of one band decoded into tensor memory by one group of four decode warps (the four groups take
+// the stages round robin, group g always into weight stage g of tensor memory): the warp takes all four k-tile rows
+// of the stage and tile columns 2*quarter, 2*quarter+1 = output columns 32*quarter .. +31, which are the TMEM lanes
+// it may access (warp index % 4 == quarter).  `wait_w` = the stage of tensor memory must first be released.
+// (Sixteen warps sharing every stage, a quarter of this work per barrier round trip, spent more instructions on the
+// hand-over than on the weights.)
 template <int BITS, int CB>
-__device__ __forceinline__ void decode_stage(const unsigned char* tstage, uint32_t tmem_wstage, int d, int lane, bool wait_w,
+__device__ __forceinline__ void decode_stage(const unsigned char* tstage, uint32_t tmem_wstage, int quarter, int lane, bool wait_w,
                                              uint32_t empty_w_bar, uint32_t empty_w_parity, unsigned* status)
 {
     constexpr int NW = 8 * BITS, TROW_BYTES = 8 * NW * 4;
-    const int krow = d >> 2, quarter = d & 3;
-    const uint32_t* trow = reinterpret_cast<const uint32_t*>(tstage + krow * TROW_BYTES);
-    uint32_t w[2][4];
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
-        uint32_t s[8];
-        const uint32_t* tile = trow + (2 * quarter + t) * NW;
-        if constexpr (BITS == 4) dq::states_4bit<CB != 2>(tile[lane], tile[(lane + 1) & 31], s);
-        else dq::lane_states<BITS>(tile, lane, s);
-        dq::decode_frag<CB>(s, w[t]);
-    }
-    if (wait_w) {
-        mbar_wait_parked(empty_w_bar, empty_w_parity, status, 40);   // the MMAs that read this weight stage are done
-        tc_fence_after();
-    }
+    for (int krow = 0; krow < 4; ++krow) {
+        const uint32_t* trow = reinterpret_cast<const uint32_t*>(tstage + krow * TROW_BYTES);
+        uint32_t w[2][4];
 #pragma unroll
-    for (int t = 0; t < 2; ++t) tc_st_frag(tmem_wstage + (uint32_t(32 * quarter + 16 * t) << 16) + 8 * krow, w[t]);
+        for (int t = 0; t < 2; ++t) {
+            uint32_t s[8];
+            const uint32_t* tile = trow + (2 * quarter + t) * NW;
+            if constexpr (BITS == 4) dq::states_4bit<CB != 2>(tile[lane], tile[(lane + 1) & 31], s);
+            else dq::lane_states<BITS>(tile, lane, s);
+            dq::decode_frag<CB>(s, w[t]);
+        }
+        if (krow == 0 && wait_w) {
+            mbar_wait_parked(empty_w_bar, empty_w_parity, status, 40);   // the MMAs that read this weight stage are done
+            tc_fence_after();
+        }
+#pragma unroll
+        for (int t = 0; t < 2; ++t) tc_st_frag(tmem_wstage + (uint32_t(32 * quarter + 16 * t) << 16) + 8 * krow, w[t]);
+    }
     tc_wait_st();
     tc_fence_before();
     __syncwarp();
@@ -353,8 +358,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SA; ++s) { mbar_init(full_a + 8 * s, 1); mbar_init(empty_a + 8 * s, 1); }
-        for (int s = 0; s < SW; ++s) { mbar_init(full_w + 8 * s, kDecodeWarps); mbar_init(empty_w + 8 * s, 1); }
-        for (int s = 0; s < ST; ++s) { mbar_init(full_t + 8 * s, 1); mbar_init(empty_t + 8 * s, kDecodeWarps); }
+        for (int s = 0; s < SW; ++s) { mbar_init(full_w + 8 * s, 4); mbar_init(empty_w + 8 * s, 1); }
+        for (int s = 0; s < ST; ++s) { mbar_init(full_t + 8 * s, 1); mbar_init(empty_t + 8 * s, 4); }
         mbar_init(acc_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -421,17 +426,19 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc(const __grid_const
         __syncwarp();
     } else if (warp >= kDecodeWarp0) {
         // ------------------------------------------------------------ decode warps
-        const int d = warp - kDecodeWarp0;
-        int st = 0, pt = 0, sw = 0, pw = 0;
-        for (int ks = 0; ks < kstages; ++ks) {
+        const int g = (warp - kDecodeWarp0) >> 2, quarter = warp & 3;   // group g: stages g, g+4, ... into weight stage g
+        static_assert(SW == 4 && ST >= 4, "one weight stage per decode group");
+        int st = g, pt = 0, pw = 0;
+        for (int ks = g; ks < kstages; ks += 4) {
             mbar_wait_parked(full_t + 8 * st, pt, p.status, 40);
-            decode_stage<BITS, CB>(t_ring + st * T_STAGE_BYTES, tmem_w + sw * 32, d, lane, ks >= SW, empty_w + 8 * sw, pw ^ 1, p.status);
+            decode_stage<BITS, CB>(t_ring + st * T_STAGE_BYTES, tmem_w + g * 32, quarter, lane, ks >= SW, empty_w + 8 * g, pw ^ 1, p.status);
             if (lane == 0) {
-                mbar_arrive(full_w + 8 * sw);
+                mbar_arrive(full_w + 8 * g);
                 mbar_arrive(empty_t + 8 * st);
             }
-            if (++st == ST) { st = 0; pt ^= 1; }
-            if (++sw == SW) { sw = 0; pw ^= 1; }
+            st += 4;
+            if (st >= ST) { st -= ST; pt ^= 1; }
+            pw ^= 1;
         }
     }
 
@@ -522,8 +529,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxSA; ++s) { mbar_init(full_a + 8 * s, 1); mbar_init(empty_a + 8 * s, 1); }
-        for (int s = 0; s < SW; ++s) { mbar_init(full_w + 8 * s, kDecodeWarps); mbar_init(empty_w + 8 * s, 1); }
-        for (int s = 0; s < ST; ++s) { mbar_init(full_t + 8 * s, 1); mbar_init(empty_t + 8 * s, kDecodeWarps); }
+        for (int s = 0; s < SW; ++s) { mbar_init(full_w + 8 * s, 4); mbar_init(empty_w + 8 * s, 1); }
+        for (int s = 0; s < ST; ++s) { mbar_init(full_t + 8 * s, 1); mbar_init(empty_t + 8 * s, 4); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full + 8 * b, 1); mbar_init(acc_empty + 8 * b, 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -622,18 +629,20 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
         }
     } else if (warp >= kDecodeWarp0) {
         // ------------------------------------------------------------ decode warps
-        const int d = warp - kDecodeWarp0;
-        int st = 0, pt = 0, sw = 0, pw = 0;
+        const int g = (warp - kDecodeWarp0) >> 2, quarter = warp & 3;   // group g: stages g, g+4, ... into weight stage g
+        static_assert(SW == 4 && ST >= 4, "one weight stage per decode group");
+        int st = g, pt = 0, pw = 0;
         const int total = my_items * kstages;
-        for (int cnt = 0; cnt < total; ++cnt) {
+        for (int cnt = g; cnt < total; cnt += 4) {
             mbar_wait_parked(full_t + 8 * st, pt, p.status, 40);
-            decode_stage<BITS, CB>(t_ring + st * T_STAGE_BYTES, tmem_w + sw * 32, d, lane, cnt >= SW, empty_w + 8 * sw, pw ^ 1, p.status);
+            decode_stage<BITS, CB>(t_ring + st * T_STAGE_BYTES, tmem_w + g * 32, quarter, lane, cnt >= SW, empty_w + 8 * g, pw ^ 1, p.status);
             if (lane == 0) {
-                mbar_arrive(full_w + 8 * sw);
+                mbar_arrive(full_w + 8 * g);
                 mbar_arrive(empty_t + 8 * st);
             }
-            if (++st == ST) { st = 0; pt ^= 1; }
-            if (++sw == SW) { sw = 0; pw ^= 1; }
+            st += 4;
+            if (st >= ST) { st -= ST; pt ^= 1; }
+            pw ^= 1;
         }
     } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + 4) {
         // ------------------------------------------------------------ epilogue warps
