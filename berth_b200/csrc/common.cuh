@@ -112,6 +112,29 @@ struct GemvProblem {
     int z, row0, rows, pad;
 };
 
+// Rotation of the rows of a grouped tensor-core launch (see rotate_rows_grouped).
+struct RotateArgs {
+    const __half* src;     // input rows [.][k]; the gate outputs in silu mode
+    const __half* src_u;   // silu mode: the up outputs
+    const int32_t* perm;   // gather mode: row r < n_perm reads src row perm[r] / div, later rows read src row r - n_perm
+    int div, n_perm;
+    const __half* suh_a;   // [n_matrices][k]
+    const __half* suh_b;   // dual mode: second scale stack
+    __half* out_a;         // [max_rows][k]
+    __half* out_b;         // dual mode: second output
+    const GemvProblem* problems;
+    const int* n_problems;
+    int chunk, k, max_problems, n_matrices, max_rows;
+};
+// out_a[row] = fp16(H128(x[row] * suh_a[matrix of the row]) / sqrt(128)) for every row the problem table covers
+// (and out_b with suh_b when `dual`); x = src, or silu(src) * src_u when `silu`, or gathered rows of src when a.perm is set.
+void rotate_rows_grouped(const RotateArgs& a, bool dual, bool silu, int sms, cudaStream_t stream);
+// launch_gemm_tc_grouped without its rotation: `xr_had` already holds the rotated rows.
+std::string launch_gemm_tc_grouped_rotated(const void* xr_had, const void* trellis_stack, int n_matrices, void* c, const void* svh_stack,
+                                           const GemvProblem* problems, const int* n_problems, int max_problems, int max_rows, int nsub,
+                                           int size_k, int size_n, int k_bits, int codebook, int out_fp32, unsigned* status, int sms,
+                                           cudaStream_t stream);
+
 // Grouped prefill launch over a stack of equally shaped matrices on the tensor cores: problem i applies
 // matrix z_i to rows [row0_i, row0_i + rows_i) of xr, rows_i <= 128 * nsub; xr_had [max_rows][k] fp16
 // receives the rotated rows.

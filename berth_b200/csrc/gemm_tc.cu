@@ -33,6 +33,7 @@
 // All waits are bounded: a wait that runs out sets a status bit and the kernel carries on and
 // exits (wrong output, no hang).
 #include "exl3_decode.cuh"
+#include "silu.cuh"
 
 #include <cuda.h>
 
@@ -785,49 +786,117 @@ void launch_tc_bits(int k_bits, int codebook, const void* a_had, const void* tre
     }
 }
 
-// Rotation of the routed rows of a grouped launch: a_had[row] = fp16(H128(x[row] * suh[matrix of the row]) / sqrt(128)).
-// One warp per row: it finds the row's problem by bisection over the table (problems are sorted by first
-// row and cover [0, total rows) without gaps), then walks the row's 128-blocks.
-__global__ void __launch_bounds__(256) k_rotate_rows_plain(const __half* __restrict__ xr, const __half* __restrict__ suh_stack,
-                                                           const GemvProblem* __restrict__ problems, const int* __restrict__ n_problems,
-                                                           __half* __restrict__ a_had, int chunk, int k, int max_problems,
-                                                           int n_matrices, int max_rows)
+// Rotation of the rows of a grouped launch: out[row] = fp16(H128(x[row] * suh[matrix of the row]) / sqrt(128)).
+// One warp per row: it finds the row's problem by bisection over the table of first rows (problems are sorted by
+// first row and cover [0, total rows) without gaps; the block keeps the table in shared memory when it fits), then
+// walks the row 256 elements at a time: a lane holds eight consecutive elements, sixteen lanes one 128-block, so
+// strides 1, 2, 4 of the butterfly stay in registers and 8..64 take four shuffle rounds.
+// MODE bits: kRotDual = a second scale stack and output from the same input row (gate and up of an MLP);
+// kRotGather = row r < n_perm reads src row perm[r] / div, later rows read src row r - n_perm;
+// kRotSilu = the input row is silu(src) * src_u, rounded to fp16 as the element-wise kernel rounds it.
+constexpr int kRotDual = 1, kRotGather = 2, kRotSilu = 4, kRotTable = 2048;
+
+__device__ __forceinline__ void had128_lane8(float (&v)[8], int lane)
 {
-    const int lane = threadIdx.x & 31, kblocks = k >> 7;
-    const int nprob = min(max(__ldg(n_problems), 0), max_problems);
-    if (nprob < 1) return;
-    const GemvProblem last = load_problem(problems, nprob - 1, n_matrices, chunk, max_rows);
-    const int total_rows = min(last.row0 + last.rows, max_rows);
-    for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < total_rows; row += gridDim.x * 8) {
-        int lo = 0, hi = nprob - 1;   // the last problem whose first row is <= row
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (__ldg(&problems[mid].row0) <= row) lo = mid; else hi = mid - 1;
+#pragma unroll
+    for (int s = 1; s < 8; s <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if ((i & s) == 0) {
+                const float a = v[i], b = v[i + s];
+                v[i] = __fadd_rn(a, b);
+                v[i + s] = __fsub_rn(a, b);
+            }
         }
-        const GemvProblem pr = load_problem(problems, lo, n_matrices, chunk, max_rows);
-        if (row < pr.row0 || row >= pr.row0 + pr.rows) continue;   // a table with gaps: leave the row alone
-        const __half* suh = suh_stack + size_t(pr.z) * k;
-#pragma unroll 4
-        for (int b = 0; b < kblocks; ++b) {
-            const size_t off = size_t(row) * k + b * 128 + lane * 4;
-            uint2 xm = *reinterpret_cast<const uint2*>(xr + off);
-            uint2 sm = __ldg(reinterpret_cast<const uint2*>(suh + b * 128 + lane * 4));
-            const __half2 x0 = *reinterpret_cast<__half2*>(&xm.x), x1 = *reinterpret_cast<__half2*>(&xm.y);
-            const __half2 s0 = *reinterpret_cast<__half2*>(&sm.x), s1 = *reinterpret_cast<__half2*>(&sm.y);
-            float v[4];
-            v[0] = __fmul_rn(__low2float(x0), __low2float(s0));
-            v[1] = __fmul_rn(__high2float(x0), __high2float(s0));
-            v[2] = __fmul_rn(__low2float(x1), __low2float(s1));
-            v[3] = __fmul_rn(__high2float(x1), __high2float(s1));
-            dq::had128_warp(v, lane);
-            uint2 o;
-            o.x = dq::pack_half2(__float2half_rn(__fmul_rn(v[0], kRScale)), __float2half_rn(__fmul_rn(v[1], kRScale)));
-            o.y = dq::pack_half2(__float2half_rn(__fmul_rn(v[2], kRScale)), __float2half_rn(__fmul_rn(v[3], kRScale)));
-            *reinterpret_cast<uint2*>(a_had + off) = o;
+    }
+#pragma unroll
+    for (int off = 1; off < 16; off <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float o = __shfl_xor_sync(dq::kFull, v[i], off);
+            v[i] = (lane & off) ? __fsub_rn(o, v[i]) : __fadd_rn(v[i], o);
         }
     }
 }
 
+__device__ __forceinline__ void rotate_store8(const float (&x)[8], const __half* suh, __half* out, int lane, bool active)
+{
+    float v[8];
+    uint4 sm = make_uint4(0u, 0u, 0u, 0u);
+    if (active) sm = __ldg(reinterpret_cast<const uint4*>(suh));
+    const uint32_t sw[4] = {sm.x, sm.y, sm.z, sm.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&sw[i]));
+        v[2 * i] = __fmul_rn(x[2 * i], f.x);
+        v[2 * i + 1] = __fmul_rn(x[2 * i + 1], f.y);
+    }
+    had128_lane8(v, lane);
+    if (active) {
+        uint4 o;
+        o.x = dq::pack_half2(__float2half_rn(__fmul_rn(v[0], kRScale)), __float2half_rn(__fmul_rn(v[1], kRScale)));
+        o.y = dq::pack_half2(__float2half_rn(__fmul_rn(v[2], kRScale)), __float2half_rn(__fmul_rn(v[3], kRScale)));
+        o.z = dq::pack_half2(__float2half_rn(__fmul_rn(v[4], kRScale)), __float2half_rn(__fmul_rn(v[5], kRScale)));
+        o.w = dq::pack_half2(__float2half_rn(__fmul_rn(v[6], kRScale)), __float2half_rn(__fmul_rn(v[7], kRScale)));
+        *reinterpret_cast<uint4*>(out) = o;
+    }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(256) k_rotate_rows_plain(const RotateArgs a)
+{
+    __shared__ int s_row0[kRotTable];
+    const int lane = threadIdx.x & 31, k = a.k;
+    const int nprob = min(max(__ldg(a.n_problems), 0), a.max_problems);
+    if (nprob < 1) return;
+    const bool tab = nprob <= kRotTable;
+    if (tab) {
+        for (int i = threadIdx.x; i < nprob; i += blockDim.x) s_row0[i] = __ldg(&a.problems[i].row0);
+        __syncthreads();
+    }
+    const GemvProblem last = load_problem(a.problems, nprob - 1, a.n_matrices, a.chunk, a.max_rows);
+    const int total_rows = min(last.row0 + last.rows, a.max_rows);
+    for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < total_rows; row += gridDim.x * 8) {
+        int src_row = row;
+        if constexpr (MODE & kRotGather) src_row = row < a.n_perm ? __ldg(a.perm + row) / a.div : row - a.n_perm;
+        int lo = 0, hi = nprob - 1;   // the last problem whose first row is <= row
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            const int r0 = tab ? s_row0[mid] : __ldg(&a.problems[mid].row0);
+            if (r0 <= row) lo = mid; else hi = mid - 1;
+        }
+        const GemvProblem pr = load_problem(a.problems, lo, a.n_matrices, a.chunk, a.max_rows);
+        if (row < pr.row0 || row >= pr.row0 + pr.rows) continue;   // a table with gaps: leave the row alone
+        const __half* xs = a.src + size_t(src_row) * k;
+        const size_t so = size_t(pr.z) * k, ro = size_t(row) * k;
+#pragma unroll 2
+        for (int c0 = 0; c0 < k; c0 += 256) {
+            const int c = c0 + lane * 8;
+            const bool active = c < k;
+            float x[8];
+            uint4 xm = make_uint4(0u, 0u, 0u, 0u);
+            if (active) xm = *reinterpret_cast<const uint4*>(xs + c);
+            uint32_t xw[4] = {xm.x, xm.y, xm.z, xm.w};
+            if constexpr (MODE & kRotSilu) {
+                uint4 um = make_uint4(0u, 0u, 0u, 0u);
+                if (active) um = *reinterpret_cast<const uint4*>(a.src_u + size_t(src_row) * k + c);
+                const uint32_t uw[4] = {um.x, um.y, um.z, um.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const __half2 g = *reinterpret_cast<const __half2*>(&xw[i]), u = *reinterpret_cast<const __half2*>(&uw[i]);
+                    xw[i] = dq::pack_half2(silu_mul_one(__low2half(g), __low2half(u), 0.0f), silu_mul_one(__high2half(g), __high2half(u), 0.0f));
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xw[i]));
+                x[2 * i] = f.x; x[2 * i + 1] = f.y;
+            }
+            rotate_store8(x, a.suh_a + so + c, a.out_a + ro + c, lane, active);
+            if constexpr (MODE & kRotDual) rotate_store8(x, a.suh_b + so + c, a.out_b + ro + c, lane, active);
+        }
+    }
+}
 }  // namespace
 
 void had_r_128(const void* input, void* output, const void* scale, int pre_scale, int rows, int cols, int fp32,
@@ -869,21 +938,34 @@ std::string launch_gemm_tc(const void* a, const void* trellis, void* c, const vo
            " block=" + std::to_string(kThreads) + " tile=" + std::to_string(args.nsub_max * SUB) + "x128x64 tmem=512";
 }
 
-// Grouped prefill linear over a stack of equally shaped matrices: problem i applies matrix z_i to rows
-// [row0_i, row0_i + rows_i) of xr (rows_i <= 128 * nsub); xr_had [max_rows][k] receives the rotated rows.
-std::string launch_gemm_tc_grouped(const void* xr, void* xr_had, const void* trellis_stack, int n_matrices, void* c,
-                                   const void* suh_stack, const void* svh_stack, const GemvProblem* problems, const int* n_problems,
-                                   int max_problems, int max_rows, int nsub, int size_k, int size_n, int k_bits, int codebook,
-                                   int out_fp32, unsigned* status, int sms, cudaStream_t stream)
+void rotate_rows_grouped(const RotateArgs& a, bool dual, bool silu, int sms, cudaStream_t stream)
 {
+    if (a.k % 128 != 0) throw std::runtime_error("exl3 grouped gemm: size_k must be a multiple of 128");
+    if (!a.src || !a.suh_a || !a.out_a || (dual && (!a.suh_b || !a.out_b)) || (silu && !a.src_u))
+        throw std::runtime_error("exl3 grouped gemm: null rotation pointer");
+    if (silu && (dual || a.perm)) throw std::runtime_error("exl3 grouped gemm: the silu rotation takes one plain input");
+    const dim3 grid(std::max(1, std::min((a.max_rows + 7) / 8, 8 * sms)));
+    const int mode = (dual ? kRotDual : 0) | (a.perm ? kRotGather : 0) | (silu ? kRotSilu : 0);
+    switch (mode) {
+        case 0: k_rotate_rows_plain<0><<<grid, 256, 0, stream>>>(a); break;
+        case kRotDual: k_rotate_rows_plain<kRotDual><<<grid, 256, 0, stream>>>(a); break;
+        case kRotGather: k_rotate_rows_plain<kRotGather><<<grid, 256, 0, stream>>>(a); break;
+        case kRotDual | kRotGather: k_rotate_rows_plain<kRotDual | kRotGather><<<grid, 256, 0, stream>>>(a); break;
+        default: k_rotate_rows_plain<kRotSilu><<<grid, 256, 0, stream>>>(a); break;
+    }
+    cuda_ok(cudaGetLastError(), "k_rotate_rows_plain launch");
+}
+
+std::string launch_gemm_tc_grouped_rotated(const void* xr_had, const void* trellis_stack, int n_matrices, void* c, const void* svh_stack,
+                                           const GemvProblem* problems, const int* n_problems, int max_problems, int max_rows, int nsub,
+                                           int size_k, int size_n, int k_bits, int codebook, int out_fp32, unsigned* status, int sms,
+                                           cudaStream_t stream)
+{
+    (void) sms;
     if (size_k % 128 != 0 || size_n % 128 != 0)
         throw std::runtime_error("exl3 grouped gemm: size_k and size_n must be multiples of 128");
     if (nsub < 1 || nsub > MAX_SUB) throw std::runtime_error("exl3 grouped gemm: row chunks must be 128, 256 or 384 rows");
     if (max_problems < 1 || max_problems > 65535) throw std::runtime_error("exl3 grouped gemm: problem count out of range");
-    k_rotate_rows_plain<<<std::max(1, std::min((max_rows + 7) / 8, 8 * sms)), 256, 0, stream>>>(
-        static_cast<const __half*>(xr), static_cast<const __half*>(suh_stack), problems, n_problems, static_cast<__half*>(xr_had),
-        nsub * SUB, size_k, max_problems, n_matrices, max_rows);
-    cuda_ok(cudaGetLastError(), "k_rotate_rows_plain launch");
     GemmArgs args;
     args.c = c;
     args.svh = static_cast<const __half*>(svh_stack);
@@ -893,9 +975,29 @@ std::string launch_gemm_tc_grouped(const void* xr, void* xr_had, const void* tre
     args.nsub_max = nsub;
     args.problems = problems; args.n_problems = n_problems; args.max_problems = max_problems; args.n_matrices = n_matrices;
     launch_tc_bits(k_bits, codebook, xr_had, trellis_stack, args, stream);
-    return "k_rotate_rows_plain + k_exl3_gemm_tc_grouped<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "> persistent items<=" +
+    return "k_exl3_gemm_tc_grouped<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "> persistent items<=" +
            std::to_string(size_n / BN) + "x" + std::to_string(max_problems) + " block=" + std::to_string(kThreads) + " tile=" +
            std::to_string(nsub * SUB) + "x128x64 tmem=512";
+}
+
+// Grouped prefill linear over a stack of equally shaped matrices: problem i applies matrix z_i to rows
+// [row0_i, row0_i + rows_i) of xr (rows_i <= 128 * nsub); xr_had [max_rows][k] receives the rotated rows.
+std::string launch_gemm_tc_grouped(const void* xr, void* xr_had, const void* trellis_stack, int n_matrices, void* c,
+                                   const void* suh_stack, const void* svh_stack, const GemvProblem* problems, const int* n_problems,
+                                   int max_problems, int max_rows, int nsub, int size_k, int size_n, int k_bits, int codebook,
+                                   int out_fp32, unsigned* status, int sms, cudaStream_t stream)
+{
+    if (max_problems < 1 || max_problems > 65535) throw std::runtime_error("exl3 grouped gemm: problem count out of range");
+    RotateArgs r{};
+    r.src = static_cast<const __half*>(xr);
+    r.suh_a = static_cast<const __half*>(suh_stack);
+    r.out_a = static_cast<__half*>(xr_had);
+    r.problems = problems; r.n_problems = n_problems;
+    r.chunk = nsub * SUB; r.k = size_k; r.max_problems = max_problems; r.n_matrices = n_matrices; r.max_rows = max_rows;
+    rotate_rows_grouped(r, false, false, sms, stream);
+    return "k_rotate_rows_plain + " + launch_gemm_tc_grouped_rotated(xr_had, trellis_stack, n_matrices, c, svh_stack, problems, n_problems,
+                                                                     max_problems, max_rows, nsub, size_k, size_n, k_bits, codebook,
+                                                                     out_fp32, status, sms, stream);
 }
 
 }  // namespace berth

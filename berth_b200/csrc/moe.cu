@@ -532,7 +532,7 @@ int routed_rows_hint(int T, int top_k, int n_experts)
 // Workspace carve-up of the expert stage for up to R routed rows.
 struct ExpertScratch {
     int* counts; int* offsets; int* n_problems; GemvProblem* problems;
-    uint32_t* afrag; float* blocksum; __half* g; __half* u; int max_problems;
+    uint32_t* afrag; uint32_t* afrag2; float* blocksum; __half* g; __half* u; int max_problems;
     size_t bytes;
 };
 ExpertScratch carve_experts(void* base, int R, int n_local, int hidden, int inter, const ExpertPlan& plan)
@@ -547,13 +547,15 @@ ExpertScratch carve_experts(void* base, int R, int n_local, int hidden, int inte
     const size_t o_prob = take(size_t(s.max_problems) * sizeof(GemvProblem));
     // rotated activations: fragment order per problem (GEMV) or plain rows (GEMM)
     const size_t o_afrag = take(plan.tg ? size_t(s.max_problems) * (kmax / 16) * plan.tg * 256 : size_t(R) * kmax * 2);
+    // GEMM path: the rows rotated with the up projection's scales (gate and up are rotated by one launch)
+    const size_t o_afrag2 = take(plan.tg ? 256 : size_t(R) * hidden * 2);
     const size_t o_bsum = take(plan.tg ? size_t(s.max_problems) * chunk * (kmax / 128) * 4 : 256);
     const size_t o_g = take(size_t(R) * inter * 2), o_u = take(size_t(R) * inter * 2);
     s.bytes = off;
     if (base) {
         char* b = static_cast<char*>(base);
         s.counts = (int*) (b + o_counts); s.offsets = (int*) (b + o_offsets); s.n_problems = (int*) (b + o_np);
-        s.problems = (GemvProblem*) (b + o_prob); s.afrag = (uint32_t*) (b + o_afrag); s.blocksum = (float*) (b + o_bsum);
+        s.problems = (GemvProblem*) (b + o_prob); s.afrag = (uint32_t*) (b + o_afrag); s.afrag2 = (uint32_t*) (b + o_afrag2); s.blocksum = (float*) (b + o_bsum);
         s.g = (__half*) (b + o_g); s.u = (__half*) (b + o_u);
     }
     return s;
@@ -620,11 +622,18 @@ void dispatch(const int32_t* keys, int n, int e0, int n_local, int chunk, const 
     cuda_ok(cudaGetLastError(), "k_moe_scatter launch");
 }
 
+// Where the expert stage's input rows come from when they are not in place: row r < n_perm is row perm[r] / div
+// of the array handed in as xr, later rows are its rows r - n_perm (perm == nullptr: xr holds the rows themselves).
+struct RowSource {
+    const int32_t* perm = nullptr;
+    int div = 1, n_perm = 0;
+};
+
 // Grouped gate/up -> silu*up -> down over routed rows xr [R][hidden]; yr fp16 [R][hidden].
 std::string experts(const berth_moe_weights* w, const void* gate_t, const void* up_t, const void* down_t, const void* gsuh,
                     const void* gsvh, const void* usuh, const void* usvh, const void* dsuh, const void* dsvh, int n_local,
                     const void* xr, void* yr, int R, int max_rows, const ExpertPlan& plan, const ExpertScratch& s, const GemvScratch& sc,
-                    int sms, cudaStream_t st, const int* rows_dev = nullptr)
+                    int sms, cudaStream_t st, const int* rows_dev = nullptr, const RowSource& src = RowSource{})
 {
     const int H = w->hidden, I = w->inter;
     // the activation between the projections: over R rows, or over the device-side count (at most max_rows)
@@ -633,15 +642,31 @@ std::string experts(const berth_moe_weights* w, const void* gate_t, const void* 
         else if (berth_ops_silu_mul(s.g, s.u, s.g, int64_t(R) * I, 0.0f, st) != 0) throw std::runtime_error(berth_ops_last_error());
     };
     if (plan.nsub) {
-        std::string d = launch_gemm_tc_grouped(xr, s.afrag, gate_t, n_local, s.g, gsuh, gsvh, s.problems, s.n_problems, s.max_problems,
-                                               max_rows, plan.nsub, H, I, w->k_bits, w->codebook, 0, sc.status, sms, st);
-        launch_gemm_tc_grouped(xr, s.afrag, up_t, n_local, s.u, usuh, usvh, s.problems, s.n_problems, s.max_problems, max_rows, plan.nsub,
-                               H, I, w->k_bits, w->codebook, 0, sc.status, sms, st);
-        act();
-        launch_gemm_tc_grouped(s.g, s.afrag, down_t, n_local, yr, dsuh, dsvh, s.problems, s.n_problems, s.max_problems, max_rows,
-                               plan.nsub, I, H, w->k_bits, w->codebook, 0, sc.status, sms, st);
-        return d;
+        // one rotation launch for gate and up (the row is read once), the activation inside the rotation for down
+        RotateArgs r{};
+        r.src = static_cast<const __half*>(xr);
+        r.perm = src.perm; r.div = src.div; r.n_perm = src.n_perm;
+        r.suh_a = static_cast<const __half*>(gsuh); r.suh_b = static_cast<const __half*>(usuh);
+        r.out_a = reinterpret_cast<__half*>(s.afrag); r.out_b = reinterpret_cast<__half*>(s.afrag2);
+        r.problems = s.problems; r.n_problems = s.n_problems;
+        r.chunk = plan.chunk; r.k = H; r.max_problems = s.max_problems; r.n_matrices = n_local; r.max_rows = max_rows;
+        rotate_rows_grouped(r, true, false, sms, st);
+        std::string d = launch_gemm_tc_grouped_rotated(s.afrag, gate_t, n_local, s.g, gsvh, s.problems, s.n_problems, s.max_problems, max_rows,
+                                                       plan.nsub, H, I, w->k_bits, w->codebook, 0, sc.status, sms, st);
+        launch_gemm_tc_grouped_rotated(s.afrag2, up_t, n_local, s.u, usvh, s.problems, s.n_problems, s.max_problems, max_rows, plan.nsub, H,
+                                       I, w->k_bits, w->codebook, 0, sc.status, sms, st);
+        RotateArgs rd{};
+        rd.src = s.g; rd.src_u = s.u;
+        rd.suh_a = static_cast<const __half*>(dsuh);
+        rd.out_a = reinterpret_cast<__half*>(s.afrag);
+        rd.problems = s.problems; rd.n_problems = s.n_problems;
+        rd.chunk = plan.chunk; rd.k = I; rd.max_problems = s.max_problems; rd.n_matrices = n_local; rd.max_rows = max_rows;
+        rotate_rows_grouped(rd, false, true, sms, st);
+        launch_gemm_tc_grouped_rotated(s.afrag, down_t, n_local, yr, dsvh, s.problems, s.n_problems, s.max_problems, max_rows, plan.nsub, I,
+                                       H, w->k_bits, w->codebook, 0, sc.status, sms, st);
+        return "k_rotate_rows_plain<gate+up> + 2 x " + d + " + k_rotate_rows_plain<silu> + 1 x (same, down)";
     }
+    if (src.perm) throw std::runtime_error("moe experts: gathered input rows are taken on the tensor-core path only");
     const int tg = plan.tg;
     std::string d = launch_gemv_grouped(xr, gate_t, n_local, s.g, gsuh, gsvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag,
                                         s.blocksum, H, I, w->k_bits, w->codebook, 0, sc, sms, st);
@@ -1083,12 +1108,18 @@ extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T,
 
         router_topk(x, w->w_router, w->router_bias, topk_idx, topk_w, logits, T, H, E, K, cs);
         dispatch(topk_idx, R, 0, E, plan.chunk, es, perm, inv, cs, fused_shared ? T : 0);
-        k_moe_gather_rows<<<std::min(R, 148 * 8), 256, 0, cs>>>((const __half*) x, perm, es.offsets + E, K, xr, H);
-        cuda_ok(cudaGetLastError(), "k_moe_gather_rows launch");
-        if (fused_shared)
-            cuda_ok(cudaMemcpyAsync(xr + size_t(R) * H, x, size_t(T) * H * 2, cudaMemcpyDeviceToDevice, cs), "moe layer: shared rows copy");
+        RowSource rows_from{};
+        if (plan.nsub) {
+            // tensor-core path: the rotation kernel gathers the rows from x itself
+            rows_from.perm = perm; rows_from.div = K; rows_from.n_perm = R;
+        } else {
+            k_moe_gather_rows<<<std::min(R, 148 * 8), 256, 0, cs>>>((const __half*) x, perm, es.offsets + E, K, xr, H);
+            cuda_ok(cudaGetLastError(), "k_moe_gather_rows launch");
+            if (fused_shared)
+                cuda_ok(cudaMemcpyAsync(xr + size_t(R) * H, x, size_t(T) * H * 2, cudaMemcpyDeviceToDevice, cs), "moe layer: shared rows copy");
+        }
         st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
-                            w->down_suh, w->down_svh, NM, xr, yr, RT, RT, plan, es, sc, info.sms, cs);
+                            w->down_suh, w->down_svh, NM, plan.nsub ? x : xr, yr, RT, RT, plan, es, sc, info.sms, cs, nullptr, rows_from);
 
         __half* ysh = fused_shared ? yr + size_t(R) * H : nullptr;
         if (SI > 0 && !fused_shared) {
