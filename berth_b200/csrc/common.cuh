@@ -156,6 +156,29 @@ __device__ __forceinline__ GemvProblem load_problem(const GemvProblem* table, in
 }
 #endif
 
+// Rotation of the rows of a grouped decode launch into MMA-fragment order (see rotate_rows_frag).
+struct RotateFragArgs {
+    const __half* src;     // input rows [.][k]; the gate outputs in silu mode
+    const __half* src_u;   // silu mode: the up outputs
+    const int32_t* perm;   // gather mode: row r < n_perm reads src row perm[r] / div, later rows read src row r - n_perm
+    int div, n_perm;
+    const __half* suh_a;   // [n_matrices][k]
+    const __half* suh_b;   // dual mode: second scale stack
+    uint32_t* afrag_a;     // max_problems * (k/16) * (tok/8) * 64 words
+    uint32_t* afrag_b;     // dual mode
+    float* bsum_a;         // max_problems * tok * (k/128) floats
+    float* bsum_b;         // dual mode
+    const GemvProblem* problems;
+    const int* n_problems;
+    int tok, k, max_problems, n_matrices, max_rows;   // tok = rows per problem: 8, 16 or 32
+};
+void rotate_rows_frag(const RotateFragArgs& a, bool dual, bool silu, int sms, cudaStream_t stream);
+// launch_gemv_grouped without its rotation: afrag / blocksum already hold the rotated rows.
+std::string launch_gemv_grouped_rotated(const void* trellis_stack, int n_experts, void* c, const void* svh_stack,
+                                        const GemvProblem* problems, const int* n_problems, int max_problems, int max_rows, int tg,
+                                        const uint32_t* afrag, float* blocksum, int size_k, int size_n, int k_bits, int codebook,
+                                        int out_fp32, const GemvScratch& scratch, int sms, cudaStream_t stream);
+
 // Grouped decode launch over a stack of equally shaped matrices (the experts of an MoE layer):
 // `problems` / `n_problems` live on the device (built by the dispatch kernels), xr fp16 [R][k] are
 // the routed rows, c the outputs [R][n]; suh_stack [experts][k], svh_stack [experts][n].

@@ -37,6 +37,7 @@
 //                affine correction, Hadamard, svh, store), in the background of the streaming warps.
 // Every mbarrier wait is bounded; a wait that runs out sets a status bit and carries on.
 #include "exl3_decode.cuh"
+#include "silu.cuh"
 #include "../../include/berth_b200.h"
 
 #include <cuda.h>
@@ -297,11 +298,21 @@ __device__ __forceinline__ void tile_mma(const uint32_t (&s)[8], float (&acc)[TG
 // elements 4*lane .. 4*lane+3 packed as two half pairs.  SUM: `sx` = sum of the 128 rounded values
 // (every lane), which the MUL1 epilogue needs.
 template <bool SUM>
+__device__ __forceinline__ uint2 rotate_bits(uint2 xr, uint2 sr, int lane, float& sx);
+
+template <bool SUM>
 __device__ __forceinline__ uint2 rotate_block(const __half* __restrict__ xrow, const __half* __restrict__ suh, int kb, int lane, float& sx)
 {
     const int kcol = kb * 128 + lane * 4;
-    uint2 xr = *reinterpret_cast<const uint2*>(xrow + kcol);
-    uint2 sr = *reinterpret_cast<const uint2*>(suh + kcol);
+    const uint2 xr = *reinterpret_cast<const uint2*>(xrow + kcol);
+    const uint2 sr = *reinterpret_cast<const uint2*>(suh + kcol);
+    return rotate_bits<SUM>(xr, sr, lane, sx);
+}
+
+// The same from the lane's four input values and four scales, already loaded.
+template <bool SUM>
+__device__ __forceinline__ uint2 rotate_bits(uint2 xr, uint2 sr, int lane, float& sx)
+{
     __half2 x0 = *reinterpret_cast<__half2*>(&xr.x), x1 = *reinterpret_cast<__half2*>(&xr.y);
     __half2 s0 = *reinterpret_cast<__half2*>(&sr.x), s1 = *reinterpret_cast<__half2*>(&sr.y);
     float v[4];
@@ -866,32 +877,52 @@ size_t launch_bits(int k_bits, int cb, int tg, bool fused, const void* t, int nm
     }
 }
 
-// Rotation for a grouped launch: routed rows xr [R][k]; one block per problem, its warps share the
+// Rotation for a grouped launch: routed rows [R][k]; one block per problem, its warps share the
 // (row, 128-block) pairs of the problem's real rows; the row's expert picks the sign-scale vector.
 // Rows past the problem's count are left as they are: a token is a column of the MMA, so whatever
 // sits there reaches only accumulators that nobody stores.
-__global__ void __launch_bounds__(256) k_rotate_rows(const __half* __restrict__ xr, const __half* __restrict__ suh_stack,
-                                                     const GemvProblem* __restrict__ problems, const int* __restrict__ n_problems,
-                                                     uint32_t* __restrict__ afrag, float* __restrict__ blocksum, int tok, int k,
-                                                     int max_problems, int n_matrices, int max_rows)
+// MODE bits: kFragDual = a second scale stack with its own fragment and block-sum outputs (gate and up read the
+// row once); kFragGather = row r < n_perm reads src row perm[r] / div, later rows src row r - n_perm;
+// kFragSilu = the input is silu(src) * src_u, rounded to fp16 as the element-wise kernel rounds it.
+constexpr int kFragDual = 1, kFragGather = 2, kFragSilu = 4;
+
+template <int MODE>
+__global__ void __launch_bounds__(256) k_rotate_rows(const RotateFragArgs a)
 {
     grid_dependency_wait();      // the problem table comes from the preceding kernel
     grid_launch_dependents();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, kblocks = k >> 7, tgs = tok >> 3;
-    const int nprob = min(max(__ldg(n_problems), 0), max_problems);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, k = a.k, kblocks = k >> 7, tgs = a.tok >> 3;
+    const int nprob = min(max(__ldg(a.n_problems), 0), a.max_problems);
     for (int pi = blockIdx.x; pi < nprob; pi += gridDim.x) {
-        const GemvProblem pr = load_problem(problems, pi, n_matrices, tok, max_rows);
-        const __half* suh = suh_stack + size_t(pr.z) * k;
+        const GemvProblem pr = load_problem(a.problems, pi, a.n_matrices, a.tok, a.max_rows);
+        const size_t so = size_t(pr.z) * k;
         const int pairs = pr.rows * kblocks;
 #pragma unroll 4
         for (int pair = warp; pair < pairs; pair += 8) {
             const int lr = pair / kblocks, b = pair - lr * kblocks;
-            float sx;
-            const uint2 o = rotate_block<true>(xr + size_t(pr.row0 + lr) * k, suh, b, lane, sx);
-            if (lane == 0) blocksum[(size_t(pi) * tok + lr) * kblocks + b] = sx;
+            const int row = pr.row0 + lr, kcol = b * 128 + lane * 4;
+            int src_row = row;
+            if constexpr (MODE & kFragGather) src_row = row < a.n_perm ? __ldg(a.perm + row) / a.div : row - a.n_perm;
+            uint2 x = *reinterpret_cast<const uint2*>(a.src + size_t(src_row) * k + kcol);
+            if constexpr (MODE & kFragSilu) {
+                const uint2 u = *reinterpret_cast<const uint2*>(a.src_u + size_t(src_row) * k + kcol);
+                const __half2 g0 = *reinterpret_cast<const __half2*>(&x.x), g1 = *reinterpret_cast<const __half2*>(&x.y);
+                const __half2 u0 = *reinterpret_cast<const __half2*>(&u.x), u1 = *reinterpret_cast<const __half2*>(&u.y);
+                x.x = dq::pack_half2(silu_mul_one(__low2half(g0), __low2half(u0), 0.0f), silu_mul_one(__high2half(g0), __high2half(u0), 0.0f));
+                x.y = dq::pack_half2(silu_mul_one(__low2half(g1), __low2half(u1), 0.0f), silu_mul_one(__high2half(g1), __high2half(u1), 0.0f));
+            }
             const int ktile = b * 8 + (lane >> 2), hsel = (lane & 3) >> 1, q = 2 * (lane & 1);
             const size_t w = (((size_t(pi) * (k >> 4) + ktile) * tgs + (lr >> 3)) * 2 + hsel) * 32 + (lr & 7) * 4 + q;
-            *reinterpret_cast<uint2*>(afrag + w) = o;
+            const size_t bs = (size_t(pi) * a.tok + lr) * kblocks + b;
+            float sx;
+            const uint2 o = rotate_bits<true>(x, __ldg(reinterpret_cast<const uint2*>(a.suh_a + so + kcol)), lane, sx);
+            if (lane == 0) a.bsum_a[bs] = sx;
+            *reinterpret_cast<uint2*>(a.afrag_a + w) = o;
+            if constexpr (MODE & kFragDual) {
+                const uint2 o2 = rotate_bits<true>(x, __ldg(reinterpret_cast<const uint2*>(a.suh_b + so + kcol)), lane, sx);
+                if (lane == 0) a.bsum_b[bs] = sx;
+                *reinterpret_cast<uint2*>(a.afrag_b + w) = o2;
+            }
         }
     }
 }
@@ -977,23 +1008,39 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
            " + k_gemv_finish";
 }
 
-std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n_experts, void* c, const void* suh_stack,
-                                const void* svh_stack, const GemvProblem* problems, const int* n_problems, int max_problems,
-                                int max_rows, int tg, uint32_t* afrag, float* blocksum, int size_k, int size_n, int k_bits,
-                                int codebook, int out_fp32, const GemvScratch& sc, int sms, cudaStream_t stream)
+void rotate_rows_frag(const RotateFragArgs& a, bool dual, bool silu, int sms, cudaStream_t stream)
+{
+    if (a.k % 128 != 0) throw std::runtime_error("exl3 grouped gemv: size_k must be a multiple of 128");
+    if (a.tok != 8 && a.tok != 16 && a.tok != 32) throw std::runtime_error("exl3 grouped gemv: token groups must be 1, 2 or 4");
+    if (!a.src || !a.suh_a || !a.afrag_a || !a.bsum_a || (dual && (!a.suh_b || !a.afrag_b || !a.bsum_b)) || (silu && !a.src_u))
+        throw std::runtime_error("exl3 grouped gemv: null rotation pointer");
+    if (silu && (dual || a.perm)) throw std::runtime_error("exl3 grouped gemv: the silu rotation takes one plain input");
+    const dim3 grid(std::max(1, std::min(a.max_problems, 16 * sms)));
+    const int mode = (dual ? kFragDual : 0) | (a.perm ? kFragGather : 0) | (silu ? kFragSilu : 0);
+    switch (mode) {
+        case 0: launch_pdl(k_rotate_rows<0>, grid, dim3(256), 0, stream, "k_rotate_rows launch", a); break;
+        case kFragDual: launch_pdl(k_rotate_rows<kFragDual>, grid, dim3(256), 0, stream, "k_rotate_rows launch", a); break;
+        case kFragGather: launch_pdl(k_rotate_rows<kFragGather>, grid, dim3(256), 0, stream, "k_rotate_rows launch", a); break;
+        case kFragDual | kFragGather:
+            launch_pdl(k_rotate_rows<kFragDual | kFragGather>, grid, dim3(256), 0, stream, "k_rotate_rows launch", a);
+            break;
+        default: launch_pdl(k_rotate_rows<kFragSilu>, grid, dim3(256), 0, stream, "k_rotate_rows launch", a); break;
+    }
+}
+
+std::string launch_gemv_grouped_rotated(const void* trellis_stack, int n_experts, void* c, const void* svh_stack,
+                                        const GemvProblem* problems, const int* n_problems, int max_problems, int max_rows, int tg,
+                                        const uint32_t* afrag, float* blocksum, int size_k, int size_n, int k_bits, int codebook,
+                                        int out_fp32, const GemvScratch& sc, int sms, cudaStream_t stream)
 {
     if (size_k % 128 != 0 || size_n % 128 != 0)
         throw std::runtime_error("exl3 grouped gemv: size_k and size_n must be multiples of 128");
     if (tg != 1 && tg != 2 && tg != 4) throw std::runtime_error("exl3 grouped gemv: token groups must be 1, 2 or 4");
     const int bu = k_bits <= 4 ? 2 : 1;
-    const int bands = size_n / 128, bgroups = (bands + bu - 1) / bu;
     int grid = sms;
     const size_t per_cta = size_t(2) * 8 * tg * bu * 128 * sizeof(float);
     if (size_t(grid) * per_cta > sc.slab_bytes) grid = int(sc.slab_bytes / per_cta);
     if (grid < 1) throw std::runtime_error("exl3 grouped gemv: split-K scratch is too small");
-    launch_pdl(k_rotate_rows, dim3(std::max(1, std::min(max_problems, 16 * sms))), dim3(256), 0, stream, "k_rotate_rows launch",
-               static_cast<const __half*>(xr), static_cast<const __half*>(suh_stack), problems, n_problems, afrag, blocksum,
-               8 * tg, size_k, max_problems, n_experts, max_rows);
     GemvArgs args;
     args.afrag = afrag;
     args.blocksum = blocksum;
@@ -1013,9 +1060,27 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
     args.n_slices = 0;
     const size_t smem = launch_bits(k_bits, codebook, tg, false, trellis_stack, n_experts, args, grid, stream);
     launch_finish(args, bu, 8 * tg, grid, codebook, stream);
-    return "k_rotate_rows + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," + std::to_string(tg) +
+    return "k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," + std::to_string(tg) +
            ",grouped> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem) +
            " + k_gemv_finish";
+}
+
+std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n_experts, void* c, const void* suh_stack,
+                                const void* svh_stack, const GemvProblem* problems, const int* n_problems, int max_problems,
+                                int max_rows, int tg, uint32_t* afrag, float* blocksum, int size_k, int size_n, int k_bits,
+                                int codebook, int out_fp32, const GemvScratch& sc, int sms, cudaStream_t stream)
+{
+    if (tg != 1 && tg != 2 && tg != 4) throw std::runtime_error("exl3 grouped gemv: token groups must be 1, 2 or 4");
+    RotateFragArgs r{};
+    r.src = static_cast<const __half*>(xr);
+    r.suh_a = static_cast<const __half*>(suh_stack);
+    r.afrag_a = afrag; r.bsum_a = blocksum;
+    r.problems = problems; r.n_problems = n_problems;
+    r.tok = 8 * tg; r.k = size_k; r.max_problems = max_problems; r.n_matrices = n_experts; r.max_rows = max_rows;
+    rotate_rows_frag(r, false, false, sms, stream);
+    return "k_rotate_rows + " + launch_gemv_grouped_rotated(trellis_stack, n_experts, c, svh_stack, problems, n_problems, max_problems,
+                                                            max_rows, tg, afrag, blocksum, size_k, size_n, k_bits, codebook, out_fp32, sc,
+                                                            sms, stream);
 }
 
 // Sliced multi-linear on the decode kernel: `n_slices` column slices of width size_n, cut from `num_had_src`

@@ -163,14 +163,15 @@ __global__ void __launch_bounds__(256) k_moe_count(const int32_t* __restrict__ k
 // `chunk` rows, experts in ascending order.  One block of 1024 threads, one expert per thread.
 // With extra_rows > 0 one more matrix (index n_local, the shared expert held behind the stack) takes
 // extra_rows rows after the routed ones: offsets[n_local + 1] then ends the table.
-__global__ void __launch_bounds__(1024) k_moe_scan(const int* __restrict__ counts, int* __restrict__ offsets,
-                                                   GemvProblem* __restrict__ problems, int* __restrict__ n_problems,
-                                                   int n_routed, int chunk, int extra_rows)
+// (scan_problems: the body, for a block of 1024 threads where thread j brings expert j's count; returns the
+// expert's first row.)
+__device__ __forceinline__ int scan_problems(int c_routed, int* __restrict__ offsets, GemvProblem* __restrict__ problems,
+                                             int* __restrict__ n_problems, int n_routed, int chunk, int extra_rows)
 {
     __shared__ int wrows[32], wprob[32];
     const int j = threadIdx.x, lane = j & 31, warp = j >> 5;
     const int n_local = n_routed + (extra_rows > 0 ? 1 : 0);
-    const int c = j < n_routed ? counts[j] : (j < n_local ? extra_rows : 0);
+    const int c = j < n_routed ? c_routed : (j < n_local ? extra_rows : 0);
     const int np = (c + chunk - 1) / chunk;
     int prow = c, pprob = np;     // inclusive warp scans
 #pragma unroll
@@ -201,6 +202,38 @@ __global__ void __launch_bounds__(1024) k_moe_scan(const int* __restrict__ count
         }
     }
     if (j == 0) { offsets[n_local] = wrows[31]; *n_problems = wprob[31]; }
+    return row0;
+}
+
+__global__ void __launch_bounds__(1024) k_moe_scan(const int* __restrict__ counts, int* __restrict__ offsets,
+                                                   GemvProblem* __restrict__ problems, int* __restrict__ n_problems,
+                                                   int n_routed, int chunk, int extra_rows)
+{
+    scan_problems(threadIdx.x < n_routed ? counts[threadIdx.x] : 0, offsets, problems, n_problems, n_routed, chunk, extra_rows);
+}
+
+// Count, scan and stable scatter in one block for a short key list (n <= kSmallKeys): thread j is local expert j
+// and walks the keys, held in shared memory, twice.  Same outputs as k_moe_count + k_moe_scan + k_moe_scatter.
+constexpr int kSmallKeys = 512;
+__global__ void __launch_bounds__(1024) k_moe_dispatch_small(const int32_t* __restrict__ keys, int n, int e0, int* __restrict__ counts,
+                                                             int* __restrict__ offsets, GemvProblem* __restrict__ problems,
+                                                             int* __restrict__ n_problems, int n_routed, int chunk, int extra_rows,
+                                                             int32_t* __restrict__ perm, int32_t* __restrict__ inv)
+{
+    __shared__ int32_t s_keys[kSmallKeys];
+    const int j = threadIdx.x;
+    for (int i = j; i < n; i += blockDim.x) s_keys[i] = keys[i];
+    __syncthreads();
+    int c = 0;
+    if (j < n_routed)
+        for (int i = 0; i < n; ++i) c += (s_keys[i] == e0 + j);
+    if (j < n_routed) counts[j] = c;
+    const int row0 = scan_problems(c, offsets, problems, n_problems, n_routed, chunk, extra_rows);
+    if (j < n_routed && c > 0) {
+        int pos = row0;
+        for (int i = 0; i < n; ++i)
+            if (s_keys[i] == e0 + j) { perm[pos] = i; inv[i] = pos; ++pos; }
+    }
 }
 
 // Stable permutation: block j walks the entries in order; the r-th entry with key e0 + j goes to
@@ -532,7 +565,7 @@ int routed_rows_hint(int T, int top_k, int n_experts)
 // Workspace carve-up of the expert stage for up to R routed rows.
 struct ExpertScratch {
     int* counts; int* offsets; int* n_problems; GemvProblem* problems;
-    uint32_t* afrag; uint32_t* afrag2; float* blocksum; __half* g; __half* u; int max_problems;
+    uint32_t* afrag; uint32_t* afrag2; float* blocksum; float* blocksum2; __half* g; __half* u; int max_problems;
     size_t bytes;
 };
 ExpertScratch carve_experts(void* base, int R, int n_local, int hidden, int inter, const ExpertPlan& plan)
@@ -547,15 +580,16 @@ ExpertScratch carve_experts(void* base, int R, int n_local, int hidden, int inte
     const size_t o_prob = take(size_t(s.max_problems) * sizeof(GemvProblem));
     // rotated activations: fragment order per problem (GEMV) or plain rows (GEMM)
     const size_t o_afrag = take(plan.tg ? size_t(s.max_problems) * (kmax / 16) * plan.tg * 256 : size_t(R) * kmax * 2);
-    // GEMM path: the rows rotated with the up projection's scales (gate and up are rotated by one launch)
-    const size_t o_afrag2 = take(plan.tg ? 256 : size_t(R) * hidden * 2);
+    // the rows rotated with the up projection's scales (gate and up are rotated by one launch)
+    const size_t o_afrag2 = take(plan.tg ? size_t(s.max_problems) * (hidden / 16) * plan.tg * 256 : size_t(R) * hidden * 2);
+    const size_t o_bsum2 = take(plan.tg ? size_t(s.max_problems) * chunk * (hidden / 128) * 4 : 256);
     const size_t o_bsum = take(plan.tg ? size_t(s.max_problems) * chunk * (kmax / 128) * 4 : 256);
     const size_t o_g = take(size_t(R) * inter * 2), o_u = take(size_t(R) * inter * 2);
     s.bytes = off;
     if (base) {
         char* b = static_cast<char*>(base);
         s.counts = (int*) (b + o_counts); s.offsets = (int*) (b + o_offsets); s.n_problems = (int*) (b + o_np);
-        s.problems = (GemvProblem*) (b + o_prob); s.afrag = (uint32_t*) (b + o_afrag); s.afrag2 = (uint32_t*) (b + o_afrag2); s.blocksum = (float*) (b + o_bsum);
+        s.problems = (GemvProblem*) (b + o_prob); s.afrag = (uint32_t*) (b + o_afrag); s.afrag2 = (uint32_t*) (b + o_afrag2); s.blocksum = (float*) (b + o_bsum); s.blocksum2 = (float*) (b + o_bsum2);
         s.g = (__half*) (b + o_g); s.u = (__half*) (b + o_u);
     }
     return s;
@@ -614,6 +648,11 @@ void dispatch(const int32_t* keys, int n, int e0, int n_local, int chunk, const 
               cudaStream_t st, int extra_rows = 0)
 {
     if (n_local + (extra_rows > 0 ? 1 : 0) > 1024) throw std::runtime_error("moe: too many local experts for the scan kernel");
+    if (n <= kSmallKeys) {
+        k_moe_dispatch_small<<<1, 1024, 0, st>>>(keys, n, e0, s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows, perm, inv);
+        cuda_ok(cudaGetLastError(), "k_moe_dispatch_small launch");
+        return;
+    }
     k_moe_count<<<n_local, 256, 0, st>>>(keys, n, e0, s.counts);
     cuda_ok(cudaGetLastError(), "k_moe_count launch");
     k_moe_scan<<<1, 1024, 0, st>>>(s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows);
@@ -636,11 +675,9 @@ std::string experts(const berth_moe_weights* w, const void* gate_t, const void* 
                     int sms, cudaStream_t st, const int* rows_dev = nullptr, const RowSource& src = RowSource{})
 {
     const int H = w->hidden, I = w->inter;
-    // the activation between the projections: over R rows, or over the device-side count (at most max_rows)
-    auto act = [&] {
-        if (rows_dev) silu_mul_rows(s.g, s.u, s.g, rows_dev, max_rows, I, st);
-        else if (berth_ops_silu_mul(s.g, s.u, s.g, int64_t(R) * I, 0.0f, st) != 0) throw std::runtime_error(berth_ops_last_error());
-    };
+    // (the activation between the projections runs inside the rotation of the down projection, over the rows of the
+    // problem table; neither row count is needed here)
+    (void) R; (void) rows_dev;
     if (plan.nsub) {
         // one rotation launch for gate and up (the row is read once), the activation inside the rotation for down
         RotateArgs r{};
@@ -666,16 +703,29 @@ std::string experts(const berth_moe_weights* w, const void* gate_t, const void* 
                                        H, w->k_bits, w->codebook, 0, sc.status, sms, st);
         return "k_rotate_rows_plain<gate+up> + 2 x " + d + " + k_rotate_rows_plain<silu> + 1 x (same, down)";
     }
-    if (src.perm) throw std::runtime_error("moe experts: gathered input rows are taken on the tensor-core path only");
     const int tg = plan.tg;
-    std::string d = launch_gemv_grouped(xr, gate_t, n_local, s.g, gsuh, gsvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag,
-                                        s.blocksum, H, I, w->k_bits, w->codebook, 0, sc, sms, st);
-    launch_gemv_grouped(xr, up_t, n_local, s.u, usuh, usvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag, s.blocksum, H, I,
-                        w->k_bits, w->codebook, 0, sc, sms, st);
-    act();
-    launch_gemv_grouped(s.g, down_t, n_local, yr, dsuh, dsvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag, s.blocksum, I, H,
-                        w->k_bits, w->codebook, 0, sc, sms, st);
-    return d;
+    RotateFragArgs r{};
+    r.src = static_cast<const __half*>(xr);
+    r.perm = src.perm; r.div = src.div; r.n_perm = src.n_perm;
+    r.suh_a = static_cast<const __half*>(gsuh); r.suh_b = static_cast<const __half*>(usuh);
+    r.afrag_a = s.afrag; r.afrag_b = s.afrag2; r.bsum_a = s.blocksum; r.bsum_b = s.blocksum2;
+    r.problems = s.problems; r.n_problems = s.n_problems;
+    r.tok = 8 * tg; r.k = H; r.max_problems = s.max_problems; r.n_matrices = n_local; r.max_rows = max_rows;
+    rotate_rows_frag(r, true, false, sms, st);
+    std::string d = launch_gemv_grouped_rotated(gate_t, n_local, s.g, gsvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag,
+                                                s.blocksum, H, I, w->k_bits, w->codebook, 0, sc, sms, st);
+    launch_gemv_grouped_rotated(up_t, n_local, s.u, usvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag2, s.blocksum2, H, I,
+                                w->k_bits, w->codebook, 0, sc, sms, st);
+    RotateFragArgs rd{};
+    rd.src = s.g; rd.src_u = s.u;
+    rd.suh_a = static_cast<const __half*>(dsuh);
+    rd.afrag_a = s.afrag; rd.bsum_a = s.blocksum;
+    rd.problems = s.problems; rd.n_problems = s.n_problems;
+    rd.tok = 8 * tg; rd.k = I; rd.max_problems = s.max_problems; rd.n_matrices = n_local; rd.max_rows = max_rows;
+    rotate_rows_frag(rd, false, true, sms, st);
+    launch_gemv_grouped_rotated(down_t, n_local, yr, dsvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag, s.blocksum, I, H,
+                                w->k_bits, w->codebook, 0, sc, sms, st);
+    return "k_rotate_rows<gate+up> + 2 x (" + d + ") + k_rotate_rows<silu> + 1 x (same, down)";
 }
 
 }  // namespace
@@ -1060,7 +1110,7 @@ extern "C" size_t berth_moe_workspace_bytes(int T, int hidden, int inter, int sh
     size_t total = 0;
     total += align256(size_t(T) * n_experts * 4);            // logits
     total += 2 * align256(size_t(R) * 4);                    // perm, inv
-    total += 2 * align256(size_t(R + T) * hidden * 2);       // xr, yr
+    total += align256(size_t(R + T) * hidden * 2);           // yr
     total += es.bytes;
     if (shared_inter > 0) {
         total += 3 * align256(size_t(T) * shared_inter * 2);                 // shared gate, up outputs + rotated
@@ -1101,25 +1151,17 @@ extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T,
         // run as matrix E of the grouped launches: its rows are the layer's own tokens, appended to the routed rows.
         const bool fused_shared = shared_behind_stacks(w);
         const int RT = fused_shared ? R + T : R, NM = fused_shared ? E + 1 : E;
-        __half* xr = (__half*) take(size_t(R + T) * H * 2);
         __half* yr = (__half*) take(size_t(R + T) * H * 2);
         ExpertScratch es = carve_experts(b, RT, NM, H, I, plan);
         b += carve_experts(nullptr, R + T, E + 1, H, I, plan).bytes;
 
         router_topk(x, w->w_router, w->router_bias, topk_idx, topk_w, logits, T, H, E, K, cs);
         dispatch(topk_idx, R, 0, E, plan.chunk, es, perm, inv, cs, fused_shared ? T : 0);
+        // the rotation kernel of gate and up gathers the routed rows (and the shared expert's) from x itself
         RowSource rows_from{};
-        if (plan.nsub) {
-            // tensor-core path: the rotation kernel gathers the rows from x itself
-            rows_from.perm = perm; rows_from.div = K; rows_from.n_perm = R;
-        } else {
-            k_moe_gather_rows<<<std::min(R, 148 * 8), 256, 0, cs>>>((const __half*) x, perm, es.offsets + E, K, xr, H);
-            cuda_ok(cudaGetLastError(), "k_moe_gather_rows launch");
-            if (fused_shared)
-                cuda_ok(cudaMemcpyAsync(xr + size_t(R) * H, x, size_t(T) * H * 2, cudaMemcpyDeviceToDevice, cs), "moe layer: shared rows copy");
-        }
+        rows_from.perm = perm; rows_from.div = K; rows_from.n_perm = R;
         st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
-                            w->down_suh, w->down_svh, NM, plan.nsub ? x : xr, yr, RT, RT, plan, es, sc, info.sms, cs, nullptr, rows_from);
+                            w->down_suh, w->down_svh, NM, x, yr, RT, RT, plan, es, sc, info.sms, cs, nullptr, rows_from);
 
         __half* ysh = fused_shared ? yr + size_t(R) * H : nullptr;
         if (SI > 0 && !fused_shared) {
@@ -1136,7 +1178,7 @@ extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T,
         }
         k_moe_combine<<<T, 256, 0, cs>>>(yr, inv, topk_w, ysh, (float*) out, H, K);
         cuda_ok(cudaGetLastError(), "k_moe_combine launch");
-        st.launch = "k_moe_router_logits + k_moe_topk + k_moe_count/scan/scatter + k_moe_gather_rows + 3 x (" + st.launch +
-                    ") + k_silu_mul + k_moe_combine" + (fused_shared ? " [shared expert as matrix E of the grouped launches]" : "");
+        st.launch = std::string("k_moe_router_logits + k_moe_topk + ") + (R <= kSmallKeys ? "k_moe_dispatch_small" : "k_moe_count/scan/scatter") +
+                    " + " + st.launch + " + k_moe_combine" + (fused_shared ? " [shared expert as matrix E of the grouped launches]" : "");
     });
 }
