@@ -846,6 +846,8 @@ template <int MODE>
 __global__ void __launch_bounds__(256) k_rotate_rows_plain(const RotateArgs a)
 {
     __shared__ int s_row0[kRotTable];
+    pdl_trigger();   // launched as a programmatic dependent; the problem table comes from the preceding kernels
+    pdl_wait();
     const int lane = threadIdx.x & 31, k = a.k;
     const int nprob = min(max(__ldg(a.n_problems), 0), a.max_problems);
     if (nprob < 1) return;
@@ -947,11 +949,11 @@ void rotate_rows_grouped(const RotateArgs& a, bool dual, bool silu, int sms, cud
     const dim3 grid(std::max(1, std::min((a.max_rows + 7) / 8, 8 * sms)));
     const int mode = (dual ? kRotDual : 0) | (a.perm ? kRotGather : 0) | (silu ? kRotSilu : 0);
     switch (mode) {
-        case 0: k_rotate_rows_plain<0><<<grid, 256, 0, stream>>>(a); break;
-        case kRotDual: k_rotate_rows_plain<kRotDual><<<grid, 256, 0, stream>>>(a); break;
-        case kRotGather: k_rotate_rows_plain<kRotGather><<<grid, 256, 0, stream>>>(a); break;
-        case kRotDual | kRotGather: k_rotate_rows_plain<kRotDual | kRotGather><<<grid, 256, 0, stream>>>(a); break;
-        default: k_rotate_rows_plain<kRotSilu><<<grid, 256, 0, stream>>>(a); break;
+        case 0: launch_pdl(k_rotate_rows_plain<0>, grid, dim3(256), 0, stream, "k_rotate_rows_plain launch", a); break;
+        case kRotDual: launch_pdl(k_rotate_rows_plain<kRotDual>, grid, dim3(256), 0, stream, "k_rotate_rows_plain launch", a); break;
+        case kRotGather: launch_pdl(k_rotate_rows_plain<kRotGather>, grid, dim3(256), 0, stream, "k_rotate_rows_plain launch", a); break;
+        case kRotDual | kRotGather: launch_pdl(k_rotate_rows_plain<kRotDual | kRotGather>, grid, dim3(256), 0, stream, "k_rotate_rows_plain launch", a); break;
+        default: launch_pdl(k_rotate_rows_plain<kRotSilu>, grid, dim3(256), 0, stream, "k_rotate_rows_plain launch", a); break;
     }
     cuda_ok(cudaGetLastError(), "k_rotate_rows_plain launch");
 }

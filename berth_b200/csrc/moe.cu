@@ -31,14 +31,17 @@ __device__ __forceinline__ float chunk_tree(const float* base, int c)
     if constexpr (S == 32) return base[c * (kRouterTok * 33)];
     else return __fadd_rn(chunk_tree<2 * S>(base, c), chunk_tree<2 * S>(base, c + S));
 }
-constexpr int kRouterWarps = 16;   // each warp accumulates two of the 32 chunks, one after the other
 // Dynamic shared memory: the token tile as fp32 [kRouterTok][H], then the chunk sums [32][kRouterTok][33].
-// 512 threads and ~97 KiB per block, so that two blocks share an SM and one block's load and reduction
-// phases overlap the other's arithmetic.
-__global__ void __launch_bounds__(kRouterWarps * 32, 2) k_moe_router_logits(const __half* __restrict__ x, const __half* __restrict__ w,
+// WARPS = 16: each warp accumulates two of the 32 chunks, one after the other; 512 threads and ~97 KiB per block,
+// so that two blocks share an SM and one block's load and reduction phases overlap the other's arithmetic.
+// WARPS = 32: one chunk per warp, for launches of fewer blocks than SMs, which the latency of a chunk's loads bounds.
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 1) k_moe_router_logits(const __half* __restrict__ x, const __half* __restrict__ w,
                                                                             const float* __restrict__ bias, float* __restrict__ logits,
                                                                             int T, int H, int E)
 {
+    pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
+    pdl_wait();
     extern __shared__ __align__(16) float rsm[];
     float* xs = rsm;                                                    // [kRouterTok][H]
     float (*part)[kRouterTok][33] = reinterpret_cast<float (*)[kRouterTok][33]>(rsm + kRouterTok * H);
@@ -46,7 +49,7 @@ __global__ void __launch_bounds__(kRouterWarps * 32, 2) k_moe_router_logits(cons
     const int e = blockIdx.x * 32 + el, t0 = blockIdx.y * kRouterTok;
     const int chunk = H / 32;
     // the tile's activations, converted once (rows past T repeat the last token; their sums are never stored)
-    for (int i = threadIdx.x * 2; i < kRouterTok * H; i += kRouterWarps * 64) {
+    for (int i = threadIdx.x * 2; i < kRouterTok * H; i += WARPS * 64) {
         const int tt = i / H, h = i - tt * H;
         const __half2 v = *reinterpret_cast<const __half2*>(x + size_t(min(t0 + tt, T - 1)) * H + h);
         xs[i] = __low2float(v);
@@ -54,7 +57,7 @@ __global__ void __launch_bounds__(kRouterWarps * 32, 2) k_moe_router_logits(cons
     }
     __syncthreads();
     const int vec_end = (chunk & 3) == 0 ? chunk : 0;   // quads are 16-byte aligned only if the chunk is a multiple of 4
-    for (int j = wq; j < 32; j += kRouterWarps) {
+    for (int j = wq; j < 32; j += WARPS) {
         const __half* wr = w + size_t(j) * chunk * E + e;
         const float* xj = xs + j * chunk;
         float acc[kRouterTok];
@@ -105,6 +108,8 @@ __global__ void __launch_bounds__(kRouterWarps * 32, 2) k_moe_router_logits(cons
 __global__ void __launch_bounds__(128) k_moe_topk(const float* __restrict__ logits, int32_t* __restrict__ topk_idx,
                                                   float* __restrict__ topk_w, int T, int E, int k)
 {
+    pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
+    pdl_wait();
     const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= T) return;
     const float* l = logits + size_t(t) * E;
@@ -144,6 +149,8 @@ __global__ void __launch_bounds__(128) k_moe_topk(const float* __restrict__ logi
 // counts[j] = number of entries whose key is e0 + j.  One block per local expert.
 __global__ void __launch_bounds__(256) k_moe_count(const int32_t* __restrict__ keys, int n, int e0, int* __restrict__ counts)
 {
+    pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
+    pdl_wait();
     const int e = e0 + blockIdx.x;
     int c = 0;
     for (int i = threadIdx.x; i < n; i += 256) c += (keys[i] == e);
@@ -209,30 +216,56 @@ __global__ void __launch_bounds__(1024) k_moe_scan(const int* __restrict__ count
                                                    GemvProblem* __restrict__ problems, int* __restrict__ n_problems,
                                                    int n_routed, int chunk, int extra_rows)
 {
+    pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
+    pdl_wait();
     scan_problems(threadIdx.x < n_routed ? counts[threadIdx.x] : 0, offsets, problems, n_problems, n_routed, chunk, extra_rows);
 }
 
-// Count, scan and stable scatter in one block for a short key list (n <= kSmallKeys): thread j is local expert j
-// and walks the keys, held in shared memory, twice.  Same outputs as k_moe_count + k_moe_scan + k_moe_scatter.
-constexpr int kSmallKeys = 512;
+// Count, scan and stable scatter in one block for a short key list (n <= kSmallKeys).  Warp 0 walks the keys 32 at
+// a time: lanes with the same key find one another with match.any, an entry's rank within its expert is the
+// expert's running count plus the equal keys in lower lanes.  Then thread j scans expert j's count and every entry
+// goes to its expert's first row plus its rank.  Same outputs as k_moe_count + k_moe_scan + k_moe_scatter.
+constexpr int kSmallKeys = 2048;
 __global__ void __launch_bounds__(1024) k_moe_dispatch_small(const int32_t* __restrict__ keys, int n, int e0, int* __restrict__ counts,
                                                              int* __restrict__ offsets, GemvProblem* __restrict__ problems,
                                                              int* __restrict__ n_problems, int n_routed, int chunk, int extra_rows,
                                                              int32_t* __restrict__ perm, int32_t* __restrict__ inv)
 {
-    __shared__ int32_t s_keys[kSmallKeys];
-    const int j = threadIdx.x;
-    for (int i = j; i < n; i += blockDim.x) s_keys[i] = keys[i];
+    pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
+    pdl_wait();
+    __shared__ int s_slot[kSmallKeys], s_rank[kSmallKeys], s_cnt[1025], s_row0[1024];
+    const int j = threadIdx.x, lane = j & 31;
+    for (int i = j; i < n; i += blockDim.x) {
+        const int key = keys[i] - e0;
+        s_slot[i] = (key >= 0 && key < n_routed) ? key : n_routed;   // slot n_routed collects the keys of other ranks
+    }
+    if (j <= n_routed) s_cnt[j] = 0;
     __syncthreads();
-    int c = 0;
-    if (j < n_routed)
-        for (int i = 0; i < n; ++i) c += (s_keys[i] == e0 + j);
+    if (j < 32) {
+        for (int base = 0; base < n; base += 32) {
+            const int i = base + lane;
+            const int slot = i < n ? s_slot[i] : n_routed;
+            const unsigned same = __match_any_sync(dq::kFull, slot);
+            const int before = s_cnt[slot];
+            __syncwarp();
+            if (lane == __ffs(same) - 1) s_cnt[slot] = before + __popc(same);
+            __syncwarp();
+            if (i < n) s_rank[i] = before + __popc(same & ((1u << lane) - 1u));
+        }
+    }
+    __syncthreads();
+    const int c = j < n_routed ? s_cnt[j] : 0;
     if (j < n_routed) counts[j] = c;
     const int row0 = scan_problems(c, offsets, problems, n_problems, n_routed, chunk, extra_rows);
-    if (j < n_routed && c > 0) {
-        int pos = row0;
-        for (int i = 0; i < n; ++i)
-            if (s_keys[i] == e0 + j) { perm[pos] = i; inv[i] = pos; ++pos; }
+    if (j < n_routed) s_row0[j] = row0;
+    __syncthreads();
+    for (int i = j; i < n; i += blockDim.x) {
+        const int slot = s_slot[i];
+        if (slot < n_routed) {
+            const int pos = s_row0[slot] + s_rank[i];
+            perm[pos] = i;
+            inv[i] = pos;
+        }
     }
 }
 
@@ -242,6 +275,8 @@ __global__ void __launch_bounds__(256) k_moe_scatter(const int32_t* __restrict__
                                                      const int* __restrict__ offsets, int32_t* __restrict__ perm,
                                                      int32_t* __restrict__ inv)
 {
+    pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
+    pdl_wait();
     const int e = e0 + blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     __shared__ int wsum[8];
     int running = offsets[blockIdx.x];
@@ -272,6 +307,8 @@ __global__ void __launch_bounds__(256) k_moe_scatter(const int32_t* __restrict__
 __global__ void __launch_bounds__(256) k_moe_gather_rows(const __half* __restrict__ x, const int32_t* __restrict__ perm,
                                                          const int* __restrict__ n_rows, int div, __half* __restrict__ xr, int H)
 {
+    pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
+    pdl_wait();
     const int R = __ldg(n_rows);
     for (int pos = blockIdx.x; pos < R; pos += gridDim.x) {
         const uint4* src = reinterpret_cast<const uint4*>(x + size_t(perm[pos] / div) * H);
@@ -284,6 +321,8 @@ __global__ void __launch_bounds__(256) k_moe_gather_rows(const __half* __restric
 __global__ void __launch_bounds__(256) k_moe_gather_n(const __half* __restrict__ x, const int32_t* __restrict__ index, int n,
                                                       int div, __half* __restrict__ dst, int H)
 {
+    pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
+    pdl_wait();
     for (int pos = blockIdx.x; pos < n; pos += gridDim.x) {
         const uint4* src = reinterpret_cast<const uint4*>(x + size_t(index[pos] / div) * H);
         uint4* d = reinterpret_cast<uint4*>(dst + size_t(pos) * H);
@@ -296,6 +335,8 @@ __global__ void __launch_bounds__(256) k_moe_combine(const __half* __restrict__ 
                                                      const float* __restrict__ topk_w, const __half* __restrict__ ysh,
                                                      float* __restrict__ out, int H, int k)
 {
+    pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
+    pdl_wait();
     const int t = blockIdx.x;
     for (int h = threadIdx.x * 2; h < H; h += 512) {
         float a0 = 0.f, a1 = 0.f;
@@ -633,13 +674,19 @@ void router_topk(const void* x, const void* w_router, const float* bias, int32_t
     static bool attr_set[kMaxDevices] = {};
     const int dev = current_device();
     if (!attr_set[dev]) {
-        cuda_ok(cudaFuncSetAttribute(k_moe_router_logits, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "router smem attribute");
+        cuda_ok(cudaFuncSetAttribute(k_moe_router_logits<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "router smem attribute");
+        cuda_ok(cudaFuncSetAttribute(k_moe_router_logits<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "router smem attribute");
         attr_set[dev] = true;
     }
-    k_moe_router_logits<<<dim3(E / 32, (T + kRouterTok - 1) / kRouterTok), kRouterWarps * 32, smem, st>>>((const __half*) x, (const __half*) w_router,
-                                                                                           bias, logits, T, H, E);
+    const dim3 rgrid(E / 32, (T + kRouterTok - 1) / kRouterTok);
+    if (int(rgrid.x * rgrid.y) <= device_info(dev).sms)
+        launch_pdl(k_moe_router_logits<32>, rgrid, dim3(32 * 32), smem, st, "k_moe_router_logits launch", (const __half*) x,
+                   (const __half*) w_router, bias, logits, T, H, E);
+    else
+        launch_pdl(k_moe_router_logits<16>, rgrid, dim3(16 * 32), smem, st, "k_moe_router_logits launch", (const __half*) x,
+                   (const __half*) w_router, bias, logits, T, H, E);
     cuda_ok(cudaGetLastError(), "k_moe_router_logits launch");
-    k_moe_topk<<<(T + 3) / 4, 128, 0, st>>>(logits, topk_idx, topk_w, T, E, k);
+    launch_pdl(k_moe_topk, dim3((T + 3) / 4), dim3(128), 0, st, "k_moe_topk launch", logits, topk_idx, topk_w, T, E, k);
     cuda_ok(cudaGetLastError(), "k_moe_topk launch");
 }
 
@@ -649,15 +696,15 @@ void dispatch(const int32_t* keys, int n, int e0, int n_local, int chunk, const 
 {
     if (n_local + (extra_rows > 0 ? 1 : 0) > 1024) throw std::runtime_error("moe: too many local experts for the scan kernel");
     if (n <= kSmallKeys) {
-        k_moe_dispatch_small<<<1, 1024, 0, st>>>(keys, n, e0, s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows, perm, inv);
+        launch_pdl(k_moe_dispatch_small, dim3(1), dim3(1024), 0, st, "k_moe_dispatch_small launch", keys, n, e0, s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows, perm, inv);
         cuda_ok(cudaGetLastError(), "k_moe_dispatch_small launch");
         return;
     }
-    k_moe_count<<<n_local, 256, 0, st>>>(keys, n, e0, s.counts);
+    launch_pdl(k_moe_count, dim3(n_local), dim3(256), 0, st, "k_moe_count launch", keys, n, e0, s.counts);
     cuda_ok(cudaGetLastError(), "k_moe_count launch");
-    k_moe_scan<<<1, 1024, 0, st>>>(s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows);
+    launch_pdl(k_moe_scan, dim3(1), dim3(1024), 0, st, "k_moe_scan launch", s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows);
     cuda_ok(cudaGetLastError(), "k_moe_scan launch");
-    k_moe_scatter<<<n_local, 256, 0, st>>>(keys, n, e0, s.offsets, perm, inv);
+    launch_pdl(k_moe_scatter, dim3(n_local), dim3(256), 0, st, "k_moe_scatter launch", keys, n, e0, s.offsets, perm, inv);
     cuda_ok(cudaGetLastError(), "k_moe_scatter launch");
 }
 
@@ -874,7 +921,7 @@ extern "C" int berth_moe_ep_send(const void* x, int T, const void* w_router, con
         es.problems = (GemvProblem*) take((size_t(R) / 8 + n_experts + 1) * sizeof(GemvProblem));
         router_topk(x, w_router, router_bias, topk_idx, topk_w, logits, T, hidden, n_experts, top_k, cs);
         dispatch(topk_idx, R, 0, n_experts, 8, es, perm, inv, cs);
-        k_moe_gather_rows<<<std::min(R, 148 * 8), 256, 0, cs>>>((const __half*) x, perm, es.offsets + n_experts, top_k, (__half*) send_rows, hidden);
+        launch_pdl(k_moe_gather_rows, dim3(std::min(R, 148 * 8)), dim3(256), 0, cs, "k_moe_gather_rows launch", (const __half*) x, perm, es.offsets + n_experts, top_k, (__half*) send_rows, hidden);
         cuda_ok(cudaGetLastError(), "k_moe_gather_rows launch");
         st.launch = "k_moe_router_logits + k_moe_topk + k_moe_count/scan/scatter + k_moe_gather_rows";
     });
@@ -932,14 +979,14 @@ extern "C" int berth_moe_ep_experts(const berth_moe_weights* w, const void* recv
         }
         dispatch(keys, n_rows, 0, NL, plan.chunk, es, perm, inv, cs, TS);
         if (n_rows > 0) {
-            k_moe_gather_rows<<<std::min(n_rows, 148 * 8), 256, 0, cs>>>((const __half*) recv_rows, perm, es.offsets + NL, 1, xr, H);
+            launch_pdl(k_moe_gather_rows, dim3(std::min(n_rows, 148 * 8)), dim3(256), 0, cs, "k_moe_gather_rows launch", (const __half*) recv_rows, perm, es.offsets + NL, 1, xr, H);
             cuda_ok(cudaGetLastError(), "k_moe_gather_rows launch");
         }
         if (TS) cuda_ok(cudaMemcpyAsync(xr + size_t(n_rows) * H, x_local, size_t(TS) * H * 2, cudaMemcpyDeviceToDevice, cs), "moe ep experts: shared rows copy");
         st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
                             w->down_suh, w->down_svh, NM, xr, yr, RT, RT, plan, es, gemv_workspace(device), info.sms, cs);
         if (n_rows > 0) {
-            k_moe_gather_n<<<std::min(n_rows, 148 * 8), 256, 0, cs>>>(yr, inv, n_rows, 1, (__half*) back, H);
+            launch_pdl(k_moe_gather_n, dim3(std::min(n_rows, 148 * 8)), dim3(256), 0, cs, "k_moe_gather_n launch", yr, inv, n_rows, 1, (__half*) back, H);
             cuda_ok(cudaGetLastError(), "k_moe_gather launch");
         }
         if (TS) cuda_ok(cudaMemcpyAsync(ysh, yr + size_t(n_rows) * H, size_t(TS) * H * 2, cudaMemcpyDeviceToDevice, cs), "moe ep experts: shared output copy");
@@ -1081,7 +1128,7 @@ extern "C" int berth_moe_p2p_experts(const berth_moe_weights* w, const void* x_l
         ExpertScratch es = carve_experts(b, max_rows, NM, H, I, plan);
         es.counts = sw.counts_local;
         __half* xr = static_cast<__half*>(pr.p[rank]);
-        k_moe_scan<<<1, 1024, 0, cs>>>(es.counts, es.offsets, es.problems, es.n_problems, NL, plan.chunk, TS);
+        launch_pdl(k_moe_scan, dim3(1), dim3(1024), 0, cs, "k_moe_scan launch", es.counts, es.offsets, es.problems, es.n_problems, NL, plan.chunk, TS);
         cuda_ok(cudaGetLastError(), "k_moe_scan launch");
         if (TS) {
             k_rows_to_offset<<<std::min(TS, 148 * 8), 256, 0, cs>>>((const __half*) x_local, xr, es.offsets + NL, TS, H, max_rows);
@@ -1176,7 +1223,7 @@ extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T,
             if (berth_ops_silu_mul(sg, su, sg, int64_t(T) * SI, 0.0f, cs) != 0) throw std::runtime_error(berth_ops_last_error());
             linear_rows(sg, w->sh_down_trellis, ysh, w->sh_down_suh, sr, w->sh_down_svh, T, SI, H, w->k_bits, w->codebook, 0, cs);
         }
-        k_moe_combine<<<T, 256, 0, cs>>>(yr, inv, topk_w, ysh, (float*) out, H, K);
+        launch_pdl(k_moe_combine, dim3(T), dim3(256), 0, cs, "k_moe_combine launch", yr, inv, topk_w, ysh, (float*) out, H, K);
         cuda_ok(cudaGetLastError(), "k_moe_combine launch");
         st.launch = std::string("k_moe_router_logits + k_moe_topk + ") + (R <= kSmallKeys ? "k_moe_dispatch_small" : "k_moe_count/scan/scatter") +
                     " + " + st.launch + " + k_moe_combine" + (fused_shared ? " [shared expert as matrix E of the grouped launches]" : "");
