@@ -651,14 +651,15 @@ bool shared_behind_stacks(const berth_moe_weights* w)
            w->sh_down_svh == at(w->down_svh, E * H * 2);
 }
 
-void check_moe_shapes(const berth_moe_weights* w, int T)
+// `routes`: the caller also runs the router over w->n_experts (an expert-parallel rank's block need not be a multiple of 32).
+void check_moe_shapes(const berth_moe_weights* w, int T, bool routes = false)
 {
     if (!w) throw std::runtime_error("moe: null weights");
     if (T < 1) throw std::runtime_error("moe: T must be positive");
     if (w->hidden % 128 || w->inter % 128 || w->hidden < 128 || w->inter < 128)
         throw std::runtime_error("moe: hidden and inter must be multiples of 128");
     if (w->shared_inter % 128) throw std::runtime_error("moe: shared_inter must be a multiple of 128");
-    if (w->n_experts < 1 || w->n_experts > 1024 || w->n_experts % 32)
+    if (w->n_experts < 1 || w->n_experts > 1024 || (routes && w->n_experts % 32))
         throw std::runtime_error("moe: n_experts must be a multiple of 32 up to 1024");
     if (w->top_k < 1 || w->top_k > 32 || w->top_k > w->n_experts) throw std::runtime_error("moe: top_k must be in 1..=32");
     if (w->hidden % 32) throw std::runtime_error("moe: hidden must be a multiple of 32");
@@ -1171,7 +1172,7 @@ extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T,
 {
     CallState& st = moe_state();
     return guarded(st, [&] {
-        check_moe_shapes(w, T);
+        check_moe_shapes(w, T, true);
         if (!x || !out || !topk_idx || !topk_w || !workspace) throw std::runtime_error("moe layer: null device pointer");
         if (!w->w_router || !w->gate_trellis || !w->up_trellis || !w->down_trellis || !w->gate_suh || !w->gate_svh ||
             !w->up_suh || !w->up_svh || !w->down_suh || !w->down_svh)
