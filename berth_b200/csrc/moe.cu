@@ -269,29 +269,31 @@ __global__ void __launch_bounds__(1024) k_moe_dispatch_small(const int32_t* __re
     }
 }
 
-// Stable permutation: block j walks the entries in order; the r-th entry with key e0 + j goes to
+// Stable permutation: block j walks the entries in order, 1024 at a time; the r-th entry with key e0 + j goes to
 // position offsets[j] + r.  perm[pos] = entry, inv[entry] = pos.
-__global__ void __launch_bounds__(256) k_moe_scatter(const int32_t* __restrict__ keys, int n, int e0,
-                                                     const int* __restrict__ offsets, int32_t* __restrict__ perm,
-                                                     int32_t* __restrict__ inv)
+__global__ void __launch_bounds__(1024) k_moe_scatter(const int32_t* __restrict__ keys, int n, int e0,
+                                                      const int* __restrict__ offsets, int32_t* __restrict__ perm,
+                                                      int32_t* __restrict__ inv)
 {
     pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
     pdl_wait();
     const int e = e0 + blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    __shared__ int wsum[8];
+    __shared__ int wsum[2][32];   // per-warp hit counts, double buffered: one barrier per pass
     int running = offsets[blockIdx.x];
-    for (int base = 0; base < n; base += 256) {
+    int buf = 0;
+    for (int base = 0; base < n; base += 1024, buf ^= 1) {
         const int i = base + threadIdx.x;
         const bool hit = i < n && keys[i] == e;
         const unsigned ballot = __ballot_sync(dq::kFull, hit);
-        if (lane == 0) wsum[warp] = __popc(ballot);
+        if (lane == 0) wsum[buf][warp] = __popc(ballot);
         __syncthreads();
-        int before = 0, total = 0;
+        // every warp reduces the 32 counts: lanes below the warp's index give the hits before it
+        const int c = wsum[buf][lane];
+        int before = lane < warp ? c : 0, total = c;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            const int c = wsum[w];
-            before += (w < warp) ? c : 0;
-            total += c;
+        for (int off = 16; off >= 1; off >>= 1) {
+            before += __shfl_xor_sync(dq::kFull, before, off);
+            total += __shfl_xor_sync(dq::kFull, total, off);
         }
         if (hit) {
             const int pos = running + before + __popc(ballot & ((1u << lane) - 1u));
@@ -299,7 +301,6 @@ __global__ void __launch_bounds__(256) k_moe_scatter(const int32_t* __restrict__
             inv[i] = pos;
         }
         running += total;
-        __syncthreads();
     }
 }
 
@@ -705,7 +706,7 @@ void dispatch(const int32_t* keys, int n, int e0, int n_local, int chunk, const 
     cuda_ok(cudaGetLastError(), "k_moe_count launch");
     launch_pdl(k_moe_scan, dim3(1), dim3(1024), 0, st, "k_moe_scan launch", s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows);
     cuda_ok(cudaGetLastError(), "k_moe_scan launch");
-    launch_pdl(k_moe_scatter, dim3(n_local), dim3(256), 0, st, "k_moe_scatter launch", keys, n, e0, s.offsets, perm, inv);
+    launch_pdl(k_moe_scatter, dim3(n_local), dim3(1024), 0, st, "k_moe_scatter launch", keys, n, e0, s.offsets, perm, inv);
     cuda_ok(cudaGetLastError(), "k_moe_scatter launch");
 }
 
