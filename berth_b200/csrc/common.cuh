@@ -171,6 +171,7 @@ struct RotateFragArgs {
     const GemvProblem* problems;
     const int* n_problems;
     int tok, k, max_problems, n_matrices, max_rows;   // tok = rows per problem: 8, 16 or 32
+    int pair;              // dual mode: 1 = the second output is problem (index + problem count) of afrag_a / bsum_a (doubled table)
 };
 void rotate_rows_frag(const RotateFragArgs& a, bool dual, bool silu, int sms, cudaStream_t stream);
 // launch_gemv_grouped without its rotation: afrag / blocksum already hold the rotated rows.

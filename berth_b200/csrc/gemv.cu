@@ -920,8 +920,13 @@ __global__ void __launch_bounds__(256) k_rotate_rows(const RotateFragArgs a)
             *reinterpret_cast<uint2*>(a.afrag_a + w) = o;
             if constexpr (MODE & kFragDual) {
                 const uint2 o2 = rotate_bits<true>(x, __ldg(reinterpret_cast<const uint2*>(a.suh_b + so + kcol)), lane, sx);
-                if (lane == 0) a.bsum_b[bs] = sx;
-                *reinterpret_cast<uint2*>(a.afrag_b + w) = o2;
+                if (a.pair) {   // the same arrays, problem pi + nprob
+                    if (lane == 0) a.bsum_a[bs + size_t(nprob) * a.tok * kblocks] = sx;
+                    *reinterpret_cast<uint2*>(a.afrag_a + w + size_t(nprob) * (k >> 4) * tgs * 64) = o2;
+                } else {
+                    if (lane == 0) a.bsum_b[bs] = sx;
+                    *reinterpret_cast<uint2*>(a.afrag_b + w) = o2;
+                }
             }
         }
     }
@@ -1012,7 +1017,7 @@ void rotate_rows_frag(const RotateFragArgs& a, bool dual, bool silu, int sms, cu
 {
     if (a.k % 128 != 0) throw std::runtime_error("exl3 grouped gemv: size_k must be a multiple of 128");
     if (a.tok != 8 && a.tok != 16 && a.tok != 32) throw std::runtime_error("exl3 grouped gemv: token groups must be 1, 2 or 4");
-    if (!a.src || !a.suh_a || !a.afrag_a || !a.bsum_a || (dual && (!a.suh_b || !a.afrag_b || !a.bsum_b)) || (silu && !a.src_u))
+    if (!a.src || !a.suh_a || !a.afrag_a || !a.bsum_a || (dual && (!a.suh_b || (!a.pair && (!a.afrag_b || !a.bsum_b)))) || (silu && !a.src_u))
         throw std::runtime_error("exl3 grouped gemv: null rotation pointer");
     if (silu && (dual || a.perm)) throw std::runtime_error("exl3 grouped gemv: the silu rotation takes one plain input");
     const dim3 grid(std::max(1, std::min(a.max_problems, 16 * sms)));

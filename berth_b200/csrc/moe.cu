@@ -172,8 +172,12 @@ __global__ void __launch_bounds__(256) k_moe_count(const int32_t* __restrict__ k
 // extra_rows rows after the routed ones: offsets[n_local + 1] then ends the table.
 // (scan_problems: the body, for a block of 1024 threads where thread j brings expert j's count; returns the
 // expert's first row.)
+// pair_rows > 0: the table is written twice, the second copy behind the first with every matrix index raised by
+// pair_matrices and every first row by pair_rows, and n_problems[1] = the doubled count: one grouped launch over the
+// doubled table then runs two stacks that lie behind one another (gate and up) on the same rows.
 __device__ __forceinline__ int scan_problems(int c_routed, int* __restrict__ offsets, GemvProblem* __restrict__ problems,
-                                             int* __restrict__ n_problems, int n_routed, int chunk, int extra_rows)
+                                             int* __restrict__ n_problems, int n_routed, int chunk, int extra_rows, int pair_rows,
+                                             int pair_matrices)
 {
     __shared__ int wrows[32], wprob[32];
     const int j = threadIdx.x, lane = j & 31, warp = j >> 5;
@@ -206,19 +210,28 @@ __device__ __forceinline__ int scan_problems(int c_routed, int* __restrict__ off
             GemvProblem pr;
             pr.z = j; pr.row0 = row0 + i * chunk; pr.rows = min(chunk, c - i * chunk); pr.pad = 0;
             problems[p0 + i] = pr;
+            if (pair_rows > 0) {
+                pr.z += pair_matrices; pr.row0 += pair_rows;
+                problems[wprob[31] + p0 + i] = pr;
+            }
         }
     }
-    if (j == 0) { offsets[n_local] = wrows[31]; *n_problems = wprob[31]; }
+    if (j == 0) {
+        offsets[n_local] = wrows[31];
+        n_problems[0] = wprob[31];
+        n_problems[1] = pair_rows > 0 ? 2 * wprob[31] : 0;
+    }
     return row0;
 }
 
 __global__ void __launch_bounds__(1024) k_moe_scan(const int* __restrict__ counts, int* __restrict__ offsets,
                                                    GemvProblem* __restrict__ problems, int* __restrict__ n_problems,
-                                                   int n_routed, int chunk, int extra_rows)
+                                                   int n_routed, int chunk, int extra_rows, int pair_rows, int pair_matrices)
 {
     pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
     pdl_wait();
-    scan_problems(threadIdx.x < n_routed ? counts[threadIdx.x] : 0, offsets, problems, n_problems, n_routed, chunk, extra_rows);
+    scan_problems(threadIdx.x < n_routed ? counts[threadIdx.x] : 0, offsets, problems, n_problems, n_routed, chunk, extra_rows, pair_rows,
+                  pair_matrices);
 }
 
 // Count, scan and stable scatter in one block for a short key list (n <= kSmallKeys).  Warp 0 walks the keys 32 at
@@ -229,7 +242,8 @@ constexpr int kSmallKeys = 2048;
 __global__ void __launch_bounds__(1024) k_moe_dispatch_small(const int32_t* __restrict__ keys, int n, int e0, int* __restrict__ counts,
                                                              int* __restrict__ offsets, GemvProblem* __restrict__ problems,
                                                              int* __restrict__ n_problems, int n_routed, int chunk, int extra_rows,
-                                                             int32_t* __restrict__ perm, int32_t* __restrict__ inv)
+                                                             int pair_rows, int pair_matrices, int32_t* __restrict__ perm,
+                                                             int32_t* __restrict__ inv)
 {
     pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
     pdl_wait();
@@ -256,7 +270,7 @@ __global__ void __launch_bounds__(1024) k_moe_dispatch_small(const int32_t* __re
     __syncthreads();
     const int c = j < n_routed ? s_cnt[j] : 0;
     if (j < n_routed) counts[j] = c;
-    const int row0 = scan_problems(c, offsets, problems, n_problems, n_routed, chunk, extra_rows);
+    const int row0 = scan_problems(c, offsets, problems, n_problems, n_routed, chunk, extra_rows, pair_rows, pair_matrices);
     if (j < n_routed) s_row0[j] = row0;
     __syncthreads();
     for (int i = j; i < n; i += blockDim.x) {
@@ -618,21 +632,22 @@ ExpertScratch carve_experts(void* base, int R, int n_local, int hidden, int inte
     const int kmax = std::max(hidden, inter);
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += align256(bytes); return o; };
-    const size_t o_counts = take(size_t(n_local) * 4), o_offsets = take(size_t(n_local + 2) * 4), o_np = take(4);
-    const size_t o_prob = take(size_t(s.max_problems) * sizeof(GemvProblem));
-    // rotated activations: fragment order per problem (GEMV) or plain rows (GEMM)
-    const size_t o_afrag = take(plan.tg ? size_t(s.max_problems) * (kmax / 16) * plan.tg * 256 : size_t(R) * kmax * 2);
-    // the rows rotated with the up projection's scales (gate and up are rotated by one launch)
-    const size_t o_afrag2 = take(plan.tg ? size_t(s.max_problems) * (hidden / 16) * plan.tg * 256 : size_t(R) * hidden * 2);
-    const size_t o_bsum2 = take(plan.tg ? size_t(s.max_problems) * chunk * (hidden / 128) * 4 : 256);
-    const size_t o_bsum = take(plan.tg ? size_t(s.max_problems) * chunk * (kmax / 128) * 4 : 256);
-    const size_t o_g = take(size_t(R) * inter * 2), o_u = take(size_t(R) * inter * 2);
+    const size_t o_counts = take(size_t(n_local) * 4), o_offsets = take(size_t(n_local + 2) * 4), o_np = take(8);
+    const size_t o_prob = take(size_t(2) * s.max_problems * sizeof(GemvProblem));   // room for the doubled (gate + up) table
+    // rotated activations: fragment order per problem (GEMV) or plain rows (GEMM); room for the rows rotated with
+    // the gate scales and, behind them, with the up scales (one rotation launch writes both)
+    const size_t half_afrag = plan.tg ? size_t(s.max_problems) * (hidden / 16) * plan.tg * 256 : size_t(R) * hidden * 2;
+    const size_t o_afrag = take(std::max(2 * half_afrag, plan.tg ? size_t(s.max_problems) * (kmax / 16) * plan.tg * 256 : size_t(R) * kmax * 2));
+    const size_t half_bsum = plan.tg ? size_t(s.max_problems) * chunk * (hidden / 128) * 4 : 128;
+    const size_t o_bsum = take(std::max(2 * half_bsum, plan.tg ? size_t(s.max_problems) * chunk * (kmax / 128) * 4 : 256));
+    const size_t o_g = take(size_t(2) * R * inter * 2);   // gate outputs, then up outputs
     s.bytes = off;
     if (base) {
         char* b = static_cast<char*>(base);
         s.counts = (int*) (b + o_counts); s.offsets = (int*) (b + o_offsets); s.n_problems = (int*) (b + o_np);
-        s.problems = (GemvProblem*) (b + o_prob); s.afrag = (uint32_t*) (b + o_afrag); s.afrag2 = (uint32_t*) (b + o_afrag2); s.blocksum = (float*) (b + o_bsum); s.blocksum2 = (float*) (b + o_bsum2);
-        s.g = (__half*) (b + o_g); s.u = (__half*) (b + o_u);
+        s.problems = (GemvProblem*) (b + o_prob); s.afrag = (uint32_t*) (b + o_afrag); s.afrag2 = (uint32_t*) (b + o_afrag + half_afrag);
+        s.blocksum = (float*) (b + o_bsum); s.blocksum2 = (float*) (b + o_bsum + half_bsum);
+        s.g = (__half*) (b + o_g); s.u = s.g + size_t(R) * inter;
     }
     return s;
 }
@@ -653,6 +668,16 @@ bool shared_behind_stacks(const berth_moe_weights* w)
 }
 
 // `routes`: the caller also runs the router over w->n_experts (an expert-parallel rank's block need not be a multiple of 32).
+// True if the up stack of n_matrices matrices (trellis and output scales) starts exactly where the gate stack
+// ends: one grouped launch over a doubled problem table then runs both projections.
+bool up_behind_gate(const berth_moe_weights* w, int n_matrices)
+{
+    const size_t H = size_t(w->hidden), I = size_t(w->inter);
+    const size_t t_hi = H / 16 * (I / 16) * 16 * size_t(w->k_bits) * 2;
+    auto at = [](const void* base, size_t bytes) { return static_cast<const void*>(static_cast<const char*>(base) + bytes); };
+    return w->up_trellis == at(w->gate_trellis, size_t(n_matrices) * t_hi) && w->up_svh == at(w->gate_svh, size_t(n_matrices) * I * 2);
+}
+
 void check_moe_shapes(const berth_moe_weights* w, int T, bool routes = false)
 {
     if (!w) throw std::runtime_error("moe: null weights");
@@ -694,17 +719,17 @@ void router_topk(const void* x, const void* w_router, const float* bias, int32_t
 
 // keys[n] -> counts/offsets/problems + perm/inv; experts [e0, e0 + n_local).
 void dispatch(const int32_t* keys, int n, int e0, int n_local, int chunk, const ExpertScratch& s, int32_t* perm, int32_t* inv,
-              cudaStream_t st, int extra_rows = 0)
+              cudaStream_t st, int extra_rows = 0, int pair_rows = 0, int pair_matrices = 0)
 {
     if (n_local + (extra_rows > 0 ? 1 : 0) > 1024) throw std::runtime_error("moe: too many local experts for the scan kernel");
     if (n <= kSmallKeys) {
-        launch_pdl(k_moe_dispatch_small, dim3(1), dim3(1024), 0, st, "k_moe_dispatch_small launch", keys, n, e0, s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows, perm, inv);
+        launch_pdl(k_moe_dispatch_small, dim3(1), dim3(1024), 0, st, "k_moe_dispatch_small launch", keys, n, e0, s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows, pair_rows, pair_matrices, perm, inv);
         cuda_ok(cudaGetLastError(), "k_moe_dispatch_small launch");
         return;
     }
     launch_pdl(k_moe_count, dim3(n_local), dim3(256), 0, st, "k_moe_count launch", keys, n, e0, s.counts);
     cuda_ok(cudaGetLastError(), "k_moe_count launch");
-    launch_pdl(k_moe_scan, dim3(1), dim3(1024), 0, st, "k_moe_scan launch", s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows);
+    launch_pdl(k_moe_scan, dim3(1), dim3(1024), 0, st, "k_moe_scan launch", s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows, pair_rows, pair_matrices);
     cuda_ok(cudaGetLastError(), "k_moe_scan launch");
     launch_pdl(k_moe_scatter, dim3(n_local), dim3(1024), 0, st, "k_moe_scatter launch", keys, n, e0, s.offsets, perm, inv);
     cuda_ok(cudaGetLastError(), "k_moe_scatter launch");
@@ -715,6 +740,7 @@ void dispatch(const int32_t* keys, int n, int e0, int n_local, int chunk, const 
 struct RowSource {
     const int32_t* perm = nullptr;
     int div = 1, n_perm = 0;
+    bool paired = false;   // the problem table was written twice (scan_problems, pair_rows = max_rows) and up lies behind gate
 };
 
 // Grouped gate/up -> silu*up -> down over routed rows xr [R][hidden]; yr fp16 [R][hidden].
@@ -727,22 +753,33 @@ std::string experts(const berth_moe_weights* w, const void* gate_t, const void* 
     // (the activation between the projections runs inside the rotation of the down projection, over the rows of the
     // problem table; neither row count is needed here)
     (void) R; (void) rows_dev;
+    // paired: gate and up are the two halves of one stack, the doubled problem table sends the second half's
+    // outputs to rows max_rows.. of the gate output buffer
+    const bool paired = src.paired;
+    const __half* u_out = paired ? s.g + size_t(max_rows) * I : s.u;
     if (plan.nsub) {
         // one rotation launch for gate and up (the row is read once), the activation inside the rotation for down
         RotateArgs r{};
         r.src = static_cast<const __half*>(xr);
         r.perm = src.perm; r.div = src.div; r.n_perm = src.n_perm;
         r.suh_a = static_cast<const __half*>(gsuh); r.suh_b = static_cast<const __half*>(usuh);
-        r.out_a = reinterpret_cast<__half*>(s.afrag); r.out_b = reinterpret_cast<__half*>(s.afrag2);
+        r.out_a = reinterpret_cast<__half*>(s.afrag);
+        r.out_b = paired ? r.out_a + size_t(max_rows) * H : reinterpret_cast<__half*>(s.afrag2);
         r.problems = s.problems; r.n_problems = s.n_problems;
         r.chunk = plan.chunk; r.k = H; r.max_problems = s.max_problems; r.n_matrices = n_local; r.max_rows = max_rows;
         rotate_rows_grouped(r, true, false, sms, st);
-        std::string d = launch_gemm_tc_grouped_rotated(s.afrag, gate_t, n_local, s.g, gsvh, s.problems, s.n_problems, s.max_problems, max_rows,
-                                                       plan.nsub, H, I, w->k_bits, w->codebook, 0, sc.status, sms, st);
-        launch_gemm_tc_grouped_rotated(s.afrag2, up_t, n_local, s.u, usvh, s.problems, s.n_problems, s.max_problems, max_rows, plan.nsub, H,
-                                       I, w->k_bits, w->codebook, 0, sc.status, sms, st);
+        std::string d;
+        if (paired) {
+            d = launch_gemm_tc_grouped_rotated(s.afrag, gate_t, 2 * n_local, s.g, gsvh, s.problems, s.n_problems + 1, 2 * s.max_problems,
+                                               2 * max_rows, plan.nsub, H, I, w->k_bits, w->codebook, 0, sc.status, sms, st);
+        } else {
+            d = launch_gemm_tc_grouped_rotated(s.afrag, gate_t, n_local, s.g, gsvh, s.problems, s.n_problems, s.max_problems, max_rows,
+                                               plan.nsub, H, I, w->k_bits, w->codebook, 0, sc.status, sms, st);
+            launch_gemm_tc_grouped_rotated(s.afrag2, up_t, n_local, s.u, usvh, s.problems, s.n_problems, s.max_problems, max_rows, plan.nsub,
+                                           H, I, w->k_bits, w->codebook, 0, sc.status, sms, st);
+        }
         RotateArgs rd{};
-        rd.src = s.g; rd.src_u = s.u;
+        rd.src = s.g; rd.src_u = u_out;
         rd.suh_a = static_cast<const __half*>(dsuh);
         rd.out_a = reinterpret_cast<__half*>(s.afrag);
         rd.problems = s.problems; rd.n_problems = s.n_problems;
@@ -750,7 +787,8 @@ std::string experts(const berth_moe_weights* w, const void* gate_t, const void* 
         rotate_rows_grouped(rd, false, true, sms, st);
         launch_gemm_tc_grouped_rotated(s.afrag, down_t, n_local, yr, dsvh, s.problems, s.n_problems, s.max_problems, max_rows, plan.nsub, I,
                                        H, w->k_bits, w->codebook, 0, sc.status, sms, st);
-        return "k_rotate_rows_plain<gate+up> + 2 x " + d + " + k_rotate_rows_plain<silu> + 1 x (same, down)";
+        return std::string("k_rotate_rows_plain<gate+up> + ") + (paired ? "1 x (gate and up as one stack) " : "2 x ") + d +
+               " + k_rotate_rows_plain<silu> + 1 x (same, down)";
     }
     const int tg = plan.tg;
     RotateFragArgs r{};
@@ -760,13 +798,20 @@ std::string experts(const berth_moe_weights* w, const void* gate_t, const void* 
     r.afrag_a = s.afrag; r.afrag_b = s.afrag2; r.bsum_a = s.blocksum; r.bsum_b = s.blocksum2;
     r.problems = s.problems; r.n_problems = s.n_problems;
     r.tok = 8 * tg; r.k = H; r.max_problems = s.max_problems; r.n_matrices = n_local; r.max_rows = max_rows;
+    r.pair = paired ? 1 : 0;
     rotate_rows_frag(r, true, false, sms, st);
-    std::string d = launch_gemv_grouped_rotated(gate_t, n_local, s.g, gsvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag,
-                                                s.blocksum, H, I, w->k_bits, w->codebook, 0, sc, sms, st);
-    launch_gemv_grouped_rotated(up_t, n_local, s.u, usvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag2, s.blocksum2, H, I,
-                                w->k_bits, w->codebook, 0, sc, sms, st);
+    std::string d;
+    if (paired) {
+        d = launch_gemv_grouped_rotated(gate_t, 2 * n_local, s.g, gsvh, s.problems, s.n_problems + 1, 2 * s.max_problems, 2 * max_rows, tg,
+                                        s.afrag, s.blocksum, H, I, w->k_bits, w->codebook, 0, sc, sms, st);
+    } else {
+        d = launch_gemv_grouped_rotated(gate_t, n_local, s.g, gsvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag,
+                                        s.blocksum, H, I, w->k_bits, w->codebook, 0, sc, sms, st);
+        launch_gemv_grouped_rotated(up_t, n_local, s.u, usvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag2, s.blocksum2, H,
+                                    I, w->k_bits, w->codebook, 0, sc, sms, st);
+    }
     RotateFragArgs rd{};
-    rd.src = s.g; rd.src_u = s.u;
+    rd.src = s.g; rd.src_u = u_out;
     rd.suh_a = static_cast<const __half*>(dsuh);
     rd.afrag_a = s.afrag; rd.bsum_a = s.blocksum;
     rd.problems = s.problems; rd.n_problems = s.n_problems;
@@ -774,7 +819,8 @@ std::string experts(const berth_moe_weights* w, const void* gate_t, const void* 
     rotate_rows_frag(rd, false, true, sms, st);
     launch_gemv_grouped_rotated(down_t, n_local, yr, dsvh, s.problems, s.n_problems, s.max_problems, max_rows, tg, s.afrag, s.blocksum, I, H,
                                 w->k_bits, w->codebook, 0, sc, sms, st);
-    return "k_rotate_rows<gate+up> + 2 x (" + d + ") + k_rotate_rows<silu> + 1 x (same, down)";
+    return std::string("k_rotate_rows<gate+up> + ") + (paired ? "1 x (gate and up as one stack: " : "2 x (") + d +
+           ") + k_rotate_rows<silu> + 1 x (same, down)";
 }
 
 }  // namespace
@@ -1130,7 +1176,7 @@ extern "C" int berth_moe_p2p_experts(const berth_moe_weights* w, const void* x_l
         ExpertScratch es = carve_experts(b, max_rows, NM, H, I, plan);
         es.counts = sw.counts_local;
         __half* xr = static_cast<__half*>(pr.p[rank]);
-        launch_pdl(k_moe_scan, dim3(1), dim3(1024), 0, cs, "k_moe_scan launch", es.counts, es.offsets, es.problems, es.n_problems, NL, plan.chunk, TS);
+        launch_pdl(k_moe_scan, dim3(1), dim3(1024), 0, cs, "k_moe_scan launch", es.counts, es.offsets, es.problems, es.n_problems, NL, plan.chunk, TS, 0, 0);
         cuda_ok(cudaGetLastError(), "k_moe_scan launch");
         if (TS) {
             k_rows_to_offset<<<std::min(TS, 148 * 8), 256, 0, cs>>>((const __half*) x_local, xr, es.offsets + NL, TS, H, max_rows);
@@ -1205,10 +1251,12 @@ extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T,
         b += carve_experts(nullptr, R + T, E + 1, H, I, plan).bytes;
 
         router_topk(x, w->w_router, w->router_bias, topk_idx, topk_w, logits, T, H, E, K, cs);
-        dispatch(topk_idx, R, 0, E, plan.chunk, es, perm, inv, cs, fused_shared ? T : 0);
+        const bool paired = up_behind_gate(w, NM);
+        dispatch(topk_idx, R, 0, E, plan.chunk, es, perm, inv, cs, fused_shared ? T : 0, paired ? RT : 0, NM);
         // the rotation kernel of gate and up gathers the routed rows (and the shared expert's) from x itself
         RowSource rows_from{};
         rows_from.perm = perm; rows_from.div = K; rows_from.n_perm = R;
+        rows_from.paired = paired;
         st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
                             w->down_suh, w->down_svh, NM, x, yr, RT, RT, plan, es, sc, info.sms, cs, nullptr, rows_from);
 

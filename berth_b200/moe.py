@@ -39,7 +39,7 @@ class MoeLayer:
     """One MoE layer resident on a GPU.  ``weights`` is the dict of ``berth_b200.synth.moe_layer_weights``
     (or the same keys filled from a checkpoint): numpy arrays are uploaded, torch tensors are kept."""
 
-    def __init__(self, device: torch.device, weights: dict, max_tokens: int, fuse_shared: bool = True):
+    def __init__(self, device: torch.device, weights: dict, max_tokens: int, fuse_shared: bool = True, pair_gate_up: bool = True):
         self.device = device
         self.dims = {k: int(weights[k]) for k in ("hidden", "inter", "shared_inter", "n_experts", "top_k", "bits", "cb")}
         self._keep = {}
@@ -79,6 +79,21 @@ class MoeLayer:
             v = on_device(v)
             self._keep[name] = v
             setattr(self.c, name, v.data_ptr())
+        # The up stack directly behind the gate stack (trellis and output scales): the library then runs both
+        # projections as one grouped launch over a doubled problem table.
+        if pair_gate_up:
+            for k in ("trellis", "svh"):
+                g, u = self._keep.get(f"gate_{k}"), self._keep.get(f"up_{k}")
+                if g is None or u is None or g.shape != u.shape or g.dtype != u.dtype:
+                    continue
+                n = g.shape[0]
+                pair = torch.cat((g, u))
+                for p, part in (("gate", pair[:n]), ("up", pair[n:])):
+                    self._keep[f"{p}_{k}"] = part
+                    setattr(self.c, f"{p}_{k}", part.data_ptr())
+                    if f"sh_{p}_{k}" in stacked:
+                        self._keep[f"sh_{p}_{k}"] = part[n - 1]
+                        setattr(self.c, f"sh_{p}_{k}", part[n - 1].data_ptr())
         self.max_tokens = 0
         self._alloc(max_tokens)
 

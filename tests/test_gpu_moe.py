@@ -54,9 +54,9 @@ def test_router_ties_and_bias(oracle):
     assert (idx == exp_idx).all()
 
 
-def _run_layer(wts, x, fuse_shared=True):
+def _run_layer(wts, x, fuse_shared=True, pair_gate_up=True):
     T = x.shape[0]
-    layer = moe.MoeLayer(torch.device("cuda"), wts, T, fuse_shared=fuse_shared)
+    layer = moe.MoeLayer(torch.device("cuda"), wts, T, fuse_shared=fuse_shared, pair_gate_up=pair_gate_up)
     out = torch.full((T, wts["hidden"]), float("nan"), dtype=torch.float32, device="cuda")
     idx = torch.empty((T, wts["top_k"]), dtype=torch.int32, device="cuda")
     w = torch.empty((T, wts["top_k"]), dtype=torch.float32, device="cuda")
@@ -163,6 +163,20 @@ def test_shared_expert_inside_the_grouped_launches(T):
     assert (idx_f == idx_p).all() and (w_f == w_p).all()
     rms = np.sqrt((plain.astype(np.float64) ** 2).mean())
     assert np.abs(fused - plain).max() <= 5e-3 * rms
+
+
+@pytest.mark.parametrize("T", [1, 5, 40, 130, 300])
+@pytest.mark.parametrize("shared", [0, 128])
+def test_gate_and_up_as_one_stack(T, shared):
+    """With the up stack stored directly behind the gate stack both projections run as one grouped launch over a
+    doubled problem table: same kernels, same summation order, hence the same bits as two launches."""
+    H, I, E, k = 256, 128, 32, 4
+    wts = synth.moe_layer_weights(1234, "pair", H, I, E, k, 4, 2, shared_inter=shared)
+    x = synth.activations(1234, f"pair.x{T}", T, H)
+    one, idx_1, w_1 = _run_layer(wts, x, pair_gate_up=True)
+    two, idx_2, w_2 = _run_layer(wts, x, pair_gate_up=False)
+    assert (idx_1 == idx_2).all() and (w_1 == w_2).all()
+    assert (one.view(np.uint32) == two.view(np.uint32)).all()
 
 
 def test_peer_memory_layer_on_one_rank():
