@@ -1025,14 +1025,16 @@ extern "C" int berth_moe_ep_experts(const berth_moe_weights* w, const void* recv
             k_moe_segment_keys<<<world * NL, 128, 0, cs>>>(seg_off, NL, n_rows, keys);
             cuda_ok(cudaGetLastError(), "k_moe_segment_keys launch");
         }
-        dispatch(keys, n_rows, 0, NL, plan.chunk, es, perm, inv, cs, TS);
+        RowSource in_place{};
+        in_place.paired = up_behind_gate(w, NM);
+        dispatch(keys, n_rows, 0, NL, plan.chunk, es, perm, inv, cs, TS, in_place.paired ? RT : 0, NM);
         if (n_rows > 0) {
             launch_pdl(k_moe_gather_rows, dim3(std::min(n_rows, 148 * 8)), dim3(256), 0, cs, "k_moe_gather_rows launch", (const __half*) recv_rows, perm, es.offsets + NL, 1, xr, H);
             cuda_ok(cudaGetLastError(), "k_moe_gather_rows launch");
         }
         if (TS) cuda_ok(cudaMemcpyAsync(xr + size_t(n_rows) * H, x_local, size_t(TS) * H * 2, cudaMemcpyDeviceToDevice, cs), "moe ep experts: shared rows copy");
         st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
-                            w->down_suh, w->down_svh, NM, xr, yr, RT, RT, plan, es, gemv_workspace(device), info.sms, cs);
+                            w->down_suh, w->down_svh, NM, xr, yr, RT, RT, plan, es, gemv_workspace(device), info.sms, cs, nullptr, in_place);
         if (n_rows > 0) {
             launch_pdl(k_moe_gather_n, dim3(std::min(n_rows, 148 * 8)), dim3(256), 0, cs, "k_moe_gather_n launch", yr, inv, n_rows, 1, (__half*) back, H);
             cuda_ok(cudaGetLastError(), "k_moe_gather launch");
@@ -1176,14 +1178,17 @@ extern "C" int berth_moe_p2p_experts(const berth_moe_weights* w, const void* x_l
         ExpertScratch es = carve_experts(b, max_rows, NM, H, I, plan);
         es.counts = sw.counts_local;
         __half* xr = static_cast<__half*>(pr.p[rank]);
-        launch_pdl(k_moe_scan, dim3(1), dim3(1024), 0, cs, "k_moe_scan launch", es.counts, es.offsets, es.problems, es.n_problems, NL, plan.chunk, TS, 0, 0);
+        RowSource in_place{};
+        in_place.paired = up_behind_gate(w, NM);
+        launch_pdl(k_moe_scan, dim3(1), dim3(1024), 0, cs, "k_moe_scan launch", es.counts, es.offsets, es.problems, es.n_problems, NL, plan.chunk, TS,
+                   in_place.paired ? max_rows : 0, NM);
         cuda_ok(cudaGetLastError(), "k_moe_scan launch");
         if (TS) {
             k_rows_to_offset<<<std::min(TS, 148 * 8), 256, 0, cs>>>((const __half*) x_local, xr, es.offsets + NL, TS, H, max_rows);
             cuda_ok(cudaGetLastError(), "k_rows_to_offset launch");
         }
         st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
-                            w->down_suh, w->down_svh, NM, xr, yr, 0, max_rows, plan, es, sc, info.sms, cs, es.offsets + NM);
+                            w->down_suh, w->down_svh, NM, xr, yr, 0, max_rows, plan, es, sc, info.sms, cs, es.offsets + NM, in_place);
         k_ep_return<<<148 * 8, 256, 0, cs>>>(yr, es.offsets, pc, sw.send_off, pt, rank, world, n_experts_total, NL, H, max_rows, max_send, sc.status);
         cuda_ok(cudaGetLastError(), "k_ep_return launch");
         k_ep_barrier<<<1, 32, 0, cs>>>(pf, 2, rank, world, epoch, sc.status);
