@@ -23,7 +23,22 @@ class MoeWeights(C.Structure):
             "sh_gate_suh", "sh_gate_svh", "sh_up_suh", "sh_up_svh", "sh_down_suh", "sh_down_svh")]
 
 
-# name -> (restype, argtypes); every symbol the header declares.
+class TensorInfo(C.Structure):
+    """``berth_tensor_info`` of include/berth_b200_checkpoint.h."""
+    _fields_ = [("name", C.c_char_p), ("shard", C.c_char_p), ("dtype", _i), ("rank", _i), ("shape", _u64 * 8),
+                ("offset", _u64), ("length", _u64)]
+
+
+class LinearInfo(C.Structure):
+    """``berth_linear_info`` of include/berth_b200_checkpoint.h."""
+    _fields_ = [("prefix", C.c_char_p), ("trellis", TensorInfo), ("input_scale", TensorInfo), ("output_scale", TensorInfo),
+                ("bias", TensorInfo), ("input_packed", _i), ("output_packed", _i), ("has_bias", _i), ("codebook", _i),
+                ("bits_x2", _i)]
+
+
+_tip, _lip = C.POINTER(TensorInfo), C.POINTER(LinearInfo)
+
+# name -> (restype, argtypes); every symbol the headers declare.
 SIGNATURES = {
     "berth_exl3_linear": (_i, [_vp] * 6 + [_i] * 6 + [_vp]),
     "berth_exl3_linear_static_scratch": (_i, [_vp] * 6 + [_i] * 6 + [_vp]),
@@ -67,6 +82,20 @@ SIGNATURES = {
     "berth_moe_last_launch": (C.c_char_p, []),
     "berth_ops_last_error": (C.c_char_p, []),
     "berth_ops_last_launch": (C.c_char_p, []),
+    "berth_ckpt_open": (_i, [C.c_char_p, C.POINTER(_vp)]),
+    "berth_ckpt_close": (None, [_vp]),
+    "berth_ckpt_n_tensors": (_i64, [_vp]),
+    "berth_ckpt_n_linears": (_i64, [_vp]),
+    "berth_ckpt_n_others": (_i64, [_vp]),
+    "berth_ckpt_tensor_at": (_i, [_vp, _i64, _tip]),
+    "berth_ckpt_tensor": (_i, [_vp, C.c_char_p, _tip]),
+    "berth_ckpt_linear_at": (_i, [_vp, _i64, _lip]),
+    "berth_ckpt_linear": (_i, [_vp, C.c_char_p, _lip]),
+    "berth_ckpt_other_at": (_i, [_vp, _i64, _tip]),
+    "berth_ckpt_read": (_i, [_vp, C.c_char_p, _vp, _u64]),
+    "berth_ckpt_scale_f16": (_i, [_vp, C.c_char_p, _i, _vp, _u64]),
+    "berth_unpack_signs": (_i, [_vp, _u64, _vp]),
+    "berth_ckpt_last_error": (C.c_char_p, []),
 }
 
 _lib = None

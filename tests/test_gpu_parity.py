@@ -348,3 +348,34 @@ def test_lm_head_shape_6bpw_against_decoded_slices():
 def _lib_reconstruct(out, trellis, size_k, slice_n, full_n, n_offset, bits, cb):
     from berth_b200 import _lib
     return _lib.lib().berth_prefill_reconstruct(out.data_ptr(), trellis.data_ptr(), size_k, slice_n, full_n, n_offset, bits, cb, None)
+
+
+# ---------------------------------------------------------------- from a checkpoint on disk
+
+def test_linear_loaded_from_a_checkpoint(oracle, tmp_path):
+    """A linear written as a safetensors checkpoint with packed input signs and an fp16 output scale, read back by
+    the library's checkpoint reader and run: the same bits as the linear run from the arrays, and parity with the
+    oracle on what was read."""
+    from berth_b200.checkpoint import Checkpoint
+    from tests.test_checkpoint_host import t, write_safetensors
+    K, N, bits, cb, m = 512, 384, 4, 2, 3
+    w = synth.linear_weights(1234, "ckpt", K, N, bits)
+    su = (synth.raw_u64(1234, "ckpt.su", K // 16) & 0xFFFF).astype(np.uint16)
+    write_safetensors(tmp_path / "model.safetensors", [
+        t("model.layers.0.mlp.gate_proj.trellis", "I16", (K // 16, N // 16, 16 * bits), w["trellis"].view(np.int16)),
+        t("model.layers.0.mlp.gate_proj.su", "I16", (K // 16,), su.view(np.int16)),
+        t("model.layers.0.mlp.gate_proj.svh", "F16", (N,), w["svh"].view(np.float16)),
+        t("model.layers.0.mlp.gate_proj.mul1", "I32", ())])
+    with Checkpoint.open(str(tmp_path)) as ck:
+        lin = ck.linear("model.layers.0.mlp.gate_proj")
+        assert (lin.k, int(lin.codebook), lin.input_packed, lin.output_packed) == (4.0, 2, True, False)
+        got = ck.load_linear(lin.prefix)
+    assert (got["trellis"].reshape(-1) == w["trellis"].reshape(-1)).all() and (got["svh"] == w["svh"].view(np.uint16)).all()
+    assert (got["suh"] == oracle.unpack_signs(su)).all()
+    x = synth.activations(1234, "ckpt.x", m, K)
+    c, ah = run_linear(x, dict(got, size_k=K, size_n=N), got["bits"], got["cb"], False)
+    exp_c, exp_ah = oracle.linear(x, got["trellis"], got["suh"], got["svh"], K, N, bits, cb, False)
+    assert (ah == exp_ah.view(np.uint16)).all()
+    y64 = oracle.linear_f64(x, got["trellis"], got["suh"], got["svh"], K, N, bits, cb)
+    mx, mean = rel_errors(c, y64)
+    assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
