@@ -193,7 +193,7 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
 
 std::string launch_gemv(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32,
-                        const GemvScratch& scratch, int sms, cudaStream_t stream);
+                        const GemvScratch& scratch, int sms, cudaStream_t stream, unsigned long long* argmax = nullptr);
 
 constexpr float kRScale = 0.088388347648f;  // 1/sqrt(128), csrc/prefill_lin/reconstruct.cu:43-44
 

@@ -95,6 +95,7 @@ struct GemvArgs {
     const __half* suh;        //   caller's buffer for the rotated activations [m][k]
     __half* a_had;
     void* c;                  // output rows [rows][n]
+    unsigned long long* argmax;   // dense launch only, may be null: per row the key of its largest output (finish_band)
     const __half* svh;        // [n], or the stack [experts][n] when grouped
     const GemvProblem* problems;   // grouped launch: one entry per (expert, chunk of <= 8*TG rows); else null
     const int* n_problems;         // grouped launch: device-side count
@@ -349,8 +350,11 @@ __device__ __forceinline__ float row_sum(const float* bsum, int kblocks, int lan
 // Last steps of one output band of one row: v = the lane's four fp32 dot products (columns
 // band*128 + 4*lane ..).  MUL1: w = S*h + B per weight  =>  sum_k x_k w_k = S*acc + B*sum_k x_k.
 template <bool MUL1>
+// `best` (may be null): per output row one 64-bit key, (order-preserving bits of the value) << 32 | ~column, raised
+// with atomicMax to the row's largest output: the greedy token of an lm_head without a pass over the logits (ties go
+// to the lower column; the value is the one that would be stored, fp16-rounded for fp16 outputs).  `c` may then be null.
 __device__ __forceinline__ void finish_band(float (&v)[4], float sx, int lane, uint2 sr, int band, void* c,
-                                            size_t out_row, int n, int out_fp32)
+                                            size_t out_row, int n, int out_fp32, unsigned long long* best = nullptr)
 {
     const int col = band * 128 + lane * 4;
     if constexpr (MUL1) {
@@ -367,12 +371,30 @@ __device__ __forceinline__ void finish_band(float (&v)[4], float sx, int lane, u
     v[2] = __fmul_rn(__fmul_rn(v[2], kRScale), __low2float(s1));
     v[3] = __fmul_rn(__fmul_rn(v[3], kRScale), __high2float(s1));
     if (out_fp32) {
-        *reinterpret_cast<float4*>(static_cast<float*>(c) + out_row * n + col) = make_float4(v[0], v[1], v[2], v[3]);
+        if (c) *reinterpret_cast<float4*>(static_cast<float*>(c) + out_row * n + col) = make_float4(v[0], v[1], v[2], v[3]);
     } else {
+        const __half h0 = __float2half_rn(v[0]), h1 = __float2half_rn(v[1]), h2 = __float2half_rn(v[2]), h3 = __float2half_rn(v[3]);
         uint2 o;
-        o.x = dq::pack_half2(__float2half_rn(v[0]), __float2half_rn(v[1]));
-        o.y = dq::pack_half2(__float2half_rn(v[2]), __float2half_rn(v[3]));
-        *reinterpret_cast<uint2*>(static_cast<__half*>(c) + out_row * n + col) = o;
+        o.x = dq::pack_half2(h0, h1);
+        o.y = dq::pack_half2(h2, h3);
+        if (c) *reinterpret_cast<uint2*>(static_cast<__half*>(c) + out_row * n + col) = o;
+        if (best) { v[0] = __half2float(h0); v[1] = __half2float(h1); v[2] = __half2float(h2); v[3] = __half2float(h3); }
+    }
+    if (best) {
+        unsigned long long key = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t bits = __float_as_uint(__fadd_rn(v[i], 0.0f));   // (-0 counts as +0, as a comparison of values would)
+            const uint32_t ord = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+            const unsigned long long k = (static_cast<unsigned long long>(ord) << 32) | (0xffffffffu - uint32_t(col + i));
+            key = k > key ? k : key;
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const unsigned long long o = __shfl_xor_sync(dq::kFull, key, off);
+            key = o > key ? o : key;
+        }
+        if (lane == 0) atomicMax(best + out_row, key);
     }
 }
 
@@ -642,7 +664,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
                             if (band < bands) {   // ragged last band group
                                 float4 t = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
                                 float v[4] = {t.x, t.y, t.z, t.w};
-                                finish_band<CB == 2>(v, sxr[r], lane, svr[b], band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32);
+                                finish_band<CB == 2>(v, sxr[r], lane, svr[b], band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
                             }
                         }
                     }
@@ -665,6 +687,7 @@ struct FinishArgs {
     const float* slabs;
     const float* blocksum;
     void* c;
+    unsigned long long* argmax;
     const __half* svh;
     const GemvProblem* problems;
     const int* n_problems;
@@ -732,8 +755,8 @@ __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
             }
         }
     }
-    if (p.mul1) finish_band<true>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32);
-    else finish_band<false>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32);
+    if (p.mul1) finish_band<true>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
+    else finish_band<false>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
 }
 
 // ---------------------------------------------------------------- rotation of the activations
@@ -937,7 +960,7 @@ void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int codebo
 {
     if (main_grid < 2) return;
     FinishArgs f;
-    f.slabs = a.slabs; f.blocksum = a.blocksum; f.c = a.c; f.svh = a.svh;
+    f.slabs = a.slabs; f.blocksum = a.blocksum; f.c = a.c; f.argmax = a.argmax; f.svh = a.svh;
     f.problems = a.problems; f.n_problems = a.n_problems;
     f.max_problems = a.max_problems; f.n_matrices = a.n_matrices; f.max_rows = a.max_rows;
     f.m = a.m; f.k = a.k; f.n = a.n; f.out_fp32 = a.out_fp32;
@@ -954,7 +977,7 @@ void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int codebo
 // per-device workspace or the fixed in-image array of the allocation-free entry point.
 std::string launch_gemv(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32,
-                        const GemvScratch& sc, int sms, cudaStream_t stream)
+                        const GemvScratch& sc, int sms, cudaStream_t stream, unsigned long long* argmax)
 {
     if (size_m > 32) throw std::runtime_error("exl3 gemv: size_m must be <= 32");
     if (size_k % 128 != 0)
@@ -996,6 +1019,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     args.suh = static_cast<const __half*>(suh);
     args.a_had = static_cast<__half*>(a_had);
     args.c = c;
+    args.argmax = argmax;
     args.svh = static_cast<const __half*>(svh);
     args.slabs = sc.slabs;
     args.status = sc.status;
@@ -1051,6 +1075,7 @@ std::string launch_gemv_grouped_rotated(const void* trellis_stack, int n_experts
     args.blocksum = blocksum;
     args.a = nullptr; args.suh = nullptr; args.a_had = nullptr;
     args.c = c;
+    args.argmax = nullptr;
     args.svh = static_cast<const __half*>(svh_stack);
     args.problems = problems;
     args.n_problems = n_problems;
@@ -1122,6 +1147,7 @@ std::string launch_gemv_sliced(const void* a, const void* b_list, const void* su
     args.blocksum = sc.blocksum;
     args.a = nullptr; args.suh = nullptr; args.a_had = nullptr;
     args.c = nullptr;
+    args.argmax = nullptr;
     args.svh = nullptr;
     args.problems = nullptr;
     args.n_problems = nullptr;

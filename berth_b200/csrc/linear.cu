@@ -4,6 +4,7 @@
 #include "../../include/berth_b200.h"
 
 #include <algorithm>
+#include <cstring>
 
 namespace berth {
 
@@ -88,6 +89,37 @@ extern "C" int berth_exl3_linear(const void* a, const void* trellis, void* c, co
         st.launch = linear_rows(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, out_fp32,
                                 (cudaStream_t) stream);
     });
+}
+
+// The decode linear with the greedy arg-max of every output row taken in the finishing step (an lm_head whose
+// logits need not be written): berth runs the linear and then its two-kernel fused sampler over the logits
+// (crates/berth-kernels/csrc/linear.cu:131-207 for the K = 6 head, csrc/sample/fused.cu:45-135 mode 0).
+extern "C" int berth_exl3_linear_argmax(const void* a, const void* trellis, void* c, const void* suh, void* a_had,
+                                        const void* svh, unsigned long long* best, int size_m, int size_k, int size_n,
+                                        int k_bits, int codebook, int out_fp32, void* stream)
+{
+    CallState& st = exl3_state();
+    return guarded(st, [&] {
+        if (!a || !trellis || !suh || !a_had || !svh || !best) throw std::runtime_error("exl3 linear argmax: null device pointer");
+        if (size_m < 1 || size_k < 1 || size_n < 1) throw std::runtime_error("exl3 linear argmax: sizes must be positive");
+        if (size_m > 32) throw std::runtime_error("exl3 linear argmax: size_m must be <= 32 (the decode kernel)");
+        check_linear_args("exl3 linear argmax", a, trellis, best, suh, a_had, svh, size_k, size_n, k_bits, codebook);
+        const int device = current_device();
+        const DeviceInfo& info = device_info(device);
+        if (info.major != 10)
+            throw std::runtime_error("exl3 linear argmax: no linked kernel for this GPU (library is built for sm_100a only)");
+        cuda_ok(cudaMemsetAsync(best, 0, size_t(size_m) * sizeof(unsigned long long), (cudaStream_t) stream), "argmax keys memset");
+        st.launch = launch_gemv(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, out_fp32,
+                                gemv_workspace(device), info.sms, (cudaStream_t) stream, best) + " [arg-max in the finishing step]";
+    });
+}
+
+extern "C" void berth_argmax_key_decode(unsigned long long key, int32_t* token, float* value)
+{
+    const uint32_t ord = uint32_t(key >> 32);
+    const uint32_t bits = (ord & 0x80000000u) ? (ord & 0x7fffffffu) : ~ord;
+    if (token) *token = int32_t(0xffffffffu - uint32_t(key & 0xffffffffu));
+    if (value) std::memcpy(value, &bits, 4);
 }
 
 extern "C" int berth_prefill_exl3_linear(const void* a, const void* trellis, void* c, const void* suh, void* a_had,

@@ -83,6 +83,25 @@ def exl3_linear_static_scratch(a, trellis, c, suh, a_had, svh, size_m: int, size
         raise Error(last_error() or f"exl3 linear (static scratch) launch failed ({rc})")
 
 
+def exl3_linear_argmax(a, trellis, c, suh, a_had, svh, best, size_m: int, size_k: int, size_n: int, k_bits: int,
+                       codebook: Codebook, out: OutDtype, stream=None) -> None:
+    """:func:`exl3_linear` (``size_m <= 32``) that also leaves, in the device array ``best`` (``size_m`` 64-bit keys),
+    the largest output of every row: the greedy token of an lm_head without a pass over the logits.  ``c`` may be
+    ``None`` (the logits are then not written).  :func:`argmax_key_decode` splits a key read back from the device."""
+    rc = _lib.lib().berth_exl3_linear_argmax(_ptr(a), _ptr(trellis), _ptr(c), _ptr(suh), _ptr(a_had), _ptr(svh), _ptr(best),
+                                             size_m, size_k, size_n, k_bits, int(codebook), int(out), _stream(stream))
+    if rc != 0:
+        raise Error(last_error() or f"exl3 linear argmax launch failed ({rc})")
+
+
+def argmax_key_decode(key: int) -> tuple:
+    """(token, value) of a key written by :func:`exl3_linear_argmax`; ties went to the lower token."""
+    import ctypes as C
+    tok, val = C.c_int32(), C.c_float()
+    _lib.lib().berth_argmax_key_decode(int(key) & 0xFFFFFFFFFFFFFFFF, C.byref(tok), C.byref(val))
+    return tok.value, val.value
+
+
 def device_cc(device: int) -> int:
     return _lib.lib().berth_device_cc(device)
 

@@ -91,6 +91,18 @@ uint64_t berth_exl3_gemm_tune_key(int size_m, int size_k, int size_n, int k_bits
 int berth_exl3_smoke_int8(int out_fp32);
 int berth_exl3_smoke_gemm(void);
 
+/* The decode linear (size_m <= 32) with the greedy arg-max of every output row taken in the finishing step: what
+ * berth does for the lm_head with the K = 6 linear (crates/berth-kernels/csrc/linear.cu:131-207) followed by the
+ * two kernels of its fused sampler in greedy mode (crates/berth-kernels/csrc/sample/fused.cu:45-135, mode 0), in
+ * the launches of the linear alone.  best: DEVICE array of size_m 64-bit keys (zeroed by the call on the stream);
+ * after the stream completes key r describes the largest output of row r, ties to the lower column, the value as
+ * stored (fp16-rounded for fp16 outputs); berth_argmax_key_decode splits a key on the host.  c may be NULL: the
+ * outputs are then not written at all.  Everything else as berth_exl3_linear. */
+int berth_exl3_linear_argmax(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
+                             unsigned long long* best, int size_m, int size_k, int size_n, int k_bits, int codebook,
+                             int out_fp32, void* stream);
+void berth_argmax_key_decode(unsigned long long key, int32_t* token, float* value);
+
 /* ------------------------------------------------------------------ prefill linear (m > 1)
  * Replaces berth_prefill_exl3_linear (crates/berth-kernels/src/prefill_lin.rs:37-52,
  * crates/berth-kernels/csrc/prefill_lin/linear.cu:232-381).  w_scratch (fp16,

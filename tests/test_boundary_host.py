@@ -170,3 +170,23 @@ def test_product_does_not_touch_the_oracle():
             text = open(os.path.join(dirpath, f), errors="replace").read()
             for needle in ("exl3o_", "import oracle", "from oracle", "libexl3_oracle"):
                 assert needle not in text, f"{f} references the oracle ({needle})"
+
+
+def test_argmax_key_decode_known_answers(lib):
+    """key = (order-preserving bits of the fp32 value) << 32 | (0xffffffff - column)."""
+    import struct
+
+    def key(value, col):
+        bits = struct.unpack("<I", struct.pack("<f", value))[0]
+        order = (~bits & 0xFFFFFFFF) if bits & 0x80000000 else bits | 0x80000000
+        return (order << 32) | (0xFFFFFFFF - col)
+
+    for value, col in ((1.5, 0), (-2.25, 7), (0.0, 248319), (-0.0, 1), (3.0e38, 12345), (-1.0e-40, 4)):
+        tok, val = kernels.argmax_key_decode(key(value, col))
+        assert tok == col and struct.pack("<f", val) == struct.pack("<f", value)
+    # larger value wins; at equal value the lower column wins
+    assert key(2.0, 9) > key(1.0, 3) and key(-1.0, 9) > key(-2.0, 3) and key(1.0, 3) > key(1.0, 9) and key(0.5, 0) > key(-0.5, 0)
+    with pytest.raises(Error, match="null"):
+        kernels.exl3_linear_argmax(None, None, None, None, None, None, None, 1, 128, 256, 4, Codebook.Mul1, OutDtype.F16)
+    with pytest.raises(Error, match="size_m"):
+        kernels.exl3_linear_argmax(P, P, P, P, P, P, P, 33, 128, 256, 4, Codebook.Mul1, OutDtype.F16)

@@ -379,3 +379,50 @@ def test_linear_loaded_from_a_checkpoint(oracle, tmp_path):
     y64 = oracle.linear_f64(x, got["trellis"], got["suh"], got["svh"], K, N, bits, cb)
     mx, mean = rel_errors(c, y64)
     assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
+
+
+# ---------------------------------------------------------------- arg-max in the finishing step
+
+def _argmax_run(x, w, bits, cb, out_fp32, with_c=True):
+    m, k = x.shape
+    n = w["size_n"]
+    xd, td, sd, vd = dev(x), dev(w["trellis"]), dev(w["suh"]), dev(w["svh"])
+    c = torch.full((m, n), float("nan"), dtype=torch.float32 if out_fp32 else torch.float16, device="cuda")
+    ah = torch.zeros((m, k), dtype=torch.float16, device="cuda")
+    best = torch.full((m,), -1, dtype=torch.int64, device="cuda")     # the call zeroes the keys itself
+    kernels.exl3_linear_argmax(xd, td, c if with_c else None, sd, ah, vd, best, m, k, n, bits, Codebook(cb),
+                               OutDtype.F32 if out_fp32 else OutDtype.F16)
+    torch.cuda.synchronize()
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+    return c.cpu().numpy(), [kernels.argmax_key_decode(int(v)) for v in best.cpu().numpy().view(np.uint64)]
+
+
+@pytest.mark.parametrize("m", [1, 2, 7, 32])
+@pytest.mark.parametrize("bits,cb,out_fp32,K,N", [(4, 2, True, 512, 384), (6, 2, False, 1024, 2048), (3, 0, True, 256, 128),
+                                                  (4, 1, False, 2048, 6144)])
+def test_linear_argmax_matches_the_stored_outputs(m, bits, cb, out_fp32, K, N):
+    """The key of every row = (largest stored output, lowest column holding it); the outputs themselves are the
+    bits of the plain linear; without an output buffer the keys are the same."""
+    w = synth.linear_weights(1234, f"am{bits}{cb}{K}", K, N, bits)
+    x = synth.activations(1234, f"am.x{m}", m, K)
+    plain, _ = run_linear(x, w, bits, cb, out_fp32)
+    c, keys = _argmax_run(x, w, bits, cb, out_fp32)
+    assert (c.view(np.uint32 if out_fp32 else np.uint16) == plain.view(np.uint32 if out_fp32 else np.uint16)).all()
+    for r, (tok, val) in enumerate(keys):
+        assert tok == int(np.argmax(plain[r])) and val == float(plain[r, tok]), (r, tok, val)
+    _, keys_only = _argmax_run(x, w, bits, cb, out_fp32, with_c=False)
+    assert keys_only == keys
+    assert "arg-max" in kernels.last_launch()
+
+
+def test_linear_argmax_ties():
+    """Zero activations give a row of zeros of either sign: every column ties as a value, the key names column 0."""
+    K, N, bits, cb = 256, 512, 4, 2
+    w = synth.linear_weights(1234, "amt", K, N, bits)
+    x = synth.activations(1234, "amt.x", 3, K)
+    x[1] = 0
+    plain, _ = run_linear(x, w, bits, cb, True)
+    assert (plain[1] == 0).all()
+    _, keys = _argmax_run(x, w, bits, cb, True)
+    assert keys[1] == (0, 0.0)
+    assert keys[0][0] == int(np.argmax(plain[0])) and keys[2][0] == int(np.argmax(plain[2]))
