@@ -227,10 +227,21 @@ def bench_lm_head(rank: int, reps: int = 10) -> dict:
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / reps
+    # the same launch with the greedy token taken in the finishing step and no logits written
+    best = torch.zeros(1, dtype=torch.int64, device=gpu.device)
+    for _ in range(3):
+        lin.forward_argmax(gpu, 1, x, best)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        lin.forward_argmax(gpu, 1, x, best)
+    e1.record()
+    torch.cuda.synchronize()
+    us_argmax = e0.elapsed_time(e1) * 1e3 / reps
     nbytes = linear_bytes(K, N, 1, 1, bits)
     pk, _ = peaks()
     return {"workload": "lm_head_6bpw_5120x248320_m1", "us": us, "gbs": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / pk,
-            "bytes": nbytes}
+            "bytes": nbytes, "us_with_argmax_no_logits": us_argmax}
 
 
 # ------------------------------------------------------------------ configuration 2: prefill GEMM

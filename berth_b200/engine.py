@@ -93,6 +93,17 @@ class Exl3Linear:
         kernels.exl3_linear(a, self.trellis, c, self.suh, self.a_had, self.svh, rows, self.size_k, self.size_n,
                             self.k_bits, self.codebook, out, gpu.raw_stream())
 
+    def forward_argmax(self, gpu: Gpu, rows: int, a: torch.Tensor, best: torch.Tensor, c: torch.Tensor | None = None,
+                       out: OutDtype = OutDtype.F32) -> None:
+        """The decode launch of an lm_head with the greedy token of every row taken in its finishing step:
+        ``best`` (int64 [rows], device) receives the keys ``kernels.argmax_key_decode`` splits; ``c`` is optional."""
+        if a.numel() * a.element_size() < rows * self.size_k * 2 or best.numel() * best.element_size() < rows * 8:
+            raise Error(f"{self.prefix}: buffer too small")
+        if self.a_had.numel() < rows * self.size_k:
+            self.a_had = torch.zeros(rows * self.size_k, dtype=torch.float16, device=gpu.device)
+        kernels.exl3_linear_argmax(a, self.trellis, c, self.suh, self.a_had, self.svh, best, rows, self.size_k, self.size_n,
+                                   self.k_bits, self.codebook, out, gpu.raw_stream())
+
     def forward_rows(self, gpu: Gpu, rows: int, a: torch.Tensor, c: torch.Tensor, out: OutDtype,
                      scratch: "RowScratch") -> None:
         """Prefill-path launch, rows > 1 (crates/berth-engine/src/device.rs:210-268)."""
