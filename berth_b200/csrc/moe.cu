@@ -104,6 +104,103 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 1) k_moe_router_
     }
 }
 
+// The same sums for launches that fill the GPU: 128 experts x kRouterTok tokens per block, a lane holds four experts
+// (2l, 2l+1, 64+2l, 65+2l of the block's 128), so one broadcast read of the token tile feeds four multiply-adds
+// instead of one -- the narrow kernel above is bound by those shared-memory reads, not by arithmetic.  Warp w adds
+// chunks w and w+16, which is the first level of the halving tree; the remaining 16-leaf tree runs at the end.
+constexpr int kWidePitch = 132;   // floats per (chunk pair, token) row of the partial sums
+template <int S>
+__device__ __forceinline__ float chunk_tree16(const float* base, int c)
+{
+    if constexpr (S == 16) return base[c * (kRouterTok * kWidePitch)];
+    else return __fadd_rn(chunk_tree16<2 * S>(base, c), chunk_tree16<2 * S>(base, c + S));
+}
+__global__ void __launch_bounds__(512, 1) k_moe_router_logits_wide(const __half* __restrict__ x, const __half* __restrict__ w,
+                                                                   const float* __restrict__ bias, float* __restrict__ logits,
+                                                                   int T, int H, int E)
+{
+    pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
+    pdl_wait();
+    extern __shared__ __align__(16) float rsm[];
+    float* xs = rsm;                              // [kRouterTok][H]
+    float* part = rsm + kRouterTok * H;           // [16][kRouterTok][kWidePitch]
+    const int wq = threadIdx.x >> 5, el = threadIdx.x & 31;
+    const int e0 = blockIdx.x * 128, t0 = blockIdx.y * kRouterTok;
+    const int chunk = H / 32;                     // a multiple of 8 (checked by the host)
+    for (int i = threadIdx.x * 2; i < kRouterTok * H; i += 1024) {
+        const int tt = i / H, h = i - tt * H;
+        const __half2 v = *reinterpret_cast<const __half2*>(x + size_t(min(t0 + tt, T - 1)) * H + h);
+        xs[i] = __low2float(v);
+        xs[i + 1] = __high2float(v);
+    }
+    __syncthreads();
+    for (int half = 0; half < 2; ++half) {
+        const int j = wq + 16 * half;
+        const __half* wr = w + size_t(j) * chunk * E + e0 + 2 * el;
+        const float* xj = xs + j * chunk;
+        float acc[kRouterTok][4];
+#pragma unroll
+        for (int tt = 0; tt < kRouterTok; ++tt) acc[tt][0] = acc[tt][1] = acc[tt][2] = acc[tt][3] = 0.f;
+        uint32_t nxt[8][2];
+#pragma unroll
+        for (int ii = 0; ii < 8; ++ii) {
+            nxt[ii][0] = *reinterpret_cast<const uint32_t*>(wr + size_t(ii) * E);
+            nxt[ii][1] = *reinterpret_cast<const uint32_t*>(wr + size_t(ii) * E + 64);
+        }
+        for (int i0 = 0; i0 < chunk; i0 += 8) {
+            float wv[8][4];
+#pragma unroll
+            for (int ii = 0; ii < 8; ++ii) {
+                const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&nxt[ii][0]));
+                const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&nxt[ii][1]));
+                wv[ii][0] = lo.x; wv[ii][1] = lo.y; wv[ii][2] = hi.x; wv[ii][3] = hi.y;
+            }
+            if (i0 + 8 < chunk) {
+#pragma unroll
+                for (int ii = 0; ii < 8; ++ii) {
+                    nxt[ii][0] = *reinterpret_cast<const uint32_t*>(wr + size_t(i0 + 8 + ii) * E);
+                    nxt[ii][1] = *reinterpret_cast<const uint32_t*>(wr + size_t(i0 + 8 + ii) * E + 64);
+                }
+            }
+#pragma unroll
+            for (int tt = 0; tt < kRouterTok; ++tt) {
+                const float4 a = *reinterpret_cast<const float4*>(xj + tt * H + i0);
+                const float4 b = *reinterpret_cast<const float4*>(xj + tt * H + i0 + 4);
+                const float xv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int ii = 0; ii < 8; ++ii) {   // k ascending for every accumulator: the checker's order
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) acc[tt][q] = __fmaf_rn(xv[ii], wv[ii][q], acc[tt][q]);
+                }
+            }
+        }
+        // first tree level: chunk w + chunk w+16 (only this warp touches these rows)
+#pragma unroll
+        for (int tt = 0; tt < kRouterTok; ++tt) {
+            float* row = part + (wq * kRouterTok + tt) * kWidePitch;
+            float2 lo = make_float2(acc[tt][0], acc[tt][1]), hi = make_float2(acc[tt][2], acc[tt][3]);
+            if (half) {
+                const float2 plo = *reinterpret_cast<const float2*>(row + 2 * el), phi = *reinterpret_cast<const float2*>(row + 64 + 2 * el);
+                lo = make_float2(__fadd_rn(plo.x, lo.x), __fadd_rn(plo.y, lo.y));
+                hi = make_float2(__fadd_rn(phi.x, hi.x), __fadd_rn(phi.y, hi.y));
+            }
+            *reinterpret_cast<float2*>(row + 2 * el) = lo;
+            *reinterpret_cast<float2*>(row + 64 + 2 * el) = hi;
+        }
+    }
+    __syncthreads();
+    // warp tt finishes token tt: lane = four experts
+    if (wq < kRouterTok && t0 + wq < T) {
+        const float* base = part + wq * kWidePitch;
+        float* out = logits + size_t(t0 + wq) * E + e0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int col = (q >> 1) * 64 + 2 * el + (q & 1);
+            out[col] = __fadd_rn(chunk_tree16<1>(base + col, 0), bias ? bias[e0 + col] : 0.f);
+        }
+    }
+}
+
 // One warp per token: k rounds of arg-max, value descending then index ascending.
 __global__ void __launch_bounds__(128) k_moe_topk(const float* __restrict__ logits, int32_t* __restrict__ topk_idx,
                                                   float* __restrict__ topk_w, int T, int E, int k)
@@ -706,7 +803,16 @@ void router_topk(const void* x, const void* w_router, const float* bias, int32_t
         attr_set[dev] = true;
     }
     const dim3 rgrid(E / 32, (T + kRouterTok - 1) / kRouterTok);
-    if (int(rgrid.x * rgrid.y) <= device_info(dev).sms)
+    const size_t smem_wide = size_t(kRouterTok) * H * 4 + size_t(16) * kRouterTok * kWidePitch * 4;
+    if (E % 128 == 0 && H % 256 == 0 && smem_wide <= 200 * 1024 && int(rgrid.x * rgrid.y) > 2 * device_info(dev).sms) {
+        static bool wide_set[kMaxDevices] = {};
+        if (!wide_set[dev]) {
+            cuda_ok(cudaFuncSetAttribute(k_moe_router_logits_wide, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "router smem attribute");
+            wide_set[dev] = true;
+        }
+        launch_pdl(k_moe_router_logits_wide, dim3(E / 128, rgrid.y), dim3(512), smem_wide, st, "k_moe_router_logits_wide launch",
+                   (const __half*) x, (const __half*) w_router, bias, logits, T, H, E);
+    } else if (int(rgrid.x * rgrid.y) <= device_info(dev).sms)
         launch_pdl(k_moe_router_logits<32>, rgrid, dim3(32 * 32), smem, st, "k_moe_router_logits launch", (const __half*) x,
                    (const __half*) w_router, bias, logits, T, H, E);
     else

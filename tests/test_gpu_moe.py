@@ -24,8 +24,10 @@ def _route(x, wr, bias, k):
     return idx.cpu().numpy(), w.cpu().numpy(), logits.cpu().numpy()
 
 
-@pytest.mark.parametrize("T", [1, 64, 1024])
+@pytest.mark.parametrize("T", [1, 64, 301, 1024])
 def test_router_topk_config3_bit_exact(oracle, T):
+    """1 and 64 tokens run the narrow logits kernel with one chunk per warp, 301 and 1024 the 128-expert-wide one
+    (301: ragged last token tile)."""
     H, E, k = 2048, 256, 8
     x = synth.activations(1234, f"c3.x{T}", T, H)
     wr = synth.router_weight(1234, "c3.gate.weight", H, E)
