@@ -181,6 +181,36 @@ def test_gate_and_up_as_one_stack(T, shared):
     assert (one.view(np.uint32) == two.view(np.uint32)).all()
 
 
+def test_moe_layer_loaded_from_a_checkpoint(tmp_path):
+    """The experts of a layer written as per-expert checkpoint tensors (`<layer>.experts.<e>.<proj>_proj.*`), read
+    back with Checkpoint.load_experts and run: the same bits as the layer built from the arrays."""
+    from berth_b200.checkpoint import Checkpoint
+    from tests.test_checkpoint_host import t, write_safetensors
+    H, I, E, k, bits, cb, T = 256, 128, 32, 4, 4, 2, 9
+    wts = synth.moe_layer_weights(1234, "ck", H, I, E, k, bits, cb)
+    tensors = []
+    for e in range(E):
+        for proj, (K, N) in (("gate", (H, I)), ("up", (H, I)), ("down", (I, H))):
+            pre = f"model.layers.0.mlp.experts.{e}.{proj}_proj"
+            tensors += [t(pre + ".trellis", "I16", (K // 16, N // 16, 16 * bits), wts[f"{proj}_trellis"][e].view(np.int16)),
+                        t(pre + ".suh", "F16", (K,), wts[f"{proj}_suh"][e]), t(pre + ".svh", "F16", (N,), wts[f"{proj}_svh"][e]),
+                        t(pre + ".mul1", "I32", ())]
+    write_safetensors(tmp_path / "model.safetensors", tensors)
+    with Checkpoint.open(str(tmp_path)) as ck:
+        assert len(ck.linears()) == 3 * E
+        got = ck.load_experts("model.layers.0.mlp", E)
+    assert (got["bits"], got["cb"]) == (bits, cb)
+    loaded = dict(wts)
+    for proj in ("gate", "up", "down"):
+        for part in ("trellis", "suh", "svh"):
+            assert (got[f"{proj}_{part}"].view(np.uint16) == np.asarray(wts[f"{proj}_{part}"]).view(np.uint16)).all()
+            loaded[f"{proj}_{part}"] = got[f"{proj}_{part}"]
+    x = synth.activations(1234, "ck.x", T, H)
+    a, idx_a, w_a = _run_layer(wts, x)
+    b, idx_b, w_b = _run_layer(loaded, x)
+    assert (idx_a == idx_b).all() and (a.view(np.uint32) == b.view(np.uint32)).all()
+
+
 def test_peer_memory_layer_on_one_rank():
     """P2pMoeLayer (exchange by peer-memory stores and flag barriers inside the kernels) on a single-rank
     group: the rank is its own peer, so the whole send / deliver / experts / return / combine chain runs,
