@@ -418,6 +418,8 @@ def cpu_pass(m: int, passes: int):
     from berth_b200 import synth
     from oracle import exl3_oracle as orc
     orc.build()
+    # all the host cores this process may use (a launcher that starts one rank per GPU sets OMP_NUM_THREADS=1)
+    orc.set_num_threads(len(os.sched_getaffinity(0)))
     ws = {name: synth.linear_weights(synth.MASTER_SEED, f"cpu.{name}", k, n, BITS, fan_in_gain=True) for name, k, n, _, _ in SHAPES}
     x = {"x": synth.activations(1234, "cpu.x", m, HIDDEN), "xa": synth.activations(1234, "cpu.xa", m, HIDDEN),
          "attn": synth.activations(1234, "cpu.attn", m, QDIM)}
