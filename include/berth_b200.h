@@ -181,7 +181,11 @@ typedef struct berth_moe_weights {
     int hidden, inter, shared_inter, n_experts, top_k, k_bits, codebook;
     const void* w_router;        /* fp16 [hidden][n_experts] */
     const float* router_bias;    /* fp32 [n_experts] or NULL */
-    /* expert stacks: trellis (E, K/16, N/16, 16*k_bits), suh [E][K], svh [E][N] */
+    /* expert stacks: trellis (E, K/16, N/16, 16*k_bits), suh [E][K], svh [E][N].
+     * Two optional placements save launches without changing a bit of the result: a shared expert of the experts'
+     * shape stored directly behind every stack (as matrix E) runs inside the grouped expert launches; the up stack
+     * (trellis and svh, shared expert included) stored directly behind the gate stack lets gate and up run as one
+     * grouped launch.  The library recognises both from the pointers. */
     const void *gate_trellis, *up_trellis, *down_trellis;
     const void *gate_suh, *gate_svh, *up_suh, *up_svh, *down_suh, *down_svh;
     /* shared expert (shared_inter > 0) */
