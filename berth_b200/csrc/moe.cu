@@ -449,22 +449,37 @@ __global__ void __launch_bounds__(256) k_moe_combine(const __half* __restrict__ 
 {
     pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
     pdl_wait();
+    // block = (token, 512 columns); the token's row positions and weights first, so that the k row reads of a column
+    // pair are independent loads
+    __shared__ int s_pos[32];
+    __shared__ float s_w[32];
     const int t = blockIdx.x;
-    for (int h = threadIdx.x * 2; h < H; h += 512) {
-        float a0 = 0.f, a1 = 0.f;
-        for (int s = 0; s < k; ++s) {
-            const float w = topk_w[size_t(t) * k + s];
-            const __half2 v = *reinterpret_cast<const __half2*>(y + size_t(inv[size_t(t) * k + s]) * H + h);
-            a0 = __fmaf_rn(w, __low2float(v), a0);
-            a1 = __fmaf_rn(w, __high2float(v), a1);
-        }
-        if (ysh) {
-            const __half2 v = *reinterpret_cast<const __half2*>(ysh + size_t(t) * H + h);
-            a0 = __fadd_rn(a0, __low2float(v));
-            a1 = __fadd_rn(a1, __high2float(v));
-        }
-        *reinterpret_cast<float2*>(out + size_t(t) * H + h) = make_float2(a0, a1);
+    if (threadIdx.x < k) {
+        s_pos[threadIdx.x] = inv[size_t(t) * k + threadIdx.x];
+        s_w[threadIdx.x] = topk_w[size_t(t) * k + threadIdx.x];
     }
+    __syncthreads();
+    const int h = blockIdx.y * 512 + threadIdx.x * 2;
+    if (h >= H) return;
+    float a0 = 0.f, a1 = 0.f;
+    for (int s0 = 0; s0 < k; s0 += 8) {
+        __half2 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (s0 + i < k) v[i] = *reinterpret_cast<const __half2*>(y + size_t(s_pos[s0 + i]) * H + h);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (s0 + i < k) {   // fmaf chain in slot order
+                a0 = __fmaf_rn(s_w[s0 + i], __low2float(v[i]), a0);
+                a1 = __fmaf_rn(s_w[s0 + i], __high2float(v[i]), a1);
+            }
+    }
+    if (ysh) {
+        const __half2 v = *reinterpret_cast<const __half2*>(ysh + size_t(t) * H + h);
+        a0 = __fadd_rn(a0, __low2float(v));
+        a1 = __fadd_rn(a1, __high2float(v));
+    }
+    *reinterpret_cast<float2*>(out + size_t(t) * H + h) = make_float2(a0, a1);
 }
 
 // Expert-parallel receive side: the rows of source s arrive sorted by local expert, cnt[s][e] of them per
@@ -1031,8 +1046,8 @@ extern "C" int berth_moe_combine(const void* y, const int32_t* inv, const float*
     CallState& st = moe_state();
     return guarded(st, [&] {
         if (!y || !inv || !topk_w || !out) throw std::runtime_error("moe combine: null device pointer");
-        if (T < 1 || hidden < 2 || hidden % 2 || top_k < 1) throw std::runtime_error("moe combine: bad sizes");
-        k_moe_combine<<<T, 256, 0, (cudaStream_t) stream>>>((const __half*) y, inv, topk_w, (const __half*) ysh, (float*) out, hidden, top_k);
+        if (T < 1 || hidden < 2 || hidden % 2 || top_k < 1 || top_k > 32) throw std::runtime_error("moe combine: bad sizes (top_k must be in 1..=32)");
+        k_moe_combine<<<dim3(T, (hidden + 511) / 512), 256, 0, (cudaStream_t) stream>>>((const __half*) y, inv, topk_w, (const __half*) ysh, (float*) out, hidden, top_k);
         cuda_ok(cudaGetLastError(), "k_moe_combine launch");
         st.launch = "k_moe_combine grid=" + std::to_string(T);
     });
@@ -1384,7 +1399,7 @@ extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T,
             if (berth_ops_silu_mul(sg, su, sg, int64_t(T) * SI, 0.0f, cs) != 0) throw std::runtime_error(berth_ops_last_error());
             linear_rows(sg, w->sh_down_trellis, ysh, w->sh_down_suh, sr, w->sh_down_svh, T, SI, H, w->k_bits, w->codebook, 0, cs);
         }
-        launch_pdl(k_moe_combine, dim3(T), dim3(256), 0, cs, "k_moe_combine launch", yr, inv, topk_w, ysh, (float*) out, H, K);
+        launch_pdl(k_moe_combine, dim3(T, (H + 511) / 512), dim3(256), 0, cs, "k_moe_combine launch", yr, inv, topk_w, ysh, (float*) out, H, K);
         cuda_ok(cudaGetLastError(), "k_moe_combine launch");
         st.launch = std::string("k_moe_router_logits + k_moe_topk + ") + (R <= kSmallKeys ? "k_moe_dispatch_small" : "k_moe_count/scan/scatter") +
                     " + " + st.launch + " + k_moe_combine" + (fused_shared ? " [shared expert as matrix E of the grouped launches]" : "");
