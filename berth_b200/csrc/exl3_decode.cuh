@@ -157,25 +157,23 @@ __device__ __forceinline__ uint32_t hi16_heavy(uint32_t a)
 
 // 4-bit tiles: eight 16-bit windows from the lane's raw word r0 and the next lane's r1
 // (13 integer operations).  Stream bytes in order: r0.b1 r0.b0 r0.b3 r0.b2 r1.b1 r1.b0.
-// HEAVY = true moves the six half-word selections to the FMA-heavy pipe (for the codebooks whose
-// arithmetic leans on the ALU pipe).
-template <bool HEAVY>
+// HEAVY = how many of the six half-word selections go to the FMA-heavy pipe (0, 2, 4 or 6), for
+// balancing the two integer pipes against the arithmetic of the codebook that follows.
+template <int HEAVY>
 __device__ __forceinline__ void states_4bit(uint32_t r0, uint32_t r1, uint32_t (&s)[8])
 {
+    static_assert(HEAVY == 0 || HEAVY == 2 || HEAVY == 4 || HEAVY == 6, "number of selections on the FMA-heavy pipe");
     s[2] = __byte_perm(r0, 0u, 0x4403);
     const uint32_t z = r1 & 0xff00u;
     s[6] = __byte_perm(r0, z, 0x4425);
     const uint32_t a0 = __byte_perm(r0, 0u, 0x1032), a1 = __byte_perm(r1, 0u, 0x1032);
     const uint32_t c4 = __funnelshift_l(a1, a0, 4), c12 = __funnelshift_l(a1, a0, 12);
-    if constexpr (HEAVY) {
-        s[0] = lo16_heavy(r0); s[4] = hi16_heavy(r0);
-        s[1] = hi16_heavy(c4); s[3] = hi16_heavy(c12);
-        s[5] = lo16_heavy(c4); s[7] = lo16_heavy(c12);
-    } else {
-        s[0] = r0 & 0xffffu; s[4] = r0 >> 16;
-        s[1] = c4 >> 16; s[3] = c12 >> 16;
-        s[5] = c4 & 0xffffu; s[7] = c12 & 0xffffu;
-    }
+    if constexpr (HEAVY >= 2) { s[0] = lo16_heavy(r0); s[4] = hi16_heavy(r0); }
+    else { s[0] = r0 & 0xffffu; s[4] = r0 >> 16; }
+    if constexpr (HEAVY >= 4) { s[1] = hi16_heavy(c4); s[5] = lo16_heavy(c4); }
+    else { s[1] = c4 >> 16; s[5] = c4 & 0xffffu; }
+    if constexpr (HEAVY >= 6) { s[3] = hi16_heavy(c12); s[7] = lo16_heavy(c12); }
+    else { s[3] = c12 >> 16; s[7] = c12 & 0xffffu; }
 }
 
 // Eight states -> the four packed fp16 pairs (j=0,1), (2,3), (4,5), (6,7): the A fragment
@@ -213,6 +211,121 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// ---------------------------------------------------------------- per-tile decode + MMA (decode GEMV, fp16 path)
+template <int BITS, int CB>
+__device__ __forceinline__ void tile_states(const uint32_t* tile, int lane, int lane1, uint32_t (&s)[8])
+{
+    // the codebooks whose arithmetic leans on the ALU pipe take their half-word selections on the FMA-heavy pipe
+    if constexpr (BITS == 4) states_4bit<(CB != 2) ? 6 : 0>(tile[lane], tile[lane1], s);
+    else lane_states<BITS>(tile, lane, s);
+}
+
+// Duplicated activation pairs for the lo/hi-as-k-slots scheme: from b0 = (x[2q], x[2q+1]) and
+// b1 = (x[2q+8], x[2q+9]) make (x,x) pairs.
+struct DupFrag { uint32_t e0, e1, o0, o1; };
+__device__ __forceinline__ DupFrag dup_pairs(uint32_t b0, uint32_t b1)
+{
+    DupFrag d;
+    d.e0 = __byte_perm(b0, 0u, 0x1010);  // (x[2q],   x[2q])
+    d.o0 = __byte_perm(b0, 0u, 0x3232);  // (x[2q+1], x[2q+1])
+    d.e1 = __byte_perm(b1, 0u, 0x1010);  // (x[2q+8], x[2q+8])
+    d.o1 = __byte_perm(b1, 0u, 0x3232);  // (x[2q+9], x[2q+9])
+    return d;
+}
+
+// Activation operand of one k-tile row: raw pairs for MUL1, duplicated pairs otherwise.
+template <int CB, int TG>
+struct RowFrag {
+    uint32_t b0[TG], b1[TG];
+    DupFrag dup[TG];
+    // `act` = the k-tile row's block in shared memory: [TG][2][32 lanes] words, lane = 4*token + q
+    __device__ __forceinline__ void load(const uint32_t* act, int lane)
+    {
+#pragma unroll
+        for (int tg = 0; tg < TG; ++tg) {
+            b0[tg] = act[tg * 64 + lane];
+            b1[tg] = act[tg * 64 + 32 + lane];
+            if constexpr (CB != 2) dup[tg] = dup_pairs(b0[tg], b1[tg]);
+        }
+    }
+};
+
+template <int CB, int TG>
+__device__ __forceinline__ void tile_mma(const uint32_t (&s)[8], float (&acc)[TG][4], const RowFrag<CB, TG>& f)
+{
+    if constexpr (CB == 2) {
+        uint32_t h[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[j] = mul1_h1024(s[j]);
+        uint32_t a[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) a[r] = __byte_perm(h[2 * r], h[2 * r + 1], 0x5410);
+#pragma unroll
+        for (int tg = 0; tg < TG; ++tg) mma_16816(acc[tg], a, f.b0[tg], f.b1[tg]);
+    } else {
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w[j] = mix32<CB>(s[j]);
+        const uint32_t ae[4] = {w[0], w[2], w[4], w[6]};   // rows 2q, 2q+8 of columns g, g+8
+        const uint32_t ao[4] = {w[1], w[3], w[5], w[7]};   // rows 2q+1, 2q+9
+#pragma unroll
+        for (int tg = 0; tg < TG; ++tg) {
+            mma_16816(acc[tg], ae, f.dup[tg].e0, f.dup[tg].e1);
+            mma_16816(acc[tg], ao, f.dup[tg].o0, f.dup[tg].o1);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- MUL1 on the integer tensor path
+// For the MUL1 codebook a weight is S*(1024 + u) + B with u = the byte sum of x = s*0x83DCD12D, so
+// sum_k a_k w_k = S * sum_k a_k u_k + (1024 S + B) * sum_k a_k.  The register x IS four u8 k-slots of
+// an m16n8k32 integer MMA: against the activation replicated over the four slots the tensor core
+// forms a_k * (b0 + b1 + b2 + b3) by itself, so the decode is window extraction plus ONE multiply
+// per weight -- no byte sum, no pair packing.  The activations enter as 16-bit block fixed point
+// (two signed 8-bit limbs, value = 256*hi + lo, one fp32 scale per rotated 128-block); the limbs of
+// a token are two of the eight columns of B, so one MMA pair per tile serves four tokens.  The
+// integer accumulation is exact; the only error is the 16-bit rounding of the rotated activation
+// (relative 2^-16 of the block maximum, below fp16's own rounding of the same value).
+//
+// D(16x8, s32) += A(16x32, u8, row) * B(32x8, s8, col)
+__device__ __forceinline__ void mma_16832_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// States of a tile for the integer path: the multiply is the only FMA-heavy work per weight, so
+// two of the six half-word selections of a 4-bit tile move there (11 ALU : 10 FMA-heavy per 8 weights).
+#ifndef BERTH_I8_HEAVY
+#define BERTH_I8_HEAVY 2
+#endif
+template <int BITS>
+__device__ __forceinline__ void tile_states_i8(const uint32_t* tile, int lane, int lane1, uint32_t (&s)[8])
+{
+    if constexpr (BITS == 4) states_4bit<BERTH_I8_HEAVY>(tile[lane], tile[lane1], s);
+    else lane_states<BITS>(tile, lane, s);
+}
+
+// One 16x16 tile against NG groups of four tokens.  Lane 4g+q holds the weights of output columns
+// g, g+8 at k-rows 2q, 2q+1, 2q+8, 2q+9 (s[0..7] in the order of the tile format); b[ng] = the lane's
+// four B words of the k-tile row: the limb of column g (token g/2 of the group, limb g%2: 0 = high)
+// at those four k-rows, each replicated over the four bytes.  acc[ng] = (col g, token q high),
+// (col g, token q low), (col g+8, high), (col g+8, low).
+template <int NG>
+__device__ __forceinline__ void tile_mma_i8(const uint32_t (&s)[8], int (&acc)[NG][4], const uint4 (&b)[NG])
+{
+    uint32_t x[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = s[j] * 0x83DCD12Du;
+#pragma unroll
+    for (int ng = 0; ng < NG; ++ng) {
+        mma_16832_u8s8(acc[ng], x[0], x[2], x[1], x[3], b[ng].x, b[ng].y);
+        mma_16832_u8s8(acc[ng], x[4], x[6], x[5], x[7], b[ng].z, b[ng].w);
+    }
 }
 
 // Unnormalised 128-point Sylvester-Hadamard transform across a warp; lane L holds elements

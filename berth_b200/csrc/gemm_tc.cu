@@ -305,7 +305,7 @@ __device__ __forceinline__ void decode_stage(const unsigned char* tstage, uint32
         for (int t = 0; t < 2; ++t) {
             uint32_t s[8];
             const uint32_t* tile = trow + (2 * quarter + t) * NW;
-            if constexpr (BITS == 4) dq::states_4bit<CB != 2>(tile[lane], tile[(lane + 1) & 31], s);
+            if constexpr (BITS == 4) dq::states_4bit<(CB != 2) ? 6 : 0>(tile[lane], tile[(lane + 1) & 31], s);
             else dq::lane_states<BITS>(tile, lane, s);
             dq::decode_frag<CB>(s, w[t]);
         }

@@ -36,7 +36,7 @@
 //                when the CTA holds a band group's whole K, finish the bands themselves (MUL1
 //                affine correction, Hadamard, svh, store), in the background of the streaming warps.
 // Every mbarrier wait is bounded; a wait that runs out sets a status bit and carries on.
-#include "exl3_decode.cuh"
+#include "gemv_common.cuh"
 #include "silu.cuh"
 #include "../../include/berth_b200.h"
 
@@ -47,10 +47,6 @@
 
 namespace berth {
 
-// ---------------------------------------------------------------- partition (host + device)
-__host__ __device__ inline long long unit_begin(int c, long long U, int G) { return (long long) c * U / G; }
-__host__ __device__ inline int unit_owner(long long u, long long U, int G) { return int(((u + 1) * G + U - 1) / U) - 1; }
-
 namespace {
 
 constexpr int kConsumerWarps = 16;
@@ -60,8 +56,6 @@ constexpr int kThreads = (kConsumerWarps + 1 + kEpiWarps) * 32;
 constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kRingBytes = 96 * 1024;
 constexpr int kFusedUnits = 26;   // most units per CTA for which the rotated activations fit in shared memory
-
-enum StatusBits : unsigned { kStFullTimeout = 1u, kStEmptyTimeout = 2u };
 
 // Compile-time geometry of a (BITS, TG) instance.
 template <int BITS, int TG>
@@ -88,124 +82,6 @@ struct Geo {
     static_assert(S >= 2 && RW >= 1 && RW * RPW == 8 && CG * RW == kConsumerWarps, "geometry");
 };
 
-struct GemvArgs {
-    const uint32_t* afrag;    // rotated activations in MMA fragment order [problem][k/16][TG][2][8][4] words
-    float* blocksum;          // [problem][8*TG or m][k/128]: sum of each rotated 128-block (MUL1 epilogue)
-    const __half* a;          // in-kernel rotation only: activations [m][k], input sign-scale [k], and the
-    const __half* suh;        //   caller's buffer for the rotated activations [m][k]
-    __half* a_had;
-    void* c;                  // output rows [rows][n]
-    unsigned long long* argmax;   // dense launch only, may be null: per row the key of its largest output (finish_band)
-    const __half* svh;        // [n], or the stack [experts][n] when grouped
-    const GemvProblem* problems;   // grouped launch: one entry per (expert, chunk of <= 8*TG rows); else null
-    const int* n_problems;         // grouped launch: device-side count
-    int max_problems, n_matrices, max_rows;   // bounds the table entries are clamped to
-    float* slabs;             // [2*G][m][BU*128]
-    unsigned* status;
-    int m, k, n, out_fp32;
-    // Sliced multi-linear (several column slices of several matrices applied to one input): device arrays
-    // with one entry per slice -- trellis address of the slice's first tile, its output scales, its
-    // output address, the full width of the matrix it was cut from (row stride of trellis and output),
-    // and which of the rotated inputs it takes.  Null b_list = not sliced.
-    const unsigned long long* b_list;
-    const unsigned long long* svh_list;
-    const unsigned long long* c_list;
-    const int* n_stride_list;
-    const int* had_src_list;
-    int n_slices;
-};
-
-// What the roles of the decode kernel need to know about problem pi of a launch.
-struct ProblemView {
-    int rows, row0, z;       // rows of the problem, first row in the activation / output arrays, matrix of the stack
-    int act;                 // which rotated-activation block set and block-sum table it reads
-    const __half* svh;       // output scales of the problem's matrix (column 0 of the problem)
-    void* c;                 // output base (row 0, column 0 of the problem)
-    int ldc;                 // output row stride in elements
-};
-template <typename Args>
-__device__ __forceinline__ ProblemView problem_view(const Args& p, int pi, int tok)
-{
-    ProblemView v;
-    v.rows = p.m; v.row0 = 0; v.z = 0; v.act = 0; v.svh = p.svh; v.c = p.c; v.ldc = p.n;
-    if (p.b_list) {
-        v.act = __ldg(p.had_src_list + pi);
-        v.svh = reinterpret_cast<const __half*>(__ldg(p.svh_list + pi));
-        v.c = reinterpret_cast<void*>(__ldg(p.c_list + pi));
-        v.ldc = __ldg(p.n_stride_list + pi);
-    } else if (p.problems) {
-        const GemvProblem pr = load_problem(p.problems, pi, p.n_matrices, tok, p.max_rows);
-        v.rows = pr.rows; v.row0 = pr.row0; v.z = pr.z; v.act = pi;
-        v.svh = p.svh + size_t(pr.z) * p.n;
-    }
-    return v;
-}
-
-// ---------------------------------------------------------------- mbarrier / TMA PTX
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded waits.  Both give up after roughly half a second, record `code` in the status word and
-// return false; the caller carries on with whatever is there.
-//   mbar_wait:        for the streaming warps, which expect the data to be there: tight polling;
-//   mbar_wait_parked: for the producer, which waits about a microsecond per stage: sleeps between
-//                     polls so that it leaves the issue slots to the decoding warps.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned* status, unsigned code)
-{
-    if (mbar_try_wait(bar, parity)) return true;
-    for (uint32_t i = 0; i < (1u << 24); ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    atomicOr(status, code);
-    return false;
-}
-__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, unsigned* status, unsigned code)
-{
-    if (mbar_try_wait(bar, parity)) return true;
-    for (uint32_t i = 0; i < (1u << 21); ++i) {
-        __nanosleep(200);
-        if (mbar_try_wait(bar, parity)) return true;
-    }
-    atomicOr(status, code);
-    return false;
-}
-// One box of the trellis view (x in 8-byte elements, y in k-tile rows, z = matrix of the stack)
-// into shared memory.
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
-                 : "memory");
-}
-// Contiguous global -> shared bulk copy (16-byte aligned, size a multiple of 16).
-__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
 __device__ __forceinline__ void epi_sync()
 {
     asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
@@ -229,192 +105,6 @@ __device__ __forceinline__ void consumer_sync()
 }
 __device__ __forceinline__ void grid_dependency_wait() { pdl_wait(); }
 __device__ __forceinline__ void grid_launch_dependents() { pdl_trigger(); }
-
-// ---------------------------------------------------------------- per-tile decode + MMA
-template <int BITS, int CB>
-__device__ __forceinline__ void tile_states(const uint32_t* tile, int lane, int lane1, uint32_t (&s)[8])
-{
-    // the codebooks whose arithmetic leans on the ALU pipe take their half-word selections on the FMA-heavy pipe
-    if constexpr (BITS == 4) dq::states_4bit<CB != 2>(tile[lane], tile[lane1], s);
-    else dq::lane_states<BITS>(tile, lane, s);
-}
-
-// Duplicated activation pairs for the lo/hi-as-k-slots scheme: from b0 = (x[2q], x[2q+1]) and
-// b1 = (x[2q+8], x[2q+9]) make (x,x) pairs.
-struct DupFrag { uint32_t e0, e1, o0, o1; };
-__device__ __forceinline__ DupFrag dup_pairs(uint32_t b0, uint32_t b1)
-{
-    DupFrag d;
-    d.e0 = __byte_perm(b0, 0u, 0x1010);  // (x[2q],   x[2q])
-    d.o0 = __byte_perm(b0, 0u, 0x3232);  // (x[2q+1], x[2q+1])
-    d.e1 = __byte_perm(b1, 0u, 0x1010);  // (x[2q+8], x[2q+8])
-    d.o1 = __byte_perm(b1, 0u, 0x3232);  // (x[2q+9], x[2q+9])
-    return d;
-}
-
-// Activation operand of one k-tile row: raw pairs for MUL1, duplicated pairs otherwise.
-template <int CB, int TG>
-struct RowFrag {
-    uint32_t b0[TG], b1[TG];
-    DupFrag dup[TG];
-    // `act` = the k-tile row's block in shared memory: [TG][2][32 lanes] words, lane = 4*token + q
-    __device__ __forceinline__ void load(const uint32_t* act, int lane)
-    {
-#pragma unroll
-        for (int tg = 0; tg < TG; ++tg) {
-            b0[tg] = act[tg * 64 + lane];
-            b1[tg] = act[tg * 64 + 32 + lane];
-            if constexpr (CB != 2) dup[tg] = dup_pairs(b0[tg], b1[tg]);
-        }
-    }
-};
-
-template <int CB, int TG>
-__device__ __forceinline__ void tile_mma(const uint32_t (&s)[8], float (&acc)[TG][4], const RowFrag<CB, TG>& f)
-{
-    if constexpr (CB == 2) {
-        uint32_t h[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) h[j] = dq::mul1_h1024(s[j]);
-        uint32_t a[4];
-#pragma unroll
-        for (int r = 0; r < 4; ++r) a[r] = __byte_perm(h[2 * r], h[2 * r + 1], 0x5410);
-#pragma unroll
-        for (int tg = 0; tg < TG; ++tg) dq::mma_16816(acc[tg], a, f.b0[tg], f.b1[tg]);
-    } else {
-        uint32_t w[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) w[j] = dq::mix32<CB>(s[j]);
-        const uint32_t ae[4] = {w[0], w[2], w[4], w[6]};   // rows 2q, 2q+8 of columns g, g+8
-        const uint32_t ao[4] = {w[1], w[3], w[5], w[7]};   // rows 2q+1, 2q+9
-#pragma unroll
-        for (int tg = 0; tg < TG; ++tg) {
-            dq::mma_16816(acc[tg], ae, f.dup[tg].e0, f.dup[tg].e1);
-            dq::mma_16816(acc[tg], ao, f.dup[tg].o0, f.dup[tg].o1);
-        }
-    }
-}
-
-// One 128-block of one activation row, whole warp: fp16(H128(x * suh) / sqrt(128)); the lane gets
-// elements 4*lane .. 4*lane+3 packed as two half pairs.  SUM: `sx` = sum of the 128 rounded values
-// (every lane), which the MUL1 epilogue needs.
-template <bool SUM>
-__device__ __forceinline__ uint2 rotate_bits(uint2 xr, uint2 sr, int lane, float& sx);
-
-template <bool SUM>
-__device__ __forceinline__ uint2 rotate_block(const __half* __restrict__ xrow, const __half* __restrict__ suh, int kb, int lane, float& sx)
-{
-    const int kcol = kb * 128 + lane * 4;
-    const uint2 xr = *reinterpret_cast<const uint2*>(xrow + kcol);
-    const uint2 sr = *reinterpret_cast<const uint2*>(suh + kcol);
-    return rotate_bits<SUM>(xr, sr, lane, sx);
-}
-
-// The same from the lane's four input values and four scales, already loaded.
-template <bool SUM>
-__device__ __forceinline__ uint2 rotate_bits(uint2 xr, uint2 sr, int lane, float& sx)
-{
-    __half2 x0 = *reinterpret_cast<__half2*>(&xr.x), x1 = *reinterpret_cast<__half2*>(&xr.y);
-    __half2 s0 = *reinterpret_cast<__half2*>(&sr.x), s1 = *reinterpret_cast<__half2*>(&sr.y);
-    float v[4];
-    v[0] = __fmul_rn(__low2float(x0), __low2float(s0));
-    v[1] = __fmul_rn(__high2float(x0), __high2float(s0));
-    v[2] = __fmul_rn(__low2float(x1), __low2float(s1));
-    v[3] = __fmul_rn(__high2float(x1), __high2float(s1));
-    dq::had128_warp(v, lane);
-    __half h[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) h[i] = __float2half_rn(__fmul_rn(v[i], kRScale));
-    uint2 o;
-    o.x = dq::pack_half2(h[0], h[1]);
-    o.y = dq::pack_half2(h[2], h[3]);
-    sx = 0.f;
-    if constexpr (SUM) {
-        sx = __fadd_rn(__fadd_rn(__half2float(h[0]), __half2float(h[1])), __fadd_rn(__half2float(h[2]), __half2float(h[3])));
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) sx = __fadd_rn(sx, __shfl_xor_sync(dq::kFull, sx, off));
-    }
-    return o;
-}
-
-// Sum over a row's block sums (the MUL1 epilogue's sum of the rotated activations), whole warp.
-__device__ __forceinline__ float row_sum(const float* bsum, int kblocks, int lane)
-{
-    float sx = 0.f;
-    for (int b = lane; b < kblocks; b += 32) sx = __fadd_rn(sx, __ldg(bsum + b));
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) sx = __fadd_rn(sx, __shfl_xor_sync(dq::kFull, sx, off));
-    return sx;
-}
-
-// Last steps of one output band of one row: v = the lane's four fp32 dot products (columns
-// band*128 + 4*lane ..).  MUL1: w = S*h + B per weight  =>  sum_k x_k w_k = S*acc + B*sum_k x_k.
-template <bool MUL1>
-// `best` (may be null): per output row one 64-bit key, (order-preserving bits of the value) << 32 | ~column, raised
-// with atomicMax to the row's largest output: the greedy token of an lm_head without a pass over the logits (ties go
-// to the lower column; the value is the one that would be stored, fp16-rounded for fp16 outputs).  `c` may then be null.
-__device__ __forceinline__ void finish_band(float (&v)[4], float sx, int lane, uint2 sr, int band, void* c,
-                                            size_t out_row, int n, int out_fp32, unsigned long long* best = nullptr)
-{
-    const int col = band * 128 + lane * 4;
-    if constexpr (MUL1) {
-        const float S1 = __half2float(__ushort_as_half(dq::kMul1S));
-        const float bsx = __fmul_rn(__half2float(__ushort_as_half(dq::kMul1B)), sx);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = __fmaf_rn(S1, v[i], bsx);
-    }
-    dq::had128_warp(v, lane);
-    uint2 srm = sr;
-    __half2 s0 = *reinterpret_cast<__half2*>(&srm.x), s1 = *reinterpret_cast<__half2*>(&srm.y);
-    v[0] = __fmul_rn(__fmul_rn(v[0], kRScale), __low2float(s0));
-    v[1] = __fmul_rn(__fmul_rn(v[1], kRScale), __high2float(s0));
-    v[2] = __fmul_rn(__fmul_rn(v[2], kRScale), __low2float(s1));
-    v[3] = __fmul_rn(__fmul_rn(v[3], kRScale), __high2float(s1));
-    if (out_fp32) {
-        if (c) *reinterpret_cast<float4*>(static_cast<float*>(c) + out_row * n + col) = make_float4(v[0], v[1], v[2], v[3]);
-    } else {
-        const __half h0 = __float2half_rn(v[0]), h1 = __float2half_rn(v[1]), h2 = __float2half_rn(v[2]), h3 = __float2half_rn(v[3]);
-        uint2 o;
-        o.x = dq::pack_half2(h0, h1);
-        o.y = dq::pack_half2(h2, h3);
-        if (c) *reinterpret_cast<uint2*>(static_cast<__half*>(c) + out_row * n + col) = o;
-        if (best) { v[0] = __half2float(h0); v[1] = __half2float(h1); v[2] = __half2float(h2); v[3] = __half2float(h3); }
-    }
-    if (best) {
-        unsigned long long key = 0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t bits = __float_as_uint(__fadd_rn(v[i], 0.0f));   // (-0 counts as +0, as a comparison of values would)
-            const uint32_t ord = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
-            const unsigned long long k = (static_cast<unsigned long long>(ord) << 32) | (0xffffffffu - uint32_t(col + i));
-            key = k > key ? k : key;
-        }
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) {
-            const unsigned long long o = __shfl_xor_sync(dq::kFull, key, off);
-            key = o > key ? o : key;
-        }
-        if (lane == 0) atomicMax(best + out_row, key);
-    }
-}
-
-// One segment (part of one band group) of a CTA's unit range.
-struct Segment {
-    int bg, kb_begin, units;
-    bool head;       // starts at the CTA's first unit (slab 2c) or later (slab 2c+1)
-    bool whole;      // covers the band group's whole K: finished in the decode kernel, no slab
-};
-__device__ __forceinline__ Segment segment_at(long long u, long long u0, long long u1, int kblocks)
-{
-    Segment s;
-    s.bg = int(u / kblocks);
-    s.kb_begin = int(u - (long long) s.bg * kblocks);
-    const long long left = u1 - u;
-    s.units = left < (long long) (kblocks - s.kb_begin) ? int(left) : kblocks - s.kb_begin;
-    s.head = (u == u0);
-    s.whole = (s.kb_begin == 0 && s.units == kblocks);
-    return s;
-}
 
 // ---------------------------------------------------------------- the kernel
 // FUSED (TG == 1, dense launches whose CTAs take at most kFusedUnits units and never a whole band
@@ -565,14 +255,14 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
                 ++ui;
 #pragma unroll
                 for (int i = 0; i < RPW; ++i) {
-                    RowFrag<CB, TG> f;
+                    dq::RowFrag<CB, TG> f;
                     f.load(act + (rs + RW * i) * (TG * 64), lane);
                     const uint32_t* rowp = stage + (rs + RW * i) * (ROW_BYTES / 4);
 #pragma unroll
                     for (int t = 0; t < NT; ++t) {
                         uint32_t st[8];
-                        tile_states<BITS, CB>(rowp + t * NW, lane, lane1, st);
-                        tile_mma<CB, TG>(st, acc[t], f);
+                        dq::tile_states<BITS, CB>(rowp + t * NW, lane, lane1, st);
+                        dq::tile_mma<CB, TG>(st, acc[t], f);
                     }
                 }
                 __syncwarp();
@@ -664,7 +354,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
                             if (band < bands) {   // ragged last band group
                                 float4 t = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
                                 float v[4] = {t.x, t.y, t.z, t.w};
-                                finish_band<CB == 2>(v, sxr[r], lane, svr[b], band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
+                                finish_band<CB == 2 ? 1 : 0>(v, sxr[r], lane, svr[b], band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
                             }
                         }
                     }
@@ -683,24 +373,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
 // warp per task sums the row's split-K slabs in CTA order (eight independent loads in flight),
 // applies the MUL1 affine correction, the 128-wide Hadamard and the output scale, and stores.  Band
 // groups whose whole K sat in one CTA straddle no boundary; the decode kernel finished those.
-struct FinishArgs {
-    const float* slabs;
-    const float* blocksum;
-    void* c;
-    unsigned long long* argmax;
-    const __half* svh;
-    const GemvProblem* problems;
-    const int* n_problems;
-    int max_problems, n_matrices, max_rows;
-    int m, k, n, out_fp32, bu, tok, main_grid, mul1;
-    const unsigned long long* b_list;      // sliced launch (see GemvArgs), else null
-    const unsigned long long* svh_list;
-    const unsigned long long* c_list;
-    const int* n_stride_list;
-    const int* had_src_list;
-    int n_slices;
-};
-
 __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
 {
     grid_launch_dependents();
@@ -755,8 +427,9 @@ __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
             }
         }
     }
-    if (p.mul1) finish_band<true>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
-    else finish_band<false>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
+    if (p.mul1 == 2) finish_band<2>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
+    else if (p.mul1) finish_band<1>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
+    else finish_band<0>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
 }
 
 // ---------------------------------------------------------------- rotation of the activations
@@ -818,6 +491,8 @@ EncodeTiledFn encode_tiled()
     return fn;
 }
 
+}  // namespace
+
 // 3-D view of a trellis stack: z = matrix, y = k-tile row (K/16), x = the row's (N/16) tiles of
 // 32*bits bytes in 8-byte elements; box = one unit (8 rows x BU bands of one matrix).  Columns
 // past the matrix read as zero.
@@ -836,6 +511,8 @@ CUtensorMap trellis_map(const void* trellis, int n_matrices, int size_k, int siz
     if (r != CUDA_SUCCESS) throw std::runtime_error("exl3 linear: cuTensorMapEncodeTiled failed (" + std::to_string(int(r)) + ")");
     return map;
 }
+
+namespace {
 
 template <int BITS, int CB, int TG, bool FUSED>
 size_t launch_one(const void* trellis, int n_matrices, const GemvArgs& args, int grid, cudaStream_t stream)
@@ -955,8 +632,10 @@ __global__ void __launch_bounds__(256) k_rotate_rows(const RotateFragArgs a)
     }
 }
 
+}  // namespace
+
 // The finishing kernel behind a decode launch of `main_grid` CTAs (nothing to do behind a single CTA).
-void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int codebook, cudaStream_t stream)
+void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int mul1, cudaStream_t stream)
 {
     if (main_grid < 2) return;
     FinishArgs f;
@@ -964,14 +643,13 @@ void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int codebo
     f.problems = a.problems; f.n_problems = a.n_problems;
     f.max_problems = a.max_problems; f.n_matrices = a.n_matrices; f.max_rows = a.max_rows;
     f.m = a.m; f.k = a.k; f.n = a.n; f.out_fp32 = a.out_fp32;
-    f.bu = bu; f.tok = tok; f.main_grid = main_grid; f.mul1 = codebook == 2;
+    f.bu = bu; f.tok = tok; f.main_grid = main_grid; f.mul1 = mul1;
     f.b_list = a.b_list; f.svh_list = a.svh_list; f.c_list = a.c_list; f.n_stride_list = a.n_stride_list; f.had_src_list = a.had_src_list;
     f.n_slices = a.n_slices;
     const int slab_rows = a.problems ? tok : a.m;
     launch_pdl(k_gemv_finish, dim3(main_grid - 1, (bu * slab_rows + 7) / 8), dim3(256), 0, stream, "k_gemv_finish launch", f);
 }
 
-}  // namespace
 
 // Launches rotation + decode GEMV for up to 32 rows.  `sc` is the split-K scratch: the library's
 // per-device workspace or the fixed in-image array of the allocation-free entry point.
@@ -983,6 +661,8 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     if (size_k % 128 != 0)
         throw std::runtime_error("exl3 linear: no linked kernel for size_k that is not a multiple of 128 (128-wide Hadamard)");
     if (k_bits < 1 || k_bits > 8) throw std::runtime_error("exl3 linear: K must be in 1..=8");
+    if (codebook == 2)   // MUL1: integer tensor path with the weights in tensor memory
+        return launch_gemv_i8(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, out_fp32, sc, sms, stream, argmax);
     const int tg = size_m <= 8 ? 1 : (size_m <= 16 ? 2 : 4);
     const int bu = k_bits <= 4 ? 2 : 1;   // bands per unit, as Geo<BITS, TG>::BU
     const int bands = size_n / 128, kblocks = size_k / 128, bgroups = (bands + bu - 1) / bu;
@@ -1031,7 +711,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     args.b_list = nullptr; args.svh_list = nullptr; args.c_list = nullptr; args.n_stride_list = nullptr; args.had_src_list = nullptr;
     args.n_slices = 0;
     const size_t smem = launch_bits(k_bits, codebook, tg, fused, trellis, 1, args, grid, stream);
-    launch_finish(args, bu, 8 * tg, grid, codebook, stream);
+    launch_finish(args, bu, 8 * tg, grid, codebook == 2 ? 1 : 0, stream);
     return std::string(fused ? "" : "k_rotate_in + ") + "k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," +
            std::to_string(tg) + (fused ? ",fused" : "") + "> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem) +
            " + k_gemv_finish";
@@ -1089,7 +769,7 @@ std::string launch_gemv_grouped_rotated(const void* trellis_stack, int n_experts
     args.b_list = nullptr; args.svh_list = nullptr; args.c_list = nullptr; args.n_stride_list = nullptr; args.had_src_list = nullptr;
     args.n_slices = 0;
     const size_t smem = launch_bits(k_bits, codebook, tg, false, trellis_stack, n_experts, args, grid, stream);
-    launch_finish(args, bu, 8 * tg, grid, codebook, stream);
+    launch_finish(args, bu, 8 * tg, grid, codebook == 2 ? 1 : 0, stream);
     return "k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," + std::to_string(tg) +
            ",grouped> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem) +
            " + k_gemv_finish";
@@ -1163,7 +843,7 @@ std::string launch_gemv_sliced(const void* a, const void* b_list, const void* su
     args.had_src_list = had_src_list;
     args.n_slices = n_slices;
     const size_t smem = launch_bits(k_bits, codebook, tg, false, nullptr, 1, args, grid, stream);
-    launch_finish(args, bu, 8 * tg, grid, codebook, stream);
+    launch_finish(args, bu, 8 * tg, grid, codebook == 2 ? 1 : 0, stream);
     return "k_rotate_in x" + std::to_string(num_had_src) + " sources + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," +
            std::to_string(tg) + ",sliced> grid=" + std::to_string(grid) + " block=" + std::to_string(kThreads) + " smem=" +
            std::to_string(smem) + " + k_gemv_finish";

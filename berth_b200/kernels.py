@@ -115,6 +115,17 @@ def device_status(device: int) -> int:
     return _lib.lib().berth_device_status(device)
 
 
+def decode_rate(k_bits: int, codebook: Codebook, path: int, warps: int = 16, iters: int = 4096) -> tuple:
+    """Bare decode rate of one SM (diagnostic): (weights per clock per SM, SM MHz during the run) of the decode
+    GEMV's inner loop on shared-memory-resident tiles.  ``path`` 0 = fp16 tensor path, 1 = MUL1 integer tensor path."""
+    import ctypes as C
+    w, mhz = C.c_double(), C.c_double()
+    rc = _lib.lib().berth_exl3_decode_rate(k_bits, int(codebook), path, warps, iters, C.byref(w), C.byref(mhz))
+    if rc != 0:
+        raise Error(last_error() or f"decode rate failed ({rc})")
+    return w.value, mhz.value
+
+
 def gemm_tune_key(size_m, size_k, size_n, k_bits, out_fp32, device, cc, sms, cb) -> int:
     return _lib.lib().berth_exl3_gemm_tune_key(size_m, size_k, size_n, k_bits, out_fp32, device, cc, sms, cb)
 

@@ -81,6 +81,15 @@ int berth_device_sms(int device);
  * with undefined output instead of hanging.  0 = clean, -1 = CUDA error.  No counterpart in berth. */
 int berth_device_status(int device);
 
+/* Diagnostic, no counterpart in berth: the bare decode rate of one SM.  Runs the inner loop of the
+ * decode GEMV (tile words in shared memory -> window extraction -> codebook arithmetic -> MMA) with
+ * no global-memory traffic on every SM with `warps` warps for `iters` iterations of eight tiles per
+ * warp, and returns the decoded weights per clock per SM (mean over the SMs) and the SM clock seen
+ * during the run.  path 0 = fp16 tensor path (every codebook), 1 = MUL1 on the integer tensor path.
+ * k_bits 3..6.  Allocates three small buffers, synchronises the device, frees them. */
+int berth_exl3_decode_rate(int k_bits, int codebook, int path, int warps, int iters,
+                           double* weights_per_clk_sm, double* sm_mhz);
+
 /* FNV-1a shape key of crates/berth-kernels/csrc/linear.cu:65-104,345-358.  Kept because berth's
  * tests pin its value; this library never tunes at run time.  No CUDA call. */
 uint64_t berth_exl3_gemm_tune_key(int size_m, int size_k, int size_n, int k_bits, int out_fp32,
