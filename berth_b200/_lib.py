@@ -43,6 +43,7 @@ SIGNATURES = {
     "berth_exl3_linear": (_i, [_vp] * 6 + [_i] * 6 + [_vp]),
     "berth_exl3_linear_static_scratch": (_i, [_vp] * 6 + [_i] * 6 + [_vp]),
     "berth_exl3_linear_argmax": (_i, [_vp] * 7 + [_i] * 6 + [_vp]),
+    "berth_exl3_linear_stack": (_i, [_vp] * 6 + [_i] * 7 + [_vp]),
     "berth_argmax_key_decode": (None, [_u64, C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
     "berth_exl3_last_error": (C.c_char_p, []),
     "berth_exl3_last_launch": (C.c_char_p, []),

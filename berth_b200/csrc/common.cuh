@@ -198,7 +198,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
 // The same linear for the MUL1 codebook on the integer tensor path (gemv_i8.cu); launch_gemv forwards to it.
 std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                            int size_m, int size_k, int size_n, int k_bits, int out_fp32, const GemvScratch& scratch, int sms,
-                           cudaStream_t stream, unsigned long long* argmax);
+                           cudaStream_t stream, unsigned long long* argmax, int n_stack = 1);
 
 constexpr float kRScale = 0.088388347648f;  // 1/sqrt(128), csrc/prefill_lin/reconstruct.cu:43-44
 

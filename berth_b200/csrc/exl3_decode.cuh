@@ -299,9 +299,9 @@ __device__ __forceinline__ void mma_16832_u8s8(int (&d)[4], uint32_t a0, uint32_
 }
 
 // States of a tile for the integer path: the multiply is the only FMA-heavy work per weight, so
-// two of the six half-word selections of a 4-bit tile move there (11 ALU : 10 FMA-heavy per 8 weights).
+// four of the six half-word selections of a 4-bit tile move there (9 ALU : 12 FMA-heavy per 8 weights; measured best).
 #ifndef BERTH_I8_HEAVY
-#define BERTH_I8_HEAVY 2
+#define BERTH_I8_HEAVY 4
 #endif
 template <int BITS>
 __device__ __forceinline__ void tile_states_i8(const uint32_t* tile, int lane, int lane1, uint32_t (&s)[8])

@@ -380,7 +380,7 @@ __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
     const int lane = threadIdx.x & 31;
     const int bands = p.n >> 7, kblocks = p.k >> 7, bu = p.bu;
     const int bgroups = (bands + bu - 1) / bu;
-    const int nprob = p.b_list ? p.n_slices : (p.problems ? min(max(__ldg(p.n_problems), 0), p.max_problems) : 1);
+    const int nprob = p.b_list ? p.n_slices : (p.problems ? min(max(__ldg(p.n_problems), 0), p.max_problems) : (p.n_stack > 1 ? p.n_stack : 1));
     const long long U = (long long) nprob * bgroups * kblocks;
     const int G = U < (long long) p.main_grid ? int(U) : p.main_grid;
     const int c = blockIdx.x + 1;                      // the boundary between the ranges of CTA c-1 and CTA c
@@ -646,6 +646,7 @@ void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int mul1, 
     f.bu = bu; f.tok = tok; f.main_grid = main_grid; f.mul1 = mul1;
     f.b_list = a.b_list; f.svh_list = a.svh_list; f.c_list = a.c_list; f.n_stride_list = a.n_stride_list; f.had_src_list = a.had_src_list;
     f.n_slices = a.n_slices;
+    f.n_stack = a.n_stack;
     const int slab_rows = a.problems ? tok : a.m;
     launch_pdl(k_gemv_finish, dim3(main_grid - 1, (bu * slab_rows + 7) / 8), dim3(256), 0, stream, "k_gemv_finish launch", f);
 }
@@ -710,6 +711,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     args.max_problems = 1; args.n_matrices = 1; args.max_rows = size_m;
     args.b_list = nullptr; args.svh_list = nullptr; args.c_list = nullptr; args.n_stride_list = nullptr; args.had_src_list = nullptr;
     args.n_slices = 0;
+    args.n_stack = 0;
     const size_t smem = launch_bits(k_bits, codebook, tg, fused, trellis, 1, args, grid, stream);
     launch_finish(args, bu, 8 * tg, grid, codebook == 2 ? 1 : 0, stream);
     return std::string(fused ? "" : "k_rotate_in + ") + "k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," +
@@ -768,6 +770,7 @@ std::string launch_gemv_grouped_rotated(const void* trellis_stack, int n_experts
     args.out_fp32 = out_fp32;
     args.b_list = nullptr; args.svh_list = nullptr; args.c_list = nullptr; args.n_stride_list = nullptr; args.had_src_list = nullptr;
     args.n_slices = 0;
+    args.n_stack = 0;
     const size_t smem = launch_bits(k_bits, codebook, tg, false, trellis_stack, n_experts, args, grid, stream);
     launch_finish(args, bu, 8 * tg, grid, codebook == 2 ? 1 : 0, stream);
     return "k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," + std::to_string(tg) +
@@ -842,6 +845,7 @@ std::string launch_gemv_sliced(const void* a, const void* b_list, const void* su
     args.n_stride_list = n_stride_list;
     args.had_src_list = had_src_list;
     args.n_slices = n_slices;
+    args.n_stack = 0;
     const size_t smem = launch_bits(k_bits, codebook, tg, false, nullptr, 1, args, grid, stream);
     launch_finish(args, bu, 8 * tg, grid, codebook == 2 ? 1 : 0, stream);
     return "k_rotate_in x" + std::to_string(num_had_src) + " sources + k_exl3_gemv<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "," +

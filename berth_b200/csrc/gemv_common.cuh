@@ -44,6 +44,10 @@ struct GemvArgs {
     const int* n_stride_list;
     const int* had_src_list;
     int n_slices;
+    // Stack of n_stack equally shaped matrices applied to the same rows (integer tensor path only; 0 or 1 = one
+    // matrix): matrix i has its trellis at index i of the 3-D map, its sign-scale vectors at suh + i*k and
+    // svh + i*n, and writes c + i*m*n, a_had + i*m*k and block sums i*m*(k/128).
+    int n_stack;
 };
 
 // What the roles of the decode kernel need to know about problem pi of a launch.
@@ -68,6 +72,10 @@ __device__ __forceinline__ ProblemView problem_view(const Args& p, int pi, int t
         const GemvProblem pr = load_problem(p.problems, pi, p.n_matrices, tok, p.max_rows);
         v.rows = pr.rows; v.row0 = pr.row0; v.z = pr.z; v.act = pi;
         v.svh = p.svh + size_t(pr.z) * p.n;
+    } else if (p.n_stack > 1) {
+        v.z = pi; v.act = pi;
+        v.svh = p.svh + size_t(pi) * p.n;
+        v.c = static_cast<unsigned char*>(p.c) + size_t(pi) * p.m * p.n * (p.out_fp32 ? 4 : 2);
     }
     return v;
 }
@@ -296,6 +304,7 @@ struct FinishArgs {
     const int* n_stride_list;
     const int* had_src_list;
     int n_slices;
+    int n_stack;                           // stack of equally shaped matrices (see GemvArgs), else 0
 };
 
 

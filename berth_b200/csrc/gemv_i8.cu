@@ -57,8 +57,9 @@ constexpr int kThreads = 22 * 32;
 constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kSmemBudget = 227 * 1024;
 
-// Compile-time geometry: BITS bits per weight, NB groups of four rows (two limb columns each).
-template <int BITS, int NB>
+// Compile-time geometry: BITS bits per weight, NB groups of four rows (two limb columns each); FUSED = the
+// limb tiles of all the CTA's units live in a shared-memory area of their own instead of the ring stages.
+template <int BITS, int NB, bool FUSED>
 struct GeoI8 {
     static constexpr int NW = 8 * BITS;
     static constexpr int BU = BITS <= 4 ? 2 : 1;
@@ -68,7 +69,7 @@ struct GeoI8 {
     static constexpr int CHUNK_BYTES = NB * 256;               // limbs of 8 weights-k: NB groups of 8 rows x 32 bytes
     static constexpr int L_BYTES = 16 * CHUNK_BYTES;           // limbs of one unit: 16 MMA k-steps
     static constexpr int B_BYTES = L_BYTES + 128;              // ... followed by the unit's block scales (one fp32 per row)
-    static constexpr int STAGE_BYTES = W_BYTES + B_BYTES;
+    static constexpr int STAGE_BYTES = FUSED ? W_BYTES : W_BYTES + B_BYTES;
     static constexpr int TOK = 4 * NB;
     static constexpr int NCOL = NB <= 2 ? 16 : 8 * NB;         // N of the MMA (16 is the least for M = 128)
     static constexpr int PITCH = BU * 128 + 4;
@@ -79,9 +80,16 @@ struct GeoI8 {
     static constexpr int NA = NA_RAW > 4 ? 4 : NA_RAW;
     static constexpr int kBarBytes = 512;
     static constexpr int RING_MAX = kSmemBudget - 1024 - OUT_FLOATS * 4 - kBarBytes - 64;
-    static constexpr int S_RAW = RING_MAX / STAGE_BYTES;
+    static constexpr int kMinArea = 80 * 1024;                 // in-kernel rotation: least size of the limb area
+    static constexpr int S_RAW = (RING_MAX - (FUSED ? kMinArea : 0)) / STAGE_BYTES;
     static constexpr int S = S_RAW > 12 ? 12 : S_RAW;
-    static constexpr size_t SMEM = 1024 + size_t(S) * STAGE_BYTES + OUT_FLOATS * 4 + kBarBytes;
+    static constexpr int AREA_BYTES = FUSED ? RING_MAX - S * STAGE_BYTES : 0;
+    static constexpr size_t SMEM = 1024 + size_t(S) * STAGE_BYTES + OUT_FLOATS * 4 + kBarBytes + AREA_BYTES;
+    // in-kernel rotation: a unit's limb tile holds 2*rows limb rows per core matrix (rows = 1, 2 or 4), core
+    // matrices 32*rows bytes apart, 16 k-steps of two core matrices, plus four scales; 512 bytes of the area stay
+    // free because the MMA reads whole 8-row core matrices (the rows past 2*rows are never used)
+    __host__ __device__ static constexpr int fused_tile_bytes(int rows) { return 1024 * rows; }
+    __host__ __device__ static constexpr int fused_max_units(int rows) { return (AREA_BYTES - 512) / (fused_tile_bytes(rows) + 16); }
     static_assert(S >= 2 && NA >= 2, "ring and tensor-memory stages");
     static_assert(W_BYTES % 128 == 0 && STAGE_BYTES % 128 == 0, "TMA destination alignment");
     static_assert((2 * S + 2 * NA + 4) * 8 <= kBarBytes, "barrier area");
@@ -108,12 +116,12 @@ __device__ __forceinline__ void tc_mma_ts_i8(uint32_t d_tmem, uint32_t a_tmem, u
 // Instruction descriptor: D s32, A u8, B s8, both K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t idesc_i8(int n) { return (2u << 4) | (0u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(128 >> 4) << 24); }
 // Shared-memory descriptor of a K-major operand without swizzle: 8-row x 16-byte core matrices of 128
-// contiguous bytes; the next core matrix along K lies 128 bytes further, the next group of 8 rows `sbo` bytes.
-__device__ __forceinline__ uint64_t smem_desc_kmajor(uint32_t addr, uint32_t sbo)
+// contiguous bytes; the next core matrix along K lies `lbo` bytes further, the next group of 8 rows `sbo` bytes.
+__device__ __forceinline__ uint64_t smem_desc_kmajor(uint32_t addr, uint32_t lbo, uint32_t sbo)
 {
     uint64_t d = 0;
     d |= uint64_t((addr & 0x3FFFF) >> 4);
-    d |= uint64_t(128 >> 4) << 16;     // leading byte offset: core matrices along K
+    d |= uint64_t(lbo >> 4) << 16;     // leading byte offset: core matrices along K
     d |= uint64_t(sbo >> 4) << 32;     // stride byte offset: 8-row groups
     d |= uint64_t(1) << 46;            // descriptor version of sm_100
     return d;
@@ -127,12 +135,30 @@ __device__ __forceinline__ void tc_st_tile(uint32_t taddr, const uint32_t (&x)[8
                  : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-// 32 lanes x 8 consecutive 32-bit columns of this warp's TMEM lane quarter.
-__device__ __forceinline__ void tc_ld8(uint32_t taddr, int (&r)[8])
+// 32 lanes x N consecutive 32-bit columns (N = 8, 16 or 32) of this warp's TMEM lane quarter; no wait.
+template <int N>
+__device__ __forceinline__ void tc_ld(uint32_t taddr, int* r)
 {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr));
+    static_assert(N == 8 || N == 16 || N == 32, "tcgen05.ld width");
+    if constexpr (N == 8) {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                     : "r"(taddr));
+    } else if constexpr (N == 16) {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                       "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                     : "r"(taddr));
+    } else {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+            "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+              "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr));
+    }
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ bool elect_one()
@@ -142,6 +168,41 @@ __device__ __forceinline__ bool elect_one()
     return pred != 0;
 }
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory"); }
+
+// The lane's four rotated fp16 values of one 128-block (lane = 4 consecutive inputs) -> block fixed point.
+// Writes the two limbs of each value, replicated over the four bytes of a 32-bit word (the four u8 k-slots of a
+// weight's product), at their place in the block's limb tile: `tile_row` = tile + (row / 4) * 256 +
+// 2 * (row % 4) * 16, k-step stride `chunk_stride`, core-matrix stride `lbo` (256 * row groups and 128 in a ring
+// stage).  Tile layout: [MMA k-step 16][row group]
+// [core matrix 2][limb row 8][16 bytes], limb row = 2 * (row % 4) + (0 high, 1 low); k-step c of a k-tile row
+// holds, in this order, the inputs 2c (c < 4) and 2(c-4)+1 of its eight.  Returns the block's scale
+// (max|a| / 32512) and, in every lane, the sum of the block's 128 integers.
+__device__ __forceinline__ float quantise_block(uint2 o, int lane, unsigned char* tile_row, int chunk_stride, int lbo, int& isum)
+{
+    const __half2 h01 = *reinterpret_cast<const __half2*>(&o.x), h23 = *reinterpret_cast<const __half2*>(&o.y);
+    const float hv[4] = {__low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23)};
+    float amax = fmaxf(fmaxf(fabsf(hv[0]), fabsf(hv[1])), fmaxf(fabsf(hv[2]), fabsf(hv[3])));
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(dq::kFull, amax, off));
+    const float scale = __fdiv_rn(amax, 32512.0f);
+    const float inv = amax > 0.f ? __fdiv_rn(32512.0f, amax) : 0.f;
+    isum = 0;
+    const int kt = lane >> 2;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int v = __float2int_rn(__fmul_rn(hv[e], inv));
+        isum += v;
+        const int hi = (v + 128) >> 8, lo = v - 256 * hi;
+        const int r = 4 * (lane & 3) + e;                       // input inside the k-tile row
+        const int chunk = kt * 2 + (r >> 3), c = ((r & 7) >> 1) + 4 * (r & 1);
+        unsigned char* w = tile_row + chunk * chunk_stride + (c >> 2) * lbo + 4 * (c & 3);
+        *reinterpret_cast<uint32_t*>(w) = uint32_t(hi & 0xff) * 0x01010101u;
+        *reinterpret_cast<uint32_t*>(w + 16) = uint32_t(lo & 0xff) * 0x01010101u;
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) isum += __shfl_xor_sync(dq::kFull, isum, off);
+    return scale;
+}
 
 #ifdef BERTH_I8_STAMPS
 __device__ unsigned long long g_i8_ts[256 * 8];
@@ -157,10 +218,17 @@ __device__ __forceinline__ void stamp(int) {}
 #define PH_STORE
 #endif
 // ---------------------------------------------------------------- the kernel
-template <int BITS, int NB>
+// FUSED (one group of four rows, dense launches in which no CTA holds a whole band group and every CTA's units fit
+// the limb area): no rotation kernel runs before this one and no limb tile travels through L2; while the first weight
+// stages are in flight the decoding and epilogue warps rotate and quantise the 128-block of every unit of the CTA
+// into a shared-memory area of its own (tiles of 2 * rows limb rows, a quarter of the ring-stage tile for one row),
+// and the CTAs that hold band group 0 also write the rotated activations and block sums for the caller and the
+// finishing kernel.
+template <int BITS, int NB, bool FUSED>
 __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_constant__ CUtensorMap tmap, const GemvArgs p)
 {
-    using G_ = GeoI8<BITS, NB>;
+    static_assert(!FUSED || NB == 1, "in-kernel rotation is built for one group of four rows");
+    using G_ = GeoI8<BITS, NB, FUSED>;
     constexpr int NW = G_::NW, BU = G_::BU, ROW_BYTES = G_::ROW_BYTES, W_BYTES = G_::W_BYTES, B_BYTES = G_::B_BYTES;
     constexpr int STAGE_BYTES = G_::STAGE_BYTES, S = G_::S, NA = G_::NA, TOK = G_::TOK, NCOL = G_::NCOL, PITCH = G_::PITCH;
     constexpr int CHUNK_BYTES = G_::CHUNK_BYTES, A_STAGE_COLS = G_::A_STAGE_COLS, D_COLS = G_::D_COLS;
@@ -170,14 +238,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
     unsigned char* ring = smem;
     float* outbuf = reinterpret_cast<float*>(ring + S * STAGE_BYTES);          // [TOK][PITCH]
     uint64_t* bars = reinterpret_cast<uint64_t*>(outbuf + G_::OUT_FLOATS);
+    unsigned char* area = reinterpret_cast<unsigned char*>(bars) + G_::kBarBytes;   // FUSED: limb tiles, then four scales per unit
     __shared__ uint32_t s_tmem_base;
+    // FUSED: limb rows per core matrix = 2 * frows, core matrices frows * 32 bytes apart
+    const int frows = p.m <= 1 ? 1 : (p.m == 2 ? 2 : 4);
+    const int flbo = 32 * frows, ftile = G_::fused_tile_bytes(frows);
 
     if (threadIdx.x == 0) stamp(0);
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bands = p.n >> 7, kblocks = p.k >> 7;
     const int bgroups = (bands + BU - 1) / BU;
-    const int nprob = p.problems ? min(max(__ldg(p.n_problems), 0), p.max_problems) : 1;
+    const int nprob = p.problems ? min(max(__ldg(p.n_problems), 0), p.max_problems) : (p.n_stack > 1 ? p.n_stack : 1);
     const long long U = (long long) nprob * bgroups * kblocks;
     const int cta = blockIdx.x;
     const int G = U < (long long) gridDim.x ? int(U) : int(gridDim.x);
@@ -194,7 +266,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, kDecodeWarps + 1 + kEpiWarps);   // decoding warps (trellis words), the MMAs (limb tile), epilogue warps (scales)
+            // decoding warps (trellis words); when the limb tiles travel through the ring also the MMAs (limb tile) and the
+            // epilogue warps (scales)
+            mbar_init(empty0 + 8 * s, FUSED ? kDecodeWarps : kDecodeWarps + 1 + kEpiWarps);
         }
         for (int s = 0; s < NA; ++s) {
             mbar_init(afull0 + 8 * s, kDecodeWarps);
@@ -210,11 +284,42 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    if (threadIdx.x == 0) stamp(6);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    if (threadIdx.x == 0) stamp(7);
     const uint32_t tmem_d = s_tmem_base;             // accumulators: [buffer][band][NCOL]
     const uint32_t tmem_a = tmem_d + D_COLS;         // weight stages: [NA][band][k-tile row of the half][16]
+    float* fscales = reinterpret_cast<float*>(area + size_t(nunits) * ftile + 512);   // FUSED: [unit][4]
+
+    if constexpr (FUSED) {
+        // In-kernel rotation: while the first weight stages are in flight, the decoding and the epilogue warps
+        // rotate and quantise the 128-block of every unit of the CTA (one warp per unit and row) into the limb area.
+        if (warp != kProducerWarp) {
+            if (warp != kMmaWarp) {
+                pdl_wait();   // the activations come from the preceding kernels
+                const int w20 = warp;   // decode warps 0..15, epilogue warps 16..19
+                for (int task = w20; task < nunits * p.m; task += kDecodeWarps + kEpiWarps) {
+                    const int j = task / p.m, t = task - j * p.m;
+                    const long long uu = u0 + j;
+                    const int gbg = int(uu / kblocks), kb = int(uu - (long long) gbg * kblocks);
+                    const int pi = gbg / bgroups, lbg = gbg - pi * bgroups;   // matrix of the stack, band group inside it
+                    float sx;
+                    const uint2 o = rotate_block<false>(p.a + size_t(t) * p.k, p.suh + size_t(pi) * p.k, kb, lane, sx);
+                    int isum;
+                    const float scale = quantise_block(o, lane, area + size_t(j) * ftile + t * 32, 2 * flbo, flbo, isum);
+                    if (lane == 0) fscales[j * 4 + t] = scale;
+                    if (lbg == 0) {   // band group 0 of a matrix meets every 128-block exactly once
+                        *reinterpret_cast<uint2*>(p.a_had + (size_t(pi) * p.m + t) * p.k + kb * 128 + lane * 4) = o;
+                        if (lane == 0) p.blocksum[(size_t(pi) * p.m + t) * kblocks + kb] = __fmul_rn(scale, __int2float_rn(isum));
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads the tiles through the async proxy
+            }
+            asm volatile("bar.sync 2, %0;" ::"n"((kDecodeWarps + kEpiWarps + 1) * 32) : "memory");   // tiles and scales are in place
+        }
+    }
 
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------ producer
@@ -230,7 +335,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
             auto issue_weights = [&](int i, uint32_t dst, uint32_t bar) {
                 int pi, lbg, kb;
                 coords(i, pi, lbg, kb);
-                const int z = p.problems ? load_problem(p.problems, pi, p.n_matrices, TOK, p.max_rows).z : 0;
+                const int z = p.problems ? load_problem(p.problems, pi, p.n_matrices, TOK, p.max_rows).z : pi;
                 tma_load_3d(dst, &tmap, lbg * (ROW_BYTES / 8), kb * 8, z, bar);
             };
             auto issue_limbs = [&](int i, uint32_t dst, uint32_t bar) {
@@ -241,21 +346,23 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
             // The weights do not depend on the rotation kernel: fill the ring with them first, then wait
             // for the limb tiles and complete those stages.
             const int pre = nunits < S ? nunits : S;
+            constexpr uint32_t kStageTx = FUSED ? W_BYTES : STAGE_BYTES;
             for (int i = 0; i < pre; ++i) {
-                mbar_arrive_expect_tx(full0 + 8 * i, STAGE_BYTES);
+                mbar_arrive_expect_tx(full0 + 8 * i, kStageTx);
                 issue_weights(i, smem_u32(ring + i * STAGE_BYTES), full0 + 8 * i);
             }
             stamp(1);
             pdl_wait();
             stamp(2);
-            for (int i = 0; i < pre; ++i) issue_limbs(i, smem_u32(ring + i * STAGE_BYTES + W_BYTES), full0 + 8 * i);
+            if constexpr (!FUSED)
+                for (int i = 0; i < pre; ++i) issue_limbs(i, smem_u32(ring + i * STAGE_BYTES + W_BYTES), full0 + 8 * i);
             int s = 0, lap = 1;
             for (int i = pre; i < nunits; ++i) {
                 mbar_wait_parked(empty0 + 8 * s, (lap - 1) & 1, p.status, kStEmptyTimeout);
-                mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                mbar_arrive_expect_tx(full0 + 8 * s, kStageTx);
                 const uint32_t dst = smem_u32(ring + s * STAGE_BYTES);
                 issue_weights(i, dst, full0 + 8 * s);
-                issue_limbs(i, dst + W_BYTES, full0 + 8 * s);
+                if constexpr (!FUSED) issue_limbs(i, dst + W_BYTES, full0 + 8 * s);
                 if (++s == S) { s = 0; ++lap; }
             }
         }
@@ -339,9 +446,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
         int s = 0, phase = 0, a_idx = 0, a_par = 0;
         for (int i = 0; i < nunits; ++i) {
             const int buf = i & 1;
-            mbar_wait_suspended(full0 + 8 * s, phase, p.status, kStFullTimeout);          // the unit's limb tile has landed
+            if constexpr (!FUSED) mbar_wait_suspended(full0 + 8 * s, phase, p.status, kStFullTimeout);   // the unit's limb tile has landed
             if (i >= 2) mbar_wait_suspended(dempty0 + 8 * buf, ((i >> 1) - 1) & 1, p.status, kStTmemTimeout);   // accumulator drained
-            const uint64_t b_desc0 = smem_desc_kmajor(smem_u32(ring + s * STAGE_BYTES + W_BYTES), kSbo);
+            const uint64_t b_desc0 = FUSED ? smem_desc_kmajor(smem_u32(area + size_t(i) * ftile), flbo, 2 * flbo)
+                                           : smem_desc_kmajor(smem_u32(ring + s * STAGE_BYTES + W_BYTES), 128, kSbo);
+            const uint32_t chunk_step = FUSED ? uint32_t(2 * flbo) >> 4 : uint32_t(CHUNK_BYTES) >> 4;
             const uint32_t d_base = tmem_d + buf * (BU * NCOL);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -357,12 +466,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
                             for (int j = 0; j < 2; ++j) {
                                 const int chunk = (4 * h + r) * 2 + j;
                                 tc_mma_ts_i8(d_base + b * NCOL, a_base + b * 64 + r * 16 + 8 * j,
-                                             b_desc0 + uint64_t((chunk * CHUNK_BYTES) >> 4), idesc, (h | r | j) ? 1u : 0u);
+                                             b_desc0 + uint64_t(chunk * chunk_step), idesc, (h | r | j) ? 1u : 0u);
                             }
                     tc_commit(aempty0 + 8 * a_idx);
                     if (h == 1) {
                         tc_commit(dfull0 + 8 * buf);
-                        tc_commit(empty0 + 8 * s);
+                        if constexpr (!FUSED) tc_commit(empty0 + 8 * s);
                     }
                 }
                 __syncwarp();
@@ -381,6 +490,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
         const int slab_rows = p.problems ? TOK : p.m;
         const size_t slab_floats = size_t(slab_rows) * BU * 128;
         int ui = 0, rs = 0, rphase = 0;
+        // In-kernel rotation: unit j's limb tile is written by these warps (warp ew takes row ew) into ring stage
+        // j % S once the stage's previous user has released it; they stay S - 1 units ahead of their own epilogue work.
         long long u = u0;
         while (u < u1) {
             const Segment sg = segment_at(u, u0, u1, kblocks);
@@ -410,35 +521,46 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
                 for (int t = 0; t < TOK; ++t) acc[b][t] = 0.f;
             for (int j = 0; j < sg.units; ++j, ++ui) {
                 const int buf = ui & 1;
-                // the unit's block scales travel with its limb tile
-                mbar_wait_suspended(full0 + 8 * rs, rphase, p.status, kStFullTimeout);
-                const float* scp = reinterpret_cast<const float*>(ring + rs * STAGE_BYTES + W_BYTES + G_::L_BYTES);
                 float sc[TOK];
+                if constexpr (FUSED) {
 #pragma unroll
-                for (int t = 0; t < TOK; ++t) sc[t] = t < rows ? scp[t] : 0.f;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(empty0 + 8 * rs);
-                if (++rs == S) { rs = 0; rphase ^= 1; }
+                    for (int t = 0; t < TOK; ++t) sc[t] = t < rows ? fscales[ui * 4 + t] : 0.f;
+                } else {
+                    // the unit's block scales travel with its limb tile
+                    mbar_wait_suspended(full0 + 8 * rs, rphase, p.status, kStFullTimeout);
+                    const float* scp = reinterpret_cast<const float*>(ring + rs * STAGE_BYTES + W_BYTES + G_::L_BYTES);
+#pragma unroll
+                    for (int t = 0; t < TOK; ++t) sc[t] = t < rows ? scp[t] : 0.f;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty0 + 8 * rs);
+                    if (++rs == S) { rs = 0; rphase ^= 1; }
+                }
                 mbar_wait_suspended(dfull0 + 8 * buf, (ui >> 1) & 1, p.status, kStTmemTimeout);
                 tc_fence_after();
                 const uint32_t d_base = tmem_d + buf * (BU * NCOL) + lane_base;
+                // the unit's s32 sums: column 2t = high-limb sum of row t, 2t+1 = low-limb sum; loads of a pass are
+                // issued together and waited for once
+                constexpr int LDW = 2 * TOK < 32 ? 2 * TOK : 32;             // columns per load
+                constexpr int PASSES = (2 * TOK) / LDW;
 #pragma unroll
-                for (int b = 0; b < BU; ++b) {
+                for (int ps = 0; ps < PASSES; ++ps) {
+                    int r[BU][LDW];
 #pragma unroll
-                    for (int c0 = 0; c0 < 2 * TOK; c0 += 8) {
-                        int r[8];
-                        tc_ld8(d_base + b * NCOL + c0, r);
-                        tc_wait_ld();
-#pragma unroll
-                        for (int tt = 0; tt < 4; ++tt) {
-                            const int t = c0 / 2 + tt;
-                            acc[b][t] = __fmaf_rn(sc[t], __int2float_rn(r[2 * tt] * 256 + r[2 * tt + 1]), acc[b][t]);
-                        }
+                    for (int b = 0; b < BU; ++b) tc_ld<LDW>(d_base + b * NCOL + ps * LDW, r[b]);
+                    tc_wait_ld();
+                    if (ps == PASSES - 1) {   // the accumulator buffer is in registers: hand it back before the arithmetic
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(dempty0 + 8 * buf);
                     }
+#pragma unroll
+                    for (int b = 0; b < BU; ++b)
+#pragma unroll
+                        for (int tt = 0; tt < LDW / 2; ++tt) {
+                            const int t = ps * (LDW / 2) + tt;
+                            acc[b][t] = __fmaf_rn(sc[t], __int2float_rn(r[b][2 * tt] * 256 + r[b][2 * tt + 1]), acc[b][t]);
+                        }
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(dempty0 + 8 * buf);
             }
             // the segment's sums: thread et owns column et of every band
             float* dst = sg.whole ? outbuf : p.slabs + size_t(sg.head ? 2 * cta : 2 * cta + 1) * slab_floats;
@@ -508,30 +630,9 @@ __global__ void __launch_bounds__(128) k_rotate_in_i8(const __half* __restrict__
         float sx;
         const uint2 o = rotate_block<false>(a + size_t(row) * k, suh, b, lane, sx);
         *reinterpret_cast<uint2*>(a_had + size_t(row) * k + b * 128 + lane * 4) = o;
-        const __half2 h01 = *reinterpret_cast<const __half2*>(&o.x), h23 = *reinterpret_cast<const __half2*>(&o.y);
-        const float hv[4] = {__low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23)};
-        float amax = fmaxf(fmaxf(fabsf(hv[0]), fabsf(hv[1])), fmaxf(fabsf(hv[2]), fabsf(hv[3])));
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(dq::kFull, amax, off));
-        const float scale = __fdiv_rn(amax, 32512.0f);
-        const float inv = amax > 0.f ? __fdiv_rn(32512.0f, amax) : 0.f;
-        int isum = 0;
-        const int kt = lane >> 2;
         const size_t record = size_t(16) * nb * 256 + 128;          // limbs, then the block's scales (one per row)
-        unsigned char* tile = limbs + size_t(b) * record + size_t(row >> 2) * 256 + (2 * (row & 3)) * 16;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int v = __float2int_rn(__fmul_rn(hv[e], inv));
-            isum += v;
-            const int hi = (v + 128) >> 8, lo = v - 256 * hi;
-            const int r = 4 * (lane & 3) + e;                       // input inside the k-tile row
-            const int chunk = kt * 2 + (r >> 3), c = ((r & 7) >> 1) + 4 * (r & 1);
-            unsigned char* w = tile + size_t(chunk) * nb * 256 + (c >> 2) * 128 + 4 * (c & 3);
-            *reinterpret_cast<uint32_t*>(w) = uint32_t(hi & 0xff) * 0x01010101u;
-            *reinterpret_cast<uint32_t*>(w + 16) = uint32_t(lo & 0xff) * 0x01010101u;
-        }
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) isum += __shfl_xor_sync(dq::kFull, isum, off);
+        int isum;
+        const float scale = quantise_block(o, lane, limbs + size_t(b) * record + size_t(row >> 2) * 256 + (2 * (row & 3)) * 16, nb * 256, 128, isum);
         if (lane == 0) {
             reinterpret_cast<float*>(limbs + size_t(b) * record + size_t(16) * nb * 256)[row] = scale;
             blocksum[size_t(row) * kblocks + b] = __fmul_rn(scale, __int2float_rn(isum));
@@ -539,11 +640,26 @@ __global__ void __launch_bounds__(128) k_rotate_in_i8(const __half* __restrict__
     }
 }
 
-template <int BITS, int NB>
+// Most units per CTA whose limb tiles fit the limb area of the in-kernel rotation.
+int fused_max_units(int k_bits, int rows)
+{
+    switch (k_bits) {
+        case 1: return GeoI8<1, 1, true>::fused_max_units(rows);
+        case 2: return GeoI8<2, 1, true>::fused_max_units(rows);
+        case 3: return GeoI8<3, 1, true>::fused_max_units(rows);
+        case 4: return GeoI8<4, 1, true>::fused_max_units(rows);
+        case 5: return GeoI8<5, 1, true>::fused_max_units(rows);
+        case 6: return GeoI8<6, 1, true>::fused_max_units(rows);
+        case 7: return GeoI8<7, 1, true>::fused_max_units(rows);
+        default: return GeoI8<8, 1, true>::fused_max_units(rows);
+    }
+}
+
+template <int BITS, int NB, bool FUSED>
 size_t launch_one(const void* trellis, int n_matrices, const GemvArgs& args, int grid, cudaStream_t stream)
 {
-    using G_ = GeoI8<BITS, NB>;
-    auto kern = k_exl3_gemv_i8<BITS, NB>;
+    using G_ = GeoI8<BITS, NB, FUSED>;
+    auto kern = k_exl3_gemv_i8<BITS, NB, FUSED>;
     static bool attr_set[kMaxDevices] = {};
     const int dev = current_device();
     if (!attr_set[dev]) {
@@ -556,27 +672,27 @@ size_t launch_one(const void* trellis, int n_matrices, const GemvArgs& args, int
 }
 
 template <int BITS>
-size_t launch_nb(int nb, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
+size_t launch_nb(int nb, bool fused, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
 {
     switch (nb) {
-        case 1: return launch_one<BITS, 1>(t, nm, a, grid, st);
-        case 2: return launch_one<BITS, 2>(t, nm, a, grid, st);
-        case 4: return launch_one<BITS, 4>(t, nm, a, grid, st);
-        default: return launch_one<BITS, 8>(t, nm, a, grid, st);
+        case 1: return fused ? launch_one<BITS, 1, true>(t, nm, a, grid, st) : launch_one<BITS, 1, false>(t, nm, a, grid, st);
+        case 2: return launch_one<BITS, 2, false>(t, nm, a, grid, st);
+        case 4: return launch_one<BITS, 4, false>(t, nm, a, grid, st);
+        default: return launch_one<BITS, 8, false>(t, nm, a, grid, st);
     }
 }
 
-size_t launch_bits(int k_bits, int nb, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
+size_t launch_bits(int k_bits, int nb, bool fused, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
 {
     switch (k_bits) {
-        case 1: return launch_nb<1>(nb, t, nm, a, grid, st);
-        case 2: return launch_nb<2>(nb, t, nm, a, grid, st);
-        case 3: return launch_nb<3>(nb, t, nm, a, grid, st);
-        case 4: return launch_nb<4>(nb, t, nm, a, grid, st);
-        case 5: return launch_nb<5>(nb, t, nm, a, grid, st);
-        case 6: return launch_nb<6>(nb, t, nm, a, grid, st);
-        case 7: return launch_nb<7>(nb, t, nm, a, grid, st);
-        case 8: return launch_nb<8>(nb, t, nm, a, grid, st);
+        case 1: return launch_nb<1>(nb, fused, t, nm, a, grid, st);
+        case 2: return launch_nb<2>(nb, fused, t, nm, a, grid, st);
+        case 3: return launch_nb<3>(nb, fused, t, nm, a, grid, st);
+        case 4: return launch_nb<4>(nb, fused, t, nm, a, grid, st);
+        case 5: return launch_nb<5>(nb, fused, t, nm, a, grid, st);
+        case 6: return launch_nb<6>(nb, fused, t, nm, a, grid, st);
+        case 7: return launch_nb<7>(nb, fused, t, nm, a, grid, st);
+        case 8: return launch_nb<8>(nb, fused, t, nm, a, grid, st);
         default: throw std::runtime_error("exl3 linear: K must be in 1..=8");
     }
 }
@@ -586,8 +702,9 @@ size_t launch_bits(int k_bits, int nb, const void* t, int nm, const GemvArgs& a,
 // Rotation + decode linear for up to 32 rows of a MUL1 matrix; same contract as launch_gemv.
 std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                            int size_m, int size_k, int size_n, int k_bits, int out_fp32, const GemvScratch& sc, int sms,
-                           cudaStream_t stream, unsigned long long* argmax)
+                           cudaStream_t stream, unsigned long long* argmax, int n_stack)
 {
+    if (n_stack < 1) n_stack = 1;
     if (size_m > 32) throw std::runtime_error("exl3 gemv: size_m must be <= 32");
     if (size_k % 128 != 0)
         throw std::runtime_error("exl3 linear: no linked kernel for size_k that is not a multiple of 128 (128-wide Hadamard)");
@@ -595,21 +712,30 @@ std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const vo
     const int nb = size_m <= 4 ? 1 : (size_m <= 8 ? 2 : (size_m <= 16 ? 4 : 8));
     const int bu = k_bits <= 4 ? 2 : 1;
     const int bands = size_n / 128, kblocks = size_k / 128, bgroups = (bands + bu - 1) / bu;
-    if (size_t(size_m) * kblocks > sc.blocksum_floats)
-        throw std::runtime_error("exl3 gemv: size_m * size_k / 128 exceeds the block-sum table of the scratch");
+    if (size_t(n_stack) * size_m * kblocks > sc.blocksum_floats)
+        throw std::runtime_error("exl3 gemv: matrices x size_m x size_k / 128 exceed the block-sum table of the scratch");
     const size_t limb_bytes = size_t(kblocks) * (size_t(16) * nb * 256 + 128);
-    if (limb_bytes > sc.afrag_bytes)
-        throw std::runtime_error("exl3 gemv: size_k * ceil(size_m / 4) exceeds the activation area of the scratch");
-    const long long units = (long long) bgroups * kblocks;
-    int grid = int(std::min<long long>(std::min<long long>(sms, units), (long long) bgroups * 16));
+    if (limb_bytes * n_stack > sc.afrag_bytes)
+        throw std::runtime_error("exl3 gemv: matrices x size_k x ceil(size_m / 4) exceed the activation area of the scratch");
+    const long long units = (long long) n_stack * bgroups * kblocks;
+    int grid = int(std::min<long long>(std::min<long long>(sms, units), (long long) n_stack * bgroups * 16));
     const size_t per_cta = size_t(2) * size_m * bu * 128 * sizeof(float);
     if (size_t(grid) * per_cta > sc.slab_bytes) grid = int(sc.slab_bytes / per_cta);
     if (grid < 1) throw std::runtime_error("exl3 gemv: split-K scratch is too small for this shape");
 
+    // In-kernel rotation for up to four rows when no CTA holds a whole band group (such a CTA finishes its bands
+    // itself and needs every block sum of the row, which other CTAs would still be writing).
+    const long long units_per_cta = (units + grid - 1) / grid;
+    const int frows = size_m <= 1 ? 1 : (size_m == 2 ? 2 : 4);
+    const bool fused = nb == 1 && units_per_cta < kblocks && units_per_cta <= fused_max_units(k_bits, frows);
     const int rot_total = size_m * kblocks;
-    launch_pdl(k_rotate_in_i8, dim3(std::min((rot_total + 3) / 4, 4 * sms)), dim3(128), 0, stream, "k_rotate_in_i8 launch",
-               static_cast<const __half*>(a), static_cast<const __half*>(suh), static_cast<__half*>(a_had),
-               reinterpret_cast<unsigned char*>(sc.afrag), sc.blocksum, size_m, size_k, nb);
+    if (!fused)
+        for (int i = 0; i < n_stack; ++i)
+            launch_pdl(k_rotate_in_i8, dim3(std::min((rot_total + 3) / 4, 4 * sms)), dim3(128), 0, stream, "k_rotate_in_i8 launch",
+                       static_cast<const __half*>(a), static_cast<const __half*>(suh) + size_t(i) * size_k,
+                       static_cast<__half*>(a_had) + size_t(i) * size_m * size_k,
+                       reinterpret_cast<unsigned char*>(sc.afrag) + size_t(i) * limb_bytes, sc.blocksum + size_t(i) * size_m * kblocks,
+                       size_m, size_k, nb);
 
     GemvArgs args{};
     args.afrag = sc.afrag;
@@ -624,10 +750,11 @@ std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const vo
     args.status = sc.status;
     args.m = size_m; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
-    args.max_problems = 1; args.n_matrices = 1; args.max_rows = size_m;
-    const size_t smem = launch_bits(k_bits, nb, trellis, 1, args, grid, stream);
+    args.max_problems = 1; args.n_matrices = n_stack; args.max_rows = size_m;
+    args.n_stack = n_stack;
+    const size_t smem = launch_bits(k_bits, nb, fused, trellis, n_stack, args, grid, stream);
     launch_finish(args, bu, 4 * nb, grid, 2, stream);
-    return "k_rotate_in_i8 + k_exl3_gemv_i8<" + std::to_string(k_bits) + "," + std::to_string(nb) + "> grid=" + std::to_string(grid) +
+ return std::string(fused ? "" : "k_rotate_in_i8 + ") + "k_exl3_gemv_i8<" + std::to_string(k_bits) + "," + std::to_string(nb) + (fused ? ",fused" : "") + (n_stack > 1 ? ",stack of " + std::to_string(n_stack) : "") + "> grid=" + std::to_string(grid) +
            " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem) + " + k_gemv_finish";
 }
 

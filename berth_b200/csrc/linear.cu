@@ -114,6 +114,30 @@ extern "C" int berth_exl3_linear_argmax(const void* a, const void* trellis, void
     });
 }
 
+// A stack of equally shaped MUL1 matrices applied to the same rows in one launch (gate and up of an MLP stored
+// one behind the other): the units of all matrices share one persistent decode launch, so launch latency, pipeline
+// ramp and the finishing kernel are paid once.
+extern "C" int berth_exl3_linear_stack(const void* a, const void* trellis_stack, void* c, const void* suh_stack, void* a_had,
+                                       const void* svh_stack, int n_matrices, int size_m, int size_k, int size_n, int k_bits,
+                                       int codebook, int out_fp32, void* stream)
+{
+    CallState& st = exl3_state();
+    return guarded(st, [&] {
+        if (!a || !trellis_stack || !c || !suh_stack || !a_had || !svh_stack) throw std::runtime_error("exl3 linear stack: null device pointer");
+        if (size_m < 1 || size_k < 1 || size_n < 1) throw std::runtime_error("exl3 linear stack: sizes must be positive");
+        if (n_matrices < 1 || n_matrices > 16) throw std::runtime_error("exl3 linear stack: n_matrices must be in 1..=16");
+        check_linear_args("exl3 linear stack", a, trellis_stack, c, suh_stack, a_had, svh_stack, size_k, size_n, k_bits, codebook);
+        if (codebook != 2 || size_m > 32)
+            throw std::runtime_error("exl3 linear stack: no linked kernel (MUL1 codebook and size_m <= 32 only)");
+        const int device = current_device();
+        const DeviceInfo& info = device_info(device);
+        if (info.major != 10)
+            throw std::runtime_error("exl3 linear stack: no linked kernel for this GPU (library is built for sm_100a only)");
+        st.launch = launch_gemv_i8(a, trellis_stack, c, suh_stack, a_had, svh_stack, size_m, size_k, size_n, k_bits, out_fp32,
+                                   gemv_workspace(device), info.sms, (cudaStream_t) stream, nullptr, n_matrices);
+    });
+}
+
 extern "C" void berth_argmax_key_decode(unsigned long long key, int32_t* token, float* value)
 {
     const uint32_t ord = uint32_t(key >> 32);

@@ -83,6 +83,16 @@ def exl3_linear_static_scratch(a, trellis, c, suh, a_had, svh, size_m: int, size
         raise Error(last_error() or f"exl3 linear (static scratch) launch failed ({rc})")
 
 
+def exl3_linear_stack(a, trellis_stack, c, suh_stack, a_had, svh_stack, n_matrices: int, size_m: int, size_k: int, size_n: int,
+                      k_bits: int, codebook: Codebook, out: OutDtype, stream=None) -> None:
+    """``n_matrices`` equally shaped MUL1 linears (stored one behind the other) applied to the same ``size_m <= 32`` rows in
+    one decode launch; ``c`` is ``[n_matrices][size_m][size_n]``, ``a_had`` ``[n_matrices][size_m][size_k]``."""
+    rc = _lib.lib().berth_exl3_linear_stack(_ptr(a), _ptr(trellis_stack), _ptr(c), _ptr(suh_stack), _ptr(a_had), _ptr(svh_stack),
+                                            n_matrices, size_m, size_k, size_n, k_bits, int(codebook), int(out), _stream(stream))
+    if rc != 0:
+        raise Error(last_error() or f"exl3 linear stack launch failed ({rc})")
+
+
 def exl3_linear_argmax(a, trellis, c, suh, a_had, svh, best, size_m: int, size_k: int, size_n: int, k_bits: int,
                        codebook: Codebook, out: OutDtype, stream=None) -> None:
     """:func:`exl3_linear` (``size_m <= 32``) that also leaves, in the device array ``best`` (``size_m`` 64-bit keys),

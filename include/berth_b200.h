@@ -112,6 +112,16 @@ int berth_exl3_linear_argmax(const void* a, const void* trellis, void* c, const 
                              int out_fp32, void* stream);
 void berth_argmax_key_decode(unsigned long long key, int32_t* token, float* value);
 
+/* A stack of n_matrices equally shaped MUL1 linears applied to the same size_m <= 32 rows in ONE decode launch:
+ * trellis_stack int16 [n][size_k/16][size_n/16][16*k_bits], suh_stack fp16 [n][size_k], svh_stack fp16 [n][size_n];
+ * outputs c [n][size_m][size_n] and a_had [n][size_m][size_k].  What berth does for the gate and up projections of
+ * an MLP with two berth_exl3_linear calls (crates/berth-engine/src/mlp.rs:118-150); a host that stores the two
+ * projections one behind the other saves a launch, a pipeline ramp and a finishing kernel.  No counterpart in berth.
+ * Other codebooks or more rows fail closed ("no linked kernel"). */
+int berth_exl3_linear_stack(const void* a, const void* trellis_stack, void* c, const void* suh_stack, void* a_had,
+                            const void* svh_stack, int n_matrices, int size_m, int size_k, int size_n, int k_bits,
+                            int codebook, int out_fp32, void* stream);
+
 /* ------------------------------------------------------------------ prefill linear (m > 1)
  * Replaces berth_prefill_exl3_linear (crates/berth-kernels/src/prefill_lin.rs:37-52,
  * crates/berth-kernels/csrc/prefill_lin/linear.cu:232-381).  w_scratch (fp16,
