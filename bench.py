@@ -11,7 +11,9 @@ Metric: effective HBM GB/s on the algorithmic bytes of the pass (trellis + sign-
 + activations in/out), value = bytes moved by all ranks / device time (CUDA events, max over
 ranks).  `e2e` is the same metric through the host-buffer API: pinned host activations are
 copied in and the results read back every step.  `roofline` is measured live for the dominant
-kernel (the gate/up GEMV).  `cpu_baseline` times the CPU oracle on a bounded sample.
+kernel (the decode launch over the stacked gate and up projections).  `cpu_baseline` times the CPU oracle on a
+bounded sample.  Extra records of the same line: the step at 8 and 32 rows, configuration 0 (one 5120x6144 linear
+over a ring of 17 seeded copies), prefill (configuration 2), lm_head, MoE (configuration 3 / 4).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--m M] [--impl reference]
 """
@@ -40,9 +42,9 @@ SHAPES = [("gate", HIDDEN, INTER, 0, "x"), ("up", HIDDEN, INTER, 0, "x"), ("down
 LAYERS = 4
 METRIC = "exl3_gemv_eff_hbm_gbs"
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_exl3_gemv launch on the gate shape
-# (5120x17408, 4 bpw, m=1), from the ncu capture summarised in profiles/k_exl3_gemv_c1_dense_decode_m1.md.
-NCU_TRAFFIC_GATE_BYTES = 44_738_560   # 44.72 MB read + 15 KB written
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch over the stacked gate and up projections
+# (2 x 5120x17408, 4 bpw, one row) from an ncu capture of this file's own step; valid for one row only.
+NCU_TRAFFIC_GATE_UP_BYTES = None
 
 
 def linear_bytes(k: int, n: int, m: int, fp32: int, bits: int = BITS) -> int:
@@ -112,8 +114,9 @@ class DecodeStack:
     """LAYERS layers of the seven 27B-shaped EXL3 linears, resident in HBM, with the host-side
     callers of berth_b200.engine (Exl3Linear / MlpLayer)."""
 
-    def __init__(self, m: int, rank: int):
-        """m = token rows per step (buffers are sized for it)."""
+    def __init__(self, m: int, rank: int, share: "DecodeStack | None" = None):
+        """m = token rows per step (buffers are sized for it); `share` = a stack whose weights (already in HBM) this
+        one uses too."""
         import torch
         from berth_b200 import synth
         from berth_b200.engine import Exl3Linear, Gpu, MlpLayer, SlicedMultiLinear
@@ -154,7 +157,11 @@ class DecodeStack:
         for l in range(LAYERS):
             lin = {}
             for name, k, n, _, _ in SHAPES:
-                w = synth.linear_weights(synth.MASTER_SEED, f"r{rank}.layers.{l}.{name}", k, n, BITS, fan_in_gain=True)
+                if share is not None:
+                    src = share.layers[l][1][name]
+                    w = {"trellis": src.trellis, "suh": src.suh, "svh": src.svh}
+                else:
+                    w = synth.linear_weights(synth.MASTER_SEED, f"r{rank}.layers.{l}.{name}", k, n, BITS, fan_in_gain=True)
                 lin[name] = Exl3Linear(self.gpu, f"layers.{l}.{name}", w["trellis"], w["suh"], w["svh"], BITS,
                                        Codebook(CB), max_rows=m)
             mlp = MlpLayer(self.gpu, lin["gate"], lin["up"], lin["down"], max_rows=m)
@@ -163,9 +170,11 @@ class DecodeStack:
             lin["qkv"] = SlicedMultiLinear(self.gpu, [lin["q"], lin["k"], lin["v"]], OutDtype.F16, max_rows=m,
                                            outputs=[self.q, self.k, self.v])
             self.layers.append((mlp, lin))
-        # gate, up, down, o: k_exl3_gemv + k_gemv_finish each (k_rotate_in in front above two rows); q/k/v: one
-        # k_rotate_in + k_exl3_gemv + k_gemv_finish for the three; one k_silu_mul
-        self.launches_per_step = 12 if m <= 2 else 16
+        # up to 4 rows: gate+up (one stacked launch), down, o: decode kernel + k_gemv_finish each, no rotation kernel;
+        # q/k/v: k_rotate_in + k_exl3_gemv + k_gemv_finish for the three; one k_silu_mul = 10 launches.
+        # 5..8 rows: + one rotation kernel per matrix of the stacked launch, and one each for down and o = 14.
+        # above: gate, up, down, o with k_rotate_in + k_exl3_gemv + k_gemv_finish each, q/k/v, silu = 16.
+        self.launches_per_step = 10 if m <= 4 else (14 if m <= 8 else 16)
 
     def step(self, i: int) -> None:
         from berth_b200.kernels import OutDtype
@@ -182,24 +191,101 @@ class DecodeStack:
         self.h_out.copy_(self.d_out, non_blocking=True)
         self.torch.cuda.current_stream().synchronize()
 
-    def time_gate_kernel(self, reps: int) -> float:
-        """Average duration (ms) of one k_exl3_gemv launch on the gate/up shape: 2*LAYERS distinct
-        44.6 MB matrices (357 MB > L2) launched back to back between two CUDA events."""
+    def time_dominant_kernel(self, reps: int):
+        """(average ms, algorithmic bytes, description) of the step's dominant launch, run back to back over the
+        LAYERS distinct layers (357 MB of gate and up weights > L2) between two CUDA events: up to eight rows the
+        decode launch over the stacked gate and up projections, above the gate linear alone."""
         torch = self.torch
+        from berth_b200 import kernels
         from berth_b200.kernels import OutDtype
-        mats = [l[1][n] for l in self.layers for n in ("gate", "up")]
-        out = self.layers[0][0].gate_out
-        for lin in mats:
+        stacked = self.layers[0][0].gate_up is not None and self.m <= 8
+        if stacked:
+            calls = [(l[0].gate_up, l[0].gate_up_out) for l in self.layers]
+            nbytes = 2 * linear_bytes(HIDDEN, INTER, self.m, 0) - 2 * self.m * HIDDEN   # the rows are read once
+            what = "gate and up 2 x 5120x17408 as one stacked decode launch"
+        else:
+            calls = [(l[1][n], l[0].gate_out) for l in self.layers for n in ("gate", "up")]
+            nbytes = linear_bytes(HIDDEN, INTER, self.m, 0)
+            what = "gate/up 5120x17408"
+        for lin, out in calls:
             lin.forward_n(self.gpu, self.m, self.x, out, OutDtype.F16)
+        name = kernels.last_launch()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         e0.record()
         for _ in range(reps):
-            for lin in mats:
+            for lin, out in calls:
                 lin.forward_n(self.gpu, self.m, self.x, out, OutDtype.F16)
         e1.record()
         torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / (reps * len(mats))
+        return e0.elapsed_time(e1) / (reps * len(calls)), nbytes, what, name
+
+    def time_steps(self, steps: int, warmup: int) -> float:
+        """ms per step, device timed."""
+        torch = self.torch
+        for i in range(warmup):
+            self.step(i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(steps):
+            self.step(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+
+def bench_rows(base: "DecodeStack", rank: int, m: int, steps: int) -> dict:
+    """The same step at m rows on the weights of `base`: value and the dominant launch's roofline entry."""
+    st = DecodeStack(m, rank, share=base)
+    ms = st.time_steps(steps, 5)
+    k_ms, k_bytes, what, name = st.time_dominant_kernel(max(4, steps // 8))
+    peak, kind = peaks()
+    sb = step_bytes(m)
+    return {"m": m, "us_per_step": ms * 1e3, "value": sb / (ms * 1e-3) / 1e9, "unit": "GB/s", "bytes_per_step": sb,
+            "frac_of_hbm_peak": sb / (ms * 1e-3) / 1e9 / peak, "gpu_launches_per_step": st.launches_per_step,
+            "roofline": {"bound": "hbm", "achieved": k_bytes / (k_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": k_bytes / (k_ms * 1e-3) / 1e9 / peak, "traffic": None, "kernel": name,
+                         "launch": f"{what} m={m}: {k_bytes} algorithmic bytes in {k_ms * 1e3:.2f} us", "peak_kind": f"of {kind}"}}
+
+
+def bench_c0(rank: int, reps: int = 12) -> dict:
+    """Configuration 0: one 5120 x 6144 linear, 4 bpw, one row, fp16 out, over a ring of 17 seeded weight copies
+    (267 MB > L2); 17 * reps launches between two CUDA events, median of 5 repeats."""
+    import torch
+    from berth_b200 import synth
+    from berth_b200.engine import Exl3Linear, Gpu
+    from berth_b200.kernels import Codebook, OutDtype
+    from berth_b200 import kernels
+    K, N, ring = 5120, 6144, 17
+    gpu = Gpu(torch.cuda.current_device())
+    lins = []
+    for i in range(ring):
+        w = synth.linear_weights(synth.MASTER_SEED, f"r{rank}.c0.{i}", K, N, BITS)
+        lins.append(Exl3Linear(gpu, f"c0.{i}", w["trellis"], w["suh"], w["svh"], BITS, Codebook(CB), max_rows=1))
+    x = torch.from_numpy(synth.activations(1234, f"r{rank}.c0.x", 1, K)).to(gpu.device)
+    c = torch.empty((1, N), dtype=torch.float16, device=gpu.device)
+    for lin in lins:
+        lin.forward_n(gpu, 1, x, c, OutDtype.F16)
+    name = kernels.last_launch()
+    times = []
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            for lin in lins:
+                lin.forward_n(gpu, 1, x, c, OutDtype.F16)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / (reps * ring))
+    ms = statistics.median(times)
+    nbytes = linear_bytes(K, N, 1, 0)
+    peak, kind = peaks()
+    return {"workload": "c0_single_linear_5120x6144_4bpw_m1", "us_per_launch": ms * 1e3, "launches_timed": reps * ring,
+            "ring": f"{ring} seeded copies, {ring * K * N // 2 / 1e6:.0f} MB", "bytes_per_launch": nbytes,
+            "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": nbytes / (ms * 1e-3) / 1e9 / peak, "traffic": None, "kernel": name, "peak_kind": f"of {kind}"}}
 
 
 # ------------------------------------------------------------------ lm_head regime
@@ -537,7 +623,7 @@ def main() -> None:
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
     # ---- dominant kernel alone
-    gate_ms = stack.time_gate_kernel(max(4, args.steps // 8))
+    gate_ms, gate_bytes, gate_what, gate_name = stack.time_dominant_kernel(max(4, args.steps // 8))
     # nvidia-smi samples every 100 ms; a short timed region ends before the first sample, so the same
     # step loop is repeated for about 1.5 s under the sampler (same kernels, same clocks regime).
     t_end = time.perf_counter() + 1.5
@@ -551,6 +637,9 @@ def main() -> None:
     clocks = sampler.stop() if rank == 0 else None
     if clocks is not None:
         clocks["window"] = "timed region + end-to-end region + 1.5 s repeat of the same step loop"
+    extras = rank == 0 and not args.no_extras
+    rows_extra = [bench_rows(stack, rank, mm, max(20, args.steps // 4)) for mm in (8, 32) if mm != args.m] if extras else None
+    c0 = bench_c0(rank) if extras else None
     prefill = bench_prefill(rank) if (rank == 0 and not args.no_extras) else None
     lm_head = bench_lm_head(rank) if (rank == 0 and not args.no_extras) else None
     moe_res = None if args.no_extras else bench_moe(rank, world)
@@ -565,7 +654,6 @@ def main() -> None:
         value = sb * args.steps * world / (ms * 1e-3) / 1e9
         e2e = sb * args.steps * world / (e2e_ms * 1e-3) / 1e9
         peak, peak_kind = peaks()
-        gate_bytes = linear_bytes(HIDDEN, INTER, args.m, 0)
         achieved = gate_bytes / (gate_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
@@ -579,13 +667,14 @@ def main() -> None:
             "frac_of_hbm_peak": value / world / peak, "peak_kind": peak_kind,
             "tokens_per_s": args.m * args.steps * world / (ms * 1e-3),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_GATE_BYTES, "kernel": "k_exl3_gemv<4,2,mg>",
-                         "launch": f"gate/up 5120x17408 m={args.m}: {gate_bytes} algorithmic bytes in {gate_ms * 1e3:.2f} us",
+                         "traffic": NCU_TRAFFIC_GATE_UP_BYTES if args.m == 1 else None, "kernel": gate_name,
+                         "launch": f"{gate_what} m={args.m}: {gate_bytes} algorithmic bytes in {gate_ms * 1e3:.2f} us",
                          "peak_kind": f"of {peak_kind}"},
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": stack.h2d_bytes,
                     "d2h_bytes_per_step": stack.d2h_bytes, "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": stack.launches_per_step * args.steps,
             "clocks": clocks,
+            "rows": rows_extra, "c0": c0,
             "prefill": prefill, "lm_head": lm_head,
             "moe": moe_res,
         }

@@ -97,12 +97,15 @@ struct GemvScratch {
     size_t afrag_bytes = 0;
     float* blocksum = nullptr;
     size_t blocksum_floats = 0;
+    unsigned* counters = nullptr;  // integer tensor path: arrival counters of the band groups (zero between launches)
+    size_t counter_words = 0;
     unsigned* status = nullptr;
 };
 // The library's own scratch: allocated once per device at first use, never grown, never freed
 // (cf. crates/berth-kernels/csrc/int8_sq.cu:20-47 of berth).
 constexpr size_t kGemvSlabBytes = size_t(32) << 20;
 constexpr size_t kGemvBlocksumFloats = size_t(32) * 4096;
+constexpr size_t kGemvCounterWords = size_t(1) << 16;
 constexpr size_t kGemvAfragBytes = size_t(8) << 20;   // size_k * ceil(size_m / 8) <= 524288
 GemvScratch gemv_workspace(int device);
 
@@ -195,10 +198,16 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32,
                         const GemvScratch& scratch, int sms, cudaStream_t stream, unsigned long long* argmax = nullptr);
 
-// The same linear for the MUL1 codebook on the integer tensor path (gemv_i8.cu); launch_gemv forwards to it.
+// The same linear for the MUL1 codebook on the integer tensor path (gemv_i8.cu), up to kI8MaxRows rows; launch_gemv
+// forwards one to four rows to it (above, the limb tiles of the rows cost more L2 traffic than the fp16 path's
+// fragments), berth_exl3_linear_stack up to eight.
+constexpr int kI8MaxRows = 8;
 std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                            int size_m, int size_k, int size_n, int k_bits, int out_fp32, const GemvScratch& scratch, int sms,
                            cudaStream_t stream, unsigned long long* argmax, int n_stack = 1);
+
+// True when launch_gemv_i8 would rotate the activations inside the decode kernel for this dense shape.
+bool gemv_i8_rotates_in_kernel(int size_m, int size_k, int size_n, int k_bits, int sms);
 
 constexpr float kRScale = 0.088388347648f;  // 1/sqrt(128), csrc/prefill_lin/reconstruct.cu:43-44
 

@@ -662,7 +662,9 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     if (size_k % 128 != 0)
         throw std::runtime_error("exl3 linear: no linked kernel for size_k that is not a multiple of 128 (128-wide Hadamard)");
     if (k_bits < 1 || k_bits > 8) throw std::runtime_error("exl3 linear: K must be in 1..=8");
-    if (codebook == 2)   // MUL1: integer tensor path with the weights in tensor memory
+    // MUL1, one row, every CTA's units within the limb area of the in-kernel rotation: integer tensor path with the
+    // weights in tensor memory (measured a few percent ahead of this kernel there, behind it elsewhere)
+    if (codebook == 2 && size_m == 1 && gemv_i8_rotates_in_kernel(size_m, size_k, size_n, k_bits, sms))
         return launch_gemv_i8(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, out_fp32, sc, sms, stream, argmax);
     const int tg = size_m <= 8 ? 1 : (size_m <= 16 ? 2 : 4);
     const int bu = k_bits <= 4 ? 2 : 1;   // bands per unit, as Geo<BITS, TG>::BU
@@ -703,6 +705,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     args.argmax = argmax;
     args.svh = static_cast<const __half*>(svh);
     args.slabs = sc.slabs;
+    args.counters = nullptr;
     args.status = sc.status;
     args.m = size_m; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
@@ -765,6 +768,7 @@ std::string launch_gemv_grouped_rotated(const void* trellis_stack, int n_experts
     args.n_matrices = n_experts;
     args.max_rows = max_rows;
     args.slabs = sc.slabs;
+    args.counters = nullptr;
     args.status = sc.status;
     args.m = 8 * tg; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
@@ -836,6 +840,7 @@ std::string launch_gemv_sliced(const void* a, const void* b_list, const void* su
     args.n_problems = nullptr;
     args.max_problems = n_slices; args.n_matrices = 1; args.max_rows = size_m;
     args.slabs = sc.slabs;
+    args.counters = nullptr;
     args.status = sc.status;
     args.m = size_m; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
@@ -880,8 +885,9 @@ constexpr int kStaticMaxRows = 32;
 constexpr int kStaticMaxKBlocks = 1024;                // size_k <= 131072
 constexpr size_t kStaticBlocksumBytes = size_t(kStaticMaxRows) * kStaticMaxKBlocks * sizeof(float);
 constexpr size_t kStaticAfragBytes = size_t(2) << 20;   // size_k * ceil(size_m / 8) <= 131072
+constexpr size_t kStaticCounterWords = 4096;             // band groups of the integer tensor path
 
-static __device__ __align__(256) unsigned char g_static_scratch[kStaticSlabBytes + kStaticAfragBytes + kStaticBlocksumBytes + 256];
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticSlabBytes + kStaticAfragBytes + kStaticBlocksumBytes + kStaticCounterWords * 4 + 256];
 
 GemvScratch g_static_ptr[kMaxDevices];
 std::mutex g_static_mu;
@@ -906,6 +912,9 @@ GemvScratch static_scratch(int device)
         s.blocksum = reinterpret_cast<float*>(b);
         s.blocksum_floats = size_t(kStaticMaxRows) * kStaticMaxKBlocks;
         b += kStaticBlocksumBytes;
+        s.counters = reinterpret_cast<unsigned*>(b);   // (a __device__ array starts out zeroed)
+        s.counter_words = kStaticCounterWords;
+        b += kStaticCounterWords * 4;
         s.status = reinterpret_cast<unsigned*>(b);
     }
     return s;

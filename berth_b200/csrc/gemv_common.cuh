@@ -32,6 +32,7 @@ struct GemvArgs {
     const int* n_problems;         // grouped launch: device-side count
     int max_problems, n_matrices, max_rows;   // bounds the table entries are clamped to
     float* slabs;             // [2*G][m][BU*128]
+    unsigned* counters;       // integer tensor path: one arrival counter per band group, zero between launches
     unsigned* status;
     int m, k, n, out_fp32;
     // Sliced multi-linear (several column slices of several matrices applied to one input): device arrays

@@ -1,4 +1,4 @@
-// EXL3 decode linear for the MUL1 codebook (size_m <= 32) on the 5th-generation tensor cores'
+// EXL3 decode linear for the MUL1 codebook (size_m <= 8) on the 5th-generation tensor cores'
 // integer path, with the decoded weights in TENSOR MEMORY.
 //
 // Why a second decode kernel.  On this SM the legacy warp-level MMA (mma.sync) executes on the same
@@ -23,15 +23,15 @@
 // Work decomposition, TMA ring, split-K slabs and the finishing kernel are those of gemv.cu: units of
 // 128 inputs x BU*128 outputs in band-group-major order, CTA c takes a contiguous range.  Inside a CTA
 // (22 warps, one CTA per SM):
-//   warp 20      TMA producer: per unit one 3-D box of trellis words and one bulk copy of the unit's
-//                activation limbs into a ring stage;
+//   warp 20      TMA producer: per unit one 3-D box of trellis words into a ring stage, and (unless the CTA
+//                rotates its activations itself, see FUSED below) one bulk copy of the unit's activation limbs;
 //   warps 0..15  decode: warp (quarter q, stream s) takes tile columns 2q, 2q+1 of one band -- the
 //                output columns whose TMEM lanes it may write -- for half of the unit's k-tile rows:
 //                shared-memory words -> eight states -> eight products x -> one tcgen05.st per tile
 //                (the lane layout of the tile format is the 16x128b store shape); the eight warps of a
 //                half-unit fill one tensor-memory stage and hand it over through an mbarrier;
 //   warp 21      allocates tensor memory; one elected lane issues per half-unit stage BU*8 MMAs
-//                (M = 128 output columns, N = 16..64 limb columns, K = 32 bytes = 8 weights), A from
+//                (M = 128 output columns, N = 16 limb columns, K = 32 bytes = 8 weights), A from
 //                tensor memory, B = the limb tile in shared memory (K-major, no swizzle), D = s32 in
 //                tensor memory, double buffered per unit; commits release the stage, the ring stage
 //                and publish the accumulator;
@@ -86,10 +86,10 @@ struct GeoI8 {
     static constexpr int AREA_BYTES = FUSED ? RING_MAX - S * STAGE_BYTES : 0;
     static constexpr size_t SMEM = 1024 + size_t(S) * STAGE_BYTES + OUT_FLOATS * 4 + kBarBytes + AREA_BYTES;
     // in-kernel rotation: a unit's limb tile holds 2*rows limb rows per core matrix (rows = 1, 2 or 4), core
-    // matrices 32*rows bytes apart, 16 k-steps of two core matrices, plus four scales; 512 bytes of the area stay
+    // matrices 32*rows bytes apart, 16 k-steps of two core matrices, plus four scales and four block sums; 512 bytes of the area stay
     // free because the MMA reads whole 8-row core matrices (the rows past 2*rows are never used)
     __host__ __device__ static constexpr int fused_tile_bytes(int rows) { return 1024 * rows; }
-    __host__ __device__ static constexpr int fused_max_units(int rows) { return (AREA_BYTES - 512) / (fused_tile_bytes(rows) + 16); }
+    __host__ __device__ static constexpr int fused_max_units(int rows) { return (AREA_BYTES - 512) / (fused_tile_bytes(rows) + 32); }
     static_assert(S >= 2 && NA >= 2, "ring and tensor-memory stages");
     static_assert(W_BYTES % 128 == 0 && STAGE_BYTES % 128 == 0, "TMA destination alignment");
     static_assert((2 * S + 2 * NA + 4) * 8 <= kBarBytes, "barrier area");
@@ -204,19 +204,6 @@ __device__ __forceinline__ float quantise_block(uint2 o, int lane, unsigned char
     return scale;
 }
 
-#ifdef BERTH_I8_STAMPS
-__device__ unsigned long long g_i8_ts[256 * 8];
-__device__ __forceinline__ void stamp(int slot) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); g_i8_ts[blockIdx.x * 8 + slot] = t; }
-__device__ long long g_i8_ph[256 * 16 * 4];
-#define PH_DECL long long ph_t = clock64(), ph_acc[4] = {0, 0, 0, 0};
-#define PH_MARK(k) { const long long now_ = clock64(); ph_acc[k] += now_ - ph_t; ph_t = now_; }
-#define PH_STORE if (lane == 0) { for (int k_ = 0; k_ < 4; ++k_) g_i8_ph[(blockIdx.x * 16 + warp) * 4 + k_] = ph_acc[k_]; }
-#else
-__device__ __forceinline__ void stamp(int) {}
-#define PH_DECL
-#define PH_MARK(k)
-#define PH_STORE
-#endif
 // ---------------------------------------------------------------- the kernel
 // FUSED (one group of four rows, dense launches in which no CTA holds a whole band group and every CTA's units fit
 // the limb area): no rotation kernel runs before this one and no limb tile travels through L2; while the first weight
@@ -244,7 +231,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
     const int frows = p.m <= 1 ? 1 : (p.m == 2 ? 2 : 4);
     const int flbo = 32 * frows, ftile = G_::fused_tile_bytes(frows);
 
-    if (threadIdx.x == 0) stamp(0);
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bands = p.n >> 7, kblocks = p.k >> 7;
@@ -263,9 +249,37 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
     const uint32_t afull0 = empty0 + 8 * S, aempty0 = afull0 + 8 * NA;
     const uint32_t dfull0 = aempty0 + 8 * NA, dempty0 = dfull0 + 16;
 
+    // The weights are the long pole of a short launch: one lane of the producer warp arms the ring's "full" barriers
+    // and issues the first stages' TMA copies before anything else in the CTA happens.
+    int pr_pi = 0, pr_lbg = 0, pr_kb = 0;   // producer lane: matrix, band group and 128-block of the next unit to fetch
+    const int pre = nunits < S ? nunits : S;
+    constexpr uint32_t kStageTx = FUSED ? W_BYTES : STAGE_BYTES;
+    auto issue_weights = [&](uint32_t dst, uint32_t bar) {
+        const int z = p.problems ? load_problem(p.problems, pr_pi, p.n_matrices, TOK, p.max_rows).z : pr_pi;
+        tma_load_3d(dst, &tmap, pr_lbg * (ROW_BYTES / 8), pr_kb * 8, z, bar);
+    };
+    auto next_unit = [&]() {
+        if (++pr_kb == kblocks) {
+            pr_kb = 0;
+            if (++pr_lbg == bgroups) { pr_lbg = 0; ++pr_pi; }
+        }
+    };
+    if (warp == kProducerWarp && lane == 0) {
+        for (int s = 0; s < S; ++s) mbar_init(full0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
+        const unsigned gbg = unsigned(u0 / kblocks);
+        pr_kb = int(u0 - (long long) gbg * kblocks);
+        pr_pi = int(gbg / unsigned(bgroups));
+        pr_lbg = int(gbg - unsigned(pr_pi) * unsigned(bgroups));
+        for (int i = 0; i < pre; ++i) {
+            mbar_arrive_expect_tx(full0 + 8 * i, kStageTx);
+            issue_weights(smem_u32(ring + i * STAGE_BYTES), full0 + 8 * i);
+            if (FUSED || i + 1 < pre) next_unit();   // (the limb tiles of these stages follow below, from the same coordinates)
+        }
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
-            mbar_init(full0 + 8 * s, 1);
             // decoding warps (trellis words); when the limb tiles travel through the ring also the MMAs (limb tile) and the
             // epilogue warps (scales)
             mbar_init(empty0 + 8 * s, FUSED ? kDecodeWarps : kDecodeWarps + 1 + kEpiWarps);
@@ -284,14 +298,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (threadIdx.x == 0) stamp(6);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (threadIdx.x == 0) stamp(7);
     const uint32_t tmem_d = s_tmem_base;             // accumulators: [buffer][band][NCOL]
     const uint32_t tmem_a = tmem_d + D_COLS;         // weight stages: [NA][band][k-tile row of the half][16]
-    float* fscales = reinterpret_cast<float*>(area + size_t(nunits) * ftile + 512);   // FUSED: [unit][4]
+    float* fscales = reinterpret_cast<float*>(area + size_t(nunits) * ftile + 512);   // FUSED: [unit][4 scales, 4 block sums]
 
     if constexpr (FUSED) {
         // In-kernel rotation: while the first weight stages are in flight, the decoding and the epilogue warps
@@ -309,11 +321,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
                     const uint2 o = rotate_block<false>(p.a + size_t(t) * p.k, p.suh + size_t(pi) * p.k, kb, lane, sx);
                     int isum;
                     const float scale = quantise_block(o, lane, area + size_t(j) * ftile + t * 32, 2 * flbo, flbo, isum);
-                    if (lane == 0) fscales[j * 4 + t] = scale;
-                    if (lbg == 0) {   // band group 0 of a matrix meets every 128-block exactly once
-                        *reinterpret_cast<uint2*>(p.a_had + (size_t(pi) * p.m + t) * p.k + kb * 128 + lane * 4) = o;
-                        if (lane == 0) p.blocksum[(size_t(pi) * p.m + t) * kblocks + kb] = __fmul_rn(scale, __int2float_rn(isum));
+                    if (lane == 0) {
+                        fscales[j * 8 + t] = scale;
+                        fscales[j * 8 + 4 + t] = __fmul_rn(scale, __int2float_rn(isum));
                     }
+                    if (lbg == 0)   // band group 0 of a matrix meets every 128-block exactly once: the caller's copy
+                        *reinterpret_cast<uint2*>(p.a_had + (size_t(pi) * p.m + t) * p.k + kb * 128 + lane * 4) = o;
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads the tiles through the async proxy
             }
@@ -324,45 +337,28 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
-            auto coords = [&](int i, int& pi, int& lbg, int& kb) {
-                const long long u = u0 + i;
-                const int gbg = int(u / kblocks);
-                kb = int(u - (long long) gbg * kblocks);
-                pi = gbg / bgroups;
-                lbg = gbg - pi * bgroups;
-            };
-            auto issue_weights = [&](int i, uint32_t dst, uint32_t bar) {
-                int pi, lbg, kb;
-                coords(i, pi, lbg, kb);
-                const int z = p.problems ? load_problem(p.problems, pi, p.n_matrices, TOK, p.max_rows).z : pi;
-                tma_load_3d(dst, &tmap, lbg * (ROW_BYTES / 8), kb * 8, z, bar);
-            };
-            auto issue_limbs = [&](int i, uint32_t dst, uint32_t bar) {
-                int pi, lbg, kb;
-                coords(i, pi, lbg, kb);
+            auto issue_limbs = [&](int pi, int kb, uint32_t dst, uint32_t bar) {
                 bulk_load_1d(dst, reinterpret_cast<const unsigned char*>(p.afrag) + (size_t(pi) * kblocks + kb) * B_BYTES, B_BYTES, bar);
             };
-            // The weights do not depend on the rotation kernel: fill the ring with them first, then wait
-            // for the limb tiles and complete those stages.
-            const int pre = nunits < S ? nunits : S;
-            constexpr uint32_t kStageTx = FUSED ? W_BYTES : STAGE_BYTES;
-            for (int i = 0; i < pre; ++i) {
-                mbar_arrive_expect_tx(full0 + 8 * i, kStageTx);
-                issue_weights(i, smem_u32(ring + i * STAGE_BYTES), full0 + 8 * i);
-            }
-            stamp(1);
             pdl_wait();
-            stamp(2);
-            if constexpr (!FUSED)
-                for (int i = 0; i < pre; ++i) issue_limbs(i, smem_u32(ring + i * STAGE_BYTES + W_BYTES), full0 + 8 * i);
+            if constexpr (!FUSED) {
+                // the limb tiles of the stages whose weights are already on their way: replay the coordinates from u0
+                unsigned gbg = unsigned(u0 / kblocks);
+                int kb = int(u0 - (long long) gbg * kblocks);
+                for (int i = 0; i < pre; ++i) {
+                    issue_limbs(int(gbg / unsigned(bgroups)), kb, smem_u32(ring + i * STAGE_BYTES + W_BYTES), full0 + 8 * i);
+                    if (++kb == kblocks) { kb = 0; ++gbg; }
+                }
+                if (pre > 0) next_unit();
+            }
             int s = 0, lap = 1;
             for (int i = pre; i < nunits; ++i) {
                 mbar_wait_parked(empty0 + 8 * s, (lap - 1) & 1, p.status, kStEmptyTimeout);
                 mbar_arrive_expect_tx(full0 + 8 * s, kStageTx);
                 const uint32_t dst = smem_u32(ring + s * STAGE_BYTES);
-                issue_weights(i, dst, full0 + 8 * s);
-                if constexpr (!FUSED) issue_limbs(i, dst + W_BYTES, full0 + 8 * s);
+                issue_weights(dst, full0 + 8 * s);
+                if constexpr (!FUSED) issue_limbs(pr_pi, pr_kb, dst + W_BYTES, full0 + 8 * s);
+                next_unit();
                 if (++s == S) { s = 0; ++lap; }
             }
         }
@@ -381,23 +377,17 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
         int pending = -1;           // weight stage whose stores are issued but not yet handed over
         // The hand-over of a stage (wait for its stores, fence, arrive) is deferred until the first tiles of the
         // next stage are decoded, so that the store latency hides behind that work.
-        PH_DECL
         auto hand_over = [&]() {
             if (pending >= 0) {
-                PH_MARK(0)
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(afull0 + 8 * pending);
                 pending = -1;
-                PH_MARK(1)
             }
         };
         for (int i = 0; i < nunits; ++i) {
-            PH_MARK(0)
             mbar_wait(full0 + 8 * s, phase, p.status, kStFullTimeout);
-            PH_MARK(2)
-            if (i == 0 && threadIdx.x == 0) stamp(3);
             const uint32_t* stage = reinterpret_cast<const uint32_t*>(ring + s * STAGE_BYTES) + word0;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -416,10 +406,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
                     if (rr == 0) {
                         hand_over();
                         // the MMAs that read this weight stage one lap ago are done (first lap: passes at once)
-                        PH_MARK(0)
                         mbar_wait(aempty0 + 8 * a_idx, a_par, p.status, kStTmemTimeout);
                         tc_fence_after();
-                        PH_MARK(3)
                     }
 #pragma unroll
                     for (int t = 0; t < 2; ++t) tc_st_tile(taddr + (uint32_t(16 * t) << 16) + 16 * rr, x[t]);
@@ -432,9 +420,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
             if (++s == S) { s = 0; phase ^= 1; }
         }
         hand_over();
-        PH_MARK(0)
-        PH_STORE
-        if (threadIdx.x == 0) stamp(4);
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
         // The whole warp runs the loop and one elected lane issues, so that addresses and descriptors live in
@@ -484,49 +469,40 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
         const int ew = warp - kEpiWarp0;                      // 0..3 = TMEM lane quarter
         const int et = ew * 32 + lane;                        // output column inside a band = TMEM lane
         const uint32_t lane_base = uint32_t(32 * ew) << 16;
-        // Block scales, block sums and the problem table come from the preceding kernels, and the slabs may
-        // still be read by the finishing kernel of the previous linear.
+        // Activations (or their limb tiles and block sums) come from the preceding kernels.
         pdl_wait();
-        const int slab_rows = p.problems ? TOK : p.m;
+        const int slab_rows = p.m;
         const size_t slab_floats = size_t(slab_rows) * BU * 128;
+        const size_t slab_stride = slab_floats + 32;          // ... followed by the rows' partial sums of the activations
+        __shared__ int s_last;
         int ui = 0, rs = 0, rphase = 0;
-        // In-kernel rotation: unit j's limb tile is written by these warps (warp ew takes row ew) into ring stage
-        // j % S once the stage's previous user has released it; they stay S - 1 units ahead of their own epilogue work.
         long long u = u0;
         while (u < u1) {
             const Segment sg = segment_at(u, u0, u1, kblocks);
             const int pi = sg.bg / bgroups, lbg = sg.bg - pi * bgroups;
             const ProblemView pv = problem_view(p, pi, TOK);
             const int rows = min(pv.rows, TOK), row0 = pv.row0;
-            constexpr int kRowsPerWarp = (TOK + kEpiWarps - 1) / kEpiWarps;
-            float sxr[kRowsPerWarp];
-            uint2 svr[BU];
-            if (sg.whole) {
-                const float* bsum = p.blocksum + size_t(pv.act) * slab_rows * kblocks;
+            float acc[BU][TOK], sxp[TOK];   // per row: dot products of this thread's column(s); sum of the quantised activations
 #pragma unroll
-                for (int r = 0; r < kRowsPerWarp; ++r) {
-                    const int row = ew + r * kEpiWarps;
-                    sxr[r] = row < rows ? row_sum(bsum + size_t(row) * kblocks, kblocks, lane) : 0.f;
-                }
+            for (int t = 0; t < TOK; ++t) {
+                sxp[t] = 0.f;
 #pragma unroll
-                for (int b = 0; b < BU; ++b) {
-                    const int band = lbg * BU + b;
-                    svr[b] = band < bands ? __ldg(reinterpret_cast<const uint2*>(pv.svh + band * 128 + lane * 4)) : make_uint2(0u, 0u);
-                }
+                for (int b = 0; b < BU; ++b) acc[b][t] = 0.f;
             }
-            float acc[BU][TOK];
-#pragma unroll
-            for (int b = 0; b < BU; ++b)
-#pragma unroll
-                for (int t = 0; t < TOK; ++t) acc[b][t] = 0.f;
             for (int j = 0; j < sg.units; ++j, ++ui) {
                 const int buf = ui & 1;
-                float sc[TOK];
+                float sc[TOK], bs[TOK];
                 if constexpr (FUSED) {
 #pragma unroll
-                    for (int t = 0; t < TOK; ++t) sc[t] = t < rows ? fscales[ui * 4 + t] : 0.f;
+                    for (int t = 0; t < TOK; ++t) {
+                        sc[t] = t < rows ? fscales[ui * 8 + t] : 0.f;
+                        bs[t] = t < rows ? fscales[ui * 8 + 4 + t] : 0.f;
+                    }
                 } else {
-                    // the unit's block scales travel with its limb tile
+                    // the unit's block scales travel with its limb tile; its block sums were left in global memory
+                    const float* bsp = p.blocksum + size_t(pv.act) * slab_rows * kblocks + sg.kb_begin + j;
+#pragma unroll
+                    for (int t = 0; t < TOK; ++t) bs[t] = t < rows ? __ldg(bsp + size_t(t) * kblocks) : 0.f;
                     mbar_wait_suspended(full0 + 8 * rs, rphase, p.status, kStFullTimeout);
                     const float* scp = reinterpret_cast<const float*>(ring + rs * STAGE_BYTES + W_BYTES + G_::L_BYTES);
 #pragma unroll
@@ -538,65 +514,91 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
                 mbar_wait_suspended(dfull0 + 8 * buf, (ui >> 1) & 1, p.status, kStTmemTimeout);
                 tc_fence_after();
                 const uint32_t d_base = tmem_d + buf * (BU * NCOL) + lane_base;
-                // the unit's s32 sums: column 2t = high-limb sum of row t, 2t+1 = low-limb sum; loads of a pass are
-                // issued together and waited for once
-                constexpr int LDW = 2 * TOK < 32 ? 2 * TOK : 32;             // columns per load
-                constexpr int PASSES = (2 * TOK) / LDW;
+                // the unit's s32 sums: column 2t = high-limb sum of row t, 2t+1 = low-limb sum
+                int r[BU][2 * TOK];
 #pragma unroll
-                for (int ps = 0; ps < PASSES; ++ps) {
-                    int r[BU][LDW];
+                for (int b = 0; b < BU; ++b) tc_ld<2 * TOK>(d_base + b * NCOL, r[b]);
+                tc_wait_ld();
+                tc_fence_before();   // the accumulator buffer is in registers: hand it back before the arithmetic
+                __syncwarp();
+                if (lane == 0) mbar_arrive(dempty0 + 8 * buf);
 #pragma unroll
-                    for (int b = 0; b < BU; ++b) tc_ld<LDW>(d_base + b * NCOL + ps * LDW, r[b]);
-                    tc_wait_ld();
-                    if (ps == PASSES - 1) {   // the accumulator buffer is in registers: hand it back before the arithmetic
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(dempty0 + 8 * buf);
-                    }
+                for (int t = 0; t < TOK; ++t) {
+                    sxp[t] = __fadd_rn(sxp[t], bs[t]);
 #pragma unroll
                     for (int b = 0; b < BU; ++b)
-#pragma unroll
-                        for (int tt = 0; tt < LDW / 2; ++tt) {
-                            const int t = ps * (LDW / 2) + tt;
-                            acc[b][t] = __fmaf_rn(sc[t], __int2float_rn(r[b][2 * tt] * 256 + r[b][2 * tt + 1]), acc[b][t]);
-                        }
+                        acc[b][t] = __fmaf_rn(sc[t], __int2float_rn(r[b][2 * t] * 256 + r[b][2 * t + 1]), acc[b][t]);
                 }
             }
-            // the segment's sums: thread et owns column et of every band
-            float* dst = sg.whole ? outbuf : p.slabs + size_t(sg.head ? 2 * cta : 2 * cta + 1) * slab_floats;
-            const int dpitch = sg.whole ? PITCH : BU * 128;
-#pragma unroll
-            for (int tok = 0; tok < TOK; ++tok) {
-                if (tok < rows) {
-#pragma unroll
-                    for (int b = 0; b < BU; ++b) {
-                        if (sg.whole) dst[tok * dpitch + b * 128 + et] = acc[b][tok];
-                        else __stcg(dst + tok * dpitch + b * 128 + et, acc[b][tok]);
-                    }
-                }
-            }
+            // ---- the segment's sums: thread et owns column et of every band
+            constexpr int kTasksPerWarp = (TOK * BU + kEpiWarps - 1) / kEpiWarps;
             if (sg.whole) {
+                // the CTA held the band group's whole K: finish the bands here
+#pragma unroll
+                for (int tok = 0; tok < TOK; ++tok)
+                    if (tok < rows)
+#pragma unroll
+                        for (int b = 0; b < BU; ++b) outbuf[tok * PITCH + b * 128 + et] = acc[b][tok];
                 epi_sync();   // outbuf complete
 #pragma unroll
-                for (int r = 0; r < kRowsPerWarp; ++r) {
-                    const int row = ew + r * kEpiWarps;
-                    if (row < rows) {
+                for (int q = 0; q < kTasksPerWarp; ++q) {
+                    const int task = ew + q * kEpiWarps, row = task / BU, b = task - row * BU, band = lbg * BU + b;
+                    if (row < rows && band < bands) {   // (ragged last band group)
+                        float sx = 0.f;
 #pragma unroll
-                        for (int b = 0; b < BU; ++b) {
-                            const int band = lbg * BU + b;
-                            if (band < bands) {   // ragged last band group
-                                float4 t = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
-                                float v[4] = {t.x, t.y, t.z, t.w};
-                                finish_band<2>(v, sxr[r], lane, svr[b], band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
-                            }
-                        }
+                        for (int t = 0; t < TOK; ++t) sx = t == row ? sxp[t] : sx;
+                        const uint2 sv = __ldg(reinterpret_cast<const uint2*>(pv.svh + band * 128 + lane * 4));
+                        const float4 t4 = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
+                        float v[4] = {t4.x, t4.y, t4.z, t4.w};
+                        finish_band<2>(v, sx, lane, sv, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
                     }
                 }
                 epi_sync();   // outbuf is free again
+            } else {
+                // K was split: leave the partial sums in this CTA's slab; the CTA that arrives last at the band group's
+                // counter sums the group's slabs in CTA order (so the result does not depend on who was last) and
+                // finishes the bands.  Nobody waits for anybody.
+                float* slab = p.slabs + size_t(sg.head ? 2 * cta : 2 * cta + 1) * slab_stride;
+#pragma unroll
+                for (int tok = 0; tok < TOK; ++tok)
+                    if (tok < rows) {
+#pragma unroll
+                        for (int b = 0; b < BU; ++b) __stcg(slab + tok * (BU * 128) + b * 128 + et, acc[b][tok]);
+                        if (et == tok) __stcg(slab + slab_floats + tok, sxp[tok]);
+                    }
+                const long long g0 = (long long) sg.bg * kblocks;
+                const int first_cta = unit_owner(g0, U, G), last_cta = unit_owner(g0 + kblocks - 1, U, G);
+                epi_sync();
+                if (et == 0) {
+                    __threadfence();
+                    const unsigned arrived = atomicAdd(p.counters + sg.bg, 1u) + 1u;
+                    s_last = arrived == unsigned(last_cta - first_cta + 1);
+                    if (s_last) p.counters[sg.bg] = 0u;   // ready for the next launch
+                }
+                epi_sync();
+                if (s_last) {
+                    __threadfence();
+                    const int first_slab = unit_begin(first_cta, U, G) >= g0 ? 2 * first_cta : 2 * first_cta + 1;
+#pragma unroll
+                    for (int q = 0; q < kTasksPerWarp; ++q) {
+                        const int task = ew + q * kEpiWarps, row = task / BU, b = task - row * BU, band = lbg * BU + b;
+                        if (row < rows && band < bands) {
+                            const uint2 sv = __ldg(reinterpret_cast<const uint2*>(pv.svh + band * 128 + lane * 4));
+                            float v[4] = {0.f, 0.f, 0.f, 0.f}, sx = 0.f;
+                            for (int c = first_cta; c <= last_cta; ++c) {
+                                const float* sl = p.slabs + size_t(c == first_cta ? first_slab : 2 * c) * slab_stride;
+                                const float4 t4 = __ldcg(reinterpret_cast<const float4*>(sl + row * (BU * 128) + b * 128 + lane * 4));
+                                sx = __fadd_rn(sx, __ldcg(sl + slab_floats + row));
+                                v[0] = __fadd_rn(v[0], t4.x); v[1] = __fadd_rn(v[1], t4.y);
+                                v[2] = __fadd_rn(v[2], t4.z); v[3] = __fadd_rn(v[3], t4.w);
+                            }
+                            finish_band<2>(v, sx, lane, sv, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
+                        }
+                    }
+                }
             }
             u += sg.units;
         }
-        if (threadIdx.x == kEpiWarp0 * 32) stamp(5);
     }
 
     // ---------------------------------------------------------------- release tensor memory
@@ -676,9 +678,7 @@ size_t launch_nb(int nb, bool fused, const void* t, int nm, const GemvArgs& a, i
 {
     switch (nb) {
         case 1: return fused ? launch_one<BITS, 1, true>(t, nm, a, grid, st) : launch_one<BITS, 1, false>(t, nm, a, grid, st);
-        case 2: return launch_one<BITS, 2, false>(t, nm, a, grid, st);
-        case 4: return launch_one<BITS, 4, false>(t, nm, a, grid, st);
-        default: return launch_one<BITS, 8, false>(t, nm, a, grid, st);
+        default: return launch_one<BITS, 2, false>(t, nm, a, grid, st);
     }
 }
 
@@ -699,17 +699,30 @@ size_t launch_bits(int k_bits, int nb, bool fused, const void* t, int nm, const 
 
 }  // namespace
 
-// Rotation + decode linear for up to 32 rows of a MUL1 matrix; same contract as launch_gemv.
+bool gemv_i8_rotates_in_kernel(int size_m, int size_k, int size_n, int k_bits, int sms)
+{
+    if (size_m < 1 || size_m > 4 || size_k % 128 != 0 || k_bits < 1 || k_bits > 8) return false;
+    const int bu = k_bits <= 4 ? 2 : 1;
+    const int bands = size_n / 128, kblocks = size_k / 128, bgroups = (bands + bu - 1) / bu;
+    const long long units = (long long) bgroups * kblocks;
+    const int grid = int(std::min<long long>(std::min<long long>(sms, units), (long long) bgroups * 16));
+    if (grid < 1) return false;
+    const long long units_per_cta = (units + grid - 1) / grid;
+    return units_per_cta < kblocks && units_per_cta <= fused_max_units(k_bits, size_m <= 1 ? 1 : (size_m == 2 ? 2 : 4));
+}
+
+// Rotation + decode linear for up to kI8MaxRows rows of a MUL1 matrix (or of a stack of n_stack equally shaped ones);
+// same contract as launch_gemv.
 std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                            int size_m, int size_k, int size_n, int k_bits, int out_fp32, const GemvScratch& sc, int sms,
                            cudaStream_t stream, unsigned long long* argmax, int n_stack)
 {
     if (n_stack < 1) n_stack = 1;
-    if (size_m > 32) throw std::runtime_error("exl3 gemv: size_m must be <= 32");
+    if (size_m > kI8MaxRows) throw std::runtime_error("exl3 gemv (integer tensor path): size_m must be <= 8");
     if (size_k % 128 != 0)
         throw std::runtime_error("exl3 linear: no linked kernel for size_k that is not a multiple of 128 (128-wide Hadamard)");
     if (k_bits < 1 || k_bits > 8) throw std::runtime_error("exl3 linear: K must be in 1..=8");
-    const int nb = size_m <= 4 ? 1 : (size_m <= 8 ? 2 : (size_m <= 16 ? 4 : 8));
+    const int nb = size_m <= 4 ? 1 : 2;
     const int bu = k_bits <= 4 ? 2 : 1;
     const int bands = size_n / 128, kblocks = size_k / 128, bgroups = (bands + bu - 1) / bu;
     if (size_t(n_stack) * size_m * kblocks > sc.blocksum_floats)
@@ -719,9 +732,11 @@ std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const vo
         throw std::runtime_error("exl3 gemv: matrices x size_k x ceil(size_m / 4) exceed the activation area of the scratch");
     const long long units = (long long) n_stack * bgroups * kblocks;
     int grid = int(std::min<long long>(std::min<long long>(sms, units), (long long) n_stack * bgroups * 16));
-    const size_t per_cta = size_t(2) * size_m * bu * 128 * sizeof(float);
+    const size_t per_cta = size_t(2) * (size_t(size_m) * bu * 128 + 32) * sizeof(float);
     if (size_t(grid) * per_cta > sc.slab_bytes) grid = int(sc.slab_bytes / per_cta);
     if (grid < 1) throw std::runtime_error("exl3 gemv: split-K scratch is too small for this shape");
+    if (size_t(n_stack) * bgroups > sc.counter_words)
+        throw std::runtime_error("exl3 gemv: matrices x size_n / 128 exceed the band-group counters of the scratch");
 
     // In-kernel rotation for up to four rows when no CTA holds a whole band group (such a CTA finishes its bands
     // itself and needs every block sum of the row, which other CTAs would still be writing).
@@ -747,19 +762,15 @@ std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const vo
     args.argmax = argmax;
     args.svh = static_cast<const __half*>(svh);
     args.slabs = sc.slabs;
+    args.counters = sc.counters;
     args.status = sc.status;
     args.m = size_m; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
     args.max_problems = 1; args.n_matrices = n_stack; args.max_rows = size_m;
     args.n_stack = n_stack;
     const size_t smem = launch_bits(k_bits, nb, fused, trellis, n_stack, args, grid, stream);
-    launch_finish(args, bu, 4 * nb, grid, 2, stream);
  return std::string(fused ? "" : "k_rotate_in_i8 + ") + "k_exl3_gemv_i8<" + std::to_string(k_bits) + "," + std::to_string(nb) + (fused ? ",fused" : "") + (n_stack > 1 ? ",stack of " + std::to_string(n_stack) : "") + "> grid=" + std::to_string(grid) +
-           " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem) + " + k_gemv_finish";
+           " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem);
 }
 
 }  // namespace berth
-#ifdef BERTH_I8_STAMPS
-extern "C" int berth_i8_phases(long long* out) { return (int) cudaMemcpyFromSymbol(out, berth::g_i8_ph, sizeof(long long) * 256 * 16 * 4); }
-extern "C" int berth_i8_stamps(unsigned long long* out) { return (int) cudaMemcpyFromSymbol(out, berth::g_i8_ts, sizeof(unsigned long long) * 256 * 8); }
-#endif

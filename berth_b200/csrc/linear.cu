@@ -127,8 +127,8 @@ extern "C" int berth_exl3_linear_stack(const void* a, const void* trellis_stack,
         if (size_m < 1 || size_k < 1 || size_n < 1) throw std::runtime_error("exl3 linear stack: sizes must be positive");
         if (n_matrices < 1 || n_matrices > 16) throw std::runtime_error("exl3 linear stack: n_matrices must be in 1..=16");
         check_linear_args("exl3 linear stack", a, trellis_stack, c, suh_stack, a_had, svh_stack, size_k, size_n, k_bits, codebook);
-        if (codebook != 2 || size_m > 32)
-            throw std::runtime_error("exl3 linear stack: no linked kernel (MUL1 codebook and size_m <= 32 only)");
+        if (codebook != 2 || size_m > kI8MaxRows)
+            throw std::runtime_error("exl3 linear stack: no linked kernel (MUL1 codebook and size_m <= 8 only)");
         const int device = current_device();
         const DeviceInfo& info = device_info(device);
         if (info.major != 10)

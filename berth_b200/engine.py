@@ -165,6 +165,43 @@ class SlicedMultiLinear:
         return self.outputs
 
 
+class StackedLinear:
+    """Equally shaped MUL1 linears that share one input (gate and up of an MLP), stored one behind the other so that
+    one decode launch (``kernels.exl3_linear_stack``) runs all of them on up to eight rows.  Construction moves the
+    sources' tensors into the stack and re-points the sources at their slices, so no weight is held twice."""
+
+    MAX_ROWS = 8
+
+    def __init__(self, gpu: Gpu, sources: list, max_rows: int = 1):
+        first = sources[0]
+        for s in sources:
+            if (s.size_k, s.size_n, s.k_bits, s.codebook) != (first.size_k, first.size_n, first.k_bits, first.codebook):
+                raise Error("StackedLinear: sources must share shape, k_bits and codebook")
+        if first.codebook != Codebook.Mul1:
+            raise Error("StackedLinear: the stacked launch exists for the MUL1 codebook only")
+        self.sources = sources
+        self.size_k, self.size_n, self.k_bits, self.codebook = first.size_k, first.size_n, first.k_bits, first.codebook
+        self.trellis = torch.stack([s.trellis for s in sources]).contiguous()
+        self.suh = torch.stack([s.suh for s in sources]).contiguous()
+        self.svh = torch.stack([s.svh for s in sources]).contiguous()
+        for i, s in enumerate(sources):
+            s.trellis, s.suh, s.svh = self.trellis[i], self.suh[i], self.svh[i]
+        self.a_had = torch.zeros(len(sources) * max_rows * self.size_k, dtype=torch.float16, device=gpu.device)
+
+    def forward_n(self, gpu: Gpu, rows: int, a: torch.Tensor, c: torch.Tensor, out: OutDtype) -> None:
+        """``c`` is ``[len(sources)][rows][size_n]`` of ``out``."""
+        if rows > self.MAX_ROWS:
+            raise Error(f"StackedLinear: {rows} rows exceed {self.MAX_ROWS}")
+        n = len(self.sources)
+        out_bytes = 2 if out == OutDtype.F16 else 4
+        if a.numel() * a.element_size() < rows * self.size_k * 2 or c.numel() * c.element_size() < n * rows * self.size_n * out_bytes:
+            raise Error("StackedLinear: buffer too small")
+        if self.a_had.numel() < n * rows * self.size_k:
+            self.a_had = torch.zeros(n * rows * self.size_k, dtype=torch.float16, device=gpu.device)
+        kernels.exl3_linear_stack(a, self.trellis, c, self.suh, self.a_had, self.svh, n, rows, self.size_k, self.size_n,
+                                  self.k_bits, self.codebook, out, gpu.raw_stream())
+
+
 class RowScratch:
     """Scratch shared by every linear of a prefill chunk.  ``weight`` is kept because the
     boundary requires a non-null pointer above 144 rows; the B200 kernels never write it, so it
@@ -188,13 +225,17 @@ class MlpLayer:
         self.hidden, self.intermediate = gate.size_k, gate.size_n
         if self.intermediate < 2 or self.intermediate % 2:
             raise Error(f"intermediate {self.intermediate} must be positive and even")
+        # gate and up as one decode launch where the library has one (MUL1, same bitrate, up to eight rows)
+        self.gate_up = None
+        if gate.codebook == Codebook.Mul1 and up.codebook == Codebook.Mul1 and gate.k_bits == up.k_bits:
+            self.gate_up = StackedLinear(gpu, [gate, up], max_rows)
         self._alloc(gpu, max_rows)
 
     def _alloc(self, gpu: Gpu, rows: int) -> None:
         n = rows * self.intermediate
         self.max_rows = rows
-        self.gate_out = torch.zeros(n, dtype=torch.float16, device=gpu.device)
-        self.up_out = torch.zeros(n, dtype=torch.float16, device=gpu.device)
+        self.gate_up_out = torch.zeros(2 * n, dtype=torch.float16, device=gpu.device)   # gate rows, then up rows
+        self.gate_out, self.up_out = self.gate_up_out[:n], self.gate_up_out[n:]
         self.activated = torch.zeros(n, dtype=torch.float16, device=gpu.device)
 
     @classmethod
@@ -216,10 +257,15 @@ class MlpLayer:
             raise Error(f"{self.gate.prefix}: buffer too small")
         if rows > self.max_rows:
             self._alloc(gpu, rows)
-        self.gate.forward_n(gpu, rows, inp, self.gate_out, OutDtype.F16)
-        self.up.forward_n(gpu, rows, inp, self.up_out, OutDtype.F16)
-        kernels.ops.silu_mul(self.gate_out, self.up_out, self.activated, rows * self.intermediate, ACT_LIMIT,
-                             gpu.raw_stream())
+        n = rows * self.intermediate
+        if self.gate_up is not None and rows <= StackedLinear.MAX_ROWS:
+            gate_out, up_out = self.gate_up_out[:n], self.gate_up_out[n:2 * n]
+            self.gate_up.forward_n(gpu, rows, inp, self.gate_up_out, OutDtype.F16)
+        else:
+            gate_out, up_out = self.gate_out, self.up_out
+            self.gate.forward_n(gpu, rows, inp, gate_out, OutDtype.F16)
+            self.up.forward_n(gpu, rows, inp, up_out, OutDtype.F16)
+        kernels.ops.silu_mul(gate_out, up_out, self.activated, n, ACT_LIMIT, gpu.raw_stream())
         self.down.forward_n(gpu, rows, self.activated, output, OutDtype.F32)
 
     def prefill(self, gpu: Gpu, rows: int, inp: torch.Tensor, output: torch.Tensor, scratch: RowScratch) -> None:

@@ -85,7 +85,7 @@ def exl3_linear_static_scratch(a, trellis, c, suh, a_had, svh, size_m: int, size
 
 def exl3_linear_stack(a, trellis_stack, c, suh_stack, a_had, svh_stack, n_matrices: int, size_m: int, size_k: int, size_n: int,
                       k_bits: int, codebook: Codebook, out: OutDtype, stream=None) -> None:
-    """``n_matrices`` equally shaped MUL1 linears (stored one behind the other) applied to the same ``size_m <= 32`` rows in
+    """``n_matrices`` equally shaped MUL1 linears (stored one behind the other) applied to the same ``size_m <= 8`` rows in
     one decode launch; ``c`` is ``[n_matrices][size_m][size_n]``, ``a_had`` ``[n_matrices][size_m][size_k]``."""
     rc = _lib.lib().berth_exl3_linear_stack(_ptr(a), _ptr(trellis_stack), _ptr(c), _ptr(suh_stack), _ptr(a_had), _ptr(svh_stack),
                                             n_matrices, size_m, size_k, size_n, k_bits, int(codebook), int(out), _stream(stream))

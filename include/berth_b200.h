@@ -112,7 +112,7 @@ int berth_exl3_linear_argmax(const void* a, const void* trellis, void* c, const 
                              int out_fp32, void* stream);
 void berth_argmax_key_decode(unsigned long long key, int32_t* token, float* value);
 
-/* A stack of n_matrices equally shaped MUL1 linears applied to the same size_m <= 32 rows in ONE decode launch:
+/* A stack of n_matrices equally shaped MUL1 linears applied to the same size_m <= 8 rows in ONE decode launch:
  * trellis_stack int16 [n][size_k/16][size_n/16][16*k_bits], suh_stack fp16 [n][size_k], svh_stack fp16 [n][size_n];
  * outputs c [n][size_m][size_n] and a_had [n][size_m][size_k].  What berth does for the gate and up projections of
  * an MLP with two berth_exl3_linear calls (crates/berth-engine/src/mlp.rs:118-150); a host that stores the two
