@@ -42,3 +42,28 @@ def rel_errors(got, y64):
 
 
 MAX_REL, MEAN_REL = 1e-2, 1e-3   # tolerance of fp32-accumulated outputs against the fp64 evaluation
+
+
+def elementwise_rel_errors(got, y64):
+    """(max, mean) of |got - y64| / |y64| over the elements with |y64| >= rms(y64): the literal element-wise reading
+    of the tolerance, where it is well defined (an element-wise ratio blows up at the zero crossings of a zero-mean
+    output, which is why rel_errors divides by the RMS instead)."""
+    y64 = np.asarray(y64, np.float64)
+    got = np.asarray(got, np.float64)
+    rms = np.sqrt((y64 ** 2).mean())
+    big = np.abs(y64) >= rms
+    if not big.any():
+        return 0.0, 0.0
+    err = np.abs(got[big] - y64[big]) / np.abs(y64[big])
+    return float(err.max()), float(err.mean())
+
+
+def assert_close(got, y64, what=""):
+    """Both forms of the tolerance: errors relative to rms(y64) over all elements, and element-wise relative errors
+    over the elements of at least RMS magnitude; max <= 1e-2 and mean <= 1e-3 each.  Returns the four numbers."""
+    assert np.isfinite(np.asarray(got, np.float64)).all(), (what, "non-finite output")
+    mx, mean = rel_errors(got, y64)
+    emx, emean = elementwise_rel_errors(got, y64)
+    assert mx <= MAX_REL and mean <= MEAN_REL, (what, "relative to rms", mx, mean)
+    assert emx <= MAX_REL and emean <= MEAN_REL, (what, "element-wise", emx, emean)
+    return mx, mean, emx, emean

@@ -9,7 +9,7 @@ torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
 from berth_b200 import kernels, moe, synth   # noqa: E402
-from tests.gpu_util import MAX_REL, MEAN_REL, dev, rel_errors   # noqa: E402
+from tests.gpu_util import MAX_REL, MEAN_REL, assert_close, dev, rel_errors   # noqa: E402
 
 
 def _route(x, wr, bias, k):
@@ -97,6 +97,46 @@ def test_moe_layer_config3_vs_oracle(oracle, T):
     y64 = oracle.moe_layer_f64(wts, x, exp_idx, exp_w)
     mx, mean = rel_errors(out, y64)
     assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
+
+
+def test_moe_layer_config3_1024_tokens_sampled_vs_oracle(oracle):
+    """Configuration 3 at 1024 tokens: the grouped tensor-core launches at their own sizes (2048 / 512, 257 matrices,
+    the doubled gate/up table, persistent CTAs).  Routing of all 1024 tokens bit-exact against the checker; the outputs
+    of twelve sampled tokens against the checker's layer and its fp64 evaluation (the layer is row-wise, so a token's
+    output does not depend on the batch it sits in)."""
+    H, I, E, k, bits, cb, T = 2048, 512, 256, 8, 4, 2, 1024
+    wts = synth.moe_layer_weights(1234, "c3", H, I, E, k, bits, cb, shared_inter=512)
+    x = synth.activations(1234, f"c3.x{T}", T, H)
+    out, idx, w = _run_layer(wts, x)
+    assert "k_exl3_gemm_tc_grouped" in moe.last_launch()
+    exp_idx, exp_w = oracle.router_topk(oracle.router_logits(x, wts["w_router"]), k)
+    assert (idx == exp_idx).all() and np.abs(w - exp_w).max() <= 1e-6
+    sample = np.array([0, 1, 77, 128, 255, 256, 383, 511, 640, 777, 1000, 1023])
+    xs = np.ascontiguousarray(x[sample])
+    exp_out, idx_s, w_s = oracle.moe_layer(wts, xs)
+    assert (idx_s == idx[sample]).all()
+    y64 = oracle.moe_layer_f64(wts, xs, idx_s, w_s)
+    assert_close(out[sample], y64, "c3 T=1024 sample")
+    assert np.abs(out[sample] - exp_out).max() <= 4e-3 * np.sqrt((y64 ** 2).mean())
+
+
+@pytest.mark.parametrize("T,nsub", [(400, 2), (600, 3), (1000, 3)])
+@pytest.mark.parametrize("fuse_shared,pair", [(True, True), (False, False)])
+def test_moe_layer_wide_grouped_tiles_vs_oracle(oracle, T, nsub, fuse_shared, pair):
+    """Few experts and many rows each, so that the expert stage cuts 256- and 384-row problems (two and three
+    128-row sub-tiles of the grouped tensor-core kernel): every token against the checker, with the shared expert
+    stacked behind the experts and the paired gate/up table, and without either."""
+    H, I, E, k, bits, cb = 256, 128, 32, 8, 4, 2
+    wts = synth.moe_layer_weights(1234, "wide", H, I, E, k, bits, cb, shared_inter=128)
+    x = synth.activations(1234, f"wide.x{T}", T, H)
+    out, idx, w = _run_layer(wts, x, fuse_shared=fuse_shared, pair_gate_up=pair)
+    assert "k_exl3_gemm_tc_grouped" in moe.last_launch()
+    assert min(3, (min(T, (2 * T * k + E - 1) // E) + 127) // 128) == nsub      # the plan berth_moe_layer derives
+    exp_out, exp_idx, exp_w = oracle.moe_layer(wts, x)
+    assert (idx == exp_idx).all() and np.abs(w - exp_w).max() <= 1e-6
+    y64 = oracle.moe_layer_f64(wts, x, exp_idx, exp_w)
+    assert_close(out, y64, f"T={T}")
+    assert np.abs(out - exp_out).max() <= 4e-3 * np.sqrt((y64 ** 2).mean())
 
 
 def test_moe_layer_skewed_routing_property():

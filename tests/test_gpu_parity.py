@@ -13,7 +13,7 @@ torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
 from berth_b200 import Codebook, OutDtype, kernels, synth   # noqa: E402
-from tests.gpu_util import MAX_REL, MEAN_REL, dev, host_u16, rel_errors, run_linear   # noqa: E402
+from tests.gpu_util import MAX_REL, MEAN_REL, assert_close, dev, host_u16, rel_errors, run_linear   # noqa: E402
 
 
 # ---------------------------------------------------------------- decoded weight tiles: bit-exact
@@ -426,3 +426,139 @@ def test_linear_argmax_ties():
     _, keys = _argmax_run(x, w, bits, cb, True)
     assert keys[1] == (0, 0.0)
     assert keys[0][0] == int(np.argmax(plain[0])) and keys[2][0] == int(np.argmax(plain[2]))
+
+
+# ---------------------------------------------------------------- MUL1 on the integer tensor path (tensor-memory decode kernel)
+
+@pytest.mark.parametrize("bits", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_integer_path_one_row_every_bitrate(oracle, bits):
+    """One row of a MUL1 linear goes through k_exl3_gemv_i8 with the rotation inside the kernel; the output within the
+    tolerance in both its forms, the rotated activations bit for bit."""
+    K, N, cb = 1024, 768, 2
+    w = synth.linear_weights(1234, f"i8b{bits}", K, N, bits)
+    x = synth.activations(1234, "i8.x1", 1, K)
+    for out_fp32 in (True, False):
+        c, ah = run_linear(x, w, bits, cb, out_fp32)
+        assert "k_exl3_gemv_i8" in kernels.last_launch() and "fused" in kernels.last_launch()
+        assert kernels.device_status(torch.cuda.current_device()) == 0
+        y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, N, bits, cb)
+        assert_close(c, y64, f"bits {bits}")
+        assert (ah == oracle.had_r_128(x, w["suh"], True).view(np.uint16)).all()
+
+
+def test_integer_path_config0_and_run_to_run(oracle):
+    """Configuration 0 (5120 x 6144, 4 bpw, one row) on the integer path: within tolerance, and bit-identical from run
+    to run (the split-K partial sums are added in CTA order whichever CTA finishes a band group)."""
+    K, N, bits, cb = 5120, 6144, 4, 2
+    w = synth.linear_weights(1234, "c0", K, N, bits)
+    x = synth.activations(1234, "c0.x", 1, K)
+    c1, _ = run_linear(x, w, bits, cb, True)
+    assert "k_exl3_gemv_i8" in kernels.last_launch()
+    y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, N, bits, cb)
+    assert_close(c1, y64, "c0")
+    for _ in range(3):
+        c2, _ = run_linear(x, w, bits, cb, True)
+        assert (c1.view(np.uint32) == c2.view(np.uint32)).all()
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+
+
+def test_integer_path_outlier_rows(oracle):
+    """Activations with a few x20 outliers and one block of zeros: the block fixed point keeps its precision (a scale
+    per 128 rotated inputs), a zero block quantises to zero."""
+    K, N, bits, cb = 2048, 512, 4, 2
+    w = synth.linear_weights(1234, "i8out", K, N, bits)
+    x = synth.activations(1234, "i8out.x", 1, K, outlier_frac=0.01).copy()
+    x[0, 256:384] = 0
+    c, ah = run_linear(x, w, bits, cb, True)
+    assert "k_exl3_gemv_i8" in kernels.last_launch()
+    y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, N, bits, cb)
+    assert_close(c, y64, "outliers")
+    assert (ah == oracle.had_r_128(x, w["suh"], True).view(np.uint16)).all()
+
+
+@pytest.mark.parametrize("ns,m,K,N,bits,out_fp32", [(2, 1, 512, 512, 4, True), (3, 3, 1024, 640, 4, False), (2, 4, 640, 384, 3, True),
+                                                    (2, 7, 640, 384, 5, False), (2, 8, 512, 256, 4, True),
+                                                    (2, 2, 256, 25600, 4, True), (2, 6, 256, 25600, 6, False)])
+def test_stacked_linear_vs_oracle(oracle, ns, m, K, N, bits, out_fp32):
+    """berth_exl3_linear_stack: ns equally shaped MUL1 matrices applied to the same rows in one launch; every matrix's
+    output against the fp64 evaluation of that matrix alone, its rotated rows bit for bit.  Up to four rows rotate
+    inside the kernel, above the limb tiles come from a rotation kernel; the two wide shapes give every CTA whole band
+    groups (finished inside the decode kernel without split-K slabs)."""
+    cb = 2
+    ws = [synth.linear_weights(1234, f"st{i}.{K}x{N}b{bits}", K, N, bits) for i in range(ns)]
+    x = synth.activations(1234, f"st.x{m}", m, K)
+    tr = dev(np.stack([w["trellis"] for w in ws]))
+    su, sv = dev(np.stack([w["suh"] for w in ws])), dev(np.stack([w["svh"] for w in ws]))
+    c = torch.full((ns, m, N), float("nan"), dtype=torch.float32 if out_fp32 else torch.float16, device="cuda")
+    ah = torch.zeros((ns, m, K), dtype=torch.float16, device="cuda")
+    kernels.exl3_linear_stack(dev(x), tr, c, su, ah, sv, ns, m, K, N, bits, Codebook(cb), OutDtype.F32 if out_fp32 else OutDtype.F16)
+    torch.cuda.synchronize()
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+    assert f"stack of {ns}" in kernels.last_launch()
+    got, ahh = c.float().cpu().numpy(), host_u16(ah)
+    for i, w in enumerate(ws):
+        y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, N, bits, cb)
+        assert_close(got[i], y64, f"matrix {i}")
+        assert (ahh[i] == oracle.had_r_128(x, w["suh"], True).view(np.uint16)).all()
+
+
+def test_stacked_linear_fails_closed():
+    K, N, bits = 256, 256, 4
+    z = lambda *s, dt=torch.float16: torch.zeros(s, dtype=dt, device="cuda")
+    tr = torch.zeros((2, K // 16, N // 16, 16 * bits), dtype=torch.int16, device="cuda")
+    for m, cb in ((9, 2), (1, 0), (1, 1)):
+        with pytest.raises(kernels.Error, match="no linked kernel"):
+            kernels.exl3_linear_stack(z(m, K), tr, z(2, m, N), z(2, K), z(2, m, K), z(2, N), 2, m, K, N, bits, Codebook(cb), OutDtype.F16)
+    with pytest.raises(kernels.Error, match="null"):
+        kernels.exl3_linear_stack(None, tr, z(2, 1, N), z(2, K), z(2, 1, K), z(2, N), 2, 1, K, N, bits, Codebook(2), OutDtype.F16)
+
+
+def test_decode_rate_diagnostic():
+    """The bare decode-rate diagnostic runs on every path and reports a plausible figure."""
+    for cb, path in ((0, 0), (1, 0), (2, 0), (2, 1), (2, 2)):
+        w, mhz = kernels.decode_rate(4, Codebook(cb), path, 16, 256)
+        assert 4.0 < w < 64.0 and 500.0 < mhz < 3000.0, (cb, path, w, mhz)
+    with pytest.raises(kernels.Error):
+        kernels.decode_rate(4, Codebook(0), 2, 16, 16)
+
+
+# ---------------------------------------------------------------- configuration 2 at its own shapes
+
+def _hadamard128():
+    h = torch.ones((1, 1), dtype=torch.float64, device="cuda")
+    for _ in range(7):
+        h = torch.cat((torch.cat((h, h), 1), torch.cat((h, -h), 1)), 0)
+    return h
+
+
+@pytest.mark.parametrize("name,K,N,bits,out_fp32", [("gate", 5120, 17408, 4, False), ("down", 17408, 5120, 5, True),
+                                                    ("q", 5120, 6144, 4, False), ("k", 5120, 1024, 3, False),
+                                                    ("o", 6144, 5120, 4, True)])
+def test_prefill_config2_shapes_against_decoded_bands(name, K, N, bits, out_fp32):
+    """Benchmark configuration 2 at its own sizes: 4096 rows with 0.1 % of the activations multiplied by 20, the 27B
+    projection shapes at 3 / 4 / 5 bpw, fp16 or fp32 outputs as the MLP and attention layers take them.  Too large for
+    the CPU checker, so eight 128-column bands per matrix are decoded with berth_prefill_reconstruct (bit-exact
+    against the checker) and evaluated in fp64 on the GPU from the rotated rows the launch wrote; the launch must
+    agree on them within the tolerance (both forms) and produce no infinity or NaN anywhere."""
+    M, cb = 4096, 2
+    w = synth.linear_weights(1234, f"c2.{name}", K, N, bits, fan_in_gain=True)
+    x = synth.activations(1234, f"c2.x.{name}", M, K, outlier_frac=0.001)
+    xd, td, sd, vd = dev(x), dev(w["trellis"]), dev(w["suh"]), dev(w["svh"])
+    c = torch.empty((M, N), dtype=torch.float32 if out_fp32 else torch.float16, device="cuda")
+    ah = torch.empty((M, K), dtype=torch.float16, device="cuda")
+    scratch = torch.empty(16, dtype=torch.float16, device="cuda")
+    kernels.prefill_lin.exl3_linear(xd, td, c, sd, ah, vd, scratch, M, K, N, bits, Codebook(cb), OutDtype.F32 if out_fp32 else OutDtype.F16)
+    torch.cuda.synchronize()
+    assert "k_exl3_gemm_tc" in kernels.prefill_lin.last_launch()
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+    assert bool(torch.isfinite(c).all())
+    a_rot = ah.double()
+    hmat = _hadamard128()
+    bands = sorted({0, N // 128 - 1} | {int(b) for b in np.random.default_rng(7).integers(0, N // 128, 6)})
+    svh = torch.from_numpy(w["svh"].astype(np.float64)).cuda()
+    for b in bands:
+        n0 = b * 128
+        wt = torch.empty((K, 128), dtype=torch.float16, device="cuda")
+        assert _lib_reconstruct(wt, td, K, 128, N, n0, bits, cb) == 0
+        y = (a_rot @ wt.double()) @ hmat / np.sqrt(128.0) * svh[n0:n0 + 128]
+        assert_close(c[:, n0:n0 + 128].double().cpu().numpy(), y.cpu().numpy(), f"{name} band {b}")
