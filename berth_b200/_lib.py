@@ -43,6 +43,7 @@ SIGNATURES = {
     "berth_exl3_linear": (_i, [_vp] * 6 + [_i] * 6 + [_vp]),
     "berth_exl3_linear_static_scratch": (_i, [_vp] * 6 + [_i] * 6 + [_vp]),
     "berth_exl3_linear_argmax": (_i, [_vp] * 7 + [_i] * 6 + [_vp]),
+    "berth_exl3_linear_add": (_i, [_vp] * 7 + [_i] * 5 + [_vp]),
     "berth_exl3_linear_stack": (_i, [_vp] * 6 + [_i] * 7 + [_vp]),
     "berth_argmax_key_decode": (None, [_u64, C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
     "berth_exl3_last_error": (C.c_char_p, []),
@@ -62,6 +63,9 @@ SIGNATURES = {
     "berth_prefill_had_r_128": (_i, [_vp] * 3 + [_i] * 4 + [_vp]),
     "berth_ops_silu_mul": (_i, [_vp] * 3 + [_i64, _f, _vp]),
     "berth_ops_add_f32": (_i, [_vp] * 3 + [_i, _vp]),
+    "berth_ops_rms_norm": (_i, [_vp] * 3 + [_i, _i, _f, _f, _f, _i, _vp]),
+    "berth_ops_rms_norm_f16": (_i, [_vp] * 3 + [_i, _i, _f, _f, _f, _vp]),
+    "berth_ops_rms_norm_res_in": (_i, [_vp] * 4 + [_i, _i, _f, _f, _f, _i, _vp]),
     "berth_moe_router_topk": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
     "berth_moe_workspace_bytes": (C.c_size_t, [_i] * 6),
     "berth_moe_layer": (_i, [C.POINTER(MoeWeights), _vp, _i, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),

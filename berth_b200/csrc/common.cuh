@@ -196,7 +196,8 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
 
 std::string launch_gemv(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32,
-                        const GemvScratch& scratch, int sms, cudaStream_t stream, unsigned long long* argmax = nullptr);
+                        const GemvScratch& scratch, int sms, cudaStream_t stream, unsigned long long* argmax = nullptr,
+                        const float* residual = nullptr);
 
 // The same linear for the MUL1 codebook on the integer tensor path (gemv_i8.cu), up to kI8MaxRows rows; launch_gemv
 // forwards one to four rows to it (above, the limb tiles of the rows cost more L2 traffic than the fp16 path's
@@ -204,7 +205,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
 constexpr int kI8MaxRows = 8;
 std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                            int size_m, int size_k, int size_n, int k_bits, int out_fp32, const GemvScratch& scratch, int sms,
-                           cudaStream_t stream, unsigned long long* argmax, int n_stack = 1);
+                           cudaStream_t stream, unsigned long long* argmax, int n_stack = 1, const float* residual = nullptr);
 
 // True when launch_gemv_i8 would rotate the activations inside the decode kernel for this dense shape.
 bool gemv_i8_rotates_in_kernel(int size_m, int size_k, int size_n, int k_bits, int sms);

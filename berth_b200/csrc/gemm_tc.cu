@@ -860,7 +860,7 @@ __global__ void __launch_bounds__(256) k_rotate_rows_plain(const RotateArgs a)
     const int total_rows = min(last.row0 + last.rows, a.max_rows);
     for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < total_rows; row += gridDim.x * 8) {
         int src_row = row;
-        if constexpr (MODE & kRotGather) src_row = row < a.n_perm ? __ldg(a.perm + row) / a.div : row - a.n_perm;
+        if constexpr (MODE & kRotGather) src_row = row < a.n_perm ? min(max(__ldg(a.perm + row) / a.div, 0), max(a.n_perm / a.div - 1, 0)) : row - a.n_perm;
         int lo = 0, hi = nprob - 1;   // the last problem whose first row is <= row
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;

@@ -354,7 +354,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
                             if (band < bands) {   // ragged last band group
                                 float4 t = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
                                 float v[4] = {t.x, t.y, t.z, t.w};
-                                finish_band<CB == 2 ? 1 : 0>(v, sxr[r], lane, svr[b], band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
+                                finish_band<CB == 2 ? 1 : 0>(v, sxr[r], lane, svr[b], band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual);
                             }
                         }
                     }
@@ -427,9 +427,9 @@ __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
             }
         }
     }
-    if (p.mul1 == 2) finish_band<2>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
-    else if (p.mul1) finish_band<1>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
-    else finish_band<0>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax);
+    if (p.mul1 == 2) finish_band<2>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual);
+    else if (p.mul1) finish_band<1>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual);
+    else finish_band<0>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual);
 }
 
 // ---------------------------------------------------------------- rotation of the activations
@@ -602,7 +602,7 @@ __global__ void __launch_bounds__(256) k_rotate_rows(const RotateFragArgs a)
             const int lr = pair / kblocks, b = pair - lr * kblocks;
             const int row = pr.row0 + lr, kcol = b * 128 + lane * 4;
             int src_row = row;
-            if constexpr (MODE & kFragGather) src_row = row < a.n_perm ? __ldg(a.perm + row) / a.div : row - a.n_perm;
+            if constexpr (MODE & kFragGather) src_row = row < a.n_perm ? min(max(__ldg(a.perm + row) / a.div, 0), max(a.n_perm / a.div - 1, 0)) : row - a.n_perm;
             uint2 x = *reinterpret_cast<const uint2*>(a.src + size_t(src_row) * k + kcol);
             if constexpr (MODE & kFragSilu) {
                 const uint2 u = *reinterpret_cast<const uint2*>(a.src_u + size_t(src_row) * k + kcol);
@@ -639,7 +639,7 @@ void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int mul1, 
 {
     if (main_grid < 2) return;
     FinishArgs f;
-    f.slabs = a.slabs; f.blocksum = a.blocksum; f.c = a.c; f.argmax = a.argmax; f.svh = a.svh;
+    f.slabs = a.slabs; f.blocksum = a.blocksum; f.c = a.c; f.argmax = a.argmax; f.residual = a.residual; f.svh = a.svh;
     f.problems = a.problems; f.n_problems = a.n_problems;
     f.max_problems = a.max_problems; f.n_matrices = a.n_matrices; f.max_rows = a.max_rows;
     f.m = a.m; f.k = a.k; f.n = a.n; f.out_fp32 = a.out_fp32;
@@ -656,8 +656,9 @@ void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int mul1, 
 // per-device workspace or the fixed in-image array of the allocation-free entry point.
 std::string launch_gemv(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32,
-                        const GemvScratch& sc, int sms, cudaStream_t stream, unsigned long long* argmax)
+                        const GemvScratch& sc, int sms, cudaStream_t stream, unsigned long long* argmax, const float* residual)
 {
+    if (residual && !out_fp32) throw std::runtime_error("exl3 linear: the residual is added to fp32 outputs only");
     if (size_m > 32) throw std::runtime_error("exl3 gemv: size_m must be <= 32");
     if (size_k % 128 != 0)
         throw std::runtime_error("exl3 linear: no linked kernel for size_k that is not a multiple of 128 (128-wide Hadamard)");
@@ -665,7 +666,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     // MUL1, one row, every CTA's units within the limb area of the in-kernel rotation: integer tensor path with the
     // weights in tensor memory (measured a few percent ahead of this kernel there, behind it elsewhere)
     if (codebook == 2 && size_m == 1 && gemv_i8_rotates_in_kernel(size_m, size_k, size_n, k_bits, sms))
-        return launch_gemv_i8(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, out_fp32, sc, sms, stream, argmax);
+        return launch_gemv_i8(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, out_fp32, sc, sms, stream, argmax, 1, residual);
     const int tg = size_m <= 8 ? 1 : (size_m <= 16 ? 2 : 4);
     const int bu = k_bits <= 4 ? 2 : 1;   // bands per unit, as Geo<BITS, TG>::BU
     const int bands = size_n / 128, kblocks = size_k / 128, bgroups = (bands + bu - 1) / bu;
@@ -703,6 +704,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     args.a_had = static_cast<__half*>(a_had);
     args.c = c;
     args.argmax = argmax;
+    args.residual = residual;
     args.svh = static_cast<const __half*>(svh);
     args.slabs = sc.slabs;
     args.counters = nullptr;
@@ -761,6 +763,7 @@ std::string launch_gemv_grouped_rotated(const void* trellis_stack, int n_experts
     args.a = nullptr; args.suh = nullptr; args.a_had = nullptr;
     args.c = c;
     args.argmax = nullptr;
+    args.residual = nullptr;
     args.svh = static_cast<const __half*>(svh_stack);
     args.problems = problems;
     args.n_problems = n_problems;
@@ -835,6 +838,7 @@ std::string launch_gemv_sliced(const void* a, const void* b_list, const void* su
     args.a = nullptr; args.suh = nullptr; args.a_had = nullptr;
     args.c = nullptr;
     args.argmax = nullptr;
+    args.residual = nullptr;
     args.svh = nullptr;
     args.problems = nullptr;
     args.n_problems = nullptr;
@@ -871,8 +875,10 @@ std::string launch_gemv_sliced(const void* a, const void* b_list, const void* su
 // cudaFree or any allocating routine.
 //
 // The scratch is one file-scope __device__ array: 4 MiB of fp32 partial-sum slabs, 2 MiB for the
-// rotated activations in fragment order, one fp32 block sum per (row, 128 inputs) (128 KiB) and a
-// status word.  Every GPU that loads the library carries it until the process exits.  All calls on
+// rotated activations in fragment order, one fp32 block sum per (row, 128 inputs) (128 KiB), 16 KiB of
+// band-group arrival counters and a status word (which berth_device_status reads and clears together with
+// the ordinary workspace's).  At 17..32 rows the 4 MiB of slabs hold the partial sums of 64 CTAs, so the
+// launch runs on 64 SMs there; up to 16 rows it takes the whole GPU.  Every GPU that loads the library carries it until the process exits.  All calls on
 // a device share it and it keeps whatever the previous call left behind: nothing needs clearing,
 // slabs, fragments and block sums are fully overwritten before they are read.  Two calls that
 // overlap on the GPU (different streams) race on it; issue them on one stream.
@@ -921,6 +927,21 @@ GemvScratch static_scratch(int device)
 }
 
 }  // namespace
+
+// Status word of the fixed in-image scratch on `device`: read and cleared (0 if the entry point was never used there).
+int read_static_status(int device)
+{
+    GemvScratch s;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mu);
+        s = g_static_ptr[device];
+    }
+    if (!s.status) return 0;
+    unsigned v = 0;
+    cuda_ok(cudaMemcpy(&v, s.status, sizeof v, cudaMemcpyDeviceToHost), "static status read");
+    if (v) cuda_ok(cudaMemset(s.status, 0, sizeof v), "static status clear");
+    return int(v);
+}
 }  // namespace berth
 
 extern "C" int berth_exl3_linear_static_scratch(const void* a, const void* trellis, void* c, const void* suh,
@@ -943,9 +964,11 @@ extern "C" int berth_exl3_linear_static_scratch(const void* a, const void* trell
         if (size_n / 128 > kStaticMaxBands)
             throw std::runtime_error("exl3 linear (static scratch): size_n " + std::to_string(size_n) +
                                      " exceeds the maximum of " + std::to_string(kStaticMaxBands * 128) + " columns");
-        if (size_k / 128 > kStaticMaxKBlocks || size_t(size_k) * ((size_m + 7) / 8) > 131072)
+        // rows are processed in groups of 8, 16 or 32 (as launch_gemv does); the rotated rows of a group share the 2 MiB area
+        const int row_groups = size_m <= 8 ? 1 : (size_m <= 16 ? 2 : 4);
+        if (size_k / 128 > kStaticMaxKBlocks || size_t(size_k) * row_groups > 131072)
             throw std::runtime_error("exl3 linear (static scratch): size_k " + std::to_string(size_k) + " with " +
-                                     std::to_string(size_m) + " rows exceeds the maximum of size_k * ceil(size_m / 8) <= 131072");
+                                     std::to_string(size_m) + " rows exceeds the maximum of size_k * g <= 131072 (g = 1, 2, 4 for up to 8, 16, 32 rows)");
         const int device = current_device();
         const DeviceInfo& info = device_info(device);
         if (info.major != 10)

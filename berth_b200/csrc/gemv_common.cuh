@@ -27,6 +27,7 @@ struct GemvArgs {
     __half* a_had;
     void* c;                  // output rows [rows][n]
     unsigned long long* argmax;   // dense launch only, may be null: per row the key of its largest output (finish_band)
+    const float* residual;        // dense launch with fp32 output only, may be null: rows [m][n] added to the output (may be c itself)
     const __half* svh;        // [n], or the stack [experts][n] when grouped
     const GemvProblem* problems;   // grouped launch: one entry per (expert, chunk of <= 8*TG rows); else null
     const int* n_problems;         // grouped launch: device-side count
@@ -226,7 +227,8 @@ template <int MUL1>
 // with atomicMax to the row's largest output: the greedy token of an lm_head without a pass over the logits (ties go
 // to the lower column; the value is the one that would be stored, fp16-rounded for fp16 outputs).  `c` may then be null.
 __device__ __forceinline__ void finish_band(float (&v)[4], float sx, int lane, uint2 sr, int band, void* c,
-                                            size_t out_row, int n, int out_fp32, unsigned long long* best = nullptr)
+                                            size_t out_row, int n, int out_fp32, unsigned long long* best = nullptr,
+                                            const float* residual = nullptr)
 {
     const int col = band * 128 + lane * 4;
     if constexpr (MUL1 != 0) {
@@ -244,6 +246,10 @@ __device__ __forceinline__ void finish_band(float (&v)[4], float sx, int lane, u
     v[2] = __fmul_rn(__fmul_rn(v[2], kRScale), __low2float(s1));
     v[3] = __fmul_rn(__fmul_rn(v[3], kRScale), __high2float(s1));
     if (out_fp32) {
+        if (residual) {   // c = residual + linear (fp32 outputs only; c may be the residual itself: each element is read, then written, by one thread)
+            const float4 r = *reinterpret_cast<const float4*>(residual + out_row * n + col);
+            v[0] = __fadd_rn(r.x, v[0]); v[1] = __fadd_rn(r.y, v[1]); v[2] = __fadd_rn(r.z, v[2]); v[3] = __fadd_rn(r.w, v[3]);
+        }
         if (c) *reinterpret_cast<float4*>(static_cast<float*>(c) + out_row * n + col) = make_float4(v[0], v[1], v[2], v[3]);
     } else {
         const __half h0 = __float2half_rn(v[0]), h1 = __float2half_rn(v[1]), h2 = __float2half_rn(v[2]), h3 = __float2half_rn(v[3]);
@@ -294,6 +300,7 @@ struct FinishArgs {
     const float* blocksum;
     void* c;
     unsigned long long* argmax;
+    const float* residual;
     const __half* svh;
     const GemvProblem* problems;
     const int* n_problems;

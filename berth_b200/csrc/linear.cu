@@ -138,6 +138,26 @@ extern "C" int berth_exl3_linear_stack(const void* a, const void* trellis_stack,
     });
 }
 
+// The decode linear with the residual added in its last step: c = residual + linear(a), fp32, size_m <= 32.  What berth
+// does with berth_exl3_linear followed by berth_ops_add_f32 (crates/berth-engine/src/model.rs:976-1022: x = x + mlp(h2)).
+extern "C" int berth_exl3_linear_add(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
+                                     const void* residual, int size_m, int size_k, int size_n, int k_bits, int codebook, void* stream)
+{
+    CallState& st = exl3_state();
+    return guarded(st, [&] {
+        if (!a || !trellis || !c || !suh || !a_had || !svh || !residual) throw std::runtime_error("exl3 linear add: null device pointer");
+        if (size_m < 1 || size_k < 1 || size_n < 1) throw std::runtime_error("exl3 linear add: sizes must be positive");
+        if (size_m > 32) throw std::runtime_error("exl3 linear add: size_m must be <= 32 (the decode kernels)");
+        check_linear_args("exl3 linear add", a, trellis, c, suh, a_had, svh, size_k, size_n, k_bits, codebook);
+        const int device = current_device();
+        const DeviceInfo& info = device_info(device);
+        if (info.major != 10)
+            throw std::runtime_error("exl3 linear add: no linked kernel for this GPU (library is built for sm_100a only)");
+        st.launch = launch_gemv(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, 1, gemv_workspace(device), info.sms,
+                                (cudaStream_t) stream, nullptr, static_cast<const float*>(residual)) + " [residual added in the last step]";
+    });
+}
+
 extern "C" void berth_argmax_key_decode(unsigned long long key, int32_t* token, float* value)
 {
     const uint32_t ord = uint32_t(key >> 32);

@@ -232,6 +232,18 @@ __global__ void __launch_bounds__(128) k_moe_topk(const float* __restrict__ logi
             const int oi = __shfl_xor_sync(dq::kFull, bi, off);
             if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
+        if (bi == 0x7fffffff) {
+            // nothing compared greater than -inf: what is left of the row is NaN (or the row is all -inf).  Take the lowest
+            // expert not selected yet, so that the k indices are always distinct and inside [0, E): the dispatch and
+            // combine kernels index arrays with them.
+            int fi = 0x7fffffff;
+#pragma unroll
+            for (int i = kMaxPerLane - 1; i >= 0; --i)
+                if (i < per && !((taken >> i) & 1u) && lane + 32 * i < E) fi = lane + 32 * i;
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) fi = min(fi, __shfl_xor_sync(dq::kFull, fi, off));
+            bi = fi;
+        }
         if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
         if (s == 0) first = bv;
         const float ex = expf(bv - first);
@@ -241,6 +253,9 @@ __global__ void __launch_bounds__(128) k_moe_topk(const float* __restrict__ logi
     }
     if (lane < k) topk_w[size_t(t) * k + lane] = mine / sum;
 }
+
+// Status bits of the expert stage: a peer's flag never arrived; rows did not fit a receive buffer or a problem table.
+enum : unsigned { kStEpTimeout = 32u, kStEpOverflow = 64u };
 
 // ---------------------------------------------------------------- dispatch
 // counts[j] = number of entries whose key is e0 + j.  One block per local expert.
@@ -272,9 +287,13 @@ __global__ void __launch_bounds__(256) k_moe_count(const int32_t* __restrict__ k
 // pair_rows > 0: the table is written twice, the second copy behind the first with every matrix index raised by
 // pair_matrices and every first row by pair_rows, and n_problems[1] = the doubled count: one grouped launch over the
 // doubled table then runs two stacks that lie behind one another (gate and up) on the same rows.
+// max_problems / max_rows: capacity of one copy of the table and of the row arrays.  Counts that ask for more (a skewed
+// exchange that delivered more rows than the caller sized the stage for) are cut there -- entries past the table are
+// not written, first rows stay inside the arrays -- and kStEpOverflow is raised in `status`: wrong numbers with a status
+// bit, never a write past the table.
 __device__ __forceinline__ int scan_problems(int c_routed, int* __restrict__ offsets, GemvProblem* __restrict__ problems,
                                              int* __restrict__ n_problems, int n_routed, int chunk, int extra_rows, int pair_rows,
-                                             int pair_matrices)
+                                             int pair_matrices, int max_problems, int max_rows, unsigned* status)
 {
     __shared__ int wrows[32], wprob[32];
     const int j = threadIdx.x, lane = j & 31, warp = j >> 5;
@@ -301,34 +320,41 @@ __device__ __forceinline__ int scan_problems(int c_routed, int* __restrict__ off
     __syncthreads();
     const int row0 = prow - c + (warp ? wrows[warp - 1] : 0);
     const int p0 = pprob - np + (warp ? wprob[warp - 1] : 0);
+    const int total = min(wprob[31], max_problems);   // problems of one copy that fit the table
     if (j < n_local) {
-        offsets[j] = row0;
-        for (int i = 0; i < np; ++i) {
+        offsets[j] = min(row0, max_rows);
+        for (int i = 0; i < np && p0 + i < max_problems; ++i) {
             GemvProblem pr;
             pr.z = j; pr.row0 = row0 + i * chunk; pr.rows = min(chunk, c - i * chunk); pr.pad = 0;
+            if (pr.row0 + pr.rows > max_rows) {   // rows past the arrays: cut the problem (load_problem clamps the rest)
+                pr.rows = max(0, max_rows - pr.row0);
+                pr.row0 = min(pr.row0, max_rows);
+            }
             problems[p0 + i] = pr;
             if (pair_rows > 0) {
                 pr.z += pair_matrices; pr.row0 += pair_rows;
-                problems[wprob[31] + p0 + i] = pr;
+                problems[total + p0 + i] = pr;
             }
         }
     }
     if (j == 0) {
-        offsets[n_local] = wrows[31];
-        n_problems[0] = wprob[31];
-        n_problems[1] = pair_rows > 0 ? 2 * wprob[31] : 0;
+        offsets[n_local] = min(wrows[31], max_rows);
+        n_problems[0] = total;
+        n_problems[1] = pair_rows > 0 ? 2 * total : 0;
+        if ((wprob[31] > max_problems || wrows[31] > max_rows) && status) atomicOr(status, kStEpOverflow);
     }
     return row0;
 }
 
 __global__ void __launch_bounds__(1024) k_moe_scan(const int* __restrict__ counts, int* __restrict__ offsets,
                                                    GemvProblem* __restrict__ problems, int* __restrict__ n_problems,
-                                                   int n_routed, int chunk, int extra_rows, int pair_rows, int pair_matrices)
+                                                   int n_routed, int chunk, int extra_rows, int pair_rows, int pair_matrices,
+                                                   int max_problems, int max_rows, unsigned* status)
 {
     pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
     pdl_wait();
     scan_problems(threadIdx.x < n_routed ? counts[threadIdx.x] : 0, offsets, problems, n_problems, n_routed, chunk, extra_rows, pair_rows,
-                  pair_matrices);
+                  pair_matrices, max_problems, max_rows, status);
 }
 
 // Count, scan and stable scatter in one block for a short key list (n <= kSmallKeys).  Warp 0 walks the keys 32 at
@@ -340,7 +366,7 @@ __global__ void __launch_bounds__(1024) k_moe_dispatch_small(const int32_t* __re
                                                              int* __restrict__ offsets, GemvProblem* __restrict__ problems,
                                                              int* __restrict__ n_problems, int n_routed, int chunk, int extra_rows,
                                                              int pair_rows, int pair_matrices, int32_t* __restrict__ perm,
-                                                             int32_t* __restrict__ inv)
+                                                             int32_t* __restrict__ inv, int max_problems, int max_rows, unsigned* status)
 {
     pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
     pdl_wait();
@@ -367,7 +393,8 @@ __global__ void __launch_bounds__(1024) k_moe_dispatch_small(const int32_t* __re
     __syncthreads();
     const int c = j < n_routed ? s_cnt[j] : 0;
     if (j < n_routed) counts[j] = c;
-    const int row0 = scan_problems(c, offsets, problems, n_problems, n_routed, chunk, extra_rows, pair_rows, pair_matrices);
+    const int row0 = scan_problems(c, offsets, problems, n_problems, n_routed, chunk, extra_rows, pair_rows, pair_matrices, max_problems,
+                                   max_rows, status);
     if (j < n_routed) s_row0[j] = row0;
     __syncthreads();
     for (int i = j; i < n; i += blockDim.x) {
@@ -445,17 +472,18 @@ __global__ void __launch_bounds__(256) k_moe_gather_n(const __half* __restrict__
 // out[t][h] = sum_s w[t][s] * y[inv[t*k+s]][h]  (fmaf chain in slot order)  + ysh[t][h]
 __global__ void __launch_bounds__(256) k_moe_combine(const __half* __restrict__ y, const int32_t* __restrict__ inv,
                                                      const float* __restrict__ topk_w, const __half* __restrict__ ysh,
-                                                     float* __restrict__ out, int H, int k)
+                                                     float* __restrict__ out, int H, int k, int n_rows)
 {
     pdl_trigger();   // launched as a programmatic dependent: let the successor become resident, then wait for the predecessor
     pdl_wait();
     // block = (token, 512 columns); the token's row positions and weights first, so that the k row reads of a column
-    // pair are independent loads
+    // pair are independent loads.  Positions are forced into [0, n_rows): a stale index array gives wrong numbers, never
+    // a wild address.
     __shared__ int s_pos[32];
     __shared__ float s_w[32];
     const int t = blockIdx.x;
     if (threadIdx.x < k) {
-        s_pos[threadIdx.x] = inv[size_t(t) * k + threadIdx.x];
+        s_pos[threadIdx.x] = min(max(inv[size_t(t) * k + threadIdx.x], 0), n_rows - 1);
         s_w[threadIdx.x] = topk_w[size_t(t) * k + threadIdx.x];
     }
     __syncthreads();
@@ -525,7 +553,6 @@ __global__ void __launch_bounds__(128) k_moe_segment_keys(const int* __restrict_
 // it sets a status bit and the layer carries on with whatever is there.
 constexpr int kMaxPeers = 8;
 struct PeerPtrs { void* p[kMaxPeers]; };
-enum : unsigned { kStEpTimeout = 32u, kStEpOverflow = 64u };
 
 // Thread s < W: tell rank s that this rank has reached `phase` of layer call `epoch`, then wait for rank s to
 // say the same.  flags: uint32 [3 phases][kMaxPeers sources] on every rank.  Everything this block wrote to
@@ -636,7 +663,8 @@ __global__ void __launch_bounds__(256) k_ep_dispatch(const __half* __restrict__ 
             if (threadIdx.x == 0) atomicOr(status, kStEpOverflow);
             continue;
         }
-        const uint4* src = reinterpret_cast<const uint4*>(x + size_t(perm[pos] / top_k) * H);
+        const int tok = min(max(perm[pos] / top_k, 0), n_send / top_k - 1);   // (n_send = tokens x top_k)
+        const uint4* src = reinterpret_cast<const uint4*>(x + size_t(tok) * H);
         uint4* out = reinterpret_cast<uint4*>(static_cast<__half*>(recv_rows.p[e / n_local]) + size_t(dst) * H);
         for (int i = threadIdx.x; i < H / 8; i += 256) out[i] = src[i];
     }
@@ -842,15 +870,17 @@ void router_topk(const void* x, const void* w_router, const float* bias, int32_t
 void dispatch(const int32_t* keys, int n, int e0, int n_local, int chunk, const ExpertScratch& s, int32_t* perm, int32_t* inv,
               cudaStream_t st, int extra_rows = 0, int pair_rows = 0, int pair_matrices = 0)
 {
+    unsigned* status = gemv_workspace(current_device()).status;
+    const int max_rows = n + extra_rows;   // the arrays the caller carved for this stage
     if (n_local + (extra_rows > 0 ? 1 : 0) > 1024) throw std::runtime_error("moe: too many local experts for the scan kernel");
     if (n <= kSmallKeys) {
-        launch_pdl(k_moe_dispatch_small, dim3(1), dim3(1024), 0, st, "k_moe_dispatch_small launch", keys, n, e0, s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows, pair_rows, pair_matrices, perm, inv);
+        launch_pdl(k_moe_dispatch_small, dim3(1), dim3(1024), 0, st, "k_moe_dispatch_small launch", keys, n, e0, s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows, pair_rows, pair_matrices, perm, inv, s.max_problems, max_rows, status);
         cuda_ok(cudaGetLastError(), "k_moe_dispatch_small launch");
         return;
     }
     launch_pdl(k_moe_count, dim3(n_local), dim3(256), 0, st, "k_moe_count launch", keys, n, e0, s.counts);
     cuda_ok(cudaGetLastError(), "k_moe_count launch");
-    launch_pdl(k_moe_scan, dim3(1), dim3(1024), 0, st, "k_moe_scan launch", s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows, pair_rows, pair_matrices);
+    launch_pdl(k_moe_scan, dim3(1), dim3(1024), 0, st, "k_moe_scan launch", s.counts, s.offsets, s.problems, s.n_problems, n_local, chunk, extra_rows, pair_rows, pair_matrices, s.max_problems, max_rows, status);
     cuda_ok(cudaGetLastError(), "k_moe_scan launch");
     launch_pdl(k_moe_scatter, dim3(n_local), dim3(1024), 0, st, "k_moe_scatter launch", keys, n, e0, s.offsets, perm, inv);
     cuda_ok(cudaGetLastError(), "k_moe_scatter launch");
@@ -1047,7 +1077,7 @@ extern "C" int berth_moe_combine(const void* y, const int32_t* inv, const float*
     return guarded(st, [&] {
         if (!y || !inv || !topk_w || !out) throw std::runtime_error("moe combine: null device pointer");
         if (T < 1 || hidden < 2 || hidden % 2 || top_k < 1 || top_k > 32) throw std::runtime_error("moe combine: bad sizes (top_k must be in 1..=32)");
-        k_moe_combine<<<dim3(T, (hidden + 511) / 512), 256, 0, (cudaStream_t) stream>>>((const __half*) y, inv, topk_w, (const __half*) ysh, (float*) out, hidden, top_k);
+        k_moe_combine<<<dim3(T, (hidden + 511) / 512), 256, 0, (cudaStream_t) stream>>>((const __half*) y, inv, topk_w, (const __half*) ysh, (float*) out, hidden, top_k, 0x7fffffff);
         cuda_ok(cudaGetLastError(), "k_moe_combine launch");
         st.launch = "k_moe_combine grid=" + std::to_string(T);
     });
@@ -1088,6 +1118,7 @@ extern "C" int berth_moe_ep_send(const void* x, int T, const void* w_router, con
         es.offsets = (int*) take(size_t(n_experts + 2) * 4);
         es.n_problems = (int*) take(4);
         es.problems = (GemvProblem*) take((size_t(R) / 8 + n_experts + 1) * sizeof(GemvProblem));
+        es.max_problems = R / 8 + n_experts;
         router_topk(x, w_router, router_bias, topk_idx, topk_w, logits, T, hidden, n_experts, top_k, cs);
         dispatch(topk_idx, R, 0, n_experts, 8, es, perm, inv, cs);
         launch_pdl(k_moe_gather_rows, dim3(std::min(R, 148 * 8)), dim3(256), 0, cs, "k_moe_gather_rows launch", (const __half*) x, perm, es.offsets + n_experts, top_k, (__half*) send_rows, hidden);
@@ -1239,6 +1270,7 @@ extern "C" int berth_moe_p2p_send(const void* x, int T, const void* w_router, co
         const P2pSendWs s = carve_p2p_send(base, std::max(T, 1), n_experts, top_k, world, n_local);
         ExpertScratch es{};
         es.counts = s.counts; es.offsets = s.offsets; es.n_problems = s.n_problems; es.problems = s.problems;
+        es.max_problems = std::max(T, 1) * top_k / 8 + n_experts;   // as carve_p2p_send sized the table
         if (T > 0) {
             router_topk(x, w_router, router_bias, topk_idx, topk_w, s.logits, T, hidden, n_experts, top_k, cs);
             dispatch(topk_idx, R, 0, n_experts, 8, es, s.perm, inv, cs);
@@ -1302,7 +1334,7 @@ extern "C" int berth_moe_p2p_experts(const berth_moe_weights* w, const void* x_l
         RowSource in_place{};
         in_place.paired = up_behind_gate(w, NM);
         launch_pdl(k_moe_scan, dim3(1), dim3(1024), 0, cs, "k_moe_scan launch", es.counts, es.offsets, es.problems, es.n_problems, NL, plan.chunk, TS,
-                   in_place.paired ? max_rows : 0, NM);
+                   in_place.paired ? max_rows : 0, NM, es.max_problems, max_rows, sc.status);
         cuda_ok(cudaGetLastError(), "k_moe_scan launch");
         if (TS) {
             k_rows_to_offset<<<std::min(TS, 148 * 8), 256, 0, cs>>>((const __half*) x_local, xr, es.offsets + NL, TS, H, max_rows);
@@ -1399,7 +1431,7 @@ extern "C" int berth_moe_layer(const berth_moe_weights* w, const void* x, int T,
             if (berth_ops_silu_mul(sg, su, sg, int64_t(T) * SI, 0.0f, cs) != 0) throw std::runtime_error(berth_ops_last_error());
             linear_rows(sg, w->sh_down_trellis, ysh, w->sh_down_suh, sr, w->sh_down_svh, T, SI, H, w->k_bits, w->codebook, 0, cs);
         }
-        launch_pdl(k_moe_combine, dim3(T, (H + 511) / 512), dim3(256), 0, cs, "k_moe_combine launch", yr, inv, topk_w, ysh, (float*) out, H, K);
+        launch_pdl(k_moe_combine, dim3(T, (H + 511) / 512), dim3(256), 0, cs, "k_moe_combine launch", yr, inv, topk_w, ysh, (float*) out, H, K, R);
         cuda_ok(cudaGetLastError(), "k_moe_combine launch");
         st.launch = std::string("k_moe_router_logits + k_moe_topk + ") + (R <= kSmallKeys ? "k_moe_dispatch_small" : "k_moe_count/scan/scatter") +
                     " + " + st.launch + " + k_moe_combine" + (fused_shared ? " [shared expert as matrix E of the grouped launches]" : "");

@@ -132,6 +132,92 @@ __global__ void __launch_bounds__(256) k_add_f32(const float* a, const float* b,
     if (i < n) c[i] = __fadd_rn(a[i], b[i]);
 }
 
+// RMSNorm of one row per block (128 threads): y = fp16(((v * r) * (w + bias)) * scale), r = 1 / sqrt(mean(v^2) + eps),
+// v = x, or with RES_IN the residual row after residual += x (written back).  The sum of squares is taken in a fixed
+// order -- thread j folds the groups of four elements j, j + 128, ... with fmaf, the 128 partial sums are added by a
+// halving tree inside each warp and as (w0 + w1) + (w2 + w3) across the four warps -- and every other step is one
+// correctly rounded fp32 operation, so the rows equal the CPU checker's bit for bit.
+template <bool X_F16, bool W_BF16, bool RES_IN>
+__global__ void __launch_bounds__(128) k_rms_norm(const void* __restrict__ x_, const uint16_t* __restrict__ w, __half* __restrict__ y,
+                                                  float* __restrict__ residual, int dim, float eps, float bias, float scale)
+{
+    pdl_trigger();
+    pdl_wait();
+    const size_t row = blockIdx.x;
+    const int j = threadIdx.x, lane = j & 31, warp = j >> 5, chunks = dim >> 2;
+    auto load4 = [&](int c) {
+        float4 v;
+        if constexpr (X_F16) {
+            const uint2 h = *reinterpret_cast<const uint2*>(static_cast<const __half*>(x_) + row * dim + 4 * c);
+            const __half2 a = *reinterpret_cast<const __half2*>(&h.x), b = *reinterpret_cast<const __half2*>(&h.y);
+            v = make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+        } else {
+            v = *reinterpret_cast<const float4*>(static_cast<const float*>(x_) + row * dim + 4 * c);
+        }
+        return v;
+    };
+    float s = 0.f;
+    for (int c = j; c < chunks; c += 128) {
+        float4 v = load4(c);
+        if constexpr (RES_IN) {
+            float4* rp = reinterpret_cast<float4*>(residual + row * dim + 4 * c);
+            const float4 r = *rp;
+            v = make_float4(__fadd_rn(r.x, v.x), __fadd_rn(r.y, v.y), __fadd_rn(r.z, v.z), __fadd_rn(r.w, v.w));
+            *rp = v;
+        }
+        s = __fmaf_rn(v.x, v.x, s); s = __fmaf_rn(v.y, v.y, s); s = __fmaf_rn(v.z, v.z, s); s = __fmaf_rn(v.w, v.w, s);
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, off));
+    __shared__ float ws[4];
+    if (lane == 0) ws[warp] = s;
+    __syncthreads();
+    const float total = __fadd_rn(__fadd_rn(ws[0], ws[1]), __fadd_rn(ws[2], ws[3]));
+    const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, float(dim)), eps)));
+    for (int c = j; c < chunks; c += 128) {
+        float4 v;
+        if constexpr (RES_IN) v = *reinterpret_cast<const float4*>(residual + row * dim + 4 * c);   // this thread's own stores
+        else v = load4(c);
+        const uint2 wr = *reinterpret_cast<const uint2*>(w + 4 * c);
+        float wf[4];
+        if constexpr (W_BF16) {
+            wf[0] = __uint_as_float(wr.x << 16); wf[1] = __uint_as_float(wr.x & 0xffff0000u);
+            wf[2] = __uint_as_float(wr.y << 16); wf[3] = __uint_as_float(wr.y & 0xffff0000u);
+        } else {
+            const __half2 a = *reinterpret_cast<const __half2*>(&wr.x), b = *reinterpret_cast<const __half2*>(&wr.y);
+            wf[0] = __low2float(a); wf[1] = __high2float(a); wf[2] = __low2float(b); wf[3] = __high2float(b);
+        }
+        const float in[4] = {v.x, v.y, v.z, v.w};
+        __half o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            o[i] = __float2half_rn(__fmul_rn(__fmul_rn(__fmul_rn(in[i], rinv), __fadd_rn(wf[i], bias)), scale));
+        uint2 st;
+        st.x = dq::pack_half2(o[0], o[1]);
+        st.y = dq::pack_half2(o[2], o[3]);
+        *reinterpret_cast<uint2*>(y + row * dim + 4 * c) = st;
+    }
+}
+
+// Host checks of crates/berth-kernels/csrc/ops/norm.cu:107-127 (berth), same wording.
+void check_rms(const void* x, const void* w, const void* y, const void* r, int rows, int dim, bool res_in, int weight_bf16)
+{
+    if (!x || !w || !y) throw std::runtime_error("rms_norm: null device pointer");
+    if (res_in && !r) throw std::runtime_error("rms_norm: RES_IN requires a residual pointer");
+    if (rows < 1 || dim < 1) throw std::runtime_error("rms_norm: rows and dim must be positive");
+    if (dim % 4 != 0) throw std::runtime_error("rms_norm: dim must be a multiple of 4");
+    if (weight_bf16 != 0 && weight_bf16 != 1) throw std::runtime_error("rms_norm: weight_bf16 must be 0 or 1");
+}
+
+template <bool X_F16, bool W_BF16, bool RES_IN>
+std::string launch_rms(const void* x, const void* w, void* y, void* r, int rows, int dim, float eps, float bias, float scale, cudaStream_t st)
+{
+    launch_pdl(k_rms_norm<X_F16, W_BF16, RES_IN>, dim3(rows), dim3(128), 0, st, "rms_norm launch", x, static_cast<const uint16_t*>(w),
+               static_cast<__half*>(y), static_cast<float*>(r), dim, eps, bias, scale);
+    return std::string("k_rms_norm<") + (X_F16 ? "half" : "float") + "," + (W_BF16 ? "bfloat16" : "half") + (RES_IN ? ",res_in" : "") +
+           "> block=128 grid=" + std::to_string(rows);
+}
+
 }  // namespace
 
 // SiLU(gate) * up over the first *n_rows rows (device-side count, at most max_rows) of row_elems fp16 each.
@@ -244,5 +330,40 @@ extern "C" int berth_ops_add_f32(const void* a, const void* b, void* c, int n, v
         launch_pdl(k_add_f32, dim3(grid), dim3(256), 0, (cudaStream_t) stream, "add_f32 launch", (const float*) a,
                    (const float*) b, (float*) c, n);
         st.launch = "k_add_f32 block=256 grid=" + std::to_string(grid);
+    });
+}
+
+// RMSNorm of berth's decode blocks: crates/berth-kernels/csrc/ops/norm.cu:129-224 (same symbols, arguments, checks).
+extern "C" int berth_ops_rms_norm(const void* x, const void* weight, void* y, int rows, int dim, float epsilon, float constant_bias,
+                                  float constant_scale, int weight_bf16, void* stream)
+{
+    CallState& st = ops_state();
+    return guarded(st, [&] {
+        check_rms(x, weight, y, nullptr, rows, dim, false, weight_bf16);
+        cudaStream_t cs = (cudaStream_t) stream;
+        st.launch = weight_bf16 ? launch_rms<false, true, false>(x, weight, y, nullptr, rows, dim, epsilon, constant_bias, constant_scale, cs)
+                                : launch_rms<false, false, false>(x, weight, y, nullptr, rows, dim, epsilon, constant_bias, constant_scale, cs);
+    });
+}
+
+extern "C" int berth_ops_rms_norm_f16(const void* x, const void* weight, void* y, int rows, int dim, float epsilon, float constant_bias,
+                                      float constant_scale, void* stream)
+{
+    CallState& st = ops_state();
+    return guarded(st, [&] {
+        check_rms(x, weight, y, nullptr, rows, dim, false, 1);
+        st.launch = launch_rms<true, true, false>(x, weight, y, nullptr, rows, dim, epsilon, constant_bias, constant_scale, (cudaStream_t) stream);
+    });
+}
+
+extern "C" int berth_ops_rms_norm_res_in(const void* x, const void* weight, void* y, void* residual, int rows, int dim, float epsilon,
+                                         float constant_bias, float constant_scale, int weight_bf16, void* stream)
+{
+    CallState& st = ops_state();
+    return guarded(st, [&] {
+        check_rms(x, weight, y, residual, rows, dim, true, weight_bf16);
+        cudaStream_t cs = (cudaStream_t) stream;
+        st.launch = weight_bf16 ? launch_rms<false, true, true>(x, weight, y, residual, rows, dim, epsilon, constant_bias, constant_scale, cs)
+                                : launch_rms<false, false, true>(x, weight, y, residual, rows, dim, epsilon, constant_bias, constant_scale, cs);
     });
 }

@@ -84,6 +84,8 @@ GemvScratch gemv_workspace(int device)
 
 // Reads and clears the status word of the library's scratch on `device` (synchronises).
 // 0 = every bounded wait of the decode kernels completed.
+int read_static_status(int device);   // gemv.cu: the fixed in-image scratch of the allocation-free entry point
+
 int read_gemv_status(int device)
 {
     GemvScratch w;
@@ -109,7 +111,7 @@ extern "C" int berth_device_cc(int device)
 
 extern "C" int berth_device_status(int device)
 {
-    try { return berth::read_gemv_status(device); } catch (const std::exception&) { cudaGetLastError(); return -1; }
+    try { return berth::read_gemv_status(device) | berth::read_static_status(device); } catch (const std::exception&) { cudaGetLastError(); return -1; }
 }
 
 extern "C" int berth_device_sms(int device)

@@ -83,6 +83,16 @@ def exl3_linear_static_scratch(a, trellis, c, suh, a_had, svh, size_m: int, size
         raise Error(last_error() or f"exl3 linear (static scratch) launch failed ({rc})")
 
 
+def exl3_linear_add(a, trellis, c, suh, a_had, svh, residual, size_m: int, size_k: int, size_n: int, k_bits: int,
+                    codebook: Codebook, stream=None) -> None:
+    """:func:`exl3_linear` (``size_m <= 32``, fp32 output) with ``residual`` added in the kernel's last step;
+    ``c`` may be ``residual``."""
+    rc = _lib.lib().berth_exl3_linear_add(_ptr(a), _ptr(trellis), _ptr(c), _ptr(suh), _ptr(a_had), _ptr(svh), _ptr(residual), size_m,
+                                          size_k, size_n, k_bits, int(codebook), _stream(stream))
+    if rc != 0:
+        raise Error(last_error() or f"exl3 linear add launch failed ({rc})")
+
+
 def exl3_linear_stack(a, trellis_stack, c, suh_stack, a_had, svh_stack, n_matrices: int, size_m: int, size_k: int, size_n: int,
                       k_bits: int, codebook: Codebook, out: OutDtype, stream=None) -> None:
     """``n_matrices`` equally shaped MUL1 linears (stored one behind the other) applied to the same ``size_m <= 8`` rows in
@@ -228,3 +238,30 @@ class ops:
         rc = _lib.lib().berth_ops_add_f32(_ptr(a), _ptr(b), _ptr(c), n, _stream(stream))
         if rc != 0:
             raise Error(ops.last_error() or f"add_f32 launch failed ({rc})")
+
+    @staticmethod
+    def rms_norm(x, weight, y, rows: int, dim: int, epsilon: float, constant_bias: float, constant_scale: float,
+                 weight_bf16: bool, stream=None) -> None:
+        """``ops::rms_norm`` (crates/berth-kernels/src/ops.rs): fp32 rows -> fp16 rows."""
+        rc = _lib.lib().berth_ops_rms_norm(_ptr(x), _ptr(weight), _ptr(y), rows, dim, epsilon, constant_bias, constant_scale,
+                                           1 if weight_bf16 else 0, _stream(stream))
+        if rc != 0:
+            raise Error(ops.last_error() or f"rms_norm launch failed ({rc})")
+
+    @staticmethod
+    def rms_norm_f16(x, weight, y, rows: int, dim: int, epsilon: float, constant_bias: float, constant_scale: float,
+                     stream=None) -> None:
+        """``ops::rms_norm_f16``: fp16 rows, bfloat16 weight -> fp16 rows."""
+        rc = _lib.lib().berth_ops_rms_norm_f16(_ptr(x), _ptr(weight), _ptr(y), rows, dim, epsilon, constant_bias, constant_scale,
+                                               _stream(stream))
+        if rc != 0:
+            raise Error(ops.last_error() or f"rms_norm_f16 launch failed ({rc})")
+
+    @staticmethod
+    def rms_norm_res_in(x, weight, y, residual, rows: int, dim: int, epsilon: float, constant_bias: float, constant_scale: float,
+                        weight_bf16: bool, stream=None) -> None:
+        """``ops::rms_norm_res_in``: residual += x in place (fp32), y = the norm of the updated residual."""
+        rc = _lib.lib().berth_ops_rms_norm_res_in(_ptr(x), _ptr(weight), _ptr(y), _ptr(residual), rows, dim, epsilon, constant_bias,
+                                                  constant_scale, 1 if weight_bf16 else 0, _stream(stream))
+        if rc != 0:
+            raise Error(ops.last_error() or f"rms_norm_res_in launch failed ({rc})")

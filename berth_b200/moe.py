@@ -19,6 +19,11 @@ from .kernels import Error, _s
 _PTR_FIELDS = [n for n, _ in _lib.MoeWeights._fields_[7:]]
 
 
+def _cur_stream(device) -> int:
+    """Raw handle of torch's current stream on `device`: the stream the layers' tensors are ordered on."""
+    return torch.cuda.current_stream(device).cuda_stream
+
+
 def last_error() -> str:
     return _s(_lib.lib().berth_moe_last_error())
 
@@ -184,21 +189,21 @@ class GpuStages:
             keys = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._check(_lib.lib().berth_moe_sort_rows(keys.data_ptr(), n, e0, n_local, perm.data_ptr(), inv.data_ptr(), offsets.data_ptr(),
                                                    ews.data_ptr(), ews.numel(), self.max_rows, self.d["hidden"], self.d["inter"],
-                                                   self.rows_hint(n, n_local), None))
+                                                   self.rows_hint(n, n_local), _cur_stream(self.device)))
         return perm[:n], inv[:n], offsets
 
     def gather(self, src, index, div: int):
         n, H = index.numel(), src.shape[1]
         dst = torch.empty((n, H), dtype=torch.float16, device=self.device)
         if n:
-            self._check(_lib.lib().berth_moe_gather(src.data_ptr(), index.data_ptr(), div, n, dst.data_ptr(), H, None))
+            self._check(_lib.lib().berth_moe_gather(src.data_ptr(), index.data_ptr(), div, n, dst.data_ptr(), H, _cur_stream(self.device)))
         return dst
 
     def experts(self, xr):
         R = xr.shape[0]
         yr = torch.empty_like(xr)
         self._check(_lib.lib().berth_moe_experts(C.byref(self.layer.c), xr.data_ptr(), yr.data_ptr(), R, self.ews_loc.data_ptr(),
-                                                 self.ews_loc.numel(), self.max_rows, self.rows_hint(R, self.d["n_experts"]), None))
+                                                 self.ews_loc.numel(), self.max_rows, self.rows_hint(R, self.d["n_experts"]), _cur_stream(self.device)))
         return yr
 
     def shared_expert(self, x, stream=None):
@@ -249,7 +254,7 @@ class GpuStages:
         bias = kp.get("router_bias")
         self._check(l.berth_moe_ep_send(x.data_ptr(), T, kp["w_router"].data_ptr(), None if bias is None else bias.data_ptr(), H, E, k,
                                         idx.data_ptr(), w.data_ptr(), inv.data_ptr(), rows.data_ptr(), counts.data_ptr(),
-                                        self._send_ws.data_ptr(), self._send_ws.numel(), None))
+                                        self._send_ws.data_ptr(), self._send_ws.numel(), _cur_stream(self.device)))
         return idx, w, inv, rows, counts
 
     def shared_is_stacked(self) -> bool:
@@ -276,7 +281,7 @@ class GpuStages:
         self._check(l.berth_moe_ep_experts(C.byref(self.layer.c), recv_rows.data_ptr() if R else None, R, cnt_recv.data_ptr(), world,
                                            x_local.data_ptr() if T else None, T, back.data_ptr() if R else None,
                                            None if ysh is None else ysh.data_ptr(), self._exp_ws.data_ptr(), self._exp_ws.numel(),
-                                           self.max_rows, self._exp_tokens, self.rows_hint(R, nl), None))
+                                           self.max_rows, self._exp_tokens, self.rows_hint(R, nl), _cur_stream(self.device)))
         return back, ysh
 
     def combine(self, y, inv, w, ysh):
@@ -284,7 +289,7 @@ class GpuStages:
         H = y.shape[1]
         out = torch.empty((T, H), dtype=torch.float32, device=self.device)
         self._check(_lib.lib().berth_moe_combine(y.data_ptr(), inv.data_ptr(), w.data_ptr(), None if ysh is None else ysh.data_ptr(),
-                                                 out.data_ptr(), T, H, k, None))
+                                                 out.data_ptr(), T, H, k, _cur_stream(self.device)))
         return out
 
 
@@ -462,7 +467,7 @@ class P2pMoeLayer:
         p = lambda t: t.data_ptr() if t.numel() else None
         st._check(l.berth_moe_p2p_send(p(x), T, kp["w_router"].data_ptr(), None if bias is None else bias.data_ptr(), H, self.E, k,
                                        p(idx), p(w), inv.data_ptr(), self.rank, self.world, self.epoch, self.cnt_ptrs, self.flag_ptrs,
-                                       self.recv_ptrs, self.max_rows, self.send_ws.data_ptr(), self.send_ws.numel(), None))
+                                       self.recv_ptrs, self.max_rows, self.send_ws.data_ptr(), self.send_ws.numel(), _cur_stream(dev)))
         stacked = st.shared_is_stacked() and T > 0
         ysh = torch.empty((T, H), dtype=torch.float16, device=dev) if stacked else None
         # rows per local expert to size the problems for: twice the mean if every rank holds as many tokens as this one
@@ -470,7 +475,7 @@ class P2pMoeLayer:
         st._check(l.berth_moe_p2p_experts(C.byref(st.layer.c), p(x), T, None if ysh is None else ysh.data_ptr(), self.rank, self.world,
                                           self.epoch, self.E, k, T, self.cnt_ptrs, self.flag_ptrs, self.recv_ptrs, self.ret_ptrs,
                                           self.max_rows, max(self.max_send, 1), hint, self.send_ws.data_ptr(), self.exp_ws.data_ptr(),
-                                          self.exp_ws.numel(), None))
+                                          self.exp_ws.numel(), _cur_stream(dev)))
         if T == 0:
             return torch.empty((0, H), dtype=torch.float32, device=dev), idx, w
         if ysh is None and getattr(st, "shared", None) is not None:

@@ -58,10 +58,12 @@ const char* berth_exl3_last_launch(void);   /* crates/berth-kernels/csrc/linear.
 /* Same linear for callers that must not allocate device memory (a host whose own planner owns
  * every byte of HBM, or a decode loop that cannot take cudaMalloc's device-wide synchronisation).
  * No counterpart in berth: its library allocates its workspaces with cudaMalloc at first use.
- * The scratch is a fixed __device__ array of about 6.1 MiB inside the library image (4 MiB
- * partial-sum slabs, 2 MiB rotated activations, 128 KiB block sums, a status word), held by
- * every GPU that loads the library until the process exits; nothing is allocated or freed.  Limits: size_m <= 32, size_n <= 131072 and size_k * ceil(size_m / 8) <= 131072;
- * larger sizes are rejected with an error.  The first
+ * The scratch is a fixed __device__ array of about 6.2 MiB inside the library image (4 MiB
+ * partial-sum slabs, 2 MiB rotated activations, 128 KiB block sums, 16 KiB counters, a status word),
+ * held by every GPU that loads the library until the process exits; nothing is allocated or freed.
+ * Limits: size_m <= 32, size_n <= 131072 and size_k * g <= 131072 with g = 1, 2, 4 for up to 8, 16, 32
+ * rows; larger sizes are rejected with an error before anything is launched.  With 17..32 rows the slab
+ * area holds the partial sums of 64 CTAs, so those launches run on 64 SMs.  The first
  * call on a device looks the array's device address up (cudaGetSymbolAddress); make that first
  * call before any stream capture begins.  All calls on a device share the scratch, which keeps
  * the previous call's contents (every part is overwritten before it is read): calls that overlap
@@ -75,10 +77,14 @@ int berth_exl3_linear_static_scratch(const void* a, const void* trellis, void* c
  * enumeration orders them: old, Ampere, Ada, Hopper, Blackwell; SM count). -1 on error. */
 int berth_device_cc(int device);
 int berth_device_sms(int device);
-/* Reads and clears the status word of the decode kernels on `device` (this call synchronises
- * the device).  The kernels never wait without a limit: a wait that runs out sets a bit here
- * (1 = a weight stage never arrived, 2 = a stage was never released) and the launch finishes
- * with undefined output instead of hanging.  0 = clean, -1 = CUDA error.  No counterpart in berth. */
+/* Reads and clears the status words of the kernels on `device`: the library's workspace and the
+ * fixed scratch of berth_exl3_linear_static_scratch, OR-ed together (this call synchronises the
+ * device).  The kernels never wait without a limit: a wait that runs out sets a bit here and the
+ * launch finishes with undefined output instead of hanging.  Bits: 1 = a weight stage never arrived,
+ * 2 = a stage was never released, 4 = a tensor-memory stage or accumulator of the integer-path decode
+ * kernel was never handed over, 16 = a wait of the tensor-core GEMM ran out, 32 = a peer's flag of the
+ * expert-parallel exchange never arrived, 64 = rows did not fit a receive buffer or a problem table of
+ * the expert stage.  0 = clean, -1 = CUDA error.  No counterpart in berth. */
 int berth_device_status(int device);
 
 /* Diagnostic, no counterpart in berth: the bare decode rate of one SM.  Runs the inner loop of the
@@ -111,6 +117,14 @@ int berth_exl3_linear_argmax(const void* a, const void* trellis, void* c, const 
                              unsigned long long* best, int size_m, int size_k, int size_n, int k_bits, int codebook,
                              int out_fp32, void* stream);
 void berth_argmax_key_decode(unsigned long long key, int32_t* token, float* value);
+
+/* The decode linear (size_m <= 32) with the residual stream added in its last step: c = residual + linear(a), fp32
+ * [size_m][size_n]; c may be the residual itself (x += mlp(h2) in place).  Bit for bit what berth_exl3_linear with
+ * out_fp32 = 1 followed by berth_ops_add_f32(residual, c, c) gives (crates/berth-engine/src/model.rs:976-1022), in
+ * the launches of the linear alone.  No counterpart in berth. */
+int berth_exl3_linear_add(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
+                          const void* residual, int size_m, int size_k, int size_n, int k_bits, int codebook,
+                          void* stream);
 
 /* A stack of n_matrices equally shaped MUL1 linears applied to the same size_m <= 8 rows in ONE decode launch:
  * trellis_stack int16 [n][size_k/16][size_n/16][16*k_bits], suh_stack fp16 [n][size_k], svh_stack fp16 [n][size_n];
@@ -158,6 +172,19 @@ int berth_ops_silu_mul(const void* gate, const void* up, void* out, int64_t nume
                        float act_limit, void* stream);
 /* c = a + b, fp32; c may alias a (crates/berth-kernels/src/ops.rs:91-97, csrc/ops/add.cu:29-54). */
 int berth_ops_add_f32(const void* a, const void* b, void* c, int n, void* stream);
+/* RMSNorm of the decode blocks: replaces berth_ops_rms_norm, berth_ops_rms_norm_f16 and berth_ops_rms_norm_res_in
+ * (crates/berth-kernels/src/ops.rs:55-80,108-118, csrc/ops/norm.cu:129-224; call sites
+ * crates/berth-engine/src/model.rs:793,854).  y fp16 [rows][dim] = ((v * r) * (weight + constant_bias)) * constant_scale,
+ * r = 1 / sqrt(mean(v^2) + epsilon); v = x (fp32; fp16 for _f16), or for _res_in the fp32 residual row after
+ * residual += x, written back in place.  weight: bfloat16 (weight_bf16 = 1; always for _f16) or fp16 [dim].
+ * dim must be a multiple of 4.  Errors through berth_ops_last_error with berth's wording. */
+int berth_ops_rms_norm(const void* x, const void* weight, void* y, int rows, int dim, float epsilon,
+                       float constant_bias, float constant_scale, int weight_bf16, void* stream);
+int berth_ops_rms_norm_f16(const void* x, const void* weight, void* y, int rows, int dim, float epsilon,
+                           float constant_bias, float constant_scale, void* stream);
+int berth_ops_rms_norm_res_in(const void* x, const void* weight, void* y, void* residual, int rows, int dim,
+                              float epsilon, float constant_bias, float constant_scale, int weight_bf16,
+                              void* stream);
 const char* berth_ops_last_error(void);
 const char* berth_ops_last_launch(void);
 

@@ -440,6 +440,57 @@ void exl3o_add_f32(const float* a, const float* b, float* c, int64_t n)
     for (int64_t i = 0; i < n; ++i) c[i] = a[i] + b[i];
 }
 
+/* RMSNorm of berth's decode blocks (crates/berth-kernels/csrc/ops/norm.cu:129-224: berth_ops_rms_norm,
+ * _f16, _res_in; semantics of crates/berth-engine/src/model.rs:76-100: epsilon inside the reciprocal square
+ * root, constant_bias added to the weight, constant_scale multiplies the normalised row):
+ *   y[e] = fp16( ((x[e] * r) * (w[e] + constant_bias)) * constant_scale ),  r = 1 / sqrt(mean(x^2) + epsilon),
+ * every step one correctly rounded fp32 operation.  The device kernel of berth lives in the absent fork, so the
+ * summation order of mean(x^2) is this build's ("spec v0"): 128 partial sums, partial j taking the groups of
+ * four consecutive elements j, j + 128, j + 256, ... in ascending order with fmaf(x, x, s); the 128 partials
+ * are added as four groups of 32 by a halving tree (strides 16, 8, 4, 2, 1), the four group sums as
+ * (g0 + g1) + (g2 + g3).  x_is_f16: the input row is fp16 (the _f16 entry point), else fp32.
+ * weight_bf16: the weight is bfloat16, else fp16.  residual != NULL (RES_IN): residual += x first (fp32, in
+ * place), and the row that is normalised is the updated residual. */
+static float bf16_to_f32(uint16_t b)
+{
+    union { uint32_t u; float f; } v;
+    v.u = (uint32_t) b << 16;
+    return v.f;
+}
+
+void exl3o_rms_norm(const void* x, int x_is_f16, const uint16_t* weight, int weight_bf16, uint16_t* y, float* residual,
+                    int rows, int dim, float epsilon, float constant_bias, float constant_scale)
+{
+    for (int r = 0; r < rows; ++r) {
+        float part[128];
+        for (int j = 0; j < 128; ++j) part[j] = 0.0f;
+        float* res = residual ? residual + (size_t) r * dim : NULL;
+        for (int e = 0; e < dim; ++e) {
+            float v = x_is_f16 ? exl3o_h2f(((const uint16_t*) x)[(size_t) r * dim + e]) : ((const float*) x)[(size_t) r * dim + e];
+            if (res) { res[e] = res[e] + v; v = res[e]; }
+            const int j = (e / 4) % 128;
+            part[j] = fmaf(v, v, part[j]);
+        }
+        float grp[4];
+        for (int g = 0; g < 4; ++g) {
+            float t[32];
+            for (int i = 0; i < 32; ++i) t[i] = part[32 * g + i];
+            for (int off = 16; off >= 1; off >>= 1)
+                for (int i = 0; i < off; ++i) t[i] = t[i] + t[i + off];
+            grp[g] = t[0];
+        }
+        const float total = (grp[0] + grp[1]) + (grp[2] + grp[3]);
+        const float mean = total / (float) dim;
+        const float rinv = 1.0f / sqrtf(mean + epsilon);
+        for (int e = 0; e < dim; ++e) {
+            const float v = res ? res[e]
+                                : (x_is_f16 ? exl3o_h2f(((const uint16_t*) x)[(size_t) r * dim + e]) : ((const float*) x)[(size_t) r * dim + e]);
+            const float w = (weight_bf16 ? bf16_to_f32(weight[e]) : exl3o_h2f(weight[e])) + constant_bias;
+            y[(size_t) r * dim + e] = exl3o_f2h(((v * rinv) * w) * constant_scale);
+        }
+    }
+}
+
 /* ------------------------------------------------------------------ host integer logic */
 
 int exl3o_gemv_cfg(int cc, int m, int k, int n, int bits, int cb, int mode, int narrow_coresident)

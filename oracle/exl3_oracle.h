@@ -76,6 +76,9 @@ void exl3o_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, int
                     float act_limit);
 /* c = a + b in fp32 (crates/berth-kernels/csrc/ops/add.cu:23-27). */
 void exl3o_add_f32(const float* a, const float* b, float* c, int64_t n);
+/* RMSNorm (berth_ops_rms_norm / _f16 / _res_in); the summation order is stated at the definition. */
+void exl3o_rms_norm(const void* x, int x_is_f16, const uint16_t* weight, int weight_bf16, uint16_t* y, float* residual,
+                    int rows, int dim, float epsilon, float constant_bias, float constant_scale);
 
 /* ---- host-only integer logic of the boundary ---- */
 /* crates/berth-kernels/csrc/prefill_lin/gemv.cu:72-101 */

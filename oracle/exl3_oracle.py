@@ -79,6 +79,8 @@ def _declare(l: C.CDLL) -> None:
     l.exl3o_linear_f64.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i]
     l.exl3o_silu_mul.argtypes = [_vp, _vp, _vp, _i64, _f]
     l.exl3o_add_f32.argtypes = [_vp, _vp, _vp, _i64]
+    l.exl3o_rms_norm.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _f, _f, _f]
+    l.exl3o_rms_norm.restype = None
     l.exl3o_gemv_cfg.restype = _i
     l.exl3o_gemv_cfg.argtypes = [_i] * 8
     l.exl3o_gemm_tune_key.restype = C.c_uint64
@@ -211,6 +213,25 @@ def add_f32(a, b) -> np.ndarray:
     c = np.empty_like(a)
     lib().exl3o_add_f32(_p(a), _p(b), _p(c), a.size)
     return c
+
+
+def rms_norm(x, weight, weight_bf16: bool, epsilon: float, constant_bias: float = 0.0, constant_scale: float = 1.0,
+             residual=None):
+    """RMSNorm rows of ``x`` (float32, or float16 for the _f16 form) with ``weight`` (uint16 bit patterns: bfloat16 or
+    float16).  Returns the float16 rows; with ``residual`` (float32 array, updated in place: residual += x) the rows
+    normalised are the updated residual (RES_IN)."""
+    x = np.ascontiguousarray(x)
+    rows, dim = x.shape
+    is_f16 = x.dtype == np.float16
+    if not is_f16:
+        x = x.astype(np.float32, copy=False)
+    w = _u16(weight)
+    y = np.empty((rows, dim), np.uint16)
+    if residual is not None:
+        assert residual.dtype == np.float32 and residual.flags["C_CONTIGUOUS"] and residual.shape == (rows, dim)
+    lib().exl3o_rms_norm(_p(x.view(np.uint16) if is_f16 else x), 1 if is_f16 else 0, _p(w), 1 if weight_bf16 else 0, _p(y),
+                         None if residual is None else _p(residual), rows, dim, epsilon, constant_bias, constant_scale)
+    return y.view(np.float16)
 
 
 def gemv_cfg(cc, m, k, n, bits, cb, mode, narrow_coresident) -> int:

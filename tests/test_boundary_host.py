@@ -190,3 +190,31 @@ def test_argmax_key_decode_known_answers(lib):
         kernels.exl3_linear_argmax(None, None, None, None, None, None, None, 1, 128, 256, 4, Codebook.Mul1, OutDtype.F16)
     with pytest.raises(Error, match="size_m"):
         kernels.exl3_linear_argmax(P, P, P, P, P, P, P, 33, 128, 256, 4, Codebook.Mul1, OutDtype.F16)
+
+
+def test_rms_norm_argument_checks(lib):
+    """Checks of crates/berth-kernels/csrc/ops/norm.cu:107-127, before any CUDA call."""
+    o = kernels.ops
+    with pytest.raises(Error, match="null device pointer"):
+        o.rms_norm(None, P, P, 1, 128, 1e-6, 1.0, 1.0, True)
+    with pytest.raises(Error, match="RES_IN requires a residual pointer"):
+        o.rms_norm_res_in(P, P, P, None, 1, 128, 1e-6, 1.0, 1.0, True)
+    with pytest.raises(Error, match="rows and dim must be positive"):
+        o.rms_norm(P, P, P, 0, 128, 1e-6, 1.0, 1.0, True)
+    with pytest.raises(Error, match="multiple of 4"):
+        o.rms_norm_f16(P, P, P, 1, 130, 1e-6, 1.0, 1.0)
+    assert lib.berth_ops_rms_norm(P, P, P, 1, 128, 1e-6, 1.0, 1.0, 2, None) == -1
+    assert "weight_bf16 must be 0 or 1" in o.last_error()
+
+
+def test_linear_add_and_stack_argument_checks(lib):
+    with pytest.raises(Error, match="null"):
+        kernels.exl3_linear_add(P, P, P, P, P, P, None, 1, 128, 128, 4, Codebook.Mul1)
+    with pytest.raises(Error, match="size_m must be <= 32"):
+        kernels.exl3_linear_add(P, P, P, P, P, P, P, 33, 128, 128, 4, Codebook.Mul1)
+    with pytest.raises(Error, match="multiple of 128"):
+        kernels.exl3_linear_add(P, P, P, P, P, P, P, 1, 128, 100, 4, Codebook.Mul1)
+    with pytest.raises(Error, match="n_matrices"):
+        kernels.exl3_linear_stack(P, P, P, P, P, P, 0, 1, 128, 128, 4, Codebook.Mul1, OutDtype.F16)
+    with pytest.raises(Error, match="no linked kernel"):
+        kernels.exl3_linear_stack(P, P, P, P, P, P, 2, 9, 128, 128, 4, Codebook.Mul1, OutDtype.F16)

@@ -56,6 +56,46 @@ def test_router_ties_and_bias(oracle):
     assert (idx == exp_idx).all()
 
 
+def test_router_topk_nan_rows_give_valid_indices():
+    """A token row of NaN activations (all its logits NaN), a row whose logits are NaN for some experts only, and an
+    ordinary row: the k indices of every row are distinct and inside [0, E) -- the dispatch and combine kernels index
+    arrays with them -- and the ordinary row is unaffected.  Only berth_moe_router_topk runs: it writes indices and
+    weights and dereferences nothing through them."""
+    H, E, k = 128, 64, 8
+    x = synth.activations(9, "nan.x", 3, H).copy()
+    x[0, :] = np.float16("nan")
+    wr = synth.router_weight(9, "nan.w", H, E).copy()
+    idx, w, logits = _route(x, wr, None, k)
+    assert np.isnan(logits[0]).all()
+    for t in range(3):
+        assert len(set(idx[t].tolist())) == k and idx[t].min() >= 0 and idx[t].max() < E, (t, idx[t])
+    assert (idx[0] == np.arange(k)).all()                      # nothing compares: the lowest experts, in order
+    # NaN for half of the experts of row 1: the finite ones win first
+    wr2 = wr.copy()
+    wr2[:, ::2] = np.float16("nan")
+    idx2, w2, logits2 = _route(x[1:2], wr2, None, k)
+    assert np.isnan(logits2[0, ::2]).all() and np.isfinite(logits2[0, 1::2]).all()
+    assert (idx2[0] % 2 == 1).all() and len(set(idx2[0].tolist())) == k
+    order = np.argsort(-logits2[0, 1::2], kind="stable")[:k] * 2 + 1
+    assert (idx2[0] == order).all()
+
+
+def test_moe_layer_with_nan_row_returns(oracle):
+    """The whole layer with one NaN token among ordinary ones: it returns with a clean status, the NaN row's output is
+    NaN, and every other token's output is what it is without the NaN row."""
+    H, I, E, k, bits, cb = 256, 128, 32, 4, 4, 2
+    wts = synth.moe_layer_weights(1234, "moe42", H, I, E, k, bits, cb, shared_inter=128)
+    x = synth.activations(1234, "nanrow.x", 6, H).copy()
+    clean, idx_c, _ = _run_layer(wts, x)
+    x[2, :] = np.float16("nan")
+    out, idx, w = _run_layer(wts, x)                            # asserts device_status == 0
+    assert np.isnan(out[2]).all()
+    keep = [0, 1, 3, 4, 5]
+    assert (idx[keep] == idx_c[keep]).all()
+    assert (out[keep].view(np.uint32) == clean[keep].view(np.uint32)).all()
+    assert len(set(idx[2].tolist())) == k and 0 <= idx[2].min() and idx[2].max() < E
+
+
 def _run_layer(wts, x, fuse_shared=True, pair_gate_up=True):
     T = x.shape[0]
     layer = moe.MoeLayer(torch.device("cuda"), wts, T, fuse_shared=fuse_shared, pair_gate_up=pair_gate_up)
@@ -284,6 +324,77 @@ def test_peer_memory_layer_on_one_rank():
     finally:
         if own_group:
             dist.destroy_process_group()
+
+
+def test_expert_stage_overflow_sets_status_and_returns():
+    """A peer-memory layer on one rank whose receive buffer is sized for fewer rows than the routing produces: the
+    senders drop the rows that do not fit, the problem table of the receiving side is cut at the buffer, status bit 64
+    is raised, the call returns (no wild access), and the next call with a fitting batch is clean."""
+    import torch.distributed as dist
+    if not dist.is_available() or not dist.is_nccl_available():
+        pytest.skip("torch.distributed with NCCL is not available")
+    H, I, E, k, bits, cb = 256, 128, 32, 4, 4, 2
+    wts = synth.moe_layer_weights(1234, "p2p1", H, I, E, k, bits, cb, shared_inter=128)
+    own_group = not dist.is_initialized()
+    if own_group:
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29534", rank=0, world_size=1,
+                                device_id=torch.device("cuda", torch.cuda.current_device()))
+    try:
+        device = torch.device("cuda", torch.cuda.current_device())
+        max_rows = 40 * k + 40                      # fits 40 tokens (and their shared-expert rows)
+        stages = moe.GpuStages(device, wts, E, max_rows=max_rows, max_rows_per_expert=64)
+        try:
+            layer = moe.P2pMoeLayer(stages, dist.group.WORLD, E, k, max_tokens=64, max_rows=max_rows)
+        except Exception as exc:
+            pytest.skip(f"symmetric memory unavailable: {exc!r}")
+        assert kernels.device_status(torch.cuda.current_device()) == 0
+        x = synth.activations(1234, "p2p.over.x", 64, H)          # 64 tokens: 256 + 64 rows > 200
+        out, idx, w = layer.forward(dev(x))
+        torch.cuda.synchronize()
+        assert kernels.device_status(torch.cuda.current_device()) & 64
+        x = synth.activations(1234, "p2p.fit.x", 24, H)
+        ref, ref_idx, _ = _run_layer(wts, x)
+        out, idx, w = layer.forward(dev(x))
+        torch.cuda.synchronize()
+        assert kernels.device_status(torch.cuda.current_device()) == 0
+        assert (idx.cpu().numpy() == ref_idx).all()
+        assert np.abs(out.cpu().numpy() - ref).max() <= 1e-3 * np.sqrt((ref.astype(np.float64) ** 2).mean())
+    finally:
+        if own_group:
+            dist.destroy_process_group()
+
+
+def test_expert_parallel_flag_wait_runs_out_and_reports():
+    """The bounded wait of the expert-parallel exchange, made to run out without harming anything: rank 0 of a
+    two-rank exchange whose "peer" buffers are ordinary local allocations that nobody else writes.  The flag of rank 1
+    never arrives, the wait gives up after its limit (well under a second per barrier), the call returns, and
+    berth_device_status reports bit 32; a following ordinary layer call is clean.  No rank is killed, nothing faults:
+    every store of the call lands in the local stand-in buffers."""
+    import ctypes as C
+    from berth_b200 import _lib
+    H, E, k, T, world = 256, 32, 4, 8, 2
+    l = _lib.lib()
+    dev_ = torch.device("cuda", torch.cuda.current_device())
+    x = dev(synth.activations(1234, "flag.x", T, H))
+    wr = dev(synth.router_weight(1234, "flag.w", H, E))
+    z = lambda n, dt=torch.uint8: torch.zeros(n, dtype=dt, device=dev_)
+    max_rows = T * k + T
+    cnt = [z(world * E * 4) for _ in range(world)]
+    flags = [z(3 * 8 * 4) for _ in range(world)]
+    recv = [z(max_rows * H * 2) for _ in range(world)]
+    ptrs = lambda ts: (C.c_void_p * world)(*[t.data_ptr() for t in ts])
+    ws = z(l.berth_moe_p2p_send_workspace_bytes(T, E, k, world))
+    idx, w, inv = z(T * k, torch.int32), z(T * k, torch.float32), z(T * k, torch.int32)
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+    rc = l.berth_moe_p2p_send(x.data_ptr(), T, wr.data_ptr(), None, H, E, k, idx.data_ptr(), w.data_ptr(), inv.data_ptr(), 0, world, 1,
+                              ptrs(cnt), ptrs(flags), ptrs(recv), max_rows, ws.data_ptr(), ws.numel(), None)
+    assert rc == 0, moe.last_error()
+    torch.cuda.synchronize()                       # returns: the waits are bounded
+    assert kernels.device_status(torch.cuda.current_device()) & 32
+    assert kernels.device_status(torch.cuda.current_device()) == 0      # read-and-clear
+    assert int(idx.min()) >= 0 and int(idx.max()) < E                    # the routing itself was done
+    wts = synth.moe_layer_weights(1234, "moe42", 256, 128, 32, 4, 4, 2, shared_inter=128)
+    _run_layer(wts, synth.activations(1234, "flag.after", 3, 256))      # asserts a clean status
 
 
 def test_peer_memory_layer_matches_nccl_layer():

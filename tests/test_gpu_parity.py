@@ -562,3 +562,70 @@ def test_prefill_config2_shapes_against_decoded_bands(name, K, N, bits, out_fp32
         assert _lib_reconstruct(wt, td, K, 128, N, n0, bits, cb) == 0
         y = (a_rot @ wt.double()) @ hmat / np.sqrt(128.0) * svh[n0:n0 + 128]
         assert_close(c[:, n0:n0 + 128].double().cpu().numpy(), y.cpu().numpy(), f"{name} band {b}")
+
+
+# ---------------------------------------------------------------- RMSNorm and the residual add: bit-exact
+
+def _bf16_bits(a):
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 5120), (5, 2048), (3, 132), (64, 6144)])
+@pytest.mark.parametrize("wbf", [True, False])
+def test_rms_norm_bit_exact(oracle, rows, dim, wbf):
+    """berth_ops_rms_norm, _f16 and _res_in against the checker, bit for bit (same summation order, every other step
+    one correctly rounded fp32 operation); the residual rows of the _res_in form as well."""
+    x = synth.activations(21, f"rms.x{rows}x{dim}", rows, dim).astype(np.float32) * 2.5
+    w32 = synth.activations(21, f"rms.w{dim}", 1, dim).astype(np.float32)[0] * 0.1
+    w = _bf16_bits(w32) if wbf else w32.astype(np.float16).view(np.uint16)
+    eps, bias, scale = 1e-6, 1.0, 0.75
+    wd = dev(w)
+    y = torch.zeros((rows, dim), dtype=torch.float16, device="cuda")
+    kernels.ops.rms_norm(torch.from_numpy(x).cuda(), wd, y, rows, dim, eps, bias, scale, wbf)
+    torch.cuda.synchronize()
+    assert "k_rms_norm" in kernels.ops.last_launch()
+    assert (host_u16(y) == oracle.rms_norm(x, w, wbf, eps, bias, scale).view(np.uint16)).all()
+    res = synth.activations(21, f"rms.r{rows}x{dim}", rows, dim).astype(np.float32)
+    res_d = torch.from_numpy(res.copy()).cuda()
+    kernels.ops.rms_norm_res_in(torch.from_numpy(x).cuda(), wd, y, res_d, rows, dim, eps, bias, scale, wbf)
+    torch.cuda.synchronize()
+    exp_res = res.copy()
+    exp_y = oracle.rms_norm(x, w, wbf, eps, bias, scale, residual=exp_res)
+    assert (res_d.cpu().numpy().view(np.uint32) == exp_res.view(np.uint32)).all()
+    assert (host_u16(y) == exp_y.view(np.uint16)).all()
+    if wbf:
+        xh = x.astype(np.float16)
+        kernels.ops.rms_norm_f16(dev(xh), wd, y, rows, dim, eps, bias, scale)
+        torch.cuda.synchronize()
+        assert (host_u16(y) == oracle.rms_norm(xh, w, True, eps, bias, scale).view(np.uint16)).all()
+
+
+@pytest.mark.parametrize("m,K,N,bits,cb", [(1, 1024, 768, 4, 2), (1, 5120, 6144, 4, 2), (3, 512, 640, 4, 2), (20, 512, 256, 5, 2),
+                                           (1, 1024, 512, 4, 0), (6, 512, 384, 3, 1)])
+def test_linear_add_equals_linear_then_add(oracle, m, K, N, bits, cb):
+    """berth_exl3_linear_add (the residual added in the decode kernel's last step) gives bit for bit what
+    berth_exl3_linear with fp32 output followed by berth_ops_add_f32 gives, also in place on the residual; and the
+    sum is the checker's fp64 linear plus the residual within the tolerance."""
+    w = synth.linear_weights(1234, f"ladd{K}x{N}b{bits}", K, N, bits)
+    x = synth.activations(1234, f"ladd.x{m}", m, K)
+    r = synth.activations(1234, f"ladd.r{m}", m, N).astype(np.float32) * 4.0
+    xd, td, sd, vd = dev(x), dev(w["trellis"]), dev(w["suh"]), dev(w["svh"])
+    rd = torch.from_numpy(r).cuda()
+    ah = torch.zeros((m, K), dtype=torch.float16, device="cuda")
+    y = torch.empty((m, N), dtype=torch.float32, device="cuda")
+    kernels.exl3_linear(xd, td, y, sd, ah, vd, m, K, N, bits, Codebook(cb), OutDtype.F32)
+    unfused = torch.empty_like(y)
+    kernels.ops.add_f32(rd, y, unfused, m * N)
+    fused = torch.full((m, N), float("nan"), dtype=torch.float32, device="cuda")
+    kernels.exl3_linear_add(xd, td, fused, sd, ah, vd, rd, m, K, N, bits, Codebook(cb))
+    assert "residual" in kernels.last_launch()
+    inplace = rd.clone()
+    kernels.exl3_linear_add(xd, td, inplace, sd, ah, vd, inplace, m, K, N, bits, Codebook(cb))
+    torch.cuda.synchronize()
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+    assert torch.equal(fused.view(torch.int32), unfused.view(torch.int32))
+    assert torch.equal(inplace.view(torch.int32), unfused.view(torch.int32))
+    y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, N, bits, cb)
+    mx, mean = rel_errors(fused.cpu().numpy() - r, y64)
+    assert mx <= MAX_REL and mean <= MEAN_REL

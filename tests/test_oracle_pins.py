@@ -299,3 +299,36 @@ def test_moe_layer_vs_composition(oracle):
     rms = np.sqrt((y64 ** 2).mean())
     err = np.abs(out - y64) / rms
     assert err.max() <= 1e-2 and err.mean() <= 1e-3
+
+
+def _bf16(a):
+    """float32 array -> bfloat16 bit patterns (round to nearest even)."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 5120), (3, 2048), (2, 132)])
+def test_rms_norm_oracle_against_float64(oracle, rows, dim):
+    """The checker's RMSNorm (one published formula, this build's summation order) against a float64 evaluation of
+    y = x / sqrt(mean(x^2) + eps) * (w + bias) * scale: within fp16 rounding; the RES_IN form updates the residual
+    exactly (fp32 add) and normalises the updated row; the fp16-input form agrees with the fp32 form on fp16 data."""
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((rows, dim)).astype(np.float32) * 3.0
+    w32 = (rng.standard_normal(dim) * 0.1).astype(np.float32)
+    eps, bias, scale = 1e-6, 1.0, 1.0
+    for wbf in (True, False):
+        w = _bf16(w32) if wbf else w32.astype(np.float16).view(np.uint16)
+        wf = (w.astype(np.uint32) << 16).view(np.float32) if wbf else w.view(np.float16).astype(np.float32)
+        y = oracle.rms_norm(x, w, wbf, eps, bias, scale).astype(np.float64)
+        x64 = x.astype(np.float64)
+        ref = x64 / np.sqrt((x64 ** 2).mean(axis=1, keepdims=True) + eps) * (wf.astype(np.float64) + bias) * scale
+        assert np.abs(y - ref).max() <= 2.0 ** -10 * np.abs(ref).max()
+        res = rng.standard_normal((rows, dim)).astype(np.float32)
+        res0 = res.copy()
+        y2 = oracle.rms_norm(x, w, wbf, eps, bias, scale, residual=res)
+        assert (res == res0 + x).all()
+        assert (y2.view(np.uint16) == oracle.rms_norm(res, w, wbf, eps, bias, scale).view(np.uint16)).all()
+    xh = x.astype(np.float16)
+    w = _bf16(w32)
+    assert (oracle.rms_norm(xh, w, True, eps, bias, scale).view(np.uint16)
+            == oracle.rms_norm(xh.astype(np.float32), w, True, eps, bias, scale).view(np.uint16)).all()

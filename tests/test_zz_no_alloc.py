@@ -5,8 +5,9 @@ HBM, or their decode loop cannot absorb the device-wide stall of an allocation. 
 library offers the same linear with its split-K scratch in a fixed array inside the library
 image.  This test drives that entry point through the C ABI twice in a row (the second call
 finds the scratch exactly as the first left it) and compares both results with the ordinary
-entry point's output on the same inputs.  Collected last on purpose, so a failure here cannot
-hide the result of any other test.
+entry point's output on the same inputs and with the CPU checker's fp64 evaluation; afterwards
+the status word of the fixed scratch (read through berth_device_status) must be clean.
+Collected last on purpose, so a failure here cannot hide the result of any other test.
 """
 import numpy as np
 import pytest
@@ -15,12 +16,12 @@ torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
 from berth_b200 import Codebook, Error, OutDtype, kernels, synth   # noqa: E402
-from tests.gpu_util import dev   # noqa: E402
+from tests.gpu_util import assert_close, dev   # noqa: E402
 
 
 @pytest.mark.parametrize("m,K,N,bits,cb,out_fp32", [(1, 5120, 6144, 4, 2, False), (3, 2048, 1024, 4, 0, True),
                                                    (32, 1024, 640, 5, 1, False)])
-def test_static_scratch_matches_ordinary_entry_point_twice(m, K, N, bits, cb, out_fp32):
+def test_static_scratch_matches_ordinary_entry_point_twice(oracle, m, K, N, bits, cb, out_fp32):
     w = synth.linear_weights(1234, f"noalloc{K}x{N}", K, N, bits)
     x = synth.activations(1234, f"noalloc.x{m}", m, K)
     xd, td, sd, vd = dev(x), dev(w["trellis"]), dev(w["suh"]), dev(w["svh"])
@@ -42,6 +43,10 @@ def test_static_scratch_matches_ordinary_entry_point_twice(m, K, N, bits, cb, ou
         # same kernel; only the split-K factor (hence the summation order) may differ
         assert diff.max() <= 2e-3 * rms, (call, diff.max() / rms)
         assert torch.equal(ah, ah_ref)
+        if call == 1:
+            y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, N, bits, cb)
+            assert_close(got.float().cpu().numpy(), y64, "static scratch")
+    assert kernels.device_status(torch.cuda.current_device()) == 0
 
 
 def test_static_scratch_rejects_sizes_beyond_its_maximum():
@@ -52,3 +57,8 @@ def test_static_scratch_rejects_sizes_beyond_its_maximum():
         kernels.exl3_linear_static_scratch(P, P, P, P, P, P, 1, 128, 131072 + 128, 4, Codebook.Mul1, OutDtype.F16)
     with pytest.raises(Error, match="null"):
         kernels.exl3_linear_static_scratch(None, P, P, P, P, P, 1, 128, 128, 4, Codebook.Mul1, OutDtype.F16)
+    # 17..32 rows are processed in four groups of eight: size_k * 4 must fit (refused before any launch)
+    with pytest.raises(Error, match="exceeds the maximum of size_k"):
+        kernels.exl3_linear_static_scratch(P, P, P, P, P, P, 17, 40960, 128, 4, Codebook.Mul1, OutDtype.F16)
+    with pytest.raises(Error, match="exceeds the maximum of size_k"):
+        kernels.exl3_linear_static_scratch(P, P, P, P, P, P, 9, 69632, 128, 4, Codebook.Default, OutDtype.F16)
