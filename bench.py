@@ -452,48 +452,225 @@ def bench_moe(rank: int, world: int, steps: int = 20, tokens=(1, 64, 1024)) -> d
             ms = float(t[0])
         total = (T // world) * world if T >= world else T
         rec = {"us_per_layer": ms * 1e3, "tokens_per_s": total / ms * 1e3}
+        if world > 1 and isinstance(layer, moe.P2pMoeLayer):
+            layer.profile = True
+            run()
+            torch.cuda.synchronize()
+            ph = layer.phase_ms()
+            layer.profile = False
+            v = torch.tensor([ph["send"], ph["experts"], ph["combine"]], device=dev, dtype=torch.float64)
+            dist.all_reduce(v, op=dist.ReduceOp.MAX)
+            rec["phases_us_max_over_ranks"] = {"send": float(v[0]) * 1e3, "experts": float(v[1]) * 1e3, "combine": float(v[2]) * 1e3}
         if weak:
             out["tokens_1024_per_rank"] = dict(rec, total_tokens=total)
         else:
             out["by_tokens"][str(T)] = rec
-    if world > 1 and isinstance(layer, moe.P2pMoeLayer) and 1024 in tokens:
-        out["c4_zipf_1056_per_rank"] = bench_moe_skewed(rank, world, steps, w, dev)
+    if world > 1:
+        t_loc = 64 // world
+        xc = torch.from_numpy(synth.activations(1234, f"c3.x64.r{rank}", max(t_loc, 1), H)).to(dev)[:t_loc]
+        chk = ep_self_check(rank, layer, xc, None)
+        if rank == 0:
+            out["ep_check"] = chk
     return out
 
 
-def bench_moe_skewed(rank: int, world: int, steps: int, w: dict, dev) -> dict:
-    """Configuration 4's layer: the same experts with a router bias that skews expert popularity (Zipf exponent
-    1.1 over a seeded rank order, strength 0.25 of the log-popularity), 1056 tokens on every rank (8448 on
-    8 GPUs = 8192 prefill + 256 decode tokens).  Reports the time of one layer and the load imbalance it ran under."""
+def _gpu_expert_stacks(dev, seed: int, n_local: int, H: int, I: int, with_shared: bool) -> dict:
+    """Expert stacks of one layer generated on the device (uniform 16-bit codes, sign-scales of magnitude about 1 with the
+    1/sqrt(fan_in) gain on the output side): seeded synthetic weights for the timing runs of configuration 4, where
+    forty layers' worth (15 GiB over all ranks) would take minutes to generate on the host."""
+    import torch
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    n = n_local + (1 if with_shared else 0)
+    def stack(k, nn):
+        t = torch.randint(-32768, 32768, (n, k // 16, nn // 16, 16 * BITS), dtype=torch.int16, device=dev, generator=g)
+        sign = lambda m, gain: ((torch.randint(0, 2, (n, m), device=dev, generator=g).float() * 2 - 1)
+                                * (1 + 0.05 * torch.randn((n, m), device=dev, generator=g)) * gain).half()
+        return t, sign(k, 1.0), sign(nn, 1.0 / np.sqrt(k))
+    w = {}
+    for p, (k, nn) in (("gate", (H, I)), ("up", (H, I)), ("down", (I, H))):
+        t, su, sv = stack(k, nn)
+        w[f"{p}_trellis"], w[f"{p}_suh"], w[f"{p}_svh"] = t[:n_local], su[:n_local], sv[:n_local]
+        if with_shared:
+            w[f"sh_{p}_trellis"], w[f"sh_{p}_suh"], w[f"sh_{p}_svh"] = t[n_local], su[n_local], sv[n_local]
+    return w
+
+
+def bench_c4(rank: int, world: int, layers: int = 40, total_tokens: int = 8448, reps: int = 3) -> dict:
+    """Configuration 4: a stack of `layers` MoE layers of configuration 3's shape, every layer with its own router and
+    expert weights, 8448 tokens (8192 prefill + 256 decode) split evenly over the ranks, router bias = the log of a
+    Zipf(s = 1.1) popularity over a seeded rank order (full strength).  The same token batch enters every layer (what
+    lies between the MoE layers of a model is outside this path).  One GPU: berth_moe_layer.  Several: experts in
+    contiguous blocks (the popularity order is a seeded permutation, so popular experts are spread over the blocks),
+    exchange by peer-memory stores.  Reports the time per layer, the phases of the expert-parallel layer, the rows each
+    rank received, the realised expert popularity beside the Zipf law, and an estimate of the exposed exchange time:
+    layer time minus the same rank's routing, expert kernels and combine measured alone on the rows it received."""
     import torch
     import torch.distributed as dist
-    from berth_b200 import moe, synth
-    H, E, K = MOE["hidden"], MOE["n_experts"], MOE["top_k"]
-    T = 1056
-    bias = synth.zipf_router_bias(1234, "c4.bias", E, s=1.1, strength=0.25)
-    stages = moe.GpuStages(dev, dict(w, router_bias=bias), E, max_rows=8 * T * K, max_rows_per_expert=1024)
-    layer = moe.P2pMoeLayer(stages, dist.group.WORLD, E, K, max_tokens=T, max_rows=8 * T * K + T)
-    x = torch.from_numpy(synth.activations(1234, f"c4.x.r{rank}", T, H)).to(dev)
-    for _ in range(3):
-        layer.forward(x)
+    from berth_b200 import kernels, moe, synth
+    dev = torch.device("cuda", torch.cuda.current_device())
+    H, I, E, K, SI = MOE["hidden"], MOE["inter"], MOE["n_experts"], MOE["top_k"], MOE["shared_inter"]
+    n_local, T = E // world, total_tokens // world
+    bias = synth.zipf_router_bias(1234, "c4.bias", E, s=1.1, strength=1.0)
+    # Static expert placement for a known skew: experts are renumbered so that the contiguous blocks of the ranks hold
+    # them dealt out by popularity (the i-th most popular expert goes to rank i % world): a relabelling of the router's
+    # columns, which leaves the layer's function unchanged.
+    by_pop = np.argsort(-bias, kind="stable")
+    place = np.empty(E, np.int64)
+    for i, e in enumerate(by_pop):
+        place[(i % world) * n_local + i // world] = e
+    bias = np.ascontiguousarray(bias[place])
+    mk = []
+    for l in range(layers):
+        w = {"hidden": H, "inter": I, "n_experts": n_local, "top_k": K, "bits": BITS, "cb": CB, "shared_inter": SI,
+             "w_router": np.ascontiguousarray(synth.router_weight(1234, f"c4.{l}.gate.weight", H, E)[:, place]), "router_bias": bias}
+        w.update(_gpu_expert_stacks(dev, 77_000 + 1000 * l + rank, n_local, H, I, True))
+        mk.append(w)
+    x = torch.from_numpy(synth.activations(1234, f"c4.x.r{rank}.of{world}", T, H)).to(dev)
+    rec = {"workload": "c4_40_layer_moe_stack_zipf", "layers": layers, "total_tokens": T * world, "tokens_per_rank": T,
+           "router_bias": "ln(rank^-1.1) over a seeded rank order, strength 1.0", "expert_weights": "generated on the device, per layer",
+           "placement": "experts dealt to the ranks by popularity (i-th most popular -> rank i % world)"}
+    if world == 1:
+        lays = [moe.MoeLayer(dev, w, 1) for w in mk]
+        lays[0]._alloc(T)
+        for l in lays[1:]:
+            l.workspace, l.max_tokens = lays[0].workspace, T      # the layers run one after the other: one workspace
+        o = torch.empty((T, H), dtype=torch.float32, device=dev)
+        idx = torch.empty((T, K), dtype=torch.int32, device=dev)
+        tw = torch.empty((T, K), dtype=torch.float32, device=dev)
+        run = lambda: [l.forward(x, o, idx, tw) for l in lays]
+        counts_of = lambda: torch.bincount(idx.flatten().to(torch.int64), minlength=E)
+    else:
+        max_rows = T * world * K + T          # room for every routed row of the batch landing on one rank
+        stages = moe.GpuStages(dev, mk[0], E, max_rows=max_rows, max_rows_per_expert=1024)
+        mls = [stages.layer] + [moe.MoeLayer(dev, w, 1) for w in mk[1:]]
+        layer = moe.P2pMoeLayer(stages, dist.group.WORLD, E, K, max_tokens=T, max_rows=max_rows)
+        rec["exchange"] = "peer-memory stores + flag barriers"
+        def run():
+            for ml in mls:
+                stages.layer = ml
+                layer.forward(x)
+        counts_of = lambda: layer._cnt.view(torch.int32).view(world, E).sum(0).to(torch.int64)
+    for _ in range(2):
+        run()
     torch.cuda.synchronize()
-    dist.barrier()
+    if world > 1:
+        dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(steps):
-        layer.forward(x)
+    for _ in range(reps):
+        run()
     e1.record()
     torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t[0])
-    cnt = layer._cnt.view(torch.int32).view(world, world, E // world).sum(dim=(0, 2)).to("cpu")   # rows received per rank
-    per_expert = layer._cnt.view(torch.int32).view(world, E).sum(0).to("cpu")
-    from berth_b200 import kernels
-    return {"us_per_layer": ms * 1e3, "tokens_per_s": T * world / ms * 1e3, "total_tokens": T * world,
-            "rows_per_rank_max_over_mean": float(cnt.max()) / max(float(cnt.float().mean()), 1.0),
-            "rows_per_expert_max_over_mean": float(per_expert.max()) / max(float(per_expert.float().mean()), 1.0),
-            "device_status": kernels.device_status(torch.cuda.current_device())}
+    ms = e0.elapsed_time(e1) / (reps * layers)
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    rec.update(us_per_layer=ms * 1e3, ms_per_stack=ms * layers, tokens_per_s=T * world / ms * 1e3,
+               device_status=kernels.device_status(torch.cuda.current_device()))
+    # realised popularity of the last layer beside the law
+    c = counts_of().float().cpu().numpy()
+    order = np.argsort(-c)
+    law = np.arange(1, E + 1, dtype=np.float64) ** -1.1
+    law = law / law.sum() * c.sum()
+    rec["popularity"] = {"rows_total": float(c.sum()), "top16_rows": [int(v) for v in c[order][:16]],
+                         "zipf_1.1_top16_rows": [round(float(v), 1) for v in law[:16]],
+                         "note": "a token selects an expert at most once, so an expert's rows saturate at the token count",
+                         "rows_per_expert_max_over_mean": float(c.max() / max(c.mean(), 1.0))}
+    if world > 1:
+        per_rank = layer._cnt.view(torch.int32).view(world, world, n_local).sum(dim=(0, 2)).float().cpu().numpy()
+        rec["rows_per_rank"] = [int(v) for v in per_rank]
+        rec["rows_per_rank_max_over_mean"] = float(per_rank.max() / max(per_rank.mean(), 1.0))
+        # phases of one layer (CUDA events inside forward), max over ranks
+        layer.profile = True
+        stages.layer = mls[-1]
+        layer.forward(x)
+        torch.cuda.synchronize()
+        ph = layer.phase_ms()
+        layer.profile = False
+        # the same rank's compute measured alone on the rows it received: routing + sort, expert kernels, combine
+        n_rows = int(per_rank[rank])
+        keys = torch.repeat_interleave(torch.arange(n_local, dtype=torch.int32, device=dev),
+                                       layer._cnt.view(torch.int32).view(world, E)[:, rank * n_local:(rank + 1) * n_local].sum(0).to(torch.int64))
+        xr = layer._recv.view(torch.float16).view(-1, H)[:max(n_rows, 1)]
+        def timed(fn, n=5):
+            fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / n
+        def route_sort():
+            idx_, _ = stages.route(x)
+            stages.sort(idx_.flatten(), 0, E)
+        t_route = timed(route_sort)
+        def experts_alone():
+            stages.sort(keys, 0, n_local, for_experts=True)
+            stages.experts(xr[:n_rows])
+        t_exp = timed(experts_alone) if n_rows > 0 else 0.0
+        inv = torch.arange(T * K, dtype=torch.int32, device=dev)
+        tw = torch.full((T, K), 1.0 / K, dtype=torch.float32, device=dev)
+        t_comb = timed(lambda: stages.combine(layer.ret_rows[: T * K], inv, tw, None))
+        v = torch.tensor([ph["send"], ph["experts"], ph["combine"], t_route, t_exp, t_comb], device=dev, dtype=torch.float64)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        send, exps, comb, t_route, t_exp, t_comb = [float(q) * 1e3 for q in v]
+        rec["phases_us_max_over_ranks"] = {"send": send, "experts": exps, "combine": comb}
+        rec["compute_alone_us_max_over_ranks"] = {"route_and_sort": t_route, "expert_kernels_on_received_rows": t_exp, "combine": t_comb}
+        rec["exposed_exchange_us"] = max(0.0, (send - t_route) + (exps - t_exp))
+        rec["exposed_exchange_note"] = ("send phase minus routing+sort alone, plus experts phase minus the expert kernels alone on the "
+                                        "received rows: count publication, three flag barriers (waiting for the busiest rank included), "
+                                        "peer stores of rows and outputs")
+    return rec
+
+
+def ep_self_check(rank: int, layer, x, w_router, n_tokens: int = 4) -> dict:
+    """Correctness evidence for the expert-parallel layer inside the bench run, without the CPU checker: the first tokens of
+    rank 0 are evaluated expert by expert through the dense decode linear (berth_exl3_linear on weights regenerated from the
+    same seeds: only the selected experts and the shared one), combined in fp64 on the host with the layer's routing weights,
+    and compared with the layer's output.  The dense linear itself is compared with the checker by the test suite."""
+    import torch
+    from berth_b200 import kernels, synth
+    from berth_b200.kernels import Codebook, OutDtype
+    H, I, E, K = MOE["hidden"], MOE["inter"], MOE["n_experts"], MOE["top_k"]
+    dev = x.device
+    out, idx, tw = layer.forward(x)
+    torch.cuda.synchronize()
+    if rank != 0 or x.shape[0] == 0:
+        return {}
+    n = min(n_tokens, x.shape[0])
+    idx_h, tw_h, out_h = idx[:n].cpu().numpy(), tw[:n].cpu().numpy().astype(np.float64), out[:n].cpu().numpy().astype(np.float64)
+    to = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).to(dev)
+    def lin(xrow, lw, k, nn):
+        c = torch.empty((1, nn), dtype=torch.float16, device=dev)
+        ah = torch.empty((1, k), dtype=torch.float16, device=dev)
+        kernels.exl3_linear(xrow, to(lw["trellis"]), c, to(lw["suh"]), ah, to(lw["svh"]), 1, k, nn, BITS, Codebook(CB), OutDtype.F16)
+        return c
+    def routed(proj, e, k, nn):     # the weights bench_moe gives expert e
+        return {"trellis": synth.trellis(1234, f"c3.experts.{proj}.{e}.trellis", k, nn, BITS),
+                "suh": synth.sign_scale(1234, f"c3.experts.{proj}.{e}.suh", k),
+                "svh": synth.sign_scale(1234, f"c3.experts.{proj}.{e}.svh", nn, 1.0 / np.sqrt(k))}
+    def shared(proj, k, nn):
+        return synth.linear_weights(1234, f"c3.shared_expert.{proj}", k, nn, BITS, fan_in_gain=True)
+    def mlp(xrow, get):
+        g, u = lin(xrow, get("gate_proj", H, I), H, I), lin(xrow, get("up_proj", H, I), H, I)
+        a = torch.empty_like(g)
+        kernels.ops.silu_mul(g, u, a, I, 0.0)
+        return lin(a, get("down_proj", I, H), I, H).double().cpu().numpy()[0]
+    worst = 0.0
+    for t in range(n):
+        xrow = x[t:t + 1].contiguous()
+        y = np.zeros(H)
+        for s_ in range(K):
+            e = int(idx_h[t, s_])
+            y += tw_h[t, s_] * mlp(xrow, lambda proj, k, nn: routed(proj, e, k, nn))
+        y += mlp(xrow, shared)
+        worst = max(worst, float(np.abs(out_h[t] - y).max() / np.sqrt((y ** 2).mean())))
+    return {"tokens_checked": n, "experts_per_token": K, "shared_expert": True, "max_abs_diff_over_row_rms": worst,
+            "against": "the same tokens through the dense decode linear, expert by expert, combined in fp64 on the host"}
 
 
 # ------------------------------------------------------------------ CPU arm
@@ -556,8 +733,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill (configuration 2) and MoE (configuration 3) measurements")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "moe", "lm_head"],
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "moe", "lm_head", "c4"],
                     help="run one of the extra measurements alone and print its record (for profiling; not the contract line)")
+    ap.add_argument("--c4-layers", type=int, default=40, help="layers of the configuration-4 stack (0 = skip it)")
     ap.add_argument("--moe-tokens", type=int, nargs="*", default=[1, 64, 1024], help="token counts of the MoE measurement")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -583,6 +761,8 @@ def main() -> None:
             rec = bench_prefill(rank, reps=max(1, min(args.steps, 5)))
         elif args.only == "lm_head":
             rec = bench_lm_head(rank, reps=max(1, min(args.steps, 20)))
+        elif args.only == "c4":
+            rec = bench_c4(rank, world, layers=max(1, args.c4_layers))
         else:
             rec = bench_moe(rank, world, steps=args.steps, tokens=tuple(args.moe_tokens))
         if rank == 0:
@@ -643,6 +823,7 @@ def main() -> None:
     prefill = bench_prefill(rank) if (rank == 0 and not args.no_extras) else None
     lm_head = bench_lm_head(rank) if (rank == 0 and not args.no_extras) else None
     moe_res = None if args.no_extras else bench_moe(rank, world)
+    c4 = None if (args.no_extras or args.c4_layers < 1) else bench_c4(rank, world, layers=args.c4_layers)
 
     if world > 1:
         t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
@@ -676,7 +857,7 @@ def main() -> None:
             "clocks": clocks,
             "rows": rows_extra, "c0": c0,
             "prefill": prefill, "lm_head": lm_head,
-            "moe": moe_res,
+            "moe": moe_res, "c4": c4,
         }
         if not args.no_cpu_baseline and world == 1:
             gbs, dt, threads = cpu_pass(args.m, 2)

@@ -449,6 +449,8 @@ class P2pMoeLayer:
         self.exp_ws = torch.empty(l.berth_moe_p2p_experts_workspace_bytes(max_rows, self.n_local, H, d["inter"]), dtype=torch.uint8, device=dev)
         self.ret_rows = self._ret.view(torch.float16).view(-1, H)
         self.last_stats = {}
+        self.profile = False      # True: forward() records CUDA events between its phases (see phase_ms)
+        self._ev = None
 
     def forward(self, x: torch.Tensor):
         """x fp16 [T_local][hidden] -> (out fp32 [T_local][hidden], topk_idx, topk_w).  Asynchronous on the
@@ -459,6 +461,9 @@ class P2pMoeLayer:
             raise Error(f"P2pMoeLayer: {T} tokens exceed max_tokens = {self.max_tokens}")
         dev, k = x.device, self.k
         self.epoch += 1
+        if self.profile:
+            self._ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            self._ev[0].record()
         idx = torch.empty((T, k), dtype=torch.int32, device=dev)
         w = torch.empty((T, k), dtype=torch.float32, device=dev)
         inv = torch.empty(max(T * k, 1), dtype=torch.int32, device=dev)
@@ -468,6 +473,8 @@ class P2pMoeLayer:
         st._check(l.berth_moe_p2p_send(p(x), T, kp["w_router"].data_ptr(), None if bias is None else bias.data_ptr(), H, self.E, k,
                                        p(idx), p(w), inv.data_ptr(), self.rank, self.world, self.epoch, self.cnt_ptrs, self.flag_ptrs,
                                        self.recv_ptrs, self.max_rows, self.send_ws.data_ptr(), self.send_ws.numel(), _cur_stream(dev)))
+        if self.profile:
+            self._ev[1].record()
         stacked = st.shared_is_stacked() and T > 0
         ysh = torch.empty((T, H), dtype=torch.float16, device=dev) if stacked else None
         # rows per local expert to size the problems for: twice the mean if every rank holds as many tokens as this one
@@ -476,9 +483,22 @@ class P2pMoeLayer:
                                           self.epoch, self.E, k, T, self.cnt_ptrs, self.flag_ptrs, self.recv_ptrs, self.ret_ptrs,
                                           self.max_rows, max(self.max_send, 1), hint, self.send_ws.data_ptr(), self.exp_ws.data_ptr(),
                                           self.exp_ws.numel(), _cur_stream(dev)))
+        if self.profile:
+            self._ev[2].record()
         if T == 0:
+            if self.profile:
+                self._ev[3].record()
             return torch.empty((0, H), dtype=torch.float32, device=dev), idx, w
         if ysh is None and getattr(st, "shared", None) is not None:
             ysh = st.shared_expert(x)
         out = st.combine(self.ret_rows[: T * k], inv[: T * k], w, ysh)
+        if self.profile:
+            self._ev[3].record()
         return out, idx, w
+
+    def phase_ms(self) -> dict:
+        """After a forward() with ``profile`` set and a synchronize: milliseconds of its three phases -- send (route,
+        top-k, sort, publish counts, barrier, peer stores of the rows, barrier), experts (problem table, the three grouped
+        projections, peer stores of the outputs, barrier) and combine."""
+        e = self._ev
+        return {"send": e[0].elapsed_time(e[1]), "experts": e[1].elapsed_time(e[2]), "combine": e[2].elapsed_time(e[3])}
