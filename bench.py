@@ -44,7 +44,7 @@ METRIC = "exl3_gemv_eff_hbm_gbs"
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode launch over the stacked gate and up projections
 # (2 x 5120x17408, 4 bpw, one row) from an ncu capture of this file's own step; valid for one row only.
-NCU_TRAFFIC_GATE_UP_BYTES = None
+NCU_TRAFFIC_GATE_UP_BYTES = 92_397_312   # 89.35 MB read + 3.05 MB written
 
 
 def linear_bytes(k: int, n: int, m: int, fp32: int, bits: int = BITS) -> int:
@@ -247,6 +247,24 @@ def bench_rows(base: "DecodeStack", rank: int, m: int, steps: int) -> dict:
             "roofline": {"bound": "hbm", "achieved": k_bytes / (k_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": k_bytes / (k_ms * 1e-3) / 1e9 / peak, "traffic": None, "kernel": name,
                          "launch": f"{what} m={m}: {k_bytes} algorithmic bytes in {k_ms * 1e3:.2f} us", "peak_kind": f"of {kind}"}}
+
+
+def bench_decode_rate() -> dict:
+    """Bare decode rate of an SM (berth_exl3_decode_rate): weights per clock per SM of the decode kernels' inner loops on
+    tiles resident in shared memory, no global-memory traffic, per codebook and path at 4 bpw (and 3, 5, 6 bpw for MUL1),
+    beside the rate the HBM roofline asks for at the clock seen during the run."""
+    from berth_b200 import kernels
+    from berth_b200.kernels import Codebook
+    peak, kind = peaks()
+    rec = {"workload": "bare_decode_rate", "warps": 16, "iters": 4096, "rates": []}
+    paths = {0: "fp16 tensor path (mma.sync m16n8k16)", 1: "integer path, mma.sync m16n8k32", 2: "integer path, tcgen05.st into tensor memory"}
+    for bits, cb, path in [(4, 0, 0), (4, 1, 0), (4, 2, 0), (4, 2, 1), (4, 2, 2), (3, 2, 0), (3, 2, 2), (5, 2, 0), (5, 2, 2), (6, 2, 0), (6, 2, 2)]:
+        w, mhz = kernels.decode_rate(bits, Codebook(cb), path, 16, 4096)
+        need = peak * 1e9 * 8 / bits / (148 * mhz * 1e6)      # weights per clock per SM at the measured HBM peak
+        rec["rates"].append({"bits": bits, "codebook": ["3inst", "mcg", "mul1"][cb], "path": paths[path], "weights_per_clk_per_sm": round(w, 2),
+                             "sm_mhz": round(mhz), "hbm_roofline_needs": round(need, 1), "ceiling_frac_of_hbm_peak": round(w / need, 3)})
+    rec["peak_kind"] = f"of {kind}"
+    return rec
 
 
 def bench_c0(rank: int, reps: int = 12) -> dict:
@@ -733,7 +751,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill (configuration 2) and MoE (configuration 3) measurements")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "moe", "lm_head", "c4"],
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "moe", "lm_head", "c4", "decode_rate"],
                     help="run one of the extra measurements alone and print its record (for profiling; not the contract line)")
     ap.add_argument("--c4-layers", type=int, default=40, help="layers of the configuration-4 stack (0 = skip it)")
     ap.add_argument("--moe-tokens", type=int, nargs="*", default=[1, 64, 1024], help="token counts of the MoE measurement")
@@ -763,6 +781,8 @@ def main() -> None:
             rec = bench_lm_head(rank, reps=max(1, min(args.steps, 20)))
         elif args.only == "c4":
             rec = bench_c4(rank, world, layers=max(1, args.c4_layers))
+        elif args.only == "decode_rate":
+            rec = bench_decode_rate() if rank == 0 else None
         else:
             rec = bench_moe(rank, world, steps=args.steps, tokens=tuple(args.moe_tokens))
         if rank == 0:
@@ -820,6 +840,7 @@ def main() -> None:
     extras = rank == 0 and not args.no_extras
     rows_extra = [bench_rows(stack, rank, mm, max(20, args.steps // 4)) for mm in (8, 32) if mm != args.m] if extras else None
     c0 = bench_c0(rank) if extras else None
+    decode_rate = bench_decode_rate() if extras else None
     prefill = bench_prefill(rank) if (rank == 0 and not args.no_extras) else None
     lm_head = bench_lm_head(rank) if (rank == 0 and not args.no_extras) else None
     moe_res = None if args.no_extras else bench_moe(rank, world)
@@ -855,7 +876,7 @@ def main() -> None:
                     "d2h_bytes_per_step": stack.d2h_bytes, "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": stack.launches_per_step * args.steps,
             "clocks": clocks,
-            "rows": rows_extra, "c0": c0,
+            "rows": rows_extra, "c0": c0, "decode_rate": decode_rate,
             "prefill": prefill, "lm_head": lm_head,
             "moe": moe_res, "c4": c4,
         }

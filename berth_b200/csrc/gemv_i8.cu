@@ -387,7 +387,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
             }
         };
         for (int i = 0; i < nunits; ++i) {
-            mbar_wait(full0 + 8 * s, phase, p.status, kStFullTimeout);
+            mbar_wait(full0 + 8 * s, phase, p.status, kStFullTimeout);   // (tight polling: a parked wait wakes up too late here)
             const uint32_t* stage = reinterpret_cast<const uint32_t*>(ring + s * STAGE_BYTES) + word0;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
