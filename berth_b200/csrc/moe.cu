@@ -647,26 +647,53 @@ __global__ void __launch_bounds__(1024) k_ep_publish_tables(const int* __restric
 }
 
 // Row pos of this rank's sorted send order -> the receive buffer of the rank that owns its expert.
+// One row of H halves from src to dst, whole warp: the 16-byte pieces of a pass are loaded together before any is
+// stored, so that a row's loads are in flight at once (dst may be peer memory).
+__device__ __forceinline__ void copy_row_warp(const __half* __restrict__ src, __half* __restrict__ dst, int H, int lane)
+{
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    const int n = H / 8;
+    for (int base = 0; base < n; base += 256) {
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int idx = base + i * 32 + lane;
+            if (idx < n) v[i] = s4[idx];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int idx = base + i * 32 + lane;
+            if (idx < n) d4[idx] = v[i];
+        }
+    }
+}
+
+// Row pos of this rank's sorted send order -> the receive buffer of the rank that owns its expert.  The position tables
+// sit in shared memory (a row's expert is found by bisection there, not through dependent global loads) and every warp
+// moves a row of its own, eight rows in flight per block.
 __global__ void __launch_bounds__(256) k_ep_dispatch(const __half* __restrict__ x, const int32_t* __restrict__ perm,
                                                      const int* __restrict__ offsets_send, const int* __restrict__ dst0, PeerPtrs recv_rows,
                                                      int E, int n_local, int top_k, int H, int n_send, int max_rows, unsigned* status)
 {
-    for (int pos = blockIdx.x; pos < n_send; pos += gridDim.x) {
+    __shared__ int s_off[1025], s_dst[1024];   // E <= 1024
+    for (int i = threadIdx.x; i < E; i += 256) { s_off[i] = offsets_send[i]; s_dst[i] = dst0[i]; }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int pos = blockIdx.x * 8 + warp; pos < n_send; pos += gridDim.x * 8) {
         int lo = 0, hi = E - 1;   // the last expert whose first position is <= pos and that has rows there
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
-            if (__ldg(offsets_send + mid) <= pos) lo = mid; else hi = mid - 1;
+            if (s_off[mid] <= pos) lo = mid; else hi = mid - 1;
         }
         const int e = lo;
-        const int dst = __ldg(dst0 + e) + pos - __ldg(offsets_send + e);
+        const int dst = s_dst[e] + pos - s_off[e];
         if (dst < 0 || dst >= max_rows) {
-            if (threadIdx.x == 0) atomicOr(status, kStEpOverflow);
+            if (lane == 0) atomicOr(status, kStEpOverflow);
             continue;
         }
         const int tok = min(max(perm[pos] / top_k, 0), n_send / top_k - 1);   // (n_send = tokens x top_k)
-        const uint4* src = reinterpret_cast<const uint4*>(x + size_t(tok) * H);
-        uint4* out = reinterpret_cast<uint4*>(static_cast<__half*>(recv_rows.p[e / n_local]) + size_t(dst) * H);
-        for (int i = threadIdx.x; i < H / 8; i += 256) out[i] = src[i];
+        copy_row_warp(x + size_t(tok) * H, static_cast<__half*>(recv_rows.p[e / n_local]) + size_t(dst) * H, H, lane);
     }
     __threadfence_system();
 }
@@ -699,34 +726,41 @@ __global__ void __launch_bounds__(256) k_rows_from_offset(const __half* __restri
 }
 
 // Expert output row p (rows sorted by local expert, inside an expert source by source) -> the source's return
-// buffer at the position the row had in the source's sorted send order.
+// buffer at the position the row had in the source's sorted send order.  Tables in shared memory, a row per warp.
 __global__ void __launch_bounds__(256) k_ep_return(const __half* __restrict__ yr, const int* __restrict__ offsets, PeerPtrs cnt_all,
                                                    const int* __restrict__ send_off, PeerPtrs ret_rows, int rank, int W, int E, int n_local,
                                                    int H, int max_rows, int max_send, unsigned* status)
 {
-    const int R = min(max(__ldg(offsets + n_local), 0), max_rows);
+    __shared__ int s_off[1025], s_cnt[1024], s_so[1024];   // W * n_local = E <= 1024
     const int* cnt = static_cast<const int*>(cnt_all.p[rank]);
-    for (int p = blockIdx.x; p < R; p += gridDim.x) {
+    for (int i = threadIdx.x; i <= n_local; i += 256) s_off[i] = offsets[i];
+    for (int i = threadIdx.x; i < W * n_local; i += 256) {
+        const int sr = i / n_local, j = i - sr * n_local;
+        s_cnt[i] = cnt[sr * E + rank * n_local + j];
+        s_so[i] = send_off[i];
+    }
+    __syncthreads();
+    const int R = min(max(s_off[n_local], 0), max_rows);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int p = blockIdx.x * 8 + warp; p < R; p += gridDim.x * 8) {
         int lo = 0, hi = n_local - 1;
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
-            if (__ldg(offsets + mid) <= p) lo = mid; else hi = mid - 1;
+            if (s_off[mid] <= p) lo = mid; else hi = mid - 1;
         }
-        const int j = lo, e = rank * n_local + j;
-        int q = p - __ldg(offsets + j), s = 0;
-        for (; s < W - 1; ++s) {
-            const int c = cnt[s * E + e];
+        const int j = lo;
+        int q = p - s_off[j], sr = 0;
+        for (; sr < W - 1; ++sr) {
+            const int c = s_cnt[sr * n_local + j];
             if (q < c) break;
             q -= c;
         }
-        const int srcpos = __ldg(send_off + s * n_local + j) + q;
+        const int srcpos = s_so[sr * n_local + j] + q;
         if (srcpos < 0 || srcpos >= max_send) {
-            if (threadIdx.x == 0) atomicOr(status, kStEpOverflow);
+            if (lane == 0) atomicOr(status, kStEpOverflow);
             continue;
         }
-        const uint4* src = reinterpret_cast<const uint4*>(yr + size_t(p) * H);
-        uint4* out = reinterpret_cast<uint4*>(static_cast<__half*>(ret_rows.p[s]) + size_t(srcpos) * H);
-        for (int i = threadIdx.x; i < H / 8; i += 256) out[i] = src[i];
+        copy_row_warp(yr + size_t(p) * H, static_cast<__half*>(ret_rows.p[sr]) + size_t(srcpos) * H, H, lane);
     }
     __threadfence_system();
 }
@@ -1280,7 +1314,7 @@ extern "C" int berth_moe_p2p_send(const void* x, int T, const void* w_router, co
         k_ep_publish_tables<<<1, 1024, 0, cs>>>(s.counts, pc, pf, rank, world, n_experts, n_local, epoch, s.dst0, s.counts_local, s.send_off, status);
         cuda_ok(cudaGetLastError(), "k_ep_publish_tables launch");
         if (R > 0) {
-            k_ep_dispatch<<<std::min(R, 148 * 8), 256, 0, cs>>>((const __half*) x, s.perm, s.offsets, s.dst0, pr, n_experts, n_local, top_k, hidden, R,
+            k_ep_dispatch<<<std::min((R + 7) / 8, 148 * 4), 256, 0, cs>>>((const __half*) x, s.perm, s.offsets, s.dst0, pr, n_experts, n_local, top_k, hidden, R,
                                                                max_rows, status);
             cuda_ok(cudaGetLastError(), "k_ep_dispatch launch");
         }
@@ -1342,7 +1376,7 @@ extern "C" int berth_moe_p2p_experts(const berth_moe_weights* w, const void* x_l
         }
         st.launch = experts(w, w->gate_trellis, w->up_trellis, w->down_trellis, w->gate_suh, w->gate_svh, w->up_suh, w->up_svh,
                             w->down_suh, w->down_svh, NM, xr, yr, 0, max_rows, plan, es, sc, info.sms, cs, es.offsets + NM, in_place);
-        k_ep_return<<<148 * 8, 256, 0, cs>>>(yr, es.offsets, pc, sw.send_off, pt, rank, world, n_experts_total, NL, H, max_rows, max_send, sc.status);
+        k_ep_return<<<148 * 4, 256, 0, cs>>>(yr, es.offsets, pc, sw.send_off, pt, rank, world, n_experts_total, NL, H, max_rows, max_send, sc.status);
         cuda_ok(cudaGetLastError(), "k_ep_return launch");
         k_ep_barrier<<<1, 32, 0, cs>>>(pf, 2, rank, world, epoch, sc.status);
         cuda_ok(cudaGetLastError(), "k_ep_barrier launch");

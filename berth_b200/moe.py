@@ -202,6 +202,8 @@ class GpuStages:
     def experts(self, xr):
         R = xr.shape[0]
         yr = torch.empty_like(xr)
+        if R == 0:     # a rank that received no rows (few tokens, many ranks): nothing to launch
+            return yr
         self._check(_lib.lib().berth_moe_experts(C.byref(self.layer.c), xr.data_ptr(), yr.data_ptr(), R, self.ews_loc.data_ptr(),
                                                  self.ews_loc.numel(), self.max_rows, self.rows_hint(R, self.d["n_experts"]), _cur_stream(self.device)))
         return yr
