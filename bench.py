@@ -264,6 +264,9 @@ def bench_decode_rate() -> dict:
         rec["rates"].append({"bits": bits, "codebook": ["3inst", "mcg", "mul1"][cb], "path": paths[path], "weights_per_clk_per_sm": round(w, 2),
                              "sm_mhz": round(mhz), "hbm_roofline_needs": round(need, 1), "ceiling_frac_of_hbm_peak": round(w / need, 3)})
     rec["peak_kind"] = f"of {kind}"
+    names = ["2 mma.sync m16n8k16", "2 mma.sync m16n8k16 + 8 lop3", "2 mma.sync m16n8k16 + 8 imad", "8 lop3 + 8 imad",
+             "2 mma.sync m16n8k32 (u8 x s8)", "2 mma.sync m16n8k32 + 8 lop3"]
+    rec["pipe_probe_clk_per_bundle_per_scheduler"] = {n: round(kernels.pipe_probe(i), 2) for i, n in enumerate(names)}
     return rec
 
 

@@ -52,6 +52,7 @@ SIGNATURES = {
     "berth_device_sms": (_i, [_i]),
     "berth_device_status": (_i, [_i]),
     "berth_exl3_decode_rate": (_i, [_i] * 5 + [C.POINTER(C.c_double)] * 2),
+    "berth_exl3_pipe_probe": (_i, [_i, _i, C.POINTER(C.c_double)]),
     "berth_exl3_gemm_tune_key": (_u64, [_i] * 9),
     "berth_exl3_smoke_int8": (_i, [_i]),
     "berth_exl3_smoke_gemm": (_i, []),

@@ -129,6 +129,53 @@ __global__ void __launch_bounds__(1024, 1) k_decode_rate(uint32_t seed, int iter
     }
 }
 
+// Pipe probe: which instructions of the decode loop share an issue pipe.  Every warp runs `iters` iterations of a fixed
+// bundle on independent registers: KIND 0 = two mma.sync.m16n8k16; 1 = the same plus eight lop3; 2 = the same plus eight
+// 32-bit multiplies; 3 = eight lop3 plus eight multiplies, no MMA; 4 = two mma.sync.m16n8k32 (u8 x s8); 5 = those plus
+// eight lop3.  Returns cycles per iteration and scheduler (the block has 16 warps, four per scheduler).
+template <int KIND>
+__global__ void __launch_bounds__(512, 1) k_pipe_probe(uint32_t seed, int iters, unsigned long long* cycles, uint32_t* sink)
+{
+    uint32_t v[8], w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { v[i] = seed + threadIdx.x * 7 + i; w[i] = seed * 3 + threadIdx.x * 5 + i; }
+    float f[2][4] = {};
+    int d[2][4] = {};
+    const uint32_t c1 = seed | 1, c2 = seed ^ 0x5555;
+    __syncthreads();
+    const unsigned long long t0 = clock64();
+    for (int it = 0; it < iters; ++it) {
+        if constexpr (KIND == 0 || KIND == 1 || KIND == 2) {
+            uint32_t a0[4] = {v[0], v[1], v[2], v[3]}, a1[4] = {w[0], w[1], w[2], w[3]};
+            dq::mma_16816(f[0], a0, c1, c2);
+            dq::mma_16816(f[1], a1, c1, c2);
+        }
+        if constexpr (KIND == 4 || KIND == 5) {
+            dq::mma_16832_u8s8(d[0], v[0], v[1], v[2], v[3], c1, c2);
+            dq::mma_16832_u8s8(d[1], w[0], w[1], w[2], w[3], c1, c2);
+        }
+        if constexpr (KIND == 1 || KIND == 3 || KIND == 5) {
+#pragma unroll
+            for (int i = 4; i < 8; ++i) { v[i] = dq::lop3_mask_xor(v[i]); w[i] = dq::lop3_mask_xor(w[i] + 1); }
+        }
+        if constexpr (KIND == 2 || KIND == 3) {
+#pragma unroll
+            for (int i = 4; i < 8; ++i) {
+                asm volatile("mad.lo.u32 %0, %0, 0x83DCD12D, 0;" : "+r"(v[KIND == 3 ? i - 4 : i]));   // (KIND 3: registers the lop3s do not touch)
+                asm volatile("mad.lo.u32 %0, %0, 0x83DCD12D, 0;" : "+r"(w[KIND == 3 ? i - 4 : i]));
+            }
+        }
+    }
+    const unsigned long long t1 = clock64();
+    uint32_t acc = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc ^= v[i] ^ w[i];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc ^= __float_as_uint(f[0][i] + f[1][i]) ^ uint32_t(d[0][i] ^ d[1][i]);
+    if (threadIdx.x == 0) cycles[blockIdx.x] = t1 - t0;
+    if (acc == 0x12345678u) sink[0] = acc;
+}
+
 template <int BITS, int CB, int PATH>
 void launch_rate(int grid, int warps, int iters, unsigned long long* cyc, unsigned long long* ns, float* sink, cudaStream_t st)
 {
@@ -201,5 +248,42 @@ extern "C" int berth_exl3_decode_rate(int k_bits, int codebook, int path, int wa
             throw;
         }
         cudaFree(cyc); cudaFree(ns); cudaFree(sink);
+    });
+}
+
+extern "C" int berth_exl3_pipe_probe(int kind, int iters, double* clk_per_iteration_per_scheduler)
+{
+    using namespace berth;
+    return guarded(exl3_state(), [&] {
+        if (!clk_per_iteration_per_scheduler) throw std::runtime_error("pipe probe: null result pointer");
+        if (kind < 0 || kind > 5 || iters < 1 || iters > (1 << 20)) throw std::runtime_error("pipe probe: kind 0..5, iters 1..2^20");
+        const int sms = device_info(current_device()).sms;
+        unsigned long long* cyc = nullptr;
+        uint32_t* sink = nullptr;
+        cuda_ok(cudaMalloc(&cyc, size_t(sms) * 8), "pipe probe alloc");
+        cuda_ok(cudaMalloc(&sink, 4), "pipe probe alloc");
+        try {
+            for (int rep = 0; rep < 2; ++rep) {
+                switch (kind) {
+                    case 0: k_pipe_probe<0><<<sms, 512>>>(12345u, iters, cyc, sink); break;
+                    case 1: k_pipe_probe<1><<<sms, 512>>>(12345u, iters, cyc, sink); break;
+                    case 2: k_pipe_probe<2><<<sms, 512>>>(12345u, iters, cyc, sink); break;
+                    case 3: k_pipe_probe<3><<<sms, 512>>>(12345u, iters, cyc, sink); break;
+                    case 4: k_pipe_probe<4><<<sms, 512>>>(12345u, iters, cyc, sink); break;
+                    default: k_pipe_probe<5><<<sms, 512>>>(12345u, iters, cyc, sink); break;
+                }
+                cuda_ok(cudaGetLastError(), "k_pipe_probe launch");
+            }
+            cuda_ok(cudaDeviceSynchronize(), "pipe probe sync");
+            std::vector<unsigned long long> h(sms);
+            cuda_ok(cudaMemcpy(h.data(), cyc, size_t(sms) * 8, cudaMemcpyDeviceToHost), "pipe probe read");
+            double c = 0;
+            for (int i = 0; i < sms; ++i) c += double(h[i]);
+            *clk_per_iteration_per_scheduler = c / sms / iters / 4.0;   // four warps per scheduler run the bundle one after the other
+        } catch (...) {
+            cudaFree(cyc); cudaFree(sink);
+            throw;
+        }
+        cudaFree(cyc); cudaFree(sink);
     });
 }

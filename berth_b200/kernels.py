@@ -146,6 +146,16 @@ def decode_rate(k_bits: int, codebook: Codebook, path: int, warps: int = 16, ite
     return w.value, mhz.value
 
 
+def pipe_probe(kind: int, iters: int = 4096) -> float:
+    """Cycles one bundle of independent instructions costs a warp scheduler (diagnostic; kinds in include/berth_b200.h)."""
+    import ctypes as C
+    v = C.c_double()
+    rc = _lib.lib().berth_exl3_pipe_probe(kind, iters, C.byref(v))
+    if rc != 0:
+        raise Error(last_error() or f"pipe probe failed ({rc})")
+    return v.value
+
+
 def gemm_tune_key(size_m, size_k, size_n, k_bits, out_fp32, device, cc, sms, cb) -> int:
     return _lib.lib().berth_exl3_gemm_tune_key(size_m, size_k, size_n, k_bits, out_fp32, device, cc, sms, cb)
 

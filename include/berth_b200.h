@@ -91,10 +91,16 @@ int berth_device_status(int device);
  * decode GEMV (tile words in shared memory -> window extraction -> codebook arithmetic -> MMA) with
  * no global-memory traffic on every SM with `warps` warps for `iters` iterations of eight tiles per
  * warp, and returns the decoded weights per clock per SM (mean over the SMs) and the SM clock seen
- * during the run.  path 0 = fp16 tensor path (every codebook), 1 = MUL1 on the integer tensor path.
+ * during the run.  path 0 = fp16 tensor path (every codebook); MUL1 on the integer path: 1 = with the warp-level
+ * mma.sync.m16n8k32, 2 = with the products stored to tensor memory as the decode kernel does (at most 16 warps).
  * k_bits 3..6.  Allocates three small buffers, synchronises the device, frees them. */
 int berth_exl3_decode_rate(int k_bits, int codebook, int path, int warps, int iters,
                            double* weights_per_clk_sm, double* sm_mhz);
+/* Diagnostic, no counterpart in berth: which instructions of the decode loop share an issue pipe.  16 warps per SM run a
+ * bundle of independent instructions `iters` times; the result is the cycles one bundle costs a warp scheduler.
+ * kind 0 = two mma.sync.m16n8k16 (fp16); 1 = those plus eight lop3; 2 = those plus eight 32-bit multiplies; 3 = eight
+ * lop3 plus eight multiplies; 4 = two mma.sync.m16n8k32 (u8 x s8); 5 = those plus eight lop3. */
+int berth_exl3_pipe_probe(int kind, int iters, double* clk_per_iteration_per_scheduler);
 
 /* FNV-1a shape key of crates/berth-kernels/csrc/linear.cu:65-104,345-358.  Kept because berth's
  * tests pin its value; this library never tunes at run time.  No CUDA call. */
