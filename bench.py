@@ -170,11 +170,13 @@ class DecodeStack:
             lin["qkv"] = SlicedMultiLinear(self.gpu, [lin["q"], lin["k"], lin["v"]], OutDtype.F16, max_rows=m,
                                            outputs=[self.q, self.k, self.v])
             self.layers.append((mlp, lin))
-        # up to 4 rows: gate+up (one stacked launch), down, o: decode kernel + k_gemv_finish each, no rotation kernel;
-        # q/k/v: k_rotate_in + k_exl3_gemv + k_gemv_finish for the three; one k_silu_mul = 10 launches.
-        # 5..8 rows: + one rotation kernel per matrix of the stacked launch, and one each for down and o = 14.
+        # one row: gate+up (one stacked integer-path launch, rotation and finishing inside it), down and o (the same kernel,
+        # one launch each), q/k/v (k_rotate_in + k_exl3_gemv + k_gemv_finish for the three), k_silu_mul = 7 launches.
+        # two rows: the stacked launch, down and o on the fp16-path kernel (k_exl3_gemv + k_gemv_finish each), q/k/v, silu = 9.
+        # 3..4 rows: k_rotate_in_i8 per stacked matrix + the stacked launch, down and o with k_rotate_in + k_exl3_gemv +
+        # k_gemv_finish each, q/k/v, silu = 13.
         # above: gate, up, down, o with k_rotate_in + k_exl3_gemv + k_gemv_finish each, q/k/v, silu = 16.
-        self.launches_per_step = 10 if m <= 4 else (14 if m <= 8 else 16)
+        self.launches_per_step = 7 if m == 1 else (9 if m == 2 else (13 if m <= 4 else 16))
 
     def step(self, i: int) -> None:
         from berth_b200.kernels import OutDtype
@@ -193,12 +195,12 @@ class DecodeStack:
 
     def time_dominant_kernel(self, reps: int):
         """(average ms, algorithmic bytes, description) of the step's dominant launch, run back to back over the
-        LAYERS distinct layers (357 MB of gate and up weights > L2) between two CUDA events: up to eight rows the
+        LAYERS distinct layers (357 MB of gate and up weights > L2) between two CUDA events: up to four rows the
         decode launch over the stacked gate and up projections, above the gate linear alone."""
         torch = self.torch
         from berth_b200 import kernels
         from berth_b200.kernels import OutDtype
-        stacked = self.layers[0][0].gate_up is not None and self.m <= 8
+        stacked = self.layers[0][0].gate_up is not None and self.m <= 4
         if stacked:
             calls = [(l[0].gate_up, l[0].gate_up_out) for l in self.layers]
             nbytes = 2 * linear_bytes(HIDDEN, INTER, self.m, 0) - 2 * self.m * HIDDEN   # the rows are read once

@@ -68,7 +68,8 @@ struct GeoI8 {
     static constexpr int W_BYTES = 8 * ROW_BYTES;
     static constexpr int CHUNK_BYTES = NB * 256;               // limbs of 8 weights-k: NB groups of 8 rows x 32 bytes
     static constexpr int L_BYTES = 16 * CHUNK_BYTES;           // limbs of one unit: 16 MMA k-steps
-    static constexpr int B_BYTES = L_BYTES + 128;              // ... followed by the unit's block scales (one fp32 per row)
+    static constexpr int B_BYTES = L_BYTES + 128;              // ... followed by the unit's block scales and block sums (16 fp32 each)
+    static_assert(NB <= 4, "the 128-byte tail of a limb record holds 16 rows");
     static constexpr int STAGE_BYTES = FUSED ? W_BYTES : W_BYTES + B_BYTES;
     static constexpr int TOK = 4 * NB;
     static constexpr int NCOL = NB <= 2 ? 16 : 8 * NB;         // N of the MMA (16 is the least for M = 128)
@@ -499,14 +500,14 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
                         bs[t] = t < rows ? fscales[ui * 8 + 4 + t] : 0.f;
                     }
                 } else {
-                    // the unit's block scales travel with its limb tile; its block sums were left in global memory
-                    const float* bsp = p.blocksum + size_t(pv.act) * slab_rows * kblocks + sg.kb_begin + j;
-#pragma unroll
-                    for (int t = 0; t < TOK; ++t) bs[t] = t < rows ? __ldg(bsp + size_t(t) * kblocks) : 0.f;
+                    // the unit's block scales and block sums travel with its limb tile
                     mbar_wait_suspended(full0 + 8 * rs, rphase, p.status, kStFullTimeout);
                     const float* scp = reinterpret_cast<const float*>(ring + rs * STAGE_BYTES + W_BYTES + G_::L_BYTES);
 #pragma unroll
-                    for (int t = 0; t < TOK; ++t) sc[t] = t < rows ? scp[t] : 0.f;
+                    for (int t = 0; t < TOK; ++t) {
+                        sc[t] = t < rows ? scp[t] : 0.f;
+                        bs[t] = t < rows ? scp[16 + t] : 0.f;
+                    }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(empty0 + 8 * rs);
                     if (++rs == S) { rs = 0; rphase ^= 1; }
@@ -617,7 +618,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
 // bytes of a 32-bit word (the four u8 k-slots of a weight's product) at its place in the limb tile of the
 // block: [MMA k-step 16][row group nb][core matrix 2][limb row 8][16 bytes], limb row = 2 * (row % 4) + (0 high,
 // 1 low); k-step c of a k-tile row holds, in this order, the inputs 2c (c < 4) and 2(c-4)+1 of its eight.
-// The block's scales (one fp32 per row) follow its limbs; blocksum[row][block] = scale * sum v.  Rows of a group that do not exist are
+// The block's scales (one fp32 per row, 16 slots) and block sums (scale * sum v, 16 slots) follow its limbs; the block
+// sums also go to blocksum[row][block].  Rows of a group that do not exist are
 // not written: their accumulator columns are never read.
 __global__ void __launch_bounds__(128) k_rotate_in_i8(const __half* __restrict__ a, const __half* __restrict__ suh,
                                                       __half* __restrict__ a_had, unsigned char* __restrict__ limbs,
@@ -636,8 +638,11 @@ __global__ void __launch_bounds__(128) k_rotate_in_i8(const __half* __restrict__
         int isum;
         const float scale = quantise_block(o, lane, limbs + size_t(b) * record + size_t(row >> 2) * 256 + (2 * (row & 3)) * 16, nb * 256, 128, isum);
         if (lane == 0) {
-            reinterpret_cast<float*>(limbs + size_t(b) * record + size_t(16) * nb * 256)[row] = scale;
-            blocksum[size_t(row) * kblocks + b] = __fmul_rn(scale, __int2float_rn(isum));
+            float* tail = reinterpret_cast<float*>(limbs + size_t(b) * record + size_t(16) * nb * 256);   // 16 scales, then 16 block sums
+            const float bsum = __fmul_rn(scale, __int2float_rn(isum));
+            tail[row] = scale;
+            tail[16 + row] = bsum;
+            blocksum[size_t(row) * kblocks + b] = bsum;
         }
     }
 }

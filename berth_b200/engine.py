@@ -170,7 +170,8 @@ class StackedLinear:
     one decode launch (``kernels.exl3_linear_stack``) runs all of them on up to eight rows.  Construction moves the
     sources' tensors into the stack and re-points the sources at their slices, so no weight is held twice."""
 
-    MAX_ROWS = 8
+    MAX_ROWS = 8        # what the library's stacked launch accepts
+    BEST_ROWS = 4       # up to here it is measured faster than one launch per matrix (above, the limb tiles of the rows cost more)
 
     def __init__(self, gpu: Gpu, sources: list, max_rows: int = 1):
         first = sources[0]
@@ -225,7 +226,7 @@ class MlpLayer:
         self.hidden, self.intermediate = gate.size_k, gate.size_n
         if self.intermediate < 2 or self.intermediate % 2:
             raise Error(f"intermediate {self.intermediate} must be positive and even")
-        # gate and up as one decode launch where the library has one (MUL1, same bitrate, up to eight rows)
+        # gate and up as one decode launch where the library has one and it pays (MUL1, same bitrate, up to four rows)
         self.gate_up = None
         if gate.codebook == Codebook.Mul1 and up.codebook == Codebook.Mul1 and gate.k_bits == up.k_bits:
             self.gate_up = StackedLinear(gpu, [gate, up], max_rows)
@@ -258,7 +259,7 @@ class MlpLayer:
         if rows > self.max_rows:
             self._alloc(gpu, rows)
         n = rows * self.intermediate
-        if self.gate_up is not None and rows <= StackedLinear.MAX_ROWS:
+        if self.gate_up is not None and rows <= StackedLinear.BEST_ROWS:
             gate_out, up_out = self.gate_up_out[:n], self.gate_up_out[n:2 * n]
             self.gate_up.forward_n(gpu, rows, inp, self.gate_up_out, OutDtype.F16)
         else:

@@ -90,7 +90,7 @@ def test_mlp_layer_forward_vs_oracle(oracle, cb, rows):
         mlp.forward_n(gpu, rows, dev(x), out)
     torch.cuda.synchronize()
     assert kernels.device_status(torch.cuda.current_device()) == 0
-    if cb == 2 and rows <= StackedLinear.MAX_ROWS:
+    if cb == 2 and rows <= StackedLinear.BEST_ROWS:
         assert "stack of 2" in kernels.last_launch() or "k_exl3_gemv" in kernels.last_launch()
     g, u, act, y64 = _mlp_oracle(oracle, x, ws, H, I, bits, cb)
     got_act = mlp.activated[:rows * I].float().cpu().numpy().reshape(rows, I)
