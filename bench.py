@@ -175,7 +175,8 @@ class DecodeStack:
         # two rows: the stacked launch, down and o on the fp16-path kernel (k_exl3_gemv + k_gemv_finish each), q/k/v, silu = 9.
         # 3..4 rows: k_rotate_in_i8 per stacked matrix + the stacked launch, down and o with k_rotate_in + k_exl3_gemv +
         # k_gemv_finish each, q/k/v, silu = 13.
-        # above: gate, up, down, o with k_rotate_in + k_exl3_gemv + k_gemv_finish each, q/k/v, silu = 16.
+        # above: gate, up, down, o with three launches each (k_rotate_in + k_exl3_gemv + k_gemv_finish up to 16 rows,
+        # k_had128 + k_exl3_gemm_tc_splitk + k_sk_finish from 17), q/k/v, silu = 16.
         self.launches_per_step = 7 if m == 1 else (9 if m == 2 else (13 if m <= 4 else 16))
 
     def step(self, i: int) -> None:

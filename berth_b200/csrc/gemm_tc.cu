@@ -173,6 +173,19 @@ __device__ __forceinline__ void tc_st_frag(uint32_t taddr, const uint32_t (&w)[4
     asm volatile("tcgen05.st.sync.aligned.16x128b.x2.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
                  : "memory");
 }
+// The same without the memory clobber: tensor memory aliases no C++ object, and every hand-over of a stage goes
+// through tc_wait_st and an mbarrier operation, which do clobber; the compiler may then schedule the shared-memory
+// loads and the arithmetic of the next tiles across the store.
+__device__ __forceinline__ void tc_st_frag_free(uint32_t taddr, const uint32_t (&w)[4])
+{
+    asm volatile("tcgen05.st.sync.aligned.16x128b.x2.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]));
+}
+// Two k-tile rows of one tile column at once: 16 lanes x 16 columns.
+__device__ __forceinline__ void tc_st_frag2_free(uint32_t taddr, const uint32_t (&w0)[4], const uint32_t (&w1)[4])
+{
+    asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(w0[0]), "r"(w0[1]), "r"(w0[2]),
+                 "r"(w0[3]), "r"(w1[0]), "r"(w1[1]), "r"(w1[2]), "r"(w1[3]));
+}
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // 32 lanes x 32 consecutive fp32 columns of this warp's TMEM lane quarter.
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32])
@@ -224,11 +237,9 @@ __device__ __forceinline__ bool elect_one()
 // (svh_s: the band's 128 scales as fp32) and 16-byte stores of rows row0 .. row0+31 below row_end.
 constexpr int kXchPitch = 129;
 constexpr int kXchFloats = 32 * kXchPitch;
-__device__ __noinline__ void epilogue_pass(uint32_t tacc, float* xch, const float* svh_s, int team, int quarter, int lane, void* c,
-                                           int out_fp32, int ldc, int col0, int row0, int row_end)
+__device__ __forceinline__ void epilogue_rows(float (&v)[32], float* xch, const float* svh_s, int team, int quarter, int lane, void* c,
+                                              int out_fp32, int ldc, int col0, int row0, int row_end)
 {
-    float v[32];
-    tc_ld32(tacc, v);
     {
         float* wp = xch + 32 * quarter + ((lane - 8 * quarter) & 31);
 #pragma unroll
@@ -285,6 +296,13 @@ __device__ __noinline__ void epilogue_pass(uint32_t tacc, float* xch, const floa
         }
     }
 }
+__device__ __noinline__ void epilogue_pass(uint32_t tacc, float* xch, const float* svh_s, int team, int quarter, int lane, void* c,
+                                           int out_fp32, int ldc, int col0, int row0, int row_end)
+{
+    float v[32];
+    tc_ld32(tacc, v);
+    epilogue_rows(v, xch, svh_s, team, quarter, lane, c, out_fp32, ldc, col0, row0, row_end);
+}
 
 // One 64-deep stage of one band decoded into tensor memory by one group of four decode warps (the four groups take
 // the stages round robin, group g always into weight stage g of tensor memory): the warp takes all four k-tile rows
@@ -292,7 +310,7 @@ __device__ __noinline__ void epilogue_pass(uint32_t tacc, float* xch, const floa
 // it may access (warp index % 4 == quarter).  `wait_w` = the stage of tensor memory must first be released.
 // (Sixteen warps sharing every stage, a quarter of this work per barrier round trip, spent more instructions on the
 // hand-over than on the weights.)
-template <int BITS, int CB>
+template <int BITS, int CB, bool SPIN = false>
 __device__ __forceinline__ void decode_stage(const unsigned char* tstage, uint32_t tmem_wstage, int quarter, int lane, bool wait_w,
                                              uint32_t empty_w_bar, uint32_t empty_w_parity, unsigned* status)
 {
@@ -309,8 +327,9 @@ __device__ __forceinline__ void decode_stage(const unsigned char* tstage, uint32
             else dq::lane_states<BITS>(tile, lane, s);
             dq::decode_frag<CB>(s, w[t]);
         }
-        if (krow == 0 && wait_w) {
-            mbar_wait_parked(empty_w_bar, empty_w_parity, status, 40);   // the MMAs that read this weight stage are done
+        if (krow == 0 && wait_w) {   // the MMAs that read this weight stage are done
+            if constexpr (SPIN) mbar_wait(empty_w_bar, empty_w_parity, status);
+            else mbar_wait_parked(empty_w_bar, empty_w_parity, status, 40);
             tc_fence_after();
         }
 #pragma unroll
@@ -561,13 +580,30 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
     };
 
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------ TMA producer of the trellis stages
+        // (its own thread: the weight stream then runs as far ahead as its ring allows and never waits for a slot
+        // of the activation ring, which is shorter and is released later, by the MMAs)
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_t) : "memory");
+            int st = 0, pt = 0, cnt = 0;
+            for (int it = 0; it < my_items; ++it) {
+                int band; GemvProblem pr;
+                item_at(it, band, pr);
+                for (int ks = 0; ks < kstages; ++ks, ++cnt) {
+                    if (cnt >= ST) mbar_wait_parked(empty_t + 8 * st, pt ^ 1, p.status, 100);
+                    mbar_arrive_expect_tx(full_t + 8 * st, T_STAGE_BYTES);
+                    tma_load_3d(smem_u32(t_ring + st * T_STAGE_BYTES), &tmap_t, band * (TROW_BYTES / 8), ks * 4, pr.z, full_t + 8 * st);
+                    if (++st == ST) { st = 0; pt ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 2) {
+        // ------------------------------------------------------------ TMA producer of the activation stages
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a64) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a32) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_t) : "memory");
-            int sa = 0, pa = 0, st = 0, pt = 0, cnt = 0;
+            int sa = 0, pa = 0, cnt = 0;
             for (int it = 0; it < my_items; ++it) {
                 int band; GemvProblem pr;
                 item_at(it, band, pr);
@@ -576,10 +612,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
                 const CUtensorMap* amap = pr.rows <= 32 ? &tmap_a32 : (pr.rows <= 64 ? &tmap_a64 : &tmap_a);
                 const int box_bytes = pr.rows <= 32 ? 32 * BK * 2 : (pr.rows <= 64 ? 64 * BK * 2 : A_SUB_BYTES);
                 for (int ks = 0; ks < kstages; ++ks, ++cnt) {
-                    if (cnt >= ST) mbar_wait_parked(empty_t + 8 * st, pt ^ 1, p.status, 100);
-                    mbar_arrive_expect_tx(full_t + 8 * st, T_STAGE_BYTES);
-                    tma_load_3d(smem_u32(t_ring + st * T_STAGE_BYTES), &tmap_t, band * (TROW_BYTES / 8), ks * 4, pr.z, full_t + 8 * st);
-                    if (++st == ST) { st = 0; pt ^= 1; }
                     if (cnt >= SAg) mbar_wait_parked(empty_a + 8 * sa, pa ^ 1, p.status, 100);
                     mbar_arrive_expect_tx(full_a + 8 * sa, max(nsub, 1) * box_bytes);
                     for (int sub = 0; sub < max(nsub, 1); ++sub)
@@ -673,6 +705,322 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// decode_stage for the small-batch kernel, where the decode warps are the bottleneck: tight polling, and the hand-over
+// of a stage to the MMA warp (wait for the tensor-memory stores, fence, arrive on `pend_w`) is deferred until the
+// first k-tile row of the NEXT stage sits decoded in registers, so the stores' latency is covered by decode work.
+// The caller hands over the last stage itself.
+template <int BITS, int CB>
+__device__ __forceinline__ void sk_decode_stage(const unsigned char* tstage, uint32_t tmem_wstage, int quarter, int lane, bool wait_w,
+                                                uint32_t empty_w_bar, uint32_t empty_w_parity, unsigned* status, uint32_t pend_w)
+{
+    constexpr int NW = 8 * BITS, TROW_BYTES = 8 * NW * 4;
+    // All eight tiles of the warp are decoded into registers before the first store: a tensor-memory store holds
+    // its source registers until it has read them, so decoding the next tile into the registers of a store in
+    // flight stalls the warp for the store's latency.
+    uint32_t w[4][2][4];
+    if constexpr (BITS == 4) {
+        uint32_t r0[4][2], r1[4][2];
+#pragma unroll
+        for (int krow = 0; krow < 4; ++krow)
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const uint32_t* tile = reinterpret_cast<const uint32_t*>(tstage + krow * TROW_BYTES) + (2 * quarter + t) * NW;
+                r0[krow][t] = tile[lane];
+                r1[krow][t] = tile[(lane + 1) & 31];
+            }
+#pragma unroll
+        for (int krow = 0; krow < 4; ++krow)
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                uint32_t s[8];
+                dq::states_4bit<(CB != 2) ? 6 : 0>(r0[krow][t], r1[krow][t], s);
+                dq::decode_frag<CB>(s, w[krow][t]);
+            }
+    } else {
+#pragma unroll
+        for (int krow = 0; krow < 4; ++krow)
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                uint32_t s[8];
+                dq::lane_states<BITS>(reinterpret_cast<const uint32_t*>(tstage + krow * TROW_BYTES) + (2 * quarter + t) * NW, lane, s);
+                dq::decode_frag<CB>(s, w[krow][t]);
+            }
+    }
+    if (pend_w) {
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pend_w);
+    }
+    if (wait_w) {   // the MMAs that read this weight stage are done
+        mbar_wait(empty_w_bar, empty_w_parity, status);
+        tc_fence_after();
+    }
+#pragma unroll
+    for (int kp = 0; kp < 2; ++kp)
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+            tc_st_frag2_free(tmem_wstage + (uint32_t(32 * quarter + 16 * t) << 16) + 16 * kp, w[2 * kp][t], w[2 * kp + 1][t]);
+}
+
+// ---------------------------------------------------------------- the small-batch kernel (9..32 rows)
+// Decode batches too large for the mma.sync decode kernel's row groups and far too small to fill the prefill
+// tiles: one persistent CTA per SM, and the matrix's work -- `bands * (K / 64)` stages of 64 x 128 weights, band
+// major -- is cut into gridDim.x equal contiguous ranges, so every SM decodes the same number of weights whatever
+// the matrix's shape (a 1024-wide k/v projection has 8 bands; by bands alone it would use 8 SMs).  A range that
+// crosses a band boundary closes one accumulator and opens the other (two buffers of 32 TMEM columns), and the
+// epilogue warps drain the closed one while the pipeline runs on.  A band that one CTA holds whole is finished
+// from tensor memory as in the prefill kernel.  A band shared by several CTAs goes through fp32 slabs (two per
+// CTA: its first segment, and any later one), which k_sk_finish, chained behind, sums in CTA order -- a fixed
+// order -- and finishes (Hadamard, output scale, store) with one warp per band and row.  (A last-arriver tail in
+// this kernel was measured first: one CTA summing up to nineteen slabs of 32 rows took 20 us on the k/v shape.)
+// Nobody waits for another CTA.  Rows: the MMA's N is the row count rounded to 16; the activation box is 32
+// rows (rows past the array read as zero).
+struct SplitKArgs {
+    void* c;
+    const __half* svh;
+    unsigned* status;
+    float* slabs;          // [grid][2][32][128] fp32
+    int m, k, n, out_fp32, grid;
+};
+constexpr int kSkRows = 32;                       // rows of the activation box and of a slab
+constexpr int kSkAStageBytes = kSkRows * BK * 2;  // 4 KiB
+constexpr int kSkSA = 8;                          // activation stages
+constexpr int kSkSW = 8;                          // decoded-weight stages in tensor memory: two per decode group, so that a
+                                                  // group stores its next stage while the MMAs still read the previous one
+constexpr int kSkWCol0 = 2 * kSkRows;             // TMEM: two accumulators of 32 columns, then the weight stages
+template <int BITS>
+struct SGeo {
+    static constexpr int T_STAGE_BYTES = TGeo<BITS>::T_STAGE_BYTES;
+    static constexpr int ST = (160 * 1024) / T_STAGE_BYTES > 24 ? 24 : (160 * 1024) / T_STAGE_BYTES;   // 24 stages up to 6 bpw, 20 at 8
+    static constexpr int kBars = 2 * kSkSA + 2 * kSkSW + 2 * ST + 4;
+    static constexpr size_t SMEM = 1024 /*align slack*/ + size_t(kSkSA) * kSkAStageBytes + size_t(ST) * T_STAGE_BYTES +
+                                   (kXchFloats + 2 * 128) * 4 + kBars * 8;
+};
+__host__ __device__ inline long long sk_range_begin(int c, long long U, int G) { return (long long) c * U / G; }
+// the CTA whose range holds unit u
+__host__ __device__ inline int sk_range_owner(long long u, long long U, int G) { return int(((u + 1) * G + U - 1) / U) - 1; }
+
+template <int BITS, int CB>
+__global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_splitk(const __grid_constant__ CUtensorMap tmap_a,
+                                                                     const __grid_constant__ CUtensorMap tmap_t, const SplitKArgs p)
+{
+    using SG_ = SGeo<BITS>;
+    constexpr int TROW_BYTES = TGeo<BITS>::TROW_BYTES, T_STAGE_BYTES = SG_::T_STAGE_BYTES, ST = SG_::ST;
+    pdl_trigger();
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int bands = p.n / BN, kstages = p.k / BK;
+    const long long U = (long long) bands * kstages;
+    const int G = int(gridDim.x);
+    const long long u0 = sk_range_begin(blockIdx.x, U, G), u1 = sk_range_begin(blockIdx.x + 1, U, G);
+    const int total = int(u1 - u0);
+    if (total < 1) return;
+    const int band0 = int(u0 / kstages), ks00 = int(u0 - (long long) band0 * kstages);
+    const int rows_pad = max((min(p.m, kSkRows) + 15) & ~15, 16);
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* a_ring = smem;
+    unsigned char* t_ring = a_ring + kSkSA * kSkAStageBytes;
+    float* xch = reinterpret_cast<float*>(t_ring + ST * T_STAGE_BYTES);
+    float* svh_s = xch + kXchFloats;                   // two buffers of 128 scales, alternating between segments
+    uint64_t* bars = reinterpret_cast<uint64_t*>(svh_s + 2 * 128);
+    __shared__ uint32_t s_tmem_base;
+
+    const uint32_t full_a = smem_u32(bars), empty_a = full_a + 8 * kSkSA;
+    const uint32_t full_w = empty_a + 8 * kSkSA, empty_w = full_w + 8 * kSkSW;
+    const uint32_t full_t = empty_w + 8 * kSkSW, empty_t = full_t + 8 * ST;
+    const uint32_t acc_full = empty_t + 8 * ST, acc_empty = acc_full + 16;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kSkSA; ++s) { mbar_init(full_a + 8 * s, 1); mbar_init(empty_a + 8 * s, 1); }
+        for (int s = 0; s < kSkSW; ++s) { mbar_init(full_w + 8 * s, 4); mbar_init(empty_w + 8 * s, 1); }
+        for (int s = 0; s < ST; ++s) { mbar_init(full_t + 8 * s, 1); mbar_init(empty_t + 8 * s, 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full + 8 * b, 1); mbar_init(acc_empty + 8 * b, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem_base;
+    const uint32_t tmem_w = tmem + kSkWCol0;   // weight stages: 32 columns (64 k) each
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer of the trellis stages
+        // Its own thread, so that the weight stream runs as far ahead as its ring allows (the DRAM latency under
+        // load is several stage times) and never waits for a slot of the short activation ring.  The weights are
+        // never written by a kernel, so they may be fetched while the predecessor on the stream is still running.
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_t) : "memory");
+            int tb = band0, tks = ks00, st = 0, pt = 0;
+            for (int i = 0; i < total; ++i) {
+                if (i >= ST) mbar_wait_parked(empty_t + 8 * st, pt ^ 1, p.status, 100);
+                mbar_arrive_expect_tx(full_t + 8 * st, T_STAGE_BYTES);
+                tma_load_3d(smem_u32(t_ring + st * T_STAGE_BYTES), &tmap_t, tb * (TROW_BYTES / 8), tks * 4, 0, full_t + 8 * st);
+                if (++st == ST) { st = 0; pt ^= 1; }
+                if (++tks == kstages) { tks = 0; ++tb; }
+            }
+        }
+    } else if (warp == 2) {
+        // ------------------------------------------------------------ TMA producer of the activation stages
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+            pdl_wait();   // the rotated rows are the predecessor's output
+            int aks = ks00, sa = 0, pa = 0;
+            for (int i = 0; i < total; ++i) {
+                if (i >= kSkSA) mbar_wait_parked(empty_a + 8 * sa, pa ^ 1, p.status, 100);
+                mbar_arrive_expect_tx(full_a + 8 * sa, kSkAStageBytes);
+                tma_load_2d(smem_u32(a_ring + sa * kSkAStageBytes), &tmap_a, aks * BK, 0, full_a + 8 * sa);
+                if (++sa == kSkSA) { sa = 0; pa ^= 1; }
+                if (++aks == kstages) aks = 0;
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (whole warp, one elected lane issues)
+        const uint32_t id = idesc_n(rows_pad);
+        int sa = 0, pa = 0, sw = 0, pw = 0, ks = ks00, seg = 0, first = 1;
+        for (int i = 0; i < total; ++i) {
+            const int buf = seg & 1;
+            if (first && seg >= 2) {   // the epilogue has drained this accumulator
+                mbar_wait(acc_empty + 8 * buf, ((seg >> 1) - 1) & 1, p.status);
+                tc_fence_after();
+            }
+            mbar_wait(full_a + 8 * sa, pa, p.status);
+            mbar_wait(full_w + 8 * sw, pw, p.status);
+            tc_fence_after();
+            const uint64_t x_desc = smem_desc_sw128(smem_u32(a_ring + sa * kSkAStageBytes));
+            const uint32_t w_t = tmem_w + sw * 32, tacc = tmem + buf * kSkRows;
+            const uint32_t bar_a = empty_a + 8 * sa, bar_w = empty_w + 8 * sw;
+            const bool last = (ks + 1 == kstages) || (i + 1 == total);
+            if (elect_one()) {
+#pragma unroll
+                for (int k16 = 0; k16 < BK / 16; ++k16) tc_mma_ts_f16(tacc, w_t + 8 * k16, x_desc + 2 * k16, id, (first && k16 == 0) ? 0u : 1u);
+                tc_commit(bar_a);
+                tc_commit(bar_w);
+                if (last) tc_commit(acc_full + 8 * buf);
+            }
+            __syncwarp();
+            if (++sa == kSkSA) { sa = 0; pa ^= 1; }
+            if (++sw == kSkSW) { sw = 0; pw ^= 1; }
+            first = 0;
+            if (last) { ++seg; first = 1; ks = 0; } else ++ks;
+        }
+    } else if (warp >= kDecodeWarp0) {
+        // ------------------------------------------------------------ decode warps
+        const int g = (warp - kDecodeWarp0) >> 2, quarter = warp & 3;   // group g: stages g, g+4, ... into weight stages g, g+4 in turn
+        static_assert(kSkSW == 8 && ST >= 4, "two weight stages per decode group");
+        int st = g, pt = 0, j = 0;
+        uint32_t pend_w = 0;
+        for (int cnt = g; cnt < total; cnt += 4, ++j) {
+            mbar_wait(full_t + 8 * st, pt, p.status);
+            const int ws = g + 4 * (j & 1);
+            sk_decode_stage<BITS, CB>(t_ring + st * T_STAGE_BYTES, tmem_w + ws * 32, quarter, lane, j >= 2, empty_w + 8 * ws,
+                                      ((j >> 1) - 1) & 1, p.status, pend_w);
+            pend_w = full_w + 8 * ws;
+            __syncwarp();   // every lane has read its words of the trellis stage
+            if (lane == 0) mbar_arrive(empty_t + 8 * st);
+            st += 4;
+            if (st >= ST) { st -= ST; pt ^= 1; }
+        }
+        if (pend_w) {
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(pend_w);
+        }
+    } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + 4) {
+        // ------------------------------------------------------------ epilogue warps
+        const int quarter = warp & 3;
+        const int n = quarter * 32 + lane;
+        pdl_wait();   // slabs, counters and the output may still be in use by the predecessor
+        int seg = 0;
+        for (long long u = u0; u < u1; ++seg) {
+            const int band = int(u / kstages), ks0 = int(u - (long long) band * kstages);
+            const int len = int(min((long long) (kstages - ks0), u1 - u));
+            u += len;
+            float* sv = svh_s + (seg & 1) * 128;
+            sv[n] = __half2float(p.svh[band * BN + n]);
+            const int buf = seg & 1;
+            mbar_wait_parked(acc_full + 8 * buf, (seg >> 1) & 1, p.status, 200);
+            tc_fence_after();
+            float v[32];
+            tc_ld32(tmem + buf * kSkRows + (uint32_t(quarter * 32) << 16), v);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + 8 * buf);   // the values are in registers
+            if (len < kstages) {
+                // a shared band: this segment's partial sums into the CTA's slab
+                float* slab = p.slabs + (size_t(blockIdx.x) * 2 + (seg ? 1 : 0)) * (kSkRows * BN);
+#pragma unroll
+                for (int r = 0; r < 32; ++r)
+                    if (r < rows_pad) __stcg(slab + r * BN + n, v[r]);
+                continue;
+            }
+            epilogue_rows(v, xch, sv, 0, quarter, lane, p.c, p.out_fp32, p.n, band * BN, 0, p.m);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// The shared bands of k_exl3_gemm_tc_splitk: block (band, group of four rows), one warp per row, a lane holds four
+// consecutive columns.  The slabs of the CTAs whose ranges meet the band are summed in CTA order (four loads in
+// flight per lane), then Hadamard, output scale, store.  Bands that one CTA held whole were finished by the main
+// kernel; their blocks return at once.
+__global__ void __launch_bounds__(128) k_sk_finish(const SplitKArgs p)
+{
+    pdl_trigger();
+    const int band = blockIdx.x, lane = threadIdx.x & 31, row = blockIdx.y * 4 + (threadIdx.x >> 5);
+    const int bands = p.n / BN, kstages = p.k / BK, G = p.grid;
+    const long long U = (long long) bands * kstages;
+    const int c_lo = sk_range_owner((long long) band * kstages, U, G);
+    const int c_hi = sk_range_owner((long long) (band + 1) * kstages - 1, U, G);
+    if (c_lo == c_hi || row >= p.m) return;
+    pdl_wait();
+    auto slab_of = [&](int cc) {
+        // CTA cc's slab of this band: slot 0 when the band is where its range begins
+        const int first_band = int(sk_range_begin(cc, U, G) / kstages);
+        return p.slabs + ((size_t(cc) * 2 + (first_band == band ? 0 : 1)) * kSkRows + row) * BN + 4 * lane;
+    };
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int cc = c_lo; cc <= c_hi; cc += 4) {
+        float4 x[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            x[i] = cc + i <= c_hi ? __ldcg(reinterpret_cast<const float4*>(slab_of(cc + i))) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (cc + i <= c_hi) {
+                v[0] = __fadd_rn(v[0], x[i].x); v[1] = __fadd_rn(v[1], x[i].y);
+                v[2] = __fadd_rn(v[2], x[i].z); v[3] = __fadd_rn(v[3], x[i].w);
+            }
+    }
+    dq::had128_warp(v, lane);
+    const uint2 sr = __ldg(reinterpret_cast<const uint2*>(p.svh + band * BN + 4 * lane));
+    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sr.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&sr.y));
+    const float o0 = __fmul_rn(__fmul_rn(v[0], kRScale), s01.x), o1 = __fmul_rn(__fmul_rn(v[1], kRScale), s01.y);
+    const float o2 = __fmul_rn(__fmul_rn(v[2], kRScale), s23.x), o3 = __fmul_rn(__fmul_rn(v[3], kRScale), s23.y);
+    const size_t at = size_t(row) * p.n + band * BN + 4 * lane;
+    if (p.out_fp32) {
+        *reinterpret_cast<float4*>(static_cast<float*>(p.c) + at) = make_float4(o0, o1, o2, o3);
+    } else {
+        uint2 o;
+        o.x = dq::pack_half2(__float2half_rn(o0), __float2half_rn(o1));
+        o.y = dq::pack_half2(__float2half_rn(o2), __float2half_rn(o3));
+        *reinterpret_cast<uint2*>(static_cast<__half*>(p.c) + at) = o;
     }
 }
 
@@ -782,6 +1130,48 @@ void launch_tc_bits(int k_bits, int codebook, const void* a_had, const void* tre
         case 6: launch_tc_cb<6>(codebook, a_had, trellis, args, stream); break;
         case 7: launch_tc_cb<7>(codebook, a_had, trellis, args, stream); break;
         case 8: launch_tc_cb<8>(codebook, a_had, trellis, args, stream); break;
+        default: throw std::runtime_error("exl3 linear: K must be in 1..=8");
+    }
+}
+
+template <int BITS, int CB>
+void launch_sk(const void* a_had, const void* trellis, const SplitKArgs& args, int grid, cudaStream_t stream)
+{
+    using SG_ = SGeo<BITS>;
+    auto kern = k_exl3_gemm_tc_splitk<BITS, CB>;
+    static bool attr_set[kMaxDevices] = {};
+    const int dev = current_device();
+    if (!attr_set[dev]) {
+        cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SG_::SMEM)), "split-k gemm smem attribute");
+        attr_set[dev] = true;
+    }
+    const CUtensorMap map_a = make_map(CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a_had, cuuint64_t(args.k), cuuint64_t(args.m),
+                                       cuuint64_t(args.k) * 2, BK, kSkRows, CU_TENSOR_MAP_SWIZZLE_128B);
+    const CUtensorMap map_t = make_trellis_map(trellis, 1, args.k, args.n, BITS, TGeo<BITS>::TROW_BYTES);
+    launch_pdl(kern, dim3(grid), dim3(kThreads), SG_::SMEM, stream, "k_exl3_gemm_tc_splitk launch", map_a, map_t, args);
+}
+
+template <int BITS>
+void launch_sk_cb(int cb, const void* a_had, const void* trellis, const SplitKArgs& a, int grid, cudaStream_t st)
+{
+    switch (cb) {
+        case 0: launch_sk<BITS, 0>(a_had, trellis, a, grid, st); break;
+        case 1: launch_sk<BITS, 1>(a_had, trellis, a, grid, st); break;
+        default: launch_sk<BITS, 2>(a_had, trellis, a, grid, st); break;
+    }
+}
+
+void launch_sk_bits(int k_bits, int codebook, const void* a_had, const void* trellis, const SplitKArgs& args, int grid, cudaStream_t stream)
+{
+    switch (k_bits) {
+        case 1: launch_sk_cb<1>(codebook, a_had, trellis, args, grid, stream); break;
+        case 2: launch_sk_cb<2>(codebook, a_had, trellis, args, grid, stream); break;
+        case 3: launch_sk_cb<3>(codebook, a_had, trellis, args, grid, stream); break;
+        case 4: launch_sk_cb<4>(codebook, a_had, trellis, args, grid, stream); break;
+        case 5: launch_sk_cb<5>(codebook, a_had, trellis, args, grid, stream); break;
+        case 6: launch_sk_cb<6>(codebook, a_had, trellis, args, grid, stream); break;
+        case 7: launch_sk_cb<7>(codebook, a_had, trellis, args, grid, stream); break;
+        case 8: launch_sk_cb<8>(codebook, a_had, trellis, args, grid, stream); break;
         default: throw std::runtime_error("exl3 linear: K must be in 1..=8");
     }
 }
@@ -938,6 +1328,38 @@ std::string launch_gemm_tc(const void* a, const void* trellis, void* c, const vo
     return "k_had128<f16,pre> + k_exl3_gemm_tc<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "> grid=" +
            std::to_string(size_n / BN) + "x" + std::to_string((size_m + args.nsub_max * SUB - 1) / (args.nsub_max * SUB)) +
            " block=" + std::to_string(kThreads) + " tile=" + std::to_string(args.nsub_max * SUB) + "x128x64 tmem=512";
+}
+
+// Decode batches of up to 32 rows on the tensor-core path: rotate the rows, then the persistent split-K kernel.
+std::string launch_gemm_tc_splitk(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
+                                  int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, const GemvScratch& sc,
+                                  int sms, cudaStream_t stream)
+{
+    if (size_k % 128 != 0)
+        throw std::runtime_error("exl3 linear: no linked kernel for size_k that is not a multiple of 128 (128-wide Hadamard)");
+    if (size_m < 1 || size_m > kSkRows) throw std::runtime_error("exl3 linear (small-batch tensor path): size_m must be in 1..=32");
+    const long long units = (long long) (size_n / BN) * (size_k / BK);
+    int grid = int(std::min<long long>(sms, units));
+    const size_t per_cta = size_t(2) * kSkRows * BN * sizeof(float);
+    if (size_t(grid) * per_cta > sc.slab_bytes) grid = int(sc.slab_bytes / per_cta);
+    if (grid < 1) throw std::runtime_error("exl3 linear: split-K scratch is too small for this shape");
+    had_r_128(a, a_had, suh, 1, size_m, size_k, 0, stream);
+    SplitKArgs args;
+    args.c = c;
+    args.svh = static_cast<const __half*>(svh);
+    args.status = sc.status;
+    args.slabs = sc.slabs;
+    args.m = size_m; args.k = size_k; args.n = size_n;
+    args.out_fp32 = out_fp32;
+    args.grid = grid;
+    launch_sk_bits(k_bits, codebook, a_had, trellis, args, grid, stream);
+    // shared bands exist unless every range boundary falls on a band boundary
+    const bool shared = units % grid != 0 || (units / grid) % (size_k / BK) != 0;
+    if (shared)
+        launch_pdl(k_sk_finish, dim3(size_n / BN, (size_m + 3) / 4), dim3(128), 0, stream, "k_sk_finish launch", args);
+    return "k_had128<f16,pre> + k_exl3_gemm_tc_splitk<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "> grid=" +
+           std::to_string(grid) + " block=" + std::to_string(kThreads) + " stage=64x128 rows=" + std::to_string((size_m + 15) / 16 * 16) +
+           (shared ? " + k_sk_finish" : "");
 }
 
 void rotate_rows_grouped(const RotateArgs& a, bool dual, bool silu, int sms, cudaStream_t stream)

@@ -12,7 +12,19 @@ std::string launch_gemm_tc(const void* a, const void* trellis, void* c, const vo
                            int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, unsigned* status,
                            cudaStream_t stream);
 
-// Two kernels serve every row count: the fused decode GEMV up to 32 rows, the tensor-core GEMM above.
+std::string launch_gemm_tc_splitk(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
+                                  int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, const GemvScratch& sc,
+                                  int sms, cudaStream_t stream);
+
+// Where the persistent split-K tensor-core kernel takes over from the decode GEMV (measured on the 27B shapes at 4 and
+// 6 bpw): from 17 rows -- the GEMV's third and fourth row group cost it 5 us on a 45 MB matrix, the tensor-core kernel's
+// time does not depend on the row count -- and only for matrices with at least eight 64 x 128 weight stages per SM; below
+// that its three launches (rotation, main kernel, finishing kernel) cost more than they save.
+constexpr int kSplitKMinRows = 17;
+constexpr long long kSplitKMinStagesPerSm = 8;
+
+// Three kernels serve every row count: the fused decode GEMV up to 16 rows (and for small matrices up to 32), the
+// persistent split-K tensor-core kernel for 17..32 rows, the tiled tensor-core GEMM above.
 std::string linear_rows(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, cudaStream_t stream)
 {
@@ -21,9 +33,13 @@ std::string linear_rows(const void* a, const void* trellis, void* c, const void*
     if (info.major != 10)
         throw std::runtime_error("exl3 linear: no linked kernel for this GPU (library is built for sm_100a only)");
     GemvScratch w = gemv_workspace(device);
-    if (size_m <= 32)
+    const long long stages = (long long) (size_n / 128) * (size_k / 64);
+    if (size_m < kSplitKMinRows || (size_m <= 32 && stages < kSplitKMinStagesPerSm * info.sms))
         return launch_gemv(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, out_fp32, w, info.sms,
                            stream);
+    if (size_m <= 32)
+        return launch_gemm_tc_splitk(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, out_fp32, w,
+                                     info.sms, stream);
     return launch_gemm_tc(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, out_fp32, w.status, stream);
 }
 

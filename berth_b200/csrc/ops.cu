@@ -59,6 +59,8 @@ template <bool FP32, bool PRE>
 __global__ void __launch_bounds__(128) k_had128(const void* __restrict__ in, void* __restrict__ out,
                                                 const __half* __restrict__ scale, int rows, int blocks_per_row)
 {
+    pdl_trigger();
+    pdl_wait();   // the input may be the output of the predecessor on the stream
     const int lane = threadIdx.x & 31;
     const long long total = (long long) rows * blocks_per_row;
     for (long long idx = (long long) blockIdx.x * 4 + (threadIdx.x >> 5); idx < total; idx += (long long) gridDim.x * 4) {
@@ -267,13 +269,12 @@ void had_r_128(const void* input, void* output, const void* scale, int pre_scale
     int grid = int(std::min<long long>((total + 3) / 4, 148LL * 16));
     const __half* sc = static_cast<const __half*>(scale);
     if (fp32) {
-        if (pre_scale) k_had128<true, true><<<grid, 128, 0, stream>>>(input, output, sc, rows, bpr);
-        else k_had128<true, false><<<grid, 128, 0, stream>>>(input, output, sc, rows, bpr);
+        if (pre_scale) launch_pdl(k_had128<true, true>, dim3(grid), dim3(128), 0, stream, "k_had128", input, output, sc, rows, bpr);
+        else launch_pdl(k_had128<true, false>, dim3(grid), dim3(128), 0, stream, "k_had128", input, output, sc, rows, bpr);
     } else {
-        if (pre_scale) k_had128<false, true><<<grid, 128, 0, stream>>>(input, output, sc, rows, bpr);
-        else k_had128<false, false><<<grid, 128, 0, stream>>>(input, output, sc, rows, bpr);
+        if (pre_scale) launch_pdl(k_had128<false, true>, dim3(grid), dim3(128), 0, stream, "k_had128", input, output, sc, rows, bpr);
+        else launch_pdl(k_had128<false, false>, dim3(grid), dim3(128), 0, stream, "k_had128", input, output, sc, rows, bpr);
     }
-    cuda_ok(cudaPeekAtLastError(), "k_had128");
 }
 
 }  // namespace berth

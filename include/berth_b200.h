@@ -118,7 +118,9 @@ int berth_exl3_smoke_gemm(void);
  * the launches of the linear alone.  best: DEVICE array of size_m 64-bit keys (zeroed by the call on the stream);
  * after the stream completes key r describes the largest output of row r, ties to the lower column, the value as
  * stored (fp16-rounded for fp16 outputs); berth_argmax_key_decode splits a key on the host.  c may be NULL: the
- * outputs are then not written at all.  Everything else as berth_exl3_linear. */
+ * outputs are then not written at all.  Everything else as berth_exl3_linear; the call always runs the decode
+ * kernel, so from 17 rows of a large matrix (where berth_exl3_linear runs the split-K tensor-core kernel) its
+ * outputs equal berth_exl3_linear's within the accumulation tolerance instead of bit for bit. */
 int berth_exl3_linear_argmax(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                              unsigned long long* best, int size_m, int size_k, int size_n, int k_bits, int codebook,
                              int out_fp32, void* stream);
@@ -127,7 +129,8 @@ void berth_argmax_key_decode(unsigned long long key, int32_t* token, float* valu
 /* The decode linear (size_m <= 32) with the residual stream added in its last step: c = residual + linear(a), fp32
  * [size_m][size_n]; c may be the residual itself (x += mlp(h2) in place).  Bit for bit what berth_exl3_linear with
  * out_fp32 = 1 followed by berth_ops_add_f32(residual, c, c) gives (crates/berth-engine/src/model.rs:976-1022), in
- * the launches of the linear alone.  No counterpart in berth. */
+ * the launches of the linear alone (always the decode kernel: from 17 rows of a large matrix, where berth_exl3_linear
+ * runs the split-K tensor-core kernel, equal within the accumulation tolerance).  No counterpart in berth. */
 int berth_exl3_linear_add(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                           const void* residual, int size_m, int size_k, int size_n, int k_bits, int codebook,
                           void* stream);
