@@ -171,13 +171,14 @@ class DecodeStack:
                                            outputs=[self.q, self.k, self.v])
             self.layers.append((mlp, lin))
         # one row: gate+up (one stacked integer-path launch, rotation and finishing inside it), down and o (the same kernel,
-        # one launch each), q/k/v (k_rotate_in + k_exl3_gemv + k_gemv_finish for the three), k_silu_mul = 7 launches.
-        # two rows: the stacked launch, down and o on the fp16-path kernel (k_exl3_gemv + k_gemv_finish each), q/k/v, silu = 9.
+        # one launch each), q/k/v (the same kernel over the three matrices, one launch), k_silu_mul = 5 launches.
+        # two rows: the stacked launch, down and o on the fp16-path kernel (k_exl3_gemv + k_gemv_finish each), q/k/v, silu = 7.
         # 3..4 rows: k_rotate_in_i8 per stacked matrix + the stacked launch, down and o with k_rotate_in + k_exl3_gemv +
-        # k_gemv_finish each, q/k/v, silu = 13.
+        # k_gemv_finish each, q/k/v (one launch), silu = 11.
         # above: gate, up, down, o with three launches each (k_rotate_in + k_exl3_gemv + k_gemv_finish up to 16 rows,
-        # k_had128 + k_exl3_gemm_tc_splitk + k_sk_finish from 17), q/k/v, silu = 16.
-        self.launches_per_step = 7 if m == 1 else (9 if m == 2 else (13 if m <= 4 else 16))
+        # k_had128 + k_exl3_gemm_tc_splitk + k_sk_finish from 17), q/k/v as one sliced launch of the fp16-path kernel
+        # (k_rotate_in + k_exl3_gemv + k_gemv_finish), silu = 16.
+        self.launches_per_step = 5 if m == 1 else (7 if m == 2 else (11 if m <= 4 else 16))
 
     def step(self, i: int) -> None:
         from berth_b200.kernels import OutDtype
@@ -870,7 +871,7 @@ def main() -> None:
             "config": {"workload": "c1_dense_27b_decode_stack_4bpw", "m": args.m, "bits": BITS, "codebook": "mul1",
                        "bytes_per_step": sb, "layers_cycled": LAYERS,
                        "l2": f"{LAYERS} distinct layers ({LAYERS * sb / 1e6:.0f} MB) cycled; inputs larger than L2",
-                       "qkv": "one sliced multi-linear launch (berth_ops_mgemm), as berth's attention layers run them",
+                       "qkv": "one launch over the three matrices, as berth's attention layers run them (berth_ops_mgemm; up to four rows the integer-path multi-matrix launch)",
                        "parallelism": "replicas" if world > 1 else "single"},
             "frac_of_hbm_peak": value / world / peak, "peak_kind": peak_kind,
             "tokens_per_s": args.m * args.steps * world / (ms * 1e-3),

@@ -207,6 +207,11 @@ std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const vo
                            int size_m, int size_k, int size_n, int k_bits, int out_fp32, const GemvScratch& scratch, int sms,
                            cudaStream_t stream, unsigned long long* argmax, int n_stack = 1, const float* residual = nullptr);
 
+// The integer-path decode kernel over up to four MUL1 matrices of different widths applied to the same rows (host arrays
+// of device pointers and widths); same contract as launch_gemv per matrix.
+std::string launch_gemv_i8_multi(const void* a, const void* const* trellis, void* const* c, const void* const* suh,
+                                 void* const* a_had, const void* const* svh, const int* size_n, int n_matrices, int size_m,
+                                 int size_k, int k_bits, int out_fp32, const GemvScratch& sc, int sms, cudaStream_t stream);
 // True when launch_gemv_i8 would rotate the activations inside the decode kernel for this dense shape.
 bool gemv_i8_rotates_in_kernel(int size_m, int size_k, int size_n, int k_bits, int sms);
 

@@ -19,6 +19,8 @@ __host__ __device__ inline int unit_owner(long long u, long long U, int G) { ret
 enum StatusBits : unsigned { kStFullTimeout = 1u, kStEmptyTimeout = 2u, kStTmemTimeout = 4u };
 
 
+constexpr int kMaxHetMatrices = 4;
+
 struct GemvArgs {
     const uint32_t* afrag;    // rotated activations in MMA fragment order [problem][k/16][TG][2][8][4] words
     float* blocksum;          // [problem][8*TG or m][k/128]: sum of each rotated 128-block (MUL1 epilogue)
@@ -50,6 +52,16 @@ struct GemvArgs {
     // matrix): matrix i has its trellis at index i of the 3-D map, its sign-scale vectors at suh + i*k and
     // svh + i*n, and writes c + i*m*n, a_had + i*m*k and block sums i*m*(k/128).
     int n_stack;
+    // The same for matrices of different widths (q, k and v of an attention block), each with its own tensors
+    // (integer tensor path only): het != 0; matrix i owns band groups het_bg[i] .. het_bg[i+1]-1 of the launch, is
+    // het_n[i] columns wide, and has its own sign-scale vectors, output and rotated-activation buffer.
+    int het;
+    int het_bg[kMaxHetMatrices + 1];
+    int het_n[kMaxHetMatrices];
+    const __half* het_suh[kMaxHetMatrices];
+    const __half* het_svh[kMaxHetMatrices];
+    void* het_c[kMaxHetMatrices];
+    __half* het_a_had[kMaxHetMatrices];
 };
 
 // What the roles of the decode kernel need to know about problem pi of a launch.

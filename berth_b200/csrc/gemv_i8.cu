@@ -212,8 +212,14 @@ __device__ __forceinline__ float quantise_block(uint2 o, int lane, unsigned char
 // into a shared-memory area of its own (tiles of 2 * rows limb rows, a quarter of the ring-stage tile for one row),
 // and the CTAs that hold band group 0 also write the rotated activations and block sums for the caller and the
 // finishing kernel.
+// The trellis views of a launch: one 3-D map (z = matrix of an equally shaped stack), or one map per matrix of a
+// launch over matrices of different widths.
+struct I8Maps {
+    CUtensorMap m[kMaxHetMatrices];
+};
+
 template <int BITS, int NB, bool FUSED>
-__global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_constant__ CUtensorMap tmap, const GemvArgs p)
+__global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_constant__ I8Maps maps, const GemvArgs p)
 {
     static_assert(!FUSED || NB == 1, "in-kernel rotation is built for one group of four rows");
     using G_ = GeoI8<BITS, NB, FUSED>;
@@ -237,7 +243,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
     const int bands = p.n >> 7, kblocks = p.k >> 7;
     const int bgroups = (bands + BU - 1) / BU;
     const int nprob = p.problems ? min(max(__ldg(p.n_problems), 0), p.max_problems) : (p.n_stack > 1 ? p.n_stack : 1);
-    const long long U = (long long) nprob * bgroups * kblocks;
+    const long long U = p.het ? (long long) p.het_bg[p.n_stack] * kblocks : (long long) nprob * bgroups * kblocks;
+    // band group of the launch -> matrix and band group inside it
+    auto split_bg = [&](int gbg, int& pi, int& lbg) {
+        if (p.het) {
+            pi = 0;
+            while (pi + 1 < p.n_stack && gbg >= p.het_bg[pi + 1]) ++pi;
+            lbg = gbg - p.het_bg[pi];
+        } else {
+            pi = gbg / bgroups;
+            lbg = gbg - pi * bgroups;
+        }
+    };
     const int cta = blockIdx.x;
     const int G = U < (long long) gridDim.x ? int(U) : int(gridDim.x);
     if (cta >= G) {
@@ -256,23 +273,22 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
     const int pre = nunits < S ? nunits : S;
     constexpr uint32_t kStageTx = FUSED ? W_BYTES : STAGE_BYTES;
     auto issue_weights = [&](uint32_t dst, uint32_t bar) {
-        const int z = p.problems ? load_problem(p.problems, pr_pi, p.n_matrices, TOK, p.max_rows).z : pr_pi;
-        tma_load_3d(dst, &tmap, pr_lbg * (ROW_BYTES / 8), pr_kb * 8, z, bar);
+        const int z = p.problems ? load_problem(p.problems, pr_pi, p.n_matrices, TOK, p.max_rows).z : (p.het ? 0 : pr_pi);
+        tma_load_3d(dst, &maps.m[p.het ? pr_pi : 0], pr_lbg * (ROW_BYTES / 8), pr_kb * 8, z, bar);
     };
     auto next_unit = [&]() {
         if (++pr_kb == kblocks) {
             pr_kb = 0;
-            if (++pr_lbg == bgroups) { pr_lbg = 0; ++pr_pi; }
+            if (++pr_lbg == (p.het ? p.het_bg[pr_pi + 1] - p.het_bg[pr_pi] : bgroups)) { pr_lbg = 0; ++pr_pi; }
         }
     };
     if (warp == kProducerWarp && lane == 0) {
         for (int s = 0; s < S; ++s) mbar_init(full0 + 8 * s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
-        const unsigned gbg = unsigned(u0 / kblocks);
+        const int gbg = int(u0 / kblocks);
         pr_kb = int(u0 - (long long) gbg * kblocks);
-        pr_pi = int(gbg / unsigned(bgroups));
-        pr_lbg = int(gbg - unsigned(pr_pi) * unsigned(bgroups));
+        split_bg(gbg, pr_pi, pr_lbg);
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.m[p.het ? pr_pi : 0]) : "memory");
         for (int i = 0; i < pre; ++i) {
             mbar_arrive_expect_tx(full0 + 8 * i, kStageTx);
             issue_weights(smem_u32(ring + i * STAGE_BYTES), full0 + 8 * i);
@@ -317,17 +333,20 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
                     const int j = task / p.m, t = task - j * p.m;
                     const long long uu = u0 + j;
                     const int gbg = int(uu / kblocks), kb = int(uu - (long long) gbg * kblocks);
-                    const int pi = gbg / bgroups, lbg = gbg - pi * bgroups;   // matrix of the stack, band group inside it
+                    int pi, lbg;   // matrix of the stack, band group inside it
+                    split_bg(gbg, pi, lbg);
                     float sx;
-                    const uint2 o = rotate_block<false>(p.a + size_t(t) * p.k, p.suh + size_t(pi) * p.k, kb, lane, sx);
+                    const uint2 o = rotate_block<false>(p.a + size_t(t) * p.k, p.het ? p.het_suh[pi] : p.suh + size_t(pi) * p.k, kb, lane, sx);
                     int isum;
                     const float scale = quantise_block(o, lane, area + size_t(j) * ftile + t * 32, 2 * flbo, flbo, isum);
                     if (lane == 0) {
                         fscales[j * 8 + t] = scale;
                         fscales[j * 8 + 4 + t] = __fmul_rn(scale, __int2float_rn(isum));
                     }
-                    if (lbg == 0)   // band group 0 of a matrix meets every 128-block exactly once: the caller's copy
-                        *reinterpret_cast<uint2*>(p.a_had + (size_t(pi) * p.m + t) * p.k + kb * 128 + lane * 4) = o;
+                    if (lbg == 0) {   // band group 0 of a matrix meets every 128-block exactly once: the caller's copy
+                        __half* ah = p.het ? p.het_a_had[pi] + size_t(t) * p.k : p.a_had + (size_t(pi) * p.m + t) * p.k;
+                        *reinterpret_cast<uint2*>(ah + kb * 128 + lane * 4) = o;
+                    }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads the tiles through the async proxy
             }
@@ -344,10 +363,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
             pdl_wait();
             if constexpr (!FUSED) {
                 // the limb tiles of the stages whose weights are already on their way: replay the coordinates from u0
-                unsigned gbg = unsigned(u0 / kblocks);
+                int gbg = int(u0 / kblocks);
                 int kb = int(u0 - (long long) gbg * kblocks);
                 for (int i = 0; i < pre; ++i) {
-                    issue_limbs(int(gbg / unsigned(bgroups)), kb, smem_u32(ring + i * STAGE_BYTES + W_BYTES), full0 + 8 * i);
+                    int pi, lbg;
+                    split_bg(gbg, pi, lbg);
+                    issue_limbs(pi, kb, smem_u32(ring + i * STAGE_BYTES + W_BYTES), full0 + 8 * i);
                     if (++kb == kblocks) { kb = 0; ++gbg; }
                 }
                 if (pre > 0) next_unit();
@@ -480,8 +501,14 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
         long long u = u0;
         while (u < u1) {
             const Segment sg = segment_at(u, u0, u1, kblocks);
-            const int pi = sg.bg / bgroups, lbg = sg.bg - pi * bgroups;
-            const ProblemView pv = problem_view(p, pi, TOK);
+            int pi, lbg;
+            split_bg(sg.bg, pi, lbg);
+            ProblemView pv = problem_view(p, pi, TOK);
+            if (p.het) {
+                pv.z = 0; pv.act = pi;
+                pv.svh = p.het_svh[pi]; pv.c = p.het_c[pi]; pv.ldc = p.het_n[pi];
+            }
+            const int bands_pi = p.het ? p.het_n[pi] >> 7 : bands;
             const int rows = min(pv.rows, TOK), row0 = pv.row0;
             float acc[BU][TOK], sxp[TOK];   // per row: dot products of this thread's column(s); sum of the quantised activations
 #pragma unroll
@@ -544,7 +571,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
 #pragma unroll
                 for (int q = 0; q < kTasksPerWarp; ++q) {
                     const int task = ew + q * kEpiWarps, row = task / BU, b = task - row * BU, band = lbg * BU + b;
-                    if (row < rows && band < bands) {   // (ragged last band group)
+                    if (row < rows && band < bands_pi) {   // (ragged last band group)
                         float sx = 0.f;
 #pragma unroll
                         for (int t = 0; t < TOK; ++t) sx = t == row ? sxp[t] : sx;
@@ -583,7 +610,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
 #pragma unroll
                     for (int q = 0; q < kTasksPerWarp; ++q) {
                         const int task = ew + q * kEpiWarps, row = task / BU, b = task - row * BU, band = lbg * BU + b;
-                        if (row < rows && band < bands) {
+                        if (row < rows && band < bands_pi) {
                             const uint2 sv = __ldg(reinterpret_cast<const uint2*>(pv.svh + band * 128 + lane * 4));
                             float v[4] = {0.f, 0.f, 0.f, 0.f}, sx = 0.f;
                             for (int c = first_cta; c <= last_cta; ++c) {
@@ -663,7 +690,7 @@ int fused_max_units(int k_bits, int rows)
 }
 
 template <int BITS, int NB, bool FUSED>
-size_t launch_one(const void* trellis, int n_matrices, const GemvArgs& args, int grid, cudaStream_t stream)
+size_t launch_one(const void* const* trellis, int n_matrices, const GemvArgs& args, int grid, cudaStream_t stream)
 {
     using G_ = GeoI8<BITS, NB, FUSED>;
     auto kern = k_exl3_gemv_i8<BITS, NB, FUSED>;
@@ -673,13 +700,22 @@ size_t launch_one(const void* trellis, int n_matrices, const GemvArgs& args, int
         cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(G_::SMEM)), "gemv i8 smem attribute");
         attr_set[dev] = true;
     }
-    const CUtensorMap map = trellis_map(trellis, n_matrices, args.k, args.n, BITS, G_::ROW_BYTES);
-    launch_pdl(kern, dim3(grid), dim3(kThreads), G_::SMEM, stream, "k_exl3_gemv_i8 launch", map, args);
+    I8Maps maps;
+    if (args.het) {
+        for (int i = 0; i < kMaxHetMatrices; ++i) {
+            const int j = i < n_matrices ? i : 0;
+            maps.m[i] = trellis_map(trellis[j], 1, args.k, args.het_n[j], BITS, G_::ROW_BYTES);
+        }
+    } else {
+        maps.m[0] = trellis_map(trellis[0], n_matrices, args.k, args.n, BITS, G_::ROW_BYTES);
+        for (int i = 1; i < kMaxHetMatrices; ++i) maps.m[i] = maps.m[0];
+    }
+    launch_pdl(kern, dim3(grid), dim3(kThreads), G_::SMEM, stream, "k_exl3_gemv_i8 launch", maps, args);
     return G_::SMEM;
 }
 
 template <int BITS>
-size_t launch_nb(int nb, bool fused, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
+size_t launch_nb(int nb, bool fused, const void* const* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
 {
     switch (nb) {
         case 1: return fused ? launch_one<BITS, 1, true>(t, nm, a, grid, st) : launch_one<BITS, 1, false>(t, nm, a, grid, st);
@@ -687,7 +723,7 @@ size_t launch_nb(int nb, bool fused, const void* t, int nm, const GemvArgs& a, i
     }
 }
 
-size_t launch_bits(int k_bits, int nb, bool fused, const void* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
+size_t launch_bits(int k_bits, int nb, bool fused, const void* const* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
 {
     switch (k_bits) {
         case 1: return launch_nb<1>(nb, fused, t, nm, a, grid, st);
@@ -774,9 +810,80 @@ std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const vo
     args.out_fp32 = out_fp32;
     args.max_problems = 1; args.n_matrices = n_stack; args.max_rows = size_m;
     args.n_stack = n_stack;
-    const size_t smem = launch_bits(k_bits, nb, fused, trellis, n_stack, args, grid, stream);
- return std::string(fused ? "" : "k_rotate_in_i8 + ") + "k_exl3_gemv_i8<" + std::to_string(k_bits) + "," + std::to_string(nb) + (fused ? ",fused" : "") + (n_stack > 1 ? ",stack of " + std::to_string(n_stack) : "") + "> grid=" + std::to_string(grid) +
+    const size_t smem = launch_bits(k_bits, nb, fused, &trellis, n_stack, args, grid, stream);
+    return std::string(fused ? "" : "k_rotate_in_i8 + ") + "k_exl3_gemv_i8<" + std::to_string(k_bits) + "," + std::to_string(nb) + (fused ? ",fused" : "") + (n_stack > 1 ? ",stack of " + std::to_string(n_stack) : "") + "> grid=" + std::to_string(grid) +
            " block=" + std::to_string(kThreads) + " smem=" + std::to_string(smem);
+}
+
+// The same kernel over up to four MUL1 matrices of different widths applied to the same rows (q, k and v of an attention
+// block), each with its own tensors: the band groups of all matrices form one unit list, so launch latency, pipeline ramp
+// and the in-kernel rotation are paid once.  The pointer arrays are host arrays.
+std::string launch_gemv_i8_multi(const void* a, const void* const* trellis, void* const* c, const void* const* suh,
+                                 void* const* a_had, const void* const* svh, const int* size_n, int n_matrices, int size_m,
+                                 int size_k, int k_bits, int out_fp32, const GemvScratch& sc, int sms, cudaStream_t stream)
+{
+    if (n_matrices < 1 || n_matrices > kMaxHetMatrices) throw std::runtime_error("exl3 linear multi: 1 to 4 matrices");
+    if (size_m < 1 || size_m > kI8MaxRows) throw std::runtime_error("exl3 linear multi: size_m must be in 1..=8");
+    if (size_k % 128 != 0)
+        throw std::runtime_error("exl3 linear: no linked kernel for size_k that is not a multiple of 128 (128-wide Hadamard)");
+    if (k_bits < 1 || k_bits > 8) throw std::runtime_error("exl3 linear: K must be in 1..=8");
+    const int nb = size_m <= 4 ? 1 : 2;
+    const int bu = k_bits <= 4 ? 2 : 1;
+    const int kblocks = size_k / 128;
+    GemvArgs args{};
+    args.het = 1;
+    int total_bg = 0, max_n = 0;
+    for (int i = 0; i < n_matrices; ++i) {
+        if (size_n[i] < 128 || size_n[i] % 128 != 0) throw std::runtime_error("exl3 linear multi: size_n must be a multiple of 128");
+        args.het_bg[i] = total_bg;
+        total_bg += (size_n[i] / 128 + bu - 1) / bu;
+        args.het_n[i] = size_n[i];
+        args.het_suh[i] = static_cast<const __half*>(suh[i]);
+        args.het_svh[i] = static_cast<const __half*>(svh[i]);
+        args.het_c[i] = c[i];
+        args.het_a_had[i] = static_cast<__half*>(a_had[i]);
+        max_n = std::max(max_n, size_n[i]);
+    }
+    for (int i = n_matrices; i <= kMaxHetMatrices; ++i) args.het_bg[i] = total_bg;
+    if (size_t(n_matrices) * size_m * kblocks > sc.blocksum_floats)
+        throw std::runtime_error("exl3 gemv: matrices x size_m x size_k / 128 exceed the block-sum table of the scratch");
+    const size_t limb_bytes = size_t(kblocks) * (size_t(16) * nb * 256 + 128);
+    if (limb_bytes * n_matrices > sc.afrag_bytes)
+        throw std::runtime_error("exl3 gemv: matrices x size_k x ceil(size_m / 4) exceed the activation area of the scratch");
+    const long long units = (long long) total_bg * kblocks;
+    int grid = int(std::min<long long>(std::min<long long>(sms, units), (long long) total_bg * 16));
+    const size_t per_cta = size_t(2) * (size_t(size_m) * bu * 128 + 32) * sizeof(float);
+    if (size_t(grid) * per_cta > sc.slab_bytes) grid = int(sc.slab_bytes / per_cta);
+    if (grid < 1) throw std::runtime_error("exl3 gemv: split-K scratch is too small for this shape");
+    if (size_t(total_bg) > sc.counter_words) throw std::runtime_error("exl3 gemv: band groups exceed the counters of the scratch");
+    const long long units_per_cta = (units + grid - 1) / grid;
+    const int frows = size_m <= 1 ? 1 : (size_m == 2 ? 2 : 4);
+    const bool fused = nb == 1 && units_per_cta < kblocks && units_per_cta <= fused_max_units(k_bits, frows);
+    const int rot_total = size_m * kblocks;
+    if (!fused)
+        for (int i = 0; i < n_matrices; ++i)
+            launch_pdl(k_rotate_in_i8, dim3(std::min((rot_total + 3) / 4, 4 * sms)), dim3(128), 0, stream, "k_rotate_in_i8 launch",
+                       static_cast<const __half*>(a), args.het_suh[i], args.het_a_had[i],
+                       reinterpret_cast<unsigned char*>(sc.afrag) + size_t(i) * limb_bytes, sc.blocksum + size_t(i) * size_m * kblocks,
+                       size_m, size_k, nb);
+    args.afrag = sc.afrag;
+    args.blocksum = sc.blocksum;
+    args.a = static_cast<const __half*>(a);
+    args.suh = args.het_suh[0];
+    args.a_had = args.het_a_had[0];
+    args.c = c[0];
+    args.svh = args.het_svh[0];
+    args.slabs = sc.slabs;
+    args.counters = sc.counters;
+    args.status = sc.status;
+    args.m = size_m; args.k = size_k; args.n = max_n;
+    args.out_fp32 = out_fp32;
+    args.max_problems = 1; args.n_matrices = n_matrices; args.max_rows = size_m;
+    args.n_stack = n_matrices;
+    const size_t smem = launch_bits(k_bits, nb, fused, trellis, n_matrices, args, grid, stream);
+    return std::string(fused ? "" : "k_rotate_in_i8 + ") + "k_exl3_gemv_i8<" + std::to_string(k_bits) + "," + std::to_string(nb) +
+           (fused ? ",fused" : "") + "," + std::to_string(n_matrices) + " matrices> grid=" + std::to_string(grid) + " block=" +
+           std::to_string(kThreads) + " smem=" + std::to_string(smem);
 }
 
 }  // namespace berth

@@ -154,6 +154,36 @@ extern "C" int berth_exl3_linear_stack(const void* a, const void* trellis_stack,
     });
 }
 
+// Up to four MUL1 matrices of different widths applied to the same rows in one decode launch (q, k and v of an attention
+// block): what berth does with one berth_ops_mgemm call over column slices (crates/berth-kernels/src/ops.rs:257-262), with
+// the pointer lists in HOST memory, so that the library can encode one TMA view per matrix and rotate inside the kernel.
+extern "C" int berth_exl3_linear_multi(const void* a, const void* const* trellis_list, void* const* c_list,
+                                       const void* const* suh_list, void* const* a_had_list, const void* const* svh_list,
+                                       const int* size_n_list, int n_matrices, int size_m, int size_k, int k_bits, int codebook,
+                                       int out_fp32, void* stream)
+{
+    CallState& st = exl3_state();
+    return guarded(st, [&] {
+        if (!a || !trellis_list || !c_list || !suh_list || !a_had_list || !svh_list || !size_n_list)
+            throw std::runtime_error("exl3 linear multi: null pointer");
+        if (n_matrices < 1 || n_matrices > 4) throw std::runtime_error("exl3 linear multi: n_matrices must be in 1..=4");
+        if (size_m < 1 || size_k < 1) throw std::runtime_error("exl3 linear multi: sizes must be positive");
+        for (int i = 0; i < n_matrices; ++i) {
+            if (size_n_list[i] < 1) throw std::runtime_error("exl3 linear multi: sizes must be positive");
+            check_linear_args("exl3 linear multi", a, trellis_list[i], c_list[i], suh_list[i], a_had_list[i], svh_list[i], size_k,
+                              size_n_list[i], k_bits, codebook);
+        }
+        if (codebook != 2 || size_m > kI8MaxRows)
+            throw std::runtime_error("exl3 linear multi: no linked kernel (MUL1 codebook and size_m <= 8 only)");
+        const int device = current_device();
+        const DeviceInfo& info = device_info(device);
+        if (info.major != 10)
+            throw std::runtime_error("exl3 linear multi: no linked kernel for this GPU (library is built for sm_100a only)");
+        st.launch = launch_gemv_i8_multi(a, trellis_list, c_list, suh_list, a_had_list, svh_list, size_n_list, n_matrices, size_m,
+                                         size_k, k_bits, out_fp32, gemv_workspace(device), info.sms, (cudaStream_t) stream);
+    });
+}
+
 // The decode linear with the residual added in its last step: c = residual + linear(a), fp32, size_m <= 32.  What berth
 // does with berth_exl3_linear followed by berth_ops_add_f32 (crates/berth-engine/src/model.rs:976-1022: x = x + mlp(h2)).
 extern "C" int berth_exl3_linear_add(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,

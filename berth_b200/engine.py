@@ -154,11 +154,28 @@ class SlicedMultiLinear:
         self.slices = len(b)
         self.a_had = torch.zeros(len(sources) * max_rows * self.size_k, dtype=torch.float16, device=gpu.device)
         self.carrier = torch.empty(1, dtype=dt, device=gpu.device)
+        # MUL1 sources, few of them: the library's multi-matrix decode launch takes the addresses from host arrays
+        # (one TMA view per matrix, rotation inside the kernel) and is the faster path for the smallest batches.
+        self.multi = None
+        if self.codebook == Codebook.Mul1 and len(sources) <= 4:
+            n = len(sources)
+            row_bytes = self.size_k * 2
+            self.multi = (kernels.pointer_list([s.trellis for s in sources]), kernels.pointer_list(self.outputs),
+                          kernels.pointer_list([s.suh for s in sources]),
+                          kernels.pointer_list([self.a_had.data_ptr() + i * max_rows * row_bytes for i in range(n)]),
+                          kernels.pointer_list([s.svh for s in sources]), kernels.int_list([s.size_n for s in sources]), n)
+
+    MULTI_ROWS = 4   # up to here the multi-matrix launch is used (above, the sliced launch of the fp16-path kernel)
 
     def forward_n(self, gpu: Gpu, rows: int, a: torch.Tensor) -> list:
         """One launch; returns the per-source outputs ``[max_rows][size_n]`` (the first ``rows`` rows are written)."""
         if rows > self.max_rows:
             raise Error(f"SlicedMultiLinear: {rows} rows exceed max_rows = {self.max_rows}")
+        if self.multi is not None and rows <= self.MULTI_ROWS:
+            t, c, suh, ah, svh, sizes, n = self.multi
+            kernels.exl3_linear_multi(a, t, c, suh, ah, svh, sizes, n, rows, self.size_k, self.k_bits, self.codebook, self.out,
+                                      gpu.stream)
+            return self.outputs
         kernels.ops.exl3_mgemm(a, self.b_list, self.carrier, self.suh_list, self.a_had, self.svh_list, rows, self.size_k, self.width,
                                self.k_bits, self.codebook, self.out, 1, self.slices, self.size_n_list, self.c_ptrs,
                                self.n_stride_list, self.had_src_list, len(self.sources), gpu.stream)

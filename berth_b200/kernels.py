@@ -103,6 +103,29 @@ def exl3_linear_stack(a, trellis_stack, c, suh_stack, a_had, svh_stack, n_matric
         raise Error(last_error() or f"exl3 linear stack launch failed ({rc})")
 
 
+def pointer_list(xs):
+    """A host array of device addresses (one per tensor or integer address of ``xs``) for :func:`exl3_linear_multi`."""
+    import ctypes
+    return (ctypes.c_void_p * max(len(xs), 1))(*[_ptr(x) for x in xs])
+
+
+def int_list(xs):
+    """A host array of C ints for :func:`exl3_linear_multi`."""
+    import ctypes
+    return (ctypes.c_int * max(len(xs), 1))(*[int(v) for v in xs])
+
+
+def exl3_linear_multi(a, trellis_list, c_list, suh_list, a_had_list, svh_list, size_n_list, n_matrices: int, size_m: int,
+                      size_k: int, k_bits: int, codebook: Codebook, out: OutDtype, stream=None) -> None:
+    """Up to four MUL1 linears of different widths applied to the same ``size_m <= 8`` rows in one decode launch (q, k and v
+    of an attention block).  The lists are host arrays built with :func:`pointer_list` / :func:`int_list` (one entry per
+    matrix); build them once per layer, not per call."""
+    rc = _lib.lib().berth_exl3_linear_multi(_ptr(a), trellis_list, c_list, suh_list, a_had_list, svh_list, size_n_list, n_matrices,
+                                            size_m, size_k, k_bits, int(codebook), int(out), _stream(stream))
+    if rc != 0:
+        raise Error(last_error() or f"exl3 linear multi launch failed ({rc})")
+
+
 def exl3_linear_argmax(a, trellis, c, suh, a_had, svh, best, size_m: int, size_k: int, size_n: int, k_bits: int,
                        codebook: Codebook, out: OutDtype, stream=None) -> None:
     """:func:`exl3_linear` (``size_m <= 32``) that also leaves, in the device array ``best`` (``size_m`` 64-bit keys),

@@ -145,6 +145,19 @@ int berth_exl3_linear_stack(const void* a, const void* trellis_stack, void* c, c
                             const void* svh_stack, int n_matrices, int size_m, int size_k, int size_n, int k_bits,
                             int codebook, int out_fp32, void* stream);
 
+/* Up to four MUL1 linears of different widths (same size_k, k_bits) applied to the same size_m <= 8 rows in ONE decode
+ * launch: the q, k and v projections of an attention block, which berth runs as one berth_ops_mgemm call over column
+ * slices (crates/berth-kernels/src/ops.rs:257-262, crates/berth-engine/src/model.rs q/k/v of the attention layers).
+ * The five pointer lists and size_n_list are HOST arrays of n_matrices entries (device pointers of each matrix's
+ * trellis, output [size_m][size_n_i], suh, a_had [size_m][size_k] and svh): with the addresses known on the host the
+ * library encodes one TMA view per matrix and rotates inside the kernel, which the device-resident lists of
+ * berth_ops_mgemm do not allow.  Per matrix the result is what berth_exl3_linear gives for one row of a MUL1 matrix
+ * (same kernel).  Other codebooks or more rows fail closed ("no linked kernel").  No counterpart in berth. */
+int berth_exl3_linear_multi(const void* a, const void* const* trellis_list, void* const* c_list,
+                            const void* const* suh_list, void* const* a_had_list, const void* const* svh_list,
+                            const int* size_n_list, int n_matrices, int size_m, int size_k, int k_bits, int codebook,
+                            int out_fp32, void* stream);
+
 /* ------------------------------------------------------------------ prefill linear (m > 1)
  * Replaces berth_prefill_exl3_linear (crates/berth-kernels/src/prefill_lin.rs:37-52,
  * crates/berth-kernels/csrc/prefill_lin/linear.cu:232-381).  w_scratch (fp16,

@@ -299,13 +299,15 @@ def test_prefill_gemm_matches_decode_kernel():
 
 
 # ---------------------------------------------------------------- sliced multi-linear (berth_ops_mgemm)
-@pytest.mark.parametrize("m,out_fp32", [(1, True), (1, False), (5, False), (20, True)])
-def test_sliced_multi_linear_vs_oracle(oracle, m, out_fp32):
+@pytest.mark.parametrize("cb", [2, 0])
+@pytest.mark.parametrize("m,out_fp32", [(1, True), (1, False), (3, False), (5, False), (20, True)])
+def test_sliced_multi_linear_vs_oracle(oracle, m, out_fp32, cb):
     """Three linears sharing one input in one launch (the q / k / v bundle of berth's attention layers,
     crates/berth-kernels/tests/ops.rs:250-345, at reduced sizes): every source's output against the fp64
-    evaluation of that source alone, and the rotated input slab of every source bit for bit."""
+    evaluation of that source alone, and the rotated input slab of every source bit for bit.  MUL1 sources run on the
+    integer-path multi-matrix launch up to four rows, everything else as column slices through berth_ops_mgemm."""
     from berth_b200.engine import Exl3Linear, Gpu, SlicedMultiLinear
-    K, bits, cb = 512, 4, 2
+    K, bits = 512, 4
     widths = (1536, 512, 256)
     gpu = Gpu(torch.cuda.current_device())
     ws = [synth.linear_weights(1234, f"mg{i}", K, n, bits) for i, n in enumerate(widths)]
@@ -317,7 +319,10 @@ def test_sliced_multi_linear_vs_oracle(oracle, m, out_fp32):
     outs = ml.forward_n(gpu, m, dev(x))
     torch.cuda.synchronize()
     assert kernels.device_status(torch.cuda.current_device()) == 0
-    assert "sliced" in kernels.ops.last_launch()
+    if cb == 2 and m <= SlicedMultiLinear.MULTI_ROWS:
+        assert "3 matrices" in kernels.last_launch()
+    else:
+        assert "sliced" in kernels.ops.last_launch()
     ah = host_u16(ml.a_had).reshape(len(ws), m, K)
     for i, w in enumerate(ws):
         y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, widths[i], bits, cb)
@@ -659,3 +664,58 @@ def test_linear_add_equals_linear_then_add(oracle, m, K, N, bits, cb):
     y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, N, bits, cb)
     mx, mean = rel_errors(fused.cpu().numpy() - r, y64)
     assert mx <= MAX_REL and mean <= MEAN_REL
+
+
+# ---------------------------------------------------------------- several MUL1 matrices of different widths in one launch
+
+@pytest.mark.parametrize("m", [1, 2, 4, 7])
+@pytest.mark.parametrize("K,Ns,bits,out_fp32", [(512, [384, 128, 128], 4, False), (5120, [6144, 1024, 1024], 4, False),
+                                                (1024, [256, 2048], 5, True), (640, [128], 3, True),
+                                                (2048, [1024, 128, 640, 384], 6, False)])
+def test_linear_multi_vs_oracle(oracle, m, K, Ns, bits, out_fp32):
+    """berth_exl3_linear_multi (q, k and v of an attention block as one integer-path launch): every matrix against the
+    fp64 oracle, its rotated rows bit for bit, identical bits on a second run, clean status."""
+    ws = [synth.linear_weights(1234, f"multi{K}.{i}.{n}.{bits}", K, n, bits, fan_in_gain=True) for i, n in enumerate(Ns)]
+    x = synth.activations(1234, f"multi.x{m}.{K}", m, K)
+    xd = dev(x)
+    dt = torch.float32 if out_fp32 else torch.float16
+    td = [dev(w["trellis"]) for w in ws]
+    sd = [dev(w["suh"]) for w in ws]
+    vd = [dev(w["svh"]) for w in ws]
+    runs = []
+    for _ in range(2):
+        cs = [torch.full((m, n), float("nan"), dtype=dt, device="cuda") for n in Ns]
+        ahs = [torch.zeros((m, K), dtype=torch.float16, device="cuda") for _ in Ns]
+        kernels.exl3_linear_multi(xd, kernels.pointer_list(td), kernels.pointer_list(cs), kernels.pointer_list(sd),
+                                  kernels.pointer_list(ahs), kernels.pointer_list(vd), kernels.int_list(Ns), len(Ns), m, K, bits,
+                                  Codebook(2), OutDtype.F32 if out_fp32 else OutDtype.F16)
+        torch.cuda.synchronize()
+        runs.append(([c.cpu().numpy() for c in cs], [host_u16(ah) for ah in ahs]))
+    assert "k_exl3_gemv_i8" in kernels.last_launch() and f"{len(Ns)} matrices" in kernels.last_launch()
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+    view = np.uint32 if out_fp32 else np.uint16
+    for i, (w, n) in enumerate(zip(ws, Ns)):
+        c, ah = runs[0][0][i], runs[0][1][i]
+        y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, n, bits, 2)
+        assert_close(c, y64, f"matrix {i}")
+        assert (ah.reshape(m, K) == oracle.had_r_128(x, w["suh"], True).view(np.uint16)).all()
+        assert (runs[1][0][i].view(view) == c.view(view)).all()
+
+
+def test_linear_multi_fails_closed():
+    K, Ns, bits = 256, [128, 128], 4
+    ws = [synth.linear_weights(1234, f"multi.fc{i}", K, n, bits) for i, n in enumerate(Ns)]
+    x = dev(synth.activations(1234, "multi.fc.x", 1, K))
+    td, sd, vd = [dev(w["trellis"]) for w in ws], [dev(w["suh"]) for w in ws], [dev(w["svh"]) for w in ws]
+    cs = [torch.zeros((1, n), dtype=torch.float16, device="cuda") for n in Ns]
+    ahs = [torch.zeros((1, K), dtype=torch.float16, device="cuda") for _ in Ns]
+    lists = lambda k: (kernels.pointer_list(td * k), kernels.pointer_list(cs * k), kernels.pointer_list(sd * k),
+                       kernels.pointer_list(ahs * k), kernels.pointer_list(vd * k), kernels.int_list(Ns * k))
+    with pytest.raises(kernels.Error, match="no linked kernel"):
+        kernels.exl3_linear_multi(x, *lists(1), 2, 1, K, bits, Codebook(0), OutDtype.F16)
+    with pytest.raises(kernels.Error, match="no linked kernel"):
+        kernels.exl3_linear_multi(x, *lists(1), 2, 9, K, bits, Codebook(2), OutDtype.F16)
+    with pytest.raises(kernels.Error, match="n_matrices"):
+        kernels.exl3_linear_multi(x, *lists(3), 6, 1, K, bits, Codebook(2), OutDtype.F16)
+    with pytest.raises(kernels.Error, match="multiple of 128"):
+        kernels.exl3_linear_multi(x, *lists(1)[:5], kernels.int_list([128, 64]), 2, 1, K, bits, Codebook(2), OutDtype.F16)
