@@ -538,12 +538,19 @@ def bench_c4(rank: int, world: int, layers: int = 40, total_tokens: int = 8448, 
     n_local, T = E // world, total_tokens // world
     bias = synth.zipf_router_bias(1234, "c4.bias", E, s=1.1, strength=1.0)
     # Static expert placement for a known skew: experts are renumbered so that the contiguous blocks of the ranks hold
-    # them dealt out by popularity (the i-th most popular expert goes to rank i % world): a relabelling of the router's
-    # columns, which leaves the layer's function unchanged.
-    by_pop = np.argsort(-bias, kind="stable")
-    place = np.empty(E, np.int64)
-    for i, e in enumerate(by_pop):
-        place[(i % world) * n_local + i // world] = e
+    # equal loads -- a relabelling of the router's columns, which leaves the layer's function unchanged.  The load of an
+    # expert is taken from a calibration count (the router of layer 0 on the first rank's tokens, evaluated with numpy on
+    # every rank alike); experts go, most loaded first, to the least loaded rank that still has a free place.
+    x_cal = synth.activations(1234, f"c4.x.r0.of{world}", T, H).astype(np.float32)
+    logit_cal = x_cal @ synth.router_weight(1234, "c4.0.gate.weight", H, E).astype(np.float32) + bias[None, :]
+    cal = np.bincount(np.argsort(-logit_cal, axis=1, kind="stable")[:, :K].ravel(), minlength=E)
+    by_load = np.argsort(-cal, kind="stable")
+    load, held = np.zeros(world, np.int64), [[] for _ in range(world)]
+    for e in by_load:
+        r = min((q for q in range(world) if len(held[q]) < n_local), key=lambda q: (load[q], q))
+        held[r].append(int(e))
+        load[r] += int(cal[e])
+    place = np.array([e for r in range(world) for e in held[r]], np.int64)
     bias = np.ascontiguousarray(bias[place])
     mk = []
     for l in range(layers):
@@ -554,7 +561,7 @@ def bench_c4(rank: int, world: int, layers: int = 40, total_tokens: int = 8448, 
     x = torch.from_numpy(synth.activations(1234, f"c4.x.r{rank}.of{world}", T, H)).to(dev)
     rec = {"workload": "c4_40_layer_moe_stack_zipf", "layers": layers, "total_tokens": T * world, "tokens_per_rank": T,
            "router_bias": "ln(rank^-1.1) over a seeded rank order, strength 1.0", "expert_weights": "generated on the device, per layer",
-           "placement": "experts dealt to the ranks by popularity (i-th most popular -> rank i % world)"}
+           "placement": "greedy by calibrated load: most loaded expert first, to the least loaded rank with a free place"}
     if world == 1:
         lays = [moe.MoeLayer(dev, w, 1) for w in mk]
         lays[0]._alloc(T)
@@ -608,9 +615,13 @@ def bench_c4(rank: int, world: int, layers: int = 40, total_tokens: int = 8448, 
         rec["rows_per_rank"] = [int(v) for v in per_rank]
         rec["rows_per_rank_max_over_mean"] = float(per_rank.max() / max(per_rank.mean(), 1.0))
         # phases of one layer (CUDA events inside forward), max over ranks
+        # (ranks aligned first, three layers, the last one counts: a rank that enters late makes the others wait in "send")
+        torch.cuda.synchronize()
+        dist.barrier()
         layer.profile = True
-        stages.layer = mls[-1]
-        layer.forward(x)
+        for ml in mls[-3:]:
+            stages.layer = ml
+            layer.forward(x)
         torch.cuda.synchronize()
         ph = layer.phase_ms()
         layer.profile = False
@@ -645,10 +656,10 @@ def bench_c4(rank: int, world: int, layers: int = 40, total_tokens: int = 8448, 
         send, exps, comb, t_route, t_exp, t_comb = [float(q) * 1e3 for q in v]
         rec["phases_us_max_over_ranks"] = {"send": send, "experts": exps, "combine": comb}
         rec["compute_alone_us_max_over_ranks"] = {"route_and_sort": t_route, "expert_kernels_on_received_rows": t_exp, "combine": t_comb}
-        rec["exposed_exchange_us"] = max(0.0, (send - t_route) + (exps - t_exp))
-        rec["exposed_exchange_note"] = ("send phase minus routing+sort alone, plus experts phase minus the expert kernels alone on the "
-                                        "received rows: count publication, three flag barriers (waiting for the busiest rank included), "
-                                        "peer stores of rows and outputs")
+        rec["exposed_exchange_us"] = max(0.0, rec["us_per_layer"] - (t_route + t_exp + t_comb))
+        rec["exposed_exchange_note"] = ("time per layer of the timed stack minus the layer's own kernels run alone on the rows this rank "
+                                        "received (routing+sort, expert kernels, combine; max over ranks): count publication, three flag "
+                                        "barriers (waiting for the busiest rank included), peer stores of rows and outputs")
     return rec
 
 

@@ -988,8 +988,8 @@ __global__ void __launch_bounds__(128) k_sk_finish(const SplitKArgs p)
     const long long U = (long long) bands * kstages;
     const int c_lo = sk_range_owner((long long) band * kstages, U, G);
     const int c_hi = sk_range_owner((long long) (band + 1) * kstages - 1, U, G);
+    pdl_wait();   // (before any return: a grid must not complete before its predecessor, its successor relies on that)
     if (c_lo == c_hi || row >= p.m) return;
-    pdl_wait();
     auto slab_of = [&](int cc) {
         // CTA cc's slab of this band: slot 0 when the band is where its range begins
         const int first_band = int(sk_range_begin(cc, U, G) / kstages);

@@ -48,7 +48,12 @@ extern "C" {
 /* ------------------------------------------------------------------ decode linear (m >= 1)
  * Replaces berth_exl3_linear (crates/berth-kernels/src/ffi.rs:7-21,
  * crates/berth-kernels/csrc/linear.cu:209-286,362-394): c = H(H(a*suh) . W(trellis)) * svh.
- * Serves every size_m: the fused decode GEMV up to 32 rows, the tcgen05 tensor-core GEMM above. */
+ * Serves every size_m: one row of a MUL1 matrix on the integer-path decode kernel (codebook byte sums in tensor
+ * memory, tcgen05.mma kind::i8, rotation and finishing inside the kernel); up to 16 rows (and up to 32 of a small
+ * matrix) the fused decode GEMV; 17..32 rows of a large matrix the persistent split-K tensor-core kernel; above, the
+ * tiled tcgen05 tensor-core GEMM.  berth_exl3_last_launch names the kernels that ran.  Programmatic-launch contract:
+ * the kernels start fetching `trellis` while the kernel before them on the stream may still be running, so the
+ * weights must be final before that kernel starts; every other tensor is touched only after the predecessor ended. */
 int berth_exl3_linear(const void* a, const void* trellis, void* c, const void* suh, void* a_had,
                       const void* svh, int size_m, int size_k, int size_n, int k_bits,
                       int codebook, int out_fp32, void* stream);
