@@ -79,6 +79,7 @@ struct GemmArgs {
     const GemvProblem* problems;   // grouped launch: one entry per (matrix, chunk of <= nsub_max*128 rows); else null
     const int* n_problems;
     int max_problems, n_matrices;
+    int epi2;   // grouped launch with 128-row problems and a short K: two epilogue teams and three decode groups (see the kernel)
 };
 
 // ---------------------------------------------------------------- PTX helpers
@@ -541,7 +542,14 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
     // With short stages (a 32-row problem's stage is 0.4 us of decode) three stages in flight did not cover an L2 miss.
     constexpr int kMaxSA = 9;
     const int a_stage = p.nsub_max * A_SUB_BYTES;
-    const int SAg = (SA * A_STAGE_BYTES) / a_stage;
+    // With a short K a 128-row item's main loop (K / 64 stages of decode) is shorter than its epilogue (four passes of
+    // transposition, Hadamard and stores by one team of four warps), and the decode warps wait for accumulators.  Then the
+    // fourth decode group works as a second epilogue team instead: team e drains accumulator buffer e (items e, e+2, ...),
+    // three groups decode into three weight stages.  Its transposition buffer lies behind seven activation stages.
+    const bool epi2 = p.epi2 != 0 && p.nsub_max == 1;
+    const int G = epi2 ? 3 : 4;                        // decode groups = weight stages in use
+    const int SAg = epi2 ? 7 : (SA * A_STAGE_BYTES) / a_stage;
+    float* xch1 = reinterpret_cast<float*>(a_ring + 7 * A_SUB_BYTES);
     const uint32_t full_a = smem_u32(bars), empty_a = full_a + 8 * kMaxSA;
     const uint32_t full_w = empty_a + 8 * kMaxSA, empty_w = full_w + 8 * SW;
     const uint32_t full_t = empty_w + 8 * SW, empty_t = full_t + 8 * ST;
@@ -655,44 +663,50 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_grouped(const __gr
                 }
                 __syncwarp();
                 if (++sa == SAg) { sa = 0; pa ^= 1; }
-                if (++sw == SW) { sw = 0; pw ^= 1; }
+                if (++sw == G) { sw = 0; pw ^= 1; }
             }
             if (elect_one()) tc_commit(acc_full + 8 * buf);
             __syncwarp();
         }
-    } else if (warp >= kDecodeWarp0) {
+    } else if (warp >= kDecodeWarp0 && !(epi2 && warp >= kDecodeWarp0 + 12)) {
         // ------------------------------------------------------------ decode warps
-        const int g = (warp - kDecodeWarp0) >> 2, quarter = warp & 3;   // group g: stages g, g+4, ... into weight stage g
+        const int g = (warp - kDecodeWarp0) >> 2, quarter = warp & 3;   // group g: stages g, g+G, ... into weight stage g
         static_assert(SW == 4 && ST >= 4, "one weight stage per decode group");
         int st = g, pt = 0, pw = 0;
         const int total = my_items * kstages;
-        for (int cnt = g; cnt < total; cnt += 4) {
+        for (int cnt = g; cnt < total; cnt += G) {
             mbar_wait_parked(full_t + 8 * st, pt, p.status, 40);
-            decode_stage<BITS, CB>(t_ring + st * T_STAGE_BYTES, tmem_w + g * 32, quarter, lane, cnt >= SW, empty_w + 8 * g, pw ^ 1, p.status);
+            decode_stage<BITS, CB>(t_ring + st * T_STAGE_BYTES, tmem_w + g * 32, quarter, lane, cnt >= G, empty_w + 8 * g, pw ^ 1, p.status);
             if (lane == 0) {
                 mbar_arrive(full_w + 8 * g);
                 mbar_arrive(empty_t + 8 * st);
             }
-            st += 4;
+            st += G;
             if (st >= ST) { st -= ST; pt ^= 1; }
             pw ^= 1;
         }
-    } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + 4) {
-        // ------------------------------------------------------------ epilogue warps
+    } else if (warp >= kEpiWarp0) {
+        // ------------------------------------------------------------ epilogue warps: team 0 (warps 4..7), and with two
+        // teams the last four warps as team 1
+        const int team = warp >= kDecodeWarp0 ? 1 : 0;
+        const int step = epi2 ? 2 : 1;
+        float* xc = team ? xch1 : xch;
+        float* svs = team ? xch1 + kXchFloats : svh_s;
         const int quarter = warp & 3;
         const int n = quarter * 32 + lane;
-        for (int it = 0; it < my_items; ++it) {
+        int turn = 0;
+        for (int it = team; it < my_items; it += step, turn ^= 1) {
             int band; GemvProblem pr;
             item_at(it, band, pr);
-            float* sv = svh_s + (it & 1) * 128;   // (the other buffer may still be read by a slower warp of the previous item)
+            float* sv = svs + turn * 128;   // (the other buffer may still be read by a slower warp of the team's previous item)
             sv[n] = __half2float(p.svh[size_t(pr.z) * p.n + band * BN + n]);
             const int buf = it % nbuf;
             mbar_wait_parked(acc_full + 8 * buf, (it / nbuf) & 1, p.status, 200);
             tc_fence_after();
-            team_sync(0);   // the scales are in place
+            team_sync(team);   // the scales are in place
             const int rows_pad = (pr.rows + 15) & ~15;
             for (int c0 = 0; c0 < rows_pad; c0 += 32)
-                epilogue_pass(tmem + buf * chunk + (uint32_t(quarter * 32) << 16) + c0, xch, sv, 0, quarter, lane, p.c, p.out_fp32, p.n,
+                epilogue_pass(tmem + buf * chunk + (uint32_t(quarter * 32) << 16) + c0, xc, sv, team, quarter, lane, p.c, p.out_fp32, p.n,
                               band * BN, pr.row0 + c0, pr.row0 + pr.rows);
             tc_fence_before();
             __syncwarp();
@@ -1309,6 +1323,7 @@ std::string launch_gemm_tc(const void* a, const void* trellis, void* c, const vo
     args.m = size_m; args.k = size_k; args.n = size_n;
     args.out_fp32 = out_fp32;
     args.problems = nullptr; args.n_problems = nullptr; args.max_problems = 0; args.n_matrices = 1;
+    args.epi2 = 0;
     // Rows per CTA: 128, 256 or 384.  More rows per decoded weight keep the kernel MMA bound, fewer rows give
     // more CTAs; pick the count with the least (waves x time of one CTA), the latter from the measured stage
     // and epilogue times of the three tile heights (ns per 64-deep stage; ns per epilogue; 1.2 us to start).
@@ -1398,6 +1413,8 @@ std::string launch_gemm_tc_grouped_rotated(const void* xr_had, const void* trell
     args.out_fp32 = out_fp32;
     args.nsub_max = nsub;
     args.problems = problems; args.n_problems = n_problems; args.max_problems = max_problems; args.n_matrices = n_matrices;
+    // a main loop of at most sixteen stages is shorter than the epilogue of a 128-row item
+    args.epi2 = (nsub == 1 && size_k <= 1024) ? 1 : 0;
     launch_tc_bits(k_bits, codebook, xr_had, trellis_stack, args, stream);
     return "k_exl3_gemm_tc_grouped<" + std::to_string(k_bits) + "," + std::to_string(codebook) + "> persistent items<=" +
            std::to_string(size_n / BN) + "x" + std::to_string(max_problems) + " block=" + std::to_string(kThreads) + " tile=" +

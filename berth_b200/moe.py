@@ -129,6 +129,15 @@ class MoeLayer:
 # data-parallel (each rank routes its own tokens), experts are split in contiguous blocks,
 # and the only exchange steps are two all-to-alls: routed rows out, expert outputs back.
 
+SHORT_K = 2048
+
+
+def cap_rows_hint(hint: int, hidden: int, inter: int) -> int:
+    """With short inner dimensions the expert stage keeps 128-row problems however many rows an expert has (the library's
+    own layer does the same): a 128-row item's epilogue runs under the next item's main loop, a taller item's does not."""
+    return 128 if hint > 128 and min(hidden, inter) <= SHORT_K else hint
+
+
 class GpuStages:
     """The compute stages of the layer on one GPU, through the C ABI.  ``weights`` holds this
     rank's expert stacks (``n_experts`` = number of LOCAL experts), the full router and the shared
@@ -141,6 +150,7 @@ class GpuStages:
         self.d = self.layer.dims
         self.E = n_experts_total
         self.max_rows, self.mrpe = max_rows, max_rows_per_expert
+        self.force_hint = None    # tests: a fixed rows-per-expert figure (problem height) instead of the derived one
         l = _lib.lib()
         # one scratch for the send-side sort over all experts, one for the local experts; the expert stage picks
         # its row chunk per call (see rows_hint), so the scratch is sized for the largest of the possible plans
@@ -175,7 +185,9 @@ class GpuStages:
         """Rows-per-expert figure the expert stage sizes its problems for: twice the mean, at least 1, at most
         the construction-time bound.  sort(for_experts=True) and experts() of one layer call must agree on it,
         which they do because both see the same row count."""
-        return max(1, min(self.mrpe, -(-2 * n_rows // max(n_local, 1))))
+        if self.force_hint is not None:
+            return self.force_hint
+        return cap_rows_hint(max(1, min(self.mrpe, -(-2 * n_rows // max(n_local, 1)))), self.d["hidden"], self.d["inter"])
 
     def sort(self, keys, e0: int, n_local: int, for_experts: bool = False):
         """Stable sort by expert.  for_experts=True also leaves the problem table of the following
@@ -480,7 +492,7 @@ class P2pMoeLayer:
         stacked = st.shared_is_stacked() and T > 0
         ysh = torch.empty((T, H), dtype=torch.float16, device=dev) if stacked else None
         # rows per local expert to size the problems for: twice the mean if every rank holds as many tokens as this one
-        hint = max(1, min(1024, -(-2 * max(T, 1) * self.world * k // self.E)))
+        hint = cap_rows_hint(max(1, min(1024, -(-2 * max(T, 1) * self.world * k // self.E))), H, st.d["inter"])
         st._check(l.berth_moe_p2p_experts(C.byref(st.layer.c), p(x), T, None if ysh is None else ysh.data_ptr(), self.rank, self.world,
                                           self.epoch, self.E, k, T, self.cnt_ptrs, self.flag_ptrs, self.recv_ptrs, self.ret_ptrs,
                                           self.max_rows, max(self.max_send, 1), hint, self.send_ws.data_ptr(), self.exp_ws.data_ptr(),

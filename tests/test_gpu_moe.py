@@ -160,23 +160,45 @@ def test_moe_layer_config3_1024_tokens_sampled_vs_oracle(oracle):
     assert np.abs(out[sample] - exp_out).max() <= 4e-3 * np.sqrt((y64 ** 2).mean())
 
 
-@pytest.mark.parametrize("T,nsub", [(400, 2), (600, 3), (1000, 3)])
+@pytest.mark.parametrize("T", [400, 1000])
 @pytest.mark.parametrize("fuse_shared,pair", [(True, True), (False, False)])
-def test_moe_layer_wide_grouped_tiles_vs_oracle(oracle, T, nsub, fuse_shared, pair):
-    """Few experts and many rows each, so that the expert stage cuts 256- and 384-row problems (two and three
-    128-row sub-tiles of the grouped tensor-core kernel): every token against the checker, with the shared expert
-    stacked behind the experts and the paired gate/up table, and without either."""
+def test_moe_layer_many_rows_per_expert_vs_oracle(oracle, T, fuse_shared, pair):
+    """Few experts and many rows each (100 to 250 rows per expert on average, far more on the popular ones): with
+    inner dimensions this short the layer keeps 128-row problems on the grouped tensor-core kernel (two epilogue
+    teams for the down projection); every token against the checker, with the shared expert stacked behind the experts
+    and the paired gate/up table, and without either."""
     H, I, E, k, bits, cb = 256, 128, 32, 8, 4, 2
     wts = synth.moe_layer_weights(1234, "wide", H, I, E, k, bits, cb, shared_inter=128)
     x = synth.activations(1234, f"wide.x{T}", T, H)
     out, idx, w = _run_layer(wts, x, fuse_shared=fuse_shared, pair_gate_up=pair)
-    assert "k_exl3_gemm_tc_grouped" in moe.last_launch()
-    assert min(3, (min(T, (2 * T * k + E - 1) // E) + 127) // 128) == nsub      # the plan berth_moe_layer derives
+    assert "k_exl3_gemm_tc_grouped" in moe.last_launch() and "tile=128x" in moe.last_launch()
     exp_out, exp_idx, exp_w = oracle.moe_layer(wts, x)
     assert (idx == exp_idx).all() and np.abs(w - exp_w).max() <= 1e-6
     y64 = oracle.moe_layer_f64(wts, x, exp_idx, exp_w)
     assert_close(out, y64, f"T={T}")
     assert np.abs(out - exp_out).max() <= 4e-3 * np.sqrt((y64 ** 2).mean())
+
+
+@pytest.mark.parametrize("T,hint", [(400, 256), (600, 384), (1000, 384), (1000, 128)])
+def test_expert_stage_wide_grouped_tiles_vs_oracle(oracle, T, hint):
+    """The expert stage with 256- and 384-row problems (two and three 128-row sub-tiles of the grouped tensor-core
+    kernel, what a layer with long inner dimensions plans): the staged path (sort / gather / experts / gather / combine
+    through the C ABI) with the problem height fixed, every token against the checker."""
+    H, I, E, k, bits, cb = 256, 128, 32, 8, 4, 2
+    wts = synth.moe_layer_weights(1234, "wide", H, I, E, k, bits, cb, shared_inter=128)
+    x = synth.activations(1234, f"wide.x{T}", T, H)
+    stages = moe.GpuStages(torch.device("cuda", torch.cuda.current_device()), wts, E, max_rows=T * k, max_rows_per_expert=T)
+    stages.force_hint = hint
+    layer = moe.EpMoeLayer.__new__(moe.EpMoeLayer)
+    layer.dist, layer.group, layer.stages = _OneRankDist, None, stages
+    layer.world, layer.rank, layer.E, layer.k, layer.n_local, layer.e0, layer.last_stats = 1, 0, E, k, E, 0, {}
+    out, idx, w = layer.forward(dev(x))
+    torch.cuda.synchronize()
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+    exp_out, exp_idx, exp_w = oracle.moe_layer(wts, x)
+    assert (idx.cpu().numpy() == exp_idx).all()
+    y64 = oracle.moe_layer_f64(wts, x, exp_idx, exp_w)
+    assert_close(out.cpu().numpy(), y64, f"T={T} hint={hint}")
 
 
 def test_moe_layer_skewed_routing_property():
