@@ -43,6 +43,7 @@ SIGNATURES = {
     "berth_exl3_linear": (_i, [_vp] * 6 + [_i] * 6 + [_vp]),
     "berth_exl3_linear_static_scratch": (_i, [_vp] * 6 + [_i] * 6 + [_vp]),
     "berth_exl3_linear_argmax": (_i, [_vp] * 7 + [_i] * 6 + [_vp]),
+    "berth_exl3_linear_sample": (_i, [_vp] * 7 + [_i] * 6 + [_f, C.c_uint, _i, _vp]),
     "berth_exl3_linear_add": (_i, [_vp] * 7 + [_i] * 5 + [_vp]),
     "berth_exl3_linear_stack": (_i, [_vp] * 6 + [_i] * 7 + [_vp]),
     "berth_exl3_linear_multi": (_i, [_vp] * 7 + [_i] * 6 + [_vp]),

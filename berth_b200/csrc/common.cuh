@@ -194,10 +194,18 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
                                 int max_rows, int tg, uint32_t* afrag, float* blocksum, int size_k, int size_n, int k_bits,
                                 int codebook, int out_fp32, const GemvScratch& scratch, int sms, cudaStream_t stream);
 
+// How the arg-max keys of a decode launch are scored: the stored output itself (greedy), or
+// output * inv_temp + Gumbel noise drawn from a counter hash of (random, row, column) -- one draw of the softmax
+// distribution at temperature 1 / inv_temp (the Gumbel-max trick).
+struct SampleArgs {
+    float inv_temp = 1.0f;
+    unsigned random = 0;
+    int gumbel = 0;
+};
 std::string launch_gemv(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32,
                         const GemvScratch& scratch, int sms, cudaStream_t stream, unsigned long long* argmax = nullptr,
-                        const float* residual = nullptr);
+                        const float* residual = nullptr, const SampleArgs& sample = SampleArgs{});
 
 // The same linear for the MUL1 codebook on the integer tensor path (gemv_i8.cu), up to kI8MaxRows rows; launch_gemv
 // forwards one to four rows to it (above, the limb tiles of the rows cost more L2 traffic than the fp16 path's
@@ -205,7 +213,8 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
 constexpr int kI8MaxRows = 8;
 std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                            int size_m, int size_k, int size_n, int k_bits, int out_fp32, const GemvScratch& scratch, int sms,
-                           cudaStream_t stream, unsigned long long* argmax, int n_stack = 1, const float* residual = nullptr);
+                           cudaStream_t stream, unsigned long long* argmax, int n_stack = 1, const float* residual = nullptr,
+                           const SampleArgs& sample = SampleArgs{});
 
 // The integer-path decode kernel over up to four MUL1 matrices of different widths applied to the same rows (host arrays
 // of device pointers and widths); same contract as launch_gemv per matrix.

@@ -354,7 +354,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
                             if (band < bands) {   // ragged last band group
                                 float4 t = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
                                 float v[4] = {t.x, t.y, t.z, t.w};
-                                finish_band<CB == 2 ? 1 : 0>(v, sxr[r], lane, svr[b], band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual);
+                                finish_band<CB == 2 ? 1 : 0>(v, sxr[r], lane, svr[b], band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual, p.sample);
                             }
                         }
                     }
@@ -427,9 +427,9 @@ __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
             }
         }
     }
-    if (p.mul1 == 2) finish_band<2>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual);
-    else if (p.mul1) finish_band<1>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual);
-    else finish_band<0>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual);
+    if (p.mul1 == 2) finish_band<2>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual, p.sample);
+    else if (p.mul1) finish_band<1>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual, p.sample);
+    else finish_band<0>(v, sx, lane, sr, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual, p.sample);
 }
 
 // ---------------------------------------------------------------- rotation of the activations
@@ -639,7 +639,7 @@ void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int mul1, 
 {
     if (main_grid < 2) return;
     FinishArgs f;
-    f.slabs = a.slabs; f.blocksum = a.blocksum; f.c = a.c; f.argmax = a.argmax; f.residual = a.residual; f.svh = a.svh;
+    f.slabs = a.slabs; f.blocksum = a.blocksum; f.c = a.c; f.argmax = a.argmax; f.sample = a.sample; f.residual = a.residual; f.svh = a.svh;
     f.problems = a.problems; f.n_problems = a.n_problems;
     f.max_problems = a.max_problems; f.n_matrices = a.n_matrices; f.max_rows = a.max_rows;
     f.m = a.m; f.k = a.k; f.n = a.n; f.out_fp32 = a.out_fp32;
@@ -656,7 +656,8 @@ void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int mul1, 
 // per-device workspace or the fixed in-image array of the allocation-free entry point.
 std::string launch_gemv(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32,
-                        const GemvScratch& sc, int sms, cudaStream_t stream, unsigned long long* argmax, const float* residual)
+                        const GemvScratch& sc, int sms, cudaStream_t stream, unsigned long long* argmax, const float* residual,
+                        const SampleArgs& sample)
 {
     if (residual && !out_fp32) throw std::runtime_error("exl3 linear: the residual is added to fp32 outputs only");
     if (size_m > 32) throw std::runtime_error("exl3 gemv: size_m must be <= 32");
@@ -666,7 +667,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     // MUL1, one row, every CTA's units within the limb area of the in-kernel rotation: integer tensor path with the
     // weights in tensor memory (measured a few percent ahead of this kernel there, behind it elsewhere)
     if (codebook == 2 && size_m == 1 && gemv_i8_rotates_in_kernel(size_m, size_k, size_n, k_bits, sms))
-        return launch_gemv_i8(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, out_fp32, sc, sms, stream, argmax, 1, residual);
+        return launch_gemv_i8(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, out_fp32, sc, sms, stream, argmax, 1, residual, sample);
     const int tg = size_m <= 8 ? 1 : (size_m <= 16 ? 2 : 4);
     const int bu = k_bits <= 4 ? 2 : 1;   // bands per unit, as Geo<BITS, TG>::BU
     const int bands = size_n / 128, kblocks = size_k / 128, bgroups = (bands + bu - 1) / bu;
@@ -704,6 +705,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     args.a_had = static_cast<__half*>(a_had);
     args.c = c;
     args.argmax = argmax;
+    args.sample = sample;
     args.residual = residual;
     args.svh = static_cast<const __half*>(svh);
     args.slabs = sc.slabs;

@@ -29,6 +29,7 @@ struct GemvArgs {
     __half* a_had;
     void* c;                  // output rows [rows][n]
     unsigned long long* argmax;   // dense launch only, may be null: per row the key of its largest output (finish_band)
+    SampleArgs sample;            // how those keys are scored
     const float* residual;        // dense launch with fp32 output only, may be null: rows [m][n] added to the output (may be c itself)
     const __half* svh;        // [n], or the stack [experts][n] when grouped
     const GemvProblem* problems;   // grouped launch: one entry per (expert, chunk of <= 8*TG rows); else null
@@ -234,13 +235,42 @@ __device__ __forceinline__ float row_sum(const float* bsum, int kblocks, int lan
 // band*128 + 4*lane ..).  MUL1: w = S*h + B per weight  =>  sum_k x_k w_k = S*acc + B*sum_k x_k.
 // MUL1 = 1: the accumulator holds sum x*(1024 + u) (fp16 tensor path); 2: it holds sum x*u (integer tensor path),
 // so the constant term is (1024 S + B) * sum x.
+// Natural logarithm of a positive normal float from exact steps only (bit tricks, IEEE add / multiply / divide, fused
+// multiply-adds in a fixed order), so that the CPU checker reproduces it bit for bit: x = 2^e * m with m in
+// (sqrt(1/2), sqrt(2)], t = (m - 1) / (m + 1), log m = 2 t (1 + t^2/3 + t^4/5 + t^6/7 + t^8/9).
+__device__ __forceinline__ float det_log(float x)
+{
+    const uint32_t bits = __float_as_uint(x);
+    int e = int(bits >> 23) - 127;
+    float m = __uint_as_float((bits & 0x007fffffu) | 0x3f800000u);
+    if (m > 1.41421354f) { m = __fmul_rn(m, 0.5f); e += 1; }
+    const float t = __fdiv_rn(__fsub_rn(m, 1.0f), __fadd_rn(m, 1.0f));
+    const float t2 = __fmul_rn(t, t);
+    float p = __fmaf_rn(t2, 0.111111112f, 0.142857149f);
+    p = __fmaf_rn(t2, p, 0.2f);
+    p = __fmaf_rn(t2, p, 0.333333343f);
+    p = __fmaf_rn(t2, p, 1.0f);
+    return __fmaf_rn(__int2float_rn(e), 0.693147182f, __fmul_rn(__fadd_rn(t, t), p));
+}
+// Standard Gumbel noise of output (row, column) of a launch seeded with `random`: a 32-bit mixing hash of the three,
+// its upper 23 bits as u = (k + 1/2) / 2^23 in (0, 1), g = -log(-log(u)).
+__device__ __forceinline__ float gumbel_noise(unsigned random, unsigned row, unsigned col)
+{
+    uint32_t x = random ^ (row * 0x9E3779B9u) ^ (col * 0x85EBCA6Bu);
+    x ^= x >> 16; x *= 0x7FEB352Du; x ^= x >> 15; x *= 0x846CA68Bu; x ^= x >> 16;
+    const float u = __fmul_rn(__fadd_rn(__uint2float_rn(x >> 9), 0.5f), 1.1920929e-7f);   // 2^-23
+    return -det_log(-det_log(u));
+}
+
 template <int MUL1>
 // `best` (may be null): per output row one 64-bit key, (order-preserving bits of the value) << 32 | ~column, raised
 // with atomicMax to the row's largest output: the greedy token of an lm_head without a pass over the logits (ties go
 // to the lower column; the value is the one that would be stored, fp16-rounded for fp16 outputs).  `c` may then be null.
+// With sample.gumbel the key's value is stored output * inv_temp + Gumbel noise of (row, column) instead: the row's key
+// then names one draw from softmax(outputs * inv_temp).
 __device__ __forceinline__ void finish_band(float (&v)[4], float sx, int lane, uint2 sr, int band, void* c,
                                             size_t out_row, int n, int out_fp32, unsigned long long* best = nullptr,
-                                            const float* residual = nullptr)
+                                            const float* residual = nullptr, const SampleArgs sample = SampleArgs{})
 {
     const int col = band * 128 + lane * 4;
     if constexpr (MUL1 != 0) {
@@ -275,7 +305,9 @@ __device__ __forceinline__ void finish_band(float (&v)[4], float sx, int lane, u
         unsigned long long key = 0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const uint32_t bits = __float_as_uint(__fadd_rn(v[i], 0.0f));   // (-0 counts as +0, as a comparison of values would)
+            float score = v[i];
+            if (sample.gumbel) score = __fmaf_rn(v[i], sample.inv_temp, gumbel_noise(sample.random, unsigned(out_row), unsigned(col + i)));
+            const uint32_t bits = __float_as_uint(__fadd_rn(score, 0.0f));   // (-0 counts as +0, as a comparison of values would)
             const uint32_t ord = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
             const unsigned long long k = (static_cast<unsigned long long>(ord) << 32) | (0xffffffffu - uint32_t(col + i));
             key = k > key ? k : key;
@@ -312,6 +344,7 @@ struct FinishArgs {
     const float* blocksum;
     void* c;
     unsigned long long* argmax;
+    SampleArgs sample;
     const float* residual;
     const __half* svh;
     const GemvProblem* problems;

@@ -578,7 +578,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
                         const uint2 sv = __ldg(reinterpret_cast<const uint2*>(pv.svh + band * 128 + lane * 4));
                         const float4 t4 = *reinterpret_cast<const float4*>(outbuf + row * PITCH + b * 128 + lane * 4);
                         float v[4] = {t4.x, t4.y, t4.z, t4.w};
-                        finish_band<2>(v, sx, lane, sv, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual);
+                        finish_band<2>(v, sx, lane, sv, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual, p.sample);
                     }
                 }
                 epi_sync();   // outbuf is free again
@@ -620,7 +620,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
                                 v[0] = __fadd_rn(v[0], t4.x); v[1] = __fadd_rn(v[1], t4.y);
                                 v[2] = __fadd_rn(v[2], t4.z); v[3] = __fadd_rn(v[3], t4.w);
                             }
-                            finish_band<2>(v, sx, lane, sv, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual);
+                            finish_band<2>(v, sx, lane, sv, band, pv.c, size_t(row0 + row), pv.ldc, p.out_fp32, p.argmax, p.residual, p.sample);
                         }
                     }
                 }
@@ -756,7 +756,7 @@ bool gemv_i8_rotates_in_kernel(int size_m, int size_k, int size_n, int k_bits, i
 // same contract as launch_gemv.
 std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                            int size_m, int size_k, int size_n, int k_bits, int out_fp32, const GemvScratch& sc, int sms,
-                           cudaStream_t stream, unsigned long long* argmax, int n_stack, const float* residual)
+                           cudaStream_t stream, unsigned long long* argmax, int n_stack, const float* residual, const SampleArgs& sample)
 {
     if (n_stack < 1) n_stack = 1;
     if (size_m > kI8MaxRows) throw std::runtime_error("exl3 gemv (integer tensor path): size_m must be <= 8");
@@ -801,6 +801,7 @@ std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const vo
     args.a_had = static_cast<__half*>(a_had);
     args.c = c;
     args.argmax = argmax;
+    args.sample = sample;
     args.residual = residual;
     args.svh = static_cast<const __half*>(svh);
     args.slabs = sc.slabs;

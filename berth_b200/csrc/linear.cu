@@ -130,6 +130,35 @@ extern "C" int berth_exl3_linear_argmax(const void* a, const void* trellis, void
     });
 }
 
+// The same with the token drawn instead of the arg-max: berth's fused sampler in its second mode (Gumbel arg-max over
+// logits * inv_temp, crates/berth-kernels/csrc/sample/fused.cu:45-135 mode 1) taken in the finishing step of the linear.
+// mode 0 = greedy (berth_exl3_linear_argmax), 1 = Gumbel with the noise of (random, row, column).
+extern "C" int berth_exl3_linear_sample(const void* a, const void* trellis, void* c, const void* suh, void* a_had,
+                                        const void* svh, unsigned long long* best, int size_m, int size_k, int size_n,
+                                        int k_bits, int codebook, int out_fp32, float inv_temp, unsigned int random, int mode,
+                                        void* stream)
+{
+    CallState& st = exl3_state();
+    return guarded(st, [&] {
+        if (!a || !trellis || !suh || !a_had || !svh || !best) throw std::runtime_error("exl3 linear sample: null device pointer");
+        if (size_m < 1 || size_k < 1 || size_n < 1) throw std::runtime_error("exl3 linear sample: sizes must be positive");
+        if (size_m > 32) throw std::runtime_error("exl3 linear sample: size_m must be <= 32 (the decode kernel)");
+        if (mode != 0 && mode != 1) throw std::runtime_error("exl3 linear sample: mode must be 0 or 1");
+        if (!(inv_temp > 0.0f) || !(inv_temp < 3.0e38f)) throw std::runtime_error("exl3 linear sample: inv_temp must be positive and finite");
+        check_linear_args("exl3 linear sample", a, trellis, best, suh, a_had, svh, size_k, size_n, k_bits, codebook);
+        const int device = current_device();
+        const DeviceInfo& info = device_info(device);
+        if (info.major != 10)
+            throw std::runtime_error("exl3 linear sample: no linked kernel for this GPU (library is built for sm_100a only)");
+        SampleArgs sample;
+        sample.inv_temp = inv_temp; sample.random = random; sample.gumbel = mode;
+        cuda_ok(cudaMemsetAsync(best, 0, size_t(size_m) * sizeof(unsigned long long), (cudaStream_t) stream), "sample keys memset");
+        st.launch = launch_gemv(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, out_fp32,
+                                gemv_workspace(device), info.sms, (cudaStream_t) stream, best, nullptr, sample) +
+                    (mode ? " [Gumbel arg-max in the finishing step]" : " [arg-max in the finishing step]");
+    });
+}
+
 // A stack of equally shaped MUL1 matrices applied to the same rows in one launch (gate and up of an MLP stored
 // one behind the other): the units of all matrices share one persistent decode launch, so launch latency, pipeline
 // ramp and the finishing kernel are paid once.

@@ -137,6 +137,18 @@ def exl3_linear_argmax(a, trellis, c, suh, a_had, svh, best, size_m: int, size_k
         raise Error(last_error() or f"exl3 linear argmax launch failed ({rc})")
 
 
+def exl3_linear_sample(a, trellis, c, suh, a_had, svh, best, size_m: int, size_k: int, size_n: int, k_bits: int,
+                       codebook: Codebook, out: OutDtype, inv_temp: float, random: int, mode: int, stream=None) -> None:
+    """:func:`exl3_linear_argmax` with berth's fused sampler in either of its modes taken in the finishing step: ``mode`` 0
+    greedy, 1 Gumbel arg-max over ``outputs * inv_temp`` with the noise of ``(random, row, column)`` -- one draw from the
+    softmax per row.  The keys in ``best`` carry the winning score and column."""
+    rc = _lib.lib().berth_exl3_linear_sample(_ptr(a), _ptr(trellis), _ptr(c), _ptr(suh), _ptr(a_had), _ptr(svh), _ptr(best),
+                                             size_m, size_k, size_n, k_bits, int(codebook), int(out), float(inv_temp),
+                                             int(random) & 0xFFFFFFFF, int(mode), _stream(stream))
+    if rc != 0:
+        raise Error(last_error() or f"exl3 linear sample launch failed ({rc})")
+
+
 def argmax_key_decode(key: int) -> tuple:
     """(token, value) of a key written by :func:`exl3_linear_argmax`; ties went to the lower token."""
     import ctypes as C

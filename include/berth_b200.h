@@ -130,6 +130,18 @@ int berth_exl3_linear_argmax(const void* a, const void* trellis, void* c, const 
                              unsigned long long* best, int size_m, int size_k, int size_n, int k_bits, int codebook,
                              int out_fp32, void* stream);
 void berth_argmax_key_decode(unsigned long long key, int32_t* token, float* value);
+/* The same with berth's fused sampler in either of the modes its serve launches (crates/berth-kernels/csrc/sample/
+ * fused.cu:45-135: berth_sample_fused, mode 0 greedy, mode 1 Gumbel arg-max over logits * inv_temp) taken in the
+ * finishing step of the linear.  mode 1: key r describes the column that maximises
+ *   stored output[r][col] * inv_temp + g(random, r, col),   g = -log(-log(u)),
+ * u = (k + 1/2) / 2^23 with k the upper 23 bits of a 32-bit mixing hash of (random, r, col) -- one draw from
+ * softmax(outputs * inv_temp) per row and value of `random`; the key's value is that score.  The noise is this
+ * library's own counter generator (berth draws from curand's Philox stream inside the fork's kernel, which is not part
+ * of berth's tree): same distribution, different stream.  The logarithm is evaluated from exact steps in a fixed order,
+ * so the CPU checker reproduces every key bit for bit from the stored outputs. */
+int berth_exl3_linear_sample(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
+                             unsigned long long* best, int size_m, int size_k, int size_n, int k_bits, int codebook,
+                             int out_fp32, float inv_temp, unsigned int random, int mode, void* stream);
 
 /* The decode linear (size_m <= 32) with the residual stream added in its last step: c = residual + linear(a), fp32
  * [size_m][size_n]; c may be the residual itself (x += mlp(h2) in place).  Bit for bit what berth_exl3_linear with

@@ -435,6 +435,56 @@ void exl3o_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, int
     for (int64_t i = 0; i < numel; ++i) out[i] = silu_mul_one(gate[i], up[i], act_limit);
 }
 
+/* Scores and keys of the sampling epilogue (berth_exl3_linear_sample; berth: fused sampler modes 0 and 1,
+ * crates/berth-kernels/csrc/sample/fused.cu:45-135).  The noise generator is this build's ("spec v0": berth draws
+ * from curand's Philox stream inside the fork's kernel): a 32-bit mixing hash of (random, row, column), its upper 23
+ * bits as u = (k + 1/2) / 2^23, g = -log(-log(u)) with the logarithm below -- exact steps in a fixed order, every
+ * one a correctly rounded fp32 operation, so the device reproduces it bit for bit. */
+static float det_log(float x)
+{
+    union { uint32_t u; float f; } v;
+    v.f = x;
+    int e = (int) (v.u >> 23) - 127;
+    v.u = (v.u & 0x007fffffu) | 0x3f800000u;
+    float m = v.f;
+    if (m > 1.41421354f) { m = m * 0.5f; e += 1; }
+    const float t = (m - 1.0f) / (m + 1.0f);
+    const float t2 = t * t;
+    float p = fmaf(t2, 0.111111112f, 0.142857149f);
+    p = fmaf(t2, p, 0.2f);
+    p = fmaf(t2, p, 0.333333343f);
+    p = fmaf(t2, p, 1.0f);
+    return fmaf((float) e, 0.693147182f, (t + t) * p);
+}
+static float gumbel_noise(uint32_t random, uint32_t row, uint32_t col)
+{
+    uint32_t x = random ^ (row * 0x9E3779B9u) ^ (col * 0x85EBCA6Bu);
+    x ^= x >> 16; x *= 0x7FEB352Du; x ^= x >> 15; x *= 0x846CA68Bu; x ^= x >> 16;
+    const float u = ((float) (x >> 9) + 0.5f) * 1.1920929e-7f;
+    return -det_log(-det_log(u));
+}
+/* keys[r] = the largest of (order-preserving bits of score) << 32 | ~column over the columns of row r, score = the
+ * output itself (mode 0) or fmaf(output, inv_temp, noise) (mode 1); outputs fp32 [rows][n] as stored (fp16 outputs
+ * converted).  scores (may be NULL) receives every score. */
+void exl3o_sample_keys(const float* outputs, int rows, int n, float inv_temp, uint32_t random, int mode, uint64_t* keys,
+                       float* scores)
+{
+    for (int r = 0; r < rows; ++r) {
+        uint64_t best = 0;
+        for (int c = 0; c < n; ++c) {
+            float s = outputs[(size_t) r * n + c];
+            if (mode) s = fmaf(s, inv_temp, gumbel_noise(random, (uint32_t) r, (uint32_t) c));
+            if (scores) scores[(size_t) r * n + c] = s;
+            union { uint32_t u; float f; } v;
+            v.f = s + 0.0f;
+            const uint32_t ord = (v.u & 0x80000000u) ? ~v.u : (v.u | 0x80000000u);
+            const uint64_t k = ((uint64_t) ord << 32) | (uint64_t) (0xffffffffu - (uint32_t) c);
+            if (k > best) best = k;
+        }
+        keys[r] = best;
+    }
+}
+
 void exl3o_add_f32(const float* a, const float* b, float* c, int64_t n)
 {
     for (int64_t i = 0; i < n; ++i) c[i] = a[i] + b[i];

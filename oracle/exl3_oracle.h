@@ -72,6 +72,8 @@ int exl3o_linear_f64(const uint16_t* a, const uint16_t* trellis, double* c, cons
 /* ---- silu(gate) * up, fp16, every step rounded to fp16
  * (crates/berth-kernels/csrc/ops/act.cu:35-69; pinned by testdata/kernels/ops/silu.*.bin) */
 uint16_t exl3o_hexp_neg(uint16_t g);   /* fp16(exp(-g)); equals the correctly rounded value at all but 2 of the 65536 inputs */
+void exl3o_sample_keys(const float* outputs, int rows, int n, float inv_temp, uint32_t random, int mode, uint64_t* keys,
+                       float* scores);
 void exl3o_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t numel,
                     float act_limit);
 /* c = a + b in fp32 (crates/berth-kernels/csrc/ops/add.cu:23-27). */

@@ -78,6 +78,8 @@ def _declare(l: C.CDLL) -> None:
     l.exl3o_linear_f64.restype = _i
     l.exl3o_linear_f64.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i]
     l.exl3o_silu_mul.argtypes = [_vp, _vp, _vp, _i64, _f]
+    l.exl3o_sample_keys.argtypes = [_vp, _i, _i, _f, C.c_uint32, _i, _vp, _vp]
+    l.exl3o_sample_keys.restype = None
     l.exl3o_add_f32.argtypes = [_vp, _vp, _vp, _i64]
     l.exl3o_rms_norm.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _f, _f, _f]
     l.exl3o_rms_norm.restype = None
@@ -198,6 +200,17 @@ def linear_f64(a, trellis, suh, svh, size_k: int, size_n: int, bits: int, cb: in
     if rc != 0:
         raise ValueError("exl3o_linear_f64: bad shape")
     return c
+
+
+def sample_keys(outputs: np.ndarray, inv_temp: float, random: int, mode: int):
+    """Keys and scores of the sampling epilogue for stored outputs ``[rows][n]`` (any float dtype, taken as fp32):
+    ``(keys uint64 [rows], scores fp32 [rows][n])``; mode 0 greedy, 1 Gumbel."""
+    o = np.ascontiguousarray(outputs.astype(np.float32))
+    rows, n = o.shape
+    keys = np.zeros(rows, np.uint64)
+    scores = np.zeros((rows, n), np.float32)
+    lib().exl3o_sample_keys(_p(o), rows, n, float(inv_temp), int(random) & 0xFFFFFFFF, int(mode), _p(keys), _p(scores))
+    return keys, scores
 
 
 def silu_mul(gate, up, act_limit: float = 0.0) -> np.ndarray:
