@@ -450,6 +450,87 @@ def test_linear_argmax_matches_the_stored_outputs(m, bits, cb, out_fp32, K, N):
     assert "arg-max" in kernels.last_launch()
 
 
+@pytest.mark.parametrize("m", [1, 3, 32])
+@pytest.mark.parametrize("bits,cb,out_fp32,K,N", [(4, 2, True, 512, 384), (6, 2, False, 1024, 2048), (3, 0, True, 256, 128),
+                                                  (4, 1, False, 1024, 6144)])
+def test_linear_sample_gumbel_keys_match_the_checker(oracle, m, bits, cb, out_fp32, K, N):
+    """berth_exl3_linear_sample, mode 1: every row's key is, bit for bit, the checker's key for the outputs the call
+    stored (score = output * inv_temp + Gumbel noise of (random, row, column)); mode 0 gives the greedy keys of
+    berth_exl3_linear_argmax; another `random` draws other tokens; without an output buffer the keys are the same."""
+    w = synth.linear_weights(1234, f"gs{bits}{cb}{K}", K, N, bits)
+    x = synth.activations(1234, f"gs.x{m}", m, K)
+    xd, td, sd, vd = dev(x), dev(w["trellis"]), dev(w["suh"]), dev(w["svh"])
+    dt = torch.float32 if out_fp32 else torch.float16
+    out = OutDtype.F32 if out_fp32 else OutDtype.F16
+
+    def run(inv_temp, random, mode, with_c=True):
+        c = torch.full((m, N), float("nan"), dtype=dt, device="cuda") if with_c else None
+        ah = torch.zeros((m, K), dtype=torch.float16, device="cuda")
+        best = torch.full((m,), -1, dtype=torch.int64, device="cuda")
+        kernels.exl3_linear_sample(xd, td, c, sd, ah, vd, best, m, K, N, bits, Codebook(cb), out, inv_temp, random, mode)
+        torch.cuda.synchronize()
+        return (None if c is None else c.float().cpu().numpy()), best.cpu().numpy().view(np.uint64)
+
+    c, keys = run(0.7, 20240517, 1)
+    assert "Gumbel" in kernels.last_launch()
+    exp_keys, scores = oracle.sample_keys(c, 0.7, 20240517, 1)
+    assert (keys == exp_keys).all()
+    for r in range(m):
+        tok, val = kernels.argmax_key_decode(int(keys[r]))
+        assert tok == int(np.argmax(scores[r])) and val == float(scores[r, tok])
+    _, keys_no_c = run(0.7, 20240517, 1, with_c=False)
+    assert (keys_no_c == keys).all()
+    c2, keys2 = run(0.7, 99, 1)
+    assert (keys2 == oracle.sample_keys(c2, 0.7, 99, 1)[0]).all()
+    if N >= 2048:
+        assert (keys2 != keys).any()
+    cg, greedy = run(1.0, 0, 0)
+    assert (greedy == oracle.sample_keys(cg, 1.0, 0, 0)[0]).all()
+    assert [kernels.argmax_key_decode(int(k))[0] for k in greedy] == [int(np.argmax(cg[r])) for r in range(m)]
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+
+
+def test_linear_sample_draws_follow_the_softmax():
+    """Gumbel arg-max over many values of `random` draws tokens with the softmax probabilities of the row: the
+    empirical frequencies of the most likely tokens agree with softmax(outputs * inv_temp) within sampling error."""
+    K, N, bits, cb, inv_temp = 256, 128, 4, 2, 0.5
+    w = synth.linear_weights(1234, "gsd", K, N, bits)
+    x = synth.activations(1234, "gsd.x", 1, K)
+    xd, td, sd, vd = dev(x), dev(w["trellis"]), dev(w["suh"]), dev(w["svh"])
+    c = torch.empty((1, N), dtype=torch.float32, device="cuda")
+    ah = torch.zeros((1, K), dtype=torch.float16, device="cuda")
+    best = torch.zeros((1,), dtype=torch.int64, device="cuda")
+    draws = 4000
+    counts = np.zeros(N)
+    for r in range(draws):
+        kernels.exl3_linear_sample(xd, td, c, sd, ah, vd, best, 1, K, N, bits, Codebook(cb), OutDtype.F32, inv_temp, 7919 * r + 1, 1)
+        counts[kernels.argmax_key_decode(int(best.cpu().numpy().view(np.uint64)[0]))[0]] += 1
+    logits = c.cpu().numpy()[0].astype(np.float64) * inv_temp
+    p = np.exp(logits - logits.max())
+    p /= p.sum()
+    top = np.argsort(-p)[:5]
+    for t in top:
+        sigma = np.sqrt(p[t] * (1 - p[t]) / draws)
+        assert abs(counts[t] / draws - p[t]) <= 5 * sigma + 1e-3, (t, counts[t] / draws, p[t])
+
+
+def test_linear_sample_fails_closed():
+    K, N = 256, 128
+    w = synth.linear_weights(1234, "gsf", K, N, 4)
+    xd, td, sd, vd = dev(synth.activations(1234, "gsf.x", 1, K)), dev(w["trellis"]), dev(w["suh"]), dev(w["svh"])
+    c = torch.empty((1, N), dtype=torch.float32, device="cuda")
+    ah = torch.zeros((1, K), dtype=torch.float16, device="cuda")
+    best = torch.zeros((1,), dtype=torch.int64, device="cuda")
+    with pytest.raises(kernels.Error, match="mode must be 0 or 1"):
+        kernels.exl3_linear_sample(xd, td, c, sd, ah, vd, best, 1, K, N, 4, Codebook(2), OutDtype.F32, 1.0, 1, 2)
+    with pytest.raises(kernels.Error, match="inv_temp"):
+        kernels.exl3_linear_sample(xd, td, c, sd, ah, vd, best, 1, K, N, 4, Codebook(2), OutDtype.F32, 0.0, 1, 1)
+    with pytest.raises(kernels.Error, match="null"):
+        kernels.exl3_linear_sample(xd, td, c, sd, ah, vd, None, 1, K, N, 4, Codebook(2), OutDtype.F32, 1.0, 1, 1)
+    with pytest.raises(kernels.Error, match="size_m"):
+        kernels.exl3_linear_sample(xd, td, c, sd, ah, vd, best, 33, K, N, 4, Codebook(2), OutDtype.F32, 1.0, 1, 1)
+
+
 def test_linear_argmax_ties():
     """Zero activations give a row of zeros of either sign: every column ties as a value, the key names column 0."""
     K, N, bits, cb = 256, 512, 4, 2

@@ -332,3 +332,26 @@ def test_rms_norm_oracle_against_float64(oracle, rows, dim):
     w = _bf16(w32)
     assert (oracle.rms_norm(xh, w, True, eps, bias, scale).view(np.uint16)
             == oracle.rms_norm(xh.astype(np.float32), w, True, eps, bias, scale).view(np.uint16)).all()
+
+
+def test_sampling_keys_of_the_checker(oracle):
+    """exl3o_sample_keys: greedy keys name the arg-max (ties to the lower column, -0 = +0); the Gumbel noise has the
+    standard Gumbel's mean and variance, is a pure function of (random, row, column), and independent across rows."""
+    rng = np.random.RandomState(5)
+    x = rng.randn(3, 4096).astype(np.float32)
+    x[1, 7] = x[1, 100] = 9.0
+    x[2] = 0.0
+    x[2, 5] = -0.0
+    keys, scores = oracle.sample_keys(x, 1.0, 0, 0)
+    assert (scores == x).all()
+    cols = [0xFFFFFFFF - (int(k) & 0xFFFFFFFF) for k in keys]
+    assert cols == [int(np.argmax(x[0])), 7, 0]
+    keys1, s1 = oracle.sample_keys(x, 1.0, 42, 1)
+    g = (s1 - x).astype(np.float64)
+    assert abs(g.mean() - 0.5772) < 0.03 and abs(g.std() - 1.2825) < 0.05
+    assert abs(np.corrcoef(g[0], g[1])[0, 1]) < 0.05
+    assert (oracle.sample_keys(x, 1.0, 42, 1)[1] == s1).all() and (oracle.sample_keys(x, 1.0, 43, 1)[1] != s1).mean() > 0.99
+    assert [0xFFFFFFFF - (int(k) & 0xFFFFFFFF) for k in keys1] == [int(np.argmax(s1[r])) for r in range(3)]
+    # inv_temp scales the outputs before the noise is added: fmaf(x, inv_temp, g)
+    _, s2 = oracle.sample_keys(x, 2.0, 42, 1)
+    assert np.allclose(s2 - 2.0 * x.astype(np.float64), g, atol=1e-5)
