@@ -99,6 +99,8 @@ struct GemvScratch {
     size_t blocksum_floats = 0;
     unsigned* counters = nullptr;  // integer tensor path: arrival counters of the band groups (zero between launches)
     size_t counter_words = 0;
+    unsigned long long* lists = nullptr;   // slice lists the library writes itself (uniform multi-linear): kGemvListEntries each of
+                                           // output addresses (8 bytes), row strides and source indices (4 bytes)
     unsigned* status = nullptr;
 };
 // The library's own scratch: allocated once per device at first use, never grown, never freed
@@ -106,6 +108,7 @@ struct GemvScratch {
 constexpr size_t kGemvSlabBytes = size_t(32) << 20;
 constexpr size_t kGemvBlocksumFloats = size_t(32) * 4096;
 constexpr size_t kGemvCounterWords = size_t(1) << 16;
+constexpr size_t kGemvListEntries = 2048;
 constexpr size_t kGemvAfragBytes = size_t(8) << 20;   // size_k * ceil(size_m / 8) <= 524288
 GemvScratch gemv_workspace(int device);
 

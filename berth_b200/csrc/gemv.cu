@@ -442,7 +442,7 @@ __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
 __global__ void __launch_bounds__(128) k_rotate_in(const __half* __restrict__ a, const __half* __restrict__ suh_in,
                                                    __half* __restrict__ a_had, uint32_t* __restrict__ afrag,
                                                    float* __restrict__ blocksum, int rows, int rows_pad, int k,
-                                                   const unsigned long long* __restrict__ suh_list, int src)
+                                                   const unsigned long long* __restrict__ suh_list, int src, long long a_src_stride)
 {
     // Trigger first: the decode kernel behind this one may then take each SM as the previous decode
     // kernel leaves it and prefetch its weights; it still waits for this grid, which itself waits here
@@ -454,6 +454,7 @@ __global__ void __launch_bounds__(128) k_rotate_in(const __half* __restrict__ a,
     if (suh_list) {   // blockIdx.y = source: its own sign-scale vector, rotated-input slab, fragment set and block sums
         src += blockIdx.y;
         suh = reinterpret_cast<const __half*>(__ldg(suh_list + src));
+        a += size_t(src) * size_t(a_src_stride);   // (uniform multi-linear with one input per matrix; else every source reads the same rows)
         a_had += size_t(src) * rows * k;
         afrag += size_t(src) * (k >> 4) * tgs * 64;
         blocksum += size_t(src) * rows * kblocks;
@@ -694,7 +695,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
         const int rot_total = 8 * tg * kblocks;
         launch_pdl(k_rotate_in, dim3(std::min((rot_total + 3) / 4, 4 * sms)), dim3(128), 0, stream, "k_rotate_in launch",
                    static_cast<const __half*>(a), static_cast<const __half*>(suh), static_cast<__half*>(a_had), sc.afrag,
-                   sc.blocksum, size_m, 8 * tg, size_k, (const unsigned long long*) nullptr, 0);
+                   sc.blocksum, size_m, 8 * tg, size_k, (const unsigned long long*) nullptr, 0, 0LL);
     }
 
     GemvArgs args;
@@ -805,12 +806,51 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
                                                             sms, stream);
 }
 
+// The slice lists of a uniform multi-linear (count equally shaped matrices, outputs one behind the other): output i at
+// c + i * out_stride_bytes, row stride n, rotated input i.
+__global__ void __launch_bounds__(256) k_uniform_lists(unsigned long long c_base, unsigned long long out_stride_bytes, int n, int count,
+                                                       unsigned long long* __restrict__ c_list, int* __restrict__ n_stride,
+                                                       int* __restrict__ had_src)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();   // the previous launch may still be reading the lists
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x) {
+        c_list[i] = c_base + (unsigned long long) i * out_stride_bytes;
+        n_stride[i] = n;
+        had_src[i] = i;
+    }
+}
+
+std::string launch_gemv_sliced(const void* a, const void* b_list, const void* suh_list, void* a_had, const void* svh_list,
+                               const void* c_list, const int* n_stride_list, const int* had_src_list, int num_had_src, int n_slices,
+                               int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, const GemvScratch& sc,
+                               int sms, cudaStream_t stream, long long a_src_stride);
+
+// Uniform multi-linear: the library writes the slice lists itself and runs the sliced launch with every matrix as one
+// slice (and one rotated input per matrix, from the shared rows or from the matrix's own).
+std::string launch_gemv_uniform(const void* a, const void* b_list, const void* suh_list, void* a_had, const void* svh_list, void* c,
+                                int count, bool per_matrix_input, int size_m, int size_k, int size_n, int k_bits, int codebook,
+                                int out_fp32, const GemvScratch& sc, int sms, cudaStream_t stream)
+{
+    if (count < 1 || size_t(count) > kGemvListEntries)
+        throw std::runtime_error("exl3_mgemm: the uniform mode takes 1 to " + std::to_string(kGemvListEntries) + " matrices");
+    unsigned long long* c_list = sc.lists;
+    int* n_stride = reinterpret_cast<int*>(sc.lists + kGemvListEntries);
+    int* had_src = n_stride + kGemvListEntries;
+    const unsigned long long stride = (unsigned long long) size_m * size_n * (out_fp32 ? 4 : 2);
+    launch_pdl(k_uniform_lists, dim3((count + 255) / 256), dim3(256), 0, stream, "k_uniform_lists launch",
+               (unsigned long long) reinterpret_cast<uintptr_t>(c), stride, size_n, count, c_list, n_stride, had_src);
+    return "k_uniform_lists + " + launch_gemv_sliced(a, b_list, suh_list, a_had, svh_list, c_list, n_stride, had_src, count, count, size_m,
+                                                      size_k, size_n, k_bits, codebook, out_fp32, sc, sms, stream,
+                                                      per_matrix_input ? (long long) size_m * size_k : 0LL);
+}
+
 // Sliced multi-linear on the decode kernel: `n_slices` column slices of width size_n, cut from `num_had_src`
 // matrices, all applied to the same size_m rows of `a`.  Every list is a DEVICE array (see GemvArgs).
 std::string launch_gemv_sliced(const void* a, const void* b_list, const void* suh_list, void* a_had, const void* svh_list,
                                const void* c_list, const int* n_stride_list, const int* had_src_list, int num_had_src, int n_slices,
                                int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, const GemvScratch& sc,
-                               int sms, cudaStream_t stream)
+                               int sms, cudaStream_t stream, long long a_src_stride)
 {
     if (size_m > 32) throw std::runtime_error("exl3_mgemm: no linked kernel for size_m above 32");
     if (size_k % 128 != 0)
@@ -833,7 +873,7 @@ std::string launch_gemv_sliced(const void* a, const void* b_list, const void* su
     const int rot_total = 8 * tg * kblocks;
     launch_pdl(k_rotate_in, dim3(std::min((rot_total + 3) / 4, 4 * sms), num_had_src), dim3(128), 0, stream, "k_rotate_in launch",
                static_cast<const __half*>(a), (const __half*) nullptr, static_cast<__half*>(a_had), sc.afrag, sc.blocksum, size_m, 8 * tg,
-               size_k, static_cast<const unsigned long long*>(suh_list), 0);
+               size_k, static_cast<const unsigned long long*>(suh_list), 0, a_src_stride);
     GemvArgs args;
     args.afrag = sc.afrag;
     args.blocksum = sc.blocksum;

@@ -272,7 +272,10 @@ namespace berth {
 std::string launch_gemv_sliced(const void* a, const void* b_list, const void* suh_list, void* a_had, const void* svh_list,
                                const void* c_list, const int* n_stride_list, const int* had_src_list, int num_had_src, int n_slices,
                                int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32, const GemvScratch& sc,
-                               int sms, cudaStream_t stream);
+                               int sms, cudaStream_t stream, long long a_src_stride = 0);
+std::string launch_gemv_uniform(const void* a, const void* b_list, const void* suh_list, void* a_had, const void* svh_list, void* c,
+                                int count, bool per_matrix_input, int size_m, int size_k, int size_n, int k_bits, int codebook,
+                                int out_fp32, const GemvScratch& sc, int sms, cudaStream_t stream);
 }
 
 extern "C" int berth_ops_mgemm(const void* a, const void* b_list, void* c, const void* suh_list, void* a_had, const void* svh_list,
@@ -299,12 +302,18 @@ extern "C" int berth_ops_mgemm(const void* a, const void* b_list, void* c, const
             if (num_had_src < 1) throw std::runtime_error("exl3_mgemm: sliced mode needs one suh entry per source");
             if (bszm_in != 1) throw std::runtime_error("exl3_mgemm: sliced mode is single-input");
         } else {
+            // uniform mode: bszm_out equally shaped matrices, outputs (bszm_out, size_m, size_n), one input for all or one each
             if (num_had_src != 0) throw std::runtime_error("exl3_mgemm: num_had_src requires had_src_list");
-            throw std::runtime_error("exl3_mgemm: no linked kernel for the uniform mode (sliced launches only)");
+            if (bszm_in != 1 && bszm_in != bszm_out)
+                throw std::runtime_error("exl3_mgemm: uniform mode takes one input for all matrices or one per matrix (bszm_in = 1 or bszm_out)");
         }
         const int device = current_device();
         const DeviceInfo& info = device_info(device);
         if (info.major != 10) throw std::runtime_error("exl3_mgemm: no linked kernel for this GPU (library is built for sm_100a only)");
+        if (!any_list)
+            st.launch = launch_gemv_uniform(a, b_list, suh_list, a_had, svh_list, c, bszm_out, bszm_in > 1, size_m, size_k, size_n, k_bits,
+                                            codebook, c_fp32, gemv_workspace(device), info.sms, (cudaStream_t) stream);
+        else
         st.launch = launch_gemv_sliced(a, b_list, suh_list, a_had, svh_list, c_ptrs, n_stride_list, had_src_list, num_had_src, bszm_out,
                                        size_m, size_k, size_n, k_bits, codebook, c_fp32, gemv_workspace(device), info.sms,
                                        (cudaStream_t) stream);

@@ -60,7 +60,7 @@ GemvScratch gemv_workspace(int device)
     GemvScratch& w = g_ws[device];
     if (!w.slabs) {
         const size_t blocksum = kGemvBlocksumFloats * sizeof(float);
-        const size_t total = kGemvSlabBytes + kGemvAfragBytes + blocksum + kGemvCounterWords * sizeof(unsigned) + 256;
+        const size_t total = kGemvSlabBytes + kGemvAfragBytes + blocksum + kGemvCounterWords * sizeof(unsigned) + kGemvListEntries * 16 + 256;
         void* p = nullptr;
         cuda_ok(cudaMalloc(&p, total), "gemv workspace");
         cuda_ok(cudaMemset(p, 0, total), "gemv workspace memset");
@@ -77,6 +77,8 @@ GemvScratch gemv_workspace(int device)
         w.counters = reinterpret_cast<unsigned*>(b);
         w.counter_words = kGemvCounterWords;
         b += kGemvCounterWords * sizeof(unsigned);
+        w.lists = reinterpret_cast<unsigned long long*>(b);
+        b += kGemvListEntries * 16;
         w.status = reinterpret_cast<unsigned*>(b);
     }
     return w;

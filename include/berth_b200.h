@@ -245,7 +245,10 @@ int berth_prefill_hgemm(const void* a, const void* b, void* c, int size_m, int s
  * one entry per slice (bszm_out of them); bszm_in = 1.  c carries only the output type.  Returns a
  * positive tag (1, 2 or 4: the launch's token groups) or -1.  Differences from berth: every K and
  * codebook is linked, size_m up to 32, no autotune; size_k must be a multiple of 128 and size_n of 256
- * (128 above 4 bits); the uniform mode (all lists null) is not linked and fails closed. */
+ * (128 above 4 bits).  Uniform mode (size_n_list, c_ptrs, n_stride_list and had_src_list all NULL, num_had_src = 0;
+ * crates/berth-kernels/csrc/ops/mgemm.cu:164-198): bszm_out equally shaped matrices (b_list, suh_list, svh_list with
+ * bszm_out entries), outputs c (bszm_out, size_m, size_n), inputs a (bszm_in, size_m, size_k) with bszm_in = 1 (one
+ * input for all) or bszm_out (one each), a_had bszm_out slabs; at most 2048 matrices. */
 int berth_ops_mgemm(const void* a, const void* b_list, void* c, const void* suh_list, void* a_had,
                     const void* svh_list, int size_m, int size_k, int size_n, int k_bits,
                     int codebook, int c_fp32, int bszm_in, int bszm_out, const int* size_n_list,

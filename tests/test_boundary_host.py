@@ -127,8 +127,10 @@ def test_mgemm_rejected_launches_do_not_call_cuda(lib):
     assert rc == -1 and "sliced mode requires" in kernels.ops.last_error()
     rc = l.berth_ops_mgemm(p, p, p, p, p, p, 1, 5120, 2048, 4, 2, 0, 2, 8, p, p, p, p, 2, null)
     assert rc == -1 and "single-input" in kernels.ops.last_error()
-    rc = l.berth_ops_mgemm(p, p, p, p, p, p, 1, 5120, 2048, 4, 2, 0, 1, 8, null, null, null, null, 0, null)
-    assert rc == -1 and "uniform mode" in kernels.ops.last_error()
+    rc = l.berth_ops_mgemm(p, p, p, p, p, p, 1, 5120, 2048, 4, 2, 0, 3, 8, null, null, null, null, 0, null)
+    assert rc == -1 and "uniform mode" in kernels.ops.last_error()     # inputs: one for all matrices, or one each
+    rc = l.berth_ops_mgemm(p, p, p, p, p, p, 1, 5120, 2048, 4, 2, 0, 1, 8, null, null, null, null, 2, null)
+    assert rc == -1 and "num_had_src requires" in kernels.ops.last_error()
 
 
 def test_exl3_gemv_cfg_matches_27b_shapes(lib):

@@ -331,6 +331,33 @@ def test_sliced_multi_linear_vs_oracle(oracle, m, out_fp32, cb):
         assert (ah[i] == oracle.had_r_128(x, w["suh"], True).view(np.uint16)).all()
 
 
+@pytest.mark.parametrize("m,per_matrix_input,out_fp32,cb", [(1, False, True, 2), (5, True, False, 2), (20, True, True, 0), (2, False, False, 1)])
+def test_uniform_multi_linear_vs_oracle(oracle, m, per_matrix_input, out_fp32, cb):
+    """berth_ops_mgemm in its uniform mode (all slice lists null): several equally shaped matrices, outputs one behind the
+    other, one input for all matrices or one each; every matrix against the fp64 evaluation of that matrix alone, and its
+    rotated-input slab bit for bit."""
+    K, N, bits, nmat = 512, 512, 4, 3
+    ws = [synth.linear_weights(1234, f"uni{i}", K, N, bits) for i in range(nmat)]
+    xs = synth.activations(1234, f"uni.x{m}", (nmat if per_matrix_input else 1) * m, K).reshape(-1, m, K)
+    td, sd, vd = [dev(w["trellis"]) for w in ws], [dev(w["suh"]) for w in ws], [dev(w["svh"]) for w in ws]
+    u64 = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device="cuda")
+    dt = torch.float32 if out_fp32 else torch.float16
+    c = torch.full((nmat, m, N), float("nan"), dtype=dt, device="cuda")
+    ah = torch.zeros((nmat, m, K), dtype=torch.float16, device="cuda")
+    xd = dev(np.ascontiguousarray(xs))
+    tag = kernels.ops.exl3_mgemm(xd, u64(td), c, u64(sd), ah, u64(vd), m, K, N, bits, Codebook(cb), OutDtype.F32 if out_fp32 else OutDtype.F16,
+                                 nmat if per_matrix_input else 1, nmat, None, None, None, None, 0)
+    torch.cuda.synchronize()
+    assert tag in (1, 2, 4) and "k_uniform_lists" in kernels.ops.last_launch()
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+    got, gah = c.float().cpu().numpy(), host_u16(ah).reshape(nmat, m, K)
+    for i, w in enumerate(ws):
+        x = xs[i if per_matrix_input else 0]
+        y64 = oracle.linear_f64(x, w["trellis"], w["suh"], w["svh"], K, N, bits, cb)
+        assert_close(got[i], y64, f"matrix {i}")
+        assert (gah[i] == oracle.had_r_128(x, w["suh"], True).view(np.uint16)).all()
+
+
 @pytest.mark.parametrize("m,k,n,ldc,out_fp32", [(5, 64, 48, 48, False), (130, 256, 512, 640, True), (47, 5120, 128, 128, False)])
 def test_prefill_hgemm_vs_numpy(m, k, n, ldc, out_fp32):
     """berth_prefill_hgemm: c[m][ldc] = a[m][k] . b[k][n] in fp16 with fp32 accumulation; columns past n stay untouched."""
