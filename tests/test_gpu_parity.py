@@ -774,6 +774,36 @@ def test_linear_add_equals_linear_then_add(oracle, m, K, N, bits, cb):
     assert mx <= MAX_REL and mean <= MEAN_REL
 
 
+def test_small_batch_tensor_path_random_shapes_vs_decode_kernel():
+    """Forty seeded random shapes (17..32 rows, every bitrate and codebook, K and N any multiples of 128 large enough for the
+    split-K kernel): its outputs against the decode GEMV's (berth_exl3_linear_add with a zero residual always runs that
+    kernel) within the accumulation tolerance of two fp32 summation orders, and a clean status."""
+    rng = np.random.RandomState(20240611)
+    sms = kernels.device_sms(torch.cuda.current_device()) if hasattr(kernels, "device_sms") else 148
+    done = 0
+    while done < 40:
+        K = 128 * int(rng.randint(1, 33))
+        N = 128 * int(rng.randint(1, 65))
+        if (N // 128) * (K // 64) < 8 * sms:
+            continue
+        m, bits, cb = int(rng.randint(17, 33)), int(rng.randint(1, 9)), int(rng.randint(0, 3))
+        w = synth.linear_weights(1234, f"skr{done}", K, N, bits)
+        x = synth.activations(1234, f"skr.x{done}", m, K)
+        xd, td, sd, vd = dev(x), dev(w["trellis"]), dev(w["suh"]), dev(w["svh"])
+        ah = torch.zeros((m, K), dtype=torch.float16, device="cuda")
+        c = torch.full((m, N), float("nan"), dtype=torch.float32, device="cuda")
+        kernels.exl3_linear(xd, td, c, sd, ah, vd, m, K, N, bits, Codebook(cb), OutDtype.F32)
+        assert "k_exl3_gemm_tc_splitk" in kernels.last_launch(), (m, K, N)
+        ref = torch.empty_like(c)
+        kernels.exl3_linear_add(xd, td, ref, sd, ah, vd, torch.zeros_like(c), m, K, N, bits, Codebook(cb))
+        torch.cuda.synchronize()
+        a, b = c.double().cpu().numpy(), ref.double().cpu().numpy()
+        rms = np.sqrt((b ** 2).mean())
+        assert np.isfinite(a).all() and np.abs(a - b).max() <= 4e-3 * rms, (m, K, N, bits, cb, np.abs(a - b).max() / rms)
+        done += 1
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+
+
 # ---------------------------------------------------------------- several MUL1 matrices of different widths in one launch
 
 @pytest.mark.parametrize("m", [1, 2, 4, 7])
