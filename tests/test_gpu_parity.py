@@ -857,3 +857,91 @@ def test_linear_multi_fails_closed():
         kernels.exl3_linear_multi(x, *lists(3), 6, 1, K, bits, Codebook(2), OutDtype.F16)
     with pytest.raises(kernels.Error, match="multiple of 128"):
         kernels.exl3_linear_multi(x, *lists(1)[:5], kernels.int_list([128, 64]), 2, 1, K, bits, Codebook(2), OutDtype.F16)
+
+
+# ---------------------------------------------------------------- the CUDA kernels against the committed golden vectors
+
+def _golden(golden_dir):
+    import json
+    d = os.path.join(golden_dir, "exl3_spec_v0")
+    with open(os.path.join(d, "meta.json")) as f:
+        return d, json.load(f)["files"]
+
+
+def test_cuda_decode_against_committed_golden_tiles(golden_dir):
+    """The decoded weights of the tiny golden matrices (3/4/5 bpw, three codebooks) and of configuration 0 as the CUDA
+    reconstruct kernel produces them: the committed rows and sampled tiles byte for byte, the whole matrices by digest."""
+    import hashlib
+    d, files = _golden(golden_dir)
+    for bits in (3, 4, 5):
+        for cb in (0, 1, 2):
+            m = files[f"tiny.b{bits}.cb{cb}.head.bin"]
+            t = dev(synth.trellis(1234, m["tensor"], 128, 256, bits))
+            out = torch.empty((128, 256), dtype=torch.float16, device="cuda")
+            kernels.prefill_lin.reconstruct(out, t, 128, 256, 256, 0, bits, Codebook(cb))
+            got = host_u16(out).reshape(128, 256)
+            head = np.fromfile(os.path.join(d, f"tiny.b{bits}.cb{cb}.head.bin"), np.uint16).reshape(16, 256)
+            assert (got[:16] == head).all()
+            assert hashlib.sha256(got.tobytes()).hexdigest() == m["sha256_whole_decoded_matrix"]
+    m = files["c0.tiles.bin"]
+    K, N = m["size_k"], m["size_n"]
+    w = synth.linear_weights(1234, m["tensor"], K, N, m["bits"])
+    out = torch.empty((K, N), dtype=torch.float16, device="cuda")
+    kernels.prefill_lin.reconstruct(out, dev(w["trellis"]), K, N, N, 0, m["bits"], Codebook(m["codebook"]))
+    got = host_u16(out).reshape(K, N)
+    tiles = np.fromfile(os.path.join(d, "c0.tiles.bin"), np.uint16).reshape(64, 16, 16)
+    for i, (kt, nt) in enumerate(m["positions"]):
+        assert (got[16 * kt:16 * kt + 16, 16 * nt:16 * nt + 16] == tiles[i]).all(), (kt, nt)
+    assert hashlib.sha256(got.tobytes()).hexdigest() == m["sha256_whole_decoded_matrix"]
+
+
+@pytest.mark.parametrize("path", ["decode", "static_scratch", "prefill_rows"])
+def test_cuda_linear_against_committed_golden_c0(golden_dir, path):
+    """Configuration 0 (5120 x 6144, 4 bpw, MUL1, one row) through the decode linear, the allocation-free entry point and
+    (as 33 copies of the row) the prefill linear: within the tolerance of the committed fp64 row, within the accumulation
+    tolerance of the committed fp32 row of the checker, rotated activations by digest."""
+    import hashlib
+    d, files = _golden(golden_dir)
+    m = files["c0.y.bin"]
+    K, N, bits, cb = m["size_k"], m["size_n"], m["bits"], m["codebook"]
+    w = synth.linear_weights(1234, m["tensor"], K, N, bits)
+    x = synth.activations(1234, m["activations"], 1, K)
+    y32 = np.fromfile(os.path.join(d, "c0.y.bin"), np.float32).reshape(1, N)
+    y64 = np.fromfile(os.path.join(d, "c0.y64.bin"), np.float64).reshape(1, N)
+    rows = 33 if path == "prefill_rows" else 1
+    xd, td, sd, vd = dev(np.repeat(x, rows, axis=0)), dev(w["trellis"]), dev(w["suh"]), dev(w["svh"])
+    c = torch.full((rows, N), float("nan"), dtype=torch.float32, device="cuda")
+    ah = torch.zeros((rows, K), dtype=torch.float16, device="cuda")
+    if path == "static_scratch":
+        kernels.exl3_linear_static_scratch(xd, td, c, sd, ah, vd, rows, K, N, bits, Codebook(cb), OutDtype.F32)
+    else:
+        kernels.exl3_linear(xd, td, c, sd, ah, vd, rows, K, N, bits, Codebook(cb), OutDtype.F32)
+    torch.cuda.synchronize()
+    got = c.cpu().numpy()
+    for r in (0, rows - 1):
+        assert_close(got[r:r + 1], y64, f"{path} row {r}")
+        assert np.abs(got[r:r + 1].astype(np.float64) - y32).max() <= 4e-3 * np.sqrt((y64 ** 2).mean())
+    assert hashlib.sha256(host_u16(ah).reshape(rows, K)[0].tobytes()).hexdigest() == m["sha256_rotated_activations"]
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+
+
+@pytest.mark.parametrize("T", [1, 64, 1024])
+def test_cuda_router_against_committed_golden_topk(golden_dir, T):
+    """Configuration 3's router at 1, 64 and 1024 tokens: the top-8 table byte for byte, the logits by digest."""
+    import hashlib
+    from berth_b200 import moe
+    d, files = _golden(golden_dir)
+    m = files[f"c3.topk.T{T}.bin"]
+    H, E, k = m["hidden"], m["n_experts"], m["top_k"]
+    x = dev(synth.activations(1234, m["activations"], T, H))
+    wr = dev(synth.router_weight(1234, m["router"], H, E))
+    logits = torch.empty((T, E), dtype=torch.float32, device="cuda")
+    idx = torch.empty((T, k), dtype=torch.int32, device="cuda")
+    tw = torch.empty((T, k), dtype=torch.float32, device="cuda")
+    moe.router_topk(x, wr, None, idx, tw, logits, T, H, E, k)
+    torch.cuda.synchronize()
+    exp = np.fromfile(os.path.join(d, f"c3.topk.T{T}.bin"), np.int32).reshape(T, k)
+    assert (idx.cpu().numpy() == exp).all()
+    assert hashlib.sha256(logits.cpu().numpy().tobytes()).hexdigest() == m["sha256_logits_f32"]
+    w = tw.cpu().numpy()
+    assert np.abs(w.sum(axis=1) - 1.0).max() <= 1e-6 and (np.diff(w, axis=1) <= 1e-7).all()   # renormalised, descending

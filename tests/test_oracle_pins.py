@@ -355,3 +355,35 @@ def test_sampling_keys_of_the_checker(oracle):
     # inv_temp scales the outputs before the noise is added: fmaf(x, inv_temp, g)
     _, s2 = oracle.sample_keys(x, 2.0, 42, 1)
     assert np.allclose(s2 - 2.0 * x.astype(np.float64), g, atol=1e-5)
+
+
+# ---------------------------------------------------------------- committed golden vectors of the checker itself
+
+def _golden_meta(golden_dir):
+    import json
+    d = os.path.join(golden_dir, "exl3_spec_v0")
+    with open(os.path.join(d, "meta.json")) as f:
+        return d, json.load(f)
+
+
+def test_checker_reproduces_its_committed_golden_vectors(oracle, golden_dir):
+    """tests/golden/exl3_spec_v0: the generator run again gives, byte for byte, the committed files and digests (decoded
+    tiles of tiny matrices at 3/4/5 bpw for the three codebooks, configuration 0's output row, 64 sampled tiles and the
+    digest of its whole decoded matrix, the top-8 tables of configuration 3 at 1/64/1024 tokens)."""
+    import hashlib
+    import importlib.util
+    d, meta = _golden_meta(golden_dir)
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(d, "make_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    files = mod.generate()
+    assert set(files) == set(meta["files"])
+    for name, (arr, entry) in files.items():
+        m = meta["files"][name]
+        raw = np.ascontiguousarray(arr).tobytes()
+        with open(os.path.join(d, name), "rb") as f:
+            assert f.read() == raw, name
+        assert hashlib.sha256(raw).hexdigest() == m["sha256"], name
+        for key, value in entry.items():
+            if key.startswith("sha256_"):
+                assert m[key] == value, (name, key)
