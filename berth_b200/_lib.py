@@ -46,6 +46,7 @@ SIGNATURES = {
     "berth_exl3_linear_sample": (_i, [_vp] * 7 + [_i] * 6 + [_f, C.c_uint, _i, _vp]),
     "berth_exl3_linear_add": (_i, [_vp] * 7 + [_i] * 5 + [_vp]),
     "berth_exl3_linear_stack": (_i, [_vp] * 6 + [_i] * 7 + [_vp]),
+    "berth_exl3_weights_streamed": (_i, [_i]),
     "berth_exl3_linear_multi": (_i, [_vp] * 7 + [_i] * 6 + [_vp]),
     "berth_argmax_key_decode": (None, [_u64, C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
     "berth_exl3_last_error": (C.c_char_p, []),

@@ -200,6 +200,10 @@ std::string launch_gemv_grouped(const void* xr, const void* trellis_stack, int n
 // How the arg-max keys of a decode launch are scored: the stored output itself (greedy), or
 // output * inv_temp + Gumbel noise drawn from a counter hash of (random, row, column) -- one draw of the softmax
 // distribution at temperature 1 / inv_temp (the Gumbel-max trick).
+// Process-wide switch set by berth_exl3_weights_streamed: true when a caller may write a trellis on the stream directly
+// before the linear that reads it; the decode kernels then fetch no weights ahead of griddepcontrol.wait.
+bool weights_streamed();
+
 struct SampleArgs {
     float inv_temp = 1.0f;
     unsigned random = 0;

@@ -799,6 +799,7 @@ struct SplitKArgs {
     unsigned* status;
     float* slabs;          // [grid][2][32][128] fp32
     int m, k, n, out_fp32, grid;
+    int defer_weights;     // no weight fetch before griddepcontrol.wait (berth_exl3_weights_streamed)
 };
 constexpr int kSkRows = 32;                       // rows of the activation box and of a slab
 constexpr int kSkAStageBytes = kSkRows * BK * 2;  // 4 KiB
@@ -875,6 +876,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemm_tc_splitk(const __gri
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_t) : "memory");
             int tb = band0, tks = ks00, st = 0, pt = 0;
+            if (p.defer_weights) pdl_wait();   // the caller may have written the weights just before this launch
             for (int i = 0; i < total; ++i) {
                 if (i >= ST) mbar_wait_parked(empty_t + 8 * st, pt ^ 1, p.status, 100);
                 mbar_arrive_expect_tx(full_t + 8 * st, T_STAGE_BYTES);
@@ -1360,6 +1362,7 @@ std::string launch_gemm_tc_splitk(const void* a, const void* trellis, void* c, c
     if (grid < 1) throw std::runtime_error("exl3 linear: split-K scratch is too small for this shape");
     had_r_128(a, a_had, suh, 1, size_m, size_k, 0, stream);
     SplitKArgs args;
+    args.defer_weights = weights_streamed() ? 1 : 0;
     args.c = c;
     args.svh = static_cast<const __half*>(svh);
     args.status = sc.status;

@@ -192,6 +192,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
             // (a grouped launch's problem table was written before the rotation kernel started, so it
             // is already visible here)
             constexpr uint32_t kStageTx = FUSED ? W_BYTES : STAGE_BYTES;
+            if (p.defer_weights) grid_dependency_wait();   // the caller may have written the weights just before this launch
             for (int i = 0; i < pre; ++i) {
                 mbar_arrive_expect_tx(full0 + 8 * i, kStageTx);
                 issue_weights(i, smem_u32(ring + i * STAGE_BYTES), full0 + 8 * i);
@@ -699,6 +700,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     }
 
     GemvArgs args;
+    args.defer_weights = weights_streamed() ? 1 : 0;
     args.afrag = sc.afrag;
     args.blocksum = sc.blocksum;
     args.a = static_cast<const __half*>(a);
@@ -761,6 +763,7 @@ std::string launch_gemv_grouped_rotated(const void* trellis_stack, int n_experts
     if (size_t(grid) * per_cta > sc.slab_bytes) grid = int(sc.slab_bytes / per_cta);
     if (grid < 1) throw std::runtime_error("exl3 grouped gemv: split-K scratch is too small");
     GemvArgs args;
+    args.defer_weights = weights_streamed() ? 1 : 0;
     args.afrag = afrag;
     args.blocksum = blocksum;
     args.a = nullptr; args.suh = nullptr; args.a_had = nullptr;
@@ -875,6 +878,7 @@ std::string launch_gemv_sliced(const void* a, const void* b_list, const void* su
                static_cast<const __half*>(a), (const __half*) nullptr, static_cast<__half*>(a_had), sc.afrag, sc.blocksum, size_m, 8 * tg,
                size_k, static_cast<const unsigned long long*>(suh_list), 0, a_src_stride);
     GemvArgs args;
+    args.defer_weights = weights_streamed() ? 1 : 0;
     args.afrag = sc.afrag;
     args.blocksum = sc.blocksum;
     args.a = nullptr; args.suh = nullptr; args.a_had = nullptr;

@@ -30,6 +30,7 @@ struct GemvArgs {
     void* c;                  // output rows [rows][n]
     unsigned long long* argmax;   // dense launch only, may be null: per row the key of its largest output (finish_band)
     SampleArgs sample;            // how those keys are scored
+    int defer_weights;            // no weight fetch before griddepcontrol.wait (berth_exl3_weights_streamed)
     const float* residual;        // dense launch with fp32 output only, may be null: rows [m][n] added to the output (may be c itself)
     const __half* svh;        // [n], or the stack [experts][n] when grouped
     const GemvProblem* problems;   // grouped launch: one entry per (expert, chunk of <= 8*TG rows); else null

@@ -289,6 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
         pr_kb = int(u0 - (long long) gbg * kblocks);
         split_bg(gbg, pr_pi, pr_lbg);
         asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.m[p.het ? pr_pi : 0]) : "memory");
+        if (p.defer_weights) pdl_wait();   // the caller may have written the weights just before this launch
         for (int i = 0; i < pre; ++i) {
             mbar_arrive_expect_tx(full0 + 8 * i, kStageTx);
             issue_weights(smem_u32(ring + i * STAGE_BYTES), full0 + 8 * i);
@@ -794,6 +795,7 @@ std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const vo
                        size_m, size_k, nb);
 
     GemvArgs args{};
+    args.defer_weights = weights_streamed() ? 1 : 0;
     args.afrag = sc.afrag;
     args.blocksum = sc.blocksum;
     args.a = static_cast<const __half*>(a);
@@ -832,6 +834,7 @@ std::string launch_gemv_i8_multi(const void* a, const void* const* trellis, void
     const int bu = k_bits <= 4 ? 2 : 1;
     const int kblocks = size_k / 128;
     GemvArgs args{};
+    args.defer_weights = weights_streamed() ? 1 : 0;
     args.het = 1;
     int total_bg = 0, max_n = 0;
     for (int i = 0; i < n_matrices; ++i) {

@@ -130,6 +130,13 @@ extern "C" int berth_exl3_linear_argmax(const void* a, const void* trellis, void
     });
 }
 
+// For hosts that write weights on the same stream directly before using them (streaming experts or layers in): after
+// berth_exl3_weights_streamed(1) the decode kernels of this process fetch no weights before their predecessor on the
+// stream has ended, which is berth's own ownership rule (crates/berth-kernels/src/lib.rs:126-133: stream order is
+// enough); the default keeps the prefetch and asks the caller to have the weights final one kernel earlier.
+namespace berth { int set_weights_streamed(int on); }
+extern "C" int berth_exl3_weights_streamed(int on) { return berth::set_weights_streamed(on); }
+
 // The same with the token drawn instead of the arg-max: berth's fused sampler in its second mode (Gumbel arg-max over
 // logits * inv_temp, crates/berth-kernels/csrc/sample/fused.cu:45-135 mode 1) taken in the finishing step of the linear.
 // mode 0 = greedy (berth_exl3_linear_argmax), 1 = Gumbel with the noise of (random, row, column).

@@ -5,6 +5,7 @@
 #include <algorithm>
 #include "../../include/berth_b200.h"
 
+#include <atomic>
 #include <mutex>
 
 namespace berth {
@@ -52,6 +53,10 @@ const DeviceInfo& device_info(int device)
     }
     return d;
 }
+
+namespace { std::atomic<int> g_weights_streamed{0}; }
+bool weights_streamed() { return g_weights_streamed.load(std::memory_order_relaxed) != 0; }
+int set_weights_streamed(int on) { return g_weights_streamed.exchange(on ? 1 : 0); }
 
 GemvScratch gemv_workspace(int device)
 {

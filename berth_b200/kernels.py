@@ -161,6 +161,12 @@ def device_cc(device: int) -> int:
     return _lib.lib().berth_device_cc(device)
 
 
+def weights_streamed(on: bool) -> bool:
+    """Process-wide: ``True`` makes every decode kernel wait for its predecessor on the stream before it fetches weights (for
+    hosts that write a trellis directly before the linear that reads it); returns the previous setting."""
+    return bool(_lib.lib().berth_exl3_weights_streamed(1 if on else 0))
+
+
 def device_sms(device: int) -> int:
     return _lib.lib().berth_device_sms(device)
 

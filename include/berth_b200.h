@@ -78,6 +78,14 @@ int berth_exl3_linear_static_scratch(const void* a, const void* trellis, void* c
                                      int size_n, int k_bits, int codebook, int out_fp32,
                                      void* stream);
 
+/* Guard for the programmatic-launch contract above.  By default the decode kernels start fetching `trellis` while the
+ * kernel before them on the stream may still be running.  A host that writes weights on the same stream directly before
+ * the linear that reads them (experts or layers streamed in) calls berth_exl3_weights_streamed(1) once: from then on no
+ * kernel of this process fetches weights before its predecessor has ended -- berth's own rule (stream order is enough,
+ * crates/berth-kernels/src/lib.rs:126-133) at the price of the overlap.  Returns the previous setting.  No CUDA call.
+ * No counterpart in berth. */
+int berth_exl3_weights_streamed(int on);
+
 /* Device queries of crates/berth-kernels/csrc/internal.h:11-13 (class 1..5 as the fork's CC_*
  * enumeration orders them: old, Ampere, Ada, Hopper, Blackwell; SM count). -1 on error. */
 int berth_device_cc(int device);

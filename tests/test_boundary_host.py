@@ -220,3 +220,10 @@ def test_linear_add_and_stack_argument_checks(lib):
         kernels.exl3_linear_stack(P, P, P, P, P, P, 0, 1, 128, 128, 4, Codebook.Mul1, OutDtype.F16)
     with pytest.raises(Error, match="no linked kernel"):
         kernels.exl3_linear_stack(P, P, P, P, P, P, 2, 9, 128, 128, 4, Codebook.Mul1, OutDtype.F16)
+
+
+def test_weights_streamed_switch_returns_the_previous_setting(lib):
+    assert lib.berth_exl3_weights_streamed(1) == 0
+    assert lib.berth_exl3_weights_streamed(1) == 1
+    assert lib.berth_exl3_weights_streamed(0) == 1
+    assert lib.berth_exl3_weights_streamed(0) == 0

@@ -945,3 +945,39 @@ def test_cuda_router_against_committed_golden_topk(golden_dir, T):
     assert hashlib.sha256(logits.cpu().numpy().tobytes()).hexdigest() == m["sha256_logits_f32"]
     w = tw.cpu().numpy()
     assert np.abs(w.sum(axis=1) - 1.0).max() <= 1e-6 and (np.diff(w, axis=1) <= 1e-7).all()   # renormalised, descending
+
+
+def test_weights_streamed_guard_changes_no_result():
+    """berth_exl3_weights_streamed(1): the decode kernels fetch no weights before their predecessor on the stream has
+    ended.  Every decode kernel (integer path, fp16 path with and without in-kernel rotation, split-K tensor-core path,
+    stacked and multi-matrix launches) gives the same bits with the guard on, also when the weights are copied into place
+    on the same stream directly before each launch."""
+    cases = [(1, 1024, 768, 4, 2), (2, 1024, 768, 4, 0), (7, 512, 640, 5, 2), (20, 2048, 5120, 4, 2), (32, 512, 256, 3, 1)]
+    assert kernels.weights_streamed(False) is False
+    try:
+        for m, K, N, bits, cb in cases:
+            w = synth.linear_weights(1234, f"guard{K}x{N}", K, N, bits)
+            x = synth.activations(1234, f"guard.x{m}", m, K)
+            ref, _ = run_linear(x, w, bits, cb, True)
+            name = kernels.last_launch()
+            kernels.weights_streamed(True)
+            got, _ = run_linear(x, w, bits, cb, True)
+            assert kernels.last_launch() == name
+            assert (got.view(np.uint32) == ref.view(np.uint32)).all(), (m, K, N)
+            # weights copied into place on the stream right before the launch, several times over
+            xd, sd, vd = dev(x), dev(w["suh"]), dev(w["svh"])
+            src, other = dev(w["trellis"]), dev(synth.trellis(1234, "guard.other", K, N, bits))
+            td = torch.empty_like(src)
+            c = torch.empty((m, N), dtype=torch.float32, device="cuda")
+            ah = torch.zeros((m, K), dtype=torch.float16, device="cuda")
+            for _ in range(8):
+                td.copy_(other)
+                kernels.exl3_linear(xd, td, c, sd, ah, vd, m, K, N, bits, Codebook(cb), OutDtype.F32)
+                td.copy_(src)
+                kernels.exl3_linear(xd, td, c, sd, ah, vd, m, K, N, bits, Codebook(cb), OutDtype.F32)
+            torch.cuda.synchronize()
+            assert (c.cpu().numpy().view(np.uint32) == ref.view(np.uint32)).all(), (m, K, N)
+            assert kernels.weights_streamed(False) is True
+    finally:
+        kernels.weights_streamed(False)
+    assert kernels.device_status(torch.cuda.current_device()) == 0
