@@ -36,6 +36,20 @@ class LinearInfo(C.Structure):
                 ("bits_x2", _i)]
 
 
+class ModelConfigStruct(C.Structure):
+    """``berth_model_config`` of include/berth_b200_checkpoint.h."""
+    _fields_ = [("arch_string", C.c_char_p)] + [(n, C.c_uint32) for n in (
+        "num_hidden_layers", "hidden_size", "head_dim", "num_attention_heads", "num_key_value_heads", "vocab_size")] + [
+        ("tie_word_embeddings", _i), ("attn_output_gate", _i)] + [(n, C.c_uint32) for n in (
+            "linear_conv_kernel_dim", "linear_num_key_heads", "linear_num_value_heads", "linear_key_head_dim",
+            "linear_value_head_dim")] + [(n, _i64) for n in (
+                "intermediate_size", "num_experts", "num_experts_per_tok", "moe_intermediate_size",
+                "shared_expert_intermediate_size", "n_layer_types")] + [
+        ("layer_types", C.POINTER(C.c_char_p)), ("quant_method", C.c_char_p), ("bits", C.c_double), ("head_bits", C.c_uint32),
+        ("codebook", C.c_char_p), ("version", C.c_char_p), ("out_scales", C.c_char_p)] + [(n, _i64) for n in (
+            "vision_bits", "mtp_bits", "calibration_rows", "calibration_cols")] + [("strings", _vp)]
+
+
 _tip, _lip = C.POINTER(TensorInfo), C.POINTER(LinearInfo)
 
 # name -> (restype, argtypes); every symbol the headers declare.
@@ -107,6 +121,9 @@ SIGNATURES = {
     "berth_ckpt_read": (_i, [_vp, C.c_char_p, _vp, _u64]),
     "berth_ckpt_scale_f16": (_i, [_vp, C.c_char_p, _i, _vp, _u64]),
     "berth_unpack_signs": (_i, [_vp, _u64, _vp]),
+    "berth_config_parse": (_i, [C.c_char_p, _u64, _vp]),
+    "berth_config_open": (_i, [C.c_char_p, _vp]),
+    "berth_config_free": (None, [_vp]),
     "berth_ckpt_last_error": (C.c_char_p, []),
 }
 

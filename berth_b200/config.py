@@ -4,20 +4,20 @@
 Text-stack fields are read from ``text_config`` when that object holds the key, otherwise from the top level;
 ``architectures`` and ``quantization_config`` are always top-level; unknown keys are ignored; integers may be written
 as integer-valued floats (``6.0``).  A failure raises :class:`~berth_b200.checkpoint.CheckpointError` with berth's
-wording: ``missing field `name``` or ``field `name`: detail`` (crates/berth-exl3/src/error.rs:6-13).  Pure host logic;
-the kernels take shapes and bitrates from the tensors, this is what an engine sizes its layers from (hidden size, MoE
-dimensions, layer kinds, head bitrate).
+wording: ``missing field `name``` or ``field `name`: detail`` (crates/berth-exl3/src/error.rs:6-13).  The parsing runs in the
+library (``berth_config_parse`` / ``berth_config_open`` of include/berth_b200_checkpoint.h, host memory only); the kernels
+take shapes and bitrates from the tensors, this is what an engine sizes its layers from (hidden size, MoE dimensions,
+layer kinds, head bitrate).
 """
 from __future__ import annotations
 
+import ctypes as C
 import dataclasses
 import json
-import math
 import os
 
+from . import _lib
 from .checkpoint import CheckpointError
-
-U32_MAX = 0xFFFFFFFF
 
 
 @dataclasses.dataclass(frozen=True)
@@ -73,171 +73,40 @@ class ModelConfig:
 
     @staticmethod
     def from_bytes(data: bytes) -> "ModelConfig":
-        try:
-            value = json.loads(data)
-        except ValueError as e:
-            raise CheckpointError(f"config.json: {e}") from None
-        return ModelConfig.from_value(value)
+        """Parses ``config.json`` bytes with the library's reader (``berth_config_parse``)."""
+        return _from_native(lambda out: _lib.lib().berth_config_parse(data, len(data), C.byref(out)))
 
     @staticmethod
     def from_directory(directory: str) -> "ModelConfig":
-        path = os.path.join(directory, "config.json")
-        try:
-            with open(path, "rb") as f:
-                data = f.read()
-        except OSError as e:
-            raise CheckpointError(f"{path}: {e.strerror}") from None
-        return ModelConfig.from_bytes(data)
+        return _from_native(lambda out: _lib.lib().berth_config_open(os.fsencode(directory), C.byref(out)))
 
     @staticmethod
     def from_value(value) -> "ModelConfig":
-        if not isinstance(value, dict):
-            raise _bad("config.json", "expected a JSON object")
-        root = value
-        text = root.get("text_config")
-        if text is not None and not isinstance(text, dict):
-            raise _bad("text_config", f"expected an object, got {_describe(text)}")
-        arch = _arch_string(root)
-        layers = _u32(_require(root, text, "num_hidden_layers"), "num_hidden_layers")
-        layer_types = _layer_types(_require(root, text, "layer_types"))
-        if len(layer_types) != layers:
-            raise _bad("layer_types", f"length {len(layer_types)} does not match num_hidden_layers {layers}")
-        if "quantization_config" not in root:
-            raise _missing("quantization_config")
-        req = lambda key: _u32(_require(root, text, key), key)
-        opt = lambda key: None if _lookup(root, text, key) is _ABSENT else _u32(_lookup(root, text, key), key)
+        """An already-decoded ``config.json`` value (serialised again for the library's reader)."""
+        return ModelConfig.from_bytes(json.dumps(value).encode())
+
+
+def _from_native(call) -> ModelConfig:
+    out = C.POINTER(_lib.ModelConfigStruct)()
+    if call(out) != 0:
+        raise CheckpointError(_lib.lib().berth_ckpt_last_error().decode())
+    try:
+        c = out.contents
+        s = lambda v: None if v is None else v.decode()
+        o = lambda v: None if v < 0 else int(v)
+        cal = None if c.calibration_rows < 0 else Calibration(int(c.calibration_rows), int(c.calibration_cols))
+        quant = QuantizationConfig(quant_method=s(c.quant_method), bits=float(c.bits), head_bits=int(c.head_bits), codebook=s(c.codebook),
+                                   version=s(c.version), vision_bits=o(c.vision_bits), mtp_bits=o(c.mtp_bits),
+                                   out_scales=s(c.out_scales), calibration=cal)
         return ModelConfig(
-            arch_string=arch, num_hidden_layers=layers, hidden_size=req("hidden_size"),
-            intermediate_size=opt("intermediate_size"), head_dim=req("head_dim"),
-            num_attention_heads=req("num_attention_heads"), num_key_value_heads=req("num_key_value_heads"),
-            vocab_size=req("vocab_size"), tie_word_embeddings=_bool(_require(root, text, "tie_word_embeddings"), "tie_word_embeddings"),
-            layer_types=layer_types, linear_conv_kernel_dim=req("linear_conv_kernel_dim"),
-            linear_num_key_heads=req("linear_num_key_heads"), linear_num_value_heads=req("linear_num_value_heads"),
-            linear_key_head_dim=req("linear_key_head_dim"), linear_value_head_dim=req("linear_value_head_dim"),
-            attn_output_gate=_bool(_require(root, text, "attn_output_gate"), "attn_output_gate"),
-            num_experts=opt("num_experts"), num_experts_per_tok=opt("num_experts_per_tok"),
-            moe_intermediate_size=opt("moe_intermediate_size"),
-            shared_expert_intermediate_size=opt("shared_expert_intermediate_size"),
-            quantization=_quant(root["quantization_config"]))
-
-
-_ABSENT = object()
-
-
-def _missing(field: str) -> CheckpointError:
-    return CheckpointError(f"missing field `{field}`")
-
-
-def _bad(field: str, detail: str) -> CheckpointError:
-    return CheckpointError(f"field `{field}`: {detail}")
-
-
-def _describe(v) -> str:
-    """config.rs:381-391."""
-    if v is None:
-        return "null"
-    if isinstance(v, bool):
-        return "true" if v else "false"
-    if isinstance(v, (int, float)):
-        return json.dumps(v)
-    if isinstance(v, str):
-        return f"string {json.dumps(v)}" if len(v.encode()) < 64 else "a long string"
-    if isinstance(v, list):
-        return "an array"
-    return "an object"
-
-
-def _lookup(root: dict, text: dict | None, key: str):
-    if text is not None and key in text:
-        return text[key]
-    return root.get(key, _ABSENT)
-
-
-def _require(root: dict, text: dict | None, key: str):
-    v = _lookup(root, text, key)
-    if v is _ABSENT:
-        raise _missing(key)
-    return v
-
-
-def _u32(v, field: str) -> int:
-    """Integers, or floats that are exactly an integer (config.rs:360-379)."""
-    if isinstance(v, int) and not isinstance(v, bool):
-        if v >= 0:
-            if v > U32_MAX:
-                raise _bad(field, f"integer {v} does not fit in u32")
-            return v
-    elif isinstance(v, float) and math.isfinite(v) and v >= 0.0 and v == math.floor(v) and v <= U32_MAX:
-        return int(v)
-    raise _bad(field, f"expected a non-negative integer, got {_describe(v)}")
-
-
-def _bool(v, field: str) -> bool:
-    if not isinstance(v, bool):
-        raise _bad(field, f"expected a bool, got {_describe(v)}")
-    return v
-
-
-def _string(v, field: str) -> str:
-    if not isinstance(v, str):
-        raise _bad(field, f"expected a string, got {_describe(v)}")
-    return v
-
-
-def _arch_string(root: dict) -> str:
-    if "architectures" not in root:
-        raise _missing("architectures")
-    v = root["architectures"]
-    if not isinstance(v, list):
-        raise _bad("architectures", f"expected an array, got {_describe(v)}")
-    if not v:
-        raise _bad("architectures", "expected a non-empty array")
-    if not isinstance(v[0], str):
-        raise _bad("architectures", f"expected a string, got {_describe(v[0])}")
-    if not v[0]:
-        raise _bad("architectures", "architecture string is empty")
-    return v[0]
-
-
-def _layer_types(v) -> tuple:
-    if not isinstance(v, list):
-        raise _bad("layer_types", f"expected an array, got {_describe(v)}")
-    for item in v:
-        if not isinstance(item, str):
-            raise _bad("layer_types", f"expected strings, got {_describe(item)}")
-    return tuple(v)
-
-
-def _quant(v) -> QuantizationConfig:
-    if not isinstance(v, dict):
-        raise _bad("quantization_config", f"expected an object, got {_describe(v)}")
-
-    def req(key, conv):
-        if key not in v:
-            raise _missing(key)
-        return conv(v[key], key)
-
-    def opt(key, conv):
-        return conv(v[key], key) if key in v else None
-
-    def number(x, key):
-        if isinstance(x, bool) or not isinstance(x, (int, float)):
-            raise _bad(key, f"expected a number, got {_describe(x)}")
-        x = float(x)
-        if not math.isfinite(x) or x < 0.0:
-            raise _bad(key, f"expected a non-negative finite number, got {x}")
-        return x
-
-    calibration = None
-    if "calibration" in v:
-        c = v["calibration"]
-        if not isinstance(c, dict):
-            raise _bad("calibration", f"expected an object, got {_describe(c)}")
-        for key in ("rows", "cols"):
-            if key not in c:
-                raise _missing(f"calibration.{key}")
-        calibration = Calibration(_u32(c["rows"], "calibration.rows"), _u32(c["cols"], "calibration.cols"))
-    return QuantizationConfig(quant_method=req("quant_method", _string), bits=req("bits", number), head_bits=req("head_bits", _u32),
-                              codebook=opt("codebook", _string), version=opt("version", _string),
-                              vision_bits=opt("vision_bits", _u32), mtp_bits=opt("mtp_bits", _u32),
-                              out_scales=opt("out_scales", _string), calibration=calibration)
+            arch_string=s(c.arch_string), num_hidden_layers=int(c.num_hidden_layers), hidden_size=int(c.hidden_size),
+            intermediate_size=o(c.intermediate_size), head_dim=int(c.head_dim), num_attention_heads=int(c.num_attention_heads),
+            num_key_value_heads=int(c.num_key_value_heads), vocab_size=int(c.vocab_size),
+            tie_word_embeddings=bool(c.tie_word_embeddings), layer_types=tuple(c.layer_types[i].decode() for i in range(c.n_layer_types)),
+            linear_conv_kernel_dim=int(c.linear_conv_kernel_dim), linear_num_key_heads=int(c.linear_num_key_heads),
+            linear_num_value_heads=int(c.linear_num_value_heads), linear_key_head_dim=int(c.linear_key_head_dim),
+            linear_value_head_dim=int(c.linear_value_head_dim), attn_output_gate=bool(c.attn_output_gate),
+            num_experts=o(c.num_experts), num_experts_per_tok=o(c.num_experts_per_tok), moe_intermediate_size=o(c.moe_intermediate_size),
+            shared_expert_intermediate_size=o(c.shared_expert_intermediate_size), quantization=quant)
+    finally:
+        _lib.lib().berth_config_free(out)

@@ -13,6 +13,8 @@
 #include <cerrno>
 #include <cstdio>
 #include <cstdlib>
+#include <cmath>
+#include <cstdio>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -39,6 +41,7 @@ struct Json {
     bool b = false;
     double num = 0;
     bool is_u64 = false;
+    bool fraction = false;   // the token was written with a fraction or an exponent
     uint64_t u64 = 0;
     std::string str;
     std::vector<Json> items;
@@ -160,6 +163,7 @@ private:
         v.kind = Json::Number;
         const std::string text(s, p_);
         v.num = std::strtod(text.c_str(), nullptr);
+        v.fraction = text.find_first_of(".eE") != std::string::npos;
         if (integral && text.size() <= 20) {
             unsigned long long u = 0;
             bool ok = true;
@@ -724,4 +728,237 @@ extern "C" int berth_unpack_signs(const void* packed_le, uint64_t bytes, uint16_
         if (bytes) { need(packed_le, "packed signs"); need(out, "output"); }
         unpack_signs(static_cast<const unsigned char*>(packed_le), bytes, out);
     });
+}
+
+// ---------------------------------------------------------------- config.json (crates/berth-exl3/src/config.rs)
+namespace {
+
+struct MissingField : std::runtime_error {
+    explicit MissingField(const std::string& field) : std::runtime_error("missing field `" + field + "`") {}
+};
+struct BadConfig : std::runtime_error {
+    BadConfig(const std::string& field, const std::string& detail) : std::runtime_error("field `" + field + "`: " + detail) {}
+};
+
+// A number as serde_json prints it: integers without a fraction, other values with the shortest digits that read back.
+std::string number_text(const Json& v)
+{
+    if (v.is_u64) return std::to_string(v.u64);
+    if (std::isfinite(v.num) && v.num == std::floor(v.num) && std::fabs(v.num) < 9.0e15 && !v.fraction)
+        return std::to_string((long long) v.num);
+    char buf[40];
+    for (int prec = 1; prec <= 17; ++prec) {
+        std::snprintf(buf, sizeof buf, "%.*g", prec, v.num);
+        if (std::strtod(buf, nullptr) == v.num) break;
+    }
+    std::string s(buf);
+    if (s.find_first_of(".eEn") == std::string::npos) s += ".0";
+    return s;
+}
+std::string quoted(const std::string& s)
+{
+    std::string out = "\"";
+    for (char c : s) {
+        if (c == '"' || c == '\\') { out += '\\'; out += c; }
+        else if (c == '\n') out += "\\n";
+        else if (c == '\t') out += "\\t";
+        else if (c == '\r') out += "\\r";
+        else out += c;
+    }
+    return out + "\"";
+}
+// config.rs:381-391
+std::string describe(const Json& v)
+{
+    switch (v.kind) {
+        case Json::Null: return "null";
+        case Json::Bool: return v.b ? "true" : "false";
+        case Json::Number: return number_text(v);
+        case Json::String: return v.str.size() < 64 ? "string " + quoted(v.str) : "a long string";
+        case Json::Array: return "an array";
+        default: return "an object";
+    }
+}
+const Json* lookup(const Json& root, const Json* text, const char* key)
+{
+    if (text)
+        if (const Json* v = text->get(key)) return v;
+    return root.get(key);
+}
+const Json& require(const Json& root, const Json* text, const char* key)
+{
+    const Json* v = lookup(root, text, key);
+    if (!v) throw MissingField(key);
+    return *v;
+}
+// Integers, or floats that are exactly an integer (config.rs:360-379).
+uint32_t expect_u32(const Json& v, const std::string& field)
+{
+    if (v.kind == Json::Number) {
+        if (v.is_u64) {
+            if (v.u64 > 0xffffffffull) throw BadConfig(field, "integer " + std::to_string(v.u64) + " does not fit in u32");
+            return uint32_t(v.u64);
+        }
+        if (std::isfinite(v.num) && v.num >= 0.0 && v.num == std::floor(v.num) && v.num <= 4294967295.0) return uint32_t(v.num);
+    }
+    throw BadConfig(field, "expected a non-negative integer, got " + describe(v));
+}
+bool expect_bool(const Json& v, const std::string& field)
+{
+    if (v.kind != Json::Bool) throw BadConfig(field, "expected a bool, got " + describe(v));
+    return v.b;
+}
+std::string expect_string(const Json& v, const std::string& field)
+{
+    if (v.kind != Json::String) throw BadConfig(field, "expected a string, got " + describe(v));
+    return v.str;
+}
+
+}  // namespace
+
+struct berth_config_strings {
+    std::string arch, quant_method, codebook, version, out_scales;
+    std::vector<std::string> layer_types;
+    std::vector<const char*> layer_ptrs;
+};
+
+namespace {
+
+void parse_config(const char* json, uint64_t bytes, berth_model_config& c, berth_config_strings& s)
+{
+    const Json root = JsonParser(json, size_t(bytes), "config.json").parse();
+    if (root.kind != Json::Object) throw BadConfig("config.json", "expected a JSON object");
+    const Json* text = root.get("text_config");
+    if (text && text->kind != Json::Object) throw BadConfig("text_config", "expected an object, got " + describe(*text));
+
+    const Json* arch = root.get("architectures");
+    if (!arch) throw MissingField("architectures");
+    if (arch->kind != Json::Array) throw BadConfig("architectures", "expected an array, got " + describe(*arch));
+    if (arch->items.empty()) throw BadConfig("architectures", "expected a non-empty array");
+    if (arch->items[0].kind != Json::String) throw BadConfig("architectures", "expected a string, got " + describe(arch->items[0]));
+    if (arch->items[0].str.empty()) throw BadConfig("architectures", "architecture string is empty");
+    s.arch = arch->items[0].str;
+
+    c.num_hidden_layers = expect_u32(require(root, text, "num_hidden_layers"), "num_hidden_layers");
+    const Json& lt = require(root, text, "layer_types");
+    if (lt.kind != Json::Array) throw BadConfig("layer_types", "expected an array, got " + describe(lt));
+    for (const Json& item : lt.items) {
+        if (item.kind != Json::String) throw BadConfig("layer_types", "expected strings, got " + describe(item));
+        s.layer_types.push_back(item.str);
+    }
+    if (s.layer_types.size() != c.num_hidden_layers)
+        throw BadConfig("layer_types", "length " + std::to_string(s.layer_types.size()) + " does not match num_hidden_layers " +
+                                           std::to_string(c.num_hidden_layers));
+    const Json* quant = root.get("quantization_config");
+    if (!quant) throw MissingField("quantization_config");
+
+    auto req = [&](const char* key) { return expect_u32(require(root, text, key), key); };
+    auto opt = [&](const char* key) -> int64_t {
+        const Json* v = lookup(root, text, key);
+        return v ? int64_t(expect_u32(*v, key)) : -1;
+    };
+    c.hidden_size = req("hidden_size");
+    c.intermediate_size = opt("intermediate_size");
+    c.head_dim = req("head_dim");
+    c.num_attention_heads = req("num_attention_heads");
+    c.num_key_value_heads = req("num_key_value_heads");
+    c.vocab_size = req("vocab_size");
+    c.tie_word_embeddings = expect_bool(require(root, text, "tie_word_embeddings"), "tie_word_embeddings") ? 1 : 0;
+    c.linear_conv_kernel_dim = req("linear_conv_kernel_dim");
+    c.linear_num_key_heads = req("linear_num_key_heads");
+    c.linear_num_value_heads = req("linear_num_value_heads");
+    c.linear_key_head_dim = req("linear_key_head_dim");
+    c.linear_value_head_dim = req("linear_value_head_dim");
+    c.attn_output_gate = expect_bool(require(root, text, "attn_output_gate"), "attn_output_gate") ? 1 : 0;
+    c.num_experts = opt("num_experts");
+    c.num_experts_per_tok = opt("num_experts_per_tok");
+    c.moe_intermediate_size = opt("moe_intermediate_size");
+    c.shared_expert_intermediate_size = opt("shared_expert_intermediate_size");
+
+    if (quant->kind != Json::Object) throw BadConfig("quantization_config", "expected an object, got " + describe(*quant));
+    auto qreq = [&](const char* key) -> const Json& {
+        const Json* v = quant->get(key);
+        if (!v) throw MissingField(key);
+        return *v;
+    };
+    c.calibration_rows = c.calibration_cols = -1;
+    if (const Json* cal = quant->get("calibration")) {
+        if (cal->kind != Json::Object) throw BadConfig("calibration", "expected an object, got " + describe(*cal));
+        const Json* rows = cal->get("rows");
+        if (!rows) throw MissingField("calibration.rows");
+        const Json* cols = cal->get("cols");
+        if (!cols) throw MissingField("calibration.cols");
+        c.calibration_rows = expect_u32(*rows, "calibration.rows");
+        c.calibration_cols = expect_u32(*cols, "calibration.cols");
+    }
+    s.quant_method = expect_string(qreq("quant_method"), "quant_method");
+    const Json& bits = qreq("bits");
+    if (bits.kind != Json::Number) throw BadConfig("bits", "expected a number, got " + describe(bits));
+    if (!std::isfinite(bits.num) || bits.num < 0.0) throw BadConfig("bits", "expected a non-negative finite number, got " + number_text(bits));
+    c.bits = bits.num;
+    c.head_bits = expect_u32(qreq("head_bits"), "head_bits");
+    auto qstr = [&](const char* key, std::string& dst) -> const char* {
+        const Json* v = quant->get(key);
+        if (!v) return nullptr;
+        dst = expect_string(*v, key);
+        return dst.c_str();
+    };
+    auto qopt = [&](const char* key) -> int64_t {
+        const Json* v = quant->get(key);
+        return v ? int64_t(expect_u32(*v, key)) : -1;
+    };
+    c.codebook = qstr("codebook", s.codebook);
+    c.version = qstr("version", s.version);
+    c.vision_bits = qopt("vision_bits");
+    c.mtp_bits = qopt("mtp_bits");
+    c.out_scales = qstr("out_scales", s.out_scales);
+    c.arch_string = s.arch.c_str();
+    c.quant_method = s.quant_method.c_str();
+    for (const std::string& t : s.layer_types) s.layer_ptrs.push_back(t.c_str());
+    c.n_layer_types = int64_t(s.layer_ptrs.size());
+    c.layer_types = s.layer_ptrs.data();
+}
+
+}  // namespace
+
+extern "C" int berth_config_parse(const char* json, uint64_t bytes, berth_model_config** out)
+{
+    return guarded([&] {
+        need(json, "json");
+        need(out, "out");
+        *out = nullptr;
+        auto* c = new berth_model_config();
+        auto* s = new berth_config_strings();
+        c->strings = s;
+        try {
+            parse_config(json, bytes, *c, *s);
+        } catch (...) {
+            delete s;
+            delete c;
+            throw;
+        }
+        *out = c;
+    });
+}
+
+extern "C" int berth_config_open(const char* directory, berth_model_config** out)
+{
+    std::string text;
+    const int rc = guarded([&] {
+        need(directory, "directory");
+        need(out, "out");
+        *out = nullptr;
+        const std::string path = std::string(directory) + "/config.json";
+        if (!is_file(path)) throw std::runtime_error(path + ": No such file or directory");
+        text = read_whole(path, kMaxIndexBytes);
+    });
+    if (rc != 0) return rc;
+    return berth_config_parse(text.data(), text.size(), out);
+}
+
+extern "C" void berth_config_free(berth_model_config* c)
+{
+    if (!c) return;
+    delete c->strings;
+    delete c;
 }

@@ -8,8 +8,8 @@
  *   unpack_signs                                  crates/berth-exl3/src/signs.rs:25-45
  * Host memory only; nothing here touches a GPU.  Every function that can fail returns 0 on success and -1 on
  * error with the message in berth_ckpt_last_error() (thread-local, valid until the next call on the thread).
- * Messages name the offending tensor or field first, as berth's Error::BadField does; model config parsing
- * (config.json) is not part of this reader. */
+ * Messages name the offending tensor or field first, as berth's Error::BadField does.  berth_config_* reads config.json
+ * (ModelConfig / QuantizationConfig of crates/berth-exl3/src/config.rs). */
 #ifndef BERTH_B200_CHECKPOINT_H
 #define BERTH_B200_CHECKPOINT_H
 
@@ -73,6 +73,34 @@ int berth_ckpt_scale_f16(const berth_ckpt* ckpt, const char* prefix, int output_
 /* Packed little-endian int16 sign words -> fp16 bit patterns: bit i of a word is element i, a set bit is -1.0
  * (0xBC00), a clear bit +1.0 (0x3C00).  `bytes` must be even; out receives bytes * 8 values. */
 int berth_unpack_signs(const void* packed_le, uint64_t bytes, uint16_t* out);
+
+/* config.json: the text stack and the quantization block (crates/berth-exl3/src/config.rs:52-160).  Text fields are read
+ * from `text_config` when that object holds the key, else from the top level; `architectures` and `quantization_config`
+ * are top-level; unknown keys are ignored; integers may be written as integer-valued floats.  Optional integers are -1
+ * and optional strings NULL when absent.  Errors through berth_ckpt_last_error with berth's wording: "missing field `x`"
+ * or "field `x`: detail".  Strings and the layer_types array stay valid until berth_config_free. */
+typedef struct berth_config_strings berth_config_strings;
+typedef struct {
+    const char* arch_string;                 /* architectures[0] */
+    uint32_t num_hidden_layers, hidden_size, head_dim, num_attention_heads, num_key_value_heads, vocab_size;
+    int tie_word_embeddings, attn_output_gate;
+    uint32_t linear_conv_kernel_dim, linear_num_key_heads, linear_num_value_heads, linear_key_head_dim, linear_value_head_dim;
+    int64_t intermediate_size, num_experts, num_experts_per_tok, moe_intermediate_size, shared_expert_intermediate_size;
+    int64_t n_layer_types;                   /* = num_hidden_layers */
+    const char* const* layer_types;          /* "linear_attention", "full_attention", or any other string as written */
+    /* quantization_config */
+    const char* quant_method;
+    double bits;
+    uint32_t head_bits;
+    const char* codebook;
+    const char* version;
+    const char* out_scales;
+    int64_t vision_bits, mtp_bits, calibration_rows, calibration_cols;
+    berth_config_strings* strings;           /* owner of the strings above */
+} berth_model_config;
+int berth_config_parse(const char* json, uint64_t bytes, berth_model_config** out);
+int berth_config_open(const char* directory, berth_model_config** out);   /* <directory>/config.json */
+void berth_config_free(berth_model_config* config);
 
 const char* berth_ckpt_last_error(void);
 
