@@ -44,7 +44,7 @@ METRIC = "exl3_gemv_eff_hbm_gbs"
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode launch over the stacked gate and up projections
 # (2 x 5120x17408, 4 bpw, one row) from an ncu capture of this file's own step; valid for one row only.
-NCU_TRAFFIC_GATE_UP_BYTES = 92_397_312   # 89.35 MB read + 3.05 MB written
+NCU_TRAFFIC_GATE_UP_BYTES = 92_805_120   # 89.35 MB read + 3.46 MB written
 
 
 def linear_bytes(k: int, n: int, m: int, fp32: int, bits: int = BITS) -> int:
