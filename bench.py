@@ -170,15 +170,16 @@ class DecodeStack:
             lin["qkv"] = SlicedMultiLinear(self.gpu, [lin["q"], lin["k"], lin["v"]], OutDtype.F16, max_rows=m,
                                            outputs=[self.q, self.k, self.v])
             self.layers.append((mlp, lin))
-        # one row: gate+up (one stacked integer-path launch, rotation and finishing inside it), down and o (the same kernel,
-        # one launch each), q/k/v (the same kernel over the three matrices, one launch), k_silu_mul = 5 launches.
-        # two rows: the stacked launch, down and o on the fp16-path kernel (k_exl3_gemv + k_gemv_finish each), q/k/v, silu = 7.
+        # one row: gate+up (one stacked integer-path launch, rotation and finishing inside it), down (the same kernel, with
+        # silu(gate) * up formed in its rotation) and o (one launch each), q/k/v (the same kernel over the three matrices,
+        # one launch) = 4 launches.
+        # two rows: the stacked launch, down and o on the fp16-path kernel (k_exl3_gemv + k_gemv_finish each), q/k/v = 6.
         # 3..4 rows: k_rotate_in_i8 per stacked matrix + the stacked launch, down and o with k_rotate_in + k_exl3_gemv +
-        # k_gemv_finish each, q/k/v (one launch), silu = 11.
-        # above: gate, up, down, o with three launches each (k_rotate_in + k_exl3_gemv + k_gemv_finish up to 16 rows,
-        # k_had128 + k_exl3_gemm_tc_splitk + k_sk_finish from 17), q/k/v as one sliced launch of the fp16-path kernel
-        # (k_rotate_in + k_exl3_gemv + k_gemv_finish), silu = 16.
-        self.launches_per_step = 5 if m == 1 else (7 if m == 2 else (11 if m <= 4 else 16))
+        # k_gemv_finish each, q/k/v (one launch) = 10.
+        # 5..16 rows: gate, up, down, o with three launches each (k_rotate_in + k_exl3_gemv + k_gemv_finish), q/k/v as one
+        # sliced launch of the fp16-path kernel (k_rotate_in + k_exl3_gemv + k_gemv_finish) = 15.
+        # above: the same with k_had128 + k_exl3_gemm_tc_splitk + k_sk_finish per linear, and k_silu_mul = 16.
+        self.launches_per_step = 4 if m == 1 else (6 if m == 2 else (10 if m <= 4 else (15 if m <= 16 else 16)))
 
     def step(self, i: int) -> None:
         from berth_b200.kernels import OutDtype

@@ -59,6 +59,7 @@ SIGNATURES = {
     "berth_exl3_linear_argmax": (_i, [_vp] * 7 + [_i] * 6 + [_vp]),
     "berth_exl3_linear_sample": (_i, [_vp] * 7 + [_i] * 6 + [_f, C.c_uint, _i, _vp]),
     "berth_exl3_linear_add": (_i, [_vp] * 7 + [_i] * 5 + [_vp]),
+    "berth_exl3_linear_silu": (_i, [_vp] * 8 + [_f] + [_i] * 6 + [_vp]),
     "berth_exl3_linear_stack": (_i, [_vp] * 6 + [_i] * 7 + [_vp]),
     "berth_exl3_weights_streamed": (_i, [_i]),
     "berth_exl3_linear_multi": (_i, [_vp] * 7 + [_i] * 6 + [_vp]),

@@ -209,10 +209,16 @@ struct SampleArgs {
     unsigned random = 0;
     int gumbel = 0;
 };
+// With `up` set the linear's input is silu(a) * up (both fp16 [m][k]), clamped to +-limit when that is not 0: the
+// rotation applies it on the fly, rounded step by step as k_silu_mul rounds it.
+struct ActInput {
+    const void* up = nullptr;
+    float limit = 0.f;
+};
 std::string launch_gemv(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32,
                         const GemvScratch& scratch, int sms, cudaStream_t stream, unsigned long long* argmax = nullptr,
-                        const float* residual = nullptr, const SampleArgs& sample = SampleArgs{});
+                        const float* residual = nullptr, const SampleArgs& sample = SampleArgs{}, const ActInput& act = ActInput{});
 
 // The same linear for the MUL1 codebook on the integer tensor path (gemv_i8.cu), up to kI8MaxRows rows; launch_gemv
 // forwards one to four rows to it (above, the limb tiles of the rows cost more L2 traffic than the fp16 path's
@@ -221,7 +227,7 @@ constexpr int kI8MaxRows = 8;
 std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                            int size_m, int size_k, int size_n, int k_bits, int out_fp32, const GemvScratch& scratch, int sms,
                            cudaStream_t stream, unsigned long long* argmax, int n_stack = 1, const float* residual = nullptr,
-                           const SampleArgs& sample = SampleArgs{});
+                           const SampleArgs& sample = SampleArgs{}, const ActInput& act = ActInput{});
 
 // The integer-path decode kernel over up to four MUL1 matrices of different widths applied to the same rows (host arrays
 // of device pointers and widths); same contract as launch_gemv per matrix.

@@ -228,7 +228,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv(const __grid_constant
                 const long long uu = u0 + i;
                 const int gbg = int(uu / kblocks), kb = int(uu - (long long) gbg * kblocks);
                 float sx;
-                const uint2 o = rotate_block<CB == 2>(p.a + size_t(t) * p.k, p.suh, kb, lane, sx);
+                const uint2 o = rotate_block<CB == 2>(p.a + size_t(t) * p.k, p.suh, kb, lane, sx, p.a_up ? p.a_up + size_t(t) * p.k : nullptr, p.act_limit);
                 // lane holds k_in = 4*(lane&3) .. +3 of k-tile (lane/4) of the block: half h = k_in/8, pair index (k_in%8)/2
                 *reinterpret_cast<uint2*>(actbuf + i * (ACT_BYTES / 4) + ((lane >> 2) * 2 + ((lane & 3) >> 1)) * 32 + t * 4 + 2 * (lane & 1)) = o;
                 if (gbg == 0) {   // band group 0 meets every 128-block exactly once
@@ -443,7 +443,8 @@ __global__ void __launch_bounds__(256) k_gemv_finish(const FinishArgs p)
 __global__ void __launch_bounds__(128) k_rotate_in(const __half* __restrict__ a, const __half* __restrict__ suh_in,
                                                    __half* __restrict__ a_had, uint32_t* __restrict__ afrag,
                                                    float* __restrict__ blocksum, int rows, int rows_pad, int k,
-                                                   const unsigned long long* __restrict__ suh_list, int src, long long a_src_stride)
+                                                   const unsigned long long* __restrict__ suh_list, int src, long long a_src_stride,
+                                                   const __half* __restrict__ a_up, float act_limit)
 {
     // Trigger first: the decode kernel behind this one may then take each SM as the previous decode
     // kernel leaves it and prefetch its weights; it still waits for this grid, which itself waits here
@@ -466,7 +467,7 @@ __global__ void __launch_bounds__(128) k_rotate_in(const __half* __restrict__ a,
         uint2 o = make_uint2(0u, 0u);
         if (row < rows) {
             float sx;
-            o = rotate_block<true>(a + size_t(row) * k, suh, b, lane, sx);
+            o = rotate_block<true>(a + size_t(row) * k, suh, b, lane, sx, a_up ? a_up + size_t(row) * k : nullptr, act_limit);
             *reinterpret_cast<uint2*>(a_had + size_t(row) * k + b * 128 + lane * 4) = o;
             if (lane == 0) blocksum[row * kblocks + b] = sx;
         }
@@ -659,7 +660,7 @@ void launch_finish(const GemvArgs& a, int bu, int tok, int main_grid, int mul1, 
 std::string launch_gemv(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                         int size_m, int size_k, int size_n, int k_bits, int codebook, int out_fp32,
                         const GemvScratch& sc, int sms, cudaStream_t stream, unsigned long long* argmax, const float* residual,
-                        const SampleArgs& sample)
+                        const SampleArgs& sample, const ActInput& act)
 {
     if (residual && !out_fp32) throw std::runtime_error("exl3 linear: the residual is added to fp32 outputs only");
     if (size_m > 32) throw std::runtime_error("exl3 gemv: size_m must be <= 32");
@@ -669,7 +670,7 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
     // MUL1, one row, every CTA's units within the limb area of the in-kernel rotation: integer tensor path with the
     // weights in tensor memory (measured a few percent ahead of this kernel there, behind it elsewhere)
     if (codebook == 2 && size_m == 1 && gemv_i8_rotates_in_kernel(size_m, size_k, size_n, k_bits, sms))
-        return launch_gemv_i8(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, out_fp32, sc, sms, stream, argmax, 1, residual, sample);
+        return launch_gemv_i8(a, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, out_fp32, sc, sms, stream, argmax, 1, residual, sample, act);
     const int tg = size_m <= 8 ? 1 : (size_m <= 16 ? 2 : 4);
     const int bu = k_bits <= 4 ? 2 : 1;   // bands per unit, as Geo<BITS, TG>::BU
     const int bands = size_n / 128, kblocks = size_k / 128, bgroups = (bands + bu - 1) / bu;
@@ -696,13 +697,16 @@ std::string launch_gemv(const void* a, const void* trellis, void* c, const void*
         const int rot_total = 8 * tg * kblocks;
         launch_pdl(k_rotate_in, dim3(std::min((rot_total + 3) / 4, 4 * sms)), dim3(128), 0, stream, "k_rotate_in launch",
                    static_cast<const __half*>(a), static_cast<const __half*>(suh), static_cast<__half*>(a_had), sc.afrag,
-                   sc.blocksum, size_m, 8 * tg, size_k, (const unsigned long long*) nullptr, 0, 0LL);
+                   sc.blocksum, size_m, 8 * tg, size_k, (const unsigned long long*) nullptr, 0, 0LL,
+                   static_cast<const __half*>(act.up), act.limit);
     }
 
-    GemvArgs args;
+    GemvArgs args{};
     args.defer_weights = weights_streamed() ? 1 : 0;
     args.afrag = sc.afrag;
     args.blocksum = sc.blocksum;
+    args.a_up = static_cast<const __half*>(act.up);
+    args.act_limit = act.limit;
     args.a = static_cast<const __half*>(a);
     args.suh = static_cast<const __half*>(suh);
     args.a_had = static_cast<__half*>(a_had);
@@ -762,7 +766,7 @@ std::string launch_gemv_grouped_rotated(const void* trellis_stack, int n_experts
     const size_t per_cta = size_t(2) * 8 * tg * bu * 128 * sizeof(float);
     if (size_t(grid) * per_cta > sc.slab_bytes) grid = int(sc.slab_bytes / per_cta);
     if (grid < 1) throw std::runtime_error("exl3 grouped gemv: split-K scratch is too small");
-    GemvArgs args;
+    GemvArgs args{};
     args.defer_weights = weights_streamed() ? 1 : 0;
     args.afrag = afrag;
     args.blocksum = blocksum;
@@ -876,8 +880,8 @@ std::string launch_gemv_sliced(const void* a, const void* b_list, const void* su
     const int rot_total = 8 * tg * kblocks;
     launch_pdl(k_rotate_in, dim3(std::min((rot_total + 3) / 4, 4 * sms), num_had_src), dim3(128), 0, stream, "k_rotate_in launch",
                static_cast<const __half*>(a), (const __half*) nullptr, static_cast<__half*>(a_had), sc.afrag, sc.blocksum, size_m, 8 * tg,
-               size_k, static_cast<const unsigned long long*>(suh_list), 0, a_src_stride);
-    GemvArgs args;
+               size_k, static_cast<const unsigned long long*>(suh_list), 0, a_src_stride, (const __half*) nullptr, 0.f);
+    GemvArgs args{};
     args.defer_weights = weights_streamed() ? 1 : 0;
     args.afrag = sc.afrag;
     args.blocksum = sc.blocksum;

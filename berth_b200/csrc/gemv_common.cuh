@@ -5,6 +5,7 @@
 #pragma once
 
 #include "exl3_decode.cuh"
+#include "silu.cuh"
 
 #include <cuda.h>
 
@@ -27,6 +28,8 @@ struct GemvArgs {
     const __half* a;          // in-kernel rotation only: activations [m][k], input sign-scale [k], and the
     const __half* suh;        //   caller's buffer for the rotated activations [m][k]
     __half* a_had;
+    const __half* a_up;       // may be null; else the rotation's input is silu(a) * a_up (rows [m][k]), clamped to +-act_limit
+    float act_limit;          //   when that is not 0, every step rounded to fp16 as k_silu_mul rounds it
     void* c;                  // output rows [rows][n]
     unsigned long long* argmax;   // dense launch only, may be null: per row the key of its largest output (finish_band)
     SampleArgs sample;            // how those keys are scored
@@ -187,11 +190,22 @@ template <bool SUM>
 __device__ __forceinline__ uint2 rotate_bits(uint2 xr, uint2 sr, int lane, float& sx);
 
 template <bool SUM>
-__device__ __forceinline__ uint2 rotate_block(const __half* __restrict__ xrow, const __half* __restrict__ suh, int kb, int lane, float& sx)
+__device__ __forceinline__ uint2 rotate_block(const __half* __restrict__ xrow, const __half* __restrict__ suh, int kb, int lane, float& sx,
+                                              const __half* __restrict__ urow = nullptr, float act_limit = 0.f)
 {
     const int kcol = kb * 128 + lane * 4;
-    const uint2 xr = *reinterpret_cast<const uint2*>(xrow + kcol);
+    uint2 xr = *reinterpret_cast<const uint2*>(xrow + kcol);
     const uint2 sr = *reinterpret_cast<const uint2*>(suh + kcol);
+    if (urow) {   // the input is silu(xrow) * urow, rounded as the element-wise kernel rounds it
+        const uint2 ur = *reinterpret_cast<const uint2*>(urow + kcol);
+        const __half* g = reinterpret_cast<const __half*>(&xr);
+        const __half* u = reinterpret_cast<const __half*>(&ur);
+        __half o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[i] = silu_mul_one(g[i], u[i], act_limit);
+        xr.x = dq::pack_half2(o[0], o[1]);
+        xr.y = dq::pack_half2(o[2], o[3]);
+    }
     return rotate_bits<SUM>(xr, sr, lane, sx);
 }
 

@@ -337,7 +337,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
                     int pi, lbg;   // matrix of the stack, band group inside it
                     split_bg(gbg, pi, lbg);
                     float sx;
-                    const uint2 o = rotate_block<false>(p.a + size_t(t) * p.k, p.het ? p.het_suh[pi] : p.suh + size_t(pi) * p.k, kb, lane, sx);
+                    const uint2 o = rotate_block<false>(p.a + size_t(t) * p.k, p.het ? p.het_suh[pi] : p.suh + size_t(pi) * p.k, kb, lane, sx,
+                                                               p.a_up ? p.a_up + size_t(t) * p.k : nullptr, p.act_limit);
                     int isum;
                     const float scale = quantise_block(o, lane, area + size_t(j) * ftile + t * 32, 2 * flbo, flbo, isum);
                     if (lane == 0) {
@@ -651,7 +652,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
 // not written: their accumulator columns are never read.
 __global__ void __launch_bounds__(128) k_rotate_in_i8(const __half* __restrict__ a, const __half* __restrict__ suh,
                                                       __half* __restrict__ a_had, unsigned char* __restrict__ limbs,
-                                                      float* __restrict__ blocksum, int rows, int k, int nb)
+                                                      float* __restrict__ blocksum, int rows, int k, int nb,
+                                                      const __half* __restrict__ a_up, float act_limit)
 {
     pdl_trigger();
     pdl_wait();
@@ -660,7 +662,7 @@ __global__ void __launch_bounds__(128) k_rotate_in_i8(const __half* __restrict__
     for (int idx = blockIdx.x * 4 + (threadIdx.x >> 5); idx < total; idx += gridDim.x * 4) {
         const int row = idx / kblocks, b = idx - row * kblocks;
         float sx;
-        const uint2 o = rotate_block<false>(a + size_t(row) * k, suh, b, lane, sx);
+        const uint2 o = rotate_block<false>(a + size_t(row) * k, suh, b, lane, sx, a_up ? a_up + size_t(row) * k : nullptr, act_limit);
         *reinterpret_cast<uint2*>(a_had + size_t(row) * k + b * 128 + lane * 4) = o;
         const size_t record = size_t(16) * nb * 256 + 128;          // limbs, then the block's scales (one per row)
         int isum;
@@ -757,7 +759,8 @@ bool gemv_i8_rotates_in_kernel(int size_m, int size_k, int size_n, int k_bits, i
 // same contract as launch_gemv.
 std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const void* suh, void* a_had, const void* svh,
                            int size_m, int size_k, int size_n, int k_bits, int out_fp32, const GemvScratch& sc, int sms,
-                           cudaStream_t stream, unsigned long long* argmax, int n_stack, const float* residual, const SampleArgs& sample)
+                           cudaStream_t stream, unsigned long long* argmax, int n_stack, const float* residual, const SampleArgs& sample,
+                           const ActInput& act)
 {
     if (n_stack < 1) n_stack = 1;
     if (size_m > kI8MaxRows) throw std::runtime_error("exl3 gemv (integer tensor path): size_m must be <= 8");
@@ -792,13 +795,15 @@ std::string launch_gemv_i8(const void* a, const void* trellis, void* c, const vo
                        static_cast<const __half*>(a), static_cast<const __half*>(suh) + size_t(i) * size_k,
                        static_cast<__half*>(a_had) + size_t(i) * size_m * size_k,
                        reinterpret_cast<unsigned char*>(sc.afrag) + size_t(i) * limb_bytes, sc.blocksum + size_t(i) * size_m * kblocks,
-                       size_m, size_k, nb);
+                       size_m, size_k, nb, static_cast<const __half*>(act.up), act.limit);
 
     GemvArgs args{};
     args.defer_weights = weights_streamed() ? 1 : 0;
     args.afrag = sc.afrag;
     args.blocksum = sc.blocksum;
     args.a = static_cast<const __half*>(a);
+    args.a_up = static_cast<const __half*>(act.up);
+    args.act_limit = act.limit;
     args.suh = static_cast<const __half*>(suh);
     args.a_had = static_cast<__half*>(a_had);
     args.c = c;
@@ -869,7 +874,7 @@ std::string launch_gemv_i8_multi(const void* a, const void* const* trellis, void
             launch_pdl(k_rotate_in_i8, dim3(std::min((rot_total + 3) / 4, 4 * sms)), dim3(128), 0, stream, "k_rotate_in_i8 launch",
                        static_cast<const __half*>(a), args.het_suh[i], args.het_a_had[i],
                        reinterpret_cast<unsigned char*>(sc.afrag) + size_t(i) * limb_bytes, sc.blocksum + size_t(i) * size_m * kblocks,
-                       size_m, size_k, nb);
+                       size_m, size_k, nb, (const __half*) nullptr, 0.f);
     args.afrag = sc.afrag;
     args.blocksum = sc.blocksum;
     args.a = static_cast<const __half*>(a);

@@ -240,6 +240,33 @@ extern "C" int berth_exl3_linear_add(const void* a, const void* trellis, void* c
     });
 }
 
+// The down projection of an MLP with the activation taken on the fly: c = [residual +] linear(silu(gate) * up).  What berth
+// does with berth_ops_silu_mul, berth_exl3_linear and (in the decode block) berth_ops_add_f32
+// (crates/berth-engine/src/mlp.rs:128-160, model.rs:976-1022), without the launch and the buffer of the activation.
+extern "C" int berth_exl3_linear_silu(const void* gate, const void* up, const void* trellis, void* c, const void* suh, void* a_had,
+                                      const void* svh, const void* residual, float act_limit, int size_m, int size_k, int size_n,
+                                      int k_bits, int codebook, int out_fp32, void* stream)
+{
+    CallState& st = exl3_state();
+    return guarded(st, [&] {
+        if (!gate || !up || !trellis || !c || !suh || !a_had || !svh) throw std::runtime_error("exl3 linear silu: null device pointer");
+        if (size_m < 1 || size_k < 1 || size_n < 1) throw std::runtime_error("exl3 linear silu: sizes must be positive");
+        if (size_m > 32) throw std::runtime_error("exl3 linear silu: size_m must be <= 32 (the decode kernels)");
+        if (residual && !out_fp32) throw std::runtime_error("exl3 linear silu: the residual is added to fp32 outputs only");
+        check_linear_args("exl3 linear silu", gate, trellis, c, suh, a_had, svh, size_k, size_n, k_bits, codebook);
+        const int device = current_device();
+        const DeviceInfo& info = device_info(device);
+        if (info.major != 10)
+            throw std::runtime_error("exl3 linear silu: no linked kernel for this GPU (library is built for sm_100a only)");
+        ActInput act;
+        act.up = up;
+        act.limit = act_limit;
+        st.launch = launch_gemv(gate, trellis, c, suh, a_had, svh, size_m, size_k, size_n, k_bits, codebook, out_fp32,
+                                gemv_workspace(device), info.sms, (cudaStream_t) stream, nullptr, static_cast<const float*>(residual),
+                                SampleArgs{}, act) + " [silu(gate) * up in the rotation" + (residual ? ", residual added in the last step]" : "]");
+    });
+}
+
 extern "C" void berth_argmax_key_decode(unsigned long long key, int32_t* token, float* value)
 {
     const uint32_t ord = uint32_t(key >> 32);

@@ -93,6 +93,20 @@ class Exl3Linear:
         kernels.exl3_linear(a, self.trellis, c, self.suh, self.a_had, self.svh, rows, self.size_k, self.size_n,
                             self.k_bits, self.codebook, out, gpu.raw_stream())
 
+    def forward_silu_n(self, gpu: Gpu, rows: int, gate: torch.Tensor, up: torch.Tensor, c: torch.Tensor, out: OutDtype,
+                       act_limit: float = 0.0, residual: torch.Tensor | None = None) -> None:
+        """``c = [residual +] (silu(gate) * up) @ W`` for up to 32 rows, the activation formed inside the launch (the
+        down projection of an MLP: crates/berth-engine/src/mlp.rs:128-160 without the ``silu_mul`` launch)."""
+        out_bytes = 2 if out == OutDtype.F16 else 4
+        need = rows * self.size_k * 2
+        if gate.numel() * gate.element_size() < need or up.numel() * up.element_size() < need or \
+                c.numel() * c.element_size() < rows * self.size_n * out_bytes:
+            raise Error(f"{self.prefix}: buffer too small")
+        if self.a_had.numel() < rows * self.size_k:
+            self.a_had = torch.zeros(rows * self.size_k, dtype=torch.float16, device=gpu.device)
+        kernels.exl3_linear_silu(gate, up, self.trellis, c, self.suh, self.a_had, self.svh, rows, self.size_k, self.size_n,
+                                 self.k_bits, self.codebook, out, act_limit, residual, gpu.raw_stream())
+
     def forward_argmax(self, gpu: Gpu, rows: int, a: torch.Tensor, best: torch.Tensor, c: torch.Tensor | None = None,
                        out: OutDtype = OutDtype.F32) -> None:
         """The decode launch of an lm_head with the greedy token of every row taken in its finishing step:
@@ -234,6 +248,10 @@ class RowScratch:
 class MlpLayer:
     """``output = down(silu(gate(input)) * up(input))``; gate/up fp16 out, down fp32 out."""
 
+    # up to here the down projection takes silu(gate) * up inside its own rotation (one launch and one buffer less; the
+    # decode kernel serves these row counts anyway); above, the element-wise kernel runs and the dispatcher chooses
+    FUSED_ACT_ROWS = 16
+
     def __init__(self, gpu: Gpu, gate: Exl3Linear, up: Exl3Linear, down: Exl3Linear, max_rows: int = 1):
         if gate.size_k != up.size_k or gate.size_n != up.size_n:
             raise Error(f"gate is {gate.size_k}x{gate.size_n}, up is {up.size_k}x{up.size_n}")
@@ -283,8 +301,20 @@ class MlpLayer:
             gate_out, up_out = self.gate_out, self.up_out
             self.gate.forward_n(gpu, rows, inp, gate_out, OutDtype.F16)
             self.up.forward_n(gpu, rows, inp, up_out, OutDtype.F16)
+        self._last = (gate_out, up_out, n)
+        if rows <= self.FUSED_ACT_ROWS:
+            self.down.forward_silu_n(gpu, rows, gate_out, up_out, output, OutDtype.F32, ACT_LIMIT)
+        else:
+            kernels.ops.silu_mul(gate_out, up_out, self.activated, n, ACT_LIMIT, gpu.raw_stream())
+            self.down.forward_n(gpu, rows, self.activated, output, OutDtype.F32)
+
+    def activation(self, gpu: Gpu) -> torch.Tensor:
+        """``silu(gate) * up`` of the last ``forward_n`` as fp16 ``[rows * intermediate]``.  Up to ``FUSED_ACT_ROWS`` rows
+        the down projection forms it on the fly and nothing holds it; this writes it out (the element-wise kernel on the
+        gate and up outputs, the same bits) for a caller that wants to look at it."""
+        gate_out, up_out, n = self._last
         kernels.ops.silu_mul(gate_out, up_out, self.activated, n, ACT_LIMIT, gpu.raw_stream())
-        self.down.forward_n(gpu, rows, self.activated, output, OutDtype.F32)
+        return self.activated[:n]
 
     def prefill(self, gpu: Gpu, rows: int, inp: torch.Tensor, output: torch.Tensor, scratch: RowScratch) -> None:
         """crates/berth-engine/src/mlp.rs:219-305."""

@@ -93,6 +93,18 @@ def exl3_linear_add(a, trellis, c, suh, a_had, svh, residual, size_m: int, size_
         raise Error(last_error() or f"exl3 linear add launch failed ({rc})")
 
 
+def exl3_linear_silu(gate, up, trellis, c, suh, a_had, svh, size_m: int, size_k: int, size_n: int, k_bits: int,
+                     codebook: Codebook, out: OutDtype, act_limit: float = 0.0, residual=None, stream=None) -> None:
+    """``c = [residual +] linear(silu(gate) * up)`` for ``size_m <= 32`` rows: the down projection of an MLP with the
+    activation formed inside the linear's rotation, bit for bit what ``ops.silu_mul`` followed by :func:`exl3_linear`
+    (and ``ops.add_f32``) gives, without the activation's launch and buffer."""
+    rc = _lib.lib().berth_exl3_linear_silu(_ptr(gate), _ptr(up), _ptr(trellis), _ptr(c), _ptr(suh), _ptr(a_had), _ptr(svh),
+                                           _ptr(residual) if residual is not None else None, float(act_limit), size_m, size_k,
+                                           size_n, k_bits, int(codebook), int(out), _stream(stream))
+    if rc != 0:
+        raise Error(last_error() or f"exl3 linear silu launch failed ({rc})")
+
+
 def exl3_linear_stack(a, trellis_stack, c, suh_stack, a_had, svh_stack, n_matrices: int, size_m: int, size_k: int, size_n: int,
                       k_bits: int, codebook: Codebook, out: OutDtype, stream=None) -> None:
     """``n_matrices`` equally shaped MUL1 linears (stored one behind the other) applied to the same ``size_m <= 8`` rows in

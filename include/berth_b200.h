@@ -160,6 +160,18 @@ int berth_exl3_linear_add(const void* a, const void* trellis, void* c, const voi
                           const void* residual, int size_m, int size_k, int size_n, int k_bits, int codebook,
                           void* stream);
 
+/* The down projection of an MLP with the activation taken on the fly (size_m <= 32, the decode kernels):
+ * c = [residual +] linear(silu(gate) * up), gate and up fp16 [size_m][size_k].  The rotation of the linear reads gate
+ * and up instead of an activation buffer and forms silu(gate) * up with every step rounded to fp16 and the clamp to
+ * +-act_limit (0 = none) exactly as berth_ops_silu_mul does, so c and a_had are bit for bit what
+ * berth_ops_silu_mul(gate, up, act) + berth_exl3_linear(act) [+ berth_ops_add_f32] give from the same kernel
+ * (crates/berth-engine/src/mlp.rs:128-160; the decode block's x += mlp(h2), model.rs:976-1022), one launch and one
+ * buffer less.  residual may be null; when set it is fp32 [size_m][size_n], needs out_fp32 = 1 and may be c itself.
+ * No counterpart in berth. */
+int berth_exl3_linear_silu(const void* gate, const void* up, const void* trellis, void* c, const void* suh, void* a_had,
+                           const void* svh, const void* residual, float act_limit, int size_m, int size_k, int size_n,
+                           int k_bits, int codebook, int out_fp32, void* stream);
+
 /* A stack of n_matrices equally shaped MUL1 linears applied to the same size_m <= 8 rows in ONE decode launch:
  * trellis_stack int16 [n][size_k/16][size_n/16][16*k_bits], suh_stack fp16 [n][size_k], svh_stack fp16 [n][size_n];
  * outputs c [n][size_m][size_n] and a_had [n][size_m][size_k].  What berth does for the gate and up projections of

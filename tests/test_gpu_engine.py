@@ -93,12 +93,13 @@ def test_mlp_layer_forward_vs_oracle(oracle, cb, rows):
     if cb == 2 and rows <= StackedLinear.BEST_ROWS:
         assert "stack of 2" in kernels.last_launch() or "k_exl3_gemv" in kernels.last_launch()
     g, u, act, y64 = _mlp_oracle(oracle, x, ws, H, I, bits, cb)
-    got_act = mlp.activated[:rows * I].float().cpu().numpy().reshape(rows, I)
+    own_act = mlp.activation(gpu).cpu().numpy().reshape(rows, I)   # up to 16 rows the layer never writes it out
+    got_act = own_act.astype(np.float32)
     rms_act = np.sqrt((act.astype(np.float64) ** 2).mean())
     assert np.abs(got_act - act.astype(np.float32)).max() <= 2e-2 * rms_act
     # the layer's own activations differ from the checker's by fp16 steps, which the down projection carries on: compare
     # with the fp64 evaluation of the down projection on the LAYER's activations, and loosely with the checker's chain
-    y64_own = oracle.linear_f64(mlp.activated[:rows * I].cpu().numpy().reshape(rows, I), ws["down"]["trellis"], ws["down"]["suh"],
+    y64_own = oracle.linear_f64(own_act, ws["down"]["trellis"], ws["down"]["suh"],
                                 ws["down"]["svh"], I, H, bits, cb)
     assert_close(out.cpu().numpy(), y64_own, "down on the layer's activations")
     rms = np.sqrt((y64 ** 2).mean())

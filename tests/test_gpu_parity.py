@@ -774,6 +774,59 @@ def test_linear_add_equals_linear_then_add(oracle, m, K, N, bits, cb):
     assert mx <= MAX_REL and mean <= MEAN_REL
 
 
+@pytest.mark.parametrize("m,K,N,bits,cb,limit,res", [
+    (1, 1024, 768, 4, 2, 0.0, False), (1, 17408, 5120, 4, 2, 0.0, True), (1, 2048, 1024, 6, 2, 3.0, False),
+    (2, 1024, 512, 4, 2, 0.0, True), (2, 512, 384, 3, 0, 0.0, False), (3, 512, 640, 4, 2, 1.5, True),
+    (8, 1024, 256, 5, 1, 0.0, False), (16, 512, 256, 2, 2, 0.0, False), (20, 512, 256, 5, 2, 0.0, True)])
+def test_linear_silu_equals_silu_mul_then_linear(oracle, m, K, N, bits, cb, limit, res):
+    """berth_exl3_linear_silu (silu(gate) * up formed inside the linear's rotation, optionally the residual added in the
+    last step) gives bit for bit the output AND the rotated activations of berth_ops_silu_mul followed by the same
+    decode launch on the activation buffer; and the output is the checker's fp64 linear of the checker's silu_mul within
+    the tolerance.  Covers the in-kernel rotation of both decode kernels and the separate rotation kernel, with a clamp
+    and without, and gate values large enough for the sigmoid to saturate."""
+    w = synth.linear_weights(1234, f"lsilu{K}x{N}b{bits}", K, N, bits)
+    g = (synth.activations(1234, f"lsilu.g{m}", m, K).astype(np.float32) * 3.0).astype(np.float16)
+    g[0, :4] = np.array([30.0, -30.0, 0.0, -0.0], dtype=np.float16)
+    u = synth.activations(1234, f"lsilu.u{m}", m, K)
+    r = synth.activations(1234, f"lsilu.r{m}", m, N).astype(np.float32) * 4.0
+    gd, ud, td, sd, vd = dev(g), dev(u), dev(w["trellis"]), dev(w["suh"]), dev(w["svh"])
+    rd = torch.from_numpy(r).cuda()
+    out = OutDtype.F32 if res else OutDtype.F16
+    odt = torch.float32 if res else torch.float16
+    act = torch.empty((m, K), dtype=torch.float16, device="cuda")
+    kernels.ops.silu_mul(gd, ud, act, m * K, limit)
+    ah0 = torch.zeros((m, K), dtype=torch.float16, device="cuda")
+    unfused = torch.empty((m, N), dtype=odt, device="cuda")
+    if res:
+        kernels.exl3_linear_add(act, td, unfused, sd, ah0, vd, rd, m, K, N, bits, Codebook(cb))
+    else:
+        kernels.exl3_linear(act, td, unfused, sd, ah0, vd, m, K, N, bits, Codebook(cb), out)
+    ah1 = torch.zeros((m, K), dtype=torch.float16, device="cuda")
+    fused = torch.full((m, N), float("nan"), dtype=odt, device="cuda")
+    kernels.exl3_linear_silu(gd, ud, td, fused, sd, ah1, vd, m, K, N, bits, Codebook(cb), out, limit, rd if res else None)
+    assert "silu(gate) * up in the rotation" in kernels.last_launch()
+    torch.cuda.synchronize()
+    assert kernels.device_status(torch.cuda.current_device()) == 0
+    view = torch.int32 if res else torch.int16
+    assert torch.equal(ah1.view(torch.int16), ah0.view(torch.int16))
+    assert torch.equal(fused.view(view), unfused.view(view))
+    act_o = oracle.silu_mul(g, u, limit)
+    assert np.array_equal(act.cpu().numpy().view(np.uint16), act_o.view(np.uint16))
+    y64 = oracle.linear_f64(act_o, w["trellis"], w["suh"], w["svh"], K, N, bits, cb)
+    got = fused.float().cpu().numpy() - (r if res else 0.0)
+    mx, mean = rel_errors(got, y64)
+    assert mx <= MAX_REL and mean <= MEAN_REL
+
+
+def test_linear_silu_rejects_what_it_cannot_run():
+    z = torch.zeros(4096, dtype=torch.float16, device="cuda")
+    t = torch.zeros((8, 8, 64), dtype=torch.int16, device="cuda")
+    with pytest.raises(kernels.Error, match="size_m must be <= 32"):
+        kernels.exl3_linear_silu(z, z, t, z, z, z, z, 33, 128, 128, 4, Codebook(2), OutDtype.F16)
+    with pytest.raises(kernels.Error, match="residual is added to fp32 outputs only"):
+        kernels.exl3_linear_silu(z, z, t, z, z, z, z, 1, 128, 128, 4, Codebook(2), OutDtype.F16, 0.0, z)
+
+
 def test_small_batch_tensor_path_random_shapes_vs_decode_kernel():
     """Forty seeded random shapes (17..32 rows, every bitrate and codebook, K and N any multiples of 128 large enough for the
     split-K kernel): its outputs against the decode GEMV's (berth_exl3_linear_add with a zero residual always runs that
