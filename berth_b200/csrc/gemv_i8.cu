@@ -182,11 +182,16 @@ __device__ __forceinline__ float quantise_block(uint2 o, int lane, unsigned char
 {
     const __half2 h01 = *reinterpret_cast<const __half2*>(&o.x), h23 = *reinterpret_cast<const __half2*>(&o.y);
     const float hv[4] = {__low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23)};
+    // the block maximum in one warp reduction: non-negative floats order as their bit patterns do; a lane of NaNs counts
+    // as 0 (fmaxf drops NaNs) unless every lane is one
     float amax = fmaxf(fmaxf(fabsf(hv[0]), fabsf(hv[1])), fmaxf(fabsf(hv[2]), fabsf(hv[3])));
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(dq::kFull, amax, off));
-    const float scale = __fdiv_rn(amax, 32512.0f);
-    const float inv = amax > 0.f ? __fdiv_rn(32512.0f, amax) : 0.f;
+    const bool lane_nan = amax != amax;
+    const unsigned top = __reduce_max_sync(dq::kFull, lane_nan ? 0u : __float_as_uint(amax));
+    amax = __all_sync(dq::kFull, lane_nan) ? amax : __uint_as_float(top);
+    // (a multiplication and an approximate division: the scale only has to be the one the sums are multiplied by later,
+    // and |a| * inv stays below 32512.5)
+    const float scale = __fmul_rn(amax, 1.0f / 32512.0f);
+    const float inv = amax > 0.f ? __fdividef(32512.0f, amax) : 0.f;
     isum = 0;
     const int kt = lane >> 2;
 #pragma unroll
@@ -200,8 +205,7 @@ __device__ __forceinline__ float quantise_block(uint2 o, int lane, unsigned char
         *reinterpret_cast<uint32_t*>(w) = uint32_t(hi & 0xff) * 0x01010101u;
         *reinterpret_cast<uint32_t*>(w + 16) = uint32_t(lo & 0xff) * 0x01010101u;
     }
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) isum += __shfl_xor_sync(dq::kFull, isum, off);
+    isum = __reduce_add_sync(dq::kFull, isum);
     return scale;
 }
 
@@ -250,6 +254,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
             pi = 0;
             while (pi + 1 < p.n_stack && gbg >= p.het_bg[pi + 1]) ++pi;
             lbg = gbg - p.het_bg[pi];
+        } else if (gbg < bgroups) {   // (one matrix: no division)
+            pi = 0;
+            lbg = gbg;
         } else {
             pi = gbg / bgroups;
             lbg = gbg - pi * bgroups;
@@ -263,6 +270,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
     }
     const long long u0 = unit_begin(cta, U, G), u1 = unit_begin(cta + 1, U, G);
     const int nunits = int(u1 - u0);
+    const int gbg0 = int(u0 / kblocks), kb0 = int(u0 - (long long) gbg0 * kblocks);   // the CTA's first band group and 128-block
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * S;
     const uint32_t afull0 = empty0 + 8 * S, aempty0 = afull0 + 8 * NA;
     const uint32_t dfull0 = aempty0 + 8 * NA, dempty0 = dfull0 + 16;
@@ -285,9 +293,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
     if (warp == kProducerWarp && lane == 0) {
         for (int s = 0; s < S; ++s) mbar_init(full0 + 8 * s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        const int gbg = int(u0 / kblocks);
-        pr_kb = int(u0 - (long long) gbg * kblocks);
-        split_bg(gbg, pr_pi, pr_lbg);
+        pr_kb = kb0;
+        split_bg(gbg0, pr_pi, pr_lbg);
         asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.m[p.het ? pr_pi : 0]) : "memory");
         if (p.defer_weights) pdl_wait();   // the caller may have written the weights just before this launch
         for (int i = 0; i < pre; ++i) {
@@ -331,9 +338,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
                 pdl_wait();   // the activations come from the preceding kernels
                 const int w20 = warp;   // decode warps 0..15, epilogue warps 16..19
                 for (int task = w20; task < nunits * p.m; task += kDecodeWarps + kEpiWarps) {
-                    const int j = task / p.m, t = task - j * p.m;
-                    const long long uu = u0 + j;
-                    const int gbg = int(uu / kblocks), kb = int(uu - (long long) gbg * kblocks);
+                    const int j = p.m == 1 ? task : task / p.m, t = task - j * p.m;
+                    int gbg = gbg0, kb = kb0 + j;   // unit u0 + j of the launch: no 64-bit division per task
+                    if (kb >= kblocks) {
+                        const int dg = kb >= 2 * kblocks ? kb / kblocks : 1;
+                        gbg += dg;
+                        kb -= dg * kblocks;
+                    }
                     int pi, lbg;   // matrix of the stack, band group inside it
                     split_bg(gbg, pi, lbg);
                     float sx;
@@ -600,14 +611,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
                 const int first_cta = unit_owner(g0, U, G), last_cta = unit_owner(g0 + kblocks - 1, U, G);
                 epi_sync();
                 if (et == 0) {
-                    __threadfence();
-                    const unsigned arrived = atomicAdd(p.counters + sg.bg, 1u) + 1u;
-                    s_last = arrived == unsigned(last_cta - first_cta + 1);
+                    // release: the slab stores of the 128 threads, ordered before this by the barrier; acquire: the slabs of
+                    // the CTAs that arrived earlier, handed on to the other threads by the next barrier
+                    unsigned old;
+                    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + sg.bg) : "memory");
+                    s_last = old + 1u == unsigned(last_cta - first_cta + 1);
                     if (s_last) p.counters[sg.bg] = 0u;   // ready for the next launch
                 }
                 epi_sync();
                 if (s_last) {
-                    __threadfence();
                     const int first_slab = unit_begin(first_cta, U, G) >= g0 ? 2 * first_cta : 2 * first_cta + 1;
 #pragma unroll
                     for (int q = 0; q < kTasksPerWarp; ++q) {
