@@ -279,6 +279,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
     // and issues the first stages' TMA copies before anything else in the CTA happens.
     int pr_pi = 0, pr_lbg = 0, pr_kb = 0;   // producer lane: matrix, band group and 128-block of the next unit to fetch
     const int pre = nunits < S ? nunits : S;
+    // FUSED: the first kPre0 stages are requested before the CTA's set-up barrier, the rest of the first lap right after it
+    // (a CTA that starts when its predecessor's last CTAs leave has this set-up on its critical path)
+    constexpr int kPre0 = FUSED ? 4 : S;
+    const int pre0 = pre < kPre0 ? pre : kPre0;
     constexpr uint32_t kStageTx = FUSED ? W_BYTES : STAGE_BYTES;
     auto issue_weights = [&](uint32_t dst, uint32_t bar) {
         const int z = p.problems ? load_problem(p.problems, pr_pi, p.n_matrices, TOK, p.max_rows).z : (p.het ? 0 : pr_pi);
@@ -297,7 +301,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
         split_bg(gbg0, pr_pi, pr_lbg);
         asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.m[p.het ? pr_pi : 0]) : "memory");
         if (p.defer_weights) pdl_wait();   // the caller may have written the weights just before this launch
-        for (int i = 0; i < pre; ++i) {
+        for (int i = 0; i < pre0; ++i) {
             mbar_arrive_expect_tx(full0 + 8 * i, kStageTx);
             issue_weights(smem_u32(ring + i * STAGE_BYTES), full0 + 8 * i);
             if (FUSED || i + 1 < pre) next_unit();   // (the limb tiles of these stages follow below, from the same coordinates)
@@ -373,6 +377,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
             auto issue_limbs = [&](int pi, int kb, uint32_t dst, uint32_t bar) {
                 bulk_load_1d(dst, reinterpret_cast<const unsigned char*>(p.afrag) + (size_t(pi) * kblocks + kb) * B_BYTES, B_BYTES, bar);
             };
+            for (int i = pre0; i < pre; ++i) {   // FUSED: the rest of the first lap
+                mbar_arrive_expect_tx(full0 + 8 * i, kStageTx);
+                issue_weights(smem_u32(ring + i * STAGE_BYTES), full0 + 8 * i);
+                next_unit();
+            }
             pdl_wait();
             if constexpr (!FUSED) {
                 // the limb tiles of the stages whose weights are already on their way: replay the coordinates from u0
@@ -449,6 +458,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_const
                 }
                 pending = a_idx;
                 if (++a_idx == NA) { a_idx = 0; a_par ^= 1; }
+                if (i == 0 && h == 0) hand_over();   // the launch's first stage: the MMA warp is waiting for it
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * s);   // every word of the ring stage has been read
