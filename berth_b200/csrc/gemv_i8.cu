@@ -136,12 +136,14 @@ __device__ __forceinline__ void tc_st_tile(uint32_t taddr, const uint32_t (&x)[8
                  : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-// 32 lanes x N consecutive 32-bit columns (N = 8, 16 or 32) of this warp's TMEM lane quarter; no wait.
+// 32 lanes x N consecutive 32-bit columns (N = 2, 8, 16 or 32) of this warp's TMEM lane quarter; no wait.
 template <int N>
 __device__ __forceinline__ void tc_ld(uint32_t taddr, int* r)
 {
-    static_assert(N == 8 || N == 16 || N == 32, "tcgen05.ld width");
-    if constexpr (N == 8) {
+    static_assert(N == 2 || N == 8 || N == 16 || N == 32, "tcgen05.ld width");
+    if constexpr (N == 2) {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(taddr));
+    } else if constexpr (N == 8) {
         asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                      : "r"(taddr));
@@ -222,13 +224,16 @@ struct I8Maps {
     CUtensorMap m[kMaxHetMatrices];
 };
 
-template <int BITS, int NB, bool FUSED>
+// ONE: the launch has one row (the epilogue warps then read two accumulator columns per band instead of eight and keep one
+// row's sums: they share their schedulers with the decode warps).
+template <int BITS, int NB, bool FUSED, bool ONE>
 __global__ void __launch_bounds__(kThreads, 1) k_exl3_gemv_i8(const __grid_constant__ I8Maps maps, const GemvArgs p)
 {
     static_assert(!FUSED || NB == 1, "in-kernel rotation is built for one group of four rows");
+    static_assert(!ONE || FUSED, "the one-row form exists for the in-kernel rotation only");
     using G_ = GeoI8<BITS, NB, FUSED>;
     constexpr int NW = G_::NW, BU = G_::BU, ROW_BYTES = G_::ROW_BYTES, W_BYTES = G_::W_BYTES, B_BYTES = G_::B_BYTES;
-    constexpr int STAGE_BYTES = G_::STAGE_BYTES, S = G_::S, NA = G_::NA, TOK = G_::TOK, NCOL = G_::NCOL, PITCH = G_::PITCH;
+    constexpr int STAGE_BYTES = G_::STAGE_BYTES, S = G_::S, NA = G_::NA, TOK = ONE ? 1 : G_::TOK, NCOL = G_::NCOL, PITCH = G_::PITCH;
     constexpr int CHUNK_BYTES = G_::CHUNK_BYTES, A_STAGE_COLS = G_::A_STAGE_COLS, D_COLS = G_::D_COLS;
 
     extern __shared__ unsigned char smem_raw[];
@@ -714,11 +719,11 @@ int fused_max_units(int k_bits, int rows)
     }
 }
 
-template <int BITS, int NB, bool FUSED>
+template <int BITS, int NB, bool FUSED, bool ONE = false>
 size_t launch_one(const void* const* trellis, int n_matrices, const GemvArgs& args, int grid, cudaStream_t stream)
 {
     using G_ = GeoI8<BITS, NB, FUSED>;
-    auto kern = k_exl3_gemv_i8<BITS, NB, FUSED>;
+    auto kern = k_exl3_gemv_i8<BITS, NB, FUSED, ONE>;
     static bool attr_set[kMaxDevices] = {};
     const int dev = current_device();
     if (!attr_set[dev]) {
@@ -743,7 +748,9 @@ template <int BITS>
 size_t launch_nb(int nb, bool fused, const void* const* t, int nm, const GemvArgs& a, int grid, cudaStream_t st)
 {
     switch (nb) {
-        case 1: return fused ? launch_one<BITS, 1, true>(t, nm, a, grid, st) : launch_one<BITS, 1, false>(t, nm, a, grid, st);
+        case 1:
+            if (fused) return a.m == 1 ? launch_one<BITS, 1, true, true>(t, nm, a, grid, st) : launch_one<BITS, 1, true>(t, nm, a, grid, st);
+            return launch_one<BITS, 1, false>(t, nm, a, grid, st);
         default: return launch_one<BITS, 2, false>(t, nm, a, grid, st);
     }
 }
