@@ -222,6 +222,21 @@ def test_linear_add_and_stack_argument_checks(lib):
         kernels.exl3_linear_stack(P, P, P, P, P, P, 2, 9, 128, 128, 4, Codebook.Mul1, OutDtype.F16)
 
 
+def test_linear_silu_argument_checks(lib):
+    """berth_exl3_linear_silu refuses on the host, before any CUDA call: a missing gate or up, more rows than the decode
+    kernels take, a residual with fp16 output, and the shapes berth_exl3_linear refuses."""
+    with pytest.raises(Error, match="null"):
+        kernels.exl3_linear_silu(P, None, P, P, P, P, P, 1, 128, 128, 4, Codebook.Mul1, OutDtype.F32)
+    with pytest.raises(Error, match="size_m must be <= 32"):
+        kernels.exl3_linear_silu(P, P, P, P, P, P, P, 33, 128, 128, 4, Codebook.Mul1, OutDtype.F32)
+    with pytest.raises(Error, match="fp32 outputs only"):
+        kernels.exl3_linear_silu(P, P, P, P, P, P, P, 1, 128, 128, 4, Codebook.Mul1, OutDtype.F16, 0.0, P)
+    with pytest.raises(Error, match="multiple of 128"):
+        kernels.exl3_linear_silu(P, P, P, P, P, P, P, 1, 128, 100, 4, Codebook.Mul1, OutDtype.F32)
+    with pytest.raises(Error, match="K must be in 1..=8"):
+        kernels.exl3_linear_silu(P, P, P, P, P, P, P, 1, 128, 128, 9, Codebook.Mul1, OutDtype.F32)
+
+
 def test_weights_streamed_switch_returns_the_previous_setting(lib):
     assert lib.berth_exl3_weights_streamed(1) == 0
     assert lib.berth_exl3_weights_streamed(1) == 1
